@@ -1,0 +1,293 @@
+"""ctypes front-end of the CPU checker (``libsynaptik_oracle.so``).
+
+Test infrastructure only: the test-suite, the smoke check and the benchmark's CPU-baseline leg
+import this module; the product package never does.  Each function forwards to the C
+restatement in ``synaptik_oracle.c`` (where the reference file:line each follows is cited) and
+returns fresh numpy arrays.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libsynaptik_oracle.so")
+_lib = None
+
+_f32p = ctypes.POINTER(ctypes.c_float)
+_i64p = ctypes.POINTER(ctypes.c_int64)
+_i32p = ctypes.POINTER(ctypes.c_int32)
+
+
+def build(force: bool = False) -> str:
+    """Compile the checker with the Makefile beside it (gcc only) and return the library path."""
+    sources = [os.path.join(_HERE, n) for n in ("synaptik_oracle.c", "cpu_baseline.c", "Makefile")]
+    stale = force or not os.path.exists(_LIB_PATH) or any(
+        os.path.getmtime(s) > os.path.getmtime(_LIB_PATH) for s in sources)
+    if stale:
+        subprocess.run(["make", "-s", "-C", _HERE, "-B", "libsynaptik_oracle.so"], check=True)
+    return _LIB_PATH
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            build()
+        _lib = ctypes.CDLL(_LIB_PATH)
+        _lib.syn_oracle_exact_sum_f32.restype = ctypes.c_float
+        _lib.syn_oracle_mse_f32.restype = ctypes.c_float
+        _lib.syn_baseline_mlp_step.restype = ctypes.c_double
+        _lib.syn_baseline_blas_name.restype = ctypes.c_char_p
+    return _lib
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _p(a: np.ndarray, t=_f32p):
+    return a.ctypes.data_as(t)
+
+
+def matmul(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """Sequential-K FP32 product of two rank-2 arrays; arbitrary strides (views) are honoured."""
+    assert a.dtype == np.float32 and b.dtype == np.float32 and a.ndim == 2 and b.ndim == 2
+    m, k = a.shape
+    k2, n = b.shape
+    assert k == k2
+    c = np.empty((m, n), dtype=np.float32)
+    lib().syn_oracle_matmul_f32(
+        ctypes.c_int64(m), ctypes.c_int64(n), ctypes.c_int64(k),
+        _p(a), ctypes.c_int64(a.strides[0] // 4), ctypes.c_int64(a.strides[1] // 4),
+        _p(b), ctypes.c_int64(b.strides[0] // 4), ctypes.c_int64(b.strides[1] // 4),
+        _p(c), ctypes.c_int64(n), ctypes.c_int64(1))
+    return c
+
+
+def matmul_rows(a: np.ndarray, b: np.ndarray, rows) -> np.ndarray:
+    """``matmul(a, b)[rows]`` without computing the other rows."""
+    rows = np.ascontiguousarray(rows, dtype=np.int64)
+    m, k = a.shape
+    _, n = b.shape
+    c = np.empty((len(rows), n), dtype=np.float32)
+    lib().syn_oracle_matmul_rows_f32(
+        ctypes.c_int64(len(rows)), _p(rows, _i64p), ctypes.c_int64(n), ctypes.c_int64(k),
+        _p(a), ctypes.c_int64(a.strides[0] // 4), ctypes.c_int64(a.strides[1] // 4),
+        _p(b), ctypes.c_int64(b.strides[0] // 4), ctypes.c_int64(b.strides[1] // 4), _p(c))
+    return c
+
+
+def relu(x) -> np.ndarray:
+    x = _f32(x)
+    y = np.empty_like(x)
+    lib().syn_oracle_relu_f32(ctypes.c_int64(x.size), _p(x), _p(y))
+    return y
+
+
+def bias_act(u, bias, relu_flag: bool):
+    """Returns (z, y): z = u + bias (row broadcast), y = relu(z) or z."""
+    u = _f32(u)
+    m, n = u.shape
+    z = np.empty_like(u)
+    y = np.empty_like(u)
+    b = _f32(bias) if bias is not None else None
+    lib().syn_oracle_bias_act_f32(ctypes.c_int64(m), ctypes.c_int64(n), _p(u),
+                                  _p(b) if b is not None else None, int(relu_flag), _p(z), _p(y))
+    return z, y
+
+
+def linear(x, weight, bias, relu_flag: bool):
+    """``Tensor.linear`` then optional ReLU: x[M,K] . weight[N,K]^T + bias -> (z, y)."""
+    u = matmul(_f32(x), _f32(weight).T)
+    return bias_act(u, bias, relu_flag)
+
+
+def exact_sum(x) -> float:
+    x = _f32(x).ravel()
+    return float(lib().syn_oracle_exact_sum_f32(ctypes.c_int64(x.size), _p(x), ctypes.c_int64(1)))
+
+
+def colsum_exact(g) -> np.ndarray:
+    g = _f32(g)
+    m, n = g.shape
+    out = np.empty(n, dtype=np.float32)
+    lib().syn_oracle_colsum_exact_f32(ctypes.c_int64(m), ctypes.c_int64(n), _p(g), _p(out))
+    return out
+
+
+def softmax(x) -> np.ndarray:
+    x = _f32(x)
+    rows, classes = x.shape
+    out = np.empty_like(x)
+    lib().syn_oracle_softmax_f32(ctypes.c_int64(rows), ctypes.c_int64(classes), _p(x), _p(out))
+    return out
+
+
+def index_cross_entropy(logits, labels):
+    """Returns (per_row, mean).  Raises ValueError for an out-of-range label."""
+    logits = _f32(logits)
+    labels = np.ascontiguousarray(labels, dtype=np.int64)
+    rows, classes = logits.shape
+    per_row = np.empty(rows, dtype=np.float32)
+    mean = ctypes.c_float(0.0)
+    status = lib().syn_oracle_index_ce_f32(ctypes.c_int64(rows), ctypes.c_int64(classes),
+                                           _p(logits), _p(labels, _i64p), _p(per_row),
+                                           ctypes.byref(mean))
+    if status:
+        raise ValueError("index target out of bounds")
+    return per_row, np.float32(mean.value)
+
+
+def index_cross_entropy_backward(logits, labels, seed: float = 1.0, count: int = 0) -> np.ndarray:
+    logits = _f32(logits)
+    labels = np.ascontiguousarray(labels, dtype=np.int64)
+    rows, classes = logits.shape
+    out = np.empty_like(logits)
+    lib().syn_oracle_index_ce_backward_f32(ctypes.c_int64(rows), ctypes.c_int64(classes),
+                                           _p(logits), _p(labels, _i64p), ctypes.c_float(seed),
+                                           ctypes.c_int64(count), _p(out))
+    return out
+
+
+def mse(prediction, target) -> np.float32:
+    p, t = _f32(prediction).ravel(), _f32(target).ravel()
+    return np.float32(lib().syn_oracle_mse_f32(ctypes.c_int64(p.size), _p(p), _p(t)))
+
+
+def mse_backward(prediction, target, seed: float = 1.0, count: int = 0) -> np.ndarray:
+    p, t = _f32(prediction), _f32(target)
+    out = np.empty_like(p)
+    lib().syn_oracle_mse_backward_f32(ctypes.c_int64(p.size), _p(p), _p(t), ctypes.c_float(seed),
+                                      ctypes.c_int64(count), _p(out))
+    return out
+
+
+def relu_backward(z, g) -> np.ndarray:
+    z, g = _f32(z), _f32(g)
+    out = np.empty_like(g)
+    lib().syn_oracle_relu_backward_f32(ctypes.c_int64(z.size), _p(z), _p(g), _p(out))
+    return out
+
+
+def argmax(x) -> np.ndarray:
+    x = _f32(x)
+    rows, classes = x.shape
+    out = np.empty(rows, dtype=np.int64)
+    lib().syn_oracle_argmax_f32(ctypes.c_int64(rows), ctypes.c_int64(classes), _p(x), _p(out, _i64p))
+    return out
+
+
+def sgd(parameter, gradient, momentum_buffer=None, lr=0.01, momentum=0.0, dampening=0.0,
+        weight_decay=0.0, nesterov=False, completed_steps=0):
+    """In-place on float32 arrays; returns True when the update committed (all finite)."""
+    assert parameter.dtype == np.float32 and parameter.flags.c_contiguous
+    g = _f32(gradient)
+    status = lib().syn_oracle_sgd_f32(
+        ctypes.c_int64(parameter.size), _p(parameter), _p(g),
+        _p(momentum_buffer) if momentum_buffer is not None else None,
+        ctypes.c_double(lr), ctypes.c_double(momentum), ctypes.c_double(dampening),
+        ctypes.c_double(weight_decay), int(nesterov), ctypes.c_int64(completed_steps))
+    return status == 0
+
+
+def adam(parameter, gradient, first, second, step, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8,
+         weight_decay=0.0, decoupled=False):
+    """In-place Adam/AdamW on float32 arrays; ``step`` counts from 1.  True when committed."""
+    for a in (parameter, first, second):
+        assert a.dtype == np.float32 and a.flags.c_contiguous
+    g = _f32(gradient)
+    status = lib().syn_oracle_adam_f32(
+        ctypes.c_int64(parameter.size), _p(parameter), _p(g), _p(first), _p(second),
+        ctypes.c_double(lr), ctypes.c_double(beta1), ctypes.c_double(beta2), ctypes.c_double(eps),
+        ctypes.c_double(weight_decay), int(decoupled), ctypes.c_int64(step))
+    return status == 0
+
+
+# --------------------------------------------------------------------------------------------
+# Composite: the training graph the backend is handed (forward, loss, backward), op by op.
+# --------------------------------------------------------------------------------------------
+def mlp_forward(x, weights, biases):
+    """Returns the list of post-activation values [a1..aL] (aL = logits, no ReLU)."""
+    acts = []
+    a = _f32(x)
+    for index, (w, b) in enumerate(zip(weights, biases)):
+        _, a = linear(a, w, b, relu_flag=index + 1 < len(weights))
+        acts.append(a)
+    return acts
+
+
+def mlp_gradients(x, labels_or_target, weights, biases, loss: str = "ce", count: int = 0):
+    """Loss and gradients of an MLP, executing the reference's backward node lists in order.
+
+    Returns (loss, [dW1, db1, dW2, db2, ...], logits).  ``loss`` is "ce" (index cross entropy,
+    MEAN) or "mse" (MEAN).  ``count`` overrides the divisor of the loss gradient.
+    """
+    x = _f32(x)
+    acts = mlp_forward(x, weights, biases)
+    logits = acts[-1]
+    if loss == "ce":
+        _, value = index_cross_entropy(logits, labels_or_target)
+        dz = index_cross_entropy_backward(logits, labels_or_target, 1.0, count)
+    else:
+        value = mse(logits, labels_or_target)
+        dz = mse_backward(logits, _f32(labels_or_target).reshape(logits.shape), 1.0, count)
+    grads = [None] * (2 * len(weights))
+    for index in range(len(weights) - 1, -1, -1):
+        a_prev = x if index == 0 else acts[index - 1]
+        grads[2 * index + 1] = colsum_exact(dz)
+        # dWt[K,N] = PERMUTE(a_prev)[K,M] . dz[M,N]; PERMUTE back gives dW[N,K]
+        grads[2 * index] = np.ascontiguousarray(matmul(a_prev.T, dz).T)
+        if index > 0:
+            da = matmul(dz, _f32(weights[index]))
+            # z > 0 <=> relu(z) > 0 for every binary32 value, so the stored activation serves
+            dz = relu_backward(a_prev, da)
+    return value, grads, logits
+
+
+# --------------------------------------------------------------------------------------------
+# Timed CPU baseline (cpu_baseline.c)
+# --------------------------------------------------------------------------------------------
+def baseline_bind_openblas() -> str:
+    """Binds an OpenBLAS the way the reference discovers one; returns the name used."""
+    explicit = os.environ.get("SYNAPTIK_OPENBLAS", "")
+    if not explicit:
+        try:
+            import glob
+            import site
+            for root in site.getsitepackages():
+                found = sorted(glob.glob(os.path.join(root, "opencv_python_headless.libs",
+                                                      "libopenblas*.so")))
+                if found:
+                    explicit = found[0]
+                    break
+        except Exception:
+            explicit = ""
+    lib().syn_baseline_bind_openblas(explicit.encode())
+    return lib().syn_baseline_blas_name().decode()
+
+
+def baseline_mlp_step(dims, x, labels, weights, biases, m1, m2, train=True, count_total=0,
+                      adam_step=1, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, threads=1,
+                      want_logits=False):
+    """Runs one CPU MLP step in place on the given float32 arrays; returns (seconds, loss, logits)."""
+    layers = len(dims) - 1
+    rows = x.shape[0]
+    lib().syn_baseline_set_threads(int(threads))
+    dims_c = (ctypes.c_int * (layers + 1))(*dims)
+    w_c = (_f32p * layers)(*[_p(w) for w in weights])
+    b_c = (_f32p * layers)(*[_p(b) for b in biases])
+    m1_c = (_f32p * (2 * layers))(*[_p(a) for a in m1]) if train else None
+    m2_c = (_f32p * (2 * layers))(*[_p(a) for a in m2]) if train else None
+    loss = ctypes.c_float(0.0)
+    logits = np.empty((rows, dims[-1]), dtype=np.float32) if want_logits else None
+    lab = np.ascontiguousarray(labels, dtype=np.int32) if labels is not None else None
+    seconds = lib().syn_baseline_mlp_step(
+        layers, dims_c, rows, _p(x), _p(lab, _i32p) if lab is not None else None, w_c, b_c,
+        m1_c, m2_c, int(train), ctypes.c_int64(count_total or rows), ctypes.c_int64(adam_step),
+        ctypes.c_double(lr), ctypes.c_double(beta1), ctypes.c_double(beta2), ctypes.c_double(eps),
+        ctypes.byref(loss), _p(logits) if logits is not None else None)
+    return seconds, np.float32(loss.value), logits

@@ -1,0 +1,221 @@
+"""Pins the CPU checker against the reference's own known-answer tests (no GPU needed)."""
+import json
+import math
+import os
+
+import numpy as np
+
+GOLDEN = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_known_answers.json")))
+
+
+def _vals(seq):
+    return np.array([float(v) for v in seq], dtype=np.float32)
+
+
+def test_matmul_integer_known_answers(oracle):
+    for key in ("matmul_int_2x3x2", "matmul_qualifier_smoke"):
+        g = GOLDEN[key]
+        a = np.array(g["a"], dtype=np.float32)
+        b = np.array(g["b"], dtype=np.float32)
+        assert np.array_equal(oracle.matmul(a, b), np.array(g["c"], dtype=np.float32)), key
+    # transposed-output form of the same product (CpuOpenBlasRouteConformanceTest.java:315)
+    g = GOLDEN["matmul_int_2x3x2"]
+    a = np.array(g["a"], dtype=np.float32)
+    b = np.array(g["b"], dtype=np.float32)
+    assert np.array_equal(oracle.matmul(b.T, a.T).ravel(), np.array([58, 139, 64, 154], dtype=np.float32))
+
+
+def test_matmul_mod5_exact_and_views(oracle):
+    g = GOLDEN["matmul_mod5"]
+    m, k, n = g["m"], g["k"], g["n"]
+    a = (np.arange(m * k) % 5 - 2).astype(np.float32).reshape(m, k)
+    b = (np.arange(k * n) % 5 - 2).astype(np.float32).reshape(k, n)
+    expect = (a.astype(np.int64) @ b.astype(np.int64)).astype(np.float32)
+    assert np.array_equal(oracle.matmul(a, b), expect)
+    # a permuted (strided) right operand, as Linear hands W[N,K] to MATMUL as a [K,N] view
+    w = np.ascontiguousarray(b.T)
+    assert np.array_equal(oracle.matmul(a, w.T), expect)
+    # K == 1 is a single product
+    assert np.array_equal(oracle.matmul(a[:, :1], b[:1, :]), a[:, :1] * b[:1, :])
+
+
+def test_matmul_is_sequential_not_pairwise(oracle):
+    # 1e8 + 1 - 1e8 in ascending k order: the 1 is absorbed; a pairwise or FMA tree would differ
+    a = np.array([[1e8, 1.0, -1e8]], dtype=np.float32)
+    b = np.ones((3, 1), dtype=np.float32)
+    assert oracle.matmul(a, b)[0, 0] == 0.0
+
+
+def test_softmax_known_answers(oracle):
+    g = GOLDEN["softmax_123"]
+    p = oracle.softmax(_vals(g["x"])[None, :])[0]
+    assert np.allclose(p, _vals(g["p"]), atol=g["tol"], rtol=0)
+    assert np.array_equal(oracle.softmax(_vals(GOLDEN["softmax_1000_1000"]["x"])[None, :])[0], _vals([0.5, 0.5]))
+    p = oracle.softmax(_vals(GOLDEN["softmax_neginf_1000"]["x"])[None, :])[0]
+    assert p[0] == 0.0 and not np.signbit(p[0]) and math.isnan(p[1])
+    assert np.array_equal(oracle.softmax(_vals(GOLDEN["softmax_0_m1000"]["x"])[None, :])[0], _vals([1.0, 0.0]))
+    p = oracle.softmax(_vals(["inf", 1.0, "inf"])[None, :])[0]
+    assert math.isnan(p[0]) and p[1] == 0.0 and math.isnan(p[2])
+
+
+def test_relu_special_values(oracle):
+    y = oracle.relu(_vals([-1.0, -0.0, 0.0, 2.5, "-inf", "inf", "nan"]))
+    assert list(y[:6]) == [0.0, 0.0, 0.0, 2.5, 0.0, float("inf")] and math.isnan(y[6])
+    assert not np.signbit(y[1])
+
+
+def test_argmax_rules(oracle):
+    nan = float("nan")
+    rows = np.array([[1, 3, 3, 2], [-0.0, 0.0, 0.0, -0.0], [0.0, -0.0, 0.0, 0.0], [1, nan, 5, nan],
+                     [-np.inf, -np.inf, -np.inf, -np.inf]], dtype=np.float32)
+    assert list(oracle.argmax(rows)) == [1, 1, 0, 1, 0]
+
+
+def test_exact_sum_rounds_once(oracle):
+    # 2^24 + 1 + 1: sequential float addition loses both ones, the exact sum keeps them
+    x = np.array([16777216.0, 1.0, 1.0], dtype=np.float32)
+    assert oracle.exact_sum(x) == 16777218.0
+    rng = np.random.default_rng(7)
+    for scale in (1e-30, 1.0, 1e30):
+        v = (rng.standard_normal(4097) * scale).astype(np.float32)
+        assert oracle.exact_sum(v) == np.float32(math.fsum(float(t) for t in v))
+    tie = np.array([1.0, 2.0 ** -24], dtype=np.float32)           # exact tie rounds to even
+    assert oracle.exact_sum(tie) == 1.0
+    assert oracle.exact_sum(np.array([1.0, 2.0 ** -24, 2.0 ** -40], dtype=np.float32)) == np.float32(1.0 + 2.0 ** -23)
+    assert oracle.exact_sum(np.array([1e-45, -1e-45, 3e-45], dtype=np.float32)) == np.float32(3e-45)
+    assert math.isnan(oracle.exact_sum(np.array([np.inf, -np.inf], dtype=np.float32)))
+
+
+def test_index_cross_entropy_and_label_check(oracle):
+    logits = np.array([[1.0, 2.0, 3.0], [0.0, 0.0, 0.0]], dtype=np.float32)
+    per_row, mean = oracle.index_cross_entropy(logits, [2, 0])
+    assert abs(per_row[0] - (-math.log(0.66524096))) < 1e-6
+    assert abs(per_row[1] - math.log(3.0)) < 1e-6
+    assert mean == np.float32((per_row[0] + per_row[1]) / np.float32(2))
+    try:
+        oracle.index_cross_entropy(logits, [3, 0])
+    except ValueError:
+        pass
+    else:
+        raise AssertionError("out-of-range label must be rejected")
+    d = oracle.index_cross_entropy_backward(logits, [2, 0])
+    p = oracle.softmax(logits)
+    hot = np.array([[0, 0, 1], [1, 0, 0]], dtype=np.float32)
+    assert np.allclose(d, (p - hot) / 2, atol=1e-7)
+    assert abs(float(d.sum())) < 1e-6
+
+
+def test_mse_exact_count_quotient(oracle):
+    p = np.array([1.0, 2.0, 4.0], dtype=np.float32)
+    t = np.array([0.0, 0.0, 0.0], dtype=np.float32)
+    assert oracle.mse(p, t) == np.float32(21.0 / 3.0)
+    assert oracle.mse(p[:3] * 0 + 1, t) == np.float32(1.0)
+    one_third = oracle.mse(np.array([1.0, 0.0, 0.0], dtype=np.float32), t)
+    assert one_third == np.float32(1.0 / 3.0)
+    assert np.array_equal(oracle.mse_backward(p, t), (p * 2) * np.float32(np.float32(1.0) / np.float32(3.0)))
+
+
+def test_sgd_scalar_training_trace(oracle):
+    g = GOLDEN["sgd_scalar_trace"]
+    w = np.array([g["w0"]], dtype=np.float32)
+    for step, s in enumerate(g["steps"]):
+        error = np.float32(w[0] * np.float32(s["x"]) - np.float32(s["t"]))
+        loss = np.float32(error * error)
+        assert abs(loss - s["loss"]) <= g["tol"]
+        grad = np.array([np.float32(2) * error * np.float32(s["x"])], dtype=np.float32)
+        assert oracle.sgd(w, grad, lr=g["lr"], completed_steps=step)
+        assert abs(w[0] - s["w_after"]) <= g["tol"]
+
+
+def test_one_linear_model_journey(oracle):
+    g = GOLDEN["one_linear_model"]
+    w = np.array([[g["w0"]]], dtype=np.float32)
+    x3 = np.array([[3.0]], dtype=np.float32)
+    assert oracle.matmul(x3, w.T)[0, 0] == g["compute_3"]
+    for key, probe, expect in (("train_1", 2.0, g["compute_2_after"]), ("train_2", 4.0, g["compute_4_after"])):
+        s = g[key]
+        x = np.array([[s["x"]]], dtype=np.float32)
+        pred = oracle.matmul(x, w.T)
+        error = pred - np.float32(s["t"])
+        assert abs(float((error * error).sum()) - s["loss"]) <= g["tol"]
+        dw = oracle.matmul((np.float32(2) * error).T, x)
+        flat = w.reshape(-1)
+        assert oracle.sgd(flat, dw.reshape(-1), lr=0.1)
+        assert abs(oracle.matmul(np.array([[probe]], dtype=np.float32), w.T)[0, 0] - expect) <= g["tol"]
+
+
+def test_adam_tracks_the_reference_double_oracle(oracle):
+    g = GOLDEN["adam_oracle_3_steps"]
+    for decoupled in (False, True):
+        p = np.array([g["p0"]], dtype=np.float32)
+        m = np.zeros(1, dtype=np.float32)
+        v = np.zeros(1, dtype=np.float32)
+        o_first = o_second = 0.0
+        for step in range(1, 4):
+            represented = float(p[0])
+            published = 2.0 * represented
+            grad = np.array([np.float32(2) * p[0]], dtype=np.float32)
+            assert oracle.adam(p, grad, m, v, step, lr=g["lr"], beta1=g["beta1"], beta2=g["beta2"],
+                               eps=g["eps"], weight_decay=g["weight_decay"], decoupled=decoupled)
+            gradient = published if decoupled else published + 0.2 * represented
+            o_first = 0.5 * o_first + 0.5 * gradient
+            o_second = 0.25 * o_second + 0.75 * gradient * gradient
+            c_first = o_first / (1.0 - 0.5 ** step)
+            c_second = o_second / (1.0 - 0.25 ** step)
+            base = represented * (1.0 - 0.1 * 0.2) if decoupled else represented
+            o_parameter = base - 0.1 * c_first / (math.sqrt(c_second) + 0.01)
+            assert abs(p[0] - o_parameter) <= g["tol_parameter"]
+            assert abs(m[0] - o_first) <= g["tol_first"]
+            assert abs(v[0] - o_second) <= g["tol_second"]
+
+
+def test_adam_scales_before_dividing(oracle):
+    g = GOLDEN["adam_scale_before_divide"]
+    f = np.float32
+    gradient = f(g["gradient"])
+    rate = f(g["lr"])
+    first_moment = f(0.5) * gradient
+    second_step_moment = f(0.5) * first_moment
+    corrected = second_step_moment / f(0.75)
+    with np.errstate(over="ignore"):
+        assert np.isinf(corrected / rate)
+    update = (rate * corrected) / rate
+    assert np.isfinite(update)
+    for decoupled in (False, True):
+        p = np.array([1.0], dtype=np.float32)
+        m = np.zeros(1, dtype=np.float32)
+        v = np.zeros(1, dtype=np.float32)
+        # step 1: second moment is g*g = inf in binary32 -> the reference rejects?  No: beta2 = 0
+        # gives v = g*g = 1e38 (finite); sqrt = 1e19; update = (lr*g)/(1e19+eps) = lr -> p stays 1.
+        assert oracle.adam(p, np.array([gradient]), m, v, 1, lr=g["lr"], beta1=g["beta1"],
+                           beta2=g["beta2"], eps=g["eps"], decoupled=decoupled)
+        assert p[0] == f(1.0) and m[0] == first_moment and v[0] == gradient * gradient
+        assert oracle.adam(p, np.array([0.0], dtype=np.float32), m, v, 2, lr=g["lr"], beta1=g["beta1"],
+                           beta2=g["beta2"], eps=g["eps"], decoupled=decoupled)
+        assert p[0] == f(1.0) - update and m[0] == second_step_moment and v[0] == 0.0
+
+
+def test_mlp_gradients_match_float64_autodiff(oracle):
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((16, 5)).astype(np.float32)
+    ws = [rng.standard_normal((7, 5)).astype(np.float32) * 0.5, rng.standard_normal((3, 7)).astype(np.float32) * 0.5]
+    bs = [rng.standard_normal(7).astype(np.float32) * 0.1, rng.standard_normal(3).astype(np.float32) * 0.1]
+    labels = rng.integers(0, 3, 16)
+    loss, grads, logits = oracle.mlp_gradients(x, labels, ws, bs, "ce")
+    # independent float64 evaluation
+    x64 = x.astype(np.float64)
+    z1 = x64 @ ws[0].T.astype(np.float64) + bs[0]
+    a1 = np.maximum(z1, 0)
+    z2 = a1 @ ws[1].T.astype(np.float64) + bs[1]
+    e = np.exp(z2 - z2.max(1, keepdims=True))
+    p = e / e.sum(1, keepdims=True)
+    ref_loss = -np.log(p[np.arange(16), labels]).mean()
+    d2 = p.copy()
+    d2[np.arange(16), labels] -= 1
+    d2 /= 16
+    dw2, db2 = d2.T @ a1, d2.sum(0)
+    d1 = (d2 @ ws[1].astype(np.float64)) * (z1 > 0)
+    dw1, db1 = d1.T @ x64, d1.sum(0)
+    assert abs(loss - ref_loss) < 1e-6
+    for got, ref in zip(grads, (dw1, db1, dw2, db2)):
+        assert np.allclose(got, ref, atol=2e-6, rtol=1e-5)
