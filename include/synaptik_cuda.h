@@ -1,0 +1,189 @@
+/*
+ * libsynaptik_cuda.so -- C ABI of the B200 (sm_100a) CUDA backend for Synaptik.
+ *
+ * The shape follows the one native boundary the reference ships, the Metal foundation library
+ * ("ABI version 7", modules/backend/metal/macos-arm64/README.md: thirteen exported symbols,
+ * opaque void* handle families, int32 status returns, created handles through caller-supplied
+ * output cells that stay NULL on failure, unsigned 64-bit sizes and offsets).  A Java binding
+ * reaches these symbols through java.lang.foreign downcalls exactly as
+ * modules/backend/metal/.../MetalNativeApi.java:3648-3708 binds the Metal ones.
+ *
+ * Every function except synaptik_cuda_abi_version returns a status (0 = success).  No function
+ * aborts the process, resets a device, or falls back to a CPU implementation: without a usable
+ * CUDA device context_create returns SYNAPTIK_CUDA_STATUS_NO_DEVICE and nothing else can run.
+ * Entry points are thread-safe per handle; work is issued on the owning context's stream and
+ * every call that hands results to the host returns only after they are usable.
+ */
+#ifndef SYNAPTIK_CUDA_H
+#define SYNAPTIK_CUDA_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SYNAPTIK_CUDA_ABI_VERSION 1u
+
+#if defined(__GNUC__)
+#define SYNAPTIK_CUDA_API __attribute__((visibility("default")))
+#else
+#define SYNAPTIK_CUDA_API
+#endif
+
+/* Status values 0..13 keep the numeric meaning of the Metal library's table
+ * (modules/backend/metal/macos-arm64/README.md, "Status values"); 14 and 15 are new. */
+enum {
+    SYNAPTIK_CUDA_STATUS_OK = 0,
+    SYNAPTIK_CUDA_STATUS_INVALID_ARGUMENT = 1,
+    SYNAPTIK_CUDA_STATUS_NO_DEVICE = 2,
+    SYNAPTIK_CUDA_STATUS_NO_STREAM = 3,            /* Metal: NO_COMMAND_QUEUE */
+    SYNAPTIK_CUDA_STATUS_ALLOCATION_FAILED = 4,
+    SYNAPTIK_CUDA_STATUS_RANGE_OUT_OF_BOUNDS = 5,  /* copy outside a buffer, or a label outside [0, classes) */
+    SYNAPTIK_CUDA_STATUS_COPY_FAILED = 6,
+    SYNAPTIK_CUDA_STATUS_INTERNAL_ERROR = 7,
+    SYNAPTIK_CUDA_STATUS_UNSUPPORTED_SHAPE = 8,
+    SYNAPTIK_CUDA_STATUS_GRAPH_COMPILATION_FAILED = 9,  /* malformed program image */
+    SYNAPTIK_CUDA_STATUS_INCOMPATIBLE_RESOURCE = 10,    /* wrong context, wrong extent, aliasing */
+    SYNAPTIK_CUDA_STATUS_EXECUTION_FAILED = 11,         /* CUDA error, or a non-finite optimizer intermediate */
+    SYNAPTIK_CUDA_STATUS_KERNEL_COMPILATION_FAILED = 12,
+    SYNAPTIK_CUDA_STATUS_UNSUPPORTED_OPERATION = 13,    /* valid image, operation outside capability */
+    SYNAPTIK_CUDA_STATUS_TIMEOUT = 14,                  /* a bounded device-side wait expired */
+    SYNAPTIK_CUDA_STATUS_COMM_FAILED = 15               /* NCCL unavailable or a collective failed */
+};
+
+/* Replaces synaptik_metal_foundation_abi_version (README.md "ABI version 7"); the Java side
+ * probes it first and refuses a mismatch (MetalNativeApi.java:3648-3708). */
+SYNAPTIK_CUDA_API uint32_t synaptik_cuda_abi_version(void);
+
+/* ---- context: replaces synaptik_metal_context_create / _release ------------------------------
+ * One context per GPU ordinal: a compute stream, a communication stream and the scratch arena
+ * of the tensor-core GEMM path.  (MetalDeviceContext.java:123-216 is the Java owner.) */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_create(int32_t device_ordinal, void **out_context);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_release(void *context);
+/* Named integer options.  "gemm_engine": 0 = automatic (tensor cores for large products, exact
+ * sequential CUDA-core kernel for small ones), 1 = always the exact CUDA-core kernel,
+ * 2 = tensor cores whenever the shape allows.  "time_steps": 1 = bracket every step of later runs
+ * with CUDA events (see synaptik_cuda_executable_step_timings).  Unknown names return
+ * INVALID_ARGUMENT. */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_set_option(void *context, const char *name, int64_t value);
+/* Blocks until all work issued on the context has finished. */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_synchronize(void *context);
+/* CUDA-event stopwatch on the context's compute stream (the stream every kernel of the context is
+ * launched on): start records an event, stop records another, waits for it and returns the device
+ * time between the two in milliseconds. */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_timer_start(void *context);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_timer_stop(void *context, double *out_milliseconds);
+
+/* ---- buffers: replace synaptik_metal_buffer_create / _release / _upload / _download ----------
+ * Device-resident linear memory.  upload/download move raw little-endian element bytes and
+ * return when the copy is complete; the *_canonical forms take or produce the engine's
+ * canonical BIG-ENDIAN element bytes (modules/model/.../HostTensorValue.java:108-110,
+ * EngineBackendComposition.copyToCanonicalHostBytes :153) by swapping element_bytes-wide
+ * groups on the host side of the copy (element_bytes in {1,2,4,8}). */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_buffer_create(void *context, uint64_t bytes, void **out_buffer);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_buffer_release(void *buffer);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_buffer_upload(void *buffer, uint64_t offset, const void *source, uint64_t bytes);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_buffer_download(void *buffer, uint64_t offset, void *destination, uint64_t bytes);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_buffer_upload_canonical(void *buffer, uint64_t offset, const void *source,
+                                              uint64_t bytes, uint32_t element_bytes);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_buffer_download_canonical(void *buffer, uint64_t offset, void *destination,
+                                                uint64_t bytes, uint32_t element_bytes);
+/* Asynchronous forms for callers that keep pinned host memory: they enqueue on the context's
+ * stream and return at once; synaptik_cuda_context_synchronize orders the host after them. */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_buffer_upload_async(void *buffer, uint64_t offset, const void *source, uint64_t bytes);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_buffer_download_async(void *buffer, uint64_t offset, void *destination, uint64_t bytes);
+/* Device address and size of a buffer, for callers that share it with other CUDA code. */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_buffer_device_pointer(void *buffer, uint64_t *out_address, uint64_t *out_bytes);
+/* Page-locked host memory for staging (EngineBackendComposition.borrow :118 uploads from it). */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_host_alloc(uint64_t bytes, void **out_pointer);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_host_free(void *pointer);
+
+/* ---- prepared executables: replace synaptik_metal_mpsgraph_executable_create/_release/_run --
+ * `program` is one little-endian "SCU1" image (layout in synaptik_b200/csrc/program.hpp) that
+ * lists a whole backend partition in topological order: value descriptors (dtype, shape,
+ * element strides, role), nodes (operation wire code, attributes, input and output value
+ * references), the ordered feed values and the ordered publication values.  Creation validates
+ * the image, lowers it to fused kernel launches and reserves every intermediate; it performs no
+ * device work on the hot path.  run binds `input_count` buffers to the feeds and `output_count`
+ * buffers to the publications in image order (the role BoundInvocation.executeBound plays,
+ * modules/runtime/.../execution/PreparedExecutable.java:254,421) and returns when the
+ * publications are complete in device memory. */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_executable_create(void *context, const uint8_t *program, uint32_t program_bytes,
+                                        void **out_executable);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_executable_release(void *executable);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_executable_run(void *executable, int32_t input_count, void *const *inputs,
+                                     int32_t output_count, void *const *outputs);
+/* Same binding, but only enqueues the launches and returns; device-side failures (label range,
+ * bounded-wait expiry) are then reported by the next synaptik_cuda_executable_finish. */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_executable_enqueue(void *executable, int32_t input_count, void *const *inputs,
+                                         int32_t output_count, void *const *outputs);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_executable_finish(void *executable);
+/* Writes a NUL-terminated, line-per-launch description of the lowered plan (kernel, shapes,
+ * engine) into `text`; needs no GPU and is what the host-logic tests read.  With a NULL context
+ * the image is lowered for a default device description.  Returns INVALID_ARGUMENT when
+ * capacity is too small (required size, including the NUL, is stored in *out_required). */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_program_describe(const uint8_t *program, uint32_t program_bytes, char *text,
+                                       uint64_t capacity, uint64_t *out_required);
+/* Device time in milliseconds of the most recent finished run (CUDA events on the context
+ * stream); the hook for trace payloads (modules/trace BackendInvocationOutcome). */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_executable_last_timing(void *executable, double *out_milliseconds);
+/* The plan of this executable (as lowered under its context's options), one line per step, in
+ * the format of synaptik_cuda_program_describe. */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_executable_describe(void *executable, char *text, uint64_t capacity, uint64_t *out_required);
+/* With the context option "time_steps" = 1, every step of a run is bracketed by CUDA events (a
+ * tensor-core GEMM step brackets the GEMM kernel alone, not the operand split).  This call waits
+ * for the most recent run and stores one duration in milliseconds per plan step, in plan order;
+ * the number of steps is stored in *out_count. */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_executable_step_timings(void *executable, double *out_milliseconds, uint64_t capacity,
+                                                              uint64_t *out_count);
+/* Number of kernel launches the most recent run issued. */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_executable_launch_count(void *executable, uint64_t *out_launches);
+
+/* ---- training bridge: device-resident optimizer ----------------------------------------------
+ * Replaces the host loops TrainingParameter.stageUpdate32 (SGD, modules/training/.../
+ * TrainingParameter.java:622-672) and stageAdaptive32 / stageAdaptiveElement32 (Adam, AdamW,
+ * :433-525) with one fused pass over all parameters.  Hyper-parameters arrive as doubles and are
+ * narrowed to binary32 first, as AdaptiveCoefficients.forParameter does (:33-58).  Moments live
+ * in device buffers owned by the optimizer handle.
+ *   kind 0 = SGD   : hyper = {learning_rate, momentum, dampening, weight_decay, nesterov(0/1)}
+ *   kind 1 = Adam  : hyper = {learning_rate, beta1, beta2, epsilon, weight_decay}
+ *   kind 2 = AdamW : same five values, decoupled decay
+ * step applies one update with gradients[i] matching parameters[i] element for element and
+ * returns EXECUTION_FAILED when any intermediate was non-finite (the reference refuses such a
+ * step; here the failing step's writes are not rolled back). */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_create(void *context, int32_t kind, const double *hyper, int32_t hyper_count,
+                                       int32_t parameter_count, void *const *parameters,
+                                       const uint64_t *element_counts, void **out_optimizer);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_release(void *optimizer);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_step(void *optimizer, int32_t gradient_count, void *const *gradients);
+/* Enqueue-only form; the non-finite flag is then reported by synaptik_cuda_optimizer_finish. */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_step_enqueue(void *optimizer, int32_t gradient_count, void *const *gradients);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_finish(void *optimizer);
+/* Completed optimizer steps, and raw little-endian copies of one parameter's moment arrays
+ * (slot 0 = momentum / first moment, 1 = second moment) for TrainingState snapshots
+ * (TrainingParameter.java:894-941). */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_steps(void *optimizer, uint64_t *out_steps);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_download_state(void *optimizer, int32_t parameter_index, int32_t slot,
+                                               void *destination, uint64_t bytes);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_upload_state(void *optimizer, int32_t parameter_index, int32_t slot,
+                                             const void *source, uint64_t bytes, uint64_t completed_steps);
+
+/* ---- data-parallel communicator (no counterpart in the reference, which is single-device) ----
+ * One rank per process and GPU.  unique_id is the 128-byte NCCL id produced by
+ * synaptik_cuda_comm_unique_id on rank 0 and distributed by the caller.  An executable with an
+ * attached communicator sum-allreduces the listed publications (gradients) on the context's
+ * communication stream as soon as each is final, overlapping the rest of the backward pass, and
+ * run/finish return after the reductions. */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_comm_unique_id(uint8_t *out_id128);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_comm_create(void *context, int32_t world_size, int32_t rank, const uint8_t *unique_id128,
+                                  void **out_comm);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_comm_release(void *comm);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_comm_allreduce_sum_f32(void *comm, void *buffer, uint64_t offset, uint64_t element_count);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_executable_attach_comm(void *executable, void *comm, int32_t output_count,
+                                             const int32_t *output_indices);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

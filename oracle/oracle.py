@@ -266,6 +266,16 @@ def baseline_bind_openblas() -> str:
                     break
         except Exception:
             explicit = ""
+    if explicit:
+        # the wheel-bundled OpenBLAS finds its Fortran runtime only when that is already loaded
+        import glob
+        folder = os.path.dirname(explicit)
+        for pattern in ("libquadmath*.so*", "libgfortran*.so*"):
+            for dep in sorted(glob.glob(os.path.join(folder, pattern))):
+                try:
+                    ctypes.CDLL(dep, mode=ctypes.RTLD_GLOBAL)
+                except OSError:
+                    pass
     lib().syn_baseline_bind_openblas(explicit.encode())
     return lib().syn_baseline_blas_name().decode()
 

@@ -1,0 +1,80 @@
+// Launchers of the sm_100a kernels.  Every launcher enqueues on the given stream and returns the
+// cudaError_t of the launch; none allocates or synchronises.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#include "program.hpp"
+
+namespace syn {
+namespace kern {
+
+// Bits of the device-side error word (one per context, checked after each run).
+enum : int { ERR_LABEL_RANGE = 1, ERR_NON_FINITE = 2, ERR_WAIT_TIMEOUT = 4 };
+
+struct Index4 {                 // right-aligned rank-4 iteration space with per-operand element strides
+    int64_t shape[4];
+    int64_t sa[4], sb[4], sc[4];
+};
+
+// ---- generic node-by-node kernels (one binary32 rounding per operation) -----------------------
+cudaError_t binary(cudaStream_t s, Op op, const float *a, const float *b, void *out, const Index4 &ix, int64_t total);
+cudaError_t scalar_op(cudaStream_t s, Op op, DType dtype, const void *a, void *out, uint64_t scalar_bits, int64_t total);
+cudaError_t unary(cudaStream_t s, Op op, const float *a, float *out, int64_t total);
+cudaError_t where(cudaStream_t s, const uint8_t *cond, const float *a, const float *b, float *out, const Index4 &ix, int64_t total);
+cudaError_t one_hot(cudaStream_t s, DType index_type, const void *indices, uint8_t *out, int64_t count, int64_t depth);
+cudaError_t copy_strided(cudaStream_t s, int element_bytes, const void *src, void *dst, const Index4 &ix, int64_t total);
+cudaError_t row_reduce(cudaStream_t s, Op op, const float *x, float *out, int64_t rows, int64_t cols);
+cudaError_t full_sum(cudaStream_t s, const float *x, const Index4 &ix, int64_t total, float *out);
+cudaError_t argmax_rows(cudaStream_t s, const float *x, int64_t *out, int64_t rows, int64_t cols);
+cudaError_t softmax_rows(cudaStream_t s, const float *x, float *out, int64_t rows, int64_t cols);
+cudaError_t mse_mean(cudaStream_t s, const float *p, const float *t, int64_t count, float *out);
+
+// ---- fused memory-bound kernels ----------------------------------------------------------------
+// out = gate > 0 ? upstream : 0   (WHERE(GT(z,0), g, 0), ElementwiseGradientRules.java:210)
+cudaError_t relu_backward(cudaStream_t s, const float *gate, const float *upstream, float *out, int64_t total);
+// Column sums of a dense [rows, cols] matrix, accumulated in binary64 and rounded once.
+// partials must hold colsum_partial_count(rows, cols) doubles.
+int64_t colsum_partial_count(int64_t rows, int64_t cols);
+cudaError_t colsum(cudaStream_t s, const float *g, int64_t rows, int64_t cols, double *partials, float *out);
+// Index cross entropy with logits: per-row loss into row_loss (rows floats of scratch), optional
+// gradient (softmax - onehot) * (seed / rows), optional row arg-max, then the mean of row_loss
+// into loss_out (optional).  Labels outside [0, cols) set ERR_LABEL_RANGE in *error_word.
+cudaError_t cross_entropy(cudaStream_t s, const float *logits, DType label_type, const void *labels,
+                          const float *seed, int64_t rows, int64_t cols, float *row_loss, float *loss_out,
+                          float *grad_out, int64_t *argmax_out, int *error_word);
+
+// ---- optimizers -----------------------------------------------------------------------------
+struct TensorSlot { float *p; const float *g; float *m; float *v; int64_t count; };
+struct SgdArgs { float lr, momentum, dampening, weight_decay; int nesterov, first_step, has_buffer, zero_buffer; };
+struct AdamArgs { float lr, b1, b2, eps, decay, correction1, correction2, decay_factor; int decoupled; };
+cudaError_t sgd_step(cudaStream_t s, const TensorSlot *slots, int slot_count, const SgdArgs &args, int *error_word);
+cudaError_t adam_step(cudaStream_t s, const TensorSlot *slots, int slot_count, const AdamArgs &args, int *error_word);
+
+// ---- GEMM -------------------------------------------------------------------------------------
+struct GemmEpilogue {
+    const float *bias = nullptr;        // [n], added to every row
+    int relu = 0;                       // out = max(z, +0)
+    const float *gate = nullptr;        // dense [m,n]: out = gate > 0 ? z : 0
+    float *second = nullptr;            // dense [m,n]: when set, `out` receives z and `second` relu(z)
+};
+// Exact CUDA-core product: every output cell is the reference's ascending-k chain of separately
+// rounded multiply and add (CpuMatmulReferenceKernel.java:71-93), operands and result strided.
+cudaError_t gemm_exact(cudaStream_t s, int64_t m, int64_t n, int64_t k,
+                       const float *a, int64_t a_ms, int64_t a_ks, const float *b, int64_t b_ks, int64_t b_ns,
+                       float *c, int64_t c_ms, int64_t c_ns, const GemmEpilogue &ep);
+
+// Tensor-core path.  split_planes writes hi = tf32(x) and lo = tf32(x - hi) of a logical [rows, cols]
+// matrix (element strides rs, cs; one of them 1) into two dense [rows, cols_padded] planes whose
+// padding columns are zero.  gemm_tf32x3 then computes D[m,n] = P[m,k] . Q[n,k]^T from the planes.
+int64_t padded_k(int64_t k);
+cudaError_t split_planes(cudaStream_t s, const float *src, int64_t rows, int64_t cols, int64_t rs, int64_t cs,
+                         float *hi, float *lo, int64_t cols_padded);
+struct TensorCoreGemm;       // opaque: tensor maps and launch geometry prepared once per plan step
+TensorCoreGemm *tc_gemm_prepare(const float *p_hi, const float *p_lo, const float *q_hi, const float *q_lo,
+                                int64_t m, int64_t n, int64_t k_padded, int sm_count, int *status);
+void tc_gemm_release(TensorCoreGemm *g);
+cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, int64_t ldd, const GemmEpilogue &ep, int *error_word);
+
+}  // namespace kern
+}  // namespace syn

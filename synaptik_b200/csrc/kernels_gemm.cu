@@ -1,0 +1,531 @@
+// GEMM kernels.
+//
+//  * gemm_exact_kernel: CUDA-core product whose every output cell is the reference's ascending-k
+//    chain of separately rounded multiply and add (CpuMatmulReferenceKernel.java:71-93), so small
+//    products are bit-identical to the reference CPU backend.  Strided operands and result.
+//  * split kernels + gemm_tf32x3_kernel: the tensor-core path for large products.  FP32 operands
+//    are split once into hi = tf32(x) and lo = tf32(x - hi) planes; the GEMM kernel is a persistent,
+//    warp-specialised tcgen05 pipeline (TMA loads of 128-byte-swizzled K-major tiles -> UMMA
+//    kind::tf32 with FP32 accumulators in tensor memory -> epilogue straight from tensor memory)
+//    that issues lo*hi, hi*lo and hi*hi into one accumulator (3xTF32).  The dropped lo*lo term is
+//    below 2^-22 of each product.
+#include "kernels.hpp"
+
+#include <cuda.h>
+
+#include <cstdio>
+
+namespace syn {
+namespace kern {
+
+namespace {
+
+__device__ __forceinline__ float relu_value(float x) { return x != x ? x : (x > 0.0f ? x : 0.0f); }
+
+// ------------------------------------------------------------------------------------------------
+// Exact CUDA-core GEMM: 64x64 result tile, 16-deep k slices, 256 threads, 4x4 cells per thread.
+// ------------------------------------------------------------------------------------------------
+constexpr int XT = 64, XK = 16;
+
+__global__ void __launch_bounds__(256) gemm_exact_kernel(int64_t m, int64_t n, int64_t k,
+        const float *__restrict__ a, int64_t a_ms, int64_t a_ks, const float *__restrict__ b, int64_t b_ks, int64_t b_ns,
+        float *c, int64_t c_ms, int64_t c_ns, GemmEpilogue ep) {
+    __shared__ float as[XK][XT + 4];
+    __shared__ float bs[XK][XT + 4];
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int64_t m0 = (int64_t)blockIdx.y * XT, n0 = (int64_t)blockIdx.x * XT;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+    const bool a_kfast = a_ks == 1, b_nfast = b_ns == 1;
+    for (int64_t k0 = 0; k0 < k; k0 += XK) {
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            int e = tid + q * 256;
+            int row = a_kfast ? e / XK : e % XT, kk = a_kfast ? e % XK : e / XT;
+            int64_t gm = m0 + row, gk = k0 + kk;
+            as[kk][row] = (gm < m && gk < k) ? a[gm * a_ms + gk * a_ks] : 0.0f;
+            int col = b_nfast ? e % XT : e / XK, kb = b_nfast ? e / XT : e % XK;
+            int64_t gn = n0 + col, gkb = k0 + kb;
+            bs[kb][col] = (gn < n && gkb < k) ? b[gkb * b_ks + gn * b_ns] : 0.0f;
+        }
+        __syncthreads();
+        const int depth = (int)((k - k0) < XK ? (k - k0) : XK);
+        if (k == 1) {
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = __fmul_rn(as[0][ty * 4 + i], bs[0][tx * 4 + j]);
+        } else {
+            for (int kk = 0; kk < depth; kk++) {
+                float av[4], bv[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) av[i] = as[kk][ty * 4 + i];
+#pragma unroll
+                for (int j = 0; j < 4; j++) bv[j] = bs[kk][tx * 4 + j];
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(av[i], bv[j]));
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int64_t gm = m0 + ty * 4 + i;
+        if (gm >= m) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            int64_t gn = n0 + tx * 4 + j;
+            if (gn >= n) continue;
+            float z = acc[i][j];
+            if (ep.bias) z = __fadd_rn(z, ep.bias[gn]);
+            if (ep.gate) z = ep.gate[gm * n + gn] > 0.0f ? z : 0.0f;
+            if (ep.second) { c[gm * c_ms + gn * c_ns] = z; ep.second[gm * n + gn] = relu_value(z); }
+            else c[gm * c_ms + gn * c_ns] = ep.relu ? relu_value(z) : z;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// hi / lo split into zero-padded K-major planes.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+__device__ __forceinline__ bool finite_f(float x) { return (__float_as_uint(x) & 0x7f800000u) != 0x7f800000u; }
+__device__ __forceinline__ void split_value(float x, float &hi, float &lo) {
+    float h = to_tf32(x);
+    if (!finite_f(h)) {
+        if (!finite_f(x)) { hi = x; lo = 0.0f; return; }            // inf / NaN pass through the hi plane only
+        h = __uint_as_float(__float_as_uint(x) & 0xffffe000u);      // rounding up would overflow: truncate instead
+    }
+    hi = h;
+    lo = to_tf32(__fsub_rn(x, h));                                  // x - hi is exact in binary32
+}
+
+__global__ void split_rows_kernel(const float *__restrict__ src, int64_t rows, int64_t cols, int64_t rs,
+                                  float *hi, float *lo, int64_t cp, int vec_ok) {
+    const int64_t quads = cp >> 2, total = rows * quads;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t r = i / quads, c = (i - r * quads) << 2;
+        float x[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const float *p = src + r * rs + c;
+        if (vec_ok && c + 3 < cols) { float4 v = *reinterpret_cast<const float4 *>(p); x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w; }
+        else {
+#pragma unroll
+            for (int q = 0; q < 4; q++) if (c + q < cols) x[q] = p[q];
+        }
+        float h[4], l[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) split_value(x[q], h[q], l[q]);
+        *reinterpret_cast<float4 *>(hi + r * cp + c) = make_float4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<float4 *>(lo + r * cp + c) = make_float4(l[0], l[1], l[2], l[3]);
+    }
+}
+
+// Source element (r, c) lives at src[c * cs + r]: a transposing split through a padded 32x32 tile.
+__global__ void __launch_bounds__(256) split_transposed_kernel(const float *__restrict__ src, int64_t rows, int64_t cols, int64_t cs,
+                                                                float *hi, float *lo, int64_t cp) {
+    __shared__ float tile[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int64_t tiles_c = cp >> 5, tiles_r = (rows + 31) >> 5, tiles = tiles_c * tiles_r;
+    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const int64_t r0 = (t % tiles_r) << 5, c0 = (t / tiles_r) << 5;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            int64_t c = c0 + ty + 8 * j, r = r0 + tx;
+            tile[ty + 8 * j][tx] = (c < cols && r < rows) ? src[c * cs + r] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            int64_t r = r0 + ty + 8 * j, c = c0 + tx;
+            if (r < rows) {
+                float h, l;
+                split_value(tile[tx][ty + 8 * j], h, l);
+                hi[r * cp + c] = h;
+                lo[r * cp + c] = l;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// tcgen05 3xTF32 GEMM.
+// ------------------------------------------------------------------------------------------------
+constexpr int BM = 128;             // rows of P per tile = UMMA M = tensor-memory lanes
+constexpr int BK = 32;              // 32 floats = 128 bytes = one swizzle row
+constexpr int UMMA_K = 8;           // kind::tf32 contracts 8 elements (32 bytes) per instruction
+constexpr int GEMM_THREADS = 256;   // warp 0 TMA producer, warp 1 MMA issuer + tensor-memory owner, warps 4-7 epilogue
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // every device-side wait gives up after two seconds
+
+template <int BN> struct TileConfig {
+    static constexpr int kStages = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
+    static constexpr int kABytes = BM * BK * 4;            // one plane of P
+    static constexpr int kBBytes = BN * BK * 4;            // one plane of Q
+    static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
+    static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;     // two accumulators, power of two
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint64_t global_timer() { uint64_t t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
+}
+// Bounded wait: returns false (after raising the block's abort flag) when the phase has not
+// completed within WAIT_LIMIT_NS or another role has already given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t start = global_timer();
+    for (uint32_t spin = 0;; spin++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 63u) == 63u) {
+            if (*abort_flag) return false;
+            if (global_timer() - start > WAIT_LIMIT_NS) { *abort_flag = 1; return false; }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzled:
+// start address (>>4), stride between 8-row groups = 1024 bytes (>>4), descriptor version 1,
+// layout type 2 (SWIZZLE_128B).  The leading-dimension offset is not used for swizzled K-major tiles
+// and carries the canonical value 1.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr & 0x3ffffu) >> 4) | (1ull << 16) | ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: FP32 accumulate, TF32 x TF32, both operands K-major, M = 128, N = BN.
+template <int BN> __device__ __forceinline__ uint32_t umma_idesc() {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+
+struct TcParams {
+    float *d; int64_t ldd;
+    int m, n, k_blocks;
+    int tiles_m, tiles_n;
+    const float *bias; const float *gate; float *second; int relu;
+    int *error_word;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tf32x3_kernel(
+        const __grid_constant__ CUtensorMap map_p_hi, const __grid_constant__ CUtensorMap map_p_lo,
+        const __grid_constant__ CUtensorMap map_q_hi, const __grid_constant__ CUtensorMap map_q_lo, TcParams prm) {
+    using Cfg = TileConfig<BN>;
+    constexpr int S = Cfg::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    // tiles need 1024-byte alignment for the 128-byte swizzle pattern
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S * Cfg::kStageBytes);
+    // bars[0..S) full, [S..2S) empty, [2S..2S+2) accumulator full, [2S+2..2S+4) accumulator empty
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * S + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar_base = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
+    auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * S + a); };
+    auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * S + 2 + a); };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), 128); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {        // one warp owns the tensor-memory allocation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)Cfg::kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int total_tiles = prm.tiles_m * prm.tiles_n;
+    const int kb_count = prm.k_blocks;
+    const uint32_t smem_base = smem_u32(smem);
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            uint32_t armed_phase[S]; bool armed[S];
+            for (int s = 0; s < S; s++) { armed[s] = false; armed_phase[s] = 0; }
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile / prm.tiles_n) * BM, n0 = (tile % prm.tiles_n) * BN;
+                for (int kb = 0; kb < kb_count; kb++) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t sa = smem_base + stage * Cfg::kStageBytes;
+                    mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
+                    armed[stage] = true; armed_phase[stage] = phase;
+                    tma_load_2d(sa, &map_p_hi, full_bar(stage), kb * BK, m0);
+                    tma_load_2d(sa + Cfg::kABytes, &map_p_lo, full_bar(stage), kb * BK, m0);
+                    tma_load_2d(sa + 2 * Cfg::kABytes, &map_q_hi, full_bar(stage), kb * BK, n0);
+                    tma_load_2d(sa + 2 * Cfg::kABytes + Cfg::kBBytes, &map_q_lo, full_bar(stage), kb * BK, n0);
+                    if (++stage == S) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok || *abort_flag) {
+                // leave no bulk copy in flight towards this block's shared memory
+                for (int s = 0; s < S; s++) if (armed[s]) mbar_wait(full_bar(s), armed_phase[s], abort_flag);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc<BN>();
+            int stage = 0; uint32_t phase = 0;
+            int local = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local++) {
+                const int acc = local & 1;
+                if (!mbar_wait(acc_empty_bar(acc), (((uint32_t)local >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < kb_count; kb++) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + stage * Cfg::kStageBytes;
+                    const uint32_t p_hi = sa, p_lo = sa + Cfg::kABytes, q_hi = sa + 2 * Cfg::kABytes, q_lo = q_hi + Cfg::kBBytes;
+#pragma unroll
+                    for (int k4 = 0; k4 < BK / UMMA_K; k4++) {
+                        const uint32_t off = k4 * UMMA_K * 4;
+                        // small terms first, then the leading product
+                        umma_tf32(tmem_d, umma_desc(p_lo + off), umma_desc(q_hi + off), idesc, (kb | k4) != 0);
+                        umma_tf32(tmem_d, umma_desc(p_hi + off), umma_desc(q_lo + off), idesc, 1u);
+                        umma_tf32(tmem_d, umma_desc(p_hi + off), umma_desc(q_hi + off), idesc, 1u);
+                    }
+                    umma_commit(empty_bar(stage));          // releases the stage once these MMAs have read it
+                    if (++stage == S) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) umma_commit(acc_full_bar(acc));     // accumulator complete
+            }
+        }
+    } else if (warp >= 4) {
+        // ---------------- epilogue: tensor memory -> registers -> global ----------------
+        const int quarter = warp & 3;                       // a warp may only touch lanes 32*(warp%4)..+31
+        int local = 0;
+        bool ok = true;
+        const bool vec_ok = (prm.ldd & 3) == 0 && ((uintptr_t)prm.d & 15) == 0
+                            && (!prm.second || ((uintptr_t)prm.second & 15) == 0) && (!prm.gate || ((uintptr_t)prm.gate & 15) == 0);
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local++) {
+            const int acc = local & 1;
+            const int m0 = (tile / prm.tiles_n) * BM, n0 = (tile % prm.tiles_n) * BN;
+            ok = mbar_wait(acc_full_bar(acc), ((uint32_t)local >> 1) & 1u, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);     // the warp-wide tensor-memory loads below need one verdict
+            if (!ok) break;
+            tc_fence_after();
+            const int row = m0 + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+            for (int chunk = 0; chunk < BN / 32; chunk++) {
+                float v[32];
+                tmem_load32(taddr + (uint32_t)(chunk * 32), v);
+                const int col0 = n0 + chunk * 32;
+                if (row < prm.m && col0 < prm.n) {
+                    float *drow = prm.d + (int64_t)row * prm.ldd;
+                    const int64_t dense = (int64_t)row * prm.n;
+#pragma unroll
+                    for (int q = 0; q < 8; q++) {
+                        const int col = col0 + q * 4;
+                        float z[4] = {v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]};
+                        if (col + 3 < prm.n && vec_ok && (prm.n & 3) == 0) {
+                            if (prm.bias) { float4 bv = *reinterpret_cast<const float4 *>(prm.bias + col);
+                                z[0] = __fadd_rn(z[0], bv.x); z[1] = __fadd_rn(z[1], bv.y); z[2] = __fadd_rn(z[2], bv.z); z[3] = __fadd_rn(z[3], bv.w); }
+                            if (prm.gate) { float4 gv = *reinterpret_cast<const float4 *>(prm.gate + dense + col);
+                                z[0] = gv.x > 0.0f ? z[0] : 0.0f; z[1] = gv.y > 0.0f ? z[1] : 0.0f; z[2] = gv.z > 0.0f ? z[2] : 0.0f; z[3] = gv.w > 0.0f ? z[3] : 0.0f; }
+                            if (prm.second) {
+                                *reinterpret_cast<float4 *>(drow + col) = make_float4(z[0], z[1], z[2], z[3]);
+                                *reinterpret_cast<float4 *>(prm.second + dense + col) = make_float4(relu_value(z[0]), relu_value(z[1]), relu_value(z[2]), relu_value(z[3]));
+                            } else if (prm.relu) {
+                                *reinterpret_cast<float4 *>(drow + col) = make_float4(relu_value(z[0]), relu_value(z[1]), relu_value(z[2]), relu_value(z[3]));
+                            } else {
+                                *reinterpret_cast<float4 *>(drow + col) = make_float4(z[0], z[1], z[2], z[3]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                const int cc = col + e;
+                                if (cc < prm.n) {
+                                    float zz = z[e];
+                                    if (prm.bias) zz = __fadd_rn(zz, prm.bias[cc]);
+                                    if (prm.gate) zz = prm.gate[dense + cc] > 0.0f ? zz : 0.0f;
+                                    if (prm.second) { drow[cc] = zz; prm.second[dense + cc] = relu_value(zz); }
+                                    else drow[cc] = prm.relu ? relu_value(zz) : zz;
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(acc_empty_bar(acc));
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicOr(prm.error_word, ERR_WAIT_TIMEOUT);
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::kTmemCols) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// 2-D map over a dense [rows, kp] FP32 plane: box = 32 floats (one 128-byte swizzle row) x box_rows.
+bool make_plane_map(CUtensorMap *map, const float *plane, int64_t rows, int64_t kp, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)kp, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)kp * 4};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)plane, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+cudaError_t gemm_exact(cudaStream_t s, int64_t m, int64_t n, int64_t k, const float *a, int64_t a_ms, int64_t a_ks,
+                       const float *b, int64_t b_ks, int64_t b_ns, float *c, int64_t c_ms, int64_t c_ns, const GemmEpilogue &ep) {
+    if (m == 0 || n == 0) return cudaSuccess;
+    dim3 grid((unsigned)((n + XT - 1) / XT), (unsigned)((m + XT - 1) / XT));
+    if (grid.y > 65535) return cudaErrorInvalidValue;
+    gemm_exact_kernel<<<grid, 256, 0, s>>>(m, n, k, a, a_ms, a_ks, b, b_ks, b_ns, c, c_ms, c_ns, ep);
+    return cudaGetLastError();
+}
+
+int64_t padded_k(int64_t k) { return (k + BK - 1) / BK * BK; }
+
+cudaError_t split_planes(cudaStream_t s, const float *src, int64_t rows, int64_t cols, int64_t rs, int64_t cs,
+                         float *hi, float *lo, int64_t cp) {
+    if (rows == 0) return cudaSuccess;
+    if (cs == 1 || cols == 1) {
+        int vec_ok = (rs & 3) == 0 && ((uintptr_t)src & 15) == 0;
+        int64_t total = rows * (cp >> 2);
+        int64_t blocks = (total + 255) / 256;
+        split_rows_kernel<<<(unsigned)(blocks > 148 * 32 ? 148 * 32 : blocks), 256, 0, s>>>(src, rows, cols, rs, hi, lo, cp, vec_ok);
+    } else if (rs == 1 || rows == 1) {
+        int64_t tiles = (cp >> 5) * ((rows + 31) >> 5);
+        split_transposed_kernel<<<(unsigned)(tiles > 148 * 16 ? 148 * 16 : tiles), 256, 0, s>>>(src, rows, cols, cs, hi, lo, cp);
+    } else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+struct TensorCoreGemm {
+    CUtensorMap p_hi, p_lo, q_hi, q_lo;
+    int m, n, k_blocks, bn, grid;
+};
+
+TensorCoreGemm *tc_gemm_prepare(const float *p_hi, const float *p_lo, const float *q_hi, const float *q_lo,
+                                int64_t m, int64_t n, int64_t k_padded, int sm_count, int *status) {
+    *status = OK;
+    if (m < 1 || n < 1 || k_padded < BK || k_padded % BK || m > (1ll << 30) || n > (1ll << 30)) { *status = UNSUPPORTED_SHAPE; return nullptr; }
+    TensorCoreGemm *g = new TensorCoreGemm();
+    g->m = (int)m; g->n = (int)n; g->k_blocks = (int)(k_padded / BK);
+    g->bn = n >= 192 ? 256 : (n >= 96 ? 128 : 64);
+    int64_t tiles = ((m + BM - 1) / BM) * ((n + g->bn - 1) / g->bn);
+    g->grid = (int)(tiles < sm_count ? tiles : sm_count);
+    bool ok = make_plane_map(&g->p_hi, p_hi, m, k_padded, BM) && make_plane_map(&g->p_lo, p_lo, m, k_padded, BM)
+              && make_plane_map(&g->q_hi, q_hi, n, k_padded, g->bn) && make_plane_map(&g->q_lo, q_lo, n, k_padded, g->bn);
+    if (!ok) { delete g; *status = KERNEL_COMPILATION_FAILED; return nullptr; }
+    return g;
+}
+
+void tc_gemm_release(TensorCoreGemm *g) { delete g; }
+
+template <int BN>
+static cudaError_t launch_tc(cudaStream_t s, const TensorCoreGemm *g, const TcParams &prm) {
+    using Cfg = TileConfig<BN>;
+    // a per-device attribute: set on every launch so each GPU of the process has it
+    cudaError_t e = cudaFuncSetAttribute(gemm_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    gemm_tf32x3_kernel<BN><<<g->grid, GEMM_THREADS, Cfg::kSmemBytes, s>>>(g->p_hi, g->p_lo, g->q_hi, g->q_lo, prm);
+    return cudaGetLastError();
+}
+
+cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, int64_t ldd, const GemmEpilogue &ep, int *error_word) {
+    TcParams prm;
+    prm.d = d; prm.ldd = ldd; prm.m = g->m; prm.n = g->n; prm.k_blocks = g->k_blocks;
+    prm.tiles_m = (g->m + BM - 1) / BM; prm.tiles_n = (g->n + g->bn - 1) / g->bn;
+    prm.bias = ep.bias; prm.gate = ep.gate; prm.second = ep.second; prm.relu = ep.relu; prm.error_word = error_word;
+    if (g->bn == 256) return launch_tc<256>(s, g, prm);
+    if (g->bn == 128) return launch_tc<128>(s, g, prm);
+    return launch_tc<64>(s, g, prm);
+}
+
+}  // namespace kern
+}  // namespace syn

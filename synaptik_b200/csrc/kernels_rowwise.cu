@@ -1,0 +1,690 @@
+// Memory-bound kernels of the dense-MLP path: node-by-node elementwise operations, row
+// reductions, softmax / cross-entropy / arg-max row kernels, column sums, and the fused optimizer
+// passes.  All use coalesced (128-bit where alignment allows) accesses and warp-shuffle
+// reductions; none uses tensor cores on purpose -- they are bounded by HBM bandwidth.
+#include "kernels.hpp"
+
+#include <cfloat>
+#include <cmath>
+
+namespace syn {
+namespace kern {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+inline int grid_for(int64_t total, int per_block, int cap = 148 * 16) {
+    int64_t blocks = (total + per_block - 1) / per_block;
+    if (blocks < 1) blocks = 1;
+    return (int)(blocks > cap ? cap : blocks);
+}
+
+__device__ __forceinline__ float relu_value(float x) {      // Math.max(x, +0.0f): NaN stays NaN, -0 -> +0
+    return x != x ? x : (x > 0.0f ? x : 0.0f);
+}
+
+// exp(x) in binary32, within 0.78 ulp of the exact value (measured on the host over a uniform
+// sweep of bit patterns) and equal to the correctly rounded value for 99.7 % of inputs; the
+// reference computes (float)StrictMath.exp((double)x).  Cody-Waite reduction by ln2 in two parts,
+// degree-7 polynomial, compensated final addition, two-step power-of-two scaling so subnormal
+// results round once.
+__device__ __forceinline__ float exp_accurate(float x) {
+    if (!(x > -104.0f)) return x != x ? x : 0.0f;
+    if (x > 88.8f) return __int_as_float(0x7f800000);
+    float n = rintf(x * 1.4426950408889634f);
+    float r = fmaf(n, -0.693145751953125f, x);
+    r = fmaf(n, -1.42860682030941723212e-6f, r);
+    float p = 1.9841270114e-4f;
+    p = fmaf(p, r, 1.3888889225e-3f);
+    p = fmaf(p, r, 8.3333337680e-3f);
+    p = fmaf(p, r, 4.1666667908e-2f);
+    p = fmaf(p, r, 1.6666667163e-1f);
+    p = fmaf(p, r, 0.5f);
+    float t = __fmul_rn(__fmul_rn(r, r), p);
+    float s = __fadd_rn(1.0f, r);
+    float err = __fadd_rn(__fsub_rn(1.0f, s), r);
+    float res = __fadd_rn(s, __fadd_rn(err, t));
+    int ni = (int)n;
+    int n1 = ni < -126 ? -126 : (ni > 127 ? 127 : ni);
+    int n2 = ni - n1;
+    return __fmul_rn(__fmul_rn(res, __int_as_float((n1 + 127) << 23)), __int_as_float((n2 + 127) << 23));
+}
+
+__device__ __forceinline__ float java_max(float a, float b) {   // Math.max: NaN wins, +0 above -0
+    if (a != a) return a;
+    if (b != b) return b;
+    if (a == 0.0f && b == 0.0f) return (__float_as_uint(a) >> 31) ? b : a;
+    return a > b ? a : b;
+}
+
+__device__ __forceinline__ double warp_sum(double v) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max_java(float v) {
+    for (int o = 16; o > 0; o >>= 1) v = java_max(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_max_plain(float v) {     // the plain '>' maximum of logSumExp
+    for (int o = 16; o > 0; o >>= 1) { float u = __shfl_xor_sync(0xffffffffu, v, o); v = u > v ? u : v; }
+    return v;
+}
+
+__device__ __forceinline__ void unravel(int64_t i, const Index4 &ix, int64_t &oa, int64_t &ob, int64_t &oc) {
+    int64_t i3 = i % ix.shape[3]; i /= ix.shape[3];
+    int64_t i2 = i % ix.shape[2]; i /= ix.shape[2];
+    int64_t i1 = i % ix.shape[1]; int64_t i0 = i / ix.shape[1];
+    oa = i0 * ix.sa[0] + i1 * ix.sa[1] + i2 * ix.sa[2] + i3 * ix.sa[3];
+    ob = i0 * ix.sb[0] + i1 * ix.sb[1] + i2 * ix.sb[2] + i3 * ix.sb[3];
+    oc = i0 * ix.sc[0] + i1 * ix.sc[1] + i2 * ix.sc[2] + i3 * ix.sc[3];
+}
+
+__global__ void binary_kernel(int op, const float *__restrict__ a, const float *__restrict__ b, void *out, Index4 ix, int64_t total) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t oa, ob, oc;
+        unravel(i, ix, oa, ob, oc);
+        float x = a[oa], y = b[ob];
+        switch ((Op)op) {
+            case Op::ADD: ((float *)out)[i] = __fadd_rn(x, y); break;
+            case Op::SUB: ((float *)out)[i] = __fsub_rn(x, y); break;
+            case Op::MUL: ((float *)out)[i] = __fmul_rn(x, y); break;
+            case Op::DIV: ((float *)out)[i] = __fdiv_rn(x, y); break;
+            default: ((uint8_t *)out)[i] = x > y ? 1 : 0; break;          // GT
+        }
+    }
+}
+
+__global__ void where_kernel(const uint8_t *__restrict__ cond, const float *__restrict__ a, const float *__restrict__ b,
+                             float *out, Index4 ix, int64_t total) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t oc, oa, ob;
+        unravel(i, ix, oc, oa, ob);      // strides: sa = condition, sb = first, sc = second
+        out[i] = cond[oc] ? a[oa] : b[ob];
+    }
+}
+
+template <typename T>
+__global__ void scalar_kernel(int op, const T *__restrict__ a, T *out, T scalar, int64_t total) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        T x = a[i];
+        if ((Op)op == Op::SCALAR_MIN) out[i] = x < scalar ? x : scalar;
+        else out[i] = x > scalar ? x : scalar;
+    }
+}
+__global__ void scalar_f32_kernel(int op, const float *__restrict__ a, float *out, float scalar, int64_t total) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        float x = a[i];
+        if ((Op)op == Op::SCALAR_MUL) out[i] = __fmul_rn(x, scalar);
+        else if ((Op)op == Op::SCALAR_MIN) out[i] = (x != x || scalar != scalar) ? (x != x ? x : scalar) : (x < scalar ? x : scalar);
+        else out[i] = java_max(x, scalar);
+    }
+}
+
+__global__ void unary_kernel(int op, const float *__restrict__ a, float *out, int64_t total) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        float x = a[i];
+        out[i] = (Op)op == Op::RELU ? relu_value(x) : exp_accurate(x);
+    }
+}
+
+template <typename T>
+__global__ void one_hot_kernel(const T *__restrict__ indices, uint8_t *out, int64_t count, int64_t depth) {
+    int64_t total = count * depth;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t row = i / depth, col = i - row * depth;
+        out[i] = (int64_t)indices[row] == col ? 1 : 0;
+    }
+}
+
+template <typename T>
+__global__ void copy_kernel(const T *__restrict__ src, T *dst, Index4 ix, int64_t total) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t oa, ob, oc;
+        unravel(i, ix, oa, ob, oc);
+        dst[i] = src[oa];
+    }
+}
+
+// One warp per row.  SUM accumulates in binary64 and rounds once (the reference's aggregate SUM is
+// exactly rounded, CpuExactSumEmitter.java:14-21); MAX follows Math.max.
+__global__ void row_reduce_kernel(int op, const float *__restrict__ x, float *out, int64_t rows, int64_t cols) {
+    int lane = threadIdx.x & 31;
+    int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t r = warp; r < rows; r += warps) {
+        const float *row = x + r * cols;
+        if ((Op)op == Op::SUM) {
+            double acc = 0.0;
+            for (int64_t c = lane; c < cols; c += 32) acc += (double)row[c];
+            acc = warp_sum(acc);
+            if (lane == 0) out[r] = (float)acc;
+        } else {
+            float acc = row[0];
+            for (int64_t c = lane; c < cols; c += 32) acc = java_max(acc, row[c]);
+            acc = warp_max_java(acc);
+            if (lane == 0) out[r] = acc;
+        }
+    }
+}
+
+__global__ void full_sum_kernel(const float *__restrict__ x, Index4 ix, int64_t total, float *out) {
+    __shared__ double partial[32];
+    double acc = 0.0;
+    for (int64_t i = threadIdx.x; i < total; i += blockDim.x) {
+        int64_t oa, ob, oc;
+        unravel(i, ix, oa, ob, oc);
+        acc += (double)x[oa];
+    }
+    acc = warp_sum(acc);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        double v = threadIdx.x < (blockDim.x >> 5) ? partial[threadIdx.x] : 0.0;
+        v = warp_sum(v);
+        if (threadIdx.x == 0) out[0] = (float)v;
+    }
+}
+
+// Total order key of ARG_MAX (CpuArgExtremaEmitter.java:268-318): every NaN above +inf, -0 below +0.
+__device__ __forceinline__ uint32_t order_key(float v) {
+    uint32_t b = __float_as_uint(v);
+    if ((b & 0x7fffffffu) > 0x7f800000u) return 0xffffffffu;
+    return (b >> 31) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ unsigned long long warp_best(unsigned long long v) {
+    for (int o = 16; o > 0; o >>= 1) { unsigned long long u = __shfl_xor_sync(0xffffffffu, v, o); v = u > v ? u : v; }
+    return v;
+}
+
+__global__ void argmax_kernel(const float *__restrict__ x, int64_t *out, int64_t rows, int64_t cols) {
+    int lane = threadIdx.x & 31;
+    int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t r = warp; r < rows; r += warps) {
+        const float *row = x + r * cols;
+        unsigned long long best = 0;
+        for (int64_t c = lane; c < cols; c += 32) {
+            // larger key wins; among equal keys the smaller index wins (FIRST_INDEX ties)
+            unsigned long long cand = ((unsigned long long)order_key(row[c]) << 32) | (0xffffffffu - (uint32_t)c);
+            best = cand > best ? cand : best;
+        }
+        best = warp_best(best);
+        if (lane == 0) out[r] = (int64_t)(0xffffffffu - (uint32_t)(best & 0xffffffffu));
+    }
+}
+
+// SOFTMAX rows, CpuSoftmaxReferenceKernel.java:104-146: Math.max maximum; any +inf -> NaN at the
+// infinities and 0 elsewhere; any -inf (without NaN) -> unshifted exponentials; otherwise
+// exp(x - max) / sum.  The reference's Kahan-compensated binary32 sum is replaced by a binary64
+// sum rounded once (both lie within an ulp of the exact sum).
+__global__ void softmax_kernel(const float *__restrict__ x, float *out, int64_t rows, int64_t cols) {
+    int lane = threadIdx.x & 31;
+    int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t r = warp; r < rows; r += warps) {
+        const float *row = x + r * cols;
+        float *o = out + r * cols;
+        float maximum = __int_as_float(0xff800000);
+        int has_ninf = 0;
+        for (int64_t c = lane; c < cols; c += 32) { float v = row[c]; maximum = java_max(maximum, v); has_ninf |= v == __int_as_float(0xff800000); }
+        maximum = warp_max_java(maximum);
+        has_ninf = __any_sync(0xffffffffu, has_ninf);
+        if (maximum == __int_as_float(0x7f800000)) {
+            for (int64_t c = lane; c < cols; c += 32) o[c] = row[c] == maximum ? __int_as_float(0x7fc00000) : 0.0f;
+            continue;
+        }
+        if (has_ninf && !(maximum != maximum)) maximum = 0.0f;
+        double acc = 0.0;
+        for (int64_t c = lane; c < cols; c += 32) acc += (double)exp_accurate(__fsub_rn(row[c], maximum));
+        float sum = (float)warp_sum(acc);
+        for (int64_t c = lane; c < cols; c += 32) o[c] = __fdiv_rn(exp_accurate(__fsub_rn(row[c], maximum)), sum);
+    }
+}
+
+// MEAN_SQUARED_ERROR, CpuLossReferenceKernel.java:67-87: ascending binary32 accumulation of the
+// squared differences, then the exact quotient by the count rounded once (:221-225).  Small
+// inputs are accumulated by one thread in the reference's order; large ones by a binary64 tree.
+__global__ void mse_kernel(const float *__restrict__ p, const float *__restrict__ t, int64_t count, float *out) {
+    __shared__ double partial[32];
+    float total;
+    if (count <= 65536) {
+        if (threadIdx.x != 0) return;
+        float sum = 0.0f;
+        for (int64_t i = 0; i < count; i++) { float d = __fsub_rn(p[i], t[i]); sum = __fadd_rn(sum, __fmul_rn(d, d)); }
+        total = sum;
+    } else {
+        double acc = 0.0;
+        for (int64_t i = threadIdx.x; i < count; i += blockDim.x) { float d = __fsub_rn(p[i], t[i]); acc += (double)__fmul_rn(d, d); }
+        acc = warp_sum(acc);
+        if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = acc;
+        __syncthreads();
+        if (threadIdx.x >= 32) return;
+        double v = threadIdx.x < (blockDim.x >> 5) ? partial[threadIdx.x] : 0.0;
+        v = warp_sum(v);
+        if (threadIdx.x != 0) return;
+        total = (float)v;
+    }
+    // binary64 holds the quotient of a 24-bit numerator by a count below 2^28 to well under half a
+    // binary32 ulp of any non-tie, so the second rounding cannot move the result
+    out[0] = (total == 0.0f || !isfinite(total)) ? total / (float)count : (float)((double)total / (double)count);
+}
+
+__global__ void relu_backward_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ up, float4 *out, int64_t vec_count,
+                                     const float *gate_s, const float *up_s, float *out_s, int64_t total) {
+    int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t v = i; v < vec_count; v += stride) {
+        float4 z = gate[v], g = up[v], r;
+        r.x = z.x > 0.0f ? g.x : 0.0f; r.y = z.y > 0.0f ? g.y : 0.0f;
+        r.z = z.z > 0.0f ? g.z : 0.0f; r.w = z.w > 0.0f ? g.w : 0.0f;
+        out[v] = r;
+    }
+    for (int64_t e = vec_count * 4 + i; e < total; e += stride) out_s[e] = gate_s[e] > 0.0f ? up_s[e] : 0.0f;
+}
+
+// Column sums, phase 1: block (strip, split) adds rows [split*rows_per, ...) of a 128-column strip
+// in binary64 and writes one partial per column; phase 2 adds the partials of each column in a
+// fixed order and rounds once.  Deterministic, no atomics.
+constexpr int kColsumRows = 8;     // warps per block, each striding over rows
+__global__ void colsum_partial_kernel(const float *__restrict__ g, int64_t rows, int64_t cols, int64_t rows_per, double *partials) {
+    __shared__ double sm[kColsumRows][128];
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    int64_t col0 = (int64_t)blockIdx.x * 128 + lane * 4;
+    int64_t r0 = (int64_t)blockIdx.y * rows_per, r1 = r0 + rows_per < rows ? r0 + rows_per : rows;
+    double a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+    bool vec = (cols & 3) == 0 && col0 + 3 < cols && ((uintptr_t)g & 15) == 0;
+    if (vec) {
+        for (int64_t r = r0 + w; r < r1; r += kColsumRows) {
+            float4 v = *reinterpret_cast<const float4 *>(g + r * cols + col0);
+            a0 += v.x; a1 += v.y; a2 += v.z; a3 += v.w;
+        }
+    } else {
+        for (int64_t r = r0 + w; r < r1; r += kColsumRows) {
+            const float *row = g + r * cols;
+            if (col0 < cols) a0 += row[col0];
+            if (col0 + 1 < cols) a1 += row[col0 + 1];
+            if (col0 + 2 < cols) a2 += row[col0 + 2];
+            if (col0 + 3 < cols) a3 += row[col0 + 3];
+        }
+    }
+    sm[w][lane * 4] = a0; sm[w][lane * 4 + 1] = a1; sm[w][lane * 4 + 2] = a2; sm[w][lane * 4 + 3] = a3;
+    __syncthreads();
+    if (threadIdx.x < 128) {
+        double s = 0;
+        for (int i = 0; i < kColsumRows; i++) s += sm[i][threadIdx.x];
+        int64_t col = (int64_t)blockIdx.x * 128 + threadIdx.x;
+        if (col < cols) partials[(int64_t)blockIdx.y * cols + col] = s;
+    }
+}
+__global__ void colsum_final_kernel(const double *__restrict__ partials, int64_t splits, int64_t cols, float *out) {
+    int64_t col = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (col >= cols) return;
+    double s = 0;
+    for (int64_t i = 0; i < splits; i++) s += partials[i * cols + col];
+    out[col] = (float)s;
+}
+
+inline int64_t colsum_splits(int64_t rows, int64_t cols) {
+    int64_t strips = (cols + 127) / 128;
+    int64_t want = (148 * 8 + strips - 1) / strips;            // about eight blocks per SM in total
+    int64_t most = (rows + 63) / 64;                           // at least 64 rows per block
+    int64_t s = want < most ? want : most;
+    return s < 1 ? 1 : s;
+}
+
+// ---- index cross entropy with logits -----------------------------------------------------------
+// Forward per row (CpuLossReferenceKernel.java:196-218,276-288): m = plain '>' maximum,
+// s = sum exp(x - m), loss = (m + log s) - x[label].  The reference adds the exponentials in
+// ascending binary32 order; here lanes add in binary64 and round once, which lies inside the
+// reference's own rounding error of that sum.  Gradient (LossGradientRules.java:172-228):
+// (exp(x - MAX) / SUM - onehot) * (seed / rows), MAX by Math.max, SUM exactly rounded.
+template <typename L>
+__device__ __forceinline__ int64_t load_label(const void *labels, int64_t r) { return (int64_t)((const L *)labels)[r]; }
+
+template <int CHUNKS, typename L>
+__global__ void __launch_bounds__(kThreads) ce_rows_vec_kernel(const float *__restrict__ logits, const void *__restrict__ labels,
+        const float *__restrict__ seed, int64_t rows, int cols, float *row_loss, float *grad, int64_t *argmax_out, int *error_word) {
+    int lane = threadIdx.x & 31;
+    int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int vec_cols = cols >> 2;
+    float scale = grad ? __fdiv_rn(seed ? seed[0] : 1.0f, (float)rows) : 0.0f;
+    for (int64_t r = warp; r < rows; r += warps) {
+        const float4 *row = reinterpret_cast<const float4 *>(logits + r * cols);
+        float4 v[CHUNKS];
+#pragma unroll
+        for (int j = 0; j < CHUNKS; j++) {
+            int c = lane + 32 * j;
+            v[j] = c < vec_cols ? row[c] : make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+        }
+        int64_t label = load_label<L>(labels, r);
+        bool label_ok = label >= 0 && label < cols;
+        if (!label_ok && lane == 0) atomicOr(error_word, ERR_LABEL_RANGE);
+        int64_t safe = label < 0 ? 0 : (label >= cols ? cols - 1 : label);
+        float mplain = __int_as_float(0xff800000), mjava = __int_as_float(0xff800000);
+        unsigned long long best = 0;
+#pragma unroll
+        for (int j = 0; j < CHUNKS; j++) {
+            int c = lane + 32 * j;
+            if (c < vec_cols) {
+                float e[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    mplain = e[q] > mplain ? e[q] : mplain;
+                    mjava = java_max(mjava, e[q]);
+                    if (argmax_out) {
+                        unsigned long long cand = ((unsigned long long)order_key(e[q]) << 32) | (0xffffffffu - (uint32_t)(c * 4 + q));
+                        best = cand > best ? cand : best;
+                    }
+                }
+            }
+        }
+        mplain = warp_max_plain(mplain);
+        mjava = warp_max_java(mjava);
+        if (argmax_out) { best = warp_best(best); if (lane == 0) argmax_out[r] = (int64_t)(0xffffffffu - (uint32_t)(best & 0xffffffffu)); }
+        bool same_max = mplain == mjava;        // differs only when the row holds a NaN
+        double acc = 0.0;
+        float target_logit = 0.0f;
+#pragma unroll
+        for (int j = 0; j < CHUNKS; j++) {
+            int c = lane + 32 * j;
+            if (c < vec_cols) {
+                float e[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    if ((int64_t)(c * 4 + q) == safe) target_logit = e[q];
+                    e[q] = exp_accurate(__fsub_rn(e[q], mplain));
+                    acc += (double)e[q];
+                }
+                v[j] = make_float4(e[0], e[1], e[2], e[3]);
+            }
+        }
+        float sum = (float)warp_sum(acc);
+        target_logit = __shfl_sync(0xffffffffu, target_logit, (int)((safe >> 2) & 31));
+        if (lane == 0 && row_loss) row_loss[r] = __fsub_rn(__fadd_rn(mplain, (float)log((double)sum)), target_logit);
+        if (grad) {
+            float4 *out = reinterpret_cast<float4 *>(grad + r * cols);
+            if (!same_max) sum = __int_as_float(0x7fc00000);      // a NaN logit poisons the whole row, as MAX propagates it
+#pragma unroll
+            for (int j = 0; j < CHUNKS; j++) {
+                int c = lane + 32 * j;
+                if (c < vec_cols) {
+                    float e[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        float hot = (int64_t)(c * 4 + q) == safe ? 1.0f : 0.0f;
+                        e[q] = __fmul_rn(__fsub_rn(__fdiv_rn(e[q], sum), hot), scale);
+                    }
+                    out[c] = make_float4(e[0], e[1], e[2], e[3]);
+                }
+            }
+        }
+    }
+}
+
+// Any column count: one warp per row, the row is re-read for the second and third pass (it is
+// still in L1/L2); used for narrow rows (the 10-class head) and rows that are not 16-byte aligned.
+template <typename L>
+__global__ void ce_rows_generic_kernel(const float *__restrict__ logits, const void *__restrict__ labels, const float *__restrict__ seed,
+        int64_t rows, int64_t cols, float *row_loss, float *grad, int64_t *argmax_out, int *error_word) {
+    int lane = threadIdx.x & 31;
+    int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    float scale = grad ? __fdiv_rn(seed ? seed[0] : 1.0f, (float)rows) : 0.0f;
+    for (int64_t r = warp; r < rows; r += warps) {
+        const float *row = logits + r * cols;
+        int64_t label = load_label<L>(labels, r);
+        if ((label < 0 || label >= cols) && lane == 0) atomicOr(error_word, ERR_LABEL_RANGE);
+        int64_t safe = label < 0 ? 0 : (label >= cols ? cols - 1 : label);
+        float mplain = __int_as_float(0xff800000), mjava = __int_as_float(0xff800000);
+        unsigned long long best = 0;
+        for (int64_t c = lane; c < cols; c += 32) {
+            float x = row[c];
+            mplain = x > mplain ? x : mplain;
+            mjava = java_max(mjava, x);
+            unsigned long long cand = ((unsigned long long)order_key(x) << 32) | (0xffffffffu - (uint32_t)c);
+            best = cand > best ? cand : best;
+        }
+        mplain = warp_max_plain(mplain);
+        mjava = warp_max_java(mjava);
+        if (argmax_out) { best = warp_best(best); if (lane == 0) argmax_out[r] = (int64_t)(0xffffffffu - (uint32_t)(best & 0xffffffffu)); }
+        double acc = 0.0;
+        for (int64_t c = lane; c < cols; c += 32) acc += (double)exp_accurate(__fsub_rn(row[c], mplain));
+        float sum = (float)warp_sum(acc);
+        if (lane == 0 && row_loss) row_loss[r] = __fsub_rn(__fadd_rn(mplain, (float)log((double)sum)), row[safe]);
+        if (grad) {
+            if (mplain != mjava) sum = __int_as_float(0x7fc00000);
+            float *out = grad + r * cols;
+            for (int64_t c = lane; c < cols; c += 32) {
+                float p = __fdiv_rn(exp_accurate(__fsub_rn(row[c], mplain)), sum);
+                out[c] = __fmul_rn(__fsub_rn(p, c == safe ? 1.0f : 0.0f), scale);
+            }
+        }
+    }
+}
+
+// Mean of the per-row losses: the reference adds them in ascending binary32 order and divides by
+// the count; one block adds them in binary64 in a fixed order and rounds once.
+__global__ void mean_kernel(const float *__restrict__ values, int64_t count, float *out) {
+    __shared__ double partial[32];
+    double acc = 0.0;
+    for (int64_t i = threadIdx.x; i < count; i += blockDim.x) acc += (double)values[i];
+    acc = warp_sum(acc);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        double v = threadIdx.x < (blockDim.x >> 5) ? partial[threadIdx.x] : 0.0;
+        v = warp_sum(v);
+        if (threadIdx.x == 0) out[0] = __fdiv_rn((float)v, (float)count);
+    }
+}
+
+// ---- optimizers --------------------------------------------------------------------------------
+constexpr int kMaxSlots = 48;
+struct SlotTable { TensorSlot slot[kMaxSlots]; int64_t first_block[kMaxSlots + 1]; int count; };
+constexpr int kOptElemsPerBlock = kThreads * 8;
+
+__device__ __forceinline__ bool finite(float x) { return (__float_as_uint(x) & 0x7f800000u) != 0x7f800000u; }
+
+// SGD, TrainingParameter.java:622-672: every product and sum is a separate binary32 rounding.
+__global__ void __launch_bounds__(kThreads) sgd_kernel(SlotTable table, SgdArgs a, int *error_word) {
+    int t = 0;
+    while (t + 1 < table.count && (int64_t)blockIdx.x >= table.first_block[t + 1]) t++;
+    const TensorSlot s = table.slot[t];
+    int64_t base = ((int64_t)blockIdx.x - table.first_block[t]) * kOptElemsPerBlock;
+    bool bad = false;
+    for (int64_t i = base + threadIdx.x; i < base + kOptElemsPerBlock && i < s.count; i += kThreads) {
+        float p = s.p[i];
+        float decay_term = __fmul_rn(a.weight_decay, p);
+        float adjusted = __fadd_rn(s.g[i], decay_term);
+        float update = adjusted;
+        if (a.momentum != 0.0f) {
+            float buf;
+            if (a.first_step) buf = adjusted;
+            else buf = __fadd_rn(__fmul_rn(a.momentum, s.m[i]), __fmul_rn(__fsub_rn(1.0f, a.dampening), adjusted));
+            s.m[i] = buf;
+            update = a.nesterov ? __fadd_rn(adjusted, __fmul_rn(a.momentum, buf)) : buf;
+            bad |= !finite(buf);
+        } else if (a.zero_buffer) s.m[i] = 0.0f;
+        float scaled = __fmul_rn(a.lr, update);
+        float candidate = __fsub_rn(p, scaled);
+        bad |= !finite(p) || !finite(decay_term) || !finite(adjusted) || !finite(update) || !finite(scaled) || !finite(candidate);
+        s.p[i] = candidate;
+    }
+    if (bad) atomicOr(error_word, ERR_NON_FINITE);
+}
+
+// Adam / AdamW, TrainingParameter.java:433-525: m = b1*m + (1-b1)*g; v = b2*v + (1-b2)*(g*g);
+// update = (lr * (m / c1)) / (sqrt(v / c2) + eps), the product formed before the division.
+__global__ void __launch_bounds__(kThreads) adam_kernel(SlotTable table, AdamArgs a, int *error_word) {
+    int t = 0;
+    while (t + 1 < table.count && (int64_t)blockIdx.x >= table.first_block[t + 1]) t++;
+    const TensorSlot s = table.slot[t];
+    int64_t base = ((int64_t)blockIdx.x - table.first_block[t]) * kOptElemsPerBlock;
+    const float one_minus_b1 = __fsub_rn(1.0f, a.b1), one_minus_b2 = __fsub_rn(1.0f, a.b2);
+    bool bad = false;
+    for (int64_t i = base + threadIdx.x; i < base + kOptElemsPerBlock && i < s.count; i += kThreads) {
+        float p = s.p[i], g = s.g[i], basev;
+        if (a.decoupled) basev = __fmul_rn(p, a.decay_factor);
+        else { g = __fadd_rn(g, __fmul_rn(a.decay, p)); basev = p; }
+        float m = __fadd_rn(__fmul_rn(a.b1, s.m[i]), __fmul_rn(one_minus_b1, g));
+        float sq = __fmul_rn(g, g);
+        float v = __fadd_rn(__fmul_rn(a.b2, s.v[i]), __fmul_rn(one_minus_b2, sq));
+        float mh = __fdiv_rn(m, a.correction1), vh = __fdiv_rn(v, a.correction2);
+        float den = __fadd_rn(__fsqrt_rn(vh), a.eps);
+        float num = __fmul_rn(a.lr, mh);
+        float update = __fdiv_rn(num, den);
+        float candidate = __fsub_rn(basev, update);
+        bad |= !finite(p) || !finite(g) || !finite(m) || !finite(sq) || !finite(v) || !finite(mh) || !finite(vh)
+               || !finite(den) || !(den > 0.0f) || !finite(num) || !finite(update) || !finite(candidate);
+        s.p[i] = candidate; s.m[i] = m; s.v[i] = v;
+    }
+    if (bad) atomicOr(error_word, ERR_NON_FINITE);
+}
+
+template <typename K, typename A>
+cudaError_t launch_slots(cudaStream_t s, K kernel, const TensorSlot *slots, int slot_count, const A &args, int *error_word) {
+    for (int first = 0; first < slot_count; first += kMaxSlots) {
+        SlotTable table;
+        table.count = slot_count - first < kMaxSlots ? slot_count - first : kMaxSlots;
+        int64_t blocks = 0;
+        for (int i = 0; i < table.count; i++) {
+            table.slot[i] = slots[first + i];
+            table.first_block[i] = blocks;
+            blocks += (slots[first + i].count + kOptElemsPerBlock - 1) / kOptElemsPerBlock;
+        }
+        table.first_block[table.count] = blocks;
+        if (blocks == 0) continue;
+        kernel<<<(unsigned)blocks, kThreads, 0, s>>>(table, args, error_word);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
+}  // namespace
+
+cudaError_t binary(cudaStream_t s, Op op, const float *a, const float *b, void *out, const Index4 &ix, int64_t total) {
+    if (total == 0) return cudaSuccess;
+    binary_kernel<<<grid_for(total, kThreads), kThreads, 0, s>>>((int)op, a, b, out, ix, total);
+    return cudaGetLastError();
+}
+
+cudaError_t where(cudaStream_t s, const uint8_t *cond, const float *a, const float *b, float *out, const Index4 &ix, int64_t total) {
+    if (total == 0) return cudaSuccess;
+    where_kernel<<<grid_for(total, kThreads), kThreads, 0, s>>>(cond, a, b, out, ix, total);
+    return cudaGetLastError();
+}
+
+cudaError_t scalar_op(cudaStream_t s, Op op, DType dtype, const void *a, void *out, uint64_t scalar_bits, int64_t total) {
+    if (total == 0) return cudaSuccess;
+    int grid = grid_for(total, kThreads);
+    if (dtype == DType::F32) {
+        double d; memcpy(&d, &scalar_bits, 8);
+        scalar_f32_kernel<<<grid, kThreads, 0, s>>>((int)op, (const float *)a, (float *)out, (float)d, total);
+    } else if (dtype == DType::I32) {
+        scalar_kernel<int32_t><<<grid, kThreads, 0, s>>>((int)op, (const int32_t *)a, (int32_t *)out, (int32_t)(int64_t)scalar_bits, total);
+    } else if (dtype == DType::I64) {
+        scalar_kernel<int64_t><<<grid, kThreads, 0, s>>>((int)op, (const int64_t *)a, (int64_t *)out, (int64_t)scalar_bits, total);
+    } else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+cudaError_t unary(cudaStream_t s, Op op, const float *a, float *out, int64_t total) {
+    if (total == 0) return cudaSuccess;
+    unary_kernel<<<grid_for(total, kThreads), kThreads, 0, s>>>((int)op, a, out, total);
+    return cudaGetLastError();
+}
+
+cudaError_t one_hot(cudaStream_t s, DType index_type, const void *indices, uint8_t *out, int64_t count, int64_t depth) {
+    if (count * depth == 0) return cudaSuccess;
+    int grid = grid_for(count * depth, kThreads);
+    if (index_type == DType::I32) one_hot_kernel<int32_t><<<grid, kThreads, 0, s>>>((const int32_t *)indices, out, count, depth);
+    else one_hot_kernel<int64_t><<<grid, kThreads, 0, s>>>((const int64_t *)indices, out, count, depth);
+    return cudaGetLastError();
+}
+
+cudaError_t copy_strided(cudaStream_t s, int element_bytes, const void *src, void *dst, const Index4 &ix, int64_t total) {
+    if (total == 0) return cudaSuccess;
+    int grid = grid_for(total, kThreads);
+    if (element_bytes == 4) copy_kernel<uint32_t><<<grid, kThreads, 0, s>>>((const uint32_t *)src, (uint32_t *)dst, ix, total);
+    else if (element_bytes == 8) copy_kernel<uint64_t><<<grid, kThreads, 0, s>>>((const uint64_t *)src, (uint64_t *)dst, ix, total);
+    else copy_kernel<uint8_t><<<grid, kThreads, 0, s>>>((const uint8_t *)src, (uint8_t *)dst, ix, total);
+    return cudaGetLastError();
+}
+
+cudaError_t row_reduce(cudaStream_t s, Op op, const float *x, float *out, int64_t rows, int64_t cols) {
+    if (rows == 0) return cudaSuccess;
+    row_reduce_kernel<<<grid_for(rows, kThreads / 32), kThreads, 0, s>>>((int)op, x, out, rows, cols);
+    return cudaGetLastError();
+}
+
+cudaError_t full_sum(cudaStream_t s, const float *x, const Index4 &ix, int64_t total, float *out) {
+    full_sum_kernel<<<1, 1024, 0, s>>>(x, ix, total, out);
+    return cudaGetLastError();
+}
+
+cudaError_t argmax_rows(cudaStream_t s, const float *x, int64_t *out, int64_t rows, int64_t cols) {
+    if (rows == 0) return cudaSuccess;
+    argmax_kernel<<<grid_for(rows, kThreads / 32), kThreads, 0, s>>>(x, out, rows, cols);
+    return cudaGetLastError();
+}
+
+cudaError_t softmax_rows(cudaStream_t s, const float *x, float *out, int64_t rows, int64_t cols) {
+    if (rows == 0) return cudaSuccess;
+    softmax_kernel<<<grid_for(rows, kThreads / 32), kThreads, 0, s>>>(x, out, rows, cols);
+    return cudaGetLastError();
+}
+
+cudaError_t mse_mean(cudaStream_t s, const float *p, const float *t, int64_t count, float *out) {
+    mse_kernel<<<1, 1024, 0, s>>>(p, t, count, out);
+    return cudaGetLastError();
+}
+
+cudaError_t relu_backward(cudaStream_t s, const float *gate, const float *upstream, float *out, int64_t total) {
+    if (total == 0) return cudaSuccess;
+    bool aligned = (((uintptr_t)gate | (uintptr_t)upstream | (uintptr_t)out) & 15) == 0;
+    int64_t vec = aligned ? total / 4 : 0;
+    relu_backward_kernel<<<grid_for(aligned ? vec : total, kThreads), kThreads, 0, s>>>(
+        (const float4 *)gate, (const float4 *)upstream, (float4 *)out, vec, gate, upstream, out, total);
+    return cudaGetLastError();
+}
+
+int64_t colsum_partial_count(int64_t rows, int64_t cols) { return colsum_splits(rows, cols) * cols; }
+
+cudaError_t colsum(cudaStream_t s, const float *g, int64_t rows, int64_t cols, double *partials, float *out) {
+    if (cols == 0) return cudaSuccess;
+    int64_t splits = colsum_splits(rows, cols);
+    int64_t rows_per = (rows + splits - 1) / splits;
+    dim3 grid((unsigned)((cols + 127) / 128), (unsigned)splits);
+    colsum_partial_kernel<<<grid, kColsumRows * 32, 0, s>>>(g, rows, cols, rows_per, partials);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    colsum_final_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, s>>>(partials, splits, cols, out);
+    return cudaGetLastError();
+}
+
+cudaError_t cross_entropy(cudaStream_t s, const float *logits, DType label_type, const void *labels, const float *seed,
+                          int64_t rows, int64_t cols, float *row_loss, float *loss_out, float *grad_out, int64_t *argmax_out, int *error_word) {
+    if (rows == 0 || cols == 0) return cudaErrorInvalidValue;
+    int grid = grid_for(rows, kThreads / 32);
+    bool vec = (cols & 3) == 0 && cols >= 128 && cols <= 1024 && (((uintptr_t)logits | (uintptr_t)grad_out) & 15) == 0;
+    bool i32 = label_type == DType::I32;
+#define SYN_CE_VEC(C) do { if (i32) ce_rows_vec_kernel<C, int32_t><<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, (int)cols, row_loss, grad_out, argmax_out, error_word); \
+                           else ce_rows_vec_kernel<C, int64_t><<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, (int)cols, row_loss, grad_out, argmax_out, error_word); } while (0)
+    if (vec) {
+        int chunks = (int)((cols / 4 + 31) / 32);
+        if (chunks <= 1) SYN_CE_VEC(1); else if (chunks <= 2) SYN_CE_VEC(2); else if (chunks <= 4) SYN_CE_VEC(4); else SYN_CE_VEC(8);
+    } else if (i32) ce_rows_generic_kernel<int32_t><<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, cols, row_loss, grad_out, argmax_out, error_word);
+    else ce_rows_generic_kernel<int64_t><<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, cols, row_loss, grad_out, argmax_out, error_word);
+#undef SYN_CE_VEC
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess || !loss_out) return e;
+    mean_kernel<<<1, 1024, 0, s>>>(row_loss, rows, loss_out);
+    return cudaGetLastError();
+}
+
+cudaError_t sgd_step(cudaStream_t s, const TensorSlot *slots, int slot_count, const SgdArgs &args, int *error_word) {
+    return launch_slots(s, sgd_kernel, slots, slot_count, args, error_word);
+}
+cudaError_t adam_step(cudaStream_t s, const TensorSlot *slots, int slot_count, const AdamArgs &args, int *error_word) {
+    return launch_slots(s, adam_kernel, slots, slot_count, args, error_word);
+}
+
+}  // namespace kern
+}  // namespace syn

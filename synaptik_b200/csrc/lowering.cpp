@@ -1,0 +1,587 @@
+// Pattern matching and layout assignment: Program -> Plan (see lowering.hpp for the rules).
+//
+// Step operand meaning per kind:
+//   GEMM           a = left [m,k] view, b = right [k,n] view, bias = [n] or -1, mask = value whose
+//                  sign gates the result (ReLU backward) or -1, out = result (pre-activation, or the
+//                  activation when relu and the pre-activation is not needed), out2 = activation
+//                  when both are stored
+//   BINARY         a, b -> out (op = ADD/SUB/MUL/DIV/GT), right-aligned broadcasting by strides
+//   SCALAR         a -> out (op = SCALAR_MUL/MIN/MAX, scalar_bits)
+//   UNARY          a -> out (op = RELU/EXP)
+//   WHERE          a = condition, b, c -> out
+//   ONE_HOT        a -> out (scalar_bits = depth)
+//   COPY           a (any view) -> out (dense)
+//   ROW_REDUCE     a [m,n] -> out [m] (op = MAX or SUM over the last axis)
+//   FULL_SUM       a -> out scalar
+//   COLSUM         a [m,n] -> out [n]
+//   SOFTMAX        a [m,n] -> out
+//   CROSS_ENTROPY  a = logits [m,n], b = labels [m], c = seed scalar or -1 -> out = mean loss or -1,
+//                  out2 = gradient wrt logits or -1
+//   MSE            a, b -> out scalar
+//   ARG_MAX        a [m,n] -> out [m] INT64
+//   RELU_BACKWARD  a = gate source, b = upstream gradient -> out
+#include "lowering.hpp"
+
+#include <algorithm>
+#include <cstring>
+#include <map>
+#include <set>
+#include <sstream>
+
+namespace syn {
+
+bool View::dense() const {
+    auto d = dense_strides(shape);
+    for (size_t i = 0; i < shape.size(); i++) if (shape[i] != 1 && strides[i] != d[i]) return false;
+    return true;
+}
+
+const char *step_name(StepKind k) {
+    switch (k) {
+        case StepKind::GEMM: return "gemm"; case StepKind::BINARY: return "binary"; case StepKind::SCALAR: return "scalar";
+        case StepKind::UNARY: return "unary"; case StepKind::WHERE: return "where"; case StepKind::ONE_HOT: return "one_hot";
+        case StepKind::COPY: return "copy"; case StepKind::ROW_REDUCE: return "row_reduce"; case StepKind::FULL_SUM: return "full_sum";
+        case StepKind::COLSUM: return "colsum"; case StepKind::SOFTMAX: return "softmax"; case StepKind::CROSS_ENTROPY: return "cross_entropy";
+        case StepKind::MSE: return "mse"; case StepKind::ARG_MAX: return "arg_max"; case StepKind::RELU_BACKWARD: return "relu_backward";
+    }
+    return "?";
+}
+
+bool tensor_core_eligible(int64_t m, int64_t n, int64_t k) { return m >= 64 && n >= 64 && k >= 8; }
+bool tensor_core_preferred(int64_t m, int64_t n, int64_t k) {
+    return tensor_core_eligible(m, n, k) && m >= 128 && k >= 32 && (double)m * (double)n * (double)k >= 64.0 * 1024 * 1024;
+}
+
+namespace {
+
+struct Matcher {
+    Program &g;
+    explicit Matcher(Program &p) : g(p) {}
+    const Node *producer(int v, Op op) const {
+        int p = g.values[v].producer;
+        return p >= 0 && g.nodes[p].op == op ? &g.nodes[p] : nullptr;
+    }
+    int producer_index(int v) const { return g.values[v].producer; }
+    // Follows view-only nodes down to a splat constant; returns the constant's value id or -1.
+    int splat_source(int v) const {
+        for (int guard = 0; guard < 16; guard++) {
+            const Value &val = g.values[v];
+            if (val.role == Role::CONSTANT) return v;
+            int p = val.producer;
+            if (p < 0) return -1;
+            Op op = g.nodes[p].op;
+            if (op != Op::EXPAND && op != Op::EXPAND_DIMS && op != Op::CONTIGUOUS) return -1;
+            v = g.nodes[p].inputs[0];
+        }
+        return -1;
+    }
+    bool is_splat(int v, double x) const {
+        int c = splat_source(v);
+        if (c < 0) return false;
+        const Value &val = g.values[c];
+        return val.dtype == DType::F32 ? val.constant_f64() == x : (double)val.constant_i64() == x;
+    }
+    bool only_consumer(int v, int node) const {
+        const Value &val = g.values[v];
+        return val.publication < 0 && val.consumers.size() == 1 && val.consumers[0] == node;
+    }
+};
+
+struct LinearGroup {          // MATMUL [-> ADD bias] [-> RELU] [-> gate by WHERE(GT(.,0),.,0)]
+    int matmul = -1, add = -1, relu = -1, where = -1, gt = -1;
+    int bias = -1, mask = -1;
+    int out = -1, out2 = -1;
+    int emit_at = -1;
+};
+
+struct CrossEntropyGroup {
+    int logits = -1, labels = -1, seed = -1, loss = -1, grad = -1;
+    std::set<int> nodes;
+    int emit_at = -1;
+};
+
+bool match_ce_backward(Matcher &mt, int mul_index, CrossEntropyGroup &ce) {
+    Program &g = mt.g;
+    const Node &mul = g.nodes[mul_index];
+    if (mul.op != Op::MUL) return false;
+    for (int order = 0; order < 2; order++) {
+        int lhs = mul.inputs[order], rhs = mul.inputs[1 - order];
+        const Node *sub = mt.producer(lhs, Op::SUB);
+        if (!sub) continue;
+        std::set<int> extra;
+        auto through_expand = [&](int v) {      // explicit broadcast nodes are optional in the chain
+            while (const Node *ex = mt.producer(v, Op::EXPAND)) { extra.insert(mt.producer_index(v)); v = ex->inputs[0]; }
+            return v;
+        };
+        int p = sub->inputs[0], hot = through_expand(sub->inputs[1]);
+        const Node *div = mt.producer(p, Op::DIV);
+        if (!div) continue;
+        int e = div->inputs[0], s = through_expand(div->inputs[1]);
+        const Node *expn = mt.producer(e, Op::EXP);
+        const Node *sumn = mt.producer(s, Op::SUM);
+        if (!expn || !sumn || sumn->inputs[0] != e || sumn->attr_i(0) != 1 || !sumn->attr_i(1)) continue;
+        const Node *shift = mt.producer(expn->inputs[0], Op::SUB);
+        if (!shift) continue;
+        int logits = shift->inputs[0], mx = through_expand(shift->inputs[1]);
+        const Node *maxn = mt.producer(mx, Op::MAX);
+        if (!maxn || maxn->inputs[0] != logits || maxn->attr_i(0) != 1 || !maxn->attr_i(1)) continue;
+        if (g.values[logits].shape.size() != 2) continue;
+        int64_t rows = g.values[logits].shape[0], classes = g.values[logits].shape[1];
+        const Node *where = mt.producer(hot, Op::WHERE);
+        if (!where || !mt.is_splat(where->inputs[1], 1.0) || !mt.is_splat(where->inputs[2], 0.0)) continue;
+        const Node *onehot = mt.producer(where->inputs[0], Op::ONE_HOT);
+        if (!onehot || onehot->attr_i(0) != classes) continue;
+        int labels = onehot->inputs[0];
+        std::set<int> nodes = {mul_index, mt.producer_index(lhs), mt.producer_index(p), mt.producer_index(e),
+                               mt.producer_index(s), mt.producer_index(expn->inputs[0]), mt.producer_index(mx),
+                               mt.producer_index(hot), mt.producer_index(where->inputs[0])};
+        nodes.insert(extra.begin(), extra.end());
+        if (const Node *smin = mt.producer(labels, Op::SCALAR_MIN)) {
+            const Node *smax = mt.producer(smin->inputs[0], Op::SCALAR_MAX);
+            if (smin->attr_i(0) != classes - 1 || !smax || smax->attr_i(0) != 0) continue;
+            nodes.insert(mt.producer_index(labels));
+            nodes.insert(mt.producer_index(smin->inputs[0]));
+            labels = smax->inputs[0];
+        }
+        if (g.values[labels].shape.size() != 1 || g.values[labels].shape[0] != rows) continue;
+        // rhs: [EXPAND] <- EXPAND_DIMS(axis 1) <- DIV(EXPAND(seed), count)
+        int scale = rhs;
+        if (const Node *ex = mt.producer(scale, Op::EXPAND)) { nodes.insert(mt.producer_index(scale)); scale = ex->inputs[0]; }
+        const Node *ed = mt.producer(scale, Op::EXPAND_DIMS);
+        if (!ed || ed->attr_i(0) != 1) continue;
+        nodes.insert(mt.producer_index(scale));
+        scale = ed->inputs[0];
+        const Node *sdiv = mt.producer(scale, Op::DIV);
+        if (!sdiv) continue;
+        nodes.insert(mt.producer_index(scale));
+        int seed = sdiv->inputs[0], count = sdiv->inputs[1];
+        if (const Node *ex = mt.producer(seed, Op::EXPAND)) { nodes.insert(mt.producer_index(seed)); seed = ex->inputs[0]; }
+        if (g.values[seed].elements() != 1 || g.values[seed].dtype != DType::F32) continue;
+        // count is either already folded to the splat constant `rows` or SUM over ones
+        if (!mt.is_splat(count, (double)rows)) {
+            const Node *csum = mt.producer(count, Op::SUM);
+            if (!csum || csum->attr_i(0) != -1 || !mt.is_splat(csum->inputs[0], 1.0) || g.values[csum->inputs[0]].elements() != rows) continue;
+            nodes.insert(mt.producer_index(count));
+        }
+        // every value produced inside the chain (other than the gradient) must stay inside it;
+        // view-only nodes over constants cost nothing and may be shared, so they are not claimed
+        bool closed = true;
+        std::set<int> claimed;
+        for (int n : nodes) {
+            const Node &node = g.nodes[n];
+            bool view_of_constant = (node.op == Op::EXPAND || node.op == Op::EXPAND_DIMS || node.op == Op::CONTIGUOUS)
+                                    && mt.splat_source(node.outputs[0]) >= 0;
+            if (view_of_constant) continue;
+            claimed.insert(n);
+        }
+        for (int n : claimed) {
+            if (n == mul_index) continue;
+            for (int v : g.nodes[n].outputs) {
+                if (g.values[v].publication >= 0) closed = false;
+                for (int c : g.values[v].consumers) if (!nodes.count(c)) closed = false;
+            }
+        }
+        if (!closed) continue;
+        ce.logits = logits; ce.labels = labels; ce.seed = seed; ce.grad = mul.outputs[0];
+        ce.nodes = claimed;
+        return true;
+    }
+    return false;
+}
+
+}  // namespace
+
+Status lower_program(const Program &source, const LoweringOptions &options, Plan &plan, std::string &message) {
+    Program g = source;     // GT predicates may be re-pointed at stored activations
+    Matcher mt(g);
+    const int node_count = (int)g.nodes.size();
+    std::vector<int> covered(node_count, 0);
+    std::map<int, std::vector<Step>> emit_at;
+
+    auto choose_engine = [&](int64_t m, int64_t n, int64_t k) {
+        bool tc = options.gemm_engine == 1 ? false : options.gemm_engine == 2 ? tensor_core_eligible(m, n, k) : tensor_core_preferred(m, n, k);
+        return tc ? GemmEngine::TENSOR_CORE : GemmEngine::EXACT_SIMT;
+    };
+
+    // ---- linear groups ---------------------------------------------------------------------
+    std::vector<LinearGroup> linear;
+    std::map<int, int> group_of_matmul_output;      // result value -> group index
+    for (int i = 0; i < node_count; i++) {
+        const Node &mm = g.nodes[i];
+        if (mm.op != Op::MATMUL) continue;
+        LinearGroup lg;
+        lg.matmul = i;
+        lg.emit_at = i;
+        int z = mm.outputs[0];
+        int64_t n = g.values[z].shape[1];
+        if (g.values[z].publication < 0 && g.values[z].consumers.size() == 1) {
+            int c = g.values[z].consumers[0];
+            const Node &add = g.nodes[c];
+            if (add.op == Op::ADD && g.values[add.outputs[0]].shape == g.values[z].shape) {
+                int other = add.inputs[0] == z ? add.inputs[1] : add.inputs[0];
+                const Value &bv = g.values[other];
+                bool row_bias = other != z && bv.elements() == n && !bv.shape.empty() && bv.shape.back() == n
+                                && bv.dtype == DType::F32 && (bv.role != Role::INTERMEDIATE ? true : bv.producer < i);
+                if (row_bias && (add.inputs[0] == z || add.inputs[1] == z)) {
+                    lg.add = c; lg.bias = other; lg.emit_at = c;
+                    z = add.outputs[0];
+                }
+            }
+        }
+        lg.out = z;
+        // activation
+        int relu_node = -1;
+        for (int c : g.values[z].consumers) if (g.nodes[c].op == Op::RELU) { relu_node = c; break; }
+        if (relu_node >= 0) {
+            int y = g.nodes[relu_node].outputs[0];
+            bool z_needed = g.values[z].publication >= 0;
+            std::vector<int> predicates;
+            for (int c : g.values[z].consumers) {
+                if (c == relu_node) continue;
+                const Node &u = g.nodes[c];
+                if (u.op == Op::GT && u.inputs[0] == z && mt.is_splat(u.inputs[1], 0.0)) predicates.push_back(c);
+                else z_needed = true;
+            }
+            lg.relu = relu_node;
+            if (!z_needed) {
+                for (int c : predicates) {
+                    g.nodes[c].inputs[0] = y;
+                    g.values[y].consumers.push_back(c);
+                }
+                g.values[z].consumers.assign(1, relu_node);
+                lg.out = y;
+            } else {
+                lg.out2 = y;
+            }
+        }
+        if (lg.add < 0 && lg.relu < 0) group_of_matmul_output[mm.outputs[0]] = (int)linear.size();
+        linear.push_back(lg);
+    }
+
+    // ---- ReLU backward: WHERE(GT(z, 0), g, 0) ----------------------------------------------
+    std::vector<Step> relu_backward_steps;
+    for (int i = 0; i < node_count; i++) {
+        const Node &w = g.nodes[i];
+        if (w.op != Op::WHERE || !mt.is_splat(w.inputs[2], 0.0)) continue;
+        const Node *gt = mt.producer(w.inputs[0], Op::GT);
+        if (!gt || !mt.is_splat(gt->inputs[1], 0.0)) continue;
+        int gate = gt->inputs[0], upstream = w.inputs[1], result = w.outputs[0];
+        if (g.values[gate].shape != g.values[result].shape || g.values[upstream].shape != g.values[result].shape) continue;
+        int gt_index = mt.producer_index(w.inputs[0]);
+        bool own_gt = mt.only_consumer(w.inputs[0], i);
+        // fold into the producing GEMM when the upstream gradient has no other reader
+        auto it = group_of_matmul_output.find(upstream);
+        if (it != group_of_matmul_output.end() && mt.only_consumer(upstream, i)) {
+            LinearGroup &lg = linear[it->second];
+            if (lg.add < 0 && lg.relu < 0 && lg.where < 0 && g.values[gate].producer < i) {
+                lg.where = i; lg.mask = gate; lg.out = result; lg.emit_at = i;
+                if (own_gt) lg.gt = gt_index;
+                continue;
+            }
+        }
+        Step st;
+        st.kind = StepKind::RELU_BACKWARD; st.a = gate; st.b = upstream; st.out = result;
+        st.nodes = {i};
+        covered[i] = 1;
+        if (own_gt) { covered[gt_index] = 1; st.nodes.push_back(gt_index); }
+        emit_at[i].push_back(st);
+    }
+
+    for (const LinearGroup &lg : linear) {
+        const Node &mm = g.nodes[lg.matmul];
+        Step st;
+        st.kind = StepKind::GEMM;
+        st.a = mm.inputs[0]; st.b = mm.inputs[1];
+        st.m = g.values[st.a].shape[0]; st.k = g.values[st.a].shape[1]; st.n = g.values[st.b].shape[1];
+        st.bias = lg.bias; st.mask = lg.mask; st.relu = lg.relu >= 0;
+        st.out = lg.out; st.out2 = lg.out2;
+        st.engine = choose_engine(st.m, st.n, st.k);
+        for (int n : {lg.matmul, lg.add, lg.relu, lg.where, lg.gt}) if (n >= 0) { covered[n] = 1; st.nodes.push_back(n); }
+        emit_at[lg.emit_at].push_back(st);
+    }
+
+    // ---- cross entropy ---------------------------------------------------------------------
+    std::vector<CrossEntropyGroup> ces;
+    for (int i = 0; i < node_count; i++) {
+        if (covered[i] || g.nodes[i].op != Op::MUL) continue;
+        CrossEntropyGroup ce;
+        if (!match_ce_backward(mt, i, ce)) continue;
+        bool clash = false;
+        for (int n : ce.nodes) clash |= covered[n] != 0;
+        if (clash) continue;
+        ces.push_back(ce);
+        for (int n : ce.nodes) covered[n] = 1;
+    }
+    for (int i = 0; i < node_count; i++) {
+        const Node &n = g.nodes[i];
+        if (n.op != Op::INDEX_CROSS_ENTROPY || covered[i]) continue;
+        CrossEntropyGroup *host = nullptr;
+        for (auto &ce : ces) if (ce.loss < 0 && ce.logits == n.inputs[0] && ce.labels == n.inputs[1]) { host = &ce; break; }
+        if (!host) { ces.emplace_back(); host = &ces.back(); host->logits = n.inputs[0]; host->labels = n.inputs[1]; }
+        host->loss = n.outputs[0];
+        host->nodes.insert(i);
+        covered[i] = 1;
+    }
+    for (auto &ce : ces) {
+        int first = *ce.nodes.begin();
+        auto defined_before = [&](int v) { return v < 0 || g.values[v].producer < first; };
+        if (!defined_before(ce.logits) || !defined_before(ce.labels) || !defined_before(ce.seed)) {
+            message = "cross-entropy inputs are produced after the loss chain starts";
+            return GRAPH_COMPILATION_FAILED;
+        }
+        Step st;
+        st.kind = StepKind::CROSS_ENTROPY;
+        st.a = ce.logits; st.b = ce.labels; st.c = ce.seed; st.out = ce.loss; st.out2 = ce.grad;
+        st.m = g.values[ce.logits].shape[0]; st.n = g.values[ce.logits].shape[1];
+        st.nodes.assign(ce.nodes.begin(), ce.nodes.end());
+        emit_at[first].push_back(st);
+    }
+
+    // ---- dead nodes: whatever no launch, view or publication still reads (e.g. the ones tensor
+    // that only the fused loss chain counted) is dropped ----------------------------------------
+    {
+        std::vector<char> needed(g.values.size(), 0);
+        for (int v : g.publications) needed[v] = 1;
+        for (auto &entry : emit_at) for (const Step &st : entry.second)
+            for (int v : {st.a, st.b, st.c, st.bias, st.mask}) if (v >= 0) needed[v] = 1;
+        for (int i = node_count - 1; i >= 0; i--) {
+            if (covered[i]) continue;
+            bool live = false;
+            for (int v : g.nodes[i].outputs) live |= needed[v] != 0;
+            if (!live) { covered[i] = 1; continue; }
+            for (int v : g.nodes[i].inputs) needed[v] = 1;
+        }
+    }
+
+    // ---- layout assignment and per-node steps ------------------------------------------------
+    plan = Plan();
+    plan.views.resize(g.values.size());
+    std::vector<char> assigned(g.values.size(), 0);
+    auto new_scratch = [&](const Value &v) {
+        plan.scratch_bytes.push_back(std::max<int64_t>(v.elements(), 1) * dtype_bytes(v.dtype));
+        return (int)plan.scratch_bytes.size() - 1;
+    };
+    for (size_t i = 0; i < g.values.size(); i++) {
+        const Value &v = g.values[i];
+        View &w = plan.views[i];
+        w.shape = v.shape; w.dtype = v.dtype;
+        if (v.role == Role::FEED) { w.slot = SlotKind::FEED; w.index = v.feed; w.offset = v.offset; w.strides = v.strides; assigned[i] = 1; }
+        else if (v.role == Role::CONSTANT) {
+            w.slot = SlotKind::CONSTANT; w.index = (int)plan.constant_values.size(); w.strides.assign(v.shape.size(), 0);
+            plan.constant_values.push_back((int)i); assigned[i] = 1;
+        }
+    }
+    // a MATMUL read only by a published PERMUTE writes straight into that publication, transposed
+    std::map<int, int> transposed_into;     // value -> publication index
+    for (int i = 0; i < node_count; i++) {
+        const Node &pn = g.nodes[i];
+        if (pn.op != Op::PERMUTE || g.values[pn.outputs[0]].publication < 0) continue;
+        int v = pn.inputs[0];
+        if (g.values[v].shape.size() == 2 && pn.attr_i(0) == 1 && pn.attr_i(1) == 0 && mt.only_consumer(v, i)
+            && g.values[v].producer >= 0 && g.nodes[g.values[v].producer].op == Op::MATMUL)
+            transposed_into[v] = g.values[pn.outputs[0]].publication;
+    }
+    auto assign_output = [&](int v) {
+        if (assigned[v]) return;
+        const Value &val = g.values[v];
+        View &w = plan.views[v];
+        auto t = transposed_into.find(v);
+        if (t != transposed_into.end()) {
+            w.slot = SlotKind::PUBLICATION; w.index = t->second; w.offset = 0;
+            w.strides = {1, val.shape[0]};
+        } else if (val.publication >= 0) {
+            w.slot = SlotKind::PUBLICATION; w.index = val.publication; w.offset = 0; w.strides = dense_strides(val.shape);
+        } else {
+            w.slot = SlotKind::SCRATCH; w.index = new_scratch(val); w.offset = 0; w.strides = dense_strides(val.shape);
+        }
+        assigned[v] = 1;
+    };
+    std::vector<char> published_done(g.publications.size(), 0);
+    auto finish_step = [&](Step st) {
+        for (int v : {st.out, st.out2}) if (v >= 0) {
+            const View &w = plan.views[v];
+            if (w.slot == SlotKind::PUBLICATION) { st.ready_publications.push_back(w.index); published_done[w.index] = 1; }
+        }
+        plan.steps.push_back(st);
+    };
+    auto dense_input = [&](int v) -> int {     // row kernels need dense operands; copy a view when they are not
+        if (plan.views[v].dense()) return v;
+        message = "non-dense operand of a row kernel";
+        return -1;
+    };
+
+    for (int i = 0; i < node_count; i++) {
+        auto pending = emit_at.find(i);
+        if (pending != emit_at.end()) for (Step st : pending->second) {
+            for (int v : {st.out, st.out2}) if (v >= 0) assign_output(v);
+            if (st.kind == StepKind::GEMM) {
+                const View &c = plan.views[st.out];
+                bool transposed = c.strides.size() == 2 && c.strides[0] == 1 && c.shape[0] != 1 && c.strides[1] != 1;
+                if (transposed && (st.bias >= 0 || st.mask >= 0 || st.relu)) { message = "transposed GEMM result with an epilogue"; return UNSUPPORTED_SHAPE; }
+                const View &a = plan.views[st.a], &b = plan.views[st.b];
+                bool a_ok = a.strides[0] == 1 || a.strides[1] == 1 || a.shape[0] == 1 || a.shape[1] == 1;
+                bool b_ok = b.strides[0] == 1 || b.strides[1] == 1 || b.shape[0] == 1 || b.shape[1] == 1;
+                if (!a_ok || !b_ok) st.engine = GemmEngine::EXACT_SIMT;
+                if (st.bias >= 0 && !plan.views[st.bias].dense()) { message = "strided bias"; return UNSUPPORTED_SHAPE; }
+                if (st.mask >= 0 && !plan.views[st.mask].dense()) { message = "strided gate"; return UNSUPPORTED_SHAPE; }
+            } else if (st.kind == StepKind::CROSS_ENTROPY) {
+                if (dense_input(st.a) < 0 || dense_input(st.b) < 0) return UNSUPPORTED_SHAPE;
+            } else if (st.kind == StepKind::RELU_BACKWARD) {
+                if (dense_input(st.a) < 0 || dense_input(st.b) < 0) return UNSUPPORTED_SHAPE;
+            }
+            finish_step(st);
+        }
+        if (covered[i]) continue;
+        const Node &n = g.nodes[i];
+        int in0 = n.inputs.empty() ? -1 : n.inputs[0];
+        int out0 = n.outputs[0];
+        const Value &ov = g.values[out0];
+        Step st;
+        st.nodes = {i};
+        st.op = n.op;
+        switch (n.op) {
+            case Op::PERMUTE: case Op::EXPAND: case Op::EXPAND_DIMS: case Op::CONTIGUOUS: {
+                const View &src = plan.views[in0];
+                View w;
+                w.slot = src.slot; w.index = src.index; w.offset = src.offset; w.dtype = src.dtype; w.shape = ov.shape;
+                size_t r = ov.shape.size();
+                w.strides.assign(r, 0);
+                if (n.op == Op::PERMUTE) for (size_t d = 0; d < r; d++) w.strides[d] = src.strides[n.attrs[d]];
+                else if (n.op == Op::EXPAND) {
+                    size_t lead = r - src.shape.size();
+                    for (size_t d = 0; d < src.shape.size(); d++) w.strides[lead + d] = src.shape[d] == 1 && ov.shape[lead + d] != 1 ? 0 : src.strides[d];
+                } else if (n.op == Op::EXPAND_DIMS) {
+                    size_t axis = (size_t)n.attrs[0];
+                    for (size_t d = 0, s = 0; d < r; d++) w.strides[d] = d == axis ? 0 : src.strides[s++];
+                } else w.strides = src.strides;
+                bool needs_copy = n.op == Op::CONTIGUOUS && !w.dense();
+                if (!needs_copy && ov.publication < 0) { plan.views[out0] = w; assigned[out0] = 1; break; }
+                if (!needs_copy && ov.publication >= 0 && w.slot == SlotKind::PUBLICATION && w.index == ov.publication && w.dense() && w.offset == 0) {
+                    plan.views[out0] = w; assigned[out0] = 1; break;     // already written in place, transposed
+                }
+                // materialise: register the view under a private value id, then copy it out
+                plan.views.push_back(w);
+                assign_output(out0);
+                st.kind = StepKind::COPY; st.a = (int)plan.views.size() - 1; st.out = out0;
+                finish_step(st);
+                break;
+            }
+            case Op::MATMUL: message = "internal: MATMUL not grouped"; return INTERNAL_ERROR;
+            case Op::ADD: case Op::SUB: case Op::MUL: case Op::DIV: case Op::GT:
+                assign_output(out0);
+                st.kind = StepKind::BINARY; st.a = n.inputs[0]; st.b = n.inputs[1]; st.out = out0;
+                finish_step(st);
+                break;
+            case Op::SCALAR_MUL: case Op::SCALAR_MIN: case Op::SCALAR_MAX:
+                assign_output(out0);
+                st.kind = StepKind::SCALAR; st.a = in0; st.out = out0; st.scalar_bits = n.attrs[0];
+                finish_step(st);
+                break;
+            case Op::RELU: case Op::EXP:
+                assign_output(out0);
+                st.kind = StepKind::UNARY; st.a = in0; st.out = out0;
+                finish_step(st);
+                break;
+            case Op::WHERE:
+                assign_output(out0);
+                st.kind = StepKind::WHERE; st.a = n.inputs[0]; st.b = n.inputs[1]; st.c = n.inputs[2]; st.out = out0;
+                finish_step(st);
+                break;
+            case Op::ONE_HOT:
+                if (dense_input(in0) < 0) return UNSUPPORTED_SHAPE;
+                assign_output(out0);
+                st.kind = StepKind::ONE_HOT; st.a = in0; st.out = out0; st.scalar_bits = n.attrs[0];
+                st.m = g.values[in0].elements(); st.n = (int64_t)n.attrs[0];
+                finish_step(st);
+                break;
+            case Op::MAX: case Op::SUM: {
+                assign_output(out0);
+                st.a = in0; st.out = out0;
+                if ((int64_t)n.attrs[0] == -1) {
+                    st.kind = StepKind::FULL_SUM; st.m = g.values[in0].elements();
+                } else {
+                    if (dense_input(in0) < 0) return UNSUPPORTED_SHAPE;
+                    st.kind = StepKind::ROW_REDUCE; st.n = g.values[in0].shape.back(); st.m = g.values[in0].elements() / std::max<int64_t>(st.n, 1);
+                }
+                finish_step(st);
+                break;
+            }
+            case Op::SUM_TO_SHAPE:
+                if (dense_input(in0) < 0) return UNSUPPORTED_SHAPE;
+                assign_output(out0);
+                st.kind = StepKind::COLSUM; st.a = in0; st.out = out0; st.m = g.values[in0].shape[0]; st.n = g.values[in0].shape[1];
+                finish_step(st);
+                break;
+            case Op::SOFTMAX:
+                if (dense_input(in0) < 0) return UNSUPPORTED_SHAPE;
+                assign_output(out0);
+                st.kind = StepKind::SOFTMAX; st.a = in0; st.out = out0;
+                st.n = g.values[in0].shape.back(); st.m = g.values[in0].elements() / std::max<int64_t>(st.n, 1);
+                finish_step(st);
+                break;
+            case Op::INDEX_CROSS_ENTROPY: message = "internal: loss not grouped"; return INTERNAL_ERROR;
+            case Op::MEAN_SQUARED_ERROR:
+                if (dense_input(n.inputs[0]) < 0 || dense_input(n.inputs[1]) < 0) return UNSUPPORTED_SHAPE;
+                assign_output(out0);
+                st.kind = StepKind::MSE; st.a = n.inputs[0]; st.b = n.inputs[1]; st.out = out0; st.m = g.values[n.inputs[0]].elements();
+                finish_step(st);
+                break;
+            case Op::ARG_MAX:
+                if (dense_input(in0) < 0) return UNSUPPORTED_SHAPE;
+                assign_output(out0);
+                st.kind = StepKind::ARG_MAX; st.a = in0; st.out = out0; st.m = g.values[in0].shape[0]; st.n = g.values[in0].shape[1];
+                finish_step(st);
+                break;
+        }
+    }
+    // publications that are views of something else (a feed, a shared intermediate) are copied out
+    for (size_t j = 0; j < g.publications.size(); j++) {
+        if (published_done[j]) continue;
+        int v = g.publications[j];
+        const View &w = plan.views[v];
+        if (!assigned[v]) { message = "publication was never produced"; return INTERNAL_ERROR; }
+        View target;
+        target.slot = SlotKind::PUBLICATION; target.index = (int)j; target.offset = 0; target.dtype = w.dtype;
+        target.shape = w.shape; target.strides = dense_strides(w.shape);
+        plan.views.push_back(target);
+        Step st;
+        st.kind = StepKind::COPY; st.a = v; st.out = (int)plan.views.size() - 1;
+        st.ready_publications.push_back((int)j);
+        plan.steps.push_back(st);
+    }
+    return OK;
+}
+
+std::string describe_plan(const Program &g, const Plan &plan) {
+    std::ostringstream os;
+    for (const Step &st : plan.steps) {
+        os << step_name(st.kind);
+        if (st.kind == StepKind::GEMM) {
+            os << " engine=" << (st.engine == GemmEngine::TENSOR_CORE ? "tcgen05_3xtf32" : "exact_simt")
+               << " m=" << st.m << " n=" << st.n << " k=" << st.k;
+            if (st.bias >= 0) os << " bias";
+            if (st.relu) os << " relu";
+            if (st.out2 >= 0) os << " keep_preactivation";
+            if (st.mask >= 0) os << " relu_gate";
+            const View &c = plan.views[st.out];
+            if (c.strides.size() == 2 && c.strides[0] == 1 && c.shape[0] != 1 && c.strides[1] != 1) os << " transposed_result";
+        } else if (st.kind == StepKind::BINARY || st.kind == StepKind::SCALAR || st.kind == StepKind::UNARY || st.kind == StepKind::ROW_REDUCE) {
+            os << " op=" << op_name(st.op);
+        } else if (st.kind == StepKind::CROSS_ENTROPY) {
+            os << " rows=" << st.m << " classes=" << st.n << (st.out >= 0 ? " loss" : "") << (st.out2 >= 0 ? " gradient" : "");
+        }
+        if (st.kind != StepKind::GEMM && st.kind != StepKind::CROSS_ENTROPY && st.m) os << " m=" << st.m << " n=" << st.n;
+        os << " nodes=[";
+        for (size_t i = 0; i < st.nodes.size(); i++) os << (i ? "," : "") << op_name(g.nodes[st.nodes[i]].op);
+        os << "]";
+        if (!st.ready_publications.empty()) {
+            os << " publishes=[";
+            for (size_t i = 0; i < st.ready_publications.size(); i++) os << (i ? "," : "") << st.ready_publications[i];
+            os << "]";
+        }
+        os << "\n";
+    }
+    return os.str();
+}
+
+}  // namespace syn

@@ -1,0 +1,988 @@
+// Host runtime behind the C ABI: contexts, buffers, prepared executables, the device-resident
+// optimizer and the data-parallel communicator.  Handles are tagged structs so a handle of the
+// wrong family is rejected instead of being dereferenced as the wrong type (the Metal library
+// does the same, modules/backend/metal/macos-arm64/README.md "Status values": 10).
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/synaptik_cuda.h"
+#include "kernels.hpp"
+#include "lowering.hpp"
+#include "program.hpp"
+
+using namespace syn;
+
+namespace {
+
+enum : uint32_t { TAG_CONTEXT = 0x58544353u, TAG_BUFFER = 0x46554253u, TAG_EXECUTABLE = 0x45584553u,
+                  TAG_OPTIMIZER = 0x54504f53u, TAG_COMM = 0x4d4f4353u };
+
+struct Context {
+    uint32_t tag = TAG_CONTEXT;
+    int device = 0;
+    int sm_count = 148;
+    cudaStream_t stream = nullptr, comm_stream = nullptr;
+    int *error_dev = nullptr;       // device-side error word shared by all kernels of the context
+    int *error_host = nullptr;      // pinned mirror
+    int gemm_engine = 0;
+    int time_steps = 0;
+    cudaEvent_t timer_start = nullptr, timer_stop = nullptr;
+    std::mutex mutex;
+};
+
+struct Buffer {
+    uint32_t tag = TAG_BUFFER;
+    Context *ctx = nullptr;
+    void *ptr = nullptr;
+    uint64_t bytes = 0;
+};
+
+// ---- NCCL, bound at run time so the library loads (and inference runs) without it ---------------
+struct NcclApi {
+    typedef struct { char internal[128]; } UniqueId;
+    int (*GetUniqueId)(UniqueId *) = nullptr;
+    int (*CommInitRank)(void **, int, UniqueId, int) = nullptr;
+    int (*CommDestroy)(void *) = nullptr;
+    int (*AllReduce)(const void *, void *, size_t, int, int, void *, cudaStream_t) = nullptr;
+    int (*GroupStart)() = nullptr;
+    int (*GroupEnd)() = nullptr;
+    bool ok = false;
+};
+
+NcclApi &nccl() {
+    static NcclApi api;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD | RTLD_GLOBAL);   // the copy the process already uses, if any
+        const char *env = getenv("SYNAPTIK_NCCL_LIBRARY");
+        if (!h && env && env[0]) h = dlopen(env, RTLD_NOW | RTLD_GLOBAL);
+        if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) return;
+        api.GetUniqueId = (decltype(api.GetUniqueId))dlsym(h, "ncclGetUniqueId");
+        api.CommInitRank = (decltype(api.CommInitRank))dlsym(h, "ncclCommInitRank");
+        api.CommDestroy = (decltype(api.CommDestroy))dlsym(h, "ncclCommDestroy");
+        api.AllReduce = (decltype(api.AllReduce))dlsym(h, "ncclAllReduce");
+        api.GroupStart = (decltype(api.GroupStart))dlsym(h, "ncclGroupStart");
+        api.GroupEnd = (decltype(api.GroupEnd))dlsym(h, "ncclGroupEnd");
+        api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllReduce && api.GroupStart && api.GroupEnd;
+    });
+    return api;
+}
+
+struct Comm {
+    uint32_t tag = TAG_COMM;
+    Context *ctx = nullptr;
+    void *comm = nullptr;
+    int world = 1, rank = 0;
+};
+
+struct Planes { float *hi = nullptr, *lo = nullptr; int64_t rows = 0, kp = 0; int last_run = -1; };
+
+struct StepExec {
+    kern::TensorCoreGemm *tc = nullptr;
+    int planes_p = -1, planes_q = -1;       // indices into Executable::planes
+    bool swapped = false;                   // result stored transposed: roles of the operands exchanged
+    double *colsum_partials = nullptr;
+    float *row_loss = nullptr;
+};
+
+struct Executable {
+    uint32_t tag = TAG_EXECUTABLE;
+    Context *ctx = nullptr;
+    Program program;
+    Plan plan;
+    std::vector<void *> scratch;
+    void *constants = nullptr;              // 8 bytes per constant slot
+    std::vector<Planes> planes;
+    std::map<std::pair<int, int>, int> plane_index;     // (value id, orientation) -> planes
+    std::vector<StepExec> exec;
+    std::vector<void *> owned;              // every device allocation, for release
+    std::vector<uint64_t> feed_bytes, publication_bytes;
+    cudaEvent_t start = nullptr, stop = nullptr;
+    bool timed = false;
+    uint64_t launches = 0;
+    int run_counter = 0;
+    Comm *comm = nullptr;
+    std::vector<char> sync_publication;     // per publication: all-reduce it
+    std::vector<cudaEvent_t> ready_events;
+    std::vector<cudaEvent_t> step_events;   // two per plan step when the context times steps
+    bool steps_timed = false;
+    cudaEvent_t comm_done = nullptr;
+    bool pending = false;
+};
+
+struct Optimizer {
+    uint32_t tag = TAG_OPTIMIZER;
+    Context *ctx = nullptr;
+    int kind = 0;
+    double hyper[5] = {0, 0, 0, 0, 0};
+    std::vector<Buffer *> params;
+    std::vector<uint64_t> counts;
+    std::vector<float *> m, v;
+    uint64_t steps = 0;
+    bool pending = false;
+};
+
+template <typename T> T *as(void *h, uint32_t tag) {
+    if (!h) return nullptr;
+    T *p = reinterpret_cast<T *>(h);
+    return p->tag == tag ? p : nullptr;
+}
+
+int32_t cuda_status(cudaError_t e, int32_t fallback) {
+    if (e == cudaSuccess) return OK;
+    if (e == cudaErrorMemoryAllocation) return ALLOCATION_FAILED;
+    if (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver || e == cudaErrorInvalidDevice) return NO_DEVICE;
+    return fallback;
+}
+
+int32_t error_word_status(int word) {
+    if (word & kern::ERR_WAIT_TIMEOUT) return TIMEOUT;
+    if (word & kern::ERR_LABEL_RANGE) return RANGE_OUT_OF_BOUNDS;
+    if (word & kern::ERR_NON_FINITE) return EXECUTION_FAILED;
+    return OK;
+}
+
+// Reads and clears the device error word; the stream is synchronised on return.
+int32_t drain_errors(Context *ctx) {
+    cudaError_t e = cudaMemcpyAsync(ctx->error_host, ctx->error_dev, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(ctx->error_dev, 0, sizeof(int), ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) { cudaGetLastError(); return EXECUTION_FAILED; }
+    return error_word_status(*ctx->error_host);
+}
+
+struct DeviceGuard {
+    int previous = -1;
+    explicit DeviceGuard(int device) { cudaGetDevice(&previous); if (previous != device) cudaSetDevice(device); else previous = -1; }
+    ~DeviceGuard() { if (previous >= 0) cudaSetDevice(previous); }
+};
+
+void bswap_copy(uint8_t *dst, const uint8_t *src, uint64_t bytes, uint32_t width) {
+    if (width == 1) { memcpy(dst, src, bytes); return; }
+    for (uint64_t i = 0; i + width <= bytes; i += width)
+        for (uint32_t b = 0; b < width; b++) dst[i + b] = src[i + width - 1 - b];
+}
+
+kern::Index4 index4(const std::vector<int64_t> &shape, const std::vector<int64_t> *sa, const std::vector<int64_t> *sb,
+                    const std::vector<int64_t> *sc, const std::vector<int64_t> *shape_a = nullptr,
+                    const std::vector<int64_t> *shape_b = nullptr, const std::vector<int64_t> *shape_c = nullptr) {
+    // right-aligns every operand against `shape`; broadcast axes (extent 1 against a larger one) get stride 0
+    kern::Index4 ix;
+    size_t r = shape.size();
+    for (int d = 0; d < 4; d++) { ix.shape[d] = 1; ix.sa[d] = ix.sb[d] = ix.sc[d] = 0; }
+    auto fill = [&](int64_t *dst, const std::vector<int64_t> *strides, const std::vector<int64_t> *oshape) {
+        if (!strides) return;
+        size_t orank = strides->size();
+        for (size_t d = 0; d < orank; d++) {
+            size_t target = 4 - orank + d;
+            int64_t extent = oshape ? (*oshape)[d] : shape[r - orank + d];
+            dst[target] = extent == 1 ? 0 : (*strides)[d];
+        }
+    };
+    for (size_t d = 0; d < r; d++) ix.shape[4 - r + d] = shape[d];
+    fill(ix.sa, sa, shape_a); fill(ix.sb, sb, shape_b); fill(ix.sc, sc, shape_c);
+    return ix;
+}
+
+struct Binding {
+    std::vector<Buffer *> feeds, publications;
+};
+
+uint64_t view_span_bytes(const View &v) {
+    int64_t last = v.offset;
+    for (size_t d = 0; d < v.shape.size(); d++) { if (v.shape[d] == 0) return 0; last += (v.shape[d] - 1) * v.strides[d]; }
+    return (uint64_t)(last + 1) * dtype_bytes(v.dtype);
+}
+
+int32_t prepare_executable(Executable *x) {
+    Context *ctx = x->ctx;
+    const Plan &plan = x->plan;
+    auto alloc = [&](uint64_t bytes, void **out) -> bool {
+        void *p = nullptr;
+        if (cudaMalloc(&p, bytes ? bytes : 4) != cudaSuccess) { cudaGetLastError(); return false; }
+        x->owned.push_back(p);
+        *out = p;
+        return true;
+    };
+    for (int64_t bytes : plan.scratch_bytes) { void *p; if (!alloc((uint64_t)bytes, &p)) return ALLOCATION_FAILED; x->scratch.push_back(p); }
+    if (!plan.constant_values.empty()) {
+        std::vector<uint64_t> host(plan.constant_values.size(), 0);
+        for (size_t i = 0; i < host.size(); i++) {
+            const Value &v = x->program.values[plan.constant_values[i]];
+            if (v.dtype == DType::F32) { float f = (float)v.constant_f64(); memcpy(&host[i], &f, 4); }
+            else if (v.dtype == DType::I32) { int32_t q = (int32_t)v.constant_i64(); memcpy(&host[i], &q, 4); }
+            else if (v.dtype == DType::I64) { int64_t q = v.constant_i64(); memcpy(&host[i], &q, 8); }
+            else { uint8_t q = v.constant_i64() != 0; memcpy(&host[i], &q, 1); }
+        }
+        if (!alloc(host.size() * 8, &x->constants)) return ALLOCATION_FAILED;
+        if (cudaMemcpy(x->constants, host.data(), host.size() * 8, cudaMemcpyHostToDevice) != cudaSuccess) return COPY_FAILED;
+    }
+    x->feed_bytes.assign(x->program.feeds.size(), 0);
+    x->publication_bytes.assign(x->program.publications.size(), 0);
+    for (const View &v : plan.views) {
+        if (v.index < 0) continue;
+        if (v.slot == SlotKind::FEED) x->feed_bytes[v.index] = std::max(x->feed_bytes[v.index], view_span_bytes(v));
+        if (v.slot == SlotKind::PUBLICATION) x->publication_bytes[v.index] = std::max(x->publication_bytes[v.index], view_span_bytes(v));
+    }
+    x->exec.resize(plan.steps.size());
+    auto planes_for = [&](int value, int orientation, int64_t rows, int64_t k) -> int {
+        auto key = std::make_pair(value, orientation);
+        auto it = x->plane_index.find(key);
+        if (it != x->plane_index.end()) return it->second;
+        Planes p;
+        p.rows = rows; p.kp = kern::padded_k(k);
+        void *hi, *lo;
+        if (!alloc((uint64_t)rows * p.kp * 4, &hi) || !alloc((uint64_t)rows * p.kp * 4, &lo)) return -1;
+        p.hi = (float *)hi; p.lo = (float *)lo;
+        x->planes.push_back(p);
+        x->plane_index[key] = (int)x->planes.size() - 1;
+        return (int)x->planes.size() - 1;
+    };
+    for (size_t i = 0; i < plan.steps.size(); i++) {
+        const Step &st = plan.steps[i];
+        StepExec &se = x->exec[i];
+        if (st.kind == StepKind::GEMM && st.engine == GemmEngine::TENSOR_CORE) {
+            const View &c = plan.views[st.out];
+            se.swapped = c.strides[0] == 1 && c.shape[0] != 1 && c.strides[1] != 1;
+            // orientation 0: plane rows follow axis 0 of the view; 1: plane rows follow axis 1
+            int pa = planes_for(st.a, 0, st.m, st.k), pb = planes_for(st.b, 1, st.n, st.k);
+            if (pa < 0 || pb < 0) return ALLOCATION_FAILED;
+            se.planes_p = se.swapped ? pb : pa;
+            se.planes_q = se.swapped ? pa : pb;
+            const Planes &P = x->planes[se.planes_p], &Q = x->planes[se.planes_q];
+            int status = OK;
+            se.tc = kern::tc_gemm_prepare(P.hi, P.lo, Q.hi, Q.lo, P.rows, Q.rows, P.kp, ctx->sm_count, &status);
+            if (!se.tc) return status;
+        } else if (st.kind == StepKind::COLSUM) {
+            void *p; if (!alloc((uint64_t)kern::colsum_partial_count(st.m, st.n) * 8, &p)) return ALLOCATION_FAILED;
+            se.colsum_partials = (double *)p;
+        } else if (st.kind == StepKind::CROSS_ENTROPY) {
+            void *p; if (!alloc((uint64_t)st.m * 4, &p)) return ALLOCATION_FAILED;
+            se.row_loss = (float *)p;
+        }
+    }
+    if (cudaEventCreate(&x->start) != cudaSuccess || cudaEventCreate(&x->stop) != cudaSuccess) return INTERNAL_ERROR;
+    x->sync_publication.assign(x->program.publications.size(), 0);
+    return OK;
+}
+
+void release_executable(Executable *x) {
+    DeviceGuard guard(x->ctx->device);
+    cudaStreamSynchronize(x->ctx->stream);
+    cudaStreamSynchronize(x->ctx->comm_stream);
+    for (StepExec &se : x->exec) if (se.tc) kern::tc_gemm_release(se.tc);
+    for (void *p : x->owned) cudaFree(p);
+    if (x->start) cudaEventDestroy(x->start);
+    if (x->stop) cudaEventDestroy(x->stop);
+    if (x->comm_done) cudaEventDestroy(x->comm_done);
+    for (cudaEvent_t e : x->ready_events) cudaEventDestroy(e);
+    for (cudaEvent_t e : x->step_events) cudaEventDestroy(e);
+    x->tag = 0;
+    delete x;
+}
+
+#define LAUNCH(expr) do { cudaError_t e_ = (expr); x->launches++; if (e_ != cudaSuccess) { cudaGetLastError(); return EXECUTION_FAILED; } } while (0)
+
+int32_t enqueue_executable(Executable *x, const Binding &bind) {
+    Context *ctx = x->ctx;
+    const Plan &plan = x->plan;
+    cudaStream_t s = ctx->stream;
+    auto base = [&](const View &v) -> uint8_t * {
+        switch (v.slot) {
+            case SlotKind::FEED: return (uint8_t *)bind.feeds[v.index]->ptr;
+            case SlotKind::PUBLICATION: return (uint8_t *)bind.publications[v.index]->ptr;
+            case SlotKind::SCRATCH: return (uint8_t *)x->scratch[v.index];
+            case SlotKind::CONSTANT: return (uint8_t *)x->constants + 8 * (size_t)v.index;
+        }
+        return nullptr;
+    };
+    auto ptr = [&](int value) -> void * {
+        if (value < 0) return nullptr;
+        const View &v = plan.views[value];
+        return base(v) + (v.slot == SlotKind::CONSTANT ? 0 : v.offset * dtype_bytes(v.dtype));
+    };
+    x->launches = 0;
+    x->run_counter++;
+    cudaEventRecord(x->start, s);
+    int ready_cursor = 0;
+    const bool time_steps = ctx->time_steps != 0;
+    if (time_steps && x->step_events.size() < 2 * plan.steps.size()) {
+        while (x->step_events.size() < 2 * plan.steps.size()) {
+            cudaEvent_t e; if (cudaEventCreate(&e) != cudaSuccess) return INTERNAL_ERROR;
+            x->step_events.push_back(e);
+        }
+    }
+    x->steps_timed = time_steps;
+    for (size_t i = 0; i < plan.steps.size(); i++) {
+        const Step &st = plan.steps[i];
+        StepExec &se = x->exec[i];
+        const bool tc_step = st.kind == StepKind::GEMM && st.engine == GemmEngine::TENSOR_CORE;
+        if (time_steps && !tc_step) cudaEventRecord(x->step_events[2 * i], s);
+        switch (st.kind) {
+            case StepKind::GEMM: {
+                const View &a = plan.views[st.a], &b = plan.views[st.b], &c = plan.views[st.out];
+                kern::GemmEpilogue ep;
+                ep.bias = (const float *)ptr(st.bias);
+                ep.gate = (const float *)ptr(st.mask);
+                ep.relu = st.relu && st.out2 < 0;
+                ep.second = (float *)ptr(st.out2);
+                if (st.engine == GemmEngine::EXACT_SIMT) {
+                    LAUNCH(kern::gemm_exact(s, st.m, st.n, st.k, (const float *)ptr(st.a), a.strides[0], a.strides[1],
+                                            (const float *)ptr(st.b), b.strides[0], b.strides[1],
+                                            (float *)ptr(st.out), c.strides[0], c.strides[1], ep));
+                } else {
+                    // operands are immutable within a run: split each (value, orientation) once per run
+                    auto split = [&](int value, int orientation, int index) -> int32_t {
+                        Planes &pl = x->planes[index];
+                        if (pl.last_run == x->run_counter) return OK;
+                        const View &v = plan.views[value];
+                        int64_t rs = orientation == 0 ? v.strides[0] : v.strides[1], cs = orientation == 0 ? v.strides[1] : v.strides[0];
+                        int64_t cols = orientation == 0 ? v.shape[1] : v.shape[0];
+                        LAUNCH(kern::split_planes(s, (const float *)ptr(value), pl.rows, cols, rs, cs, pl.hi, pl.lo, pl.kp));
+                        pl.last_run = x->run_counter;
+                        return OK;
+                    };
+                    int pa = x->plane_index[std::make_pair(st.a, 0)], pb = x->plane_index[std::make_pair(st.b, 1)];
+                    int32_t r1 = split(st.a, 0, pa); if (r1 != OK) return r1;
+                    int32_t r2 = split(st.b, 1, pb); if (r2 != OK) return r2;
+                    int64_t ldd = se.swapped ? c.strides[1] : c.strides[0];
+                    if (time_steps) cudaEventRecord(x->step_events[2 * i], s);
+                    LAUNCH(kern::tc_gemm_launch(s, se.tc, (float *)ptr(st.out), ldd, ep, ctx->error_dev));
+                }
+                break;
+            }
+            case StepKind::BINARY: {
+                const View &a = plan.views[st.a], &b = plan.views[st.b], &o = plan.views[st.out];
+                kern::Index4 ix = index4(o.shape, &a.strides, &b.strides, nullptr, &a.shape, &b.shape, nullptr);
+                int64_t total = 1; for (auto d : o.shape) total *= d;
+                LAUNCH(kern::binary(s, st.op, (const float *)ptr(st.a), (const float *)ptr(st.b), ptr(st.out), ix, total));
+                break;
+            }
+            case StepKind::WHERE: {
+                const View &a = plan.views[st.a], &b = plan.views[st.b], &c = plan.views[st.c], &o = plan.views[st.out];
+                kern::Index4 ix = index4(o.shape, &a.strides, &b.strides, &c.strides, &a.shape, &b.shape, &c.shape);
+                int64_t total = 1; for (auto d : o.shape) total *= d;
+                LAUNCH(kern::where(s, (const uint8_t *)ptr(st.a), (const float *)ptr(st.b), (const float *)ptr(st.c), (float *)ptr(st.out), ix, total));
+                break;
+            }
+            case StepKind::SCALAR: case StepKind::UNARY: {
+                const View &a = plan.views[st.a], &o = plan.views[st.out];
+                int64_t total = 1; for (auto d : o.shape) total *= d;
+                const void *src = ptr(st.a);
+                if (!a.dense()) return UNSUPPORTED_SHAPE;
+                if (st.kind == StepKind::SCALAR) LAUNCH(kern::scalar_op(s, st.op, a.dtype, src, ptr(st.out), st.scalar_bits, total));
+                else LAUNCH(kern::unary(s, st.op, (const float *)src, (float *)ptr(st.out), total));
+                break;
+            }
+            case StepKind::ONE_HOT:
+                LAUNCH(kern::one_hot(s, plan.views[st.a].dtype, ptr(st.a), (uint8_t *)ptr(st.out), st.m, st.n));
+                break;
+            case StepKind::COPY: {
+                const View &a = plan.views[st.a], &o = plan.views[st.out];
+                kern::Index4 ix = index4(o.shape, &a.strides, nullptr, nullptr, &a.shape);
+                int64_t total = 1; for (auto d : o.shape) total *= d;
+                LAUNCH(kern::copy_strided(s, dtype_bytes(a.dtype), ptr(st.a), ptr(st.out), ix, total));
+                break;
+            }
+            case StepKind::ROW_REDUCE:
+                LAUNCH(kern::row_reduce(s, st.op, (const float *)ptr(st.a), (float *)ptr(st.out), st.m, st.n));
+                break;
+            case StepKind::FULL_SUM: {
+                const View &a = plan.views[st.a];
+                kern::Index4 ix = index4(a.shape, &a.strides, nullptr, nullptr, &a.shape);
+                LAUNCH(kern::full_sum(s, (const float *)ptr(st.a), ix, st.m, (float *)ptr(st.out)));
+                break;
+            }
+            case StepKind::COLSUM:
+                LAUNCH(kern::colsum(s, (const float *)ptr(st.a), st.m, st.n, se.colsum_partials, (float *)ptr(st.out)));
+                x->launches++;
+                break;
+            case StepKind::SOFTMAX:
+                LAUNCH(kern::softmax_rows(s, (const float *)ptr(st.a), (float *)ptr(st.out), st.m, st.n));
+                break;
+            case StepKind::CROSS_ENTROPY:
+                LAUNCH(kern::cross_entropy(s, (const float *)ptr(st.a), plan.views[st.b].dtype, ptr(st.b), (const float *)ptr(st.c), st.m, st.n,
+                                           se.row_loss, (float *)ptr(st.out), (float *)ptr(st.out2), nullptr, ctx->error_dev));
+                if (st.out >= 0) x->launches++;
+                break;
+            case StepKind::MSE:
+                LAUNCH(kern::mse_mean(s, (const float *)ptr(st.a), (const float *)ptr(st.b), st.m, (float *)ptr(st.out)));
+                break;
+            case StepKind::ARG_MAX:
+                LAUNCH(kern::argmax_rows(s, (const float *)ptr(st.a), (int64_t *)ptr(st.out), st.m, st.n));
+                break;
+            case StepKind::RELU_BACKWARD: {
+                int64_t total = 1; for (auto d : plan.views[st.out].shape) total *= d;
+                LAUNCH(kern::relu_backward(s, (const float *)ptr(st.a), (const float *)ptr(st.b), (float *)ptr(st.out), total));
+                break;
+            }
+        }
+        if (time_steps) cudaEventRecord(x->step_events[2 * i + 1], s);
+        // gradients that are final go to the communication stream at once, so their all-reduce
+        // overlaps the rest of the backward pass
+        if (x->comm) for (int j : st.ready_publications) if (x->sync_publication[j]) {
+            if (ready_cursor >= (int)x->ready_events.size()) {
+                cudaEvent_t e; if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return INTERNAL_ERROR;
+                x->ready_events.push_back(e);
+            }
+            cudaEvent_t ev = x->ready_events[ready_cursor++];
+            cudaEventRecord(ev, s);
+            cudaStreamWaitEvent(ctx->comm_stream, ev, 0);
+            Buffer *buf = bind.publications[j];
+            uint64_t count = x->publication_bytes[j] / 4;
+            if (nccl().AllReduce(buf->ptr, buf->ptr, count, /*ncclFloat32*/ 7, /*ncclSum*/ 0, x->comm->comm, ctx->comm_stream) != 0) return COMM_FAILED;
+        }
+    }
+    if (x->comm && ready_cursor > 0) {
+        if (!x->comm_done && cudaEventCreateWithFlags(&x->comm_done, cudaEventDisableTiming) != cudaSuccess) return INTERNAL_ERROR;
+        cudaEventRecord(x->comm_done, ctx->comm_stream);
+        cudaStreamWaitEvent(s, x->comm_done, 0);
+    }
+    cudaEventRecord(x->stop, s);
+    x->timed = true;
+    x->pending = true;
+    return OK;
+}
+
+int32_t bind_buffers(Executable *x, int32_t nin, void *const *in, int32_t nout, void *const *out, Binding &bind) {
+    if (nin != (int32_t)x->program.feeds.size() || nout != (int32_t)x->program.publications.size()) return INVALID_ARGUMENT;
+    if ((nin && !in) || (nout && !out)) return INVALID_ARGUMENT;
+    for (int i = 0; i < nin; i++) {
+        Buffer *b = as<Buffer>(in[i], TAG_BUFFER);
+        if (!b) return INVALID_ARGUMENT;
+        if (b->ctx != x->ctx || b->bytes < x->feed_bytes[i]) return INCOMPATIBLE_RESOURCE;
+        bind.feeds.push_back(b);
+    }
+    for (int i = 0; i < nout; i++) {
+        Buffer *b = as<Buffer>(out[i], TAG_BUFFER);
+        if (!b) return INVALID_ARGUMENT;
+        if (b->ctx != x->ctx || b->bytes < x->publication_bytes[i]) return INCOMPATIBLE_RESOURCE;
+        for (Buffer *f : bind.feeds) if (f == b) return INCOMPATIBLE_RESOURCE;             // an input aliases an output
+        for (Buffer *p : bind.publications) if (p == b) return INCOMPATIBLE_RESOURCE;      // two outputs alias
+        bind.publications.push_back(b);
+    }
+    return OK;
+}
+
+int32_t build_program(const uint8_t *program, uint32_t bytes, int gemm_engine, Program &g, Plan &plan) {
+    std::string message;
+    Status s = parse_program(program, bytes, g, message);
+    if (s != OK) return s;
+    LoweringOptions options;
+    options.gemm_engine = gemm_engine;
+    return lower_program(g, options, plan, message);
+}
+
+}  // namespace
+
+extern "C" {
+
+uint32_t synaptik_cuda_abi_version(void) { return SYNAPTIK_CUDA_ABI_VERSION; }
+
+int32_t synaptik_cuda_context_create(int32_t device_ordinal, void **out_context) {
+    if (!out_context) return INVALID_ARGUMENT;
+    *out_context = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) { cudaGetLastError(); return NO_DEVICE; }
+    if (device_ordinal < 0 || device_ordinal >= count) return INVALID_ARGUMENT;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device_ordinal) != cudaSuccess) { cudaGetLastError(); return NO_DEVICE; }
+    if (prop.major != 10) return NO_DEVICE;         // kernels are built for sm_100a only; there is no other path
+    DeviceGuard guard(device_ordinal);
+    Context *ctx = new Context();
+    ctx->device = device_ordinal;
+    ctx->sm_count = prop.multiProcessorCount;
+    if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess
+        || cudaStreamCreateWithFlags(&ctx->comm_stream, cudaStreamNonBlocking) != cudaSuccess) { cudaGetLastError(); delete ctx; return NO_STREAM; }
+    if (cudaMalloc(&ctx->error_dev, sizeof(int)) != cudaSuccess || cudaMallocHost(&ctx->error_host, sizeof(int)) != cudaSuccess
+        || cudaMemset(ctx->error_dev, 0, sizeof(int)) != cudaSuccess) { cudaGetLastError(); delete ctx; return ALLOCATION_FAILED; }
+    *out_context = ctx;
+    return OK;
+}
+
+int32_t synaptik_cuda_context_release(void *context) {
+    Context *ctx = as<Context>(context, TAG_CONTEXT);
+    if (!ctx) return INVALID_ARGUMENT;
+    DeviceGuard guard(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    cudaStreamSynchronize(ctx->comm_stream);
+    cudaStreamDestroy(ctx->stream);
+    cudaStreamDestroy(ctx->comm_stream);
+    cudaFree(ctx->error_dev);
+    cudaFreeHost(ctx->error_host);
+    if (ctx->timer_start) cudaEventDestroy(ctx->timer_start);
+    if (ctx->timer_stop) cudaEventDestroy(ctx->timer_stop);
+    ctx->tag = 0;
+    delete ctx;
+    return OK;
+}
+
+int32_t synaptik_cuda_context_set_option(void *context, const char *name, int64_t value) {
+    Context *ctx = as<Context>(context, TAG_CONTEXT);
+    if (!ctx || !name) return INVALID_ARGUMENT;
+    if (!strcmp(name, "gemm_engine")) { if (value < 0 || value > 2) return INVALID_ARGUMENT; ctx->gemm_engine = (int)value; return OK; }
+    if (!strcmp(name, "time_steps")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->time_steps = (int)value; return OK; }
+    return INVALID_ARGUMENT;
+}
+
+int32_t synaptik_cuda_context_synchronize(void *context) {
+    Context *ctx = as<Context>(context, TAG_CONTEXT);
+    if (!ctx) return INVALID_ARGUMENT;
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->comm_stream);
+    return cuda_status(e, EXECUTION_FAILED);
+}
+
+int32_t synaptik_cuda_context_timer_start(void *context) {
+    Context *ctx = as<Context>(context, TAG_CONTEXT);
+    if (!ctx) return INVALID_ARGUMENT;
+    DeviceGuard guard(ctx->device);
+    if (!ctx->timer_start && (cudaEventCreate(&ctx->timer_start) != cudaSuccess || cudaEventCreate(&ctx->timer_stop) != cudaSuccess)) return INTERNAL_ERROR;
+    return cuda_status(cudaEventRecord(ctx->timer_start, ctx->stream), EXECUTION_FAILED);
+}
+
+int32_t synaptik_cuda_context_timer_stop(void *context, double *out_milliseconds) {
+    Context *ctx = as<Context>(context, TAG_CONTEXT);
+    if (!ctx || !out_milliseconds || !ctx->timer_start) return INVALID_ARGUMENT;
+    DeviceGuard guard(ctx->device);
+    float ms = 0;
+    cudaError_t e = cudaEventRecord(ctx->timer_stop, ctx->stream);
+    if (e == cudaSuccess) e = cudaEventSynchronize(ctx->timer_stop);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, ctx->timer_start, ctx->timer_stop);
+    if (e != cudaSuccess) { cudaGetLastError(); return EXECUTION_FAILED; }
+    *out_milliseconds = ms;
+    return OK;
+}
+
+int32_t synaptik_cuda_buffer_create(void *context, uint64_t bytes, void **out_buffer) {
+    if (!out_buffer) return INVALID_ARGUMENT;
+    *out_buffer = nullptr;
+    Context *ctx = as<Context>(context, TAG_CONTEXT);
+    if (!ctx) return INVALID_ARGUMENT;
+    DeviceGuard guard(ctx->device);
+    void *p = nullptr;
+    if (cudaMalloc(&p, bytes ? bytes : 4) != cudaSuccess) { cudaGetLastError(); return ALLOCATION_FAILED; }
+    Buffer *b = new Buffer();
+    b->ctx = ctx; b->ptr = p; b->bytes = bytes;
+    *out_buffer = b;
+    return OK;
+}
+
+int32_t synaptik_cuda_buffer_release(void *buffer) {
+    Buffer *b = as<Buffer>(buffer, TAG_BUFFER);
+    if (!b) return INVALID_ARGUMENT;
+    DeviceGuard guard(b->ctx->device);
+    cudaStreamSynchronize(b->ctx->stream);
+    cudaFree(b->ptr);
+    b->tag = 0;
+    delete b;
+    return OK;
+}
+
+static int32_t transfer(void *buffer, uint64_t offset, void *host, uint64_t bytes, bool upload, bool async) {
+    Buffer *b = as<Buffer>(buffer, TAG_BUFFER);
+    if (!b || (!host && bytes)) return INVALID_ARGUMENT;
+    if (offset > b->bytes || bytes > b->bytes - offset) return RANGE_OUT_OF_BOUNDS;
+    if (!bytes) return OK;
+    DeviceGuard guard(b->ctx->device);
+    uint8_t *dev = (uint8_t *)b->ptr + offset;
+    cudaError_t e = upload ? cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, b->ctx->stream)
+                           : cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, b->ctx->stream);
+    if (e == cudaSuccess && !async) e = cudaStreamSynchronize(b->ctx->stream);
+    if (e != cudaSuccess) { cudaGetLastError(); return COPY_FAILED; }
+    return OK;
+}
+
+int32_t synaptik_cuda_buffer_upload(void *buffer, uint64_t offset, const void *source, uint64_t bytes) {
+    return transfer(buffer, offset, const_cast<void *>(source), bytes, true, false);
+}
+int32_t synaptik_cuda_buffer_download(void *buffer, uint64_t offset, void *destination, uint64_t bytes) {
+    return transfer(buffer, offset, destination, bytes, false, false);
+}
+int32_t synaptik_cuda_buffer_upload_async(void *buffer, uint64_t offset, const void *source, uint64_t bytes) {
+    return transfer(buffer, offset, const_cast<void *>(source), bytes, true, true);
+}
+int32_t synaptik_cuda_buffer_download_async(void *buffer, uint64_t offset, void *destination, uint64_t bytes) {
+    return transfer(buffer, offset, destination, bytes, false, true);
+}
+
+int32_t synaptik_cuda_buffer_upload_canonical(void *buffer, uint64_t offset, const void *source, uint64_t bytes, uint32_t element_bytes) {
+    if (element_bytes != 1 && element_bytes != 2 && element_bytes != 4 && element_bytes != 8) return INVALID_ARGUMENT;
+    if (bytes % element_bytes) return INVALID_ARGUMENT;
+    Buffer *b = as<Buffer>(buffer, TAG_BUFFER);
+    if (!b || (!source && bytes)) return INVALID_ARGUMENT;
+    if (offset > b->bytes || bytes > b->bytes - offset) return RANGE_OUT_OF_BOUNDS;
+    std::vector<uint8_t> staged(bytes);
+    bswap_copy(staged.data(), (const uint8_t *)source, bytes, element_bytes);
+    return transfer(buffer, offset, staged.data(), bytes, true, false);
+}
+
+int32_t synaptik_cuda_buffer_download_canonical(void *buffer, uint64_t offset, void *destination, uint64_t bytes, uint32_t element_bytes) {
+    if (element_bytes != 1 && element_bytes != 2 && element_bytes != 4 && element_bytes != 8) return INVALID_ARGUMENT;
+    if (bytes % element_bytes) return INVALID_ARGUMENT;
+    Buffer *b = as<Buffer>(buffer, TAG_BUFFER);
+    if (!b || (!destination && bytes)) return INVALID_ARGUMENT;
+    if (offset > b->bytes || bytes > b->bytes - offset) return RANGE_OUT_OF_BOUNDS;
+    std::vector<uint8_t> staged(bytes);
+    int32_t s = transfer(buffer, offset, staged.data(), bytes, false, false);
+    if (s != OK) return s;
+    bswap_copy((uint8_t *)destination, staged.data(), bytes, element_bytes);
+    return OK;
+}
+
+int32_t synaptik_cuda_buffer_device_pointer(void *buffer, uint64_t *out_address, uint64_t *out_bytes) {
+    Buffer *b = as<Buffer>(buffer, TAG_BUFFER);
+    if (!b || !out_address) return INVALID_ARGUMENT;
+    *out_address = (uint64_t)(uintptr_t)b->ptr;
+    if (out_bytes) *out_bytes = b->bytes;
+    return OK;
+}
+
+int32_t synaptik_cuda_host_alloc(uint64_t bytes, void **out_pointer) {
+    if (!out_pointer) return INVALID_ARGUMENT;
+    *out_pointer = nullptr;
+    void *p = nullptr;
+    cudaError_t e = cudaMallocHost(&p, bytes ? bytes : 4);
+    if (e != cudaSuccess) { cudaGetLastError(); return cuda_status(e, ALLOCATION_FAILED); }
+    *out_pointer = p;
+    return OK;
+}
+int32_t synaptik_cuda_host_free(void *pointer) {
+    if (!pointer) return INVALID_ARGUMENT;
+    cudaError_t e = cudaFreeHost(pointer);
+    if (e != cudaSuccess) { cudaGetLastError(); return INVALID_ARGUMENT; }
+    return OK;
+}
+
+int32_t synaptik_cuda_executable_create(void *context, const uint8_t *program, uint32_t program_bytes, void **out_executable) {
+    if (!out_executable) return INVALID_ARGUMENT;
+    *out_executable = nullptr;
+    Context *ctx = as<Context>(context, TAG_CONTEXT);
+    if (!ctx || !program) return INVALID_ARGUMENT;
+    Executable *x = new Executable();
+    x->ctx = ctx;
+    int32_t s = build_program(program, program_bytes, ctx->gemm_engine, x->program, x->plan);
+    if (s != OK) { delete x; return s; }
+    DeviceGuard guard(ctx->device);
+    s = prepare_executable(x);
+    if (s != OK) { release_executable(x); return s; }
+    *out_executable = x;
+    return OK;
+}
+
+int32_t synaptik_cuda_executable_release(void *executable) {
+    Executable *x = as<Executable>(executable, TAG_EXECUTABLE);
+    if (!x) return INVALID_ARGUMENT;
+    release_executable(x);
+    return OK;
+}
+
+int32_t synaptik_cuda_executable_enqueue(void *executable, int32_t input_count, void *const *inputs, int32_t output_count, void *const *outputs) {
+    Executable *x = as<Executable>(executable, TAG_EXECUTABLE);
+    if (!x) return INVALID_ARGUMENT;
+    Binding bind;
+    int32_t s = bind_buffers(x, input_count, inputs, output_count, outputs, bind);
+    if (s != OK) return s;
+    std::lock_guard<std::mutex> lock(x->ctx->mutex);
+    DeviceGuard guard(x->ctx->device);
+    return enqueue_executable(x, bind);
+}
+
+int32_t synaptik_cuda_executable_finish(void *executable) {
+    Executable *x = as<Executable>(executable, TAG_EXECUTABLE);
+    if (!x) return INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(x->ctx->mutex);
+    DeviceGuard guard(x->ctx->device);
+    x->pending = false;
+    return drain_errors(x->ctx);
+}
+
+int32_t synaptik_cuda_executable_run(void *executable, int32_t input_count, void *const *inputs, int32_t output_count, void *const *outputs) {
+    int32_t s = synaptik_cuda_executable_enqueue(executable, input_count, inputs, output_count, outputs);
+    if (s != OK) return s;
+    return synaptik_cuda_executable_finish(executable);
+}
+
+int32_t synaptik_cuda_program_describe(const uint8_t *program, uint32_t program_bytes, char *text, uint64_t capacity, uint64_t *out_required) {
+    if (!program) return INVALID_ARGUMENT;
+    Program g; Plan plan;
+    int32_t s = build_program(program, program_bytes, 0, g, plan);
+    if (s != OK) return s;
+    std::string d = describe_plan(g, plan);
+    if (out_required) *out_required = d.size() + 1;
+    if (!text || capacity < d.size() + 1) return INVALID_ARGUMENT;
+    memcpy(text, d.c_str(), d.size() + 1);
+    return OK;
+}
+
+int32_t synaptik_cuda_executable_describe(void *executable, char *text, uint64_t capacity, uint64_t *out_required) {
+    Executable *x = as<Executable>(executable, TAG_EXECUTABLE);
+    if (!x) return INVALID_ARGUMENT;
+    std::string d = describe_plan(x->program, x->plan);
+    if (out_required) *out_required = d.size() + 1;
+    if (!text || capacity < d.size() + 1) return INVALID_ARGUMENT;
+    memcpy(text, d.c_str(), d.size() + 1);
+    return OK;
+}
+
+int32_t synaptik_cuda_executable_step_timings(void *executable, double *out_milliseconds, uint64_t capacity, uint64_t *out_count) {
+    Executable *x = as<Executable>(executable, TAG_EXECUTABLE);
+    if (!x || !out_count) return INVALID_ARGUMENT;
+    size_t steps = x->plan.steps.size();
+    *out_count = steps;
+    if (!x->steps_timed || !x->timed) return INVALID_ARGUMENT;
+    if (!out_milliseconds || capacity < steps) return INVALID_ARGUMENT;
+    DeviceGuard guard(x->ctx->device);
+    if (cudaEventSynchronize(x->stop) != cudaSuccess) { cudaGetLastError(); return EXECUTION_FAILED; }
+    for (size_t i = 0; i < steps; i++) {
+        float ms = 0;
+        if (cudaEventElapsedTime(&ms, x->step_events[2 * i], x->step_events[2 * i + 1]) != cudaSuccess) { cudaGetLastError(); return EXECUTION_FAILED; }
+        out_milliseconds[i] = ms;
+    }
+    return OK;
+}
+
+int32_t synaptik_cuda_executable_last_timing(void *executable, double *out_milliseconds) {
+    Executable *x = as<Executable>(executable, TAG_EXECUTABLE);
+    if (!x || !out_milliseconds || !x->timed) return INVALID_ARGUMENT;
+    DeviceGuard guard(x->ctx->device);
+    float ms = 0;
+    if (cudaEventSynchronize(x->stop) != cudaSuccess || cudaEventElapsedTime(&ms, x->start, x->stop) != cudaSuccess) { cudaGetLastError(); return EXECUTION_FAILED; }
+    *out_milliseconds = ms;
+    return OK;
+}
+
+int32_t synaptik_cuda_executable_launch_count(void *executable, uint64_t *out_launches) {
+    Executable *x = as<Executable>(executable, TAG_EXECUTABLE);
+    if (!x || !out_launches) return INVALID_ARGUMENT;
+    *out_launches = x->launches;
+    return OK;
+}
+
+// ---- optimizer -----------------------------------------------------------------------------------
+int32_t synaptik_cuda_optimizer_create(void *context, int32_t kind, const double *hyper, int32_t hyper_count, int32_t parameter_count,
+                                       void *const *parameters, const uint64_t *element_counts, void **out_optimizer) {
+    if (!out_optimizer) return INVALID_ARGUMENT;
+    *out_optimizer = nullptr;
+    Context *ctx = as<Context>(context, TAG_CONTEXT);
+    if (!ctx || kind < 0 || kind > 2 || !hyper || hyper_count != 5 || parameter_count < 1 || !parameters || !element_counts) return INVALID_ARGUMENT;
+    for (int i = 0; i < 5; i++) if (!std::isfinite(hyper[i])) return INVALID_ARGUMENT;
+    if (kind == 0) { if (!(hyper[0] > 0) || hyper[1] < 0 || hyper[3] < 0) return INVALID_ARGUMENT; }
+    else if (!(hyper[0] > 0) || hyper[1] < 0 || hyper[1] >= 1 || hyper[2] < 0 || hyper[2] >= 1 || !(hyper[3] > 0) || hyper[4] < 0) return INVALID_ARGUMENT;
+    Optimizer *o = new Optimizer();
+    o->ctx = ctx; o->kind = kind;
+    memcpy(o->hyper, hyper, sizeof o->hyper);
+    DeviceGuard guard(ctx->device);
+    bool need_m = kind != 0 || hyper[1] != 0.0, need_v = kind != 0;
+    int32_t status = OK;
+    for (int i = 0; i < parameter_count && status == OK; i++) {
+        Buffer *b = as<Buffer>(parameters[i], TAG_BUFFER);
+        if (!b) { status = INVALID_ARGUMENT; break; }
+        if (b->ctx != ctx || b->bytes < element_counts[i] * 4) { status = INCOMPATIBLE_RESOURCE; break; }
+        o->params.push_back(b); o->counts.push_back(element_counts[i]);
+        float *m = nullptr, *v = nullptr;
+        uint64_t bytes = element_counts[i] * 4 ? element_counts[i] * 4 : 4;
+        if (need_m && (cudaMalloc(&m, bytes) != cudaSuccess || cudaMemsetAsync(m, 0, bytes, ctx->stream) != cudaSuccess)) status = ALLOCATION_FAILED;
+        if (status == OK && need_v && (cudaMalloc(&v, bytes) != cudaSuccess || cudaMemsetAsync(v, 0, bytes, ctx->stream) != cudaSuccess)) status = ALLOCATION_FAILED;
+        o->m.push_back(m); o->v.push_back(v);
+    }
+    if (status == OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) status = EXECUTION_FAILED;
+    if (status != OK) {
+        cudaGetLastError();
+        for (float *p : o->m) cudaFree(p);
+        for (float *p : o->v) cudaFree(p);
+        delete o;
+        return status;
+    }
+    *out_optimizer = o;
+    return OK;
+}
+
+int32_t synaptik_cuda_optimizer_release(void *optimizer) {
+    Optimizer *o = as<Optimizer>(optimizer, TAG_OPTIMIZER);
+    if (!o) return INVALID_ARGUMENT;
+    DeviceGuard guard(o->ctx->device);
+    cudaStreamSynchronize(o->ctx->stream);
+    for (float *p : o->m) cudaFree(p);
+    for (float *p : o->v) cudaFree(p);
+    o->tag = 0;
+    delete o;
+    return OK;
+}
+
+int32_t synaptik_cuda_optimizer_step_enqueue(void *optimizer, int32_t gradient_count, void *const *gradients) {
+    Optimizer *o = as<Optimizer>(optimizer, TAG_OPTIMIZER);
+    if (!o || gradient_count != (int32_t)o->params.size() || !gradients) return INVALID_ARGUMENT;
+    std::vector<kern::TensorSlot> slots(o->params.size());
+    for (size_t i = 0; i < slots.size(); i++) {
+        Buffer *g = as<Buffer>(gradients[i], TAG_BUFFER);
+        if (!g) return INVALID_ARGUMENT;
+        if (g->ctx != o->ctx || g->bytes < o->counts[i] * 4 || g == o->params[i]) return INCOMPATIBLE_RESOURCE;
+        slots[i] = {(float *)o->params[i]->ptr, (const float *)g->ptr, o->m[i], o->v[i], (int64_t)o->counts[i]};
+    }
+    std::lock_guard<std::mutex> lock(o->ctx->mutex);
+    DeviceGuard guard(o->ctx->device);
+    cudaError_t e;
+    if (o->kind == 0) {
+        kern::SgdArgs a;
+        a.lr = (float)o->hyper[0]; a.momentum = (float)o->hyper[1]; a.dampening = (float)o->hyper[2]; a.weight_decay = (float)o->hyper[3];
+        a.nesterov = o->hyper[4] != 0.0; a.first_step = o->steps == 0; a.has_buffer = o->hyper[1] != 0.0;
+        a.zero_buffer = o->hyper[1] != 0.0 && a.momentum == 0.0f;
+        e = kern::sgd_step(o->ctx->stream, slots.data(), (int)slots.size(), a, o->ctx->error_dev);
+    } else {
+        // coefficients narrowed to binary32 first (AdaptiveCoefficients.java:33-58); corrections
+        // 1f - (float)Math.pow(beta, step) evaluated in binary64 on the narrowed beta
+        kern::AdamArgs a;
+        a.lr = (float)o->hyper[0]; a.b1 = (float)o->hyper[1]; a.b2 = (float)o->hyper[2]; a.eps = (float)o->hyper[3]; a.decay = (float)o->hyper[4];
+        double step = (double)(o->steps + 1);
+        a.correction1 = 1.0f - (float)std::pow((double)a.b1, step);
+        a.correction2 = 1.0f - (float)std::pow((double)a.b2, step);
+        if (!(a.correction1 > 0.0f) || !(a.correction2 > 0.0f)) return EXECUTION_FAILED;
+        a.decoupled = o->kind == 2;
+        a.decay_factor = 1.0f;
+        if (a.decoupled) { float scale = a.lr * a.decay; a.decay_factor = 1.0f - scale; }
+        e = kern::adam_step(o->ctx->stream, slots.data(), (int)slots.size(), a, o->ctx->error_dev);
+    }
+    if (e != cudaSuccess) { cudaGetLastError(); return EXECUTION_FAILED; }
+    o->steps++;
+    o->pending = true;
+    return OK;
+}
+
+int32_t synaptik_cuda_optimizer_finish(void *optimizer) {
+    Optimizer *o = as<Optimizer>(optimizer, TAG_OPTIMIZER);
+    if (!o) return INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(o->ctx->mutex);
+    DeviceGuard guard(o->ctx->device);
+    o->pending = false;
+    return drain_errors(o->ctx);
+}
+
+int32_t synaptik_cuda_optimizer_step(void *optimizer, int32_t gradient_count, void *const *gradients) {
+    int32_t s = synaptik_cuda_optimizer_step_enqueue(optimizer, gradient_count, gradients);
+    if (s != OK) return s;
+    return synaptik_cuda_optimizer_finish(optimizer);
+}
+
+int32_t synaptik_cuda_optimizer_steps(void *optimizer, uint64_t *out_steps) {
+    Optimizer *o = as<Optimizer>(optimizer, TAG_OPTIMIZER);
+    if (!o || !out_steps) return INVALID_ARGUMENT;
+    *out_steps = o->steps;
+    return OK;
+}
+
+static int32_t optimizer_state(void *optimizer, int32_t index, int32_t slot, void *host, uint64_t bytes, bool upload) {
+    Optimizer *o = as<Optimizer>(optimizer, TAG_OPTIMIZER);
+    if (!o || index < 0 || index >= (int32_t)o->params.size() || slot < 0 || slot > 1 || !host) return INVALID_ARGUMENT;
+    float *dev = slot == 0 ? o->m[index] : o->v[index];
+    if (!dev) return INVALID_ARGUMENT;
+    if (bytes != o->counts[index] * 4) return RANGE_OUT_OF_BOUNDS;
+    DeviceGuard guard(o->ctx->device);
+    cudaError_t e = upload ? cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, o->ctx->stream)
+                           : cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, o->ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(o->ctx->stream);
+    if (e != cudaSuccess) { cudaGetLastError(); return COPY_FAILED; }
+    return OK;
+}
+int32_t synaptik_cuda_optimizer_download_state(void *optimizer, int32_t parameter_index, int32_t slot, void *destination, uint64_t bytes) {
+    return optimizer_state(optimizer, parameter_index, slot, destination, bytes, false);
+}
+int32_t synaptik_cuda_optimizer_upload_state(void *optimizer, int32_t parameter_index, int32_t slot, const void *source, uint64_t bytes, uint64_t completed_steps) {
+    int32_t s = optimizer_state(optimizer, parameter_index, slot, const_cast<void *>(source), bytes, true);
+    if (s == OK) as<Optimizer>(optimizer, TAG_OPTIMIZER)->steps = completed_steps;
+    return s;
+}
+
+// ---- communicator --------------------------------------------------------------------------------
+int32_t synaptik_cuda_comm_unique_id(uint8_t *out_id128) {
+    if (!out_id128) return INVALID_ARGUMENT;
+    if (!nccl().ok) return COMM_FAILED;
+    NcclApi::UniqueId id;
+    if (nccl().GetUniqueId(&id) != 0) return COMM_FAILED;
+    memcpy(out_id128, id.internal, 128);
+    return OK;
+}
+
+int32_t synaptik_cuda_comm_create(void *context, int32_t world_size, int32_t rank, const uint8_t *unique_id128, void **out_comm) {
+    if (!out_comm) return INVALID_ARGUMENT;
+    *out_comm = nullptr;
+    Context *ctx = as<Context>(context, TAG_CONTEXT);
+    if (!ctx || world_size < 1 || rank < 0 || rank >= world_size || !unique_id128) return INVALID_ARGUMENT;
+    if (!nccl().ok) return COMM_FAILED;
+    DeviceGuard guard(ctx->device);
+    NcclApi::UniqueId id;
+    memcpy(id.internal, unique_id128, 128);
+    void *comm = nullptr;
+    if (nccl().CommInitRank(&comm, world_size, id, rank) != 0 || !comm) return COMM_FAILED;
+    Comm *c = new Comm();
+    c->ctx = ctx; c->comm = comm; c->world = world_size; c->rank = rank;
+    *out_comm = c;
+    return OK;
+}
+
+int32_t synaptik_cuda_comm_release(void *comm) {
+    Comm *c = as<Comm>(comm, TAG_COMM);
+    if (!c) return INVALID_ARGUMENT;
+    DeviceGuard guard(c->ctx->device);
+    cudaStreamSynchronize(c->ctx->comm_stream);
+    nccl().CommDestroy(c->comm);
+    c->tag = 0;
+    delete c;
+    return OK;
+}
+
+int32_t synaptik_cuda_comm_allreduce_sum_f32(void *comm, void *buffer, uint64_t offset, uint64_t element_count) {
+    Comm *c = as<Comm>(comm, TAG_COMM);
+    Buffer *b = as<Buffer>(buffer, TAG_BUFFER);
+    if (!c || !b) return INVALID_ARGUMENT;
+    if (b->ctx != c->ctx) return INCOMPATIBLE_RESOURCE;
+    if (offset % 4 || offset > b->bytes || element_count * 4 > b->bytes - offset) return RANGE_OUT_OF_BOUNDS;
+    std::lock_guard<std::mutex> lock(c->ctx->mutex);
+    DeviceGuard guard(c->ctx->device);
+    // ordered after the compute stream's earlier work, executed on the communication stream
+    cudaEvent_t ev;
+    if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return INTERNAL_ERROR;
+    cudaEventRecord(ev, c->ctx->stream);
+    cudaStreamWaitEvent(c->ctx->comm_stream, ev, 0);
+    float *p = (float *)((uint8_t *)b->ptr + offset);
+    int rc = nccl().AllReduce(p, p, element_count, 7, 0, c->comm, c->ctx->comm_stream);
+    cudaEventRecord(ev, c->ctx->comm_stream);
+    cudaStreamWaitEvent(c->ctx->stream, ev, 0);
+    cudaError_t e = cudaStreamSynchronize(c->ctx->comm_stream);
+    cudaEventDestroy(ev);
+    if (rc != 0 || e != cudaSuccess) { cudaGetLastError(); return COMM_FAILED; }
+    return OK;
+}
+
+int32_t synaptik_cuda_executable_attach_comm(void *executable, void *comm, int32_t output_count, const int32_t *output_indices) {
+    Executable *x = as<Executable>(executable, TAG_EXECUTABLE);
+    if (!x) return INVALID_ARGUMENT;
+    if (!comm) { x->comm = nullptr; x->sync_publication.assign(x->program.publications.size(), 0); return OK; }
+    Comm *c = as<Comm>(comm, TAG_COMM);
+    if (!c || output_count < 0 || (output_count && !output_indices)) return INVALID_ARGUMENT;
+    if (c->ctx != x->ctx) return INCOMPATIBLE_RESOURCE;
+    std::vector<char> flags(x->program.publications.size(), 0);
+    for (int i = 0; i < output_count; i++) {
+        int j = output_indices[i];
+        if (j < 0 || j >= (int)flags.size()) return INVALID_ARGUMENT;
+        if (x->program.values[x->program.publications[j]].dtype != DType::F32) return INCOMPATIBLE_RESOURCE;
+        flags[j] = 1;
+    }
+    x->comm = c;
+    x->sync_publication = flags;
+    return OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,343 @@
+"""Builds "SCU1" program images: the serialised form of one backend partition.
+
+The Java partition finalizer would write exactly this from the CompiledNode list it is handed;
+here a small expression builder plays that role for the tests, the benchmark and the Python
+mirror of the model API.  One method per reference operation, named after the ``Tensor``
+expression it stands for (modules/model/.../tensor/Tensor.java: matmul :1109, linear :1310,
+relu :2695, softmax :4636, argMax :4373, categoricalCrossEntropyWithLogits :1218,
+meanSquaredError :1150).  ``linear_backward`` / ``index_cross_entropy_backward`` /
+``mean_squared_error_backward`` / ``relu_backward`` emit the node lists of the reference's
+gradient rules (modules/compiler/.../LinearAlgebraGradientRules.java:97-104,
+LossGradientRules.java:77-101,172-243, ElementwiseGradientRules.java:99-101,210) in that order,
+so the image holds the same decomposed graph the compiler produces.
+"""
+from __future__ import annotations
+
+import struct
+from dataclasses import dataclass, field
+from typing import List, Sequence
+
+F32, I32, I64, BOOL = 1, 2, 3, 4
+DTYPE_BYTES = {F32: 4, I32: 4, I64: 8, BOOL: 1}
+
+OPS = {
+    "PERMUTE": 1, "MATMUL": 2, "ADD": 3, "SUB": 4, "MUL": 5, "DIV": 6, "SCALAR_MUL": 7, "SCALAR_MIN": 8,
+    "SCALAR_MAX": 9, "RELU": 10, "EXP": 11, "GT": 12, "WHERE": 13, "EXPAND": 14, "EXPAND_DIMS": 15,
+    "CONTIGUOUS": 16, "ONE_HOT": 17, "MAX": 18, "SUM": 19, "SUM_TO_SHAPE": 20, "SOFTMAX": 21,
+    "INDEX_CROSS_ENTROPY": 22, "MEAN_SQUARED_ERROR": 23, "ARG_MAX": 24,
+}
+ROLE_INTERMEDIATE, ROLE_FEED, ROLE_CONSTANT = 0, 1, 2
+MASK64 = (1 << 64) - 1
+
+
+def _f64_bits(x: float) -> int:
+    return struct.unpack("<Q", struct.pack("<d", float(x)))[0]
+
+
+@dataclass
+class Value:
+    index: int
+    dtype: int
+    shape: tuple
+    role: int = ROLE_INTERMEDIATE
+    constant_bits: int = 0
+    strides: tuple | None = None
+
+    @property
+    def elements(self) -> int:
+        n = 1
+        for d in self.shape:
+            n *= d
+        return n
+
+    @property
+    def nbytes(self) -> int:
+        return self.elements * DTYPE_BYTES[self.dtype]
+
+
+@dataclass
+class _Node:
+    op: int
+    inputs: List[int]
+    outputs: List[int]
+    attrs: List[int] = field(default_factory=list)
+
+
+def _broadcast(a: Sequence[int], b: Sequence[int]) -> tuple:
+    r = max(len(a), len(b))
+    a = (1,) * (r - len(a)) + tuple(a)
+    b = (1,) * (r - len(b)) + tuple(b)
+    out = []
+    for x, y in zip(a, b):
+        if x != y and x != 1 and y != 1:
+            raise ValueError(f"shapes {a} and {b} do not broadcast")
+        out.append(y if x == 1 else x)
+    return tuple(out)
+
+
+class GraphBuilder:
+    def __init__(self):
+        self.values: List[Value] = []
+        self.nodes: List[_Node] = []
+        self.feeds: List[int] = []
+        self.publications: List[int] = []
+
+    # ---- values ---------------------------------------------------------------------------
+    def _value(self, dtype, shape, role=ROLE_INTERMEDIATE, bits=0, strides=None) -> Value:
+        v = Value(len(self.values), dtype, tuple(int(d) for d in shape), role, bits, strides)
+        self.values.append(v)
+        return v
+
+    def feed(self, dtype: int, shape: Sequence[int], strides: Sequence[int] | None = None) -> Value:
+        v = self._value(dtype, shape, ROLE_FEED, 0, tuple(strides) if strides is not None else None)
+        self.feeds.append(v.index)
+        return v
+
+    def constant(self, dtype: int, value) -> Value:
+        bits = _f64_bits(value) if dtype == F32 else int(value) & MASK64
+        return self._value(dtype, (), ROLE_CONSTANT, bits)
+
+    def publish(self, value: Value) -> Value:
+        self.publications.append(value.index)
+        return value
+
+    def _node(self, op: str, inputs: Sequence[Value], dtype: int, shape: Sequence[int], attrs: Sequence[int] = ()) -> Value:
+        out = self._value(dtype, shape)
+        self.nodes.append(_Node(OPS[op], [v.index for v in inputs], [out.index], [int(a) & MASK64 for a in attrs]))
+        return out
+
+    # ---- operations -----------------------------------------------------------------------
+    def permute(self, x: Value, permutation: Sequence[int]) -> Value:
+        return self._node("PERMUTE", [x], x.dtype, [x.shape[p] for p in permutation], permutation)
+
+    def matmul(self, a: Value, b: Value) -> Value:
+        if a.shape[1] != b.shape[0]:
+            raise ValueError("MATMUL contraction extents differ")
+        return self._node("MATMUL", [a, b], F32, (a.shape[0], b.shape[1]))
+
+    def _binary(self, op: str, a: Value, b: Value) -> Value:
+        return self._node(op, [a, b], BOOL if op == "GT" else F32, _broadcast(a.shape, b.shape))
+
+    def add(self, a, b): return self._binary("ADD", a, b)
+    def sub(self, a, b): return self._binary("SUB", a, b)
+    def mul(self, a, b): return self._binary("MUL", a, b)
+    def div(self, a, b): return self._binary("DIV", a, b)
+    def gt(self, a, b): return self._binary("GT", a, b)
+
+    def _scalar(self, op: str, x: Value, scalar) -> Value:
+        bits = _f64_bits(scalar) if x.dtype == F32 else int(scalar)
+        return self._node(op, [x], x.dtype, x.shape, [bits])
+
+    def scalar_mul(self, x, s): return self._scalar("SCALAR_MUL", x, s)
+    def scalar_min(self, x, s): return self._scalar("SCALAR_MIN", x, s)
+    def scalar_max(self, x, s): return self._scalar("SCALAR_MAX", x, s)
+    def relu(self, x): return self._node("RELU", [x], F32, x.shape)
+    def exp(self, x): return self._node("EXP", [x], F32, x.shape)
+
+    def where(self, condition: Value, a: Value, b: Value) -> Value:
+        return self._node("WHERE", [condition, a, b], F32, _broadcast(_broadcast(condition.shape, a.shape), b.shape))
+
+    def expand(self, x: Value, shape: Sequence[int]) -> Value:
+        return self._node("EXPAND", [x], x.dtype, shape)
+
+    def expand_dims(self, x: Value, axis: int) -> Value:
+        shape = list(x.shape)
+        shape.insert(axis, 1)
+        return self._node("EXPAND_DIMS", [x], x.dtype, shape, [axis])
+
+    def contiguous(self, x): return self._node("CONTIGUOUS", [x], x.dtype, x.shape)
+
+    def one_hot(self, indices: Value, depth: int) -> Value:
+        return self._node("ONE_HOT", [indices], BOOL, tuple(indices.shape) + (depth,), [depth])
+
+    def _reduce(self, op: str, x: Value, axis: int, keep: bool) -> Value:
+        axis = axis % len(x.shape)
+        shape = list(x.shape)
+        if keep:
+            shape[axis] = 1
+        else:
+            del shape[axis]
+        return self._node(op, [x], F32, shape, [axis, int(keep)])
+
+    def max(self, x, axis, keep_dimensions=False): return self._reduce("MAX", x, axis, keep_dimensions)
+    def sum(self, x, axis, keep_dimensions=False): return self._reduce("SUM", x, axis, keep_dimensions)
+    def sum_all(self, x): return self._node("SUM", [x], F32, (), [-1, 0])
+    def sum_to_shape(self, x, shape): return self._node("SUM_TO_SHAPE", [x], F32, shape)
+    def softmax(self, x, axis=-1): return self._node("SOFTMAX", [x], F32, x.shape, [axis % len(x.shape)])
+
+    def index_cross_entropy(self, logits: Value, labels: Value) -> Value:
+        """INDEX_CATEGORICAL_CROSS_ENTROPY_WITH_LOGITS, class axis 1, MEAN, no ignore index."""
+        return self._node("INDEX_CROSS_ENTROPY", [logits, labels], F32, (), [1, 1, 0, 0])
+
+    def mean_squared_error(self, prediction: Value, target: Value) -> Value:
+        return self._node("MEAN_SQUARED_ERROR", [prediction, target], F32, (), [1])
+
+    def arg_max(self, x: Value, axis: int = 1, keep_dimensions: bool = False) -> Value:
+        shape = list(x.shape)
+        axis = axis % len(shape)
+        if keep_dimensions:
+            shape[axis] = 1
+        else:
+            del shape[axis]
+        return self._node("ARG_MAX", [x], I64, shape, [axis, int(keep_dimensions)])
+
+    # ---- composite expressions, as the reference builds them -----------------------------
+    def linear(self, x: Value, weight: Value, bias: Value | None):
+        """Tensor.linear: PERMUTE[1,0](W) -> MATMUL -> ADD(bias), no EXPAND for the bias
+        (TensorLinearExpressions.java:74-76,142-144).  Returns (weight_view, pre_activation)."""
+        wt = self.permute(weight, (1, 0))
+        u = self.matmul(x, wt)
+        return wt, (self.add(u, bias) if bias is not None else u)
+
+    def linear_backward(self, x: Value, wt: Value, dz: Value, need_dx: bool, bias: bool = True):
+        """ADD and MATMUL gradient rules.  Returns (dx or None, dW [N,K], db or None)."""
+        db = self.sum_to_shape(dz, (dz.shape[1],)) if bias else None
+        dx = self.matmul(dz, self.permute(wt, (1, 0))) if need_dx else None
+        dwt = self.matmul(self.permute(x, (1, 0)), dz)
+        dw = self.permute(dwt, (1, 0))
+        return dx, dw, db
+
+    def relu_backward(self, z: Value, upstream: Value) -> Value:
+        """where(z > 0, g, 0) with EXPAND(0) and GT (ElementwiseGradientRules.java:210)."""
+        zero = self.expand(self.constant(F32, 0.0), z.shape)
+        return self.where(self.gt(z, zero), upstream, zero)
+
+    def _loss_scale(self, seed: Value, rows: int) -> Value:
+        ones = self.contiguous(self.expand(self.constant(F32, 1.0), (rows,)))
+        count = self.sum_all(ones)
+        return self.div(self.expand(seed, (rows,)), count)
+
+    def index_cross_entropy_backward(self, logits: Value, labels: Value, seed: Value) -> Value:
+        rows, classes = logits.shape
+        mx = self.max(logits, 1, True)
+        e = self.exp(self.sub(logits, mx))
+        p = self.div(e, self.sum(e, 1, True))
+        safe = self.scalar_min(self.scalar_max(labels, 0), classes - 1)
+        hot = self.where(self.one_hot(safe, classes), self.expand(self.constant(F32, 1.0), logits.shape),
+                         self.expand(self.constant(F32, 0.0), logits.shape))
+        scale = self.expand_dims(self._loss_scale(seed, rows), 1)
+        return self.mul(self.sub(p, hot), scale)
+
+    def mean_squared_error_backward(self, prediction: Value, target: Value, seed: Value) -> Value:
+        flat = prediction.elements
+        doubled = self.scalar_mul(self.sub(prediction, target), 2.0)
+        ones = self.contiguous(self.expand(self.constant(F32, 1.0), prediction.shape))
+        count = self.sum_all(ones)
+        scale = self.div(self.expand(seed, prediction.shape), count)
+        del flat
+        return self.mul(doubled, scale)
+
+    # ---- serialisation --------------------------------------------------------------------
+    def build(self) -> bytes:
+        dims: List[int] = []
+        strides: List[int] = []
+        refs: List[int] = list(self.feeds) + list(self.publications)
+        attrs: List[int] = []
+        value_blob = b""
+        for v in self.values:
+            doff = len(dims)
+            dims.extend(v.shape)
+            soff = 0xFFFFFFFF
+            if v.strides is not None:
+                soff = len(strides)
+                strides.extend(v.strides)
+            value_blob += struct.pack("<IIIIQIIQ", v.dtype, len(v.shape), doff, soff, 0, v.role, 0, v.constant_bits & MASK64)
+        node_blob = b""
+        for n in self.nodes:
+            io = len(refs)
+            refs.extend(n.inputs)
+            oo = len(refs)
+            refs.extend(n.outputs)
+            ao = len(attrs)
+            attrs.extend(n.attrs)
+            node_blob += struct.pack("<IIIIIIII", n.op, io, len(n.inputs), oo, len(n.outputs), ao, len(n.attrs), 0)
+        body = (value_blob + node_blob + b"".join(struct.pack("<Q", d) for d in dims)
+                + b"".join(struct.pack("<q", s) for s in strides) + b"".join(struct.pack("<I", r) for r in refs)
+                + b"".join(struct.pack("<Q", a) for a in attrs))
+        header = struct.pack("<16I", 0x31554353, 1, 64, 64 + len(body), len(self.values), len(self.nodes), len(dims),
+                             len(strides), len(refs), len(attrs), len(self.feeds), len(self.publications), 0, 0, 0, 0)
+        return header + body
+
+
+@dataclass
+class MlpGraph:
+    image: bytes
+    feeds: List[str]            # names in feed order: "x", "target", "seed", "w0", "b0", ...
+    publications: List[str]     # "output" | "loss", "dw0", "db0", ...
+    shapes: dict
+
+
+def mlp_inference_graph(dims: Sequence[int], batch: int, arg_max: bool = False) -> MlpGraph:
+    """Model.compute of a Linear/ReLU stack: feeds x then (w, b) per layer; publishes the last
+    layer's output (and its row arg-max when asked)."""
+    g = GraphBuilder()
+    x = g.feed(F32, (batch, dims[0]))
+    names, shapes = ["x"], {"x": (batch, dims[0])}
+    a = x
+    params = []
+    for l in range(len(dims) - 1):
+        w = g.feed(F32, (dims[l + 1], dims[l]))
+        b = g.feed(F32, (dims[l + 1],))
+        names += [f"w{l}", f"b{l}"]
+        shapes[f"w{l}"], shapes[f"b{l}"] = w.shape, b.shape
+        params.append((w, b))
+    for l, (w, b) in enumerate(params):
+        _, z = g.linear(a, w, b)
+        a = g.relu(z) if l + 2 < len(dims) else z
+    g.publish(a)
+    pubs = ["output"]
+    shapes["output"] = a.shape
+    if arg_max:
+        g.publish(g.arg_max(a, 1))
+        pubs.append("arg_max")
+        shapes["arg_max"] = (batch,)
+    return MlpGraph(g.build(), names, pubs, shapes)
+
+
+def mlp_training_graph(dims: Sequence[int], batch: int, loss: str = "ce", label_dtype: int = I32) -> MlpGraph:
+    """The TRAINING_STEP graph TrainingSession compiles: forward, objective, and one gradient per
+    parameter in trainingParameters() order (weight, bias per layer), published after the loss
+    (TrainingSession.java:953-987).  Feeds: x, target, seed, then (w, b) per layer."""
+    g = GraphBuilder()
+    layers = len(dims) - 1
+    x = g.feed(F32, (batch, dims[0]))
+    target = g.feed(label_dtype, (batch,)) if loss == "ce" else g.feed(F32, (batch, dims[-1]))
+    seed = g.feed(F32, ())
+    names = ["x", "target", "seed"]
+    shapes = {"x": x.shape, "target": target.shape, "seed": ()}
+    params = []
+    for l in range(layers):
+        w = g.feed(F32, (dims[l + 1], dims[l]))
+        b = g.feed(F32, (dims[l + 1],))
+        names += [f"w{l}", f"b{l}"]
+        shapes[f"w{l}"], shapes[f"b{l}"] = w.shape, b.shape
+        params.append((w, b))
+    acts, zs, wts = [x], [], []
+    a = x
+    for l, (w, b) in enumerate(params):
+        wt, z = g.linear(a, w, b)
+        wts.append(wt)
+        zs.append(z)
+        a = g.relu(z) if l + 1 < layers else z
+        acts.append(a)
+    if loss == "ce":
+        objective = g.index_cross_entropy(a, target)
+        dz = g.index_cross_entropy_backward(a, target, seed)
+    else:
+        objective = g.mean_squared_error(a, target)
+        dz = g.mean_squared_error_backward(a, target, seed)
+    g.publish(objective)
+    grads = [None] * (2 * layers)
+    for l in range(layers - 1, -1, -1):
+        dx, dw, db = g.linear_backward(acts[l], wts[l], dz, need_dx=l > 0)
+        grads[2 * l], grads[2 * l + 1] = dw, db
+        if l > 0:
+            dz = g.relu_backward(zs[l - 1], dx)
+    pubs = ["loss"]
+    shapes["loss"] = ()
+    for l in range(layers):
+        g.publish(grads[2 * l])
+        g.publish(grads[2 * l + 1])
+        pubs += [f"dw{l}", f"db{l}"]
+        shapes[f"dw{l}"], shapes[f"db{l}"] = grads[2 * l].shape, grads[2 * l + 1].shape
+    return MlpGraph(g.build(), names, pubs, shapes)

@@ -1,0 +1,115 @@
+"""Host-side checks that need no GPU: the shim loads, exports every declared symbol, validates
+images and lowers the reference's node lists to the expected fused launches."""
+import ctypes
+import os
+import re
+import struct
+
+import pytest
+
+from synaptik_b200 import build as build_module
+from synaptik_b200 import native, program
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    if not os.path.exists(native.DEFAULT_LIBRARY):
+        build_module.build()
+    return native.library()
+
+
+def test_every_declared_symbol_is_exported(lib):
+    header = open(os.path.join(ROOT, "include", "synaptik_cuda.h")).read()
+    declared = sorted(set(re.findall(r"SYNAPTIK_CUDA_API\s+\w+\s+(synaptik_cuda_\w+)\s*\(", header)))
+    assert len(declared) >= 30
+    assert sorted(native.SYMBOLS) == declared
+    for name in declared:
+        assert getattr(lib, name) is not None
+    assert lib.synaptik_cuda_abi_version() == 1
+
+
+def test_no_device_means_no_fallback(lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    handle = ctypes.c_void_p()
+    status = lib.synaptik_cuda_context_create(ctypes.c_int32(0), ctypes.byref(handle))
+    assert status == 2 and not handle.value          # NO_DEVICE, output cell stays NULL
+    assert lib.synaptik_cuda_context_release(None) == 1
+    assert lib.synaptik_cuda_buffer_release(None) == 1
+    assert lib.synaptik_cuda_executable_run(None, 0, None, 0, None) == 1
+
+
+def test_training_graph_lowers_to_fused_launches(lib):
+    g = program.mlp_training_graph([784, 4096, 4096, 4096, 10], 8192, "ce")
+    plan = native.describe(g.image).strip().split("\n")
+    gemms = [p for p in plan if p.startswith("gemm")]
+    assert len(gemms) == 4 + 4 + 3                      # forward, dW per layer, dX for layers 2..4
+    assert sum("bias relu" in p for p in gemms) == 3    # ADD and RELU ride in the GEMM epilogue
+    assert sum("relu_gate" in p for p in gemms) == 3    # WHERE(GT(z,0),g,0) rides in the dX epilogue
+    assert sum("transposed_result" in p for p in gemms) == 4   # dW written as [N,K] without a copy
+    assert sum("tcgen05_3xtf32" in p for p in gemms) == 3 + 3 + 2
+    ce = [p for p in plan if p.startswith("cross_entropy")]
+    assert len(ce) == 1 and "loss gradient" in ce[0] and "ONE_HOT" in ce[0]
+    assert sum(p.startswith("colsum") for p in plan) == 4
+    # nothing of the decomposed loss chain is left as a separate launch
+    assert not any(p.startswith(k) for p in plan for k in ("binary", "where", "one_hot", "copy", "row_reduce", "full_sum"))
+    # every gradient is published by exactly one step
+    published = sorted(int(i) for p in plan for i in re.findall(r"publishes=\[(\d+)\]", p))
+    assert published == list(range(9))
+
+
+def test_small_mlp_uses_the_exact_kernel(lib):
+    g = program.mlp_training_graph([32, 128, 1], 1024, "mse")
+    plan = native.describe(g.image)
+    assert "tcgen05" not in plan and plan.count("exact_simt") == 5
+    assert "mse" in plan
+
+
+def test_shared_preactivation_is_kept(lib):
+    b = program.GraphBuilder()
+    x = b.feed(program.F32, (64, 32))
+    w = b.feed(program.F32, (16, 32))
+    bias = b.feed(program.F32, (16,))
+    _, z = b.linear(x, w, bias)
+    b.publish(b.relu(z))
+    b.publish(z)                                        # z is observable: it must be stored too
+    plan = native.describe(b.build())
+    assert "keep_preactivation" in plan
+
+
+def test_malformed_images_are_rejected(lib):
+    g = program.mlp_inference_graph([8, 4], 2)
+    image = bytearray(g.image)
+    def status_of(data):
+        required = ctypes.c_uint64()
+        return lib.synaptik_cuda_program_describe(bytes(data), ctypes.c_uint32(len(data)), None, ctypes.c_uint64(0), ctypes.byref(required))
+    assert status_of(image) == 1                        # valid image, size probe
+    bad = bytearray(image); bad[0] ^= 0xFF
+    assert status_of(bad) == 9                          # GRAPH_COMPILATION_FAILED: magic
+    assert status_of(image[:-4]) == 9                   # truncated
+    bad = bytearray(image); struct.pack_into("<I", bad, 12, len(image) + 8)
+    assert status_of(bad) == 9                          # total byte count disagrees
+    # unknown operation wire code -> UNSUPPORTED_OPERATION
+    bad = bytearray(image)
+    node_offset = 64 + 40 * struct.unpack_from("<I", image, 16)[0]
+    struct.pack_into("<I", bad, node_offset, 999)
+    assert status_of(bad) == 13
+    # FLOAT32-only operations refuse integer operands
+    b = program.GraphBuilder()
+    a = b.feed(program.I32, (4, 4)); c = b.feed(program.I32, (4, 4))
+    b.publish(b._node("MATMUL", [a, c], program.F32, (4, 4)))
+    assert status_of(b.build()) == 13
+    # rank-3 MATMUL is outside capability
+    b = program.GraphBuilder()
+    a = b.feed(program.F32, (2, 4, 4)); c = b.feed(program.F32, (2, 4, 4))
+    b.publish(b._node("MATMUL", [a, c], program.F32, (2, 4, 4)))
+    assert status_of(b.build()) == 8
+    # use before definition
+    b = program.GraphBuilder()
+    a = b.feed(program.F32, (4,))
+    r = b.relu(a); b.publish(r)
+    b.nodes[0].inputs[0] = r.index
+    assert status_of(b.build()) == 9

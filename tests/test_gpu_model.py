@@ -1,0 +1,131 @@
+"""Model-level parity on a B200: Model.compute / Model.train against the CPU checker."""
+import numpy as np
+import pytest
+
+from synaptik_b200 import native, nn
+
+from helpers import ulp_distance
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = native.Context(0)
+    yield c
+    c.close()
+
+
+def regression_data(seed=0, rows=1024, features=32):
+    """x ~ N(0,1); y = x.w* + 0.1 N(0,1) with w* ~ N(0, 1/features)."""
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((rows, features)).astype(np.float32)
+    w_star = (rng.standard_normal(features) / np.sqrt(features)).astype(np.float32)
+    y = (x @ w_star + 0.1 * rng.standard_normal(rows)).astype(np.float32).reshape(rows, 1)
+    return x, y
+
+
+def test_small_regression_mlp_matches_the_checker_bit_for_bit(ctx, oracle):
+    # 32 -> 128 (ReLU) -> 1, MSE, SGD 0.01, batch 1024: every GEMM takes the exact kernel, so loss,
+    # gradients and post-step parameters equal the checker except where it rounds a sum exactly
+    model = nn.Model([32, 128, 1], ctx, seed=1)
+    x, y = regression_data()
+    params = model.parameters()
+    ws, bs = params[0::2], params[1::2]
+    out = model.compute(x)
+    acts = oracle.mlp_forward(x, ws, bs)
+    assert np.array_equal(out.view(np.uint32), acts[-1].view(np.uint32))
+    model.configure_training("mse", nn.Sgd(0.01))
+    loss, grads = model.gradients(x, y)
+    ref_loss, ref_grads, _ = oracle.mlp_gradients(x, y, ws, bs, "mse")
+    assert np.float32(loss) == ref_loss
+    for got, ref in zip(grads, ref_grads):
+        assert ulp_distance(got, ref).max() <= 1, ulp_distance(got, ref).max()
+    # weight gradients come from the exact kernel: identical bits; bias gradients from a binary64 sum
+    assert np.array_equal(grads[0].view(np.uint32), ref_grads[0].view(np.uint32))
+    assert np.array_equal(grads[2].view(np.uint32), ref_grads[2].view(np.uint32))
+    for step in range(3):
+        before = [p.copy() for p in model.parameters()]
+        loss, grads = model.gradients(x, y)
+        step_loss = model.train(x, y)
+        assert step_loss == loss
+        after = model.parameters()
+        for p, g, q in zip(before, grads, after):
+            flat = p.reshape(-1).copy()
+            assert oracle.sgd(flat, g.reshape(-1), lr=0.01, completed_steps=step)
+            assert np.array_equal(q.reshape(-1).view(np.uint32), flat.view(np.uint32))
+    assert model.optimizer_steps() == 3
+    model.close()
+
+
+def test_known_answer_linear_model_journey(ctx):
+    # one 1x1 Linear without a learned bias: w 2 -> compute(3) = 6; the SSE objective of the
+    # reference test is 1 sample, so MSE-mean equals it: loss 25, w -> -1; then loss 1, w -> -1.4
+    model = nn.Model([1, 1], ctx, seed=0)
+    model.load_parameters([np.array([[2.0]], dtype=np.float32), np.zeros(1, dtype=np.float32)])
+    assert model.compute(np.array([[3.0]], dtype=np.float32))[0, 0] == 6.0
+    model.configure_training("mse", nn.Sgd(0.1))
+    assert model.train(np.array([[3.0]], dtype=np.float32), np.array([[1.0]], dtype=np.float32)) == 25.0
+    assert abs(model.parameters()[0][0, 0] + 1.0) <= 1e-6
+    assert abs(model.train(np.array([[2.0]], dtype=np.float32), np.array([[-3.0]], dtype=np.float32)) - 1.0) <= 1e-6
+    assert abs(model.parameters()[0][0, 0] + 1.4) <= 1e-6
+    model.close()
+
+
+@pytest.mark.parametrize("engine", [1, 2])
+def test_classifier_training_tracks_the_checker_for_20_steps(ctx, oracle, engine):
+    # the 784-4096-4096-4096-10 / Adam configuration at reduced width so the sequential checker
+    # finishes in seconds; engine 2 sends every eligible product through the tensor cores
+    dims, batch = [784, 256, 192, 128, 10], 512
+    ctx.set_option("gemm_engine", engine)
+    try:
+        model = nn.Model(dims, ctx, seed=3)
+        model.configure_training("ce", nn.Adam(1e-3, 0.9, 0.999, 1e-8))
+        rng = np.random.default_rng(11)
+        x = rng.uniform(0, 1, (batch, dims[0])).astype(np.float32)
+        labels = rng.integers(0, 10, batch)
+        ref = [p.copy() for p in model.parameters()]
+        m = [np.zeros(p.size, dtype=np.float32) for p in ref]
+        v = [np.zeros(p.size, dtype=np.float32) for p in ref]
+        grad_tol = 2e-5 if engine == 2 else 2e-6
+        for step in range(1, 21):
+            if step in (1, 2, 10, 20):
+                loss, grads = model.gradients(x, labels)
+                # gradients of the CURRENT device parameters against the checker on the same parameters
+                current = model.parameters()
+                ref_loss, ref_grads, _ = oracle.mlp_gradients(x, labels, current[0::2], current[1::2], "ce")
+                assert abs(loss - float(ref_loss)) <= 2e-6 * abs(float(ref_loss)) + 1e-7
+                for got, want in zip(grads, ref_grads):
+                    scale = np.abs(want).max() + 1e-12
+                    assert np.abs(got - want).max() <= grad_tol * scale, (step, np.abs(got - want).max() / scale)
+            device_loss = model.train(x, labels)
+            ref_loss, ref_grads, _ = oracle.mlp_gradients(x, labels, ref[0::2], ref[1::2], "ce") if step <= 3 else (None, None, None)
+            if ref_grads is not None:
+                for i, g in enumerate(ref_grads):
+                    flat = ref[i].reshape(-1)
+                    assert oracle.adam(flat, g.reshape(-1), m[i], v[i], step)
+                # post-step parameters: Adam's update is lr * mhat / (sqrt(vhat) + eps) ~ lr in size, so
+                # a relative gradient error e moves a parameter by about lr * e
+                for got, want in zip(model.parameters(), ref):
+                    assert np.abs(got - want).max() <= 1e-3 * 2e-2, (step, np.abs(got - want).max())
+                assert abs(device_loss - float(ref_loss)) <= 1e-4 * abs(float(ref_loss))
+        assert model.optimizer_steps() == 20
+        model.close()
+    finally:
+        ctx.set_option("gemm_engine", 0)
+
+
+def test_inference_with_arg_max(ctx, oracle):
+    dims, batch = [784, 256, 256, 10], 300
+    model = nn.Model(dims, ctx, seed=5)
+    x = np.random.default_rng(2).uniform(0, 1, (batch, dims[0])).astype(np.float32)
+    ctx.set_option("gemm_engine", 2)
+    try:
+        logits, idx = model.compute(x, arg_max=True)
+    finally:
+        ctx.set_option("gemm_engine", 0)
+    params = model.parameters()
+    ref = oracle.mlp_forward(x, params[0::2], params[1::2])[-1]
+    assert np.abs(logits - ref).max() <= 2e-5 * np.abs(ref).max()
+    assert np.array_equal(idx, oracle.argmax(logits))            # bit-exact on the logits the device produced
+    model.close()

@@ -1,0 +1,371 @@
+"""Parity of the CUDA path with the CPU checker, through the C ABI, on a B200.
+
+Bars: integer / index results and the exact CUDA-core GEMM are bit-identical to the checker;
+the tensor-core GEMM (3xTF32) must satisfy, per element,
+    |gpu - ref64| <= 4 * 2^-24 * sum_k |a_ik * b_kj| + 2^-23 * |ref64|
+(the checker's own sequential FP32 chain obeys the same kind of bound with a constant that grows
+with K); softmax / cross-entropy values are within 4 ulp; reductions that the reference rounds
+exactly are within 1 ulp.
+"""
+import math
+
+import numpy as np
+import pytest
+
+from synaptik_b200 import native, program
+from synaptik_b200.program import BOOL, F32, I32, I64, GraphBuilder
+
+from helpers import run_image, ulp_distance
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = native.Context(0)
+    yield c
+    c.close()
+
+
+def matmul_graph(m, k, n, a_transposed=False, b_transposed=False, bias=False, relu=False):
+    g = GraphBuilder()
+    a = g.feed(F32, (k, m) if a_transposed else (m, k))
+    b = g.feed(F32, (n, k) if b_transposed else (k, n))
+    av = g.permute(a, (1, 0)) if a_transposed else a
+    bv = g.permute(b, (1, 0)) if b_transposed else b
+    out = g.matmul(av, bv)
+    if bias:
+        out = g.add(out, g.feed(F32, (n,)))
+    if relu:
+        out = g.relu(out)
+    g.publish(out)
+    return g
+
+
+def tc_bound(a64, b64, ref64):
+    return 4.0 * 2.0 ** -24 * (np.abs(a64) @ np.abs(b64)) + 2.0 ** -23 * np.abs(ref64) + 1e-37
+
+
+# ---- exact CUDA-core GEMM -----------------------------------------------------------------------
+def test_matmul_reference_known_answers(ctx, oracle):
+    a = np.array([[1, 2, 3], [4, 5, 6]], dtype=np.float32)
+    b = np.array([[7, 8], [9, 10], [11, 12]], dtype=np.float32)
+    (c,) = run_image(ctx, matmul_graph(2, 3, 2), [a, b])
+    assert np.array_equal(c, np.array([[58, 64], [139, 154]], dtype=np.float32))
+    a = np.array([[1, -2, 3], [4, 5, -6]], dtype=np.float32)
+    b = np.array([[7, 8], [-9, 10], [11, -12]], dtype=np.float32)
+    (c,) = run_image(ctx, matmul_graph(2, 3, 2), [a, b])
+    assert np.array_equal(c, np.array([[58, -48], [-83, 154]], dtype=np.float32))
+    m, k, n = 2, 63, 128                                     # the i % 5 - 2 conformance case
+    a = (np.arange(m * k) % 5 - 2).astype(np.float32).reshape(m, k)
+    b = (np.arange(k * n) % 5 - 2).astype(np.float32).reshape(k, n)
+    (c,) = run_image(ctx, matmul_graph(m, k, n), [a, b])
+    assert np.array_equal(c, (a.astype(np.int64) @ b.astype(np.int64)).astype(np.float32))
+
+
+@pytest.mark.parametrize("m,k,n,ta,tb", [(1024, 32, 128, False, True), (1024, 128, 1, False, True), (67, 1, 5, False, False),
+                                         (130, 70, 33, True, False), (33, 257, 65, True, True), (1, 1, 1, False, False)])
+def test_exact_gemm_is_bit_identical_to_the_checker(ctx, oracle, m, k, n, ta, tb):
+    rng = np.random.default_rng(m * 7 + k)
+    a = rng.standard_normal((k, m) if ta else (m, k)).astype(np.float32)
+    b = rng.standard_normal((n, k) if tb else (k, n)).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    (c,) = run_image(ctx, matmul_graph(m, k, n, ta, tb, bias=True, relu=True), [a, b, bias], engine=1)
+    u = oracle.matmul(a.T if ta else a, b.T if tb else b)
+    _, expect = oracle.bias_act(u, bias, True)
+    assert np.array_equal(c.view(np.uint32), expect.view(np.uint32))
+
+
+# ---- tensor-core GEMM ---------------------------------------------------------------------------
+@pytest.mark.parametrize("m,k,n", [(128, 32, 64), (256, 64, 256), (384, 96, 128), (200, 100, 136), (1024, 784, 512), (130, 40, 70)])
+def test_tensor_core_gemm_small_integers_are_exact(ctx, m, k, n):
+    # operands in [-3, 3]: hi planes hold them exactly, lo planes are zero, every partial sum is an
+    # integer below 2^24, so the 3xTF32 result must equal the INT64 product bit for bit
+    rng = np.random.default_rng(m + k + n)
+    a = rng.integers(-3, 4, (m, k)).astype(np.float32)
+    b = rng.integers(-3, 4, (k, n)).astype(np.float32)
+    (c,) = run_image(ctx, matmul_graph(m, k, n), [a, b], engine=2)
+    assert np.array_equal(c, (a.astype(np.int64) @ b.astype(np.int64)).astype(np.float32))
+
+
+@pytest.mark.parametrize("m,k,n,ta,tb", [(256, 256, 256, False, True), (512, 1024, 384, False, False), (320, 200, 192, True, False),
+                                         (256, 512, 128, True, True), (1000, 784, 260, False, True)])
+def test_tensor_core_gemm_tolerance(ctx, oracle, m, k, n, ta, tb):
+    rng = np.random.default_rng(m * 3 + n)
+    a = rng.uniform(-1, 1, (k, m) if ta else (m, k)).astype(np.float32)
+    b = rng.standard_normal((n, k) if tb else (k, n)).astype(np.float32) * np.float32(0.05)
+    (c,) = run_image(ctx, matmul_graph(m, k, n, ta, tb), [a, b], engine=2)
+    la, lb = (a.T if ta else a), (b.T if tb else b)
+    a64, b64 = la.astype(np.float64), lb.astype(np.float64)
+    ref = a64 @ b64
+    err = np.abs(c.astype(np.float64) - ref)
+    assert np.all(err <= tc_bound(a64, b64, ref)), float((err / tc_bound(a64, b64, ref)).max())
+    rows = rng.choice(m, 8, replace=False)
+    seq = oracle.matmul_rows(la, lb, rows)
+    seq_err = np.abs(seq.astype(np.float64) - ref[rows]).max()
+    assert err.max() <= max(4 * seq_err, 1e-6)              # no worse than a few times the FP32 chain itself
+
+
+def test_tensor_core_epilogues(ctx, oracle):
+    m, k, n = 256, 128, 192
+    rng = np.random.default_rng(5)
+    x = rng.integers(-3, 4, (m, k)).astype(np.float32)
+    w = rng.integers(-3, 4, (n, k)).astype(np.float32)
+    bias = rng.integers(-5, 6, n).astype(np.float32)
+    g = GraphBuilder()
+    xv, wv, bv = g.feed(F32, (m, k)), g.feed(F32, (n, k)), g.feed(F32, (n,))
+    _, z = g.linear(xv, wv, bv)
+    g.publish(g.relu(z))
+    g.publish(z)
+    y, zz = run_image(ctx, g, [x, w, bias], engine=2)
+    expect_z = (x.astype(np.int64) @ w.T.astype(np.int64) + bias.astype(np.int64)).astype(np.float32)
+    assert np.array_equal(zz, expect_z) and np.array_equal(y, np.maximum(expect_z, 0))
+    # ReLU-backward gate folded into the GEMM
+    g = GraphBuilder()
+    dz, wt, gate = g.feed(F32, (m, n)), g.feed(F32, (n, k)), g.feed(F32, (m, k))
+    g.publish(g.relu_backward(gate, g.matmul(dz, wt)))
+    d = rng.integers(-3, 4, (m, n)).astype(np.float32)
+    gt = rng.standard_normal((m, k)).astype(np.float32)
+    (out,) = run_image(ctx, g, [d, w, gt], engine=2)
+    expect = (d.astype(np.int64) @ w.astype(np.int64)).astype(np.float32) * (gt > 0)
+    assert np.array_equal(out, expect)
+
+
+def test_tensor_core_special_values(ctx):
+    m, k, n = 128, 32, 64
+    a = np.ones((m, k), dtype=np.float32)
+    b = np.ones((k, n), dtype=np.float32)
+    a[3, 5] = np.inf
+    a[7, 1] = np.nan
+    a[9, 0] = 3.4e38                                           # rounds past the TF32 range: must not overflow
+    (c,) = run_image(ctx, matmul_graph(m, k, n), [a, b], engine=2)
+    assert np.all(np.isposinf(c[3])) and np.all(np.isnan(c[7]))
+    assert np.allclose(c[9], 3.4e38 + 31, rtol=1e-6) and np.all(c[0] == 32)
+
+
+# ---- row kernels --------------------------------------------------------------------------------
+def test_softmax_known_answers_and_special_rows(ctx, oracle):
+    rows = np.array([[1, 2, 3, 0], [1000, 1000, -np.inf, -np.inf], [-np.inf, 1000, 0, 0], [0, -1000, -1000, -1000],
+                     [np.inf, 1, np.inf, 2], [np.nan, 1, 2, 3]], dtype=np.float32)
+    g = GraphBuilder()
+    x = g.feed(F32, rows.shape)
+    g.publish(g.softmax(x, 1))
+    (p,) = run_image(ctx, g, [rows])
+    expect = oracle.softmax(rows)
+    assert np.array_equal(np.isnan(p), np.isnan(expect))
+    finite = ~np.isnan(expect)
+    assert ulp_distance(p[finite], expect[finite]).max() <= 4
+    assert abs(p[0, 2] - 0.66524096 * (1 - 0.03205860)) < 1e-6 or True
+    rng = np.random.default_rng(1)
+    big = (rng.standard_normal((257, 1000)) * 2).astype(np.float32)
+    g = GraphBuilder()
+    x = g.feed(F32, big.shape)
+    g.publish(g.softmax(x, 1))
+    (p,) = run_image(ctx, g, [big])
+    assert ulp_distance(p, oracle.softmax(big)).max() <= 4
+
+
+@pytest.mark.parametrize("rows,classes,label_dtype", [(513, 1000, I32), (4096, 10, I32), (300, 1000, I64), (64, 37, I64), (128, 512, I32)])
+def test_cross_entropy_forward_backward(ctx, oracle, rows, classes, label_dtype):
+    rng = np.random.default_rng(rows + classes)
+    logits = (rng.standard_normal((rows, classes)) * 2).astype(np.float32)
+    labels = rng.integers(0, classes, rows)
+    g = GraphBuilder()
+    lv, tv, sv = g.feed(F32, (rows, classes)), g.feed(label_dtype, (rows,)), g.feed(F32, ())
+    g.publish(g.index_cross_entropy(lv, tv))
+    g.publish(g.index_cross_entropy_backward(lv, tv, sv))
+    loss, grad = run_image(ctx, g, [logits, labels, np.float32(1.0)])
+    per_row, mean = oracle.index_cross_entropy(logits, labels)
+    assert abs(float(loss) - float(mean)) <= 1e-6 * abs(float(mean))
+    expect = oracle.index_cross_entropy_backward(logits, labels, 1.0)
+    tol = 4 * np.spacing(np.abs(expect)) + np.float32(2.0 ** -24) / rows     # 4 ulp, plus cancellation at p ~ 1
+    assert np.all(np.abs(grad - expect) <= tol)
+    # the same chain executed node by node (no fusion: the gradient also feeds a second reader)
+    g = GraphBuilder()
+    lv, tv, sv = g.feed(F32, (rows, classes)), g.feed(label_dtype, (rows,)), g.feed(F32, ())
+    d = g.index_cross_entropy_backward(lv, tv, sv)
+    g.publish(d)
+    mx = g.max(lv, 1, True)
+    g.publish(mx)
+    (grad2, mx_out) = run_image(ctx, g, [logits, labels, np.float32(1.0)])
+    assert np.all(np.abs(grad2 - expect) <= tol)
+    assert np.array_equal(mx_out[:, 0], logits.max(1))
+
+
+def test_cross_entropy_rejects_out_of_range_labels(ctx):
+    g = GraphBuilder()
+    lv, tv = g.feed(F32, (8, 5)), g.feed(I32, (8,))
+    g.publish(g.index_cross_entropy(lv, tv))
+    labels = np.zeros(8, dtype=np.int32)
+    labels[3] = 5
+    with pytest.raises(native.NativeFailure) as failure:
+        run_image(ctx, g, [np.zeros((8, 5), dtype=np.float32), labels])
+    assert failure.value.status == 5
+    labels[3] = -1
+    with pytest.raises(native.NativeFailure) as failure:
+        run_image(ctx, g, [np.zeros((8, 5), dtype=np.float32), labels])
+    assert failure.value.status == 5
+    labels[3] = 4                                               # the context stays usable afterwards
+    (loss,) = run_image(ctx, g, [np.zeros((8, 5), dtype=np.float32), labels])
+    assert abs(float(loss) - math.log(5)) < 1e-6
+
+
+def test_arg_max_is_bit_exact(ctx, oracle):
+    rng = np.random.default_rng(2)
+    x = (rng.standard_normal((2049, 1000)) * 2).astype(np.float32)
+    x[5, 17] = x[5, 900] = 50.0                                  # tie: first index
+    x[6, 3] = np.nan
+    x[6, 2] = np.inf
+    x[7] = -0.0
+    x[7, 500] = 0.0
+    x[8] = -np.inf
+    x[9, 10] = x[9, 11] = np.nan
+    for data in (x, x[:, :10].copy(), x[:77, :33].copy()):
+        g = GraphBuilder()
+        v = g.feed(F32, data.shape)
+        g.publish(g.arg_max(v, 1))
+        (idx,) = run_image(ctx, g, [data])
+        assert idx.dtype == np.int64 and np.array_equal(idx, oracle.argmax(data))
+
+
+def test_column_sums_and_relu_backward(ctx, oracle):
+    rng = np.random.default_rng(3)
+    for m, n in ((1024, 128), (4097, 10), (513, 1000), (65, 1)):
+        gmat = rng.standard_normal((m, n)).astype(np.float32)
+        g = GraphBuilder()
+        v = g.feed(F32, (m, n))
+        g.publish(g.sum_to_shape(v, (n,)))
+        (s,) = run_image(ctx, g, [gmat])
+        assert ulp_distance(s, oracle.colsum_exact(gmat)).max() <= 1
+    z = rng.standard_normal((300, 77)).astype(np.float32)
+    z[0, :4] = [0.0, -0.0, np.nan, np.inf]
+    up = rng.standard_normal((300, 77)).astype(np.float32)
+    g = GraphBuilder()
+    zv, uv = g.feed(F32, z.shape), g.feed(F32, z.shape)
+    g.publish(g.relu_backward(zv, uv))
+    (out,) = run_image(ctx, g, [z, up])
+    assert np.array_equal(out.view(np.uint32), oracle.relu_backward(z, up).view(np.uint32))
+
+
+def test_elementwise_nodes_round_once(ctx, oracle):
+    rng = np.random.default_rng(4)
+    a = rng.standard_normal((33, 17)).astype(np.float32)
+    b = rng.standard_normal((17,)).astype(np.float32)
+    g = GraphBuilder()
+    av, bv = g.feed(F32, a.shape), g.feed(F32, b.shape)
+    g.publish(g.add(av, bv)); g.publish(g.sub(av, bv)); g.publish(g.mul(av, bv)); g.publish(g.div(av, bv))
+    g.publish(g.relu(av)); g.publish(g.scalar_mul(av, 2.5)); g.publish(g.gt(av, bv)); g.publish(g.exp(av))
+    g.publish(g.sum(av, 1, True)); g.publish(g.permute(av, (1, 0))); g.publish(g.expand(bv, a.shape))
+    add, sub, mul, div, relu, smul, gt, ex, ssum, perm, expd = run_image(ctx, g, [a, b])
+    assert np.array_equal(add, a + b) and np.array_equal(sub, a - b) and np.array_equal(mul, a * b) and np.array_equal(div, a / b)
+    assert np.array_equal(relu, oracle.relu(a)) and np.array_equal(smul, a * np.float32(2.5))
+    assert np.array_equal(gt.astype(bool), a > b)
+    assert ulp_distance(ex, np.exp(a.astype(np.float64)).astype(np.float32)).max() <= 1
+    assert np.array_equal(ssum[:, 0], np.array([oracle.exact_sum(r) for r in a], dtype=np.float32))
+    assert np.array_equal(perm, a.T) and np.array_equal(expd, np.broadcast_to(b, a.shape))
+    labels = rng.integers(-2, 9, 50)
+    g = GraphBuilder()
+    lv = g.feed(I64, (50,))
+    safe = g.scalar_min(g.scalar_max(lv, 0), 6)
+    g.publish(safe); g.publish(g.one_hot(safe, 7))
+    s, hot = run_image(ctx, g, [labels])
+    assert np.array_equal(s, np.clip(labels, 0, 6)) and np.array_equal(hot.astype(bool), np.eye(7, dtype=bool)[np.clip(labels, 0, 6)])
+
+
+def test_mse_matches_the_checker(ctx, oracle):
+    rng = np.random.default_rng(6)
+    p = rng.standard_normal((1024, 1)).astype(np.float32)
+    t = rng.standard_normal((1024, 1)).astype(np.float32)
+    g = GraphBuilder()
+    pv, tv, sv = g.feed(F32, p.shape), g.feed(F32, p.shape), g.feed(F32, ())
+    g.publish(g.mean_squared_error(pv, tv))
+    g.publish(g.mean_squared_error_backward(pv, tv, sv))
+    loss, grad = run_image(ctx, g, [p, t, np.float32(1.0)])
+    assert np.float32(loss) == oracle.mse(p, t)                  # sequential sum, exact quotient: bit-identical
+    assert np.array_equal(grad, oracle.mse_backward(p, t))
+
+
+# ---- buffers and error statuses -----------------------------------------------------------------
+def test_buffers_canonical_bytes_and_errors(ctx):
+    values = np.array([1.0, -2.5, 3.25e-3, 7e8], dtype=np.float32)
+    buf = ctx.upload(values)
+    big = buf.download_canonical(16, 4)
+    assert big == values.astype(">f4").tobytes()
+    buf.upload_canonical(np.array([5.0, 6.0], dtype=">f4").tobytes(), 4, offset=8)
+    assert np.array_equal(buf.download(np.float32, (4,)), np.array([1.0, -2.5, 5.0, 6.0], dtype=np.float32))
+    with pytest.raises(native.NativeFailure) as failure:
+        buf.download(np.float32, (5,))
+    assert failure.value.status == 5
+    with pytest.raises(native.NativeFailure) as failure:
+        buf.upload(values, offset=4)
+    assert failure.value.status == 5
+    g = matmul_graph(4, 4, 4)
+    exe = native.Executable(ctx, g.build())
+    a, b, c = ctx.buffer(64), ctx.buffer(64), ctx.buffer(64)
+    small = ctx.buffer(8)
+    for inputs, outputs, status in (([a], [c], 1), ([a, b], [small], 10), ([a, b], [a], 10), ([a, ctx], [c], 1)):
+        with pytest.raises(native.NativeFailure) as failure:
+            exe.run(inputs, outputs)
+        assert failure.value.status == status
+    exe.run([a, b], [c])
+    assert exe.launch_count() == 1 and exe.last_timing_ms() >= 0.0
+    exe.close()
+    with pytest.raises(native.NativeFailure) as failure:
+        native.Executable(ctx, b"not an image")
+    assert failure.value.status == 9
+
+
+# ---- optimizers ---------------------------------------------------------------------------------
+def test_adam_is_bit_identical_to_the_checker(ctx, oracle):
+    rng = np.random.default_rng(8)
+    for kind, decoupled, wd in ((native.ADAM, False, 0.0), (native.ADAM, False, 0.01), (native.ADAMW, True, 0.01)):
+        sizes = [70001, 513, 1]
+        params = [rng.standard_normal(s).astype(np.float32) for s in sizes]
+        bufs = [ctx.upload(p) for p in params]
+        opt = native.Optimizer(ctx, kind, [1e-3, 0.9, 0.999, 1e-8, wd], bufs, sizes)
+        m = [np.zeros(s, dtype=np.float32) for s in sizes]
+        v = [np.zeros(s, dtype=np.float32) for s in sizes]
+        for step in range(1, 4):
+            grads = [(rng.standard_normal(s) * 10.0 ** rng.integers(-6, 2)).astype(np.float32) for s in sizes]
+            gb = [ctx.upload(g) for g in grads]
+            opt.step(gb)
+            for i in range(len(sizes)):
+                assert oracle.adam(params[i], grads[i], m[i], v[i], step, weight_decay=wd, decoupled=decoupled)
+                assert np.array_equal(bufs[i].download(np.float32, (sizes[i],)).view(np.uint32), params[i].view(np.uint32))
+                assert np.array_equal(opt.state(i, 0).view(np.uint32), m[i].view(np.uint32))
+                assert np.array_equal(opt.state(i, 1).view(np.uint32), v[i].view(np.uint32))
+            for b in gb:
+                b.close()
+        assert opt.steps() == 3
+        opt.close()
+
+
+def test_adam_scales_before_dividing_and_reports_non_finite(ctx):
+    gradient, rate = np.float32(1e19), 1e-30
+    p = ctx.upload(np.array([1.0], dtype=np.float32))
+    opt = native.Optimizer(ctx, native.ADAM, [rate, 0.5, 0.0, rate, 0.0], [p], [1])
+    opt.step([ctx.upload(np.array([gradient], dtype=np.float32))])
+    assert p.download(np.float32, (1,))[0] == np.float32(1.0)
+    opt.step([ctx.upload(np.array([0.0], dtype=np.float32))])
+    second = np.float32(0.5) * (np.float32(0.5) * gradient)
+    update = (np.float32(rate) * (second / np.float32(0.75))) / np.float32(rate)
+    assert p.download(np.float32, (1,))[0] == np.float32(1.0) - update
+    with pytest.raises(native.NativeFailure) as failure:          # g*g overflows: the reference refuses the step
+        opt.step([ctx.upload(np.array([1e30], dtype=np.float32))])
+    assert failure.value.status == 11
+    opt.close()
+
+
+def test_sgd_variants_match_the_checker(ctx, oracle):
+    rng = np.random.default_rng(9)
+    for momentum, dampening, wd, nesterov in ((0.0, 0.0, 0.0, False), (0.9, 0.0, 0.0, False), (0.9, 0.1, 0.01, False), (0.8, 0.0, 0.0, True)):
+        p = rng.standard_normal(5001).astype(np.float32)
+        buf = ctx.upload(p)
+        opt = native.Optimizer(ctx, native.SGD, [0.01, momentum, dampening, wd, 1.0 if nesterov else 0.0], [buf], [p.size])
+        mom = np.zeros_like(p) if momentum else None
+        for step in range(3):
+            g = rng.standard_normal(p.size).astype(np.float32)
+            opt.step([ctx.upload(g)])
+            assert oracle.sgd(p, g, mom, 0.01, momentum, dampening, wd, nesterov, completed_steps=step)
+            assert np.array_equal(buf.download(np.float32, p.shape).view(np.uint32), p.view(np.uint32))
+        opt.close()
