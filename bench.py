@@ -301,8 +301,76 @@ def run_cuda(args):
     return 0
 
 
+def run_kernel_case(args):
+    """Single-GPU kernel cases behind the same C ABI: BASELINE.json configs[1] (fused dense layer,
+    forward and backward) and configs[2] (classifier head).  Used for the roofline lines and as the
+    small workloads of the ncu captures."""
+    from synaptik_b200 import native, program
+    from synaptik_b200.program import F32, I32, GraphBuilder
+    ctx = native.Context(0)
+    rng = np.random.default_rng(3)
+    g = GraphBuilder()
+    peak_data, peak_kind = peaks()
+    if args.case == "gemm":
+        m, k, n = args.m, args.k, args.n
+        x, w, b, dy = g.feed(F32, (m, k)), g.feed(F32, (n, k)), g.feed(F32, (n,)), g.feed(F32, (m, n))
+        wt, z = g.linear(x, w, b)
+        g.publish(g.relu(z))
+        if not args.forward_only:
+            dz = g.relu_backward(z, dy)
+            dx, dw, db = g.linear_backward(x, wt, dz, need_dx=True)
+            for v in (dx, dw, db):
+                g.publish(v)
+        bound = np.sqrt(6.0 / (k + n))
+        feeds = [rng.uniform(-1, 1, (m, k)).astype(np.float32), rng.uniform(-bound, bound, (n, k)).astype(np.float32),
+                 rng.uniform(-0.1, 0.1, n).astype(np.float32), rng.standard_normal((m, n)).astype(np.float32)]
+        work = (2.0 if args.forward_only else 6.0) * m * k * n
+        unit, denom, bound_kind = "TFLOP/s", peak_data["bf16_tflops"] / 6.0, "tensor"
+        name = f"dense_layer_{'fwd' if args.forward_only else 'fwd_bwd'}_m{m}_k{k}_n{n}"
+    else:
+        rows, classes = args.m, args.n
+        logits, labels, seed = g.feed(F32, (rows, classes)), g.feed(I32, (rows,)), g.feed(F32, ())
+        g.publish(g.index_cross_entropy(logits, labels))
+        g.publish(g.index_cross_entropy_backward(logits, labels, seed))
+        g.publish(g.arg_max(logits, 1))
+        feeds = [(rng.standard_normal((rows, classes)) * 2).astype(np.float32), rng.integers(0, classes, rows).astype(np.int32),
+                 np.array(1.0, dtype=np.float32)]
+        work = 8.0 * rows * classes + 8.0 * rows + 4.0 * rows * classes + 8.0 * rows      # loss+gradient pass, arg-max pass
+        unit, denom, bound_kind = "GB/s", peak_data["hbm_gbs"], "hbm"
+        name = f"classifier_head_rows{rows}_classes{classes}"
+    exe = native.Executable(ctx, g.build())
+    inputs = [ctx.upload(a) for a in feeds]
+    outputs = [ctx.buffer(max(g.values[i].nbytes, 4)) for i in g.publications]
+    for _ in range(max(args.warmup, 1)):
+        exe.run(inputs, outputs)
+    ctx.set_option("time_steps", 1)
+    ctx.timer_start()
+    for _ in range(args.steps):
+        exe.enqueue(inputs, outputs)
+    ms = ctx.timer_stop()
+    exe.finish()
+    plan = exe.describe().strip().split("\n")
+    steps = exe.step_timings_ms()
+    rate = work * args.steps / (ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9)
+    line = {"metric": f"{args.case}_{unit}", "value": rate, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 1),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": name}, "gpu_launches": exe.launch_count() * args.steps,
+            "roofline": {"bound": bound_kind, "achieved": rate, "peak": denom, "unit": unit, "frac": rate / denom,
+                         "peak_source": peak_kind + (" bf16_tflops / 2 / 3" if unit == "TFLOP/s" else " hbm_gbs"), "traffic": None},
+            "steps_ms": {line.split(" nodes=")[0]: t for line, t in zip(plan, steps)}}
+    print(json.dumps(line))
+    exe.close()
+    ctx.close()
+    return 0
+
+
 def main():
     parser = argparse.ArgumentParser()
+    parser.add_argument("--case", default="train", choices=["train", "gemm", "ce"])
+    parser.add_argument("--m", type=int, default=16384)
+    parser.add_argument("--k", type=int, default=4096)
+    parser.add_argument("--n", type=int, default=4096)
+    parser.add_argument("--forward-only", action="store_true")
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=10)
     parser.add_argument("--warmup", type=int, default=3)
@@ -311,6 +379,8 @@ def main():
     args = parser.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.case != "train":
+        return run_kernel_case(args)
     return run_cuda(args)
 
 

@@ -66,8 +66,9 @@ class Model:
     """
 
     def __init__(self, dims: Sequence[int], context: native.Context | None = None, seed: int = 0,
-                 comm: native.Comm | None = None, world_size: int = 1):
+                 comm: native.Comm | None = None, world_size: int = 1, bias: bool = True):
         self.dims = list(dims)
+        self.bias = bias
         self.layers = len(self.dims) - 1
         self.context = context or native.Context(0)
         self.comm = comm
@@ -78,7 +79,7 @@ class Model:
         for l in range(self.layers):
             w = glorot_uniform(rng, self.dims[l + 1], self.dims[l])
             b = np.zeros(self.dims[l + 1], dtype=np.float32)
-            for array in (w, b):
+            for array in ((w, b) if bias else (w,)):
                 self.param_buffers.append(self.context.upload(array))
                 self.param_shapes.append(array.shape)
         self._inference = {}
@@ -102,7 +103,7 @@ class Model:
     def _inference_state(self, batch: int, arg_max: bool):
         key = (batch, arg_max)
         if key not in self._inference:
-            graph = program.mlp_inference_graph(self.dims, batch, arg_max)
+            graph = program.mlp_inference_graph(self.dims, batch, arg_max, bias=self.bias)
             exe = native.Executable(self.context, graph.image)
             x = self.context.buffer(batch * self.dims[0] * 4)
             out = self.context.buffer(batch * self.dims[-1] * 4)
@@ -139,7 +140,7 @@ class Model:
         if self._loss is None:
             raise RuntimeError("configure_training first")
         if batch not in self._training:
-            graph = program.mlp_training_graph(self.dims, batch, self._loss)
+            graph = program.mlp_training_graph(self.dims, batch, self._loss, bias=self.bias)
             exe = native.Executable(self.context, graph.image)
             x = self.context.buffer(batch * self.dims[0] * 4)
             t = self.context.buffer(batch * 4 if self._loss == "ce" else batch * self.dims[-1] * 4)

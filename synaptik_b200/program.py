@@ -267,7 +267,7 @@ class MlpGraph:
     shapes: dict
 
 
-def mlp_inference_graph(dims: Sequence[int], batch: int, arg_max: bool = False) -> MlpGraph:
+def mlp_inference_graph(dims: Sequence[int], batch: int, arg_max: bool = False, bias: bool = True) -> MlpGraph:
     """Model.compute of a Linear/ReLU stack: feeds x then (w, b) per layer; publishes the last
     layer's output (and its row arg-max when asked)."""
     g = GraphBuilder()
@@ -277,9 +277,13 @@ def mlp_inference_graph(dims: Sequence[int], batch: int, arg_max: bool = False) 
     params = []
     for l in range(len(dims) - 1):
         w = g.feed(F32, (dims[l + 1], dims[l]))
-        b = g.feed(F32, (dims[l + 1],))
-        names += [f"w{l}", f"b{l}"]
-        shapes[f"w{l}"], shapes[f"b{l}"] = w.shape, b.shape
+        names.append(f"w{l}")
+        shapes[f"w{l}"] = w.shape
+        b = None
+        if bias:
+            b = g.feed(F32, (dims[l + 1],))
+            names.append(f"b{l}")
+            shapes[f"b{l}"] = b.shape
         params.append((w, b))
     for l, (w, b) in enumerate(params):
         _, z = g.linear(a, w, b)
@@ -294,7 +298,7 @@ def mlp_inference_graph(dims: Sequence[int], batch: int, arg_max: bool = False) 
     return MlpGraph(g.build(), names, pubs, shapes)
 
 
-def mlp_training_graph(dims: Sequence[int], batch: int, loss: str = "ce", label_dtype: int = I32) -> MlpGraph:
+def mlp_training_graph(dims: Sequence[int], batch: int, loss: str = "ce", label_dtype: int = I32, bias: bool = True) -> MlpGraph:
     """The TRAINING_STEP graph TrainingSession compiles: forward, objective, and one gradient per
     parameter in trainingParameters() order (weight, bias per layer), published after the loss
     (TrainingSession.java:953-987).  Feeds: x, target, seed, then (w, b) per layer."""
@@ -308,9 +312,13 @@ def mlp_training_graph(dims: Sequence[int], batch: int, loss: str = "ce", label_
     params = []
     for l in range(layers):
         w = g.feed(F32, (dims[l + 1], dims[l]))
-        b = g.feed(F32, (dims[l + 1],))
-        names += [f"w{l}", f"b{l}"]
-        shapes[f"w{l}"], shapes[f"b{l}"] = w.shape, b.shape
+        names.append(f"w{l}")
+        shapes[f"w{l}"] = w.shape
+        b = None
+        if bias:
+            b = g.feed(F32, (dims[l + 1],))
+            names.append(f"b{l}")
+            shapes[f"b{l}"] = b.shape
         params.append((w, b))
     acts, zs, wts = [x], [], []
     a = x
@@ -329,7 +337,7 @@ def mlp_training_graph(dims: Sequence[int], batch: int, loss: str = "ce", label_
     g.publish(objective)
     grads = [None] * (2 * layers)
     for l in range(layers - 1, -1, -1):
-        dx, dw, db = g.linear_backward(acts[l], wts[l], dz, need_dx=l > 0)
+        dx, dw, db = g.linear_backward(acts[l], wts[l], dz, need_dx=l > 0, bias=bias)
         grads[2 * l], grads[2 * l + 1] = dw, db
         if l > 0:
             dz = g.relu_backward(zs[l - 1], dx)
@@ -337,7 +345,10 @@ def mlp_training_graph(dims: Sequence[int], batch: int, loss: str = "ce", label_
     shapes["loss"] = ()
     for l in range(layers):
         g.publish(grads[2 * l])
-        g.publish(grads[2 * l + 1])
-        pubs += [f"dw{l}", f"db{l}"]
-        shapes[f"dw{l}"], shapes[f"db{l}"] = grads[2 * l].shape, grads[2 * l + 1].shape
+        pubs.append(f"dw{l}")
+        shapes[f"dw{l}"] = grads[2 * l].shape
+        if bias:
+            g.publish(grads[2 * l + 1])
+            pubs.append(f"db{l}")
+            shapes[f"db{l}"] = grads[2 * l + 1].shape
     return MlpGraph(g.build(), names, pubs, shapes)
