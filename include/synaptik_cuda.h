@@ -183,6 +183,27 @@ SYNAPTIK_CUDA_API int32_t synaptik_cuda_comm_allreduce_sum_f32(void *comm, void 
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_executable_attach_comm(void *executable, void *comm, int32_t output_count,
                                              const int32_t *output_indices);
 
+/* ---- column sums for callers that must not allocate (no counterpart in the reference) ---------
+ * Some callers hold a device context in which allocation is off limits: code running inside a
+ * memory-pool or capture-sensitive region of a host framework, a plugin that was handed fixed
+ * buffers by its owner, a real-time loop that may not touch the allocator.  For them this one
+ * entry point computes out[n] = sum over rows of in[row, n] (the bias gradient, FP32 in and out,
+ * binary64 accumulation, fixed summation order) exactly like the SUM_TO_SHAPE step of an
+ * executable, but keeps its intermediate partial sums in a 2 MiB array that is part of the library
+ * image on every GPU that loads it, and calls no allocating routine of CUDA or of any library.
+ *   - `input` holds rows x cols dense row-major floats at byte offset 0, `output` at least cols
+ *     floats; both are buffers of `context`.
+ *   - Shapes whose partial sums do not fit the array (more than 262144 of them) are refused with
+ *     UNSUPPORTED_SHAPE: every shape of at most 131072 columns fits, none above 262144 columns
+ *     does, in between it depends on the row count.
+ *   - The first call on a device looks up the array's device address; make that first call
+ *     outside any stream capture.
+ *   - All calls on a device share the one array.  A call overwrites every partial it later reads,
+ *     so nothing is left over from the previous call, but two calls whose kernels overlap on the
+ *     GPU (different contexts or streams) would race on it: serialise them.
+ * The work is enqueued on the context's stream and the call returns after it has finished. */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_column_sums_no_alloc(void *context, void *input, uint64_t rows, uint64_t cols, void *output);
+
 #ifdef __cplusplus
 }
 #endif

@@ -37,6 +37,12 @@ cudaError_t relu_backward(cudaStream_t s, const float *gate, const float *upstre
 // partials must hold colsum_partial_count(rows, cols) doubles.
 int64_t colsum_partial_count(int64_t rows, int64_t cols);
 cudaError_t colsum(cudaStream_t s, const float *g, int64_t rows, int64_t cols, double *partials, float *out);
+// The same two column-sum kernels, with the partial sums kept in a fixed file-scope device array
+// (kStaticColsumPartials doubles, 2 MiB, resident on every GPU that loads the library) so that the
+// call performs no allocation at all.  `device` must be the current device.  Returns
+// cudaErrorInvalidValue when colsum_partial_count(rows, cols) exceeds the array.
+constexpr int64_t kStaticColsumPartials = 262144;
+cudaError_t colsum_static(cudaStream_t s, int device, const float *g, int64_t rows, int64_t cols, float *out);
 // Index cross entropy with logits: per-row loss into row_loss (rows floats of scratch), optional
 // gradient (softmax - onehot) * (seed / rows), optional row arg-max, then the mean of row_loss
 // into loss_out (optional).  Labels outside [0, cols) set ERR_LABEL_RANGE in *error_word.

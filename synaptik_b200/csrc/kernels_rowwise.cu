@@ -6,6 +6,7 @@
 
 #include <cfloat>
 #include <cmath>
+#include <mutex>
 
 namespace syn {
 namespace kern {
@@ -657,6 +658,34 @@ cudaError_t colsum(cudaStream_t s, const float *g, int64_t rows, int64_t cols, d
     if (e != cudaSuccess) return e;
     colsum_final_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, s>>>(partials, splits, cols, out);
     return cudaGetLastError();
+}
+
+// ---- column sums without any allocation ----------------------------------------------------------
+// Scratch for callers that cannot allocate device memory.  In host code the array's name is only a
+// stand-in for the symbol, never a device address, so the address is looked up once per device
+// (with that device current) and the kernels receive the looked-up pointer.
+static __device__ __align__(256) double g_colsum_static_partials[kStaticColsumPartials];
+static double *g_colsum_static_address[64];
+static std::mutex g_colsum_static_mutex;
+
+cudaError_t colsum_static(cudaStream_t s, int device, const float *g, int64_t rows, int64_t cols, float *out) {
+    if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+    if (cols == 0) return cudaSuccess;
+    if (colsum_partial_count(rows, cols) > kStaticColsumPartials) return cudaErrorInvalidValue;
+    double *partials;
+    {
+        std::lock_guard<std::mutex> lock(g_colsum_static_mutex);
+        if (!g_colsum_static_address[device]) {
+            void *address = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&address, g_colsum_static_partials);
+            if (e != cudaSuccess) return e;
+            g_colsum_static_address[device] = static_cast<double *>(address);
+        }
+        partials = g_colsum_static_address[device];
+    }
+    // phase 1 writes every partial that phase 2 reads, so nothing of an earlier call survives and
+    // nothing has to be cleared first
+    return colsum(s, g, rows, cols, partials, out);
 }
 
 cudaError_t cross_entropy(cudaStream_t s, const float *logits, DType label_type, const void *labels, const float *seed,

@@ -985,4 +985,22 @@ int32_t synaptik_cuda_executable_attach_comm(void *executable, void *comm, int32
     return OK;
 }
 
+// Column sums whose scratch lives in a static device array: no allocation of any kind on this path
+// (no device or pinned memory, no containers).
+int32_t synaptik_cuda_column_sums_no_alloc(void *context, void *input, uint64_t rows, uint64_t cols, void *output) {
+    Context *ctx = as<Context>(context, TAG_CONTEXT);
+    Buffer *in = as<Buffer>(input, TAG_BUFFER), *out = as<Buffer>(output, TAG_BUFFER);
+    if (!ctx || !in || !out) return INVALID_ARGUMENT;
+    if (in->ctx != ctx || out->ctx != ctx || in == out) return INCOMPATIBLE_RESOURCE;
+    if (rows > (1ull << 40) || cols > (1ull << 30)) return UNSUPPORTED_SHAPE;
+    if (rows * cols * 4 > in->bytes || cols * 4 > out->bytes) return RANGE_OUT_OF_BOUNDS;
+    if (kern::colsum_partial_count((int64_t)rows, (int64_t)cols) > kern::kStaticColsumPartials) return UNSUPPORTED_SHAPE;
+    std::lock_guard<std::mutex> lock(ctx->mutex);
+    DeviceGuard guard(ctx->device);
+    cudaError_t e = kern::colsum_static(ctx->stream, ctx->device, (const float *)in->ptr, (int64_t)rows, (int64_t)cols, (float *)out->ptr);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) { cudaGetLastError(); return EXECUTION_FAILED; }
+    return OK;
+}
+
 }  // extern "C"

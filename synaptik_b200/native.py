@@ -43,6 +43,7 @@ SYMBOLS = [
     "synaptik_cuda_optimizer_download_state", "synaptik_cuda_optimizer_upload_state",
     "synaptik_cuda_comm_unique_id", "synaptik_cuda_comm_create", "synaptik_cuda_comm_release",
     "synaptik_cuda_comm_allreduce_sum_f32", "synaptik_cuda_executable_attach_comm",
+    "synaptik_cuda_column_sums_no_alloc",
 ]
 
 
@@ -304,6 +305,13 @@ class Optimizer:
         if self._h:
             _check("optimizer_release", library().synaptik_cuda_optimizer_release(self._h))
             self._h = ctypes.c_void_p()
+
+
+def column_sums_no_alloc(context: Context, source: Buffer, rows: int, cols: int, destination: Buffer) -> None:
+    """Column sums of a dense [rows, cols] FP32 buffer into `destination`, for callers that must not
+    allocate: the scratch is a fixed array inside the library (see include/synaptik_cuda.h)."""
+    _check("column_sums_no_alloc", library().synaptik_cuda_column_sums_no_alloc(
+        context._h, source._h, ctypes.c_uint64(rows), ctypes.c_uint64(cols), destination._h))
 
 
 def comm_unique_id() -> bytes:
