@@ -167,6 +167,8 @@ def run_cuda(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     ctx = native.Context(local_rank)
+    if os.environ.get("SYNAPTIK_BENCH_FUSED_PLANES") == "0":
+        ctx.set_option("fused_planes", 0)
     comm = None
     if distributed:
         holder = [native.comm_unique_id() if rank == 0 else None]
@@ -284,7 +286,8 @@ def run_cuda(args):
                          "frac": achieved / emulated_peak if emulated_peak else None, "traffic": None,
                          "peak_source": f"{peak_kind} bf16_tflops_sustained / 2 (TF32) / 3 (3xTF32)",
                          "launches_per_step": gemm_launches, "ms_per_step_in_kernel": ms,
-                         "step_time_shares": {k: v / total_step for k, v in sorted(shares.items())}},
+                         "step_time_shares": {k: v / total_step for k, v in sorted(shares.items())},
+                         "steps_ms": [[line.split(" nodes=")[0], round(t, 4)] for line, t in zip(plan, step_ms)]},
             "model_tflops": step_flops(GLOBAL_BATCH) * args.steps / (resident_ms * 1e-3) / 1e12,
         }
         if world == 1 and not args.no_cpu_baseline:
@@ -335,7 +338,7 @@ def run_kernel_case(args):
         g.publish(g.arg_max(logits, 1))
         feeds = [(rng.standard_normal((rows, classes)) * 2).astype(np.float32), rng.integers(0, classes, rows).astype(np.int32),
                  np.array(1.0, dtype=np.float32)]
-        work = 8.0 * rows * classes + 8.0 * rows + 4.0 * rows * classes + 8.0 * rows      # loss+gradient pass, arg-max pass
+        work = 8.0 * rows * classes + 12.0 * rows + 4.0          # one pass: read logits, write gradient, labels, arg-max, loss
         unit, denom, bound_kind = "GB/s", peak_data["hbm_gbs"], "hbm"
         name = f"classifier_head_rows{rows}_classes{classes}"
     exe = native.Executable(ctx, g.build())

@@ -64,7 +64,9 @@ SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_release(void *context);
 /* Named integer options.  "gemm_engine": 0 = automatic (tensor cores for large products, exact
  * sequential CUDA-core kernel for small ones), 1 = always the exact CUDA-core kernel,
  * 2 = tensor cores whenever the shape allows.  "time_steps": 1 = bracket every step of later runs
- * with CUDA events (see synaptik_cuda_executable_step_timings).  Unknown names return
+ * with CUDA events (see synaptik_cuda_executable_step_timings).  "fused_planes": 0 = executables
+ * created afterwards split GEMM operands in separate passes instead of in the producing GEMM's
+ * epilogue (default 1).  Unknown names return
  * INVALID_ARGUMENT. */
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_set_option(void *context, const char *name, int64_t value);
 /* Blocks until all work issued on the context has finished. */

@@ -9,7 +9,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libsynaptik_cuda.so")
-SOURCES = ["program.cpp", "lowering.cpp", "kernels_rowwise.cu", "kernels_gemm.cu", "runtime.cu"]
+SOURCES = ["program.cpp", "lowering.cpp", "kernels_rowwise.cu", "kernels_gemm.cu", "kernels_skinny.cu", "runtime.cu"]
 HEADERS = ["program.hpp", "lowering.hpp", "kernels.hpp", os.path.join("..", "..", "include", "synaptik_cuda.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall", "--expt-relaxed-constexpr"]

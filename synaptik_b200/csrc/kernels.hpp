@@ -63,12 +63,32 @@ struct GemmEpilogue {
     int relu = 0;                       // out = max(z, +0)
     const float *gate = nullptr;        // dense [m,n]: out = gate > 0 ? z : 0
     float *second = nullptr;            // dense [m,n]: when set, `out` receives z and `second` relu(z)
+    // tensor-core kernel only: also write the hi/lo operand planes of the result (the activation when
+    // relu / second is set) for later GEMMs, [m, plane_ld] and / or transposed [n, tplane_ld]
+    float *plane_hi = nullptr, *plane_lo = nullptr; int64_t plane_ld = 0;
+    float *tplane_hi = nullptr, *tplane_lo = nullptr; int64_t tplane_ld = 0;
 };
 // Exact CUDA-core product: every output cell is the reference's ascending-k chain of separately
 // rounded multiply and add (CpuMatmulReferenceKernel.java:71-93), operands and result strided.
 cudaError_t gemm_exact(cudaStream_t s, int64_t m, int64_t n, int64_t k,
                        const float *a, int64_t a_ms, int64_t a_ks, const float *b, int64_t b_ks, int64_t b_ns,
                        float *c, int64_t c_ms, int64_t c_ns, const GemmEpilogue &ep);
+
+// Streaming kernels for products with one extent of at most 16 (kernels_skinny.cu).  The
+// *_supported predicates are pure host functions used by the lowering.
+//   narrow_out    C[m, n<=16] = A[m,k] (row-major, lda) . W[n,k]^T (rows ldw) (+ bias, ReLU)
+//   narrow_inner  C[m, n] (row-major, ldc) = A[m, k<=16] . B[k, n] (row-major, ldb), optional gate; exact chain
+//   narrow_reduce D[i, j<=16] = sum_r S[r, i] * T[r, j]  (S rows lds, i contiguous), two-phase, fixed order
+bool narrow_out_supported(int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldw);
+cudaError_t gemm_narrow_out(cudaStream_t s, int sm_count, int64_t m, int64_t n, int64_t k, const float *a, int64_t lda,
+                            const float *w, int64_t ldw, const float *bias, int relu, float *c, int64_t c_ms, int64_t c_ns);
+bool narrow_inner_supported(int64_t m, int64_t n, int64_t k, int64_t ldb, int64_t ldc);
+cudaError_t gemm_narrow_inner(cudaStream_t s, int64_t m, int64_t n, int64_t k, const float *a, int64_t lda,
+                              const float *b, int64_t ldb, const float *gate, float *c, int64_t ldc);
+bool narrow_reduce_supported(int64_t wide, int64_t n, int64_t depth, int64_t lds);
+int64_t narrow_reduce_partial_floats(int64_t wide, int64_t n, int64_t depth);
+cudaError_t gemm_narrow_reduce(cudaStream_t s, int64_t wide, int64_t n, int64_t depth, const float *src, int64_t lds,
+                               const float *t, int64_t ldt, float *partial, float *out, int64_t stride_wide, int64_t stride_narrow);
 
 // Tensor-core path.  split_planes writes hi = tf32(x) and lo = tf32(x - hi) of a logical [rows, cols]
 // matrix (element strides rs, cs; one of them 1) into two dense [rows, cols_padded] planes whose
@@ -78,7 +98,7 @@ cudaError_t split_planes(cudaStream_t s, const float *src, int64_t rows, int64_t
                          float *hi, float *lo, int64_t cols_padded);
 struct TensorCoreGemm;       // opaque: tensor maps and launch geometry prepared once per plan step
 TensorCoreGemm *tc_gemm_prepare(const float *p_hi, const float *p_lo, const float *q_hi, const float *q_lo,
-                                int64_t m, int64_t n, int64_t k_padded, int sm_count, int *status);
+                                int64_t m, int64_t n, int64_t k_padded, int sm_count, int promote, int *status);
 void tc_gemm_release(TensorCoreGemm *g);
 cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, int64_t ldd, const GemmEpilogue &ep, int *error_word);
 

@@ -14,6 +14,7 @@
 #include <cuda.h>
 
 #include <cstdio>
+#include <cstdlib>
 
 namespace syn {
 namespace kern {
@@ -254,8 +255,71 @@ struct TcParams {
     int m, n, k_blocks;
     int tiles_m, tiles_n;
     const float *bias; const float *gate; float *second; int relu;
+    float *nhi, *nlo; int64_t nld;          // optional [m, nld] hi/lo planes of the result
+    float *thi, *tlo; int64_t tld; int m_pad;   // optional transposed [n, tld] planes, tld = m_pad = m rounded up to 32
     int *error_word;
 };
+
+
+// Finishes four adjacent result cells of one row: bias, ReLU-backward gate, activation, the stores
+// of the result (and of the second output), and the hi/lo operand planes when later GEMMs read this
+// result.  row_ok is false for the rows past m that only exist as zero padding of the transposed
+// planes.
+__device__ __forceinline__ void epilogue_emit4(const TcParams &prm, int row, bool row_ok, int col,
+                                               float z0, float z1, float z2, float z3, bool vec_ok) {
+    float *drow = prm.d + (int64_t)row * prm.ldd;
+    const int64_t dense = (int64_t)row * prm.n;
+    float z[4] = {z0, z1, z2, z3};
+    float y[4];                             // the value later GEMMs read: activation or (gated) result
+    if (!row_ok) {
+        y[0] = y[1] = y[2] = y[3] = 0.0f;
+    } else if (col + 3 < prm.n && vec_ok && (prm.n & 3) == 0) {
+        if (prm.bias) { float4 bv = *reinterpret_cast<const float4 *>(prm.bias + col);
+            z[0] = __fadd_rn(z[0], bv.x); z[1] = __fadd_rn(z[1], bv.y); z[2] = __fadd_rn(z[2], bv.z); z[3] = __fadd_rn(z[3], bv.w); }
+        if (prm.gate) { float4 gv = *reinterpret_cast<const float4 *>(prm.gate + dense + col);
+            z[0] = gv.x > 0.0f ? z[0] : 0.0f; z[1] = gv.y > 0.0f ? z[1] : 0.0f; z[2] = gv.z > 0.0f ? z[2] : 0.0f; z[3] = gv.w > 0.0f ? z[3] : 0.0f; }
+#pragma unroll
+        for (int e = 0; e < 4; e++) y[e] = (prm.second || prm.relu) ? relu_value(z[e]) : z[e];
+        if (prm.second) {
+            *reinterpret_cast<float4 *>(drow + col) = make_float4(z[0], z[1], z[2], z[3]);
+            *reinterpret_cast<float4 *>(prm.second + dense + col) = make_float4(y[0], y[1], y[2], y[3]);
+        } else {
+            *reinterpret_cast<float4 *>(drow + col) = make_float4(y[0], y[1], y[2], y[3]);
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int cc = col + e;
+            y[e] = 0.0f;
+            if (cc < prm.n) {
+                float zz = z[e];
+                if (prm.bias) zz = __fadd_rn(zz, prm.bias[cc]);
+                if (prm.gate) zz = prm.gate[dense + cc] > 0.0f ? zz : 0.0f;
+                y[e] = (prm.second || prm.relu) ? relu_value(zz) : zz;
+                if (prm.second) { drow[cc] = zz; prm.second[dense + cc] = y[e]; }
+                else drow[cc] = y[e];
+            }
+        }
+    }
+    if (prm.nhi || prm.thi) {
+        // operand planes for the GEMMs that read this result, written here instead of by a separate
+        // split pass; columns past n and rows past m are zero padding
+        float h[4], l[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) split_value(y[e], h[e], l[e]);
+        if (prm.nhi && row_ok) {
+            *reinterpret_cast<float4 *>(prm.nhi + (int64_t)row * prm.nld + col) = make_float4(h[0], h[1], h[2], h[3]);
+            *reinterpret_cast<float4 *>(prm.nlo + (int64_t)row * prm.nld + col) = make_float4(l[0], l[1], l[2], l[3]);
+        }
+        if (prm.thi) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) if (col + e < prm.n) {
+                prm.thi[(int64_t)(col + e) * prm.tld + row] = h[e];       // lanes hold consecutive rows: coalesced
+                prm.tlo[(int64_t)(col + e) * prm.tld + row] = l[e];
+            }
+        }
+    }
+}
 
 template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tf32x3_kernel(
@@ -376,40 +440,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tf32x3_kernel(
                 float v[32];
                 tmem_load32(taddr + (uint32_t)(chunk * 32), v);
                 const int col0 = n0 + chunk * 32;
-                if (row < prm.m && col0 < prm.n) {
-                    float *drow = prm.d + (int64_t)row * prm.ldd;
-                    const int64_t dense = (int64_t)row * prm.n;
+                const bool row_ok = row < prm.m;
+                const bool row_pad = !row_ok && prm.thi != nullptr && row < prm.m_pad;     // zero padding of the transposed planes
+                if ((row_ok || row_pad) && col0 < prm.n) {
 #pragma unroll
-                    for (int q = 0; q < 8; q++) {
-                        const int col = col0 + q * 4;
-                        float z[4] = {v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]};
-                        if (col + 3 < prm.n && vec_ok && (prm.n & 3) == 0) {
-                            if (prm.bias) { float4 bv = *reinterpret_cast<const float4 *>(prm.bias + col);
-                                z[0] = __fadd_rn(z[0], bv.x); z[1] = __fadd_rn(z[1], bv.y); z[2] = __fadd_rn(z[2], bv.z); z[3] = __fadd_rn(z[3], bv.w); }
-                            if (prm.gate) { float4 gv = *reinterpret_cast<const float4 *>(prm.gate + dense + col);
-                                z[0] = gv.x > 0.0f ? z[0] : 0.0f; z[1] = gv.y > 0.0f ? z[1] : 0.0f; z[2] = gv.z > 0.0f ? z[2] : 0.0f; z[3] = gv.w > 0.0f ? z[3] : 0.0f; }
-                            if (prm.second) {
-                                *reinterpret_cast<float4 *>(drow + col) = make_float4(z[0], z[1], z[2], z[3]);
-                                *reinterpret_cast<float4 *>(prm.second + dense + col) = make_float4(relu_value(z[0]), relu_value(z[1]), relu_value(z[2]), relu_value(z[3]));
-                            } else if (prm.relu) {
-                                *reinterpret_cast<float4 *>(drow + col) = make_float4(relu_value(z[0]), relu_value(z[1]), relu_value(z[2]), relu_value(z[3]));
-                            } else {
-                                *reinterpret_cast<float4 *>(drow + col) = make_float4(z[0], z[1], z[2], z[3]);
-                            }
-                        } else {
-#pragma unroll
-                            for (int e = 0; e < 4; e++) {
-                                const int cc = col + e;
-                                if (cc < prm.n) {
-                                    float zz = z[e];
-                                    if (prm.bias) zz = __fadd_rn(zz, prm.bias[cc]);
-                                    if (prm.gate) zz = prm.gate[dense + cc] > 0.0f ? zz : 0.0f;
-                                    if (prm.second) { drow[cc] = zz; prm.second[dense + cc] = relu_value(zz); }
-                                    else drow[cc] = prm.relu ? relu_value(zz) : zz;
-                                }
-                            }
-                        }
-                    }
+                    for (int q = 0; q < 8; q++)
+                        epilogue_emit4(prm, row, row_ok, col0 + q * 4, v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3], vec_ok);
                 }
             }
             tc_fence_before();
@@ -418,6 +454,195 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tf32x3_kernel(
     }
 
     // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicOr(prm.error_word, ERR_WAIT_TIMEOUT);
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::kTmemCols) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// The same pipeline with FP32 promotion.  Measured on B200: every tcgen05.mma adds its products into
+// the FP32 accumulator with truncation (toward zero), so a sum kept in tensor memory over the whole
+// contraction drifts by about 0.2 * K units of 2^-24 of the running sum.  Here tensor memory only
+// ever holds the partial sum of CHUNK_KB k-blocks (128 contraction steps); eight epilogue warps
+// add each finished partial into round-to-nearest FP32 register sums (128 per thread at BN = 256)
+// while the tensor core already works on the next partial in the other tensor-memory buffer.
+// The truncation is then relative to a short partial sum and the drift no longer grows with K.
+// ------------------------------------------------------------------------------------------------
+constexpr int PROMOTED_THREADS = 384;   // warp 0 producer, warp 1 MMA issuer, warps 4-11 epilogue
+constexpr int CHUNK_KB = 4;
+
+__device__ __forceinline__ void tmem_load16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+}
+
+template <int BN>
+__global__ void __launch_bounds__(PROMOTED_THREADS, 1) gemm_tf32x3_promoted_kernel(
+        const __grid_constant__ CUtensorMap map_p_hi, const __grid_constant__ CUtensorMap map_p_lo,
+        const __grid_constant__ CUtensorMap map_q_hi, const __grid_constant__ CUtensorMap map_q_lo, TcParams prm) {
+    using Cfg = TileConfig<BN>;
+    constexpr int S = Cfg::kStages;
+    constexpr int CPT = BN / 2;             // result columns per epilogue thread
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S * Cfg::kStageBytes);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * S + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar_base = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
+    auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * S + a); };
+    auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * S + 2 + a); };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), 256); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)Cfg::kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int total_tiles = prm.tiles_m * prm.tiles_n;
+    const int kb_count = prm.k_blocks;
+    const uint32_t smem_base = smem_u32(smem);
+
+    // the two epilogue warpgroups hold the register sums: hand them the registers the producer /
+    // issuer warpgroup does not need
+    if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            uint32_t armed_phase[S]; bool armed[S];
+            for (int s = 0; s < S; s++) { armed[s] = false; armed_phase[s] = 0; }
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile / prm.tiles_n) * BM, n0 = (tile % prm.tiles_n) * BN;
+                for (int kb = 0; kb < kb_count; kb++) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t sa = smem_base + stage * Cfg::kStageBytes;
+                    mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
+                    armed[stage] = true; armed_phase[stage] = phase;
+                    tma_load_2d(sa, &map_p_hi, full_bar(stage), kb * BK, m0);
+                    tma_load_2d(sa + Cfg::kABytes, &map_p_lo, full_bar(stage), kb * BK, m0);
+                    tma_load_2d(sa + 2 * Cfg::kABytes, &map_q_hi, full_bar(stage), kb * BK, n0);
+                    tma_load_2d(sa + 2 * Cfg::kABytes + Cfg::kBBytes, &map_q_lo, full_bar(stage), kb * BK, n0);
+                    if (++stage == S) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok || *abort_flag) {
+                for (int s = 0; s < S; s++) if (armed[s]) mbar_wait(full_bar(s), armed_phase[s], abort_flag);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc<BN>();
+            int stage = 0; uint32_t phase = 0;
+            uint32_t partial = 0;               // running count of partial sums: selects the tensor-memory buffer
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                for (int kb0 = 0; kb0 < kb_count && ok; kb0 += CHUNK_KB, partial++) {
+                    const int buf = partial & 1;
+                    if (!mbar_wait(acc_empty_bar(buf), ((partial >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                    const int kb1 = kb0 + CHUNK_KB < kb_count ? kb0 + CHUNK_KB : kb_count;
+                    for (int kb = kb0; kb < kb1; kb++) {
+                        if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint32_t sa = smem_base + stage * Cfg::kStageBytes;
+                        const uint32_t p_hi = sa, p_lo = sa + Cfg::kABytes, q_hi = sa + 2 * Cfg::kABytes, q_lo = q_hi + Cfg::kBBytes;
+#pragma unroll
+                        for (int k4 = 0; k4 < BK / UMMA_K; k4++) {
+                            const uint32_t off = k4 * UMMA_K * 4;
+                            umma_tf32(tmem_d, umma_desc(p_lo + off), umma_desc(q_hi + off), idesc, (kb != kb0 || k4 != 0) ? 1u : 0u);
+                            umma_tf32(tmem_d, umma_desc(p_hi + off), umma_desc(q_lo + off), idesc, 1u);
+                            umma_tf32(tmem_d, umma_desc(p_hi + off), umma_desc(q_hi + off), idesc, 1u);
+                        }
+                        umma_commit(empty_bar(stage));
+                        if (++stage == S) { stage = 0; phase ^= 1u; }
+                    }
+                    if (ok) umma_commit(acc_full_bar(buf));
+                }
+            }
+        }
+    }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+        const int quarter = warp & 3;           // tensor-memory lanes 32*quarter .. +31
+        const int half = (warp - 4) >> 2;       // which half of the tile's columns
+        uint32_t partial = 0;
+        bool ok = true;
+        const bool vec_ok = (prm.ldd & 3) == 0 && ((uintptr_t)prm.d & 15) == 0
+                            && (!prm.second || ((uintptr_t)prm.second & 15) == 0) && (!prm.gate || ((uintptr_t)prm.gate & 15) == 0);
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int m0 = (tile / prm.tiles_n) * BM, n0 = (tile % prm.tiles_n) * BN;
+            float sum[CPT];
+            for (int kb0 = 0; kb0 < kb_count; kb0 += CHUNK_KB, partial++) {
+                const int buf = partial & 1;
+                ok = mbar_wait(acc_full_bar(buf), (partial >> 1) & 1u, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * CPT);
+                if (kb0 == 0) {
+#pragma unroll
+                    for (int s16 = 0; s16 < CPT / 16; s16++) {
+                        float t[16];
+                        tmem_load16(taddr + (uint32_t)(s16 * 16), t);
+#pragma unroll
+                        for (int i = 0; i < 16; i++) sum[s16 * 16 + i] = t[i];
+                    }
+                } else {
+#pragma unroll
+                    for (int s16 = 0; s16 < CPT / 16; s16++) {
+                        float t[16];
+                        tmem_load16(taddr + (uint32_t)(s16 * 16), t);
+#pragma unroll
+                        for (int i = 0; i < 16; i++) sum[s16 * 16 + i] = __fadd_rn(sum[s16 * 16 + i], t[i]);
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(acc_empty_bar(buf));
+            }
+            if (!ok) break;
+            const int row = m0 + quarter * 32 + lane;
+            const bool row_ok = row < prm.m;
+            const bool row_pad = !row_ok && prm.thi != nullptr && row < prm.m_pad;
+            if (row_ok || row_pad) {
+#pragma unroll
+                for (int g = 0; g < CPT / 4; g++) {
+                    const int col = n0 + half * CPT + g * 4;
+                    if ((col & ~31) < prm.n)
+                        epilogue_emit4(prm, row, row_ok, col, sum[g * 4], sum[g * 4 + 1], sum[g * 4 + 2], sum[g * 4 + 3], vec_ok);
+                }
+            }
+        }
+    }
+
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag) atomicOr(prm.error_word, ERR_WAIT_TIMEOUT);
@@ -485,18 +710,37 @@ cudaError_t split_planes(cudaStream_t s, const float *src, int64_t rows, int64_t
     return cudaGetLastError();
 }
 
+// Test hook: SYNAPTIK_CUDA_TILE_N=64|128|256 pins the tile width (read once).
+static int forced_tile_n() {
+    static int value = -1;
+    if (value < 0) { const char *e = getenv("SYNAPTIK_CUDA_TILE_N"); value = e ? atoi(e) : 0; }
+    return value;
+}
+
 struct TensorCoreGemm {
     CUtensorMap p_hi, p_lo, q_hi, q_lo;
     int m, n, k_blocks, bn, grid;
+    int promote;
 };
 
 TensorCoreGemm *tc_gemm_prepare(const float *p_hi, const float *p_lo, const float *q_hi, const float *q_lo,
-                                int64_t m, int64_t n, int64_t k_padded, int sm_count, int *status) {
+                                int64_t m, int64_t n, int64_t k_padded, int sm_count, int promote, int *status) {
     *status = OK;
     if (m < 1 || n < 1 || k_padded < BK || k_padded % BK || m > (1ll << 30) || n > (1ll << 30)) { *status = UNSUPPORTED_SHAPE; return nullptr; }
     TensorCoreGemm *g = new TensorCoreGemm();
     g->m = (int)m; g->n = (int)n; g->k_blocks = (int)(k_padded / BK);
-    g->bn = n >= 192 ? 256 : (n >= 96 ? 128 : 64);
+    g->promote = promote;
+    // tile width: the widest tile has the best operand reuse, but a persistent grid pays for the last
+    // partial wave; take the width with the least (waves x width), narrower tiles handicapped a little
+    auto cost = [&](int bn) {
+        int64_t t = ((m + BM - 1) / BM) * ((n + bn - 1) / bn);
+        int64_t waves = (t + sm_count - 1) / sm_count;
+        return (double)waves * bn * (bn == 256 ? 1.0 : (bn == 128 ? 1.05 : 1.15));
+    };
+    g->bn = 64;
+    if (n >= 96 && cost(128) <= cost(g->bn)) g->bn = 128;
+    if (n >= 192 && cost(256) <= cost(g->bn)) g->bn = 256;
+    if (forced_tile_n() == 64 || forced_tile_n() == 128 || forced_tile_n() == 256) g->bn = forced_tile_n();
     int64_t tiles = ((m + BM - 1) / BM) * ((n + g->bn - 1) / g->bn);
     g->grid = (int)(tiles < sm_count ? tiles : sm_count);
     bool ok = make_plane_map(&g->p_hi, p_hi, m, k_padded, BM) && make_plane_map(&g->p_lo, p_lo, m, k_padded, BM)
@@ -513,12 +757,26 @@ static cudaError_t launch_tc(cudaStream_t s, const TensorCoreGemm *g, const TcPa
     // a per-device attribute: set on every launch so each GPU of the process has it
     cudaError_t e = cudaFuncSetAttribute(gemm_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
-    gemm_tf32x3_kernel<BN><<<g->grid, GEMM_THREADS, Cfg::kSmemBytes, s>>>(g->p_hi, g->p_lo, g->q_hi, g->q_lo, prm);
+    if (g->promote) {
+        // the kernel redistributes registers between its warpgroups (72 and 216 per thread); that only
+        // terminates when the launch allocation covers the sum, so check it instead of trusting it
+        cudaFuncAttributes attr;
+        e = cudaFuncGetAttributes(&attr, gemm_tf32x3_promoted_kernel<BN>);
+        if (e != cudaSuccess) return e;
+        if (attr.numRegs * PROMOTED_THREADS < 128 * 72 + 256 * 216) return cudaErrorLaunchOutOfResources;
+        e = cudaFuncSetAttribute(gemm_tf32x3_promoted_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        if (e != cudaSuccess) return e;
+        gemm_tf32x3_promoted_kernel<BN><<<g->grid, PROMOTED_THREADS, Cfg::kSmemBytes, s>>>(g->p_hi, g->p_lo, g->q_hi, g->q_lo, prm);
+    } else {
+        gemm_tf32x3_kernel<BN><<<g->grid, GEMM_THREADS, Cfg::kSmemBytes, s>>>(g->p_hi, g->p_lo, g->q_hi, g->q_lo, prm);
+    }
     return cudaGetLastError();
 }
 
 cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, int64_t ldd, const GemmEpilogue &ep, int *error_word) {
     TcParams prm;
+    prm.nhi = ep.plane_hi; prm.nlo = ep.plane_lo; prm.nld = ep.plane_ld;
+    prm.thi = ep.tplane_hi; prm.tlo = ep.tplane_lo; prm.tld = ep.tplane_ld; prm.m_pad = (int)ep.tplane_ld;
     prm.d = d; prm.ldd = ldd; prm.m = g->m; prm.n = g->n; prm.k_blocks = g->k_blocks;
     prm.tiles_m = (g->m + BM - 1) / BM; prm.tiles_n = (g->n + g->bn - 1) / g->bn;
     prm.bias = ep.bias; prm.gate = ep.gate; prm.second = ep.second; prm.relu = ep.relu; prm.error_word = error_word;

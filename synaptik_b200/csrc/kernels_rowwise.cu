@@ -52,6 +52,31 @@ __device__ __forceinline__ float exp_accurate(float x) {
     return __fmul_rn(__fmul_rn(res, __int_as_float((n1 + 127) << 23)), __int_as_float((n2 + 127) << 23));
 }
 
+// exp(x) for finite x <= 0 (logits shifted by their row maximum), the hot form inside the row
+// kernels: same reduction and polynomial as exp_accurate, rounding to the nearest integer by the
+// 1.5 * 2^23 trick, scaling by a power of two assembled in the exponent field.  Within 1.03 ulp,
+// equal to the correctly rounded value for 99.2 % of inputs (host sweep).  Arguments below -87.33
+// are clamped there, so results that would be subnormal come out as 1.18e-38: an absolute error
+// below 1.2e-38 next to a row maximum whose exponential is 1.  NaN and infinities are not handled
+// here: rows that contain them take the careful path.
+__device__ __forceinline__ float exp_shifted(float x) {
+    const float magic = 12582912.0f;
+    x = fmaxf(x, -87.33f);
+    float t = fmaf(x, 1.4426950408889634f, magic);
+    float n = __fsub_rn(t, magic);
+    float r = fmaf(n, -0.693145751953125f, x);
+    r = fmaf(n, -1.42860682030941723212e-6f, r);
+    float q = 1.9841270114e-4f;
+    q = fmaf(q, r, 1.3888889225e-3f);
+    q = fmaf(q, r, 8.3333337680e-3f);
+    q = fmaf(q, r, 4.1666667908e-2f);
+    q = fmaf(q, r, 1.6666667163e-1f);
+    q = fmaf(q, r, 0.5f);
+    float res = __fadd_rn(fmaf(__fmul_rn(r, r), q, r), 1.0f);
+    int biased = __float_as_int(t) - (0x4b400000 - 127);        // n + 127 >= 1, n read from the low bits of t
+    return __fmul_rn(res, __int_as_float(biased << 23));
+}
+
 __device__ __forceinline__ float java_max(float a, float b) {   // Math.max: NaN wins, +0 above -0
     if (a != a) return a;
     if (b != b) return b;
@@ -197,14 +222,90 @@ __device__ __forceinline__ unsigned long long warp_best(unsigned long long v) {
     return v;
 }
 
-__global__ void argmax_kernel(const float *__restrict__ x, int64_t *out, int64_t rows, int64_t cols) {
+__device__ __forceinline__ uint32_t warp_umax(uint32_t v) {
+    for (int o = 16; o > 0; o >>= 1) { uint32_t u = __shfl_xor_sync(0xffffffffu, v, o); v = u > v ? u : v; }
+    return v;
+}
+__device__ __forceinline__ uint32_t warp_umin(uint32_t v) {
+    for (int o = 16; o > 0; o >>= 1) { uint32_t u = __shfl_xor_sync(0xffffffffu, v, o); v = u < v ? u : v; }
+    return v;
+}
+
+// Row arg-max of a row held in registers (lane l holds float4 chunks l, l+32, ...).  Common rows
+// (no NaN, maximum not a zero) take the cheap route: plain maximum, then the first column equal to
+// it.  Rows with a NaN or a zero maximum take the total-order key so that NaN wins and -0 < +0.
+template <int CHUNKS>
+__device__ __forceinline__ int64_t warp_row_argmax(const float4 (&v)[CHUNKS], int vec_cols, int lane) {
+    float m = __int_as_float(0xff800000);
+    uint32_t magnitude = 0;
+#pragma unroll
+    for (int j = 0; j < CHUNKS; j++) {
+        if (lane + 32 * j < vec_cols) {
+            const float e[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                m = fmaxf(m, e[q]);
+                uint32_t a = __float_as_uint(e[q]) & 0x7fffffffu;
+                magnitude = a > magnitude ? a : magnitude;
+            }
+        }
+    }
+    m = warp_max_plain(m);
+    magnitude = warp_umax(magnitude);
+    if (magnitude <= 0x7f800000u && m != 0.0f) {
+        uint32_t first = 0xffffffffu;
+#pragma unroll
+        for (int j = CHUNKS - 1; j >= 0; j--) {
+            const int c = lane + 32 * j;
+            if (c < vec_cols) {
+                if (v[j].w == m) first = (uint32_t)(c * 4 + 3);
+                if (v[j].z == m) first = (uint32_t)(c * 4 + 2);
+                if (v[j].y == m) first = (uint32_t)(c * 4 + 1);
+                if (v[j].x == m) first = (uint32_t)(c * 4);
+            }
+        }
+        return (int64_t)warp_umin(first);
+    }
+    unsigned long long best = 0;
+#pragma unroll
+    for (int j = 0; j < CHUNKS; j++) {
+        const int c = lane + 32 * j;
+        if (c < vec_cols) {
+            const float e[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                unsigned long long cand = ((unsigned long long)order_key(e[q]) << 32) | (0xffffffffu - (uint32_t)(c * 4 + q));
+                best = cand > best ? cand : best;
+            }
+        }
+    }
+    best = warp_best(best);
+    return (int64_t)(0xffffffffu - (uint32_t)(best & 0xffffffffu));
+}
+
+template <int CHUNKS>
+__global__ void __launch_bounds__(kThreads) argmax_vec_kernel(const float *__restrict__ x, int64_t *out, int64_t rows, int cols) {
+    int lane = threadIdx.x & 31;
+    int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int vec_cols = cols >> 2;
+    for (int64_t r = warp; r < rows; r += warps) {
+        const float4 *row = reinterpret_cast<const float4 *>(x + r * cols);
+        float4 v[CHUNKS];
+#pragma unroll
+        for (int j = 0; j < CHUNKS; j++) if (lane + 32 * j < vec_cols) v[j] = row[lane + 32 * j];
+        int64_t best = warp_row_argmax<CHUNKS>(v, vec_cols, lane);
+        if (lane == 0) out[r] = best;
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) argmax_kernel(const float *__restrict__ x, int64_t *out, int64_t rows, int64_t cols) {
     int lane = threadIdx.x & 31;
     int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     for (int64_t r = warp; r < rows; r += warps) {
         const float *row = x + r * cols;
+        // larger key wins; among equal keys the smaller index wins (FIRST_INDEX ties)
         unsigned long long best = 0;
         for (int64_t c = lane; c < cols; c += 32) {
-            // larger key wins; among equal keys the smaller index wins (FIRST_INDEX ties)
             unsigned long long cand = ((unsigned long long)order_key(row[c]) << 32) | (0xffffffffu - (uint32_t)c);
             best = cand > best ? cand : best;
         }
@@ -339,88 +440,122 @@ inline int64_t colsum_splits(int64_t rows, int64_t cols) {
 template <typename L>
 __device__ __forceinline__ int64_t load_label(const void *labels, int64_t r) { return (int64_t)((const L *)labels)[r]; }
 
-template <int CHUNKS, typename L>
-__global__ void __launch_bounds__(kThreads) ce_rows_vec_kernel(const float *__restrict__ logits, const void *__restrict__ labels,
+// One row, any values (NaN, infinities, signed zeros), any width: re-reads the row from memory for
+// each pass.  The careful route of the fast kernel and the body of the generic kernel.
+__device__ __noinline__ void ce_row_careful(const float *__restrict__ row, int64_t cols, int64_t safe, float scale,
+                                            float *loss_out, float *grad_row, int64_t *argmax_out, int lane) {
+    float mplain = __int_as_float(0xff800000), mjava = __int_as_float(0xff800000);
+    unsigned long long best = 0;
+    for (int64_t c = lane; c < cols; c += 32) {
+        float x = row[c];
+        mplain = x > mplain ? x : mplain;
+        mjava = java_max(mjava, x);
+        unsigned long long cand = ((unsigned long long)order_key(x) << 32) | (0xffffffffu - (uint32_t)c);
+        best = cand > best ? cand : best;
+    }
+    mplain = warp_max_plain(mplain);
+    mjava = warp_max_java(mjava);
+    if (argmax_out) { best = warp_best(best); if (lane == 0) *argmax_out = (int64_t)(0xffffffffu - (uint32_t)(best & 0xffffffffu)); }
+    double acc = 0.0;
+    for (int64_t c = lane; c < cols; c += 32) acc += (double)exp_accurate(__fsub_rn(row[c], mplain));
+    float sum = (float)warp_sum(acc);
+    if (lane == 0 && loss_out) *loss_out = __fsub_rn(__fadd_rn(mplain, (float)log((double)sum)), row[safe]);
+    if (grad_row) {
+        // the gradient's MAX aggregate follows Math.max: a NaN logit poisons the whole row
+        if (mplain != mjava) sum = __int_as_float(0x7fc00000);
+        for (int64_t c = lane; c < cols; c += 32) {
+            float p = __fdiv_rn(exp_accurate(__fsub_rn(row[c], mplain)), sum);
+            grad_row[c] = __fmul_rn(__fsub_rn(p, c == safe ? 1.0f : 0.0f), scale);
+        }
+    }
+}
+
+template <int CHUNKS, typename L, bool GRAD, bool ARGMAX>
+__global__ void __launch_bounds__(kThreads, CHUNKS >= 8 ? 3 : 4) ce_rows_vec_kernel(const float *__restrict__ logits, const void *__restrict__ labels,
         const float *__restrict__ seed, int64_t rows, int cols, float *row_loss, float *grad, int64_t *argmax_out, int *error_word) {
     int lane = threadIdx.x & 31;
     int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     const int vec_cols = cols >> 2;
-    float scale = grad ? __fdiv_rn(seed ? seed[0] : 1.0f, (float)rows) : 0.0f;
+    const float scale = GRAD ? __fdiv_rn(seed ? seed[0] : 1.0f, (float)rows) : 0.0f;
     for (int64_t r = warp; r < rows; r += warps) {
-        const float4 *row = reinterpret_cast<const float4 *>(logits + r * cols);
+        const float *row_s = logits + r * cols;
+        const float4 *row = reinterpret_cast<const float4 *>(row_s);
         float4 v[CHUNKS];
 #pragma unroll
-        for (int j = 0; j < CHUNKS; j++) {
-            int c = lane + 32 * j;
-            v[j] = c < vec_cols ? row[c] : make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
-        }
+        for (int j = 0; j < CHUNKS; j++) v[j] = lane + 32 * j < vec_cols ? row[lane + 32 * j] : make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
         int64_t label = load_label<L>(labels, r);
-        bool label_ok = label >= 0 && label < cols;
-        if (!label_ok && lane == 0) atomicOr(error_word, ERR_LABEL_RANGE);
-        int64_t safe = label < 0 ? 0 : (label >= cols ? cols - 1 : label);
-        float mplain = __int_as_float(0xff800000), mjava = __int_as_float(0xff800000);
-        unsigned long long best = 0;
+        if ((label < 0 || label >= cols) && lane == 0) atomicOr(error_word, ERR_LABEL_RANGE);
+        const int safe = (int)(label < 0 ? 0 : (label >= cols ? cols - 1 : label));
+        // maximum (fmaxf skips NaN like the reference's plain '>' scan) and a probe that turns NaN
+        // for any NaN or infinity in the row: x * 0 accumulates on the FMA pipe
+        float mplain = __int_as_float(0xff800000), probe = 0.0f;
 #pragma unroll
         for (int j = 0; j < CHUNKS; j++) {
-            int c = lane + 32 * j;
-            if (c < vec_cols) {
-                float e[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
-#pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    mplain = e[q] > mplain ? e[q] : mplain;
-                    mjava = java_max(mjava, e[q]);
-                    if (argmax_out) {
-                        unsigned long long cand = ((unsigned long long)order_key(e[q]) << 32) | (0xffffffffu - (uint32_t)(c * 4 + q));
-                        best = cand > best ? cand : best;
-                    }
-                }
-            }
+            mplain = fmaxf(fmaxf(mplain, fmaxf(v[j].x, v[j].y)), fmaxf(v[j].z, v[j].w));
+            probe = fmaf(v[j].x, 0.0f, probe); probe = fmaf(v[j].y, 0.0f, probe);
+            probe = fmaf(v[j].z, 0.0f, probe); probe = fmaf(v[j].w, 0.0f, probe);
         }
         mplain = warp_max_plain(mplain);
-        mjava = warp_max_java(mjava);
-        if (argmax_out) { best = warp_best(best); if (lane == 0) argmax_out[r] = (int64_t)(0xffffffffu - (uint32_t)(best & 0xffffffffu)); }
-        bool same_max = mplain == mjava;        // differs only when the row holds a NaN
+        const bool careful = __any_sync(0xffffffffu, probe != probe) || (ARGMAX && mplain == 0.0f);
+        if (careful) {      // rare: non-finite logits, or a zero maximum whose sign decides the arg-max
+            ce_row_careful(row_s, cols, safe, scale, row_loss ? row_loss + r : nullptr, GRAD ? grad + r * cols : nullptr,
+                           ARGMAX ? argmax_out + r : nullptr, lane);
+            continue;
+        }
+        if (ARGMAX) {       // finite row, non-zero maximum: the first column equal to it
+            uint32_t first = 0xffffffffu;
+#pragma unroll
+            for (int j = CHUNKS - 1; j >= 0; j--) {
+                const uint32_t c4 = (uint32_t)(lane + 32 * j) * 4;
+                first = v[j].w == mplain ? c4 + 3 : first;
+                first = v[j].z == mplain ? c4 + 2 : first;
+                first = v[j].y == mplain ? c4 + 1 : first;
+                first = v[j].x == mplain ? c4 : first;
+            }
+            first = warp_umin(first);
+            if (lane == 0) argmax_out[r] = (int64_t)first;
+        }
         double acc = 0.0;
-        float target_logit = 0.0f;
 #pragma unroll
         for (int j = 0; j < CHUNKS; j++) {
-            int c = lane + 32 * j;
-            if (c < vec_cols) {
+            // padding lanes hold -FLT_MAX: their exponential clamps to 1.18e-38, far below rounding
+            float e0 = exp_shifted(__fsub_rn(v[j].x, mplain)), e1 = exp_shifted(__fsub_rn(v[j].y, mplain));
+            float e2 = exp_shifted(__fsub_rn(v[j].z, mplain)), e3 = exp_shifted(__fsub_rn(v[j].w, mplain));
+            v[j] = make_float4(e0, e1, e2, e3);
+            if (lane + 32 * j < vec_cols) acc += (double)__fadd_rn(__fadd_rn(e0, e1), __fadd_rn(e2, e3));
+        }
+        const float sum = (float)warp_sum(acc);            // finite, at least 1: the maximum contributes exp(0)
+        const int owner = (safe >> 2) & 31;
+        const float target_logit = row_s[safe];            // a cache hit; avoids selecting it out of the registers
+        if (lane == 0 && row_loss) row_loss[r] = __fsub_rn(__fadd_rn(mplain, (float)log((double)sum)), target_logit);
+        if (GRAD) {
+            float4 *out = reinterpret_cast<float4 *>(grad + r * cols);
+            // p = e / sum as one reciprocal per row plus a remainder-corrected product per element;
+            // (p - onehot) * scale equals p * scale everywhere but at the label, which its owner fixes up
+            const float rcp = __frcp_rn(sum);
+#pragma unroll
+            for (int j = 0; j < CHUNKS; j++) {
                 float e[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
-                    if ((int64_t)(c * 4 + q) == safe) target_logit = e[q];
-                    e[q] = exp_accurate(__fsub_rn(e[q], mplain));
-                    acc += (double)e[q];
+                    float p = __fmul_rn(e[q], rcp);
+                    p = fmaf(fmaf(-p, sum, e[q]), rcp, p);
+                    e[q] = __fmul_rn(p, scale);
                 }
-                v[j] = make_float4(e[0], e[1], e[2], e[3]);
+                if (lane + 32 * j < vec_cols) out[lane + 32 * j] = make_float4(e[0], e[1], e[2], e[3]);
             }
-        }
-        float sum = (float)warp_sum(acc);
-        target_logit = __shfl_sync(0xffffffffu, target_logit, (int)((safe >> 2) & 31));
-        if (lane == 0 && row_loss) row_loss[r] = __fsub_rn(__fadd_rn(mplain, (float)log((double)sum)), target_logit);
-        if (grad) {
-            float4 *out = reinterpret_cast<float4 *>(grad + r * cols);
-            if (!same_max) sum = __int_as_float(0x7fc00000);      // a NaN logit poisons the whole row, as MAX propagates it
-#pragma unroll
-            for (int j = 0; j < CHUNKS; j++) {
-                int c = lane + 32 * j;
-                if (c < vec_cols) {
-                    float e[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        float hot = (int64_t)(c * 4 + q) == safe ? 1.0f : 0.0f;
-                        e[q] = __fmul_rn(__fsub_rn(__fdiv_rn(e[q], sum), hot), scale);
-                    }
-                    out[c] = make_float4(e[0], e[1], e[2], e[3]);
-                }
+            if (lane == owner) {
+                const float te = exp_shifted(__fsub_rn(target_logit, mplain));
+                float p = __fmul_rn(te, rcp);
+                p = fmaf(fmaf(-p, sum, te), rcp, p);
+                grad[r * cols + safe] = __fmul_rn(__fsub_rn(p, 1.0f), scale);     // same thread as the float4 store above: ordered
             }
         }
     }
 }
 
-// Any column count: one warp per row, the row is re-read for the second and third pass (it is
-// still in L1/L2); used for narrow rows (the 10-class head) and rows that are not 16-byte aligned.
+// Any column count: one warp per row through the careful routine; used for narrow rows (the
+// 10-class head) and rows that are not 16-byte aligned.
 template <typename L>
 __global__ void ce_rows_generic_kernel(const float *__restrict__ logits, const void *__restrict__ labels, const float *__restrict__ seed,
         int64_t rows, int64_t cols, float *row_loss, float *grad, int64_t *argmax_out, int *error_word) {
@@ -428,34 +563,11 @@ __global__ void ce_rows_generic_kernel(const float *__restrict__ logits, const v
     int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     float scale = grad ? __fdiv_rn(seed ? seed[0] : 1.0f, (float)rows) : 0.0f;
     for (int64_t r = warp; r < rows; r += warps) {
-        const float *row = logits + r * cols;
         int64_t label = load_label<L>(labels, r);
         if ((label < 0 || label >= cols) && lane == 0) atomicOr(error_word, ERR_LABEL_RANGE);
         int64_t safe = label < 0 ? 0 : (label >= cols ? cols - 1 : label);
-        float mplain = __int_as_float(0xff800000), mjava = __int_as_float(0xff800000);
-        unsigned long long best = 0;
-        for (int64_t c = lane; c < cols; c += 32) {
-            float x = row[c];
-            mplain = x > mplain ? x : mplain;
-            mjava = java_max(mjava, x);
-            unsigned long long cand = ((unsigned long long)order_key(x) << 32) | (0xffffffffu - (uint32_t)c);
-            best = cand > best ? cand : best;
-        }
-        mplain = warp_max_plain(mplain);
-        mjava = warp_max_java(mjava);
-        if (argmax_out) { best = warp_best(best); if (lane == 0) argmax_out[r] = (int64_t)(0xffffffffu - (uint32_t)(best & 0xffffffffu)); }
-        double acc = 0.0;
-        for (int64_t c = lane; c < cols; c += 32) acc += (double)exp_accurate(__fsub_rn(row[c], mplain));
-        float sum = (float)warp_sum(acc);
-        if (lane == 0 && row_loss) row_loss[r] = __fsub_rn(__fadd_rn(mplain, (float)log((double)sum)), row[safe]);
-        if (grad) {
-            if (mplain != mjava) sum = __int_as_float(0x7fc00000);
-            float *out = grad + r * cols;
-            for (int64_t c = lane; c < cols; c += 32) {
-                float p = __fdiv_rn(exp_accurate(__fsub_rn(row[c], mplain)), sum);
-                out[c] = __fmul_rn(__fsub_rn(p, c == safe ? 1.0f : 0.0f), scale);
-            }
-        }
+        ce_row_careful(logits + r * cols, cols, safe, scale, row_loss ? row_loss + r : nullptr, grad ? grad + r * cols : nullptr,
+                       argmax_out ? argmax_out + r : nullptr, lane);
     }
 }
 
@@ -622,7 +734,14 @@ cudaError_t full_sum(cudaStream_t s, const float *x, const Index4 &ix, int64_t t
 
 cudaError_t argmax_rows(cudaStream_t s, const float *x, int64_t *out, int64_t rows, int64_t cols) {
     if (rows == 0) return cudaSuccess;
-    argmax_kernel<<<grid_for(rows, kThreads / 32), kThreads, 0, s>>>(x, out, rows, cols);
+    const int grid = grid_for(rows, kThreads / 32);
+    if ((cols & 3) == 0 && cols >= 128 && cols <= 1024 && ((uintptr_t)x & 15) == 0) {
+        int chunks = (int)((cols / 4 + 31) / 32);
+        if (chunks <= 1) argmax_vec_kernel<1><<<grid, kThreads, 0, s>>>(x, out, rows, (int)cols);
+        else if (chunks <= 2) argmax_vec_kernel<2><<<grid, kThreads, 0, s>>>(x, out, rows, (int)cols);
+        else if (chunks <= 4) argmax_vec_kernel<4><<<grid, kThreads, 0, s>>>(x, out, rows, (int)cols);
+        else argmax_vec_kernel<8><<<grid, kThreads, 0, s>>>(x, out, rows, (int)cols);
+    } else argmax_kernel<<<grid, kThreads, 0, s>>>(x, out, rows, cols);
     return cudaGetLastError();
 }
 
@@ -694,14 +813,20 @@ cudaError_t cross_entropy(cudaStream_t s, const float *logits, DType label_type,
     int grid = grid_for(rows, kThreads / 32);
     bool vec = (cols & 3) == 0 && cols >= 128 && cols <= 1024 && (((uintptr_t)logits | (uintptr_t)grad_out) & 15) == 0;
     bool i32 = label_type == DType::I32;
-#define SYN_CE_VEC(C) do { if (i32) ce_rows_vec_kernel<C, int32_t><<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, (int)cols, row_loss, grad_out, argmax_out, error_word); \
-                           else ce_rows_vec_kernel<C, int64_t><<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, (int)cols, row_loss, grad_out, argmax_out, error_word); } while (0)
+#define SYN_CE_ARGS <<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, (int)cols, row_loss, grad_out, argmax_out, error_word)
+#define SYN_CE_VEC2(C, L) do { if (grad_out && argmax_out) ce_rows_vec_kernel<C, L, true, true> SYN_CE_ARGS; \
+                               else if (grad_out) ce_rows_vec_kernel<C, L, true, false> SYN_CE_ARGS; \
+                               else if (argmax_out) ce_rows_vec_kernel<C, L, false, true> SYN_CE_ARGS; \
+                               else ce_rows_vec_kernel<C, L, false, false> SYN_CE_ARGS; } while (0)
+#define SYN_CE_VEC(C) do { if (i32) SYN_CE_VEC2(C, int32_t); else SYN_CE_VEC2(C, int64_t); } while (0)
     if (vec) {
         int chunks = (int)((cols / 4 + 31) / 32);
         if (chunks <= 1) SYN_CE_VEC(1); else if (chunks <= 2) SYN_CE_VEC(2); else if (chunks <= 4) SYN_CE_VEC(4); else SYN_CE_VEC(8);
     } else if (i32) ce_rows_generic_kernel<int32_t><<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, cols, row_loss, grad_out, argmax_out, error_word);
     else ce_rows_generic_kernel<int64_t><<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, cols, row_loss, grad_out, argmax_out, error_word);
 #undef SYN_CE_VEC
+#undef SYN_CE_VEC2
+#undef SYN_CE_ARGS
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess || !loss_out) return e;
     mean_kernel<<<1, 1024, 0, s>>>(row_loss, rows, loss_out);

@@ -16,11 +16,12 @@
 //   COLSUM         a [m,n] -> out [n]
 //   SOFTMAX        a [m,n] -> out
 //   CROSS_ENTROPY  a = logits [m,n], b = labels [m], c = seed scalar or -1 -> out = mean loss or -1,
-//                  out2 = gradient wrt logits or -1
+//                  out2 = gradient wrt logits or -1, out3 = row arg-max (INT64) or -1
 //   MSE            a, b -> out scalar
 //   ARG_MAX        a [m,n] -> out [m] INT64
 //   RELU_BACKWARD  a = gate source, b = upstream gradient -> out
 #include "lowering.hpp"
+#include "kernels.hpp"
 
 #include <algorithm>
 #include <cstring>
@@ -43,6 +44,15 @@ const char *step_name(StepKind k) {
         case StepKind::COPY: return "copy"; case StepKind::ROW_REDUCE: return "row_reduce"; case StepKind::FULL_SUM: return "full_sum";
         case StepKind::COLSUM: return "colsum"; case StepKind::SOFTMAX: return "softmax"; case StepKind::CROSS_ENTROPY: return "cross_entropy";
         case StepKind::MSE: return "mse"; case StepKind::ARG_MAX: return "arg_max"; case StepKind::RELU_BACKWARD: return "relu_backward";
+    }
+    return "?";
+}
+
+const char *engine_name(GemmEngine e) {
+    switch (e) {
+        case GemmEngine::EXACT_SIMT: return "exact_simt"; case GemmEngine::TENSOR_CORE: return "tcgen05_3xtf32";
+        case GemmEngine::NARROW_OUT: return "narrow_out"; case GemmEngine::NARROW_INNER: return "narrow_inner";
+        case GemmEngine::NARROW_REDUCE: return "narrow_reduce";
     }
     return "?";
 }
@@ -95,7 +105,7 @@ struct LinearGroup {          // MATMUL [-> ADD bias] [-> RELU] [-> gate by WHER
 };
 
 struct CrossEntropyGroup {
-    int logits = -1, labels = -1, seed = -1, loss = -1, grad = -1;
+    int logits = -1, labels = -1, seed = -1, loss = -1, grad = -1, argmax = -1;
     std::set<int> nodes;
     int emit_at = -1;
 };
@@ -322,6 +332,17 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
         host->nodes.insert(i);
         covered[i] = 1;
     }
+    // a row ARG_MAX over the same logits rides in the same pass (the row is already in registers)
+    for (int i = 0; i < node_count; i++) {
+        const Node &n = g.nodes[i];
+        if (n.op != Op::ARG_MAX || covered[i]) continue;
+        for (auto &ce : ces) if (ce.argmax < 0 && ce.logits == n.inputs[0] && i > *ce.nodes.begin()) {
+            ce.argmax = n.outputs[0];
+            ce.nodes.insert(i);
+            covered[i] = 1;
+            break;
+        }
+    }
     for (auto &ce : ces) {
         int first = *ce.nodes.begin();
         auto defined_before = [&](int v) { return v < 0 || g.values[v].producer < first; };
@@ -331,7 +352,7 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
         }
         Step st;
         st.kind = StepKind::CROSS_ENTROPY;
-        st.a = ce.logits; st.b = ce.labels; st.c = ce.seed; st.out = ce.loss; st.out2 = ce.grad;
+        st.a = ce.logits; st.b = ce.labels; st.c = ce.seed; st.out = ce.loss; st.out2 = ce.grad; st.out3 = ce.argmax;
         st.m = g.values[ce.logits].shape[0]; st.n = g.values[ce.logits].shape[1];
         st.nodes.assign(ce.nodes.begin(), ce.nodes.end());
         emit_at[first].push_back(st);
@@ -398,7 +419,7 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
     };
     std::vector<char> published_done(g.publications.size(), 0);
     auto finish_step = [&](Step st) {
-        for (int v : {st.out, st.out2}) if (v >= 0) {
+        for (int v : {st.out, st.out2, st.out3}) if (v >= 0) {
             const View &w = plan.views[v];
             if (w.slot == SlotKind::PUBLICATION) { st.ready_publications.push_back(w.index); published_done[w.index] = 1; }
         }
@@ -413,7 +434,7 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
     for (int i = 0; i < node_count; i++) {
         auto pending = emit_at.find(i);
         if (pending != emit_at.end()) for (Step st : pending->second) {
-            for (int v : {st.out, st.out2}) if (v >= 0) assign_output(v);
+            for (int v : {st.out, st.out2, st.out3}) if (v >= 0) assign_output(v);
             if (st.kind == StepKind::GEMM) {
                 const View &c = plan.views[st.out];
                 bool transposed = c.strides.size() == 2 && c.strides[0] == 1 && c.shape[0] != 1 && c.strides[1] != 1;
@@ -422,6 +443,20 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
                 bool a_ok = a.strides[0] == 1 || a.strides[1] == 1 || a.shape[0] == 1 || a.shape[1] == 1;
                 bool b_ok = b.strides[0] == 1 || b.strides[1] == 1 || b.shape[0] == 1 || b.shape[1] == 1;
                 if (!a_ok || !b_ok) st.engine = GemmEngine::EXACT_SIMT;
+                // large products with one extent of at most 16 stream through the narrow kernels
+                if (options.gemm_engine != 1 && st.engine == GemmEngine::EXACT_SIMT && st.out2 < 0
+                    && (double)st.m * (double)st.n * (double)st.k >= 16.0 * 1024 * 1024) {
+                    const bool c_rows = c.strides[1] == 1 || c.shape[1] == 1;
+                    if (st.n <= 16 && st.mask < 0 && a.strides[1] == 1 && b.strides[0] == 1
+                        && kern::narrow_out_supported(st.m, st.n, st.k, a.strides[0], b.strides[1]))
+                        st.engine = GemmEngine::NARROW_OUT;
+                    else if (st.k <= 16 && st.bias < 0 && !st.relu && a.strides[1] == 1 && b.strides[1] == 1 && c_rows && !transposed
+                             && kern::narrow_inner_supported(st.m, st.n, st.k, b.strides[0], c.strides[0]))
+                        st.engine = GemmEngine::NARROW_INNER;
+                    else if (st.n <= 16 && st.bias < 0 && !st.relu && st.mask < 0 && a.strides[0] == 1 && b.strides[1] == 1
+                             && kern::narrow_reduce_supported(st.m, st.n, st.k, a.strides[1]))
+                        st.engine = GemmEngine::NARROW_REDUCE;
+                }
                 if (st.bias >= 0 && !plan.views[st.bias].dense()) { message = "strided bias"; return UNSUPPORTED_SHAPE; }
                 if (st.mask >= 0 && !plan.views[st.mask].dense()) { message = "strided gate"; return UNSUPPORTED_SHAPE; }
             } else if (st.kind == StepKind::CROSS_ENTROPY) {
@@ -557,7 +592,7 @@ std::string describe_plan(const Program &g, const Plan &plan) {
     for (const Step &st : plan.steps) {
         os << step_name(st.kind);
         if (st.kind == StepKind::GEMM) {
-            os << " engine=" << (st.engine == GemmEngine::TENSOR_CORE ? "tcgen05_3xtf32" : "exact_simt")
+            os << " engine=" << engine_name(st.engine)
                << " m=" << st.m << " n=" << st.n << " k=" << st.k;
             if (st.bias >= 0) os << " bias";
             if (st.relu) os << " relu";
@@ -568,7 +603,7 @@ std::string describe_plan(const Program &g, const Plan &plan) {
         } else if (st.kind == StepKind::BINARY || st.kind == StepKind::SCALAR || st.kind == StepKind::UNARY || st.kind == StepKind::ROW_REDUCE) {
             os << " op=" << op_name(st.op);
         } else if (st.kind == StepKind::CROSS_ENTROPY) {
-            os << " rows=" << st.m << " classes=" << st.n << (st.out >= 0 ? " loss" : "") << (st.out2 >= 0 ? " gradient" : "");
+            os << " rows=" << st.m << " classes=" << st.n << (st.out >= 0 ? " loss" : "") << (st.out2 >= 0 ? " gradient" : "") << (st.out3 >= 0 ? " arg_max" : "");
         }
         if (st.kind != StepKind::GEMM && st.kind != StepKind::CROSS_ENTROPY && st.m) os << " m=" << st.m << " n=" << st.n;
         os << " nodes=[";

@@ -43,13 +43,14 @@ enum class StepKind : int {
 };
 const char *step_name(StepKind k);
 
-enum class GemmEngine : int { EXACT_SIMT = 0, TENSOR_CORE = 1 };
+enum class GemmEngine : int { EXACT_SIMT = 0, TENSOR_CORE = 1, NARROW_OUT = 2, NARROW_INNER = 3, NARROW_REDUCE = 4 };
+const char *engine_name(GemmEngine e);
 
 struct Step {
     StepKind kind = StepKind::BINARY;
     Op op = Op::ADD;                // BINARY / SCALAR / UNARY / ROW_REDUCE flavour
     int a = -1, b = -1, c = -1;     // input value ids (meaning per kind, see lowering.cpp)
-    int out = -1, out2 = -1;        // output value ids
+    int out = -1, out2 = -1, out3 = -1;   // output value ids
     int bias = -1, mask = -1;       // GEMM epilogue operands
     bool relu = false;
     int64_t m = 0, n = 0, k = 0;    // GEMM extents, or rows / cols of row kernels

@@ -6,6 +6,7 @@
 #include <dlfcn.h>
 
 #include <algorithm>
+#include <array>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -35,6 +36,8 @@ struct Context {
     int *error_host = nullptr;      // pinned mirror
     int gemm_engine = 0;
     int time_steps = 0;
+    int fused_planes = 1;
+    int gemm_promote = 0;
     cudaEvent_t timer_start = nullptr, timer_stop = nullptr;
     std::mutex mutex;
 };
@@ -88,12 +91,24 @@ struct Comm {
 
 struct Planes { float *hi = nullptr, *lo = nullptr; int64_t rows = 0, kp = 0; int last_run = -1; };
 
+// Identity of an operand's planes: the storage it views and how the plane rows / columns walk it.
+// Two program values that view the same storage the same way (a value and PERMUTE of PERMUTE of it)
+// share planes; a value and its transpose do not.
+typedef std::array<int64_t, 7> PlaneKey;
+PlaneKey plane_key(const View &v, int orientation) {
+    int r = orientation, c = 1 - orientation;
+    return PlaneKey{(int64_t)v.slot, (int64_t)v.index, v.offset, v.shape[r], v.shape[r] == 1 ? 0 : v.strides[r],
+                    v.shape[c], v.shape[c] == 1 ? 0 : v.strides[c]};
+}
+
 struct StepExec {
     kern::TensorCoreGemm *tc = nullptr;
     int planes_p = -1, planes_q = -1;       // indices into Executable::planes
     bool swapped = false;                   // result stored transposed: roles of the operands exchanged
     double *colsum_partials = nullptr;
     float *row_loss = nullptr;
+    float *narrow_partials = nullptr;
+    int emit_planes = -1, emit_tplanes = -1;    // planes this tensor-core step writes from its epilogue
 };
 
 struct Executable {
@@ -104,7 +119,7 @@ struct Executable {
     std::vector<void *> scratch;
     void *constants = nullptr;              // 8 bytes per constant slot
     std::vector<Planes> planes;
-    std::map<std::pair<int, int>, int> plane_index;     // (value id, orientation) -> planes
+    std::map<PlaneKey, int> plane_index;
     std::vector<StepExec> exec;
     std::vector<void *> owned;              // every device allocation, for release
     std::vector<uint64_t> feed_bytes, publication_bytes;
@@ -237,7 +252,7 @@ int32_t prepare_executable(Executable *x) {
     }
     x->exec.resize(plan.steps.size());
     auto planes_for = [&](int value, int orientation, int64_t rows, int64_t k) -> int {
-        auto key = std::make_pair(value, orientation);
+        PlaneKey key = plane_key(plan.views[value], orientation);
         auto it = x->plane_index.find(key);
         if (it != x->plane_index.end()) return it->second;
         Planes p;
@@ -262,8 +277,11 @@ int32_t prepare_executable(Executable *x) {
             se.planes_q = se.swapped ? pa : pb;
             const Planes &P = x->planes[se.planes_p], &Q = x->planes[se.planes_q];
             int status = OK;
-            se.tc = kern::tc_gemm_prepare(P.hi, P.lo, Q.hi, Q.lo, P.rows, Q.rows, P.kp, ctx->sm_count, &status);
+            se.tc = kern::tc_gemm_prepare(P.hi, P.lo, Q.hi, Q.lo, P.rows, Q.rows, P.kp, ctx->sm_count, ctx->gemm_promote, &status);
             if (!se.tc) return status;
+        } else if (st.kind == StepKind::GEMM && st.engine == GemmEngine::NARROW_REDUCE) {
+            void *p; if (!alloc((uint64_t)kern::narrow_reduce_partial_floats(st.m, st.n, st.k) * 4, &p)) return ALLOCATION_FAILED;
+            se.narrow_partials = (float *)p;
         } else if (st.kind == StepKind::COLSUM) {
             void *p; if (!alloc((uint64_t)kern::colsum_partial_count(st.m, st.n) * 8, &p)) return ALLOCATION_FAILED;
             se.colsum_partials = (double *)p;
@@ -271,6 +289,23 @@ int32_t prepare_executable(Executable *x) {
             void *p; if (!alloc((uint64_t)st.m * 4, &p)) return ALLOCATION_FAILED;
             se.row_loss = (float *)p;
         }
+    }
+    // a tensor-core GEMM whose dense result is later read as a GEMM operand writes that operand's
+    // planes itself (both orientations if asked), which removes the separate split pass
+    for (size_t i = 0; i < plan.steps.size(); i++) {
+        const Step &st = plan.steps[i];
+        StepExec &se = x->exec[i];
+        // worth it only when the producer's main loop is long enough to hide the extra stores behind
+        // the next tile (measured: a K = 784 producer doubles in time, K = 4096 producers gain)
+        if (st.kind != StepKind::GEMM || st.engine != GemmEngine::TENSOR_CORE || se.swapped || !ctx->fused_planes || st.k < 2048) continue;
+        const View &u = plan.views[st.out2 >= 0 ? st.out2 : st.out];
+        if (u.shape.size() != 2 || !u.dense()) continue;
+        auto normal = x->plane_index.find(plane_key(u, 0));
+        if (normal != x->plane_index.end()) se.emit_planes = normal->second;
+        View t = u;                                         // the transposed view of the same storage
+        std::swap(t.shape[0], t.shape[1]); std::swap(t.strides[0], t.strides[1]);
+        auto transposed = x->plane_index.find(plane_key(t, 0));
+        if (transposed != x->plane_index.end()) se.emit_tplanes = transposed->second;
     }
     if (cudaEventCreate(&x->start) != cudaSuccess || cudaEventCreate(&x->stop) != cudaSuccess) return INTERNAL_ERROR;
     x->sync_publication.assign(x->program.publications.size(), 0);
@@ -337,7 +372,21 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                 ep.gate = (const float *)ptr(st.mask);
                 ep.relu = st.relu && st.out2 < 0;
                 ep.second = (float *)ptr(st.out2);
-                if (st.engine == GemmEngine::EXACT_SIMT) {
+                cudaError_t narrow = cudaErrorInvalidValue;
+                if (st.engine == GemmEngine::NARROW_OUT)
+                    narrow = kern::gemm_narrow_out(s, ctx->sm_count, st.m, st.n, st.k, (const float *)ptr(st.a), a.strides[0], (const float *)ptr(st.b),
+                                                   b.strides[1], ep.bias, ep.relu, (float *)ptr(st.out), c.strides[0], c.strides[1]);
+                else if (st.engine == GemmEngine::NARROW_INNER)
+                    narrow = kern::gemm_narrow_inner(s, st.m, st.n, st.k, (const float *)ptr(st.a), a.strides[0], (const float *)ptr(st.b),
+                                                     b.strides[0], ep.gate, (float *)ptr(st.out), c.strides[0]);
+                else if (st.engine == GemmEngine::NARROW_REDUCE)
+                    narrow = kern::gemm_narrow_reduce(s, st.m, st.n, st.k, (const float *)ptr(st.a), a.strides[1], (const float *)ptr(st.b),
+                                                      b.strides[0], se.narrow_partials, (float *)ptr(st.out), c.strides[0], c.strides[1]);
+                if (st.engine != GemmEngine::TENSOR_CORE && st.engine != GemmEngine::EXACT_SIMT && narrow == cudaSuccess) {
+                    x->launches += st.engine == GemmEngine::NARROW_REDUCE ? 2 : 1;
+                } else if (st.engine != GemmEngine::TENSOR_CORE) {
+                    // the exact kernel takes every shape and alignment (and is what a misaligned view falls back to)
+                    cudaGetLastError();
                     LAUNCH(kern::gemm_exact(s, st.m, st.n, st.k, (const float *)ptr(st.a), a.strides[0], a.strides[1],
                                             (const float *)ptr(st.b), b.strides[0], b.strides[1],
                                             (float *)ptr(st.out), c.strides[0], c.strides[1], ep));
@@ -353,10 +402,18 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                         pl.last_run = x->run_counter;
                         return OK;
                     };
-                    int pa = x->plane_index[std::make_pair(st.a, 0)], pb = x->plane_index[std::make_pair(st.b, 1)];
+                    int pa = x->plane_index[plane_key(plan.views[st.a], 0)], pb = x->plane_index[plane_key(plan.views[st.b], 1)];
                     int32_t r1 = split(st.a, 0, pa); if (r1 != OK) return r1;
                     int32_t r2 = split(st.b, 1, pb); if (r2 != OK) return r2;
                     int64_t ldd = se.swapped ? c.strides[1] : c.strides[0];
+                    if (se.emit_planes >= 0) {
+                        Planes &pl = x->planes[se.emit_planes];
+                        ep.plane_hi = pl.hi; ep.plane_lo = pl.lo; ep.plane_ld = pl.kp; pl.last_run = x->run_counter;
+                    }
+                    if (se.emit_tplanes >= 0) {
+                        Planes &pl = x->planes[se.emit_tplanes];
+                        ep.tplane_hi = pl.hi; ep.tplane_lo = pl.lo; ep.tplane_ld = pl.kp; pl.last_run = x->run_counter;
+                    }
                     if (time_steps) cudaEventRecord(x->step_events[2 * i], s);
                     LAUNCH(kern::tc_gemm_launch(s, se.tc, (float *)ptr(st.out), ldd, ep, ctx->error_dev));
                 }
@@ -413,7 +470,7 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                 break;
             case StepKind::CROSS_ENTROPY:
                 LAUNCH(kern::cross_entropy(s, (const float *)ptr(st.a), plan.views[st.b].dtype, ptr(st.b), (const float *)ptr(st.c), st.m, st.n,
-                                           se.row_loss, (float *)ptr(st.out), (float *)ptr(st.out2), nullptr, ctx->error_dev));
+                                           se.row_loss, (float *)ptr(st.out), (float *)ptr(st.out2), (int64_t *)ptr(st.out3), ctx->error_dev));
                 if (st.out >= 0) x->launches++;
                 break;
             case StepKind::MSE:
@@ -532,6 +589,8 @@ int32_t synaptik_cuda_context_set_option(void *context, const char *name, int64_
     Context *ctx = as<Context>(context, TAG_CONTEXT);
     if (!ctx || !name) return INVALID_ARGUMENT;
     if (!strcmp(name, "gemm_engine")) { if (value < 0 || value > 2) return INVALID_ARGUMENT; ctx->gemm_engine = (int)value; return OK; }
+    if (!strcmp(name, "gemm_promote")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->gemm_promote = (int)value; return OK; }
+    if (!strcmp(name, "fused_planes")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->fused_planes = (int)value; return OK; }
     if (!strcmp(name, "time_steps")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->time_steps = (int)value; return OK; }
     return INVALID_ARGUMENT;
 }

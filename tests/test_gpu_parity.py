@@ -373,3 +373,41 @@ def test_sgd_variants_match_the_checker(ctx, oracle):
             assert oracle.sgd(p, g, mom, 0.01, momentum, dampening, wd, nesterov, completed_steps=step)
             assert np.array_equal(buf.download(np.float32, p.shape).view(np.uint32), p.view(np.uint32))
         opt.close()
+
+
+# ---- streaming kernels for products with a narrow extent -----------------------------------------
+def test_narrow_head_kernels(ctx, oracle):
+    rows, wide, classes = 8192, 512, 10                      # large enough for the automatic choice to pick them
+    rng = np.random.default_rng(12)
+    act = rng.uniform(0, 1, (rows, wide)).astype(np.float32)
+    w = (rng.standard_normal((classes, wide)) * 0.05).astype(np.float32)
+    bias = rng.standard_normal(classes).astype(np.float32)
+    dz = (rng.standard_normal((rows, classes)) * 1e-3).astype(np.float32)
+    gate = rng.standard_normal((rows, wide)).astype(np.float32)
+    g = GraphBuilder()
+    av, wv, bv, dv, gv = g.feed(F32, act.shape), g.feed(F32, w.shape), g.feed(F32, bias.shape), g.feed(F32, dz.shape), g.feed(F32, gate.shape)
+    wt, logits = g.linear(av, wv, bv)
+    g.publish(logits)                                         # narrow result
+    dx, dw, _ = g.linear_backward(av, wt, dv, need_dx=True, bias=False)
+    g.publish(g.relu_backward(gv, dx))                        # narrow contraction with the gate folded in
+    g.publish(dw)                                             # narrow weight gradient
+    plan = native.describe(g.build())
+    assert "narrow_out" in plan and "narrow_inner" in plan and "narrow_reduce" in plan
+    out, dxg, dwg = run_image(ctx, g, [act, w, bias, dz, gate])
+    ref = act.astype(np.float64) @ w.T.astype(np.float64) + bias
+    bound = (wide + 2) * 2.0 ** -24 * (np.abs(act).astype(np.float64) @ np.abs(w.T).astype(np.float64) + np.abs(bias))
+    assert np.all(np.abs(out - ref) <= bound)
+    assert np.abs(out - ref).max() <= 64 * 2.0 ** -24 * np.abs(ref).max()
+    sample = rng.choice(rows, 64, replace=False)
+    expect = oracle.relu_backward(gate[sample], oracle.matmul_rows(dz, w, sample))
+    assert np.array_equal(dxg[sample].view(np.uint32), expect.view(np.uint32))      # the reference's exact chain
+    ref_dw = dz.T.astype(np.float64) @ act.astype(np.float64)
+    assert np.abs(dwg - ref_dw).max() <= 2e-6 * np.abs(ref_dw).max()
+    # integer operands: all three are exact
+    acti = rng.integers(-3, 4, act.shape).astype(np.float32)
+    wi = rng.integers(-3, 4, w.shape).astype(np.float32)
+    dzi = rng.integers(-2, 3, dz.shape).astype(np.float32)
+    out, dxg, dwg = run_image(ctx, g, [acti, wi, bias * 0, dzi, gate])
+    assert np.array_equal(out, (acti.astype(np.int64) @ wi.T.astype(np.int64)).astype(np.float32))
+    assert np.array_equal(dxg, (dzi.astype(np.int64) @ wi.astype(np.int64)).astype(np.float32) * (gate > 0))
+    assert np.array_equal(dwg, (dzi.T.astype(np.int64) @ acti.astype(np.int64)).astype(np.float32))
