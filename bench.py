@@ -169,6 +169,8 @@ def run_cuda(args):
     ctx = native.Context(local_rank)
     if os.environ.get("SYNAPTIK_BENCH_FUSED_PLANES") == "0":
         ctx.set_option("fused_planes", 0)
+    if os.environ.get("SYNAPTIK_BENCH_PROMOTE") in ("0", "1"):
+        ctx.set_option("gemm_promote", int(os.environ["SYNAPTIK_BENCH_PROMOTE"]))
     comm = None
     if distributed:
         holder = [native.comm_unique_id() if rank == 0 else None]

@@ -66,7 +66,10 @@ SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_release(void *context);
  * 2 = tensor cores whenever the shape allows.  "time_steps": 1 = bracket every step of later runs
  * with CUDA events (see synaptik_cuda_executable_step_timings).  "fused_planes": 0 = executables
  * created afterwards split GEMM operands in separate passes instead of in the producing GEMM's
- * epilogue (default 1).  Unknown names return
+ * epilogue (default 1; only used while "gemm_promote" is 0).  "gemm_promote": 1 (default) = the
+ * tensor-core GEMM keeps only short partial sums (256 or 512 contraction steps) in tensor memory and
+ * adds them into round-to-nearest FP32 register sums; 0 = one tensor-memory accumulator over the
+ * whole contraction (faster epilogue, error grows with K).  Unknown names return
  * INVALID_ARGUMENT. */
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_set_option(void *context, const char *name, int64_t value);
 /* Blocks until all work issued on the context has finished. */

@@ -220,14 +220,20 @@ def mlp_forward(x, weights, biases):
     return acts
 
 
-def mlp_gradients(x, labels_or_target, weights, biases, loss: str = "ce", count: int = 0):
+def mlp_gradients(x, labels_or_target, weights, biases, loss: str = "ce", count: int = 0, hidden=None):
     """Loss and gradients of an MLP, executing the reference's backward node lists in order.
 
     Returns (loss, [dW1, db1, dW2, db2, ...], logits).  ``loss`` is "ce" (index cross entropy,
-    MEAN) or "mse" (MEAN).  ``count`` overrides the divisor of the loss gradient.
+    MEAN) or "mse" (MEAN).  ``count`` overrides the divisor of the loss gradient.  ``hidden``
+    (the hidden activations a1..a(L-1)) replaces the checker's own forward values in the backward
+    pass and in the last layer, so that a device's backward pass can be checked on the device's own
+    ReLU gates (a pre-activation within rounding distance of zero may legitimately take the other
+    branch on another implementation).
     """
     x = _f32(x)
     acts = mlp_forward(x, weights, biases)
+    if hidden is not None:
+        acts = [_f32(h) for h in hidden] + [linear(_f32(hidden[-1]), weights[-1], biases[-1], relu_flag=False)[1]]
     logits = acts[-1]
     if loss == "ce":
         _, value = index_cross_entropy(logits, labels_or_target)

@@ -257,6 +257,7 @@ struct TcParams {
     const float *bias; const float *gate; float *second; int relu;
     float *nhi, *nlo; int64_t nld;          // optional [m, nld] hi/lo planes of the result
     float *thi, *tlo; int64_t tld; int m_pad;   // optional transposed [n, tld] planes, tld = m_pad = m rounded up to 32
+    int chunk_kb;                            // promoted kernel: k-blocks per tensor-memory partial sum
     int *error_word;
 };
 
@@ -468,13 +469,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tf32x3_kernel(
 // The same pipeline with FP32 promotion.  Measured on B200: every tcgen05.mma adds its products into
 // the FP32 accumulator with truncation (toward zero), so a sum kept in tensor memory over the whole
 // contraction drifts by about 0.2 * K units of 2^-24 of the running sum.  Here tensor memory only
-// ever holds the partial sum of CHUNK_KB k-blocks (128 contraction steps); eight epilogue warps
+// ever holds the partial sum of chunk_kb k-blocks (32 contraction steps each); eight epilogue warps
 // add each finished partial into round-to-nearest FP32 register sums (128 per thread at BN = 256)
 // while the tensor core already works on the next partial in the other tensor-memory buffer.
 // The truncation is then relative to a short partial sum and the drift no longer grows with K.
 // ------------------------------------------------------------------------------------------------
 constexpr int PROMOTED_THREADS = 384;   // warp 0 producer, warp 1 MMA issuer, warps 4-11 epilogue
-constexpr int CHUNK_KB = 4;
 
 __device__ __forceinline__ void tmem_load16(uint32_t taddr, float (&v)[16]) {
     uint32_t r[16];
@@ -527,6 +527,7 @@ __global__ void __launch_bounds__(PROMOTED_THREADS, 1) gemm_tf32x3_promoted_kern
 
     const int total_tiles = prm.tiles_m * prm.tiles_n;
     const int kb_count = prm.k_blocks;
+    const int CHUNK_KB = prm.chunk_kb;
     const uint32_t smem_base = smem_u32(smem);
 
     // the two epilogue warpgroups hold the register sums: hand them the registers the producer /
@@ -717,10 +718,16 @@ static int forced_tile_n() {
     return value;
 }
 
+static int forced_chunk_kb() {
+    static int value = -1;
+    if (value < 0) { const char *e = getenv("SYNAPTIK_CUDA_CHUNK_KB"); value = e ? atoi(e) : 0; }
+    return value;
+}
+
 struct TensorCoreGemm {
     CUtensorMap p_hi, p_lo, q_hi, q_lo;
     int m, n, k_blocks, bn, grid;
-    int promote;
+    int promote, chunk_kb;
 };
 
 TensorCoreGemm *tc_gemm_prepare(const float *p_hi, const float *p_lo, const float *q_hi, const float *q_lo,
@@ -730,6 +737,12 @@ TensorCoreGemm *tc_gemm_prepare(const float *p_hi, const float *p_lo, const floa
     TensorCoreGemm *g = new TensorCoreGemm();
     g->m = (int)m; g->n = (int)n; g->k_blocks = (int)(k_padded / BK);
     g->promote = promote;
+    // Partial-sum length.  The epilogue warps that add the partials also write the finished tile, and
+    // the tensor core can run only two partials ahead of them, so short partials stall it at every
+    // tile end unless the tile's main loop is very long (the weight gradients, K = batch).  Measured on
+    // the 65536 x 4096 x 4096 layers: partials of 4 k-blocks cost 17 % of the step, 16 k-blocks nothing.
+    g->chunk_kb = g->k_blocks >= 256 ? 8 : 16;
+    if (forced_chunk_kb() > 0) g->chunk_kb = forced_chunk_kb();
     // tile width: the widest tile has the best operand reuse, but a persistent grid pays for the last
     // partial wave; take the width with the least (waves x width), narrower tiles handicapped a little
     auto cost = [&](int bn) {
@@ -779,6 +792,7 @@ cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, in
     prm.thi = ep.tplane_hi; prm.tlo = ep.tplane_lo; prm.tld = ep.tplane_ld; prm.m_pad = (int)ep.tplane_ld;
     prm.d = d; prm.ldd = ldd; prm.m = g->m; prm.n = g->n; prm.k_blocks = g->k_blocks;
     prm.tiles_m = (g->m + BM - 1) / BM; prm.tiles_n = (g->n + g->bn - 1) / g->bn;
+    prm.chunk_kb = g->chunk_kb;
     prm.bias = ep.bias; prm.gate = ep.gate; prm.second = ep.second; prm.relu = ep.relu; prm.error_word = error_word;
     if (g->bn == 256) return launch_tc<256>(s, g, prm);
     if (g->bn == 128) return launch_tc<128>(s, g, prm);

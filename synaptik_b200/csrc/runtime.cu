@@ -37,7 +37,7 @@ struct Context {
     int gemm_engine = 0;
     int time_steps = 0;
     int fused_planes = 1;
-    int gemm_promote = 0;
+    int gemm_promote = 1;
     cudaEvent_t timer_start = nullptr, timer_stop = nullptr;
     std::mutex mutex;
 };
@@ -297,7 +297,7 @@ int32_t prepare_executable(Executable *x) {
         StepExec &se = x->exec[i];
         // worth it only when the producer's main loop is long enough to hide the extra stores behind
         // the next tile (measured: a K = 784 producer doubles in time, K = 4096 producers gain)
-        if (st.kind != StepKind::GEMM || st.engine != GemmEngine::TENSOR_CORE || se.swapped || !ctx->fused_planes || st.k < 2048) continue;
+        if (st.kind != StepKind::GEMM || st.engine != GemmEngine::TENSOR_CORE || se.swapped || !ctx->fused_planes || ctx->gemm_promote || st.k < 2048) continue;
         const View &u = plan.views[st.out2 >= 0 ? st.out2 : st.out];
         if (u.shape.size() != 2 || !u.dense()) continue;
         auto normal = x->plane_index.find(plane_key(u, 0));

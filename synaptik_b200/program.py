@@ -298,7 +298,8 @@ def mlp_inference_graph(dims: Sequence[int], batch: int, arg_max: bool = False, 
     return MlpGraph(g.build(), names, pubs, shapes)
 
 
-def mlp_training_graph(dims: Sequence[int], batch: int, loss: str = "ce", label_dtype: int = I32, bias: bool = True) -> MlpGraph:
+def mlp_training_graph(dims: Sequence[int], batch: int, loss: str = "ce", label_dtype: int = I32, bias: bool = True,
+                       publish_activations: bool = False) -> MlpGraph:
     """The TRAINING_STEP graph TrainingSession compiles: forward, objective, and one gradient per
     parameter in trainingParameters() order (weight, bias per layer), published after the loss
     (TrainingSession.java:953-987).  Feeds: x, target, seed, then (w, b) per layer."""
@@ -351,4 +352,9 @@ def mlp_training_graph(dims: Sequence[int], batch: int, loss: str = "ce", label_
             g.publish(grads[2 * l + 1])
             pubs.append(f"db{l}")
             shapes[f"db{l}"] = grads[2 * l + 1].shape
+    if publish_activations:          # hidden activations, for checks that need the device's own ReLU gates
+        for l in range(1, layers):
+            g.publish(acts[l])
+            pubs.append(f"a{l}")
+            shapes[f"a{l}"] = acts[l].shape
     return MlpGraph(g.build(), names, pubs, shapes)

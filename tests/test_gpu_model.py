@@ -72,6 +72,40 @@ def test_known_answer_linear_model_journey(ctx):
     model.close()
 
 
+def test_backward_pass_on_the_devices_own_relu_gates(ctx, oracle):
+    # forward values within tolerance; then the backward pass checked against the checker run on
+    # the device's hidden activations, so a pre-activation that rounds to the other side of zero
+    # on the device (a legitimate outcome of any other summation order) cannot blur the comparison
+    from synaptik_b200 import program
+    dims, batch = [784, 256, 192, 128, 10], 512
+    rng = np.random.default_rng(11)
+    x = rng.uniform(0, 1, (batch, dims[0])).astype(np.float32)
+    labels = rng.integers(0, 10, batch).astype(np.int32)
+    ws = [nn.glorot_uniform(rng, dims[i + 1], dims[i]) for i in range(4)]
+    bs = [(rng.standard_normal(dims[i + 1]) * 0.05).astype(np.float32) for i in range(4)]
+    graph = program.mlp_training_graph(dims, batch, "ce", publish_activations=True)
+    ctx.set_option("gemm_engine", 2)
+    try:
+        exe = native.Executable(ctx, graph.image)
+    finally:
+        ctx.set_option("gemm_engine", 0)
+    feeds = [x, labels, np.array(1.0, dtype=np.float32)] + [a for pair in zip(ws, bs) for a in pair]
+    inputs = [ctx.upload(a) for a in feeds]
+    outputs = [ctx.buffer(max(int(np.prod(graph.shapes[name])) * 4, 4)) for name in graph.publications]
+    exe.run(inputs, outputs)
+    got = {name: buf.download(np.float32, graph.shapes[name]) for name, buf in zip(graph.publications, outputs)}
+    exe.close()
+    ref_acts = oracle.mlp_forward(x, ws, bs)
+    for l in (1, 2, 3):
+        assert np.abs(got[f"a{l}"] - ref_acts[l - 1]).max() <= 2e-5 * np.abs(ref_acts[l - 1]).max()
+    loss, grads, _ = oracle.mlp_gradients(x, labels, ws, bs, "ce", hidden=[got["a1"], got["a2"], got["a3"]])
+    assert abs(float(got["loss"]) - float(loss)) <= 1e-5 * abs(float(loss))
+    names = [n for l in range(4) for n in (f"dw{l}", f"db{l}")]
+    for name, want in zip(names, grads):
+        scale = np.abs(want).max() + 1e-12
+        assert np.abs(got[name] - want).max() <= 2e-5 * scale, (name, np.abs(got[name] - want).max() / scale)
+
+
 @pytest.mark.parametrize("engine", [1, 2])
 def test_classifier_training_tracks_the_checker_for_20_steps(ctx, oracle, engine):
     # the 784-4096-4096-4096-10 / Adam configuration at reduced width so the sequential checker
@@ -96,8 +130,13 @@ def test_classifier_training_tracks_the_checker_for_20_steps(ctx, oracle, engine
                 ref_loss, ref_grads, _ = oracle.mlp_gradients(x, labels, current[0::2], current[1::2], "ce")
                 assert abs(loss - float(ref_loss)) <= (1e-5 if engine == 2 else 2e-6) * abs(float(ref_loss)) + 1e-7
                 for got, want in zip(grads, ref_grads):
-                    scale = np.abs(want).max() + 1e-12
-                    assert np.abs(got - want).max() <= grad_tol * scale, (step, np.abs(got - want).max() / scale)
+                    if engine == 1:
+                        scale = np.abs(want).max() + 1e-12
+                        assert np.abs(got - want).max() <= grad_tol * scale, (step, np.abs(got - want).max() / scale)
+                    else:
+                        # a hidden pre-activation within rounding distance of zero may gate differently than
+                        # in the checker: one sample's contribution, about 1/batch of the gradient
+                        assert np.linalg.norm(got - want) <= 5e-3 * np.linalg.norm(want) + 1e-12, step
             device_loss = model.train(x, labels)
             ref_loss, ref_grads, _ = oracle.mlp_gradients(x, labels, ref[0::2], ref[1::2], "ce") if step <= 3 else (None, None, None)
             if ref_grads is not None:
@@ -108,13 +147,16 @@ def test_classifier_training_tracks_the_checker_for_20_steps(ctx, oracle, engine
                 # a relative gradient error e moves a parameter by about lr * e
                 # Adam divides by sqrt(vhat) + eps, so a gradient entry near zero turns an absolute
                 # gradient error of 1e-8 into a visible fraction of lr: no entry can move further
-                # than 2 * lr per step, and the mean drift stays at rounding level
+                # than 2 * lr per step, and the mean drift stays at rounding level (on the tensor-core
+                # engine a hidden unit gated the other way than in the checker moves its own bias and
+                # weights visibly, so only the looser mean holds there; the tight checks of that engine
+                # are the backward-on-own-gates test above and the bit-exact optimizer tests)
                 for got, want in zip(model.parameters(), ref):
                     drift = np.abs(got - want)
                     if engine == 1:
                         assert drift.max() <= 1e-3 * 2e-2, (step, drift.max())
-                    assert drift.max() <= 2e-3 * step and drift.mean() <= 2e-6 * step, (step, drift.max(), drift.mean())
-                assert abs(device_loss - float(ref_loss)) <= 1e-4 * abs(float(ref_loss))
+                    assert drift.max() <= 2e-3 * step and drift.mean() <= (2e-6 if engine == 1 else 1e-4) * step, (step, drift.max(), drift.mean())
+                assert abs(device_loss - float(ref_loss)) <= (1e-4 if engine == 1 else 1e-3) * abs(float(ref_loss))
         assert model.optimizer_steps() == 20
         model.close()
     finally:
