@@ -7,7 +7,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-LIB_DIR = os.path.join(HERE, "lib")
+LIB_DIR = os.path.join(HERE, os.environ.get("SYNAPTIK_LIB_DIR", "lib"))
 LIB_PATH = os.path.join(LIB_DIR, "libsynaptik_cuda.so")
 SOURCES = ["program.cpp", "lowering.cpp", "kernels_rowwise.cu", "kernels_gemm.cu", "kernels_skinny.cu", "runtime.cu"]
 HEADERS = ["program.hpp", "lowering.hpp", "kernels.hpp", os.path.join("..", "..", "include", "synaptik_cuda.h")]
@@ -24,6 +24,7 @@ def _nvcc() -> str:
 
 def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(LIB_DIR, exist_ok=True)
+    extra = os.environ.get("SYNAPTIK_NVCC_EXTRA", "").split()
     inputs = [os.path.join(CSRC, s) for s in SOURCES + HEADERS]
     newest = max(os.path.getmtime(p) for p in inputs)
     objects = []
@@ -32,7 +33,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         obj = os.path.join(LIB_DIR, os.path.splitext(source)[0] + ".o")
         objects.append(obj)
         if force or not os.path.exists(obj) or os.path.getmtime(obj) < newest:
-            cmd = [_nvcc(), *NVCC_FLAGS, "-x", "cu", "-c", os.path.join(CSRC, source), "-o", obj]
+            cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-x", "cu", "-c", os.path.join(CSRC, source), "-o", obj]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             procs.append((source, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

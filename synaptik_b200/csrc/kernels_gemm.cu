@@ -162,13 +162,18 @@ __global__ void __launch_bounds__(256) split_transposed_kernel(const float *__re
 // tcgen05 3xTF32 GEMM.
 // ------------------------------------------------------------------------------------------------
 constexpr int BM = 128;             // rows of P per tile = UMMA M = tensor-memory lanes
-constexpr int BK = 32;              // 32 floats = 128 bytes = one swizzle row
+#ifndef SYN_GEMM_BK
+#define SYN_GEMM_BK 32
+#endif
+constexpr int BK = SYN_GEMM_BK;     // floats per k-block: 32 (128-byte swizzle rows) or 16 (64-byte swizzle rows, twice the stages)
+constexpr int KPAD = 32;            // planes are padded to a multiple of 32 columns whatever BK is
+static_assert(BK == 32 || BK == 16, "k-block must be one 128-byte or one 64-byte swizzle row");
 constexpr int UMMA_K = 8;           // kind::tf32 contracts 8 elements (32 bytes) per instruction
 constexpr int GEMM_THREADS = 256;   // warp 0 TMA producer, warp 1 MMA issuer + tensor-memory owner, warps 4-7 epilogue
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // every device-side wait gives up after two seconds
 
 template <int BN> struct TileConfig {
-    static constexpr int kStages = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
+    static constexpr int kStages = (BN == 256 ? 2 : (BN == 128 ? 3 : 4)) * (32 / BK);
     static constexpr int kABytes = BM * BK * 4;            // one plane of P
     static constexpr int kBBytes = BN * BK * 4;            // one plane of Q
     static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
@@ -218,7 +223,9 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
 // layout type 2 (SWIZZLE_128B).  The leading-dimension offset is not used for swizzled K-major tiles
 // and carries the canonical value 1.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    return (uint64_t)((smem_addr & 0x3ffffu) >> 4) | (1ull << 16) | ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
+    // stride between 8-row groups = 8 * row bytes; layout type 2 = SWIZZLE_128B, 4 = SWIZZLE_64B
+    return (uint64_t)((smem_addr & 0x3ffffu) >> 4) | (1ull << 16) | ((uint64_t)((8u * BK * 4u) >> 4) << 32) | (1ull << 46)
+           | ((uint64_t)(BK == 32 ? 2 : 4) << 61);
 }
 // Instruction descriptor: FP32 accumulate, TF32 x TF32, both operands K-major, M = 128, N = BN.
 template <int BN> __device__ __forceinline__ uint32_t umma_idesc() {
@@ -680,7 +687,7 @@ bool make_plane_map(CUtensorMap *map, const float *plane, int64_t rows, int64_t 
     cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
     cuuint32_t elem[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)plane, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+              BK == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 }  // namespace
@@ -694,7 +701,7 @@ cudaError_t gemm_exact(cudaStream_t s, int64_t m, int64_t n, int64_t k, const fl
     return cudaGetLastError();
 }
 
-int64_t padded_k(int64_t k) { return (k + BK - 1) / BK * BK; }
+int64_t padded_k(int64_t k) { return (k + KPAD - 1) / KPAD * KPAD; }
 
 cudaError_t split_planes(cudaStream_t s, const float *src, int64_t rows, int64_t cols, int64_t rs, int64_t cs,
                          float *hi, float *lo, int64_t cp) {
@@ -740,8 +747,8 @@ TensorCoreGemm *tc_gemm_prepare(const float *p_hi, const float *p_lo, const floa
     // Partial-sum length.  The epilogue warps that add the partials also write the finished tile, and
     // the tensor core can run only two partials ahead of them, so short partials stall it at every
     // tile end unless the tile's main loop is very long (the weight gradients, K = batch).  Measured on
-    // the 65536 x 4096 x 4096 layers: partials of 4 k-blocks cost 17 % of the step, 16 k-blocks nothing.
-    g->chunk_kb = g->k_blocks >= 256 ? 8 : 16;
+    // the 65536 x 4096 x 4096 layers: partials of 128 contraction steps cost 17 % of the step, 512 nothing.
+    g->chunk_kb = (g->k_blocks * BK >= 8192 ? 256 : 512) / BK;
     if (forced_chunk_kb() > 0) g->chunk_kb = forced_chunk_kb();
     // tile width: the widest tile has the best operand reuse, but a persistent grid pays for the last
     // partial wave; take the width with the least (waves x width), narrower tiles handicapped a little
