@@ -69,7 +69,9 @@ SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_release(void *context);
  * epilogue (default 1; only used while "gemm_promote" is 0).  "gemm_promote": 1 (default) = the
  * tensor-core GEMM keeps only short partial sums (256 or 512 contraction steps) in tensor memory and
  * adds them into round-to-nearest FP32 register sums; 0 = one tensor-memory accumulator over the
- * whole contraction (faster epilogue, error grows with K).  Unknown names return
+ * whole contraction (faster epilogue, error grows with K).  "gemm_pair": 1 (default) = products with
+ * at least 256 rows use two-SM tiles (clusters of two blocks, tcgen05 cta_group::2); 0 = one-SM tiles
+ * only.  Unknown names return
  * INVALID_ARGUMENT. */
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_set_option(void *context, const char *name, int64_t value);
 /* Blocks until all work issued on the context has finished. */

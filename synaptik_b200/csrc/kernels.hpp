@@ -94,11 +94,14 @@ cudaError_t gemm_narrow_reduce(cudaStream_t s, int64_t wide, int64_t n, int64_t 
 // matrix (element strides rs, cs; one of them 1) into two dense [rows, cols_padded] planes whose
 // padding columns are zero.  gemm_tf32x3 then computes D[m,n] = P[m,k] . Q[n,k]^T from the planes.
 int64_t padded_k(int64_t k);
+// Row pitch (floats) of a plane with k_padded columns: a pitch that is a multiple of 2 KB gets one more
+// 128-byte line so that the rows of a tile do not all fall on the same L2 sets.
+int64_t plane_pitch(int64_t k_padded);
 cudaError_t split_planes(cudaStream_t s, const float *src, int64_t rows, int64_t cols, int64_t rs, int64_t cs,
                          float *hi, float *lo, int64_t cols_padded);
 struct TensorCoreGemm;       // opaque: tensor maps and launch geometry prepared once per plan step
 TensorCoreGemm *tc_gemm_prepare(const float *p_hi, const float *p_lo, const float *q_hi, const float *q_lo,
-                                int64_t m, int64_t n, int64_t k_padded, int sm_count, int promote, int *status);
+                                int64_t m, int64_t n, int64_t k_padded, int64_t pitch, int sm_count, int promote, int *status);
 void tc_gemm_release(TensorCoreGemm *g);
 cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, int64_t ldd, const GemmEpilogue &ep, int *error_word);
 

@@ -661,6 +661,238 @@ __global__ void __launch_bounds__(PROMOTED_THREADS, 1) gemm_tf32x3_promoted_kern
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Two-SM variant (cta_group::2).  A cluster of two blocks works on one 256 x BN tile: each block
+// loads its own 128 rows of P and its own half (BN / 2 rows) of Q, the even block issues one
+// tcgen05.mma.cta_group::2 (M = 256) per step that reads both blocks' shared memory, and each block
+// keeps the accumulator rows of its 128 result rows in its own tensor memory.  Per SM this halves
+// the Q bytes that TMA writes and the tensor core reads from shared memory, which is what bounds the
+// one-SM kernel (12 KB of operands per 128-clock MMA plus the refill is more than 128 B/clock).
+// Partial sums are promoted to FP32 register sums exactly as in the kernel above.
+// Barriers: full[s] lives in the even block and counts the bytes of both blocks' loads; empty[s] and
+// acc_full[b] exist in both blocks and are signalled by two tcgen05.commit of the even block;
+// acc_empty[b] lives in the even block and is signalled by the epilogue threads of both.
+// ------------------------------------------------------------------------------------------------
+template <int BN> struct PairConfig {
+    static constexpr int kStages = BN == 256 ? 3 : 4;
+    static constexpr int kABytes = BM * BK * 4;                // one plane of this block's 128 rows of P
+    static constexpr int kBBytes = (BN / 2) * BK * 4;          // one plane of this block's half of Q
+    static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
+    static constexpr int kTmemCols = 2 * BN;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_addr), "r"(rank));
+    return out;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const uint64_t start = global_timer();
+    for (uint32_t spin = 0;; spin++) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if ((spin & 63u) == 63u) {
+            if (*abort_flag) return false;
+            if (global_timer() - start > WAIT_LIMIT_NS) { *abort_flag = 1; return false; }
+        }
+    }
+}
+// TMA load of the two-SM form: the completion bytes may be counted on a barrier of the partner block.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t cluster_bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void umma_tf32_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+template <int BN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1) gemm_tf32x3_pair_kernel(
+        const __grid_constant__ CUtensorMap map_p_hi, const __grid_constant__ CUtensorMap map_p_lo,
+        const __grid_constant__ CUtensorMap map_q_hi, const __grid_constant__ CUtensorMap map_q_lo, TcParams prm) {
+    using Cfg = PairConfig<BN>;
+    constexpr int S = Cfg::kStages;
+    constexpr int CPT = BN / 2;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S * Cfg::kStageBytes);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * S + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const uint32_t bar_base = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
+    auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * S + a); };
+    auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * S + 2 + a); };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), 512); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {        // the same warp of both blocks allocates the pair's tensor memory together
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)Cfg::kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();     // the partner's barriers are initialised before anything signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int total_tiles = prm.tiles_m * prm.tiles_n;      // tiles of 256 x BN
+    const int kb_count = prm.k_blocks;
+    const int CHUNK_KB = prm.chunk_kb;
+    const uint32_t smem_base = smem_u32(smem);
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+    if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
+                const int m0 = (tile / prm.tiles_n) * (2 * BM) + (int)rank * BM;
+                const int n0 = (tile % prm.tiles_n) * BN + (int)rank * (BN / 2);
+                for (int kb = 0; kb < kb_count; kb++) {
+                    if (!mbar_wait_cluster(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t sa = smem_base + stage * Cfg::kStageBytes;
+                    const uint32_t leader_full = map_to_rank(full_bar(stage), 0);
+                    if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * Cfg::kStageBytes);
+                    tma_load_2d_pair(sa, &map_p_hi, leader_full, kb * BK, m0);
+                    tma_load_2d_pair(sa + Cfg::kABytes, &map_p_lo, leader_full, kb * BK, m0);
+                    tma_load_2d_pair(sa + 2 * Cfg::kABytes, &map_q_hi, leader_full, kb * BK, n0);
+                    tma_load_2d_pair(sa + 2 * Cfg::kABytes + Cfg::kBBytes, &map_q_lo, leader_full, kb * BK, n0);
+                    if (++stage == S) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1 && rank == 0) {
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+            int stage = 0; uint32_t phase = 0;
+            uint32_t partial = 0;
+            bool ok = true;
+            for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
+                for (int kb0 = 0; kb0 < kb_count && ok; kb0 += CHUNK_KB, partial++) {
+                    const int buf = partial & 1;
+                    if (!mbar_wait_cluster(acc_empty_bar(buf), ((partial >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                    const int kb1 = kb0 + CHUNK_KB < kb_count ? kb0 + CHUNK_KB : kb_count;
+                    for (int kb = kb0; kb < kb1; kb++) {
+                        if (!mbar_wait_cluster(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint32_t sa = smem_base + stage * Cfg::kStageBytes;
+                        const uint32_t p_hi = sa, p_lo = sa + Cfg::kABytes, q_hi = sa + 2 * Cfg::kABytes, q_lo = q_hi + Cfg::kBBytes;
+#pragma unroll
+                        for (int k4 = 0; k4 < BK / UMMA_K; k4++) {
+                            const uint32_t off = k4 * UMMA_K * 4;
+                            umma_tf32_pair(tmem_d, umma_desc(p_lo + off), umma_desc(q_hi + off), idesc, (kb != kb0 || k4 != 0) ? 1u : 0u);
+                            umma_tf32_pair(tmem_d, umma_desc(p_hi + off), umma_desc(q_lo + off), idesc, 1u);
+                            umma_tf32_pair(tmem_d, umma_desc(p_hi + off), umma_desc(q_hi + off), idesc, 1u);
+                        }
+                        umma_commit_pair(empty_bar(stage));                      // this block's producer
+                        umma_commit_pair(map_to_rank(empty_bar(stage), 1));      // the partner's producer
+                        if (++stage == S) { stage = 0; phase ^= 1u; }
+                    }
+                    if (ok) {
+                        umma_commit_pair(acc_full_bar(buf));
+                        umma_commit_pair(map_to_rank(acc_full_bar(buf), 1));
+                    }
+                }
+            }
+        }
+    }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+        const int quarter = warp & 3;
+        const int half = (warp - 4) >> 2;
+        uint32_t partial = 0;
+        bool ok = true;
+        const bool vec_ok = (prm.ldd & 3) == 0 && ((uintptr_t)prm.d & 15) == 0
+                            && (!prm.second || ((uintptr_t)prm.second & 15) == 0) && (!prm.gate || ((uintptr_t)prm.gate & 15) == 0);
+        for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
+            const int m0 = (tile / prm.tiles_n) * (2 * BM) + (int)rank * BM, n0 = (tile % prm.tiles_n) * BN;
+            float sum[CPT];
+            for (int kb0 = 0; kb0 < kb_count; kb0 += CHUNK_KB, partial++) {
+                const int buf = partial & 1;
+                ok = mbar_wait_cluster(acc_full_bar(buf), (partial >> 1) & 1u, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * CPT);
+                if (kb0 == 0) {
+#pragma unroll
+                    for (int s16 = 0; s16 < CPT / 16; s16++) {
+                        float t[16];
+                        tmem_load16(taddr + (uint32_t)(s16 * 16), t);
+#pragma unroll
+                        for (int i = 0; i < 16; i++) sum[s16 * 16 + i] = t[i];
+                    }
+                } else {
+#pragma unroll
+                    for (int s16 = 0; s16 < CPT / 16; s16++) {
+                        float t[16];
+                        tmem_load16(taddr + (uint32_t)(s16 * 16), t);
+#pragma unroll
+                        for (int i = 0; i < 16; i++) sum[s16 * 16 + i] = __fadd_rn(sum[s16 * 16 + i], t[i]);
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive_cluster(map_to_rank(acc_empty_bar(buf), 0));
+            }
+            if (!ok) break;
+            const int row = m0 + quarter * 32 + lane;
+            const bool row_ok = row < prm.m;
+            const bool row_pad = !row_ok && prm.thi != nullptr && row < prm.m_pad;
+            if (row_ok || row_pad) {
+#pragma unroll
+                for (int g = 0; g < CPT / 4; g++) {
+                    const int col = n0 + half * CPT + g * 4;
+                    if ((col & ~31) < prm.n)
+                        epilogue_emit4(prm, row, row_ok, col, sum[g * 4], sum[g * 4 + 1], sum[g * 4 + 2], sum[g * 4 + 3], vec_ok);
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    __syncwarp();
+    cluster_sync_all();     // neither block frees tensor memory or leaves while the partner may still signal it
+    if (threadIdx.x == 0 && *abort_flag) atomicOr(prm.error_word, ERR_WAIT_TIMEOUT);
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::kTmemCols) : "memory");
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -679,11 +911,11 @@ EncodeTiledFn encode_fn() {
 }
 
 // 2-D map over a dense [rows, kp] FP32 plane: box = 32 floats (one 128-byte swizzle row) x box_rows.
-bool make_plane_map(CUtensorMap *map, const float *plane, int64_t rows, int64_t kp, int box_rows) {
+bool make_plane_map(CUtensorMap *map, const float *plane, int64_t rows, int64_t kp, int64_t pitch, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {(cuuint64_t)kp, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)kp * 4};
+    cuuint64_t strides[1] = {(cuuint64_t)pitch * 4};
     cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
     cuuint32_t elem[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)plane, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -702,6 +934,7 @@ cudaError_t gemm_exact(cudaStream_t s, int64_t m, int64_t n, int64_t k, const fl
 }
 
 int64_t padded_k(int64_t k) { return (k + KPAD - 1) / KPAD * KPAD; }
+int64_t plane_pitch(int64_t k_padded) { return k_padded % 512 == 0 ? k_padded + 32 : k_padded; }
 
 cudaError_t split_planes(cudaStream_t s, const float *src, int64_t rows, int64_t cols, int64_t rs, int64_t cs,
                          float *hi, float *lo, int64_t cp) {
@@ -734,11 +967,13 @@ static int forced_chunk_kb() {
 struct TensorCoreGemm {
     CUtensorMap p_hi, p_lo, q_hi, q_lo;
     int m, n, k_blocks, bn, grid;
-    int promote, chunk_kb;
+    int promote, chunk_kb, pair;
 };
 
 TensorCoreGemm *tc_gemm_prepare(const float *p_hi, const float *p_lo, const float *q_hi, const float *q_lo,
-                                int64_t m, int64_t n, int64_t k_padded, int sm_count, int promote, int *status) {
+                                int64_t m, int64_t n, int64_t k_padded, int64_t pitch, int sm_count, int promote, int *status) {
+    const int pair_requested = promote >> 1;      // bit 1 of the mode: two-SM tiles
+    promote &= 1;
     *status = OK;
     if (m < 1 || n < 1 || k_padded < BK || k_padded % BK || m > (1ll << 30) || n > (1ll << 30)) { *status = UNSUPPORTED_SHAPE; return nullptr; }
     TensorCoreGemm *g = new TensorCoreGemm();
@@ -763,8 +998,24 @@ TensorCoreGemm *tc_gemm_prepare(const float *p_hi, const float *p_lo, const floa
     if (forced_tile_n() == 64 || forced_tile_n() == 128 || forced_tile_n() == 256) g->bn = forced_tile_n();
     int64_t tiles = ((m + BM - 1) / BM) * ((n + g->bn - 1) / g->bn);
     g->grid = (int)(tiles < sm_count ? tiles : sm_count);
-    bool ok = make_plane_map(&g->p_hi, p_hi, m, k_padded, BM) && make_plane_map(&g->p_lo, p_lo, m, k_padded, BM)
-              && make_plane_map(&g->q_hi, q_hi, n, k_padded, g->bn) && make_plane_map(&g->q_lo, q_lo, n, k_padded, g->bn);
+    // two-SM tiles (256 x 256 or 256 x 128) when the shape fills them
+    g->pair = pair_requested && m >= 2 * BM && n >= 96 && sm_count >= 2;
+    if (g->pair) {
+        auto pair_cost = [&](int bn) {
+            int64_t t = ((m + 2 * BM - 1) / (2 * BM)) * ((n + bn - 1) / bn);
+            int64_t waves = (t + sm_count / 2 - 1) / (sm_count / 2);
+            return (double)waves * bn * (bn == 256 ? 1.0 : 1.25);   // 128-wide pair tiles are shared-memory bound again
+        };
+        g->bn = (n >= 192 && pair_cost(256) <= pair_cost(128)) ? 256 : 128;
+        if (forced_tile_n() == 128 || forced_tile_n() == 256) g->bn = forced_tile_n();
+        int64_t pair_tiles = ((m + 2 * BM - 1) / (2 * BM)) * ((n + g->bn - 1) / g->bn);
+        int64_t pairs = sm_count / 2;
+        g->grid = (int)(2 * (pair_tiles < pairs ? pair_tiles : pairs));
+        g->promote = 1;
+    }
+    const int q_box = g->pair ? g->bn / 2 : g->bn;
+    bool ok = make_plane_map(&g->p_hi, p_hi, m, k_padded, pitch, BM) && make_plane_map(&g->p_lo, p_lo, m, k_padded, pitch, BM)
+              && make_plane_map(&g->q_hi, q_hi, n, k_padded, pitch, q_box) && make_plane_map(&g->q_lo, q_lo, n, k_padded, pitch, q_box);
     if (!ok) { delete g; *status = KERNEL_COMPILATION_FAILED; return nullptr; }
     return g;
 }
@@ -777,7 +1028,18 @@ static cudaError_t launch_tc(cudaStream_t s, const TensorCoreGemm *g, const TcPa
     // a per-device attribute: set on every launch so each GPU of the process has it
     cudaError_t e = cudaFuncSetAttribute(gemm_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
-    if (g->promote) {
+    if (g->pair) {
+        if constexpr (BN >= 128) {
+            using Pair = PairConfig<BN>;
+            cudaFuncAttributes attr;
+            e = cudaFuncGetAttributes(&attr, gemm_tf32x3_pair_kernel<BN>);
+            if (e != cudaSuccess) return e;
+            if (attr.numRegs * PROMOTED_THREADS < 128 * 72 + 256 * 216) return cudaErrorLaunchOutOfResources;
+            e = cudaFuncSetAttribute(gemm_tf32x3_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Pair::kSmemBytes);
+            if (e != cudaSuccess) return e;
+            gemm_tf32x3_pair_kernel<BN><<<g->grid, PROMOTED_THREADS, Pair::kSmemBytes, s>>>(g->p_hi, g->p_lo, g->q_hi, g->q_lo, prm);
+        } else return cudaErrorInvalidValue;
+    } else if (g->promote) {
         // the kernel redistributes registers between its warpgroups (72 and 216 per thread); that only
         // terminates when the launch allocation covers the sum, so check it instead of trusting it
         cudaFuncAttributes attr;
@@ -798,7 +1060,8 @@ cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, in
     prm.nhi = ep.plane_hi; prm.nlo = ep.plane_lo; prm.nld = ep.plane_ld;
     prm.thi = ep.tplane_hi; prm.tlo = ep.tplane_lo; prm.tld = ep.tplane_ld; prm.m_pad = (int)ep.tplane_ld;
     prm.d = d; prm.ldd = ldd; prm.m = g->m; prm.n = g->n; prm.k_blocks = g->k_blocks;
-    prm.tiles_m = (g->m + BM - 1) / BM; prm.tiles_n = (g->n + g->bn - 1) / g->bn;
+    const int tile_m = g->pair ? 2 * BM : BM;
+    prm.tiles_m = (g->m + tile_m - 1) / tile_m; prm.tiles_n = (g->n + g->bn - 1) / g->bn;
     prm.chunk_kb = g->chunk_kb;
     prm.bias = ep.bias; prm.gate = ep.gate; prm.second = ep.second; prm.relu = ep.relu; prm.error_word = error_word;
     if (g->bn == 256) return launch_tc<256>(s, g, prm);

@@ -38,6 +38,7 @@ struct Context {
     int time_steps = 0;
     int fused_planes = 1;
     int gemm_promote = 1;
+    int gemm_pair = 1;
     cudaEvent_t timer_start = nullptr, timer_stop = nullptr;
     std::mutex mutex;
 };
@@ -89,7 +90,7 @@ struct Comm {
     int world = 1, rank = 0;
 };
 
-struct Planes { float *hi = nullptr, *lo = nullptr; int64_t rows = 0, kp = 0; int last_run = -1; };
+struct Planes { float *hi = nullptr, *lo = nullptr; int64_t rows = 0, kp = 0, pitch = 0; int last_run = -1; };
 
 // Identity of an operand's planes: the storage it views and how the plane rows / columns walk it.
 // Two program values that view the same storage the same way (a value and PERMUTE of PERMUTE of it)
@@ -256,9 +257,9 @@ int32_t prepare_executable(Executable *x) {
         auto it = x->plane_index.find(key);
         if (it != x->plane_index.end()) return it->second;
         Planes p;
-        p.rows = rows; p.kp = kern::padded_k(k);
+        p.rows = rows; p.kp = kern::padded_k(k); p.pitch = kern::plane_pitch(p.kp);
         void *hi, *lo;
-        if (!alloc((uint64_t)rows * p.kp * 4, &hi) || !alloc((uint64_t)rows * p.kp * 4, &lo)) return -1;
+        if (!alloc((uint64_t)rows * p.pitch * 4, &hi) || !alloc((uint64_t)rows * p.pitch * 4, &lo)) return -1;
         p.hi = (float *)hi; p.lo = (float *)lo;
         x->planes.push_back(p);
         x->plane_index[key] = (int)x->planes.size() - 1;
@@ -277,7 +278,7 @@ int32_t prepare_executable(Executable *x) {
             se.planes_q = se.swapped ? pa : pb;
             const Planes &P = x->planes[se.planes_p], &Q = x->planes[se.planes_q];
             int status = OK;
-            se.tc = kern::tc_gemm_prepare(P.hi, P.lo, Q.hi, Q.lo, P.rows, Q.rows, P.kp, ctx->sm_count, ctx->gemm_promote, &status);
+            se.tc = kern::tc_gemm_prepare(P.hi, P.lo, Q.hi, Q.lo, P.rows, Q.rows, P.kp, P.pitch, ctx->sm_count, ctx->gemm_promote | (ctx->gemm_pair << 1), &status);
             if (!se.tc) return status;
         } else if (st.kind == StepKind::GEMM && st.engine == GemmEngine::NARROW_REDUCE) {
             void *p; if (!alloc((uint64_t)kern::narrow_reduce_partial_floats(st.m, st.n, st.k) * 4, &p)) return ALLOCATION_FAILED;
@@ -398,7 +399,7 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                         const View &v = plan.views[value];
                         int64_t rs = orientation == 0 ? v.strides[0] : v.strides[1], cs = orientation == 0 ? v.strides[1] : v.strides[0];
                         int64_t cols = orientation == 0 ? v.shape[1] : v.shape[0];
-                        LAUNCH(kern::split_planes(s, (const float *)ptr(value), pl.rows, cols, rs, cs, pl.hi, pl.lo, pl.kp));
+                        LAUNCH(kern::split_planes(s, (const float *)ptr(value), pl.rows, cols, rs, cs, pl.hi, pl.lo, pl.pitch));
                         pl.last_run = x->run_counter;
                         return OK;
                     };
@@ -408,11 +409,11 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                     int64_t ldd = se.swapped ? c.strides[1] : c.strides[0];
                     if (se.emit_planes >= 0) {
                         Planes &pl = x->planes[se.emit_planes];
-                        ep.plane_hi = pl.hi; ep.plane_lo = pl.lo; ep.plane_ld = pl.kp; pl.last_run = x->run_counter;
+                        ep.plane_hi = pl.hi; ep.plane_lo = pl.lo; ep.plane_ld = pl.pitch; pl.last_run = x->run_counter;
                     }
                     if (se.emit_tplanes >= 0) {
                         Planes &pl = x->planes[se.emit_tplanes];
-                        ep.tplane_hi = pl.hi; ep.tplane_lo = pl.lo; ep.tplane_ld = pl.kp; pl.last_run = x->run_counter;
+                        ep.tplane_hi = pl.hi; ep.tplane_lo = pl.lo; ep.tplane_ld = pl.pitch; pl.last_run = x->run_counter;
                     }
                     if (time_steps) cudaEventRecord(x->step_events[2 * i], s);
                     LAUNCH(kern::tc_gemm_launch(s, se.tc, (float *)ptr(st.out), ldd, ep, ctx->error_dev));
@@ -560,6 +561,7 @@ int32_t synaptik_cuda_context_create(int32_t device_ordinal, void **out_context)
     Context *ctx = new Context();
     ctx->device = device_ordinal;
     ctx->sm_count = prop.multiProcessorCount;
+    if (const char *e = getenv("SYNAPTIK_CUDA_GEMM_PAIR")) ctx->gemm_pair = atoi(e) != 0;      // test hook for the default
     if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess
         || cudaStreamCreateWithFlags(&ctx->comm_stream, cudaStreamNonBlocking) != cudaSuccess) { cudaGetLastError(); delete ctx; return NO_STREAM; }
     if (cudaMalloc(&ctx->error_dev, sizeof(int)) != cudaSuccess || cudaMallocHost(&ctx->error_host, sizeof(int)) != cudaSuccess
@@ -589,6 +591,7 @@ int32_t synaptik_cuda_context_set_option(void *context, const char *name, int64_
     Context *ctx = as<Context>(context, TAG_CONTEXT);
     if (!ctx || !name) return INVALID_ARGUMENT;
     if (!strcmp(name, "gemm_engine")) { if (value < 0 || value > 2) return INVALID_ARGUMENT; ctx->gemm_engine = (int)value; return OK; }
+    if (!strcmp(name, "gemm_pair")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->gemm_pair = (int)value; return OK; }
     if (!strcmp(name, "gemm_promote")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->gemm_promote = (int)value; return OK; }
     if (!strcmp(name, "fused_planes")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->fused_planes = (int)value; return OK; }
     if (!strcmp(name, "time_steps")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->time_steps = (int)value; return OK; }
