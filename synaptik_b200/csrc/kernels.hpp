@@ -64,9 +64,8 @@ struct GemmEpilogue {
     const float *gate = nullptr;        // dense [m,n]: out = gate > 0 ? z : 0
     float *second = nullptr;            // dense [m,n]: when set, `out` receives z and `second` relu(z)
     // tensor-core kernel only: also write the hi/lo operand planes of the result (the activation when
-    // relu / second is set) for later GEMMs, [m, plane_ld] and / or transposed [n, tplane_ld]
+    // relu / second is set) for later GEMMs, [m, plane_ld]
     float *plane_hi = nullptr, *plane_lo = nullptr; int64_t plane_ld = 0;
-    float *tplane_hi = nullptr, *tplane_lo = nullptr; int64_t tplane_ld = 0;
 };
 // Exact CUDA-core product: every output cell is the reference's ascending-k chain of separately
 // rounded multiply and add (CpuMatmulReferenceKernel.java:71-93), operands and result strided.
@@ -90,18 +89,23 @@ int64_t narrow_reduce_partial_floats(int64_t wide, int64_t n, int64_t depth);
 cudaError_t gemm_narrow_reduce(cudaStream_t s, int64_t wide, int64_t n, int64_t depth, const float *src, int64_t lds,
                                const float *t, int64_t ldt, float *partial, float *out, int64_t stride_wide, int64_t stride_narrow);
 
-// Tensor-core path.  split_planes writes hi = tf32(x) and lo = tf32(x - hi) of a logical [rows, cols]
-// matrix (element strides rs, cs; one of them 1) into two dense [rows, cols_padded] planes whose
-// padding columns are zero.  gemm_tf32x3 then computes D[m,n] = P[m,k] . Q[n,k]^T from the planes.
+// Tensor-core path.  split_planes writes hi = tf32(x) and lo = tf32(x - hi) of a row-major
+// [rows, cols] matrix (row stride rs, unit column stride) into two [rows, pitch] planes whose padding
+// columns are zero.  A GEMM operand with `extent` rows (m or n) and contraction length k is given
+// either as K-major planes [extent, padded_k(k)] or, when the operand's storage is contiguous along
+// its rows instead, as MN-major planes [k, padded_k(extent)]; the kernel reads both forms directly,
+// so no operand is ever transposed in memory.  The product is D[m,n] = sum_k P[m,k] * Q[n,k].
 int64_t padded_k(int64_t k);
 // Row pitch (floats) of a plane with k_padded columns: a pitch that is a multiple of 2 KB gets one more
 // 128-byte line so that the rows of a tile do not all fall on the same L2 sets.
 int64_t plane_pitch(int64_t k_padded);
-cudaError_t split_planes(cudaStream_t s, const float *src, int64_t rows, int64_t cols, int64_t rs, int64_t cs,
-                         float *hi, float *lo, int64_t cols_padded);
+cudaError_t split_planes(cudaStream_t s, const float *src, int64_t rows, int64_t cols, int64_t rs,
+                         float *hi, float *lo, int64_t pitch);
+struct TcOperand { const float *hi = nullptr, *lo = nullptr; int64_t pitch = 0; int mn_major = 0; };
 struct TensorCoreGemm;       // opaque: tensor maps and launch geometry prepared once per plan step
-TensorCoreGemm *tc_gemm_prepare(const float *p_hi, const float *p_lo, const float *q_hi, const float *q_lo,
-                                int64_t m, int64_t n, int64_t k_padded, int64_t pitch, int sm_count, int promote, int *status);
+// mode: bit 0 = FP32 promotion of partial sums, bit 1 = two-SM tiles where the shape fills them
+TensorCoreGemm *tc_gemm_prepare(const TcOperand &p, const TcOperand &q, int64_t m, int64_t n, int64_t k,
+                                int sm_count, int mode, int *status);
 void tc_gemm_release(TensorCoreGemm *g);
 cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, int64_t ldd, const GemmEpilogue &ep, int *error_word);
 

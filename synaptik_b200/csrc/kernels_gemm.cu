@@ -130,50 +130,18 @@ __global__ void split_rows_kernel(const float *__restrict__ src, int64_t rows, i
     }
 }
 
-// Source element (r, c) lives at src[c * cs + r]: a transposing split through a padded 32x32 tile.
-__global__ void __launch_bounds__(256) split_transposed_kernel(const float *__restrict__ src, int64_t rows, int64_t cols, int64_t cs,
-                                                                float *hi, float *lo, int64_t cp) {
-    __shared__ float tile[32][33];
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    const int64_t tiles_c = cp >> 5, tiles_r = (rows + 31) >> 5, tiles = tiles_c * tiles_r;
-    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
-        const int64_t r0 = (t % tiles_r) << 5, c0 = (t / tiles_r) << 5;
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            int64_t c = c0 + ty + 8 * j, r = r0 + tx;
-            tile[ty + 8 * j][tx] = (c < cols && r < rows) ? src[c * cs + r] : 0.0f;
-        }
-        __syncthreads();
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            int64_t r = r0 + ty + 8 * j, c = c0 + tx;
-            if (r < rows) {
-                float h, l;
-                split_value(tile[tx][ty + 8 * j], h, l);
-                hi[r * cp + c] = h;
-                lo[r * cp + c] = l;
-            }
-        }
-        __syncthreads();
-    }
-}
-
 // ------------------------------------------------------------------------------------------------
 // tcgen05 3xTF32 GEMM.
 // ------------------------------------------------------------------------------------------------
 constexpr int BM = 128;             // rows of P per tile = UMMA M = tensor-memory lanes
-#ifndef SYN_GEMM_BK
-#define SYN_GEMM_BK 32
-#endif
-constexpr int BK = SYN_GEMM_BK;     // floats per k-block: 32 (128-byte swizzle rows) or 16 (64-byte swizzle rows, twice the stages)
-constexpr int KPAD = 32;            // planes are padded to a multiple of 32 columns whatever BK is
-static_assert(BK == 32 || BK == 16, "k-block must be one 128-byte or one 64-byte swizzle row");
+constexpr int BK = 32;              // floats per k-block: one 128-byte swizzle row
+constexpr int KPAD = 32;            // planes are padded to a multiple of 32 columns
 constexpr int UMMA_K = 8;           // kind::tf32 contracts 8 elements (32 bytes) per instruction
 constexpr int GEMM_THREADS = 256;   // warp 0 TMA producer, warp 1 MMA issuer + tensor-memory owner, warps 4-7 epilogue
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // every device-side wait gives up after two seconds
 
 template <int BN> struct TileConfig {
-    static constexpr int kStages = (BN == 256 ? 2 : (BN == 128 ? 3 : 4)) * (32 / BK);
+    static constexpr int kStages = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
     static constexpr int kABytes = BM * BK * 4;            // one plane of P
     static constexpr int kBBytes = BN * BK * 4;            // one plane of Q
     static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
@@ -218,18 +186,50 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
                  ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
 
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzled:
-// start address (>>4), stride between 8-row groups = 1024 bytes (>>4), descriptor version 1,
-// layout type 2 (SWIZZLE_128B).  The leading-dimension offset is not used for swizzled K-major tiles
-// and carries the canonical value 1.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    // stride between 8-row groups = 8 * row bytes; layout type 2 = SWIZZLE_128B, 4 = SWIZZLE_64B
-    return (uint64_t)((smem_addr & 0x3ffffu) >> 4) | (1ull << 16) | ((uint64_t)((8u * BK * 4u) >> 4) << 32) | (1ull << 46)
-           | ((uint64_t)(BK == 32 ? 2 : 4) << 61);
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z) : "memory");
 }
-// Instruction descriptor: FP32 accumulate, TF32 x TF32, both operands K-major, M = 128, N = BN.
-template <int BN> __device__ __forceinline__ uint32_t umma_idesc() {
-    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// One operand tile of k-block kb starting at operand row r0 (a multiple of 32).  K-major planes are
+// [rows, k]: a 2-D box at (k, row).  MN-major planes are [k, rows] seen through a 3-D map
+// (32 rows, k, rows / 32): a box at (0, k, row / 32), whose first coordinate is always 0.
+__device__ __forceinline__ void load_operand(uint32_t dst, const CUtensorMap *map, uint32_t bar, int kb, int r0, int mn_major) {
+    if (mn_major) tma_load_3d(dst, map, bar, 0, kb * BK, r0 >> 5);
+    else tma_load_2d(dst, map, bar, kb * BK, r0);
+}
+
+// Shared-memory matrix descriptors (descriptor version 1), two operand layouts.
+// K-major: the tile is [rows][32 floats of k], 128-byte swizzle (layout type 2); each 128-byte row
+//   holds one row's k-block, groups of 8 rows are 1024 bytes apart (stride offset); the leading offset
+//   is unused and carries 1.  One MMA (8 contraction steps) advances the start address by 32 bytes
+//   inside the swizzle row.
+// MN-major: the tile is [rows / 32][32 k][32 floats of rows]; each 128-byte row holds 32 consecutive
+//   rows of the operand at one k.  For 32-bit elements the tensor core reads this form only in the
+//   128-byte swizzle with 32-byte atoms (layout type 1; the plain 128-byte swizzle returns zeros,
+//   measured): the pattern repeats every 4 k, groups of 4 k are 512 bytes apart (stride offset) and the
+//   next 32 operand rows start 4096 bytes later (leading offset).  One MMA covers 8 k = two groups and
+//   advances the start address by 1024 bytes.  TMA writes the matching pattern with
+//   CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B.
+struct OperandForm { uint64_t fixed; uint32_t k8_step; };
+__device__ __forceinline__ OperandForm operand_form(int mn_major) {
+    OperandForm f;
+    if (mn_major) {
+        f.fixed = ((uint64_t)((BK * 128u) >> 4) << 16) | ((uint64_t)(512u >> 4) << 32) | (1ull << 46) | (1ull << 61);
+        f.k8_step = 1024u;
+    } else {
+        f.fixed = (1ull << 16) | ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
+        f.k8_step = (uint32_t)(UMMA_K * 4);
+    }
+    return f;
+}
+__device__ __forceinline__ uint64_t umma_desc(const OperandForm &f, uint32_t smem_addr) {
+    return f.fixed | (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+}
+// Instruction descriptor: FP32 accumulate, TF32 x TF32, M rows, N = BN columns, operand majors
+// (bit 15: P is MN-major, bit 16: Q is MN-major).
+__device__ __forceinline__ uint32_t umma_idesc(int rows, int bn, int p_mn, int q_mn) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(p_mn != 0) << 15) | ((uint32_t)(q_mn != 0) << 16)
+           | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(rows >> 4) << 24);
 }
 __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
@@ -263,7 +263,7 @@ struct TcParams {
     int tiles_m, tiles_n;
     const float *bias; const float *gate; float *second; int relu;
     float *nhi, *nlo; int64_t nld;          // optional [m, nld] hi/lo planes of the result
-    float *thi, *tlo; int64_t tld; int m_pad;   // optional transposed [n, tld] planes, tld = m_pad = m rounded up to 32
+    int p_mn, q_mn;                          // operand planes are MN-major ([k, rows]) instead of K-major ([rows, k])
     int chunk_kb;                            // promoted kernel: k-blocks per tensor-memory partial sum
     int *error_word;
 };
@@ -271,17 +271,14 @@ struct TcParams {
 
 // Finishes four adjacent result cells of one row: bias, ReLU-backward gate, activation, the stores
 // of the result (and of the second output), and the hi/lo operand planes when later GEMMs read this
-// result.  row_ok is false for the rows past m that only exist as zero padding of the transposed
-// planes.
-__device__ __forceinline__ void epilogue_emit4(const TcParams &prm, int row, bool row_ok, int col,
+// result.
+__device__ __forceinline__ void epilogue_emit4(const TcParams &prm, int row, int col,
                                                float z0, float z1, float z2, float z3, bool vec_ok) {
     float *drow = prm.d + (int64_t)row * prm.ldd;
     const int64_t dense = (int64_t)row * prm.n;
     float z[4] = {z0, z1, z2, z3};
     float y[4];                             // the value later GEMMs read: activation or (gated) result
-    if (!row_ok) {
-        y[0] = y[1] = y[2] = y[3] = 0.0f;
-    } else if (col + 3 < prm.n && vec_ok && (prm.n & 3) == 0) {
+    if (col + 3 < prm.n && vec_ok && (prm.n & 3) == 0) {
         if (prm.bias) { float4 bv = *reinterpret_cast<const float4 *>(prm.bias + col);
             z[0] = __fadd_rn(z[0], bv.x); z[1] = __fadd_rn(z[1], bv.y); z[2] = __fadd_rn(z[2], bv.z); z[3] = __fadd_rn(z[3], bv.w); }
         if (prm.gate) { float4 gv = *reinterpret_cast<const float4 *>(prm.gate + dense + col);
@@ -309,23 +306,14 @@ __device__ __forceinline__ void epilogue_emit4(const TcParams &prm, int row, boo
             }
         }
     }
-    if (prm.nhi || prm.thi) {
+    if (prm.nhi) {
         // operand planes for the GEMMs that read this result, written here instead of by a separate
         // split pass; columns past n and rows past m are zero padding
         float h[4], l[4];
 #pragma unroll
         for (int e = 0; e < 4; e++) split_value(y[e], h[e], l[e]);
-        if (prm.nhi && row_ok) {
-            *reinterpret_cast<float4 *>(prm.nhi + (int64_t)row * prm.nld + col) = make_float4(h[0], h[1], h[2], h[3]);
-            *reinterpret_cast<float4 *>(prm.nlo + (int64_t)row * prm.nld + col) = make_float4(l[0], l[1], l[2], l[3]);
-        }
-        if (prm.thi) {
-#pragma unroll
-            for (int e = 0; e < 4; e++) if (col + e < prm.n) {
-                prm.thi[(int64_t)(col + e) * prm.tld + row] = h[e];       // lanes hold consecutive rows: coalesced
-                prm.tlo[(int64_t)(col + e) * prm.tld + row] = l[e];
-            }
-        }
+        *reinterpret_cast<float4 *>(prm.nhi + (int64_t)row * prm.nld + col) = make_float4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<float4 *>(prm.nlo + (int64_t)row * prm.nld + col) = make_float4(l[0], l[1], l[2], l[3]);
     }
 }
 
@@ -384,10 +372,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tf32x3_kernel(
                     const uint32_t sa = smem_base + stage * Cfg::kStageBytes;
                     mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
                     armed[stage] = true; armed_phase[stage] = phase;
-                    tma_load_2d(sa, &map_p_hi, full_bar(stage), kb * BK, m0);
-                    tma_load_2d(sa + Cfg::kABytes, &map_p_lo, full_bar(stage), kb * BK, m0);
-                    tma_load_2d(sa + 2 * Cfg::kABytes, &map_q_hi, full_bar(stage), kb * BK, n0);
-                    tma_load_2d(sa + 2 * Cfg::kABytes + Cfg::kBBytes, &map_q_lo, full_bar(stage), kb * BK, n0);
+                    load_operand(sa, &map_p_hi, full_bar(stage), kb, m0, prm.p_mn);
+                    load_operand(sa + Cfg::kABytes, &map_p_lo, full_bar(stage), kb, m0, prm.p_mn);
+                    load_operand(sa + 2 * Cfg::kABytes, &map_q_hi, full_bar(stage), kb, n0, prm.q_mn);
+                    load_operand(sa + 2 * Cfg::kABytes + Cfg::kBBytes, &map_q_lo, full_bar(stage), kb, n0, prm.q_mn);
                     if (++stage == S) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -399,7 +387,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tf32x3_kernel(
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc<BN>();
+            const uint32_t idesc = umma_idesc(BM, BN, prm.p_mn, prm.q_mn);
+            const OperandForm pf = operand_form(prm.p_mn), qf = operand_form(prm.q_mn);
             int stage = 0; uint32_t phase = 0;
             int local = 0;
             bool ok = true;
@@ -415,11 +404,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tf32x3_kernel(
                     const uint32_t p_hi = sa, p_lo = sa + Cfg::kABytes, q_hi = sa + 2 * Cfg::kABytes, q_lo = q_hi + Cfg::kBBytes;
 #pragma unroll
                     for (int k4 = 0; k4 < BK / UMMA_K; k4++) {
-                        const uint32_t off = k4 * UMMA_K * 4;
+                        const uint32_t po = k4 * pf.k8_step, qo = k4 * qf.k8_step;
                         // small terms first, then the leading product
-                        umma_tf32(tmem_d, umma_desc(p_lo + off), umma_desc(q_hi + off), idesc, (kb | k4) != 0);
-                        umma_tf32(tmem_d, umma_desc(p_hi + off), umma_desc(q_lo + off), idesc, 1u);
-                        umma_tf32(tmem_d, umma_desc(p_hi + off), umma_desc(q_hi + off), idesc, 1u);
+                        umma_tf32(tmem_d, umma_desc(pf, p_lo + po), umma_desc(qf, q_hi + qo), idesc, (kb | k4) != 0);
+                        umma_tf32(tmem_d, umma_desc(pf, p_hi + po), umma_desc(qf, q_lo + qo), idesc, 1u);
+                        umma_tf32(tmem_d, umma_desc(pf, p_hi + po), umma_desc(qf, q_hi + qo), idesc, 1u);
                     }
                     umma_commit(empty_bar(stage));          // releases the stage once these MMAs have read it
                     if (++stage == S) { stage = 0; phase ^= 1u; }
@@ -449,11 +438,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tf32x3_kernel(
                 tmem_load32(taddr + (uint32_t)(chunk * 32), v);
                 const int col0 = n0 + chunk * 32;
                 const bool row_ok = row < prm.m;
-                const bool row_pad = !row_ok && prm.thi != nullptr && row < prm.m_pad;     // zero padding of the transposed planes
-                if ((row_ok || row_pad) && col0 < prm.n) {
+                if (row_ok && col0 < prm.n) {
 #pragma unroll
                     for (int q = 0; q < 8; q++)
-                        epilogue_emit4(prm, row, row_ok, col0 + q * 4, v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3], vec_ok);
+                        epilogue_emit4(prm, row, col0 + q * 4, v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3], vec_ok);
                 }
             }
             tc_fence_before();
@@ -554,10 +542,10 @@ __global__ void __launch_bounds__(PROMOTED_THREADS, 1) gemm_tf32x3_promoted_kern
                     const uint32_t sa = smem_base + stage * Cfg::kStageBytes;
                     mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
                     armed[stage] = true; armed_phase[stage] = phase;
-                    tma_load_2d(sa, &map_p_hi, full_bar(stage), kb * BK, m0);
-                    tma_load_2d(sa + Cfg::kABytes, &map_p_lo, full_bar(stage), kb * BK, m0);
-                    tma_load_2d(sa + 2 * Cfg::kABytes, &map_q_hi, full_bar(stage), kb * BK, n0);
-                    tma_load_2d(sa + 2 * Cfg::kABytes + Cfg::kBBytes, &map_q_lo, full_bar(stage), kb * BK, n0);
+                    load_operand(sa, &map_p_hi, full_bar(stage), kb, m0, prm.p_mn);
+                    load_operand(sa + Cfg::kABytes, &map_p_lo, full_bar(stage), kb, m0, prm.p_mn);
+                    load_operand(sa + 2 * Cfg::kABytes, &map_q_hi, full_bar(stage), kb, n0, prm.q_mn);
+                    load_operand(sa + 2 * Cfg::kABytes + Cfg::kBBytes, &map_q_lo, full_bar(stage), kb, n0, prm.q_mn);
                     if (++stage == S) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -567,7 +555,8 @@ __global__ void __launch_bounds__(PROMOTED_THREADS, 1) gemm_tf32x3_promoted_kern
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc<BN>();
+            const uint32_t idesc = umma_idesc(BM, BN, prm.p_mn, prm.q_mn);
+            const OperandForm pf = operand_form(prm.p_mn), qf = operand_form(prm.q_mn);
             int stage = 0; uint32_t phase = 0;
             uint32_t partial = 0;               // running count of partial sums: selects the tensor-memory buffer
             bool ok = true;
@@ -585,10 +574,10 @@ __global__ void __launch_bounds__(PROMOTED_THREADS, 1) gemm_tf32x3_promoted_kern
                         const uint32_t p_hi = sa, p_lo = sa + Cfg::kABytes, q_hi = sa + 2 * Cfg::kABytes, q_lo = q_hi + Cfg::kBBytes;
 #pragma unroll
                         for (int k4 = 0; k4 < BK / UMMA_K; k4++) {
-                            const uint32_t off = k4 * UMMA_K * 4;
-                            umma_tf32(tmem_d, umma_desc(p_lo + off), umma_desc(q_hi + off), idesc, (kb != kb0 || k4 != 0) ? 1u : 0u);
-                            umma_tf32(tmem_d, umma_desc(p_hi + off), umma_desc(q_lo + off), idesc, 1u);
-                            umma_tf32(tmem_d, umma_desc(p_hi + off), umma_desc(q_hi + off), idesc, 1u);
+                            const uint32_t po = k4 * pf.k8_step, qo = k4 * qf.k8_step;
+                            umma_tf32(tmem_d, umma_desc(pf, p_lo + po), umma_desc(qf, q_hi + qo), idesc, (kb != kb0 || k4 != 0) ? 1u : 0u);
+                            umma_tf32(tmem_d, umma_desc(pf, p_hi + po), umma_desc(qf, q_lo + qo), idesc, 1u);
+                            umma_tf32(tmem_d, umma_desc(pf, p_hi + po), umma_desc(qf, q_hi + qo), idesc, 1u);
                         }
                         umma_commit(empty_bar(stage));
                         if (++stage == S) { stage = 0; phase ^= 1u; }
@@ -639,13 +628,12 @@ __global__ void __launch_bounds__(PROMOTED_THREADS, 1) gemm_tf32x3_promoted_kern
             if (!ok) break;
             const int row = m0 + quarter * 32 + lane;
             const bool row_ok = row < prm.m;
-            const bool row_pad = !row_ok && prm.thi != nullptr && row < prm.m_pad;
-            if (row_ok || row_pad) {
+            if (row_ok) {
 #pragma unroll
                 for (int g = 0; g < CPT / 4; g++) {
                     const int col = n0 + half * CPT + g * 4;
                     if ((col & ~31) < prm.n)
-                        epilogue_emit4(prm, row, row_ok, col, sum[g * 4], sum[g * 4 + 1], sum[g * 4 + 2], sum[g * 4 + 3], vec_ok);
+                        epilogue_emit4(prm, row, col, sum[g * 4], sum[g * 4 + 1], sum[g * 4 + 2], sum[g * 4 + 3], vec_ok);
                 }
             }
         }
@@ -717,6 +705,14 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
     asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, uint32_t cluster_bar, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void load_operand_pair(uint32_t dst, const CUtensorMap *map, uint32_t cluster_bar, int kb, int r0, int mn_major) {
+    if (mn_major) tma_load_3d_pair(dst, map, cluster_bar, 0, kb * BK, r0 >> 5);
+    else tma_load_2d_pair(dst, map, cluster_bar, kb * BK, r0);
+}
 __device__ __forceinline__ void umma_tf32_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
@@ -783,17 +779,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1)
                     const uint32_t sa = smem_base + stage * Cfg::kStageBytes;
                     const uint32_t leader_full = map_to_rank(full_bar(stage), 0);
                     if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * Cfg::kStageBytes);
-                    tma_load_2d_pair(sa, &map_p_hi, leader_full, kb * BK, m0);
-                    tma_load_2d_pair(sa + Cfg::kABytes, &map_p_lo, leader_full, kb * BK, m0);
-                    tma_load_2d_pair(sa + 2 * Cfg::kABytes, &map_q_hi, leader_full, kb * BK, n0);
-                    tma_load_2d_pair(sa + 2 * Cfg::kABytes + Cfg::kBBytes, &map_q_lo, leader_full, kb * BK, n0);
+                    load_operand_pair(sa, &map_p_hi, leader_full, kb, m0, prm.p_mn);
+                    load_operand_pair(sa + Cfg::kABytes, &map_p_lo, leader_full, kb, m0, prm.p_mn);
+                    load_operand_pair(sa + 2 * Cfg::kABytes, &map_q_hi, leader_full, kb, n0, prm.q_mn);
+                    load_operand_pair(sa + 2 * Cfg::kABytes + Cfg::kBBytes, &map_q_lo, leader_full, kb, n0, prm.q_mn);
                     if (++stage == S) { stage = 0; phase ^= 1u; }
                 }
             }
         }
     } else if (warp == 1 && rank == 0) {
         if (lane == 0) {
-            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+            const uint32_t idesc = umma_idesc(2 * BM, BN, prm.p_mn, prm.q_mn);
+            const OperandForm pf = operand_form(prm.p_mn), qf = operand_form(prm.q_mn);
             int stage = 0; uint32_t phase = 0;
             uint32_t partial = 0;
             bool ok = true;
@@ -811,10 +808,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1)
                         const uint32_t p_hi = sa, p_lo = sa + Cfg::kABytes, q_hi = sa + 2 * Cfg::kABytes, q_lo = q_hi + Cfg::kBBytes;
 #pragma unroll
                         for (int k4 = 0; k4 < BK / UMMA_K; k4++) {
-                            const uint32_t off = k4 * UMMA_K * 4;
-                            umma_tf32_pair(tmem_d, umma_desc(p_lo + off), umma_desc(q_hi + off), idesc, (kb != kb0 || k4 != 0) ? 1u : 0u);
-                            umma_tf32_pair(tmem_d, umma_desc(p_hi + off), umma_desc(q_lo + off), idesc, 1u);
-                            umma_tf32_pair(tmem_d, umma_desc(p_hi + off), umma_desc(q_hi + off), idesc, 1u);
+                            const uint32_t po = k4 * pf.k8_step, qo = k4 * qf.k8_step;
+                            umma_tf32_pair(tmem_d, umma_desc(pf, p_lo + po), umma_desc(qf, q_hi + qo), idesc, (kb != kb0 || k4 != 0) ? 1u : 0u);
+                            umma_tf32_pair(tmem_d, umma_desc(pf, p_hi + po), umma_desc(qf, q_lo + qo), idesc, 1u);
+                            umma_tf32_pair(tmem_d, umma_desc(pf, p_hi + po), umma_desc(qf, q_hi + qo), idesc, 1u);
                         }
                         umma_commit_pair(empty_bar(stage));                      // this block's producer
                         umma_commit_pair(map_to_rank(empty_bar(stage), 1));      // the partner's producer
@@ -869,13 +866,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1)
             if (!ok) break;
             const int row = m0 + quarter * 32 + lane;
             const bool row_ok = row < prm.m;
-            const bool row_pad = !row_ok && prm.thi != nullptr && row < prm.m_pad;
-            if (row_ok || row_pad) {
+            if (row_ok) {
 #pragma unroll
                 for (int g = 0; g < CPT / 4; g++) {
                     const int col = n0 + half * CPT + g * 4;
                     if ((col & ~31) < prm.n)
-                        epilogue_emit4(prm, row, row_ok, col, sum[g * 4], sum[g * 4 + 1], sum[g * 4 + 2], sum[g * 4 + 3], vec_ok);
+                        epilogue_emit4(prm, row, col, sum[g * 4], sum[g * 4 + 1], sum[g * 4 + 2], sum[g * 4 + 3], vec_ok);
                 }
             }
         }
@@ -910,7 +906,7 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// 2-D map over a dense [rows, kp] FP32 plane: box = 32 floats (one 128-byte swizzle row) x box_rows.
+// 2-D map over a K-major [rows, kp] FP32 plane: box = 32 floats (one 128-byte swizzle row) x box_rows.
 bool make_plane_map(CUtensorMap *map, const float *plane, int64_t rows, int64_t kp, int64_t pitch, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
@@ -919,7 +915,20 @@ bool make_plane_map(CUtensorMap *map, const float *plane, int64_t rows, int64_t 
     cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
     cuuint32_t elem[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)plane, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              BK == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+// 3-D map over an MN-major [k, rows_padded] plane, seen as (32 rows, k, rows_padded / 32): one box of
+// (32, 32, box_rows / 32) lands in shared memory as box_rows / 32 consecutive [32 k][128 byte] slabs
+// in the 32-byte-atom swizzle, which is the MN-major operand layout.  Contraction steps past k read as zero.
+bool make_plane_map_mn(CUtensorMap *map, const float *plane, int64_t k, int64_t rows_padded, int64_t pitch, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[3] = {32, (cuuint64_t)k, (cuuint64_t)(rows_padded / 32)};
+    cuuint64_t strides[2] = {(cuuint64_t)pitch * 4, 128};
+    cuuint32_t box[3] = {32, (cuuint32_t)BK, (cuuint32_t)(box_rows / 32)};
+    cuuint32_t elem[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void *)plane, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 }  // namespace
@@ -936,18 +945,13 @@ cudaError_t gemm_exact(cudaStream_t s, int64_t m, int64_t n, int64_t k, const fl
 int64_t padded_k(int64_t k) { return (k + KPAD - 1) / KPAD * KPAD; }
 int64_t plane_pitch(int64_t k_padded) { return k_padded % 512 == 0 ? k_padded + 32 : k_padded; }
 
-cudaError_t split_planes(cudaStream_t s, const float *src, int64_t rows, int64_t cols, int64_t rs, int64_t cs,
+cudaError_t split_planes(cudaStream_t s, const float *src, int64_t rows, int64_t cols, int64_t rs,
                          float *hi, float *lo, int64_t cp) {
     if (rows == 0) return cudaSuccess;
-    if (cs == 1 || cols == 1) {
-        int vec_ok = (rs & 3) == 0 && ((uintptr_t)src & 15) == 0;
-        int64_t total = rows * (cp >> 2);
-        int64_t blocks = (total + 255) / 256;
-        split_rows_kernel<<<(unsigned)(blocks > 148 * 32 ? 148 * 32 : blocks), 256, 0, s>>>(src, rows, cols, rs, hi, lo, cp, vec_ok);
-    } else if (rs == 1 || rows == 1) {
-        int64_t tiles = (cp >> 5) * ((rows + 31) >> 5);
-        split_transposed_kernel<<<(unsigned)(tiles > 148 * 16 ? 148 * 16 : tiles), 256, 0, s>>>(src, rows, cols, cs, hi, lo, cp);
-    } else return cudaErrorInvalidValue;
+    int vec_ok = (rs & 3) == 0 && ((uintptr_t)src & 15) == 0;
+    int64_t total = rows * (cp >> 2);
+    int64_t blocks = (total + 255) / 256;
+    split_rows_kernel<<<(unsigned)(blocks > 148 * 32 ? 148 * 32 : blocks), 256, 0, s>>>(src, rows, cols, rs, hi, lo, cp, vec_ok);
     return cudaGetLastError();
 }
 
@@ -968,16 +972,18 @@ struct TensorCoreGemm {
     CUtensorMap p_hi, p_lo, q_hi, q_lo;
     int m, n, k_blocks, bn, grid;
     int promote, chunk_kb, pair;
+    int p_mn, q_mn;
 };
 
-TensorCoreGemm *tc_gemm_prepare(const float *p_hi, const float *p_lo, const float *q_hi, const float *q_lo,
-                                int64_t m, int64_t n, int64_t k_padded, int64_t pitch, int sm_count, int promote, int *status) {
+TensorCoreGemm *tc_gemm_prepare(const TcOperand &p, const TcOperand &q, int64_t m, int64_t n, int64_t k,
+                                int sm_count, int promote, int *status) {
     const int pair_requested = promote >> 1;      // bit 1 of the mode: two-SM tiles
     promote &= 1;
     *status = OK;
-    if (m < 1 || n < 1 || k_padded < BK || k_padded % BK || m > (1ll << 30) || n > (1ll << 30)) { *status = UNSUPPORTED_SHAPE; return nullptr; }
+    if (m < 1 || n < 1 || k < 1 || m > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30)) { *status = UNSUPPORTED_SHAPE; return nullptr; }
     TensorCoreGemm *g = new TensorCoreGemm();
-    g->m = (int)m; g->n = (int)n; g->k_blocks = (int)(k_padded / BK);
+    g->m = (int)m; g->n = (int)n; g->k_blocks = (int)((k + BK - 1) / BK);
+    g->p_mn = p.mn_major; g->q_mn = q.mn_major;
     g->promote = promote;
     // Partial-sum length.  The epilogue warps that add the partials also write the finished tile, and
     // the tensor core can run only two partials ahead of them, so short partials stall it at every
@@ -1014,8 +1020,12 @@ TensorCoreGemm *tc_gemm_prepare(const float *p_hi, const float *p_lo, const floa
         g->promote = 1;
     }
     const int q_box = g->pair ? g->bn / 2 : g->bn;
-    bool ok = make_plane_map(&g->p_hi, p_hi, m, k_padded, pitch, BM) && make_plane_map(&g->p_lo, p_lo, m, k_padded, pitch, BM)
-              && make_plane_map(&g->q_hi, q_hi, n, k_padded, pitch, q_box) && make_plane_map(&g->q_lo, q_lo, n, k_padded, pitch, q_box);
+    auto maps = [&](const TcOperand &o, int64_t extent, int box_rows, CUtensorMap *hi, CUtensorMap *lo) {
+        if (o.mn_major) return make_plane_map_mn(hi, o.hi, k, padded_k(extent), o.pitch, box_rows)
+                               && make_plane_map_mn(lo, o.lo, k, padded_k(extent), o.pitch, box_rows);
+        return make_plane_map(hi, o.hi, extent, padded_k(k), o.pitch, box_rows) && make_plane_map(lo, o.lo, extent, padded_k(k), o.pitch, box_rows);
+    };
+    bool ok = maps(p, m, BM, &g->p_hi, &g->p_lo) && maps(q, n, q_box, &g->q_hi, &g->q_lo);
     if (!ok) { delete g; *status = KERNEL_COMPILATION_FAILED; return nullptr; }
     return g;
 }
@@ -1058,7 +1068,7 @@ static cudaError_t launch_tc(cudaStream_t s, const TensorCoreGemm *g, const TcPa
 cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, int64_t ldd, const GemmEpilogue &ep, int *error_word) {
     TcParams prm;
     prm.nhi = ep.plane_hi; prm.nlo = ep.plane_lo; prm.nld = ep.plane_ld;
-    prm.thi = ep.tplane_hi; prm.tlo = ep.tplane_lo; prm.tld = ep.tplane_ld; prm.m_pad = (int)ep.tplane_ld;
+    prm.p_mn = g->p_mn; prm.q_mn = g->q_mn;
     prm.d = d; prm.ldd = ldd; prm.m = g->m; prm.n = g->n; prm.k_blocks = g->k_blocks;
     const int tile_m = g->pair ? 2 * BM : BM;
     prm.tiles_m = (g->m + tile_m - 1) / tile_m; prm.tiles_n = (g->n + g->bn - 1) / g->bn;

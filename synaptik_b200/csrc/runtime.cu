@@ -104,12 +104,13 @@ PlaneKey plane_key(const View &v, int orientation) {
 
 struct StepExec {
     kern::TensorCoreGemm *tc = nullptr;
-    int planes_p = -1, planes_q = -1;       // indices into Executable::planes
+    int planes_a = -1, planes_b = -1;       // indices into Executable::planes of the MATMUL's two operands
+    int orient_a = 0, orient_b = 1;         // which axis of the operand view the plane rows follow
     bool swapped = false;                   // result stored transposed: roles of the operands exchanged
     double *colsum_partials = nullptr;
     float *row_loss = nullptr;
     float *narrow_partials = nullptr;
-    int emit_planes = -1, emit_tplanes = -1;    // planes this tensor-core step writes from its epilogue
+    int emit_planes = -1;                   // planes this tensor-core step writes from its epilogue
 };
 
 struct Executable {
@@ -271,14 +272,24 @@ int32_t prepare_executable(Executable *x) {
         if (st.kind == StepKind::GEMM && st.engine == GemmEngine::TENSOR_CORE) {
             const View &c = plan.views[st.out];
             se.swapped = c.strides[0] == 1 && c.shape[0] != 1 && c.strides[1] != 1;
-            // orientation 0: plane rows follow axis 0 of the view; 1: plane rows follow axis 1
-            int pa = planes_for(st.a, 0, st.m, st.k), pb = planes_for(st.b, 1, st.n, st.k);
-            if (pa < 0 || pb < 0) return ALLOCATION_FAILED;
-            se.planes_p = se.swapped ? pb : pa;
-            se.planes_q = se.swapped ? pa : pb;
-            const Planes &P = x->planes[se.planes_p], &Q = x->planes[se.planes_q];
+            // Plane rows follow the axis of the operand view that is NOT contiguous, so every split is a
+            // row split; an operand whose contraction axis is the strided one is handed to the kernel as
+            // MN-major planes ([k, rows]) instead of being transposed.  Orientation 0: plane rows follow
+            // axis 0 of the view, 1: axis 1.  A = [m, k] is K-major at orientation 0, B = [k, n] at 1.
+            const View &va = plan.views[st.a], &vb = plan.views[st.b];
+            se.orient_a = (va.strides[1] == 1 || va.shape[1] == 1) ? 0 : 1;
+            se.orient_b = (vb.strides[0] == 1 || vb.shape[0] == 1) ? 1 : 0;
+            if ((se.orient_a == 1 && va.strides[0] != 1) || (se.orient_b == 0 && vb.strides[1] != 1)) return UNSUPPORTED_SHAPE;
+            se.planes_a = se.orient_a == 0 ? planes_for(st.a, 0, st.m, st.k) : planes_for(st.a, 1, st.k, st.m);
+            se.planes_b = se.orient_b == 1 ? planes_for(st.b, 1, st.n, st.k) : planes_for(st.b, 0, st.k, st.n);
+            if (se.planes_a < 0 || se.planes_b < 0) return ALLOCATION_FAILED;
+            const Planes &A = x->planes[se.planes_a], &B = x->planes[se.planes_b];
+            kern::TcOperand oa, ob;
+            oa.hi = A.hi; oa.lo = A.lo; oa.pitch = A.pitch; oa.mn_major = se.orient_a == 1;
+            ob.hi = B.hi; ob.lo = B.lo; ob.pitch = B.pitch; ob.mn_major = se.orient_b == 0;
             int status = OK;
-            se.tc = kern::tc_gemm_prepare(P.hi, P.lo, Q.hi, Q.lo, P.rows, Q.rows, P.kp, P.pitch, ctx->sm_count, ctx->gemm_promote | (ctx->gemm_pair << 1), &status);
+            se.tc = se.swapped ? kern::tc_gemm_prepare(ob, oa, st.n, st.m, st.k, ctx->sm_count, ctx->gemm_promote | (ctx->gemm_pair << 1), &status)
+                               : kern::tc_gemm_prepare(oa, ob, st.m, st.n, st.k, ctx->sm_count, ctx->gemm_promote | (ctx->gemm_pair << 1), &status);
             if (!se.tc) return status;
         } else if (st.kind == StepKind::GEMM && st.engine == GemmEngine::NARROW_REDUCE) {
             void *p; if (!alloc((uint64_t)kern::narrow_reduce_partial_floats(st.m, st.n, st.k) * 4, &p)) return ALLOCATION_FAILED;
@@ -292,7 +303,7 @@ int32_t prepare_executable(Executable *x) {
         }
     }
     // a tensor-core GEMM whose dense result is later read as a GEMM operand writes that operand's
-    // planes itself (both orientations if asked), which removes the separate split pass
+    // planes itself, which removes the separate split pass
     for (size_t i = 0; i < plan.steps.size(); i++) {
         const Step &st = plan.steps[i];
         StepExec &se = x->exec[i];
@@ -303,10 +314,6 @@ int32_t prepare_executable(Executable *x) {
         if (u.shape.size() != 2 || !u.dense()) continue;
         auto normal = x->plane_index.find(plane_key(u, 0));
         if (normal != x->plane_index.end()) se.emit_planes = normal->second;
-        View t = u;                                         // the transposed view of the same storage
-        std::swap(t.shape[0], t.shape[1]); std::swap(t.strides[0], t.strides[1]);
-        auto transposed = x->plane_index.find(plane_key(t, 0));
-        if (transposed != x->plane_index.end()) se.emit_tplanes = transposed->second;
     }
     if (cudaEventCreate(&x->start) != cudaSuccess || cudaEventCreate(&x->stop) != cudaSuccess) return INTERNAL_ERROR;
     x->sync_publication.assign(x->program.publications.size(), 0);
@@ -397,23 +404,17 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                         Planes &pl = x->planes[index];
                         if (pl.last_run == x->run_counter) return OK;
                         const View &v = plan.views[value];
-                        int64_t rs = orientation == 0 ? v.strides[0] : v.strides[1], cs = orientation == 0 ? v.strides[1] : v.strides[0];
-                        int64_t cols = orientation == 0 ? v.shape[1] : v.shape[0];
-                        LAUNCH(kern::split_planes(s, (const float *)ptr(value), pl.rows, cols, rs, cs, pl.hi, pl.lo, pl.pitch));
+                        LAUNCH(kern::split_planes(s, (const float *)ptr(value), pl.rows, v.shape[1 - orientation], v.strides[orientation],
+                                                  pl.hi, pl.lo, pl.pitch));
                         pl.last_run = x->run_counter;
                         return OK;
                     };
-                    int pa = x->plane_index[plane_key(plan.views[st.a], 0)], pb = x->plane_index[plane_key(plan.views[st.b], 1)];
-                    int32_t r1 = split(st.a, 0, pa); if (r1 != OK) return r1;
-                    int32_t r2 = split(st.b, 1, pb); if (r2 != OK) return r2;
+                    int32_t r1 = split(st.a, se.orient_a, se.planes_a); if (r1 != OK) return r1;
+                    int32_t r2 = split(st.b, se.orient_b, se.planes_b); if (r2 != OK) return r2;
                     int64_t ldd = se.swapped ? c.strides[1] : c.strides[0];
                     if (se.emit_planes >= 0) {
                         Planes &pl = x->planes[se.emit_planes];
                         ep.plane_hi = pl.hi; ep.plane_lo = pl.lo; ep.plane_ld = pl.pitch; pl.last_run = x->run_counter;
-                    }
-                    if (se.emit_tplanes >= 0) {
-                        Planes &pl = x->planes[se.emit_tplanes];
-                        ep.tplane_hi = pl.hi; ep.tplane_lo = pl.lo; ep.tplane_ld = pl.pitch; pl.last_run = x->run_counter;
                     }
                     if (time_steps) cudaEventRecord(x->step_events[2 * i], s);
                     LAUNCH(kern::tc_gemm_launch(s, se.tc, (float *)ptr(st.out), ldd, ep, ctx->error_dev));
