@@ -71,8 +71,10 @@ SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_release(void *context);
  * adds them into round-to-nearest FP32 register sums; 0 = one tensor-memory accumulator over the
  * whole contraction (faster epilogue, error grows with K).  "gemm_pair": 1 (default) = products with
  * at least 256 rows use two-SM tiles (clusters of two blocks, tcgen05 cta_group::2); 0 = one-SM tiles
- * only.  Unknown names return
- * INVALID_ARGUMENT. */
+ * only.  "gemm_slices": 1 (default) = a two-SM product without epilogue work (a weight gradient) may
+ * split its contraction into up to four slices when that shortens the last wave of the persistent
+ * grid; the slices' partial products are added in ascending order by a second kernel; 0 = never.
+ * Unknown names return INVALID_ARGUMENT. */
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_set_option(void *context, const char *name, int64_t value);
 /* Blocks until all work issued on the context has finished. */
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_synchronize(void *context);

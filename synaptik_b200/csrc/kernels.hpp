@@ -103,11 +103,17 @@ cudaError_t split_planes(cudaStream_t s, const float *src, int64_t rows, int64_t
                          float *hi, float *lo, int64_t pitch);
 struct TcOperand { const float *hi = nullptr, *lo = nullptr; int64_t pitch = 0; int mn_major = 0; };
 struct TensorCoreGemm;       // opaque: tensor maps and launch geometry prepared once per plan step
-// mode: bit 0 = FP32 promotion of partial sums, bit 1 = two-SM tiles where the shape fills them
+// mode: bit 0 = FP32 promotion of partial sums, bit 1 = two-SM tiles where the shape fills them,
+// bit 2 = the launch will have no epilogue work (bias, gate, activation, second output, planes), so the
+// contraction may be split into slices whose partial products are added by a second kernel; such a
+// GEMM needs tc_gemm_workspace_floats(g) floats of scratch at launch.
 TensorCoreGemm *tc_gemm_prepare(const TcOperand &p, const TcOperand &q, int64_t m, int64_t n, int64_t k,
                                 int sm_count, int mode, int *status);
 void tc_gemm_release(TensorCoreGemm *g);
-cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, int64_t ldd, const GemmEpilogue &ep, int *error_word);
+int64_t tc_gemm_workspace_floats(const TensorCoreGemm *g);
+int tc_gemm_launches(const TensorCoreGemm *g);
+cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, int64_t ldd, const GemmEpilogue &ep, float *workspace,
+                           int *error_word);
 
 }  // namespace kern
 }  // namespace syn

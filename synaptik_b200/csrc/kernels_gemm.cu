@@ -267,6 +267,14 @@ struct TcParams {
     int chunk_kb;                            // promoted kernel: k-blocks per tensor-memory partial sum
     int *error_word;
 };
+// Kept apart from TcParams on purpose: with 128 register sums per epilogue thread the 256-wide kernels
+// sit at the edge of their register budget, and growing TcParams pushed ptxas into an allocation that
+// ran the epilogue-bound K = 784 layer 40 % slower (measured).  After touching either struct compare
+// -Xptxas -v: 204 bytes of spill stores / 224 of spill loads for the <256> two-SM kernel is the good state.
+struct SliceParams {                         // two-SM kernel: split of the contraction into slices
+    int slices, kb_per_slice;
+    float *ws; int64_t ld;                   // workspace [slices][m][ld] of the slices' partial products
+};
 
 
 // Finishes four adjacent result cells of one row: bias, ReLU-backward gate, activation, the stores
@@ -483,6 +491,7 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, float (&v)[16]) {
 #pragma unroll
     for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
 }
+
 
 template <int BN>
 __global__ void __launch_bounds__(PROMOTED_THREADS, 1) gemm_tf32x3_promoted_kernel(
@@ -721,10 +730,10 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
 }
 
-template <int BN>
+template <int BN, bool SLICED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1) gemm_tf32x3_pair_kernel(
         const __grid_constant__ CUtensorMap map_p_hi, const __grid_constant__ CUtensorMap map_p_lo,
-        const __grid_constant__ CUtensorMap map_q_hi, const __grid_constant__ CUtensorMap map_q_lo, TcParams prm) {
+        const __grid_constant__ CUtensorMap map_q_hi, const __grid_constant__ CUtensorMap map_q_lo, TcParams prm, SliceParams slc) {
     using Cfg = PairConfig<BN>;
     constexpr int S = Cfg::kStages;
     constexpr int CPT = BN / 2;
@@ -761,6 +770,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1)
 
     const int total_tiles = prm.tiles_m * prm.tiles_n;      // tiles of 256 x BN
     const int kb_count = prm.k_blocks;
+    // a unit is one tile over one slice of the contraction; without slicing a unit is a tile and the
+    // slice arithmetic below folds away at compile time
+    const int total_units = SLICED ? total_tiles * slc.slices : total_tiles;
+    const int kb_per_slice = SLICED ? slc.kb_per_slice : kb_count;
     const int CHUNK_KB = prm.chunk_kb;
     const uint32_t smem_base = smem_u32(smem);
     const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
@@ -771,10 +784,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1)
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
-            for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
+            for (int unit = pair; unit < total_units && ok; unit += pairs) {
+                const int tile = SLICED ? unit % total_tiles : unit, slice = SLICED ? unit / total_tiles : 0;
                 const int m0 = (tile / prm.tiles_n) * (2 * BM) + (int)rank * BM;
                 const int n0 = (tile % prm.tiles_n) * BN + (int)rank * (BN / 2);
-                for (int kb = 0; kb < kb_count; kb++) {
+                const int kb_first = slice * kb_per_slice;
+                const int kb_last = (SLICED && kb_first + kb_per_slice < kb_count) ? kb_first + kb_per_slice : kb_count;
+                for (int kb = kb_first; kb < kb_last; kb++) {
                     if (!mbar_wait_cluster(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
                     const uint32_t sa = smem_base + stage * Cfg::kStageBytes;
                     const uint32_t leader_full = map_to_rank(full_bar(stage), 0);
@@ -794,13 +810,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1)
             int stage = 0; uint32_t phase = 0;
             uint32_t partial = 0;
             bool ok = true;
-            for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
-                for (int kb0 = 0; kb0 < kb_count && ok; kb0 += CHUNK_KB, partial++) {
+            for (int unit = pair; unit < total_units && ok; unit += pairs) {
+                const int kb_first = SLICED ? (unit / total_tiles) * kb_per_slice : 0;
+                const int kb_last = (SLICED && kb_first + kb_per_slice < kb_count) ? kb_first + kb_per_slice : kb_count;
+                for (int kb0 = kb_first; kb0 < kb_last && ok; kb0 += CHUNK_KB, partial++) {
                     const int buf = partial & 1;
                     if (!mbar_wait_cluster(acc_empty_bar(buf), ((partial >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
-                    const int kb1 = kb0 + CHUNK_KB < kb_count ? kb0 + CHUNK_KB : kb_count;
+                    const int kb1 = kb0 + CHUNK_KB < kb_last ? kb0 + CHUNK_KB : kb_last;
                     for (int kb = kb0; kb < kb1; kb++) {
                         if (!mbar_wait_cluster(full_bar(stage), phase, abort_flag)) { ok = false; break; }
                         tc_fence_after();
@@ -833,17 +851,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1)
         bool ok = true;
         const bool vec_ok = (prm.ldd & 3) == 0 && ((uintptr_t)prm.d & 15) == 0
                             && (!prm.second || ((uintptr_t)prm.second & 15) == 0) && (!prm.gate || ((uintptr_t)prm.gate & 15) == 0);
-        for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
+        for (int unit = pair; unit < total_units && ok; unit += pairs) {
+            const int tile = SLICED ? unit % total_tiles : unit, slice = SLICED ? unit / total_tiles : 0;
             const int m0 = (tile / prm.tiles_n) * (2 * BM) + (int)rank * BM, n0 = (tile % prm.tiles_n) * BN;
+            const int kb_first = slice * kb_per_slice;
+            const int kb_last = (SLICED && kb_first + kb_per_slice < kb_count) ? kb_first + kb_per_slice : kb_count;
             float sum[CPT];
-            for (int kb0 = 0; kb0 < kb_count; kb0 += CHUNK_KB, partial++) {
+            for (int kb0 = kb_first; kb0 < kb_last; kb0 += CHUNK_KB, partial++) {
                 const int buf = partial & 1;
                 ok = mbar_wait_cluster(acc_full_bar(buf), (partial >> 1) & 1u, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * CPT);
-                if (kb0 == 0) {
+                if (kb0 == kb_first) {
 #pragma unroll
                     for (int s16 = 0; s16 < CPT / 16; s16++) {
                         float t[16];
@@ -866,7 +887,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1)
             if (!ok) break;
             const int row = m0 + quarter * 32 + lane;
             const bool row_ok = row < prm.m;
-            if (row_ok) {
+            if constexpr (SLICED) {
+                // a slice of a split contraction writes its raw partial product to the workspace
+                // ([slice][m][slice_ld]; the launch guarantees there is no other epilogue work then);
+                // slice_combine_kernel adds the slices in a fixed order
+                if (row_ok) {
+                    float *wrow = slc.ws + ((int64_t)slice * prm.m + row) * slc.ld;
+#pragma unroll
+                    for (int g = 0; g < CPT / 4; g++) {
+                        const int col = n0 + half * CPT + g * 4;
+                        if (col < slc.ld)
+                            *reinterpret_cast<float4 *>(wrow + col) = make_float4(sum[g * 4], sum[g * 4 + 1], sum[g * 4 + 2], sum[g * 4 + 3]);
+                    }
+                }
+            } else if (row_ok) {
 #pragma unroll
                 for (int g = 0; g < CPT / 4; g++) {
                     const int col = n0 + half * CPT + g * 4;
@@ -886,6 +920,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1)
         __syncwarp();
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::kTmemCols) : "memory");
+    }
+}
+
+// Adds the slices of a split contraction in ascending order, one binary32 rounding per addition.
+__global__ void slice_combine_kernel(const float *__restrict__ ws, int slices, int64_t m, int64_t n, int64_t slice_ld, float *d, int64_t ldd) {
+    const int64_t quads = slice_ld >> 2, total = m * quads;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / quads, c = (i - r * quads) << 2;
+        float4 acc = *reinterpret_cast<const float4 *>(ws + r * slice_ld + c);
+        for (int sl = 1; sl < slices; sl++) {
+            const float4 v = *reinterpret_cast<const float4 *>(ws + ((int64_t)sl * m + r) * slice_ld + c);
+            acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y); acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+        }
+        float *out = d + r * ldd + c;
+        if (c + 3 < n && (ldd & 3) == 0 && ((uintptr_t)d & 15) == 0) *reinterpret_cast<float4 *>(out) = acc;
+        else { const float v[4] = {acc.x, acc.y, acc.z, acc.w}; for (int e = 0; e < 4; e++) if (c + e < n) out[e] = v[e]; }
     }
 }
 
@@ -973,17 +1023,20 @@ struct TensorCoreGemm {
     int m, n, k_blocks, bn, grid;
     int promote, chunk_kb, pair;
     int p_mn, q_mn;
+    int slices, kb_per_slice; int64_t slice_ld;
 };
 
 TensorCoreGemm *tc_gemm_prepare(const TcOperand &p, const TcOperand &q, int64_t m, int64_t n, int64_t k,
                                 int sm_count, int promote, int *status) {
-    const int pair_requested = promote >> 1;      // bit 1 of the mode: two-SM tiles
+    const int pair_requested = (promote >> 1) & 1;      // bit 1 of the mode: two-SM tiles
+    const int may_slice = (promote >> 2) & 1;           // bit 2: the result has no epilogue, the contraction may be split
     promote &= 1;
     *status = OK;
     if (m < 1 || n < 1 || k < 1 || m > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30)) { *status = UNSUPPORTED_SHAPE; return nullptr; }
     TensorCoreGemm *g = new TensorCoreGemm();
     g->m = (int)m; g->n = (int)n; g->k_blocks = (int)((k + BK - 1) / BK);
     g->p_mn = p.mn_major; g->q_mn = q.mn_major;
+    g->slices = 1; g->kb_per_slice = g->k_blocks; g->slice_ld = (n + 3) / 4 * 4;
     g->promote = promote;
     // Partial-sum length.  The epilogue warps that add the partials also write the finished tile, and
     // the tensor core can run only two partials ahead of them, so short partials stall it at every
@@ -1016,8 +1069,24 @@ TensorCoreGemm *tc_gemm_prepare(const TcOperand &p, const TcOperand &q, int64_t 
         if (forced_tile_n() == 128 || forced_tile_n() == 256) g->bn = forced_tile_n();
         int64_t pair_tiles = ((m + 2 * BM - 1) / (2 * BM)) * ((n + g->bn - 1) / g->bn);
         int64_t pairs = sm_count / 2;
-        g->grid = (int)(2 * (pair_tiles < pairs ? pair_tiles : pairs));
         g->promote = 1;
+        // A persistent grid pays for its last partial wave: 256 tiles on 74 pairs take 4 waves for 3.46
+        // waves of work.  Splitting the contraction into slices makes the units shorter and the tail
+        // smaller (2 slices: 512 units, 7 half-length waves for 6.92); the slices' partial products go to
+        // a workspace and are added in a fixed order by a second kernel.
+        if (may_slice) {
+            double best = 1e30;
+            for (int sl = 1; sl <= 4; sl++) {
+                const int per = (g->k_blocks + sl - 1) / sl;
+                if (sl > 1 && per < 64) break;                  // slices shorter than 2048 steps do not pay for their epilogue
+                const int64_t units = pair_tiles * ((g->k_blocks + per - 1) / per);
+                const int64_t waves = (units + pairs - 1) / pairs;
+                const double cost = (double)waves * per * (1.0 + 0.02 * (sl - 1));
+                if (cost < best) { best = cost; g->slices = (g->k_blocks + per - 1) / per; g->kb_per_slice = per; }
+            }
+        }
+        const int64_t units = pair_tiles * g->slices;
+        g->grid = (int)(2 * (units < pairs ? units : pairs));
     }
     const int q_box = g->pair ? g->bn / 2 : g->bn;
     auto maps = [&](const TcOperand &o, int64_t extent, int box_rows, CUtensorMap *hi, CUtensorMap *lo) {
@@ -1031,9 +1100,10 @@ TensorCoreGemm *tc_gemm_prepare(const TcOperand &p, const TcOperand &q, int64_t 
 }
 
 void tc_gemm_release(TensorCoreGemm *g) { delete g; }
+int64_t tc_gemm_workspace_floats(const TensorCoreGemm *g) { return g->slices > 1 ? (int64_t)g->slices * g->m * g->slice_ld : 0; }
 
 template <int BN>
-static cudaError_t launch_tc(cudaStream_t s, const TensorCoreGemm *g, const TcParams &prm) {
+static cudaError_t launch_tc(cudaStream_t s, const TensorCoreGemm *g, const TcParams &prm, const SliceParams &slc) {
     using Cfg = TileConfig<BN>;
     // a per-device attribute: set on every launch so each GPU of the process has it
     cudaError_t e = cudaFuncSetAttribute(gemm_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
@@ -1041,13 +1111,18 @@ static cudaError_t launch_tc(cudaStream_t s, const TensorCoreGemm *g, const TcPa
     if (g->pair) {
         if constexpr (BN >= 128) {
             using Pair = PairConfig<BN>;
-            cudaFuncAttributes attr;
-            e = cudaFuncGetAttributes(&attr, gemm_tf32x3_pair_kernel<BN>);
+            auto launch_pair = [&](auto kernel) -> cudaError_t {
+                cudaFuncAttributes attr;
+                cudaError_t pe = cudaFuncGetAttributes(&attr, kernel);
+                if (pe != cudaSuccess) return pe;
+                if (attr.numRegs * PROMOTED_THREADS < 128 * 72 + 256 * 216) return cudaErrorLaunchOutOfResources;
+                pe = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Pair::kSmemBytes);
+                if (pe != cudaSuccess) return pe;
+                kernel<<<g->grid, PROMOTED_THREADS, Pair::kSmemBytes, s>>>(g->p_hi, g->p_lo, g->q_hi, g->q_lo, prm, slc);
+                return cudaSuccess;
+            };
+            e = g->slices > 1 ? launch_pair(gemm_tf32x3_pair_kernel<BN, true>) : launch_pair(gemm_tf32x3_pair_kernel<BN, false>);
             if (e != cudaSuccess) return e;
-            if (attr.numRegs * PROMOTED_THREADS < 128 * 72 + 256 * 216) return cudaErrorLaunchOutOfResources;
-            e = cudaFuncSetAttribute(gemm_tf32x3_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Pair::kSmemBytes);
-            if (e != cudaSuccess) return e;
-            gemm_tf32x3_pair_kernel<BN><<<g->grid, PROMOTED_THREADS, Pair::kSmemBytes, s>>>(g->p_hi, g->p_lo, g->q_hi, g->q_lo, prm);
         } else return cudaErrorInvalidValue;
     } else if (g->promote) {
         // the kernel redistributes registers between its warpgroups (72 and 216 per thread); that only
@@ -1065,8 +1140,12 @@ static cudaError_t launch_tc(cudaStream_t s, const TensorCoreGemm *g, const TcPa
     return cudaGetLastError();
 }
 
-cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, int64_t ldd, const GemmEpilogue &ep, int *error_word) {
+cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, int64_t ldd, const GemmEpilogue &ep, float *workspace,
+                           int *error_word) {
     TcParams prm;
+    SliceParams slc;
+    slc.slices = g->slices; slc.kb_per_slice = g->kb_per_slice; slc.ws = workspace; slc.ld = g->slice_ld;
+    if (g->slices > 1 && (!workspace || ep.bias || ep.gate || ep.second || ep.relu || ep.plane_hi)) return cudaErrorInvalidValue;
     prm.nhi = ep.plane_hi; prm.nlo = ep.plane_lo; prm.nld = ep.plane_ld;
     prm.p_mn = g->p_mn; prm.q_mn = g->q_mn;
     prm.d = d; prm.ldd = ldd; prm.m = g->m; prm.n = g->n; prm.k_blocks = g->k_blocks;
@@ -1074,10 +1153,14 @@ cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, in
     prm.tiles_m = (g->m + tile_m - 1) / tile_m; prm.tiles_n = (g->n + g->bn - 1) / g->bn;
     prm.chunk_kb = g->chunk_kb;
     prm.bias = ep.bias; prm.gate = ep.gate; prm.second = ep.second; prm.relu = ep.relu; prm.error_word = error_word;
-    if (g->bn == 256) return launch_tc<256>(s, g, prm);
-    if (g->bn == 128) return launch_tc<128>(s, g, prm);
-    return launch_tc<64>(s, g, prm);
+    cudaError_t e = g->bn == 256 ? launch_tc<256>(s, g, prm, slc) : g->bn == 128 ? launch_tc<128>(s, g, prm, slc) : launch_tc<64>(s, g, prm, slc);
+    if (e != cudaSuccess || g->slices <= 1) return e;
+    const int64_t total = (int64_t)g->m * (g->slice_ld >> 2);
+    const int64_t blocks = (total + 255) / 256;
+    slice_combine_kernel<<<(unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks), 256, 0, s>>>(workspace, g->slices, g->m, g->n, g->slice_ld, d, ldd);
+    return cudaGetLastError();
 }
+int tc_gemm_launches(const TensorCoreGemm *g) { return g->slices > 1 ? 2 : 1; }
 
 }  // namespace kern
 }  // namespace syn

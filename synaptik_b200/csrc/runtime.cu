@@ -39,6 +39,7 @@ struct Context {
     int fused_planes = 1;
     int gemm_promote = 1;
     int gemm_pair = 1;
+    int gemm_slices = 1;                    // split long contractions of epilogue-free GEMMs when that shortens the last wave
     cudaEvent_t timer_start = nullptr, timer_stop = nullptr;
     std::mutex mutex;
 };
@@ -122,6 +123,7 @@ struct Executable {
     void *constants = nullptr;              // 8 bytes per constant slot
     std::vector<Planes> planes;
     std::map<PlaneKey, int> plane_index;
+    float *gemm_workspace = nullptr;        // partial products of GEMMs whose contraction is split into slices
     std::vector<StepExec> exec;
     std::vector<void *> owned;              // every device allocation, for release
     std::vector<uint64_t> feed_bytes, publication_bytes;
@@ -253,6 +255,7 @@ int32_t prepare_executable(Executable *x) {
         if (v.slot == SlotKind::PUBLICATION) x->publication_bytes[v.index] = std::max(x->publication_bytes[v.index], view_span_bytes(v));
     }
     x->exec.resize(plan.steps.size());
+    int64_t workspace_floats = 0;               // one workspace serves every sliced GEMM: the steps run in stream order
     auto planes_for = [&](int value, int orientation, int64_t rows, int64_t k) -> int {
         PlaneKey key = plane_key(plan.views[value], orientation);
         auto it = x->plane_index.find(key);
@@ -288,8 +291,11 @@ int32_t prepare_executable(Executable *x) {
             oa.hi = A.hi; oa.lo = A.lo; oa.pitch = A.pitch; oa.mn_major = se.orient_a == 1;
             ob.hi = B.hi; ob.lo = B.lo; ob.pitch = B.pitch; ob.mn_major = se.orient_b == 0;
             int status = OK;
-            se.tc = se.swapped ? kern::tc_gemm_prepare(ob, oa, st.n, st.m, st.k, ctx->sm_count, ctx->gemm_promote | (ctx->gemm_pair << 1), &status)
-                               : kern::tc_gemm_prepare(oa, ob, st.m, st.n, st.k, ctx->sm_count, ctx->gemm_promote | (ctx->gemm_pair << 1), &status);
+            const bool plain = st.bias < 0 && st.mask < 0 && !st.relu && st.out2 < 0;
+            const int mode = ctx->gemm_promote | (ctx->gemm_pair << 1) | ((plain && ctx->gemm_slices) ? 4 : 0);
+            se.tc = se.swapped ? kern::tc_gemm_prepare(ob, oa, st.n, st.m, st.k, ctx->sm_count, mode, &status)
+                               : kern::tc_gemm_prepare(oa, ob, st.m, st.n, st.k, ctx->sm_count, mode, &status);
+            if (se.tc) workspace_floats = std::max(workspace_floats, kern::tc_gemm_workspace_floats(se.tc));
             if (!se.tc) return status;
         } else if (st.kind == StepKind::GEMM && st.engine == GemmEngine::NARROW_REDUCE) {
             void *p; if (!alloc((uint64_t)kern::narrow_reduce_partial_floats(st.m, st.n, st.k) * 4, &p)) return ALLOCATION_FAILED;
@@ -301,6 +307,10 @@ int32_t prepare_executable(Executable *x) {
             void *p; if (!alloc((uint64_t)st.m * 4, &p)) return ALLOCATION_FAILED;
             se.row_loss = (float *)p;
         }
+    }
+    if (workspace_floats > 0) {
+        void *p; if (!alloc((uint64_t)workspace_floats * 4, &p)) return ALLOCATION_FAILED;
+        x->gemm_workspace = (float *)p;
     }
     // a tensor-core GEMM whose dense result is later read as a GEMM operand writes that operand's
     // planes itself, which removes the separate split pass
@@ -417,7 +427,8 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                         ep.plane_hi = pl.hi; ep.plane_lo = pl.lo; ep.plane_ld = pl.pitch; pl.last_run = x->run_counter;
                     }
                     if (time_steps) cudaEventRecord(x->step_events[2 * i], s);
-                    LAUNCH(kern::tc_gemm_launch(s, se.tc, (float *)ptr(st.out), ldd, ep, ctx->error_dev));
+                    LAUNCH(kern::tc_gemm_launch(s, se.tc, (float *)ptr(st.out), ldd, ep, x->gemm_workspace, ctx->error_dev));
+                    x->launches += kern::tc_gemm_launches(se.tc) - 1;
                 }
                 break;
             }
@@ -592,6 +603,7 @@ int32_t synaptik_cuda_context_set_option(void *context, const char *name, int64_
     Context *ctx = as<Context>(context, TAG_CONTEXT);
     if (!ctx || !name) return INVALID_ARGUMENT;
     if (!strcmp(name, "gemm_engine")) { if (value < 0 || value > 2) return INVALID_ARGUMENT; ctx->gemm_engine = (int)value; return OK; }
+    if (!strcmp(name, "gemm_slices")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->gemm_slices = (int)value; return OK; }
     if (!strcmp(name, "gemm_pair")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->gemm_pair = (int)value; return OK; }
     if (!strcmp(name, "gemm_promote")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->gemm_promote = (int)value; return OK; }
     if (!strcmp(name, "fused_planes")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->fused_planes = (int)value; return OK; }
