@@ -93,6 +93,43 @@ def test_tensor_core_gemm_small_integers_are_exact(ctx, m, k, n):
     assert np.array_equal(c, (a.astype(np.int64) @ b.astype(np.int64)).astype(np.float32))
 
 
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+def test_tensor_core_operand_layouts_are_exact_on_small_integers(ctx, ta, tb):
+    # every combination of K-major and MN-major operand tiles (a strided operand is read as MN-major
+    # tiles, never transposed in memory), on one-SM tiles (m = 128) and two-SM tiles (m = 512)
+    for m, k, n in [(128, 64, 128), (512, 1000, 384)]:
+        rng = np.random.default_rng(m + 2 * int(ta) + int(tb))
+        a = rng.integers(-4, 5, (k, m) if ta else (m, k)).astype(np.float32)
+        b = rng.integers(-4, 5, (n, k) if tb else (k, n)).astype(np.float32)
+        (c,) = run_image(ctx, matmul_graph(m, k, n, ta, tb), [a, b], engine=2)
+        la, lb = (a.T if ta else a), (b.T if tb else b)
+        assert np.array_equal(c, (la.astype(np.int64) @ lb.astype(np.int64)).astype(np.float32))
+
+
+def test_sliced_contraction_matches_unsliced(ctx):
+    # an epilogue-free two-SM product with a long contraction is split into slices that a second kernel
+    # adds in order: exact on small integers, and within one rounding per slice of the unsliced result
+    m, k, n = 512, 16384, 384
+    rng = np.random.default_rng(5)
+    a = rng.integers(-2, 3, (k, m)).astype(np.float32)
+    b = rng.integers(-2, 3, (k, n)).astype(np.float32)
+    (c,) = run_image(ctx, matmul_graph(m, k, n, True, False), [a, b], engine=2)
+    assert np.array_equal(c, (a.T.astype(np.int64) @ b.astype(np.int64)).astype(np.float32))
+    a = rng.standard_normal((k, m)).astype(np.float32)
+    b = rng.standard_normal((k, n)).astype(np.float32)
+    (sliced,) = run_image(ctx, matmul_graph(m, k, n, True, False), [a, b], engine=2)
+    ctx.set_option("gemm_slices", 0)
+    try:
+        (whole,) = run_image(ctx, matmul_graph(m, k, n, True, False), [a, b], engine=2)
+    finally:
+        ctx.set_option("gemm_slices", 1)
+    assert not np.array_equal(sliced, whole)            # the slices really are separate partial sums
+    a64, b64 = a.T.astype(np.float64), b.astype(np.float64)
+    ref = a64 @ b64
+    bound = tc_bound(a64, b64, ref)
+    assert np.all(np.abs(sliced - ref) <= bound) and np.all(np.abs(whole - ref) <= bound)
+
+
 @pytest.mark.parametrize("m,k,n,ta,tb", [(256, 256, 256, False, True), (512, 1024, 384, False, False), (320, 200, 192, True, False),
                                          (256, 512, 128, True, True), (1000, 784, 260, False, True)])
 def test_tensor_core_gemm_tolerance(ctx, oracle, m, k, n, ta, tb):
