@@ -1,0 +1,163 @@
+"""Parity at the benchmark configurations' full sizes, where the CPU checker cannot compute the
+whole result in seconds: sampled rows / blocks against binary64 arithmetic, plus properties that do
+not depend on the size (exact power-of-two scaling, a checksum of checksums, gradient rows that sum
+to zero, index outputs bit-exact).  Everything goes through the C ABI."""
+import numpy as np
+import pytest
+
+from helpers import run_image
+from synaptik_b200 import native
+from synaptik_b200.program import F32, I32, GraphBuilder
+
+pytestmark = pytest.mark.gpu
+
+TWO_M24 = 2.0 ** -24
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = native.Context(0)
+    yield c
+    c.close()
+
+
+def dense_layer_graph(m, k, n):
+    """Y = relu(X W^T + b) with dX, dW, db for an upstream gradient (the standalone fused dense layer)."""
+    g = GraphBuilder()
+    x, w, b, dy = g.feed(F32, (m, k)), g.feed(F32, (n, k)), g.feed(F32, (n,)), g.feed(F32, (m, n))
+    wt, z = g.linear(x, w, b)
+    g.publish(g.relu(z))
+    dz = g.relu_backward(z, dy)
+    dx, dw, db = g.linear_backward(x, wt, dz, need_dx=True)
+    for v in (dx, dw, db):
+        g.publish(v)
+    return g
+
+
+def tc_bound(abs_products_sum, k):
+    # the tensor-core tolerance of the parity suite: (8 + min(K, 512) / 4) * 2^-24 * sum |a b|
+    return (8.0 + min(k, 512) / 4.0) * TWO_M24 * abs_products_sum + 1e-30
+
+
+@pytest.mark.parametrize("m,k,n", [(4096, 1024, 1024), (65536, 4096, 4096)])
+def test_dense_layer_forward_and_backward_at_full_size(ctx, m, k, n):
+    rng = np.random.default_rng(m + k)
+    bound = np.sqrt(6.0 / (k + n))
+    x = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    w = rng.uniform(-bound, bound, (n, k)).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, n).astype(np.float32)
+    dy = rng.standard_normal((m, n)).astype(np.float32)
+    y, dx, dw, db = run_image(ctx, dense_layer_graph(m, k, n), [x, w, b, dy])
+
+    rows = rng.choice(m, 48, replace=False)
+    x64, w64 = x[rows].astype(np.float64), w.astype(np.float64)
+    z_ref = x64 @ w64.T + b.astype(np.float64)
+    z_tol = tc_bound(np.abs(x64) @ np.abs(w64).T, k) + 2 * TWO_M24 * np.abs(z_ref)     # + the bias rounding
+    # forward: the stored activation of the sampled rows
+    assert np.all(np.abs(y[rows] - np.maximum(z_ref, 0.0)) <= z_tol)
+    assert np.all(y >= 0.0) and np.all(np.isfinite(y))
+    # dX on the device's own gates (a pre-activation within rounding of zero may gate either way)
+    dz64 = np.where(y[rows] > 0.0, dy[rows], 0.0).astype(np.float64)
+    dx_ref = dz64 @ w64
+    assert np.all(np.abs(dx[rows] - dx_ref) <= tc_bound(np.abs(dz64) @ np.abs(w64), n))
+    # dW and db: a 64 x 64 block and 256 columns, contraction over the whole batch, device gates
+    cols_n, cols_k = rng.choice(n, 64, replace=False), rng.choice(k, 64, replace=False)
+    dz_cols = np.where(y[:, cols_n] > 0.0, dy[:, cols_n], 0.0).astype(np.float64)
+    x_cols = x[:, cols_k].astype(np.float64)
+    dw_ref = dz_cols.T @ x_cols
+    assert np.all(np.abs(dw[np.ix_(cols_n, cols_k)] - dw_ref) <= tc_bound(np.abs(dz_cols).T @ np.abs(x_cols), m))
+    db_ref = dz_cols.sum(axis=0)
+    assert np.all(np.abs(db[cols_n] - db_ref) <= 1.5 * TWO_M24 * np.abs(db_ref) + 1e-30)       # binary64 sums, one rounding
+    # size-independent check of every output element: a checksum of checksums.  sum_r dX[r, :] must equal
+    # (sum_r dZ[r, :]) W, and sum over everything of dW equals (column sums of dZ) . (column sums of X)
+    dz_all = np.where(y > 0.0, dy, np.float32(0.0))
+    col_dz = dz_all.sum(axis=0, dtype=np.float64)
+    lhs = dx.sum(axis=0, dtype=np.float64)
+    rhs = col_dz @ w64
+    scale = np.abs(dz_all).sum(axis=0, dtype=np.float64) @ np.abs(w64)
+    assert np.all(np.abs(lhs - rhs) <= 64 * TWO_M24 * scale)
+    total_dw = dw.sum(dtype=np.float64)
+    # (the dW checksum: sum_ij dW[i, j] = sum_r (sum_i dZ[r, i]) (sum_j X[r, j]))
+    per_row = dz_all.sum(axis=1, dtype=np.float64) * x.sum(axis=1, dtype=np.float64)
+    budget = (np.abs(dz_all).sum(axis=1, dtype=np.float64) * np.abs(x).sum(axis=1, dtype=np.float64)).sum()
+    assert abs(total_dw - per_row.sum()) <= 64 * TWO_M24 * budget
+
+
+def test_power_of_two_scaling_is_exact_at_full_size(ctx):
+    # scaling an operand by a power of two scales every split plane, product and partial sum exactly, so
+    # the tensor-core product of (4 X) must be 4 times the product of X bit for bit: a check of every
+    # element of a 65536 x 4096 result that needs no reference arithmetic
+    m, k, n = 65536, 1024, 4096
+    rng = np.random.default_rng(11)
+    x = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    w = rng.uniform(-0.05, 0.05, (n, k)).astype(np.float32)
+
+    def product(a):
+        g = GraphBuilder()
+        xv, wv = g.feed(F32, (m, k)), g.feed(F32, (n, k))
+        g.publish(g.matmul(xv, g.permute(wv, (1, 0))))
+        (out,) = run_image(ctx, g, [a, w])
+        return out
+
+    base = product(x)
+    assert np.array_equal(product(x * np.float32(4.0)), base * np.float32(4.0))
+
+
+def test_classifier_head_at_full_size(ctx):
+    rows, classes = 65536, 1000
+    rng = np.random.default_rng(7)
+    logits = (rng.standard_normal((rows, classes)) * 2).astype(np.float32)
+    labels = rng.integers(0, classes, rows).astype(np.int32)
+    g = GraphBuilder()
+    lv, yv, sv = g.feed(F32, (rows, classes)), g.feed(I32, (rows,)), g.feed(F32, ())
+    g.publish(g.index_cross_entropy(lv, yv))
+    g.publish(g.index_cross_entropy_backward(lv, yv, sv))
+    g.publish(g.arg_max(lv, 1))
+    loss, grad, best = run_image(ctx, g, [logits, labels, np.array(1.0, dtype=np.float32)])
+    # index output: bit-exact against first-index arg-max over every row
+    assert np.array_equal(best, np.argmax(logits, axis=1).astype(np.int64))
+    # loss against binary64 log-sum-exp over every row
+    l64 = logits.astype(np.float64)
+    mx = l64.max(axis=1)
+    lse = mx + np.log(np.exp(l64 - mx[:, None]).sum(axis=1))
+    ref_loss = float((lse - l64[np.arange(rows), labels]).mean())
+    assert abs(float(loss) - ref_loss) <= 1e-6 * abs(ref_loss)
+    # gradient: every row sums to zero up to rounding (softmax minus one-hot), the label entry is
+    # the only negative one, and sampled rows match binary64 arithmetic to 4 ulp of the row's largest entry
+    row_sums = grad.sum(axis=1, dtype=np.float64)
+    assert np.all(np.abs(row_sums) <= 64 * TWO_M24 / rows)
+    assert np.all(grad[np.arange(rows), labels] < 0.0)
+    assert int((grad < 0.0).sum()) == rows
+    sample = rng.choice(rows, 64, replace=False)
+    p = np.exp(l64[sample] - lse[sample][:, None])
+    p[np.arange(len(sample)), labels[sample]] -= 1.0
+    ref_grad = p / rows
+    tol = 4 * TWO_M24 * np.abs(ref_grad).max(axis=1, keepdims=True) + 4 * TWO_M24 * np.abs(ref_grad)
+    assert np.all(np.abs(grad[sample] - ref_grad) <= tol)
+
+
+def test_classifier_inference_at_full_size(ctx):
+    # BASELINE inference configuration: 784-4096-4096-4096-10, batch 8192 per GPU, arg-max published
+    from synaptik_b200 import nn
+    dims, batch = [784, 4096, 4096, 4096, 10], 8192
+    rng = np.random.default_rng(21)
+    model = nn.Model(dims, ctx, seed=3)
+    # biases start at zero in the reference's initialisation; give them values so the epilogue is exercised
+    params = model.parameters()
+    for i in range(1, len(params), 2):
+        params[i] = rng.uniform(-0.1, 0.1, params[i].shape).astype(np.float32)
+    model.load_parameters(params)
+    x = rng.uniform(0, 1, (batch, dims[0])).astype(np.float32)
+    logits, best = model.compute(x, arg_max=True)
+    # binary64 forward pass of sampled rows with the model's own parameters
+    sample = rng.choice(batch, 32, replace=False)
+    h = x[sample].astype(np.float64)
+    weights, biases = params[0::2], params[1::2]
+    for layer, (w, b) in enumerate(zip(weights, biases)):
+        h = h @ w.astype(np.float64).T + b.astype(np.float64)
+        if layer + 1 < len(weights):
+            h = np.maximum(h, 0.0)
+    assert np.all(np.abs(logits[sample] - h) <= 2e-5 * np.abs(h).max())
+    # index output: bit-exact arg-max of the device's own logits, over every row
+    assert np.array_equal(best, np.argmax(logits, axis=1).astype(np.int64))
+    model.close()
