@@ -102,6 +102,14 @@ SYNAPTIK_CUDA_API int32_t synaptik_cuda_buffer_download_canonical(void *buffer, 
  * stream and return at once; synaptik_cuda_context_synchronize orders the host after them. */
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_buffer_upload_async(void *buffer, uint64_t offset, const void *source, uint64_t bytes);
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_buffer_download_async(void *buffer, uint64_t offset, void *destination, uint64_t bytes);
+/* Upload from pinned host memory on the context's copy stream, concurrently with the work already
+ * enqueued on the compute stream (a training loop fills the next batch's buffers while the current
+ * step runs; no counterpart in the Metal ABI, whose memory is unified).  Ordering is by buffer: the
+ * copy starts after every executable run enqueued so far that was bound to this buffer, and every
+ * later run bound to it (and every later upload / download of it) starts after the copy.
+ * synaptik_cuda_context_synchronize also waits for prefetches.  Optimizer steps are not tracked: do
+ * not prefetch into a parameter or gradient buffer. */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_buffer_prefetch(void *buffer, uint64_t offset, const void *source, uint64_t bytes);
 /* Device address and size of a buffer, for callers that share it with other CUDA code. */
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_buffer_device_pointer(void *buffer, uint64_t *out_address, uint64_t *out_bytes);
 /* Page-locked host memory for staging (EngineBackendComposition.borrow :118 uploads from it). */

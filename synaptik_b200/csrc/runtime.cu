@@ -31,7 +31,7 @@ struct Context {
     uint32_t tag = TAG_CONTEXT;
     int device = 0;
     int sm_count = 148;
-    cudaStream_t stream = nullptr, comm_stream = nullptr;
+    cudaStream_t stream = nullptr, comm_stream = nullptr, copy_stream = nullptr;
     int *error_dev = nullptr;       // device-side error word shared by all kernels of the context
     int *error_host = nullptr;      // pinned mirror
     int gemm_engine = 0;
@@ -49,6 +49,10 @@ struct Buffer {
     Context *ctx = nullptr;
     void *ptr = nullptr;
     uint64_t bytes = 0;
+    // prefetch ordering (created on first use): `filled` is recorded on the copy stream after a
+    // prefetch, `released` on the compute stream after every executable run bound to the buffer
+    cudaEvent_t filled = nullptr, released = nullptr;
+    bool fill_pending = false, release_recorded = false;
 };
 
 // ---- NCCL, bound at run time so the library loads (and inference runs) without it ---------------
@@ -367,6 +371,11 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
     };
     x->launches = 0;
     x->run_counter++;
+    // buffers filled by a prefetch on the copy stream: this run (and, by stream order, every later
+    // one) starts after the copy
+    for (const std::vector<Buffer *> *group : {&bind.feeds, &bind.publications})
+        for (Buffer *b : *group)
+            if (b->fill_pending) { cudaStreamWaitEvent(s, b->filled, 0); b->fill_pending = false; }
     cudaEventRecord(x->start, s);
     int ready_cursor = 0;
     const bool time_steps = ctx->time_steps != 0;
@@ -520,6 +529,10 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
         cudaStreamWaitEvent(s, x->comm_done, 0);
     }
     cudaEventRecord(x->stop, s);
+    // a later prefetch into one of these buffers has to wait for this run
+    for (const std::vector<Buffer *> *group : {&bind.feeds, &bind.publications})
+        for (Buffer *b : *group)
+            if (b->released) { cudaEventRecord(b->released, s); b->release_recorded = true; }
     x->timed = true;
     x->pending = true;
     return OK;
@@ -575,7 +588,8 @@ int32_t synaptik_cuda_context_create(int32_t device_ordinal, void **out_context)
     ctx->sm_count = prop.multiProcessorCount;
     if (const char *e = getenv("SYNAPTIK_CUDA_GEMM_PAIR")) ctx->gemm_pair = atoi(e) != 0;      // test hook for the default
     if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess
-        || cudaStreamCreateWithFlags(&ctx->comm_stream, cudaStreamNonBlocking) != cudaSuccess) { cudaGetLastError(); delete ctx; return NO_STREAM; }
+        || cudaStreamCreateWithFlags(&ctx->comm_stream, cudaStreamNonBlocking) != cudaSuccess
+        || cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking) != cudaSuccess) { cudaGetLastError(); delete ctx; return NO_STREAM; }
     if (cudaMalloc(&ctx->error_dev, sizeof(int)) != cudaSuccess || cudaMallocHost(&ctx->error_host, sizeof(int)) != cudaSuccess
         || cudaMemset(ctx->error_dev, 0, sizeof(int)) != cudaSuccess) { cudaGetLastError(); delete ctx; return ALLOCATION_FAILED; }
     *out_context = ctx;
@@ -590,6 +604,7 @@ int32_t synaptik_cuda_context_release(void *context) {
     cudaStreamSynchronize(ctx->comm_stream);
     cudaStreamDestroy(ctx->stream);
     cudaStreamDestroy(ctx->comm_stream);
+    cudaStreamDestroy(ctx->copy_stream);
     cudaFree(ctx->error_dev);
     cudaFreeHost(ctx->error_host);
     if (ctx->timer_start) cudaEventDestroy(ctx->timer_start);
@@ -617,6 +632,7 @@ int32_t synaptik_cuda_context_synchronize(void *context) {
     DeviceGuard guard(ctx->device);
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->comm_stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->copy_stream);
     return cuda_status(e, EXECUTION_FAILED);
 }
 
@@ -660,6 +676,9 @@ int32_t synaptik_cuda_buffer_release(void *buffer) {
     if (!b) return INVALID_ARGUMENT;
     DeviceGuard guard(b->ctx->device);
     cudaStreamSynchronize(b->ctx->stream);
+    cudaStreamSynchronize(b->ctx->copy_stream);
+    if (b->filled) cudaEventDestroy(b->filled);
+    if (b->released) cudaEventDestroy(b->released);
     cudaFree(b->ptr);
     b->tag = 0;
     delete b;
@@ -673,6 +692,7 @@ static int32_t transfer(void *buffer, uint64_t offset, void *host, uint64_t byte
     if (!bytes) return OK;
     DeviceGuard guard(b->ctx->device);
     uint8_t *dev = (uint8_t *)b->ptr + offset;
+    if (b->fill_pending) { cudaStreamWaitEvent(b->ctx->stream, b->filled, 0); b->fill_pending = false; }
     cudaError_t e = upload ? cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, b->ctx->stream)
                            : cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, b->ctx->stream);
     if (e == cudaSuccess && !async) e = cudaStreamSynchronize(b->ctx->stream);
@@ -691,6 +711,26 @@ int32_t synaptik_cuda_buffer_upload_async(void *buffer, uint64_t offset, const v
 }
 int32_t synaptik_cuda_buffer_download_async(void *buffer, uint64_t offset, void *destination, uint64_t bytes) {
     return transfer(buffer, offset, destination, bytes, false, true);
+}
+
+int32_t synaptik_cuda_buffer_prefetch(void *buffer, uint64_t offset, const void *source, uint64_t bytes) {
+    Buffer *b = as<Buffer>(buffer, TAG_BUFFER);
+    if (!b || (!source && bytes)) return INVALID_ARGUMENT;
+    if (offset > b->bytes || bytes > b->bytes - offset) return RANGE_OUT_OF_BOUNDS;
+    if (!bytes) return OK;
+    Context *ctx = b->ctx;
+    std::lock_guard<std::mutex> lock(ctx->mutex);
+    DeviceGuard guard(ctx->device);
+    if (!b->filled && (cudaEventCreateWithFlags(&b->filled, cudaEventDisableTiming) != cudaSuccess
+                       || cudaEventCreateWithFlags(&b->released, cudaEventDisableTiming) != cudaSuccess)) { cudaGetLastError(); return INTERNAL_ERROR; }
+    // the copy may not overtake the runs already enqueued that read or write this buffer
+    cudaError_t e = cudaSuccess;
+    if (b->release_recorded) e = cudaStreamWaitEvent(ctx->copy_stream, b->released, 0);
+    if (e == cudaSuccess) e = cudaMemcpyAsync((uint8_t *)b->ptr + offset, source, bytes, cudaMemcpyHostToDevice, ctx->copy_stream);
+    if (e == cudaSuccess) e = cudaEventRecord(b->filled, ctx->copy_stream);
+    if (e != cudaSuccess) { cudaGetLastError(); return COPY_FAILED; }
+    b->fill_pending = true;
+    return OK;
 }
 
 int32_t synaptik_cuda_buffer_upload_canonical(void *buffer, uint64_t offset, const void *source, uint64_t bytes, uint32_t element_bytes) {

@@ -33,7 +33,7 @@ SYMBOLS = [
     "synaptik_cuda_buffer_create", "synaptik_cuda_buffer_release", "synaptik_cuda_buffer_upload",
     "synaptik_cuda_buffer_download", "synaptik_cuda_buffer_upload_canonical",
     "synaptik_cuda_buffer_download_canonical", "synaptik_cuda_buffer_upload_async",
-    "synaptik_cuda_buffer_download_async", "synaptik_cuda_buffer_device_pointer",
+    "synaptik_cuda_buffer_download_async", "synaptik_cuda_buffer_prefetch", "synaptik_cuda_buffer_device_pointer",
     "synaptik_cuda_host_alloc", "synaptik_cuda_host_free",
     "synaptik_cuda_executable_create", "synaptik_cuda_executable_release", "synaptik_cuda_executable_run",
     "synaptik_cuda_executable_enqueue", "synaptik_cuda_executable_finish", "synaptik_cuda_program_describe",
@@ -150,6 +150,11 @@ class Buffer:
 
     def upload_async(self, pointer: int, nbytes: int, offset: int = 0) -> None:
         _check("buffer_upload_async", library().synaptik_cuda_buffer_upload_async(
+            self._h, ctypes.c_uint64(offset), ctypes.c_void_p(pointer), ctypes.c_uint64(nbytes)))
+
+    def prefetch(self, pointer: int, nbytes: int, offset: int = 0) -> None:
+        """Upload from pinned memory on the copy stream, overlapping the compute stream's work."""
+        _check("buffer_prefetch", library().synaptik_cuda_buffer_prefetch(
             self._h, ctypes.c_uint64(offset), ctypes.c_void_p(pointer), ctypes.c_uint64(nbytes)))
 
     def download_async(self, pointer: int, nbytes: int, offset: int = 0) -> None:

@@ -327,6 +327,45 @@ def test_mse_matches_the_checker(ctx, oracle):
     assert np.array_equal(grad, oracle.mse_backward(p, t))
 
 
+def test_prefetch_overlaps_and_stays_ordered(ctx):
+    # double-buffered feeding: while run i is enqueued, the operands of run i + 1 are copied on the
+    # copy stream into the other buffer; a prefetch into a buffer waits for the run that still reads it,
+    # and a run waits for the prefetch of its buffer.  Nothing is synchronised until the end.
+    m, k, n = 256, 512, 384
+    rng = np.random.default_rng(17)
+    g = matmul_graph(m, k, n)
+    exe = native.Executable(ctx, g.build())
+    b_host = rng.integers(-3, 4, (k, n)).astype(np.float32)
+    b_buf = ctx.upload(b_host)
+    a_bufs = [ctx.buffer(m * k * 4), ctx.buffer(m * k * 4)]
+    steps = 6
+    hosts, outs = [], []
+    for i in range(steps):
+        pinned = native.PinnedArray((m, k), np.float32)
+        pinned.array[...] = rng.integers(-3, 4, (m, k)).astype(np.float32)
+        hosts.append(pinned)
+        outs.append(ctx.buffer(m * n * 4))
+    a_bufs[0].prefetch(hosts[0].pointer, hosts[0].nbytes)
+    for i in range(steps):
+        if i + 1 < steps:
+            a_bufs[(i + 1) & 1].prefetch(hosts[i + 1].pointer, hosts[i + 1].nbytes)
+        exe.enqueue([a_bufs[i & 1], b_buf], [outs[i]])
+    exe.finish()
+    for i in range(steps):
+        want = (hosts[i].array.astype(np.int64) @ b_host.astype(np.int64)).astype(np.float32)
+        assert np.array_equal(outs[i].download(np.float32, (m, n)), want), i
+    # a plain upload after a prefetch of the same buffer lands after it
+    a_bufs[0].prefetch(hosts[1].pointer, hosts[1].nbytes)
+    a_bufs[0].upload(hosts[2].array)
+    assert np.array_equal(a_bufs[0].download(np.float32, (m, k)), hosts[2].array)
+    ctx.synchronize()
+    exe.close()
+    for h in hosts:
+        h.close()
+    for b in a_bufs + outs + [b_buf]:
+        b.close()
+
+
 # ---- buffers and error statuses -----------------------------------------------------------------
 def test_buffers_canonical_bytes_and_errors(ctx):
     values = np.array([1.0, -2.5, 3.25e-3, 7e8], dtype=np.float32)
