@@ -36,7 +36,12 @@ cudaError_t relu_backward(cudaStream_t s, const float *gate, const float *upstre
 // Column sums of a dense [rows, cols] matrix, accumulated in binary64 and rounded once.
 // partials must hold colsum_partial_count(rows, cols) doubles.
 int64_t colsum_partial_count(int64_t rows, int64_t cols);
-cudaError_t colsum(cudaStream_t s, const float *g, int64_t rows, int64_t cols, double *partials, float *out);
+// With plane_hi / plane_lo set (row pitch `pitch` floats, columns past `cols` already zero) the same pass
+// also writes the hi / lo operand planes of g for the tensor-core products that read it; allowed when
+// colsum_can_split(g, cols, pitch).
+bool colsum_can_split(const float *g, int64_t cols, int64_t pitch);
+cudaError_t colsum(cudaStream_t s, const float *g, int64_t rows, int64_t cols, double *partials, float *out,
+                   float *plane_hi = nullptr, float *plane_lo = nullptr, int64_t pitch = 0);
 // The same two column-sum kernels, with the partial sums kept in a fixed file-scope device array
 // (kStaticColsumPartials doubles, 2 MiB, resident on every GPU that loads the library) so that the
 // call performs no allocation at all.  `device` must be the current device.  Returns

@@ -10,6 +10,7 @@
 //    that issues lo*hi, hi*lo and hi*hi into one accumulator (3xTF32).  The dropped lo*lo term is
 //    below 2^-22 of each product.
 #include "kernels.hpp"
+#include "split.cuh"
 
 #include <cuda.h>
 
@@ -94,22 +95,6 @@ __global__ void __launch_bounds__(256) gemm_exact_kernel(int64_t m, int64_t n, i
 // ------------------------------------------------------------------------------------------------
 // hi / lo split into zero-padded K-major planes.
 // ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ float to_tf32(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return __uint_as_float(r);
-}
-__device__ __forceinline__ bool finite_f(float x) { return (__float_as_uint(x) & 0x7f800000u) != 0x7f800000u; }
-__device__ __forceinline__ void split_value(float x, float &hi, float &lo) {
-    float h = to_tf32(x);
-    if (!finite_f(h)) {
-        if (!finite_f(x)) { hi = x; lo = 0.0f; return; }            // inf / NaN pass through the hi plane only
-        h = __uint_as_float(__float_as_uint(x) & 0xffffe000u);      // rounding up would overflow: truncate instead
-    }
-    hi = h;
-    lo = to_tf32(__fsub_rn(x, h));                                  // x - hi is exact in binary32
-}
-
 __global__ void split_rows_kernel(const float *__restrict__ src, int64_t rows, int64_t cols, int64_t rs,
                                   float *hi, float *lo, int64_t cp, int vec_ok) {
     const int64_t quads = cp >> 2, total = rows * quads;

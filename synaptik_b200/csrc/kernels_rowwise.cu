@@ -3,6 +3,7 @@
 // passes.  All use coalesced (128-bit where alignment allows) accesses and warp-shuffle
 // reductions; none uses tensor cores on purpose -- they are bounded by HBM bandwidth.
 #include "kernels.hpp"
+#include "split.cuh"
 
 #include <cfloat>
 #include <cmath>
@@ -385,7 +386,12 @@ __global__ void relu_backward_kernel(const float4 *__restrict__ gate, const floa
 // in binary64 and writes one partial per column; phase 2 adds the partials of each column in a
 // fixed order and rounds once.  Deterministic, no atomics.
 constexpr int kColsumRows = 8;     // warps per block, each striding over rows
-__global__ void colsum_partial_kernel(const float *__restrict__ g, int64_t rows, int64_t cols, int64_t rows_per, double *partials) {
+// PLANES: the pass also writes the hi / lo operand planes (row pitch `pitch`) of the matrix it reads,
+// so a gradient that is both summed over rows (bias gradient) and fed to tensor-core products is read
+// from HBM once for both.
+template <bool PLANES>
+__global__ void colsum_partial_kernel(const float *__restrict__ g, int64_t rows, int64_t cols, int64_t rows_per, double *partials,
+                                      float *hi, float *lo, int64_t pitch) {
     __shared__ double sm[kColsumRows][128];
     int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     int64_t col0 = (int64_t)blockIdx.x * 128 + lane * 4;
@@ -393,9 +399,33 @@ __global__ void colsum_partial_kernel(const float *__restrict__ g, int64_t rows,
     double a0 = 0, a1 = 0, a2 = 0, a3 = 0;
     bool vec = (cols & 3) == 0 && col0 + 3 < cols && ((uintptr_t)g & 15) == 0;
     if (vec) {
-        for (int64_t r = r0 + w; r < r1; r += kColsumRows) {
+        // four rows per trip, their loads issued together: one row in flight per warp left the pass
+        // latency-bound once it also wrote the planes
+        int64_t r = r0 + w;
+        for (; r + 3 * kColsumRows < r1; r += 4 * kColsumRows) {
+            float4 v[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) v[q] = *reinterpret_cast<const float4 *>(g + (r + q * kColsumRows) * cols + col0);
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                a0 += v[q].x; a1 += v[q].y; a2 += v[q].z; a3 += v[q].w;
+                if (PLANES) {
+                    float4 h, l;
+                    split_value(v[q].x, h.x, l.x); split_value(v[q].y, h.y, l.y); split_value(v[q].z, h.z, l.z); split_value(v[q].w, h.w, l.w);
+                    *reinterpret_cast<float4 *>(hi + (r + q * kColsumRows) * pitch + col0) = h;
+                    *reinterpret_cast<float4 *>(lo + (r + q * kColsumRows) * pitch + col0) = l;
+                }
+            }
+        }
+        for (; r < r1; r += kColsumRows) {
             float4 v = *reinterpret_cast<const float4 *>(g + r * cols + col0);
             a0 += v.x; a1 += v.y; a2 += v.z; a3 += v.w;
+            if (PLANES) {
+                float4 h, l;
+                split_value(v.x, h.x, l.x); split_value(v.y, h.y, l.y); split_value(v.z, h.z, l.z); split_value(v.w, h.w, l.w);
+                *reinterpret_cast<float4 *>(hi + r * pitch + col0) = h;
+                *reinterpret_cast<float4 *>(lo + r * pitch + col0) = l;
+            }
         }
     } else {
         for (int64_t r = r0 + w; r < r1; r += kColsumRows) {
@@ -767,12 +797,22 @@ cudaError_t relu_backward(cudaStream_t s, const float *gate, const float *upstre
 
 int64_t colsum_partial_count(int64_t rows, int64_t cols) { return colsum_splits(rows, cols) * cols; }
 
-cudaError_t colsum(cudaStream_t s, const float *g, int64_t rows, int64_t cols, double *partials, float *out) {
+bool colsum_can_split(const float *g, int64_t cols, int64_t pitch) {
+    return (cols & 3) == 0 && (pitch & 3) == 0 && ((uintptr_t)g & 15) == 0;
+}
+
+cudaError_t colsum(cudaStream_t s, const float *g, int64_t rows, int64_t cols, double *partials, float *out,
+                   float *plane_hi, float *plane_lo, int64_t pitch) {
     if (cols == 0) return cudaSuccess;
     int64_t splits = colsum_splits(rows, cols);
     int64_t rows_per = (rows + splits - 1) / splits;
     dim3 grid((unsigned)((cols + 127) / 128), (unsigned)splits);
-    colsum_partial_kernel<<<grid, kColsumRows * 32, 0, s>>>(g, rows, cols, rows_per, partials);
+    if (plane_hi) {
+        if (!colsum_can_split(g, cols, pitch) || !plane_lo) return cudaErrorInvalidValue;
+        colsum_partial_kernel<true><<<grid, kColsumRows * 32, 0, s>>>(g, rows, cols, rows_per, partials, plane_hi, plane_lo, pitch);
+    } else {
+        colsum_partial_kernel<false><<<grid, kColsumRows * 32, 0, s>>>(g, rows, cols, rows_per, partials, nullptr, nullptr, 0);
+    }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     colsum_final_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, s>>>(partials, splits, cols, out);
@@ -804,7 +844,7 @@ cudaError_t colsum_static(cudaStream_t s, int device, const float *g, int64_t ro
     }
     // phase 1 writes every partial that phase 2 reads, so nothing of an earlier call survives and
     // nothing has to be cleared first
-    return colsum(s, g, rows, cols, partials, out);
+    return colsum(s, g, rows, cols, partials, out, nullptr, nullptr, 0);
 }
 
 cudaError_t cross_entropy(cudaStream_t s, const float *logits, DType label_type, const void *labels, const float *seed,

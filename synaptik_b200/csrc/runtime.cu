@@ -268,6 +268,10 @@ int32_t prepare_executable(Executable *x) {
         p.rows = rows; p.kp = kern::padded_k(k); p.pitch = kern::plane_pitch(p.kp);
         void *hi, *lo;
         if (!alloc((uint64_t)rows * p.pitch * 4, &hi) || !alloc((uint64_t)rows * p.pitch * 4, &lo)) return -1;
+        // padding columns are zero from the start: the pass that fills planes beside the column sums
+        // only writes the real columns
+        if (cudaMemsetAsync(hi, 0, (uint64_t)rows * p.pitch * 4, ctx->stream) != cudaSuccess
+            || cudaMemsetAsync(lo, 0, (uint64_t)rows * p.pitch * 4, ctx->stream) != cudaSuccess) return -1;
         p.hi = (float *)hi; p.lo = (float *)lo;
         x->planes.push_back(p);
         x->plane_index[key] = (int)x->planes.size() - 1;
@@ -483,10 +487,23 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                 LAUNCH(kern::full_sum(s, (const float *)ptr(st.a), ix, st.m, (float *)ptr(st.out)));
                 break;
             }
-            case StepKind::COLSUM:
-                LAUNCH(kern::colsum(s, (const float *)ptr(st.a), st.m, st.n, se.colsum_partials, (float *)ptr(st.out)));
+            case StepKind::COLSUM: {
+                // a gradient that tensor-core products read as row planes is split in the same pass
+                float *hi = nullptr, *lo = nullptr; int64_t pitch = 0;
+                const View &v = plan.views[st.a];
+                if (v.shape.size() == 2 && v.dense()) {
+                    auto it = x->plane_index.find(plane_key(v, 0));
+                    if (it != x->plane_index.end()) {
+                        Planes &pl = x->planes[it->second];
+                        if (pl.last_run != x->run_counter && pl.rows == st.m && kern::colsum_can_split((const float *)ptr(st.a), st.n, pl.pitch)) {
+                            hi = pl.hi; lo = pl.lo; pitch = pl.pitch; pl.last_run = x->run_counter;
+                        }
+                    }
+                }
+                LAUNCH(kern::colsum(s, (const float *)ptr(st.a), st.m, st.n, se.colsum_partials, (float *)ptr(st.out), hi, lo, pitch));
                 x->launches++;
                 break;
+            }
             case StepKind::SOFTMAX:
                 LAUNCH(kern::softmax_rows(s, (const float *)ptr(st.a), (float *)ptr(st.out), st.m, st.n));
                 break;
