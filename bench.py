@@ -301,7 +301,12 @@ def run_cuda(args):
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": "gemm_tf32x3_pair_kernel", "achieved": achieved, "peak": emulated_peak, "unit": "TFLOP/s",
-                         "frac": achieved / emulated_peak if emulated_peak else None, "traffic": None,
+                         "frac": achieved / emulated_peak if emulated_peak else None,
+                         # DRAM bytes per launch (read + written, mean over the step's 8 GEMM launches) from the
+                         # committed ncu capture of exactly these launches; other shapes were not captured
+                         "traffic": 8.67e9 if rows == GLOBAL_BATCH else None,
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, profiles/train_step_launch_list.md" if rows == GLOBAL_BATCH else None,
+                         "algorithmic_bytes_per_launch": 28.7e9 / 8 if rows == GLOBAL_BATCH else None,
                          "peak_source": f"{peak_kind} bf16_tflops_sustained / 2 (TF32) / 3 (3xTF32)",
                          "launches_per_step": gemm_launches, "ms_per_step_in_kernel": ms,
                          "step_time_shares": {k: v / total_step for k, v in sorted(shares.items())},
