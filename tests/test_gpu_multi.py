@@ -1,5 +1,6 @@
-"""Two-rank data-parallel training on two B200s (skipped with fewer): every rank must end with the
-same parameters, and they must match a single-rank run on the whole batch within the GEMM tolerance."""
+"""Data-parallel training on 2, 4 and 8 B200s (as many as the box has; skipped with one): after every
+one of 20 Adam steps the ranks must hold identical parameters, and those must match a single-rank
+run on the whole batch within the GEMM tolerance."""
 import json
 import os
 import subprocess
@@ -32,18 +33,19 @@ rng = np.random.default_rng(5)
 x = rng.uniform(0, 1, (batch, dims[0])).astype(np.float32)
 labels = rng.integers(0, 10, batch)
 rows = batch // world
-losses = []
-for step in range(5):
+losses, history, same = [], [], True
+for step in range(20):
     losses.append(model.train(x[rank * rows:(rank + 1) * rows], labels[rank * rows:(rank + 1) * rows]))
-params = np.concatenate([p.reshape(-1) for p in model.parameters()])
-t = torch.from_numpy(params).cuda()
-gathered = [torch.empty_like(t) for _ in range(world)]
-dist.all_gather(gathered, t)
+    params = np.concatenate([p.reshape(-1) for p in model.parameters()])
+    history.append(params)
+    t = torch.from_numpy(params).cuda()
+    gathered = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(gathered, t)
+    same = same and all(bool(torch.equal(gathered[0], g)) for g in gathered)
 l = torch.tensor(losses, dtype=torch.float64, device="cuda")
 dist.all_reduce(l)
 if rank == 0:
-    same = all(bool(torch.equal(gathered[0], g)) for g in gathered)
-    np.save(os.environ["SYN_OUT"] + f".w{world}.npy", params)
+    np.save(os.environ["SYN_OUT"] + f".w{world}.npy", np.stack(history))
     json.dump({"replicas_identical": same, "losses": (l / world).tolist()}, open(os.environ["SYN_OUT"] + f".w{world}.json", "w"))
 model.close()
 if comm is not None: comm.close()
@@ -61,18 +63,24 @@ def _run(world, out, port):
     subprocess.run(cmd, env=env, check=True, timeout=600)
 
 
-def test_two_ranks_match_one_rank(tmp_path):
+def test_ranks_match_one_rank_after_every_step(tmp_path):
     import torch
-    if torch.cuda.device_count() < 2:
+    available = torch.cuda.device_count()
+    if available < 2:
         pytest.skip("needs two GPUs")
     out = str(tmp_path / "dp")
     _run(1, out, 29731)
-    _run(2, out, 29733)
-    one, two = np.load(out + ".w1.npy"), np.load(out + ".w2.npy")
-    info1, info2 = json.load(open(out + ".w1.json")), json.load(open(out + ".w2.json"))
-    assert info2["replicas_identical"]
-    # Adam turns gradient rounding differences near zero into fractions of lr: bound the drift per entry
-    # by 2*lr*steps and on average by a rounding-level amount
-    drift = np.abs(one - two)
-    assert drift.max() <= 2e-3 * 5 and drift.mean() <= 1e-5
-    assert np.allclose(info1["losses"], info2["losses"], rtol=2e-4)
+    one = np.load(out + ".w1.npy")                      # [steps, parameters]
+    info1 = json.load(open(out + ".w1.json"))
+    for world in [w for w in (2, 4, 8) if w <= available]:
+        _run(world, out, 29731 + 2 * world)
+        many = np.load(out + f".w{world}.npy")
+        info = json.load(open(out + f".w{world}.json"))
+        assert info["replicas_identical"], world
+        # Adam turns gradient rounding differences near zero into fractions of lr: bound the drift per
+        # entry by 2 * lr * (steps so far) and on average by 1 % of lr per step (the trajectories of two
+        # summation orders drift apart slowly; measured on 4 ranks: 5e-5 after 17 steps), after every step
+        for step in range(one.shape[0]):
+            drift = np.abs(one[step] - many[step])
+            assert drift.max() <= 2e-3 * (step + 1) and drift.mean() <= 1e-5 * (step + 1), (world, step, drift.max(), drift.mean())
+        assert np.allclose(info1["losses"], info["losses"], rtol=2e-4), world
