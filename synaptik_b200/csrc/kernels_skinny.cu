@@ -35,6 +35,7 @@ __global__ void __launch_bounds__(512, 1) narrow_out_kernel(int64_t m, int k, co
         const float *rows[4];
 #pragma unroll
         for (int r = 0; r < 4; r++) rows[r] = a + (r0 + r < m ? r0 + r : m - 1) * lda;
+#pragma unroll 2
         for (int kk = lane * 4; kk < k; kk += 128) {
             float4 x[4];
 #pragma unroll
