@@ -177,14 +177,33 @@ SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_step(void *optimizer, int32_t 
 /* Enqueue-only form; the non-finite flag is then reported by synaptik_cuda_optimizer_finish. */
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_step_enqueue(void *optimizer, int32_t gradient_count, void *const *gradients);
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_finish(void *optimizer);
-/* Completed optimizer steps, and raw little-endian copies of one parameter's moment arrays
- * (slot 0 = momentum / first moment, 1 = second moment) for TrainingState snapshots
- * (TrainingParameter.java:894-941). */
+/* Gradient modes of one training run (modules/training/.../GradientMode.java:4-22 as applied by
+ * TrainingSession.java:583-640).  RESET_AND_STEP (0): update from this run's gradients, drop any
+ * pending sum.  ACCUMULATE (1): pending = pending + gradient (one binary32 addition per element,
+ * TrainingParameter.java:373-390); parameters, moments and the step count do not change.
+ * ACCUMULATE_AND_STEP (2): update from pending + gradient, then clear the pending sum.  A non-finite
+ * sum reports status 11 like any other non-finite intermediate.  zero_grad clears the pending sum
+ * (TrainingSession.zeroGrad, :640-652); accumulated_runs counts the runs in it. */
+enum { SYNAPTIK_CUDA_GRADIENT_RESET_AND_STEP = 0, SYNAPTIK_CUDA_GRADIENT_ACCUMULATE = 1, SYNAPTIK_CUDA_GRADIENT_ACCUMULATE_AND_STEP = 2 };
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_run(void *optimizer, int32_t gradient_mode, int32_t gradient_count, void *const *gradients);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_run_enqueue(void *optimizer, int32_t gradient_mode, int32_t gradient_count, void *const *gradients);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_zero_grad(void *optimizer);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_accumulated_runs(void *optimizer, uint64_t *out_runs);
+/* Completed optimizer steps, and copies of one parameter's optimizer-width arrays for TrainingState
+ * snapshots and restores (TrainingParameter.java:894-941, :1000-1060): slot 0 = momentum / first
+ * moment, 1 = second moment, 2 = pending gradient sum.  The plain forms move raw little-endian
+ * binary32; the _canonical forms move the big-endian element bytes the snapshot stores.
+ * set_progress restores the two counters of a snapshot. */
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_steps(void *optimizer, uint64_t *out_steps);
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_download_state(void *optimizer, int32_t parameter_index, int32_t slot,
                                                void *destination, uint64_t bytes);
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_upload_state(void *optimizer, int32_t parameter_index, int32_t slot,
                                              const void *source, uint64_t bytes, uint64_t completed_steps);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_download_state_canonical(void *optimizer, int32_t parameter_index, int32_t slot,
+                                                         void *destination, uint64_t bytes);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_upload_state_canonical(void *optimizer, int32_t parameter_index, int32_t slot,
+                                                       const void *source, uint64_t bytes);
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_set_progress(void *optimizer, uint64_t completed_steps, uint64_t accumulated_runs);
 
 /* ---- data-parallel communicator (no counterpart in the reference, which is single-device) ----
  * One rank per process and GPU.  unique_id is the 128-byte NCCL id produced by

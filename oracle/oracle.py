@@ -194,6 +194,13 @@ def sgd(parameter, gradient, momentum_buffer=None, lr=0.01, momentum=0.0, dampen
     return status == 0
 
 
+def accumulate(accumulated, gradient):
+    """In-place pending gradient sum (GradientMode.ACCUMULATE); True when committed (all finite)."""
+    assert accumulated.dtype == np.float32 and accumulated.flags.c_contiguous
+    g = _f32(gradient)
+    return lib().syn_oracle_accumulate_f32(ctypes.c_int64(accumulated.size), _p(accumulated), _p(g)) == 0
+
+
 def adam(parameter, gradient, first, second, step, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8,
          weight_decay=0.0, decoupled=False):
     """In-place Adam/AdamW on float32 arrays; ``step`` counts from 1.  True when committed."""

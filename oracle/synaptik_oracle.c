@@ -456,3 +456,21 @@ SYN_EXPORT int syn_oracle_adam_f32(int64_t count, float *parameter, const float 
 }
 
 SYN_EXPORT uint32_t syn_oracle_version(void) { return 1; }
+
+/* ------------------------------------------------------------------------------------------ */
+/* Pending gradient sum of GradientMode.ACCUMULATE / ACCUMULATE_AND_STEP                        */
+/* (modules/training/.../TrainingParameter.java:373-390, applied by TrainingSession.java:601-604): */
+/* candidate[i] = accumulated[i] + gradient[i], one binary32 addition; every candidate must be   */
+/* finite or nothing is committed.  Returns 0, or 1 with the sum left unchanged.                 */
+/* ------------------------------------------------------------------------------------------ */
+SYN_EXPORT int syn_oracle_accumulate_f32(int64_t count, float *accumulated, const float *gradient) {
+    for (int64_t i = 0; i < count; i++) {
+        volatile float candidate = accumulated[i] + gradient[i];
+        if (!isfinite(candidate)) return 1;
+    }
+    for (int64_t i = 0; i < count; i++) {
+        volatile float candidate = accumulated[i] + gradient[i];
+        accumulated[i] = candidate;
+    }
+    return 0;
+}

@@ -56,11 +56,15 @@ cudaError_t cross_entropy(cudaStream_t s, const float *logits, DType label_type,
                           float *grad_out, int64_t *argmax_out, int *error_word);
 
 // ---- optimizers -----------------------------------------------------------------------------
-struct TensorSlot { float *p; const float *g; float *m; float *v; int64_t count; };
-struct SgdArgs { float lr, momentum, dampening, weight_decay; int nesterov, first_step, has_buffer, zero_buffer; };
-struct AdamArgs { float lr, b1, b2, eps, decay, correction1, correction2, decay_factor; int decoupled; };
+// acc: pending gradient sum of the tensor (TrainingParameter.java:373-390), used per `gradient_mode`:
+// 0 the step uses g (and clears acc when clear_acc is set), 2 the step uses acc + g and clears acc.
+struct TensorSlot { float *p; const float *g; float *m; float *v; int64_t count; float *acc; };
+struct SgdArgs { float lr, momentum, dampening, weight_decay; int nesterov, first_step, has_buffer, zero_buffer; int gradient_mode, clear_acc; };
+struct AdamArgs { float lr, b1, b2, eps, decay, correction1, correction2, decay_factor; int decoupled; int gradient_mode, clear_acc; };
 cudaError_t sgd_step(cudaStream_t s, const TensorSlot *slots, int slot_count, const SgdArgs &args, int *error_word);
 cudaError_t adam_step(cudaStream_t s, const TensorSlot *slots, int slot_count, const AdamArgs &args, int *error_word);
+// acc = acc + g for every tensor (GradientMode.ACCUMULATE), one launch; a non-finite sum sets ERR_NON_FINITE.
+cudaError_t accumulate_gradients(cudaStream_t s, const TensorSlot *slots, int slot_count, int *error_word);
 
 // ---- GEMM -------------------------------------------------------------------------------------
 struct GemmEpilogue {

@@ -633,8 +633,11 @@ __global__ void __launch_bounds__(kThreads) sgd_kernel(SlotTable table, SgdArgs 
     bool bad = false;
     for (int64_t i = base + threadIdx.x; i < base + kOptElemsPerBlock && i < s.count; i += kThreads) {
         float p = s.p[i];
+        float g = s.g[i];
+        if (a.gradient_mode == 2) { g = __fadd_rn(s.acc[i], g); bad |= !finite(g); s.acc[i] = 0.0f; }
+        else if (a.clear_acc) s.acc[i] = 0.0f;
         float decay_term = __fmul_rn(a.weight_decay, p);
-        float adjusted = __fadd_rn(s.g[i], decay_term);
+        float adjusted = __fadd_rn(g, decay_term);
         float update = adjusted;
         if (a.momentum != 0.0f) {
             float buf;
@@ -663,6 +666,8 @@ __global__ void __launch_bounds__(kThreads) adam_kernel(SlotTable table, AdamArg
     bool bad = false;
     for (int64_t i = base + threadIdx.x; i < base + kOptElemsPerBlock && i < s.count; i += kThreads) {
         float p = s.p[i], g = s.g[i], basev;
+        if (a.gradient_mode == 2) { g = __fadd_rn(s.acc[i], g); bad |= !finite(g); s.acc[i] = 0.0f; }
+        else if (a.clear_acc) s.acc[i] = 0.0f;
         if (a.decoupled) basev = __fmul_rn(p, a.decay_factor);
         else { g = __fadd_rn(g, __fmul_rn(a.decay, p)); basev = p; }
         float m = __fadd_rn(__fmul_rn(a.b1, s.m[i]), __fmul_rn(one_minus_b1, g));
@@ -676,6 +681,22 @@ __global__ void __launch_bounds__(kThreads) adam_kernel(SlotTable table, AdamArg
         bad |= !finite(p) || !finite(g) || !finite(m) || !finite(sq) || !finite(v) || !finite(mh) || !finite(vh)
                || !finite(den) || !(den > 0.0f) || !finite(num) || !finite(update) || !finite(candidate);
         s.p[i] = candidate; s.m[i] = m; s.v[i] = v;
+    }
+    if (bad) atomicOr(error_word, ERR_NON_FINITE);
+}
+
+// GradientMode.ACCUMULATE (TrainingParameter.java:373-390): the pending sum takes one binary32 addition per run.
+struct NoArgs {};
+__global__ void __launch_bounds__(kThreads) accumulate_kernel(SlotTable table, NoArgs, int *error_word) {
+    int t = 0;
+    while (t + 1 < table.count && (int64_t)blockIdx.x >= table.first_block[t + 1]) t++;
+    const TensorSlot s = table.slot[t];
+    int64_t base = ((int64_t)blockIdx.x - table.first_block[t]) * kOptElemsPerBlock;
+    bool bad = false;
+    for (int64_t i = base + threadIdx.x; i < base + kOptElemsPerBlock && i < s.count; i += kThreads) {
+        float sum = __fadd_rn(s.acc[i], s.g[i]);
+        bad |= !finite(sum);
+        s.acc[i] = sum;
     }
     if (bad) atomicOr(error_word, ERR_NON_FINITE);
 }
@@ -878,6 +899,9 @@ cudaError_t sgd_step(cudaStream_t s, const TensorSlot *slots, int slot_count, co
 }
 cudaError_t adam_step(cudaStream_t s, const TensorSlot *slots, int slot_count, const AdamArgs &args, int *error_word) {
     return launch_slots(s, adam_kernel, slots, slot_count, args, error_word);
+}
+cudaError_t accumulate_gradients(cudaStream_t s, const TensorSlot *slots, int slot_count, int *error_word) {
+    return launch_slots(s, accumulate_kernel, slots, slot_count, NoArgs{}, error_word);
 }
 
 }  // namespace kern

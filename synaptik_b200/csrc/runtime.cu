@@ -152,7 +152,10 @@ struct Optimizer {
     std::vector<Buffer *> params;
     std::vector<uint64_t> counts;
     std::vector<float *> m, v;
+    std::vector<float *> acc;               // pending gradient sums, allocated on the first accumulating run
     uint64_t steps = 0;
+    uint64_t accumulated_runs = 0;          // runs in the pending sum (TrainingSession.java:593-594)
+    bool acc_dirty = false;                 // the pending sums may be non-zero
     bool pending = false;
 };
 
@@ -949,29 +952,51 @@ int32_t synaptik_cuda_optimizer_release(void *optimizer) {
     cudaStreamSynchronize(o->ctx->stream);
     for (float *p : o->m) cudaFree(p);
     for (float *p : o->v) cudaFree(p);
+    for (float *p : o->acc) cudaFree(p);
     o->tag = 0;
     delete o;
     return OK;
 }
 
-int32_t synaptik_cuda_optimizer_step_enqueue(void *optimizer, int32_t gradient_count, void *const *gradients) {
+static int32_t optimizer_enqueue(void *optimizer, int32_t mode, int32_t gradient_count, void *const *gradients) {
     Optimizer *o = as<Optimizer>(optimizer, TAG_OPTIMIZER);
-    if (!o || gradient_count != (int32_t)o->params.size() || !gradients) return INVALID_ARGUMENT;
+    if (!o || gradient_count != (int32_t)o->params.size() || !gradients || mode < 0 || mode > 2) return INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(o->ctx->mutex);
+    DeviceGuard guard(o->ctx->device);
+    if (mode != 0 && o->acc.empty()) {
+        // pending sums start at zero (TrainingParameter.java:103-109)
+        for (size_t i = 0; i < o->params.size(); i++) {
+            void *p = nullptr;
+            uint64_t bytes = o->counts[i] * 4 ? o->counts[i] * 4 : 4;
+            if (cudaMalloc(&p, bytes) != cudaSuccess) { cudaGetLastError(); for (float *q : o->acc) cudaFree(q); o->acc.clear(); return ALLOCATION_FAILED; }
+            cudaMemsetAsync(p, 0, bytes, o->ctx->stream);
+            o->acc.push_back((float *)p);
+        }
+    }
     std::vector<kern::TensorSlot> slots(o->params.size());
     for (size_t i = 0; i < slots.size(); i++) {
         Buffer *g = as<Buffer>(gradients[i], TAG_BUFFER);
         if (!g) return INVALID_ARGUMENT;
         if (g->ctx != o->ctx || g->bytes < o->counts[i] * 4 || g == o->params[i]) return INCOMPATIBLE_RESOURCE;
-        slots[i] = {(float *)o->params[i]->ptr, (const float *)g->ptr, o->m[i], o->v[i], (int64_t)o->counts[i]};
+        slots[i] = {(float *)o->params[i]->ptr, (const float *)g->ptr, o->m[i], o->v[i], (int64_t)o->counts[i],
+                    o->acc.empty() ? nullptr : o->acc[i]};
     }
-    std::lock_guard<std::mutex> lock(o->ctx->mutex);
-    DeviceGuard guard(o->ctx->device);
     cudaError_t e;
+    const int clear_acc = mode == 0 && o->acc_dirty;       // RESET_AND_STEP drops an earlier pending sum
+    if (mode == 1) {
+        e = kern::accumulate_gradients(o->ctx->stream, slots.data(), (int)slots.size(), o->ctx->error_dev);
+        if (e != cudaSuccess) { cudaGetLastError(); return EXECUTION_FAILED; }
+        o->accumulated_runs++;
+        o->acc_dirty = true;
+        o->pending = true;
+        return OK;
+    }
     if (o->kind == 0) {
         kern::SgdArgs a;
         a.lr = (float)o->hyper[0]; a.momentum = (float)o->hyper[1]; a.dampening = (float)o->hyper[2]; a.weight_decay = (float)o->hyper[3];
         a.nesterov = o->hyper[4] != 0.0; a.first_step = o->steps == 0; a.has_buffer = o->hyper[1] != 0.0;
         a.zero_buffer = o->hyper[1] != 0.0 && a.momentum == 0.0f;
+        a.gradient_mode = mode; a.clear_acc = clear_acc;
         e = kern::sgd_step(o->ctx->stream, slots.data(), (int)slots.size(), a, o->ctx->error_dev);
     } else {
         // coefficients narrowed to binary32 first (AdaptiveCoefficients.java:33-58); corrections
@@ -985,11 +1010,47 @@ int32_t synaptik_cuda_optimizer_step_enqueue(void *optimizer, int32_t gradient_c
         a.decoupled = o->kind == 2;
         a.decay_factor = 1.0f;
         if (a.decoupled) { float scale = a.lr * a.decay; a.decay_factor = 1.0f - scale; }
+        a.gradient_mode = mode; a.clear_acc = clear_acc;
         e = kern::adam_step(o->ctx->stream, slots.data(), (int)slots.size(), a, o->ctx->error_dev);
     }
     if (e != cudaSuccess) { cudaGetLastError(); return EXECUTION_FAILED; }
     o->steps++;
+    o->accumulated_runs = 0;
+    o->acc_dirty = false;
     o->pending = true;
+    return OK;
+}
+
+int32_t synaptik_cuda_optimizer_step_enqueue(void *optimizer, int32_t gradient_count, void *const *gradients) {
+    return optimizer_enqueue(optimizer, 0, gradient_count, gradients);
+}
+
+int32_t synaptik_cuda_optimizer_run_enqueue(void *optimizer, int32_t gradient_mode, int32_t gradient_count, void *const *gradients) {
+    return optimizer_enqueue(optimizer, gradient_mode, gradient_count, gradients);
+}
+
+int32_t synaptik_cuda_optimizer_run(void *optimizer, int32_t gradient_mode, int32_t gradient_count, void *const *gradients) {
+    int32_t s = optimizer_enqueue(optimizer, gradient_mode, gradient_count, gradients);
+    if (s != OK) return s;
+    return synaptik_cuda_optimizer_finish(optimizer);
+}
+
+int32_t synaptik_cuda_optimizer_zero_grad(void *optimizer) {
+    Optimizer *o = as<Optimizer>(optimizer, TAG_OPTIMIZER);
+    if (!o) return INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(o->ctx->mutex);
+    DeviceGuard guard(o->ctx->device);
+    for (size_t i = 0; i < o->acc.size(); i++)
+        if (cudaMemsetAsync(o->acc[i], 0, o->counts[i] * 4, o->ctx->stream) != cudaSuccess) { cudaGetLastError(); return EXECUTION_FAILED; }
+    o->accumulated_runs = 0;
+    o->acc_dirty = false;
+    return OK;
+}
+
+int32_t synaptik_cuda_optimizer_accumulated_runs(void *optimizer, uint64_t *out_runs) {
+    Optimizer *o = as<Optimizer>(optimizer, TAG_OPTIMIZER);
+    if (!o || !out_runs) return INVALID_ARGUMENT;
+    *out_runs = o->accumulated_runs;
     return OK;
 }
 
@@ -1015,26 +1076,62 @@ int32_t synaptik_cuda_optimizer_steps(void *optimizer, uint64_t *out_steps) {
     return OK;
 }
 
-static int32_t optimizer_state(void *optimizer, int32_t index, int32_t slot, void *host, uint64_t bytes, bool upload) {
+static int32_t optimizer_state(void *optimizer, int32_t index, int32_t slot, void *host, uint64_t bytes, bool upload, bool canonical) {
     Optimizer *o = as<Optimizer>(optimizer, TAG_OPTIMIZER);
-    if (!o || index < 0 || index >= (int32_t)o->params.size() || slot < 0 || slot > 1 || !host) return INVALID_ARGUMENT;
-    float *dev = slot == 0 ? o->m[index] : o->v[index];
-    if (!dev) return INVALID_ARGUMENT;
+    if (!o || index < 0 || index >= (int32_t)o->params.size() || slot < 0 || slot > 2 || !host) return INVALID_ARGUMENT;
     if (bytes != o->counts[index] * 4) return RANGE_OUT_OF_BOUNDS;
+    std::lock_guard<std::mutex> lock(o->ctx->mutex);
     DeviceGuard guard(o->ctx->device);
-    cudaError_t e = upload ? cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, o->ctx->stream)
-                           : cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, o->ctx->stream);
+    if (slot == 2 && o->acc.empty()) {
+        if (!upload) {                      // no run has accumulated yet: the pending sum is all zeros
+            memset(host, 0, bytes);
+            return OK;
+        }
+        for (size_t i = 0; i < o->params.size(); i++) {
+            void *p = nullptr;
+            uint64_t size = o->counts[i] * 4 ? o->counts[i] * 4 : 4;
+            if (cudaMalloc(&p, size) != cudaSuccess) { cudaGetLastError(); for (float *q : o->acc) cudaFree(q); o->acc.clear(); return ALLOCATION_FAILED; }
+            cudaMemsetAsync(p, 0, size, o->ctx->stream);
+            o->acc.push_back((float *)p);
+        }
+    }
+    float *dev = slot == 0 ? o->m[index] : slot == 1 ? o->v[index] : o->acc[index];
+    if (!dev) return INVALID_ARGUMENT;
+    std::vector<uint8_t> staged;
+    void *side = host;
+    if (canonical) {                        // big-endian FLOAT32 elements, TrainingParameter.java:894-941
+        staged.resize(bytes);
+        if (upload) bswap_copy(staged.data(), (const uint8_t *)host, bytes, 4);
+        side = staged.data();
+    }
+    cudaError_t e = upload ? cudaMemcpyAsync(dev, side, bytes, cudaMemcpyHostToDevice, o->ctx->stream)
+                           : cudaMemcpyAsync(side, dev, bytes, cudaMemcpyDeviceToHost, o->ctx->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(o->ctx->stream);
     if (e != cudaSuccess) { cudaGetLastError(); return COPY_FAILED; }
+    if (canonical && !upload) bswap_copy((uint8_t *)host, staged.data(), bytes, 4);
+    if (upload && slot == 2) o->acc_dirty = true;
     return OK;
 }
 int32_t synaptik_cuda_optimizer_download_state(void *optimizer, int32_t parameter_index, int32_t slot, void *destination, uint64_t bytes) {
-    return optimizer_state(optimizer, parameter_index, slot, destination, bytes, false);
+    return optimizer_state(optimizer, parameter_index, slot, destination, bytes, false, false);
 }
 int32_t synaptik_cuda_optimizer_upload_state(void *optimizer, int32_t parameter_index, int32_t slot, const void *source, uint64_t bytes, uint64_t completed_steps) {
-    int32_t s = optimizer_state(optimizer, parameter_index, slot, const_cast<void *>(source), bytes, true);
+    int32_t s = optimizer_state(optimizer, parameter_index, slot, const_cast<void *>(source), bytes, true, false);
     if (s == OK) as<Optimizer>(optimizer, TAG_OPTIMIZER)->steps = completed_steps;
     return s;
+}
+int32_t synaptik_cuda_optimizer_download_state_canonical(void *optimizer, int32_t parameter_index, int32_t slot, void *destination, uint64_t bytes) {
+    return optimizer_state(optimizer, parameter_index, slot, destination, bytes, false, true);
+}
+int32_t synaptik_cuda_optimizer_upload_state_canonical(void *optimizer, int32_t parameter_index, int32_t slot, const void *source, uint64_t bytes) {
+    return optimizer_state(optimizer, parameter_index, slot, const_cast<void *>(source), bytes, true, true);
+}
+int32_t synaptik_cuda_optimizer_set_progress(void *optimizer, uint64_t completed_steps, uint64_t accumulated_runs) {
+    Optimizer *o = as<Optimizer>(optimizer, TAG_OPTIMIZER);
+    if (!o) return INVALID_ARGUMENT;
+    o->steps = completed_steps;
+    o->accumulated_runs = accumulated_runs;
+    return OK;
 }
 
 // ---- communicator --------------------------------------------------------------------------------

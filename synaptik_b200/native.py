@@ -41,6 +41,9 @@ SYMBOLS = [
     "synaptik_cuda_optimizer_create", "synaptik_cuda_optimizer_release", "synaptik_cuda_optimizer_step",
     "synaptik_cuda_optimizer_step_enqueue", "synaptik_cuda_optimizer_finish", "synaptik_cuda_optimizer_steps",
     "synaptik_cuda_optimizer_download_state", "synaptik_cuda_optimizer_upload_state",
+    "synaptik_cuda_optimizer_run", "synaptik_cuda_optimizer_run_enqueue", "synaptik_cuda_optimizer_zero_grad",
+    "synaptik_cuda_optimizer_accumulated_runs", "synaptik_cuda_optimizer_download_state_canonical",
+    "synaptik_cuda_optimizer_upload_state_canonical", "synaptik_cuda_optimizer_set_progress",
     "synaptik_cuda_comm_unique_id", "synaptik_cuda_comm_create", "synaptik_cuda_comm_release",
     "synaptik_cuda_comm_allreduce_sum_f32", "synaptik_cuda_executable_attach_comm",
     "synaptik_cuda_column_sums_no_alloc",
@@ -288,6 +291,36 @@ class Optimizer:
 
     def finish(self) -> None:
         _check("optimizer_finish", library().synaptik_cuda_optimizer_finish(self._h))
+
+    RESET_AND_STEP, ACCUMULATE, ACCUMULATE_AND_STEP = 0, 1, 2
+
+    def run(self, gradient_mode: int, gradients: Sequence[Buffer]) -> None:
+        """One training run's optimizer side under a GradientMode (TrainingSession.runValues)."""
+        _check("optimizer_run", library().synaptik_cuda_optimizer_run(
+            self._h, ctypes.c_int32(gradient_mode), ctypes.c_int32(len(gradients)), _handles(gradients)))
+
+    def zero_grad(self) -> None:
+        _check("optimizer_zero_grad", library().synaptik_cuda_optimizer_zero_grad(self._h))
+
+    def accumulated_runs(self) -> int:
+        n = ctypes.c_uint64()
+        _check("optimizer_accumulated_runs", library().synaptik_cuda_optimizer_accumulated_runs(self._h, ctypes.byref(n)))
+        return int(n.value)
+
+    def state_canonical(self, index: int, slot: int) -> bytes:
+        """Big-endian FLOAT32 bytes of one optimizer-width array, as TrainingState stores them."""
+        out = ctypes.create_string_buffer(self.counts[index] * 4)
+        _check("optimizer_download_state_canonical", library().synaptik_cuda_optimizer_download_state_canonical(
+            self._h, ctypes.c_int32(index), ctypes.c_int32(slot), out, ctypes.c_uint64(self.counts[index] * 4)))
+        return out.raw
+
+    def restore_canonical(self, index: int, slot: int, data: bytes) -> None:
+        _check("optimizer_upload_state_canonical", library().synaptik_cuda_optimizer_upload_state_canonical(
+            self._h, ctypes.c_int32(index), ctypes.c_int32(slot), data, ctypes.c_uint64(len(data))))
+
+    def set_progress(self, completed_steps: int, accumulated_runs: int) -> None:
+        _check("optimizer_set_progress", library().synaptik_cuda_optimizer_set_progress(
+            self._h, ctypes.c_uint64(completed_steps), ctypes.c_uint64(accumulated_runs)))
 
     def steps(self) -> int:
         n = ctypes.c_uint64()

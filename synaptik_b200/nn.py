@@ -154,15 +154,45 @@ class Model:
             self._training[batch] = (exe, x, t, seed, loss, grads)
         return self._training[batch]
 
-    def train(self, x: np.ndarray, target: np.ndarray) -> float:
-        """Model.train: one RESET_AND_STEP on the batch; returns the objective (this rank's mean)."""
+    def train(self, x: np.ndarray, target: np.ndarray, gradient_mode: int = native.Optimizer.RESET_AND_STEP) -> float:
+        """Model.train / TrainingSession.runValues: one run on the batch under a GradientMode
+        (RESET_AND_STEP by default); returns the objective (this rank's mean)."""
         x = np.ascontiguousarray(x, dtype=np.float32)
         exe, xbuf, tbuf, seed, loss, grads = self.training_state(x.shape[0])
         xbuf.upload(x)
         tbuf.upload(np.ascontiguousarray(target, dtype=np.int32 if self._loss == "ce" else np.float32))
         exe.run([xbuf, tbuf, seed] + self.param_buffers, [loss] + grads)
-        self._optimizer.step(grads)
+        self._optimizer.run(gradient_mode, grads)
         return float(loss.download(np.float32, (1,))[0])
+
+    def zero_grad(self) -> None:
+        """TrainingSession.zeroGrad: drops the pending gradient sum."""
+        self._optimizer.zero_grad()
+
+    def state(self) -> dict:
+        """TrainingSession.state(): detached canonical (big-endian) parameter, optimizer-slot and
+        pending-gradient bytes per parameter plus the two progress counters."""
+        entries = []
+        for index, (buf, shape) in enumerate(zip(self.param_buffers, self.param_shapes)):
+            nbytes = int(np.prod(shape)) * 4
+            entry = {"shape": tuple(shape), "parameter": buf.download_canonical(nbytes, 4),
+                     "momentum": self._optimizer.state_canonical(index, 0),
+                     "accumulated": self._optimizer.state_canonical(index, 2)}
+            if not isinstance(self._optimizer_config, Sgd):
+                entry["second"] = self._optimizer.state_canonical(index, 1)
+            entries.append(entry)
+        return {"optimizer_steps": self._optimizer.steps(), "accumulated_gradient_runs": self._optimizer.accumulated_runs(),
+                "parameters": entries}
+
+    def restore(self, state: dict) -> None:
+        """TrainingSession.restore: the inverse of state()."""
+        for index, (buf, entry) in enumerate(zip(self.param_buffers, state["parameters"])):
+            buf.upload_canonical(entry["parameter"], 4)
+            self._optimizer.restore_canonical(index, 0, entry["momentum"])
+            if "second" in entry:
+                self._optimizer.restore_canonical(index, 1, entry["second"])
+            self._optimizer.restore_canonical(index, 2, entry["accumulated"])
+        self._optimizer.set_progress(state["optimizer_steps"], state["accumulated_gradient_runs"])
 
     def gradients(self, x: np.ndarray, target: np.ndarray):
         """Runs forward and backward without stepping; returns (loss, [dW0, db0, ...])."""

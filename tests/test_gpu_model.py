@@ -177,3 +177,30 @@ def test_inference_with_arg_max(ctx, oracle):
     assert np.abs(logits - ref).max() <= 2e-5 * np.abs(ref).max()
     assert np.array_equal(idx, oracle.argmax(logits))            # bit-exact on the logits the device produced
     model.close()
+
+
+def test_training_state_snapshot_restores_a_run_exactly(ctx):
+    # TrainingSession.state() / restore: a model restored from a snapshot taken mid-accumulation continues
+    # bit for bit like the one it was taken from
+    dims, batch = [32, 64, 10], 128
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal((batch, dims[0])).astype(np.float32)
+    labels = rng.integers(0, 10, batch)
+    a = nn.Model(dims, ctx, seed=5)
+    a.configure_training("ce", nn.Adam(1e-2))
+    a.train(x, labels)
+    a.train(x, labels, native.Optimizer.ACCUMULATE)
+    snapshot = a.state()
+    assert snapshot["optimizer_steps"] == 1 and snapshot["accumulated_gradient_runs"] == 1
+    first = np.frombuffer(snapshot["parameters"][0]["parameter"], ">f4").astype(np.float32).reshape(snapshot["parameters"][0]["shape"])
+    assert np.array_equal(first, a.parameters()[0])                 # canonical bytes are big-endian FLOAT32
+    b = nn.Model(dims, ctx, seed=99)
+    b.configure_training("ce", nn.Adam(1e-2))
+    b.restore(snapshot)
+    for model in (a, b):
+        model.train(x, labels, native.Optimizer.ACCUMULATE_AND_STEP)
+        model.train(x, labels)
+    for pa, pb in zip(a.parameters(), b.parameters()):
+        assert np.array_equal(pa, pb)
+    assert a.optimizer_steps() == b.optimizer_steps() == 3
+    a.close(); b.close()

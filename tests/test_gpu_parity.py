@@ -421,6 +421,111 @@ def test_adam_is_bit_identical_to_the_checker(ctx, oracle):
         opt.close()
 
 
+@pytest.mark.parametrize("kind", ["adam", "sgd"])
+def test_gradient_modes_match_the_checker(ctx, oracle, kind):
+    # ACCUMULATE, ACCUMULATE, ACCUMULATE_AND_STEP, then RESET_AND_STEP after a dangling ACCUMULATE:
+    # pending sums, parameters, moments and counters after every run, bit for bit
+    rng = np.random.default_rng(23)
+    shapes = [(37, 19), (19,), (5000,)]
+    params = [rng.standard_normal(s).astype(np.float32) for s in shapes]
+    bufs = [ctx.upload(p) for p in params]
+    hyper = [1e-3, 0.9, 0.999, 1e-8, 0.0] if kind == "adam" else [0.05, 0.9, 0.0, 0.0, 0.0]
+    opt = native.Optimizer(ctx, 1 if kind == "adam" else 0, hyper, bufs, [p.size for p in params])
+    ref = [p.copy().reshape(-1) for p in params]
+    m = [np.zeros(p.size, np.float32) for p in params]
+    v = [np.zeros(p.size, np.float32) for p in params]
+    acc = [np.zeros(p.size, np.float32) for p in params]
+    steps = 0
+    script = [native.Optimizer.ACCUMULATE, native.Optimizer.ACCUMULATE, native.Optimizer.ACCUMULATE_AND_STEP,
+              native.Optimizer.ACCUMULATE, native.Optimizer.RESET_AND_STEP, native.Optimizer.ACCUMULATE_AND_STEP]
+    runs = 0
+    for mode in script:
+        grads = [(rng.standard_normal(p.size) * 0.1).astype(np.float32) for p in params]
+        gbufs = [ctx.upload(g) for g in grads]
+        opt.run(mode, gbufs)
+        for i, g in enumerate(grads):
+            if mode == native.Optimizer.ACCUMULATE:
+                assert oracle.accumulate(acc[i], g)
+                continue
+            used = g
+            if mode == native.Optimizer.ACCUMULATE_AND_STEP:
+                assert oracle.accumulate(acc[i], g)
+                used = acc[i].copy()
+            if kind == "adam":
+                assert oracle.adam(ref[i], used, m[i], v[i], steps + 1)
+            else:
+                assert oracle.sgd(ref[i], used, m[i], lr=0.05, momentum=0.9, completed_steps=steps)
+            acc[i][...] = 0.0
+        if mode == native.Optimizer.ACCUMULATE:
+            runs += 1
+        else:
+            steps += 1
+            runs = 0
+        assert opt.steps() == steps and opt.accumulated_runs() == runs
+        for i, b in enumerate(bufs):
+            assert np.array_equal(b.download(np.float32, (params[i].size,)), ref[i]), (mode, i)
+            assert np.array_equal(opt.state(i, 0), m[i]) and np.array_equal(opt.state(i, 2), acc[i])
+            if kind == "adam":
+                assert np.array_equal(opt.state(i, 1), v[i])
+        for b in gbufs:
+            b.close()
+    # snapshot bytes are the big-endian FLOAT32 elements TrainingState stores; restoring them round-trips
+    opt.run(native.Optimizer.ACCUMULATE, [ctx.upload(np.full(p.size, 0.25, np.float32)) for p in params])
+    blob = opt.state_canonical(2, 2)
+    assert blob == np.full(params[2].size, 0.25, ">f4").tobytes()
+    opt.zero_grad()
+    assert opt.accumulated_runs() == 0 and not opt.state(2, 2).any()
+    opt.restore_canonical(2, 2, blob)
+    opt.set_progress(steps, 1)
+    assert np.array_equal(opt.state(2, 2), np.full(params[2].size, 0.25, np.float32)) and opt.accumulated_runs() == 1
+    opt.close()
+    for b in bufs:
+        b.close()
+
+
+@pytest.mark.parametrize("decoupled", [False, True])
+def test_gradient_mode_journey_of_the_reference(ctx, oracle, decoupled):
+    # the protocol of AdamOptimizerTest.bothAlgorithmsFollowIndependentMultiStepOracleAndAllGradientModes
+    # (modules/training/src/test/.../AdamOptimizerTest.java:32-66) on a FLOAT32 scalar: objective p * p,
+    # Adam / AdamW(0.1, 0.5, 0.25, 0.01, 0.2); counters as asserted there, values against the checker
+    hyper = dict(lr=0.1, beta1=0.5, beta2=0.25, eps=0.01, weight_decay=0.2, decoupled=decoupled)
+    p_buf = ctx.upload(np.array([2.0], np.float32))
+    opt = native.Optimizer(ctx, 2 if decoupled else 1, [0.1, 0.5, 0.25, 0.01, 0.2], [p_buf], [1])
+    ref, m, v = np.array([2.0], np.float32), np.zeros(1, np.float32), np.zeros(1, np.float32)
+
+    def run(mode):
+        g = ctx.upload(np.float32(2.0) * p_buf.download(np.float32, (1,)))      # d(p * p)/dp at the device's p
+        opt.run(mode, [g])
+        g.close()
+
+    def check():
+        assert np.array_equal(p_buf.download(np.float32, (1,)), ref)
+        assert np.array_equal(opt.state(0, 0), m) and np.array_equal(opt.state(0, 1), v)
+
+    run(native.Optimizer.RESET_AND_STEP)
+    assert oracle.adam(ref, np.array([4.0], np.float32), m, v, 1, **hyper)
+    check()
+    current = np.float32(2.0) * ref.copy()
+    run(native.Optimizer.ACCUMULATE)
+    run(native.Optimizer.ACCUMULATE)
+    assert opt.steps() == 1 and opt.accumulated_runs() == 2
+    check()
+    opt.zero_grad()
+    assert opt.accumulated_runs() == 0
+    run(native.Optimizer.ACCUMULATE)
+    run(native.Optimizer.ACCUMULATE_AND_STEP)
+    assert oracle.adam(ref, current + current, m, v, 2, **hyper)
+    check()
+    assert opt.steps() == 2 and opt.accumulated_runs() == 0
+    grad = np.float32(2.0) * ref.copy()
+    run(native.Optimizer.RESET_AND_STEP)
+    assert oracle.adam(ref, grad, m, v, 3, **hyper)
+    check()
+    assert opt.steps() == 3
+    opt.close()
+    p_buf.close()
+
+
 def test_adam_scales_before_dividing_and_reports_non_finite(ctx):
     gradient, rate = np.float32(1e19), 1e-30
     p = ctx.upload(np.array([1.0], dtype=np.float32))

@@ -219,3 +219,14 @@ def test_mlp_gradients_match_float64_autodiff(oracle):
     assert abs(loss - ref_loss) < 1e-6
     for got, ref in zip(grads, (dw1, db1, dw2, db2)):
         assert np.allclose(got, ref, atol=2e-6, rtol=1e-5)
+
+
+def test_pending_gradient_sum_is_all_or_nothing(oracle):
+    # TrainingParameter.stageAccumulation (TrainingParameter.java:373-390): one binary32 addition per
+    # element, committed only when every candidate is finite
+    acc = np.array([1.0, 2.0 ** -24, 3.0e38], np.float32)
+    assert oracle.accumulate(acc, np.array([2.0 ** -24, 2.0 ** -24, 0.0], np.float32))
+    assert np.array_equal(acc, np.array([1.0, 2.0 ** -23, 3.0e38], np.float32))     # 1 + 2^-24 rounds to even
+    before = acc.copy()
+    assert not oracle.accumulate(acc, np.array([0.0, 0.0, 3.0e38], np.float32))   # overflow: rejected
+    assert np.array_equal(acc, before)
