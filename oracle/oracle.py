@@ -88,6 +88,33 @@ def relu(x) -> np.ndarray:
     return y
 
 
+def tanh(x) -> np.ndarray:
+    x = _f32(x)
+    y = np.empty_like(x)
+    lib().syn_oracle_activation_f32(0, ctypes.c_int64(x.size), _p(x), _p(y))
+    return y
+
+
+def sigmoid(x) -> np.ndarray:
+    x = _f32(x)
+    y = np.empty_like(x)
+    lib().syn_oracle_activation_f32(1, ctypes.c_int64(x.size), _p(x), _p(y))
+    return y
+
+
+def activation_backward(kind: str, output, upstream) -> np.ndarray:
+    """The reference's gradient node lists, one binary32 rounding per node
+    (ElementwiseGradientRules.java:205-206,210): relu where(y > 0, g, 0); tanh g * (1 - y * y);
+    sigmoid (g * y) * (1 - y)."""
+    y, g = _f32(output), _f32(upstream)
+    if kind == "relu":
+        return relu_backward(y, g)
+    one = np.float32(1.0)
+    if kind == "tanh":
+        return (g * (one - (y * y).astype(np.float32)).astype(np.float32)).astype(np.float32)
+    return ((g * y).astype(np.float32) * (one - y).astype(np.float32)).astype(np.float32)
+
+
 def bias_act(u, bias, relu_flag: bool):
     """Returns (z, y): z = u + bias (row broadcast), y = relu(z) or z."""
     u = _f32(u)
@@ -217,17 +244,21 @@ def adam(parameter, gradient, first, second, step, lr=1e-3, beta1=0.9, beta2=0.9
 # --------------------------------------------------------------------------------------------
 # Composite: the training graph the backend is handed (forward, loss, backward), op by op.
 # --------------------------------------------------------------------------------------------
-def mlp_forward(x, weights, biases):
-    """Returns the list of post-activation values [a1..aL] (aL = logits, no ReLU)."""
+def mlp_forward(x, weights, biases, activation: str = "relu"):
+    """Returns the list of post-activation values [a1..aL] (aL = logits, no activation)."""
     acts = []
     a = _f32(x)
     for index, (w, b) in enumerate(zip(weights, biases)):
-        _, a = linear(a, w, b, relu_flag=index + 1 < len(weights))
+        hidden_layer = index + 1 < len(weights)
+        z, a = linear(a, w, b, relu_flag=hidden_layer and activation == "relu")
+        if hidden_layer and activation != "relu":
+            a = tanh(z) if activation == "tanh" else sigmoid(z)
         acts.append(a)
     return acts
 
 
-def mlp_gradients(x, labels_or_target, weights, biases, loss: str = "ce", count: int = 0, hidden=None):
+def mlp_gradients(x, labels_or_target, weights, biases, loss: str = "ce", count: int = 0, hidden=None,
+                  activation: str = "relu"):
     """Loss and gradients of an MLP, executing the reference's backward node lists in order.
 
     Returns (loss, [dW1, db1, dW2, db2, ...], logits).  ``loss`` is "ce" (index cross entropy,
@@ -238,7 +269,7 @@ def mlp_gradients(x, labels_or_target, weights, biases, loss: str = "ce", count:
     branch on another implementation).
     """
     x = _f32(x)
-    acts = mlp_forward(x, weights, biases)
+    acts = mlp_forward(x, weights, biases, activation)
     if hidden is not None:
         acts = [_f32(h) for h in hidden] + [linear(_f32(hidden[-1]), weights[-1], biases[-1], relu_flag=False)[1]]
     logits = acts[-1]
@@ -257,7 +288,7 @@ def mlp_gradients(x, labels_or_target, weights, biases, loss: str = "ce", count:
         if index > 0:
             da = matmul(dz, _f32(weights[index]))
             # z > 0 <=> relu(z) > 0 for every binary32 value, so the stored activation serves
-            dz = relu_backward(a_prev, da)
+            dz = activation_backward(activation, a_prev, da)
     return value, grads, logits
 
 

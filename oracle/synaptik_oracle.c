@@ -474,3 +474,21 @@ SYN_EXPORT int syn_oracle_accumulate_f32(int64_t count, float *accumulated, cons
     }
     return 0;
 }
+
+/* ------------------------------------------------------------------------------------------ */
+/* TANH and SIGMOID on FLOAT32 (modules/backend/cpu/.../reference/CpuScalarReferenceKernel.java   */
+/* :1729-1742): the value widened to double, StrictMath.tanh, or the two-branch sigmoid of        */
+/* CpuScalarEmitter.java:429-439 (1 / (1 + exp(-x)) for x >= 0, exp(x) / (1 + exp(x)) below and   */
+/* for NaN), then one narrowing to float.  glibc stands in for fdlibm as for exp and log.         */
+/* op: 0 = tanh, 1 = sigmoid.                                                                    */
+/* ------------------------------------------------------------------------------------------ */
+SYN_EXPORT void syn_oracle_activation_f32(int op, int64_t count, const float *x, float *y) {
+    for (int64_t i = 0; i < count; i++) {
+        double v = (double)x[i];
+        double r;
+        if (op == 0) r = tanh(v);
+        else if (v < 0.0 || v != v) { double e = exp(v); r = e / (1.0 + e); }
+        else r = 1.0 / (1.0 + exp(-v));
+        y[i] = (float)r;
+    }
+}

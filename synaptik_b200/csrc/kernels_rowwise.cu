@@ -148,10 +148,27 @@ __global__ void scalar_f32_kernel(int op, const float *__restrict__ a, float *ou
     }
 }
 
+// TANH and SIGMOID follow the reference's FLOAT32 path: the elementary function in binary64, one
+// narrowing to binary32 (CpuScalarReferenceKernel.java:1729-1742; sigmoid as 1 / (1 + exp(-x)) for
+// x >= 0 and exp(x) / (1 + exp(x)) below, CpuScalarEmitter.java:429-439).  The device's binary64 tanh
+// and exp are within 1-2 ulp of binary64, so the narrowed result differs from (float)StrictMath only on
+// rounding ties of probability ~2^-28.
+__device__ __forceinline__ float tanh_value(float x) { return (float)tanh((double)x); }
+__device__ __forceinline__ float sigmoid_value(float x) {
+    const double v = (double)x;
+    if (v < 0.0 || v != v) { const double e = exp(v); return (float)(e / (1.0 + e)); }
+    return (float)(1.0 / (1.0 + exp(-v)));
+}
+
 __global__ void unary_kernel(int op, const float *__restrict__ a, float *out, int64_t total) {
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         float x = a[i];
-        out[i] = (Op)op == Op::RELU ? relu_value(x) : exp_accurate(x);
+        switch ((Op)op) {
+            case Op::RELU: out[i] = relu_value(x); break;
+            case Op::TANH: out[i] = tanh_value(x); break;
+            case Op::SIGMOID: out[i] = sigmoid_value(x); break;
+            default: out[i] = exp_accurate(x); break;
+        }
     }
 }
 

@@ -66,9 +66,12 @@ class Model:
     """
 
     def __init__(self, dims: Sequence[int], context: native.Context | None = None, seed: int = 0,
-                 comm: native.Comm | None = None, world_size: int = 1, bias: bool = True):
+                 comm: native.Comm | None = None, world_size: int = 1, bias: bool = True, activation: str = "relu"):
+        if activation not in ("relu", "tanh", "sigmoid"):
+            raise ValueError("activation must be 'relu', 'tanh' or 'sigmoid'")
         self.dims = list(dims)
         self.bias = bias
+        self.activation = activation
         self.layers = len(self.dims) - 1
         self.context = context or native.Context(0)
         self.comm = comm
@@ -103,7 +106,7 @@ class Model:
     def _inference_state(self, batch: int, arg_max: bool):
         key = (batch, arg_max)
         if key not in self._inference:
-            graph = program.mlp_inference_graph(self.dims, batch, arg_max, bias=self.bias)
+            graph = program.mlp_inference_graph(self.dims, batch, arg_max, bias=self.bias, activation=self.activation)
             exe = native.Executable(self.context, graph.image)
             x = self.context.buffer(batch * self.dims[0] * 4)
             out = self.context.buffer(batch * self.dims[-1] * 4)
@@ -140,7 +143,7 @@ class Model:
         if self._loss is None:
             raise RuntimeError("configure_training first")
         if batch not in self._training:
-            graph = program.mlp_training_graph(self.dims, batch, self._loss, bias=self.bias)
+            graph = program.mlp_training_graph(self.dims, batch, self._loss, bias=self.bias, activation=self.activation)
             exe = native.Executable(self.context, graph.image)
             x = self.context.buffer(batch * self.dims[0] * 4)
             t = self.context.buffer(batch * 4 if self._loss == "ce" else batch * self.dims[-1] * 4)

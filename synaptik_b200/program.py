@@ -24,7 +24,7 @@ OPS = {
     "PERMUTE": 1, "MATMUL": 2, "ADD": 3, "SUB": 4, "MUL": 5, "DIV": 6, "SCALAR_MUL": 7, "SCALAR_MIN": 8,
     "SCALAR_MAX": 9, "RELU": 10, "EXP": 11, "GT": 12, "WHERE": 13, "EXPAND": 14, "EXPAND_DIMS": 15,
     "CONTIGUOUS": 16, "ONE_HOT": 17, "MAX": 18, "SUM": 19, "SUM_TO_SHAPE": 20, "SOFTMAX": 21,
-    "INDEX_CROSS_ENTROPY": 22, "MEAN_SQUARED_ERROR": 23, "ARG_MAX": 24,
+    "INDEX_CROSS_ENTROPY": 22, "MEAN_SQUARED_ERROR": 23, "ARG_MAX": 24, "TANH": 25, "SIGMOID": 26,
 }
 ROLE_INTERMEDIATE, ROLE_FEED, ROLE_CONSTANT = 0, 1, 2
 MASK64 = (1 << 64) - 1
@@ -133,6 +133,11 @@ class GraphBuilder:
     def scalar_max(self, x, s): return self._scalar("SCALAR_MAX", x, s)
     def relu(self, x): return self._node("RELU", [x], F32, x.shape)
     def exp(self, x): return self._node("EXP", [x], F32, x.shape)
+    def tanh(self, x): return self._node("TANH", [x], F32, x.shape)
+    def sigmoid(self, x): return self._node("SIGMOID", [x], F32, x.shape)
+
+    def activation(self, kind: str, x: Value) -> Value:
+        return {"relu": self.relu, "tanh": self.tanh, "sigmoid": self.sigmoid}[kind](x)
 
     def where(self, condition: Value, a: Value, b: Value) -> Value:
         return self._node("WHERE", [condition, a, b], F32, _broadcast(_broadcast(condition.shape, a.shape), b.shape))
@@ -202,6 +207,21 @@ class GraphBuilder:
         zero = self.expand(self.constant(F32, 0.0), z.shape)
         return self.where(self.gt(z, zero), upstream, zero)
 
+    def tanh_backward(self, output: Value, upstream: Value) -> Value:
+        """g * (1 - y * y) with EXPAND(1) (ElementwiseGradientRules.java:206)."""
+        one = self.expand(self.constant(F32, 1.0), output.shape)
+        return self.mul(upstream, self.sub(one, self.mul(output, output)))
+
+    def sigmoid_backward(self, output: Value, upstream: Value) -> Value:
+        """(g * y) * (1 - y) with EXPAND(1) (ElementwiseGradientRules.java:205)."""
+        one = self.expand(self.constant(F32, 1.0), output.shape)
+        return self.mul(self.mul(upstream, output), self.sub(one, output))
+
+    def activation_backward(self, kind: str, pre_activation: Value, output: Value, upstream: Value) -> Value:
+        if kind == "relu":
+            return self.relu_backward(pre_activation, upstream)
+        return self.tanh_backward(output, upstream) if kind == "tanh" else self.sigmoid_backward(output, upstream)
+
     def _loss_scale(self, seed: Value, rows: int) -> Value:
         ones = self.contiguous(self.expand(self.constant(F32, 1.0), (rows,)))
         count = self.sum_all(ones)
@@ -267,9 +287,10 @@ class MlpGraph:
     shapes: dict
 
 
-def mlp_inference_graph(dims: Sequence[int], batch: int, arg_max: bool = False, bias: bool = True) -> MlpGraph:
-    """Model.compute of a Linear/ReLU stack: feeds x then (w, b) per layer; publishes the last
-    layer's output (and its row arg-max when asked)."""
+def mlp_inference_graph(dims: Sequence[int], batch: int, arg_max: bool = False, bias: bool = True,
+                        activation: str = "relu") -> MlpGraph:
+    """Model.compute of a Linear/activation stack (ModelBuilder.linear().relu() / .tanh() / .sigmoid()):
+    feeds x then (w, b) per layer; publishes the last layer's output (and its row arg-max when asked)."""
     g = GraphBuilder()
     x = g.feed(F32, (batch, dims[0]))
     names, shapes = ["x"], {"x": (batch, dims[0])}
@@ -287,7 +308,7 @@ def mlp_inference_graph(dims: Sequence[int], batch: int, arg_max: bool = False, 
         params.append((w, b))
     for l, (w, b) in enumerate(params):
         _, z = g.linear(a, w, b)
-        a = g.relu(z) if l + 2 < len(dims) else z
+        a = g.activation(activation, z) if l + 2 < len(dims) else z
     g.publish(a)
     pubs = ["output"]
     shapes["output"] = a.shape
@@ -299,7 +320,7 @@ def mlp_inference_graph(dims: Sequence[int], batch: int, arg_max: bool = False, 
 
 
 def mlp_training_graph(dims: Sequence[int], batch: int, loss: str = "ce", label_dtype: int = I32, bias: bool = True,
-                       publish_activations: bool = False) -> MlpGraph:
+                       publish_activations: bool = False, activation: str = "relu") -> MlpGraph:
     """The TRAINING_STEP graph TrainingSession compiles: forward, objective, and one gradient per
     parameter in trainingParameters() order (weight, bias per layer), published after the loss
     (TrainingSession.java:953-987).  Feeds: x, target, seed, then (w, b) per layer."""
@@ -327,7 +348,7 @@ def mlp_training_graph(dims: Sequence[int], batch: int, loss: str = "ce", label_
         wt, z = g.linear(a, w, b)
         wts.append(wt)
         zs.append(z)
-        a = g.relu(z) if l + 1 < layers else z
+        a = g.activation(activation, z) if l + 1 < layers else z
         acts.append(a)
     if loss == "ce":
         objective = g.index_cross_entropy(a, target)
@@ -341,7 +362,7 @@ def mlp_training_graph(dims: Sequence[int], batch: int, loss: str = "ce", label_
         dx, dw, db = g.linear_backward(acts[l], wts[l], dz, need_dx=l > 0, bias=bias)
         grads[2 * l], grads[2 * l + 1] = dw, db
         if l > 0:
-            dz = g.relu_backward(zs[l - 1], dx)
+            dz = g.activation_backward(activation, zs[l - 1], acts[l], dx)
     pubs = ["loss"]
     shapes["loss"] = ()
     for l in range(layers):

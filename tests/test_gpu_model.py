@@ -204,3 +204,45 @@ def test_training_state_snapshot_restores_a_run_exactly(ctx):
         assert np.array_equal(pa, pb)
     assert a.optimizer_steps() == b.optimizer_steps() == 3
     a.close(); b.close()
+
+
+@pytest.mark.parametrize("activation", ["tanh", "sigmoid"])
+def test_tanh_and_sigmoid_networks_match_the_checker(ctx, oracle, activation):
+    # ModelBuilder.linear().tanh() / .sigmoid() stacks: forward, gradients and three Adam steps on the
+    # exact GEMM engine; the activations differ from the checker by at most 1 ulp on rare ties, so the
+    # comparison is at rounding level rather than bit for bit
+    dims, batch = [48, 96, 64, 10], 256
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal((batch, dims[0])).astype(np.float32)
+    labels = rng.integers(0, 10, batch)
+    ctx.set_option("gemm_engine", 1)
+    try:
+        model = nn.Model(dims, ctx, seed=12, activation=activation)
+        params = model.parameters()
+        for i in range(1, len(params), 2):
+            params[i] = rng.uniform(-0.1, 0.1, params[i].shape).astype(np.float32)
+        model.load_parameters(params)
+        model.configure_training("ce", nn.Adam(1e-3))
+        logits = model.compute(x)
+        want_logits = oracle.mlp_forward(x, params[0::2], params[1::2], activation)[-1]
+        assert np.abs(logits - want_logits).max() <= 4e-6 * np.abs(want_logits).max()
+        loss, grads = model.gradients(x, labels)
+        ref_loss, ref_grads, _ = oracle.mlp_gradients(x, labels, params[0::2], params[1::2], "ce", activation=activation)
+        assert abs(loss - float(ref_loss)) <= 2e-6 * abs(float(ref_loss))
+        for got, want in zip(grads, ref_grads):
+            assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max() + 1e-12
+        ref = [p.copy().reshape(-1) for p in params]
+        m = [np.zeros(p.size, np.float32) for p in params]
+        v = [np.zeros(p.size, np.float32) for p in params]
+        for step in range(1, 4):
+            _, g_ref, _ = oracle.mlp_gradients(x, labels, [r.reshape(p.shape) for r, p in zip(ref[0::2], params[0::2])],
+                                               [r for r in ref[1::2]], "ce", activation=activation)
+            model.train(x, labels)
+            for i, g in enumerate(g_ref):
+                assert oracle.adam(ref[i], g.reshape(-1), m[i], v[i], step)
+            for got, want in zip(model.parameters(), ref):
+                drift = np.abs(got.reshape(-1) - want)
+                assert drift.max() <= 2e-3 * step and drift.mean() <= 2e-6 * step, (step, drift.max(), drift.mean())
+        model.close()
+    finally:
+        ctx.set_option("gemm_engine", 0)

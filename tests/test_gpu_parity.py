@@ -366,6 +366,37 @@ def test_prefetch_overlaps_and_stays_ordered(ctx):
         b.close()
 
 
+@pytest.mark.parametrize("kind", ["tanh", "sigmoid"])
+def test_tanh_and_sigmoid_nodes(ctx, oracle, kind):
+    # binary64 function and one narrowing on both sides: identical except on the rare rounding tie
+    # where the two binary64 libraries differ in the last place (stated bound: 1 ulp)
+    rng = np.random.default_rng(3)
+    x = np.concatenate([rng.standard_normal(200000) * 4, rng.uniform(-110, 110, 50000),
+                        [0.0, -0.0, np.inf, -np.inf, np.nan, 1e-30, -1e-30, 88.0, -88.0, 104.0, -104.0]]).astype(np.float32)
+    g = GraphBuilder()
+    v = g.feed(F32, x.shape)
+    g.publish(getattr(g, kind)(v))
+    (got,) = run_image(ctx, g, [x])
+    want = getattr(oracle, kind)(x)
+    finite = np.isfinite(want)
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    assert ulp_distance(got[finite], want[finite]).max() <= 1
+    assert (got[finite] == want[finite]).mean() >= 0.9999
+    assert np.array_equal(np.signbit(got[finite]), np.signbit(want[finite]))
+
+
+@pytest.mark.parametrize("kind", ["tanh", "sigmoid"])
+def test_tanh_and_sigmoid_backward_chains_round_per_node(ctx, oracle, kind):
+    rng = np.random.default_rng(4)
+    y = (np.tanh(rng.standard_normal((64, 96))) if kind == "tanh" else rng.uniform(0, 1, (64, 96))).astype(np.float32)
+    up = rng.standard_normal((64, 96)).astype(np.float32)
+    g = GraphBuilder()
+    yv, uv = g.feed(F32, y.shape), g.feed(F32, y.shape)
+    g.publish(g.tanh_backward(yv, uv) if kind == "tanh" else g.sigmoid_backward(yv, uv))
+    (got,) = run_image(ctx, g, [y, up])
+    assert np.array_equal(got, oracle.activation_backward(kind, y, up))
+
+
 # ---- buffers and error statuses -----------------------------------------------------------------
 def test_buffers_canonical_bytes_and_errors(ctx):
     values = np.array([1.0, -2.5, 3.25e-3, 7e8], dtype=np.float32)

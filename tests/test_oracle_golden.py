@@ -230,3 +230,16 @@ def test_pending_gradient_sum_is_all_or_nothing(oracle):
     before = acc.copy()
     assert not oracle.accumulate(acc, np.array([0.0, 0.0, 3.0e38], np.float32))   # overflow: rejected
     assert np.array_equal(acc, before)
+
+
+def test_tanh_and_sigmoid_special_values(oracle):
+    # the reference's tests hold no FLOAT32 known answers for these two; the values below follow from the
+    # definition (binary64 function, one narrowing: CpuScalarReferenceKernel.java:1729-1742)
+    x = np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 20.0, -20.0, -104.0], np.float32)
+    t, s = oracle.tanh(x), oracle.sigmoid(x)
+    assert t[0] == 0.0 and not np.signbit(t[0]) and t[1] == 0.0 and np.signbit(t[1])
+    assert t[2] == 1.0 and t[3] == -1.0 and np.isnan(t[4]) and t[5] == 1.0 and t[6] == -1.0
+    assert s[0] == 0.5 and s[1] == 0.5 and s[2] == 1.0 and s[3] == 0.0 and np.isnan(s[4]) and s[5] == 1.0
+    assert s[6] == np.float32(np.exp(-20.0) / (1.0 + np.exp(-20.0))) and s[7] == 0.0       # underflows past the subnormals
+    y = oracle.tanh(np.array([0.5], np.float32))
+    assert oracle.activation_backward("tanh", y, np.array([2.0], np.float32))[0] == np.float32(2.0) * (np.float32(1.0) - y[0] * y[0])
