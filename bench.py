@@ -167,10 +167,11 @@ def run_cuda(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     ctx = native.Context(local_rank)
-    if os.environ.get("SYNAPTIK_BENCH_FUSED_PLANES") == "0":
-        ctx.set_option("fused_planes", 0)
-    if os.environ.get("SYNAPTIK_BENCH_PROMOTE") in ("0", "1"):
-        ctx.set_option("gemm_promote", int(os.environ["SYNAPTIK_BENCH_PROMOTE"]))
+    # experiment hook: SYNAPTIK_BENCH_OPTIONS="gemm_dynamic=0,gemm_slices=0" sets context options before the
+    # executable is created (the defaults are what the numbers in the repository were measured with)
+    for item in filter(None, os.environ.get("SYNAPTIK_BENCH_OPTIONS", "").split(",")):
+        name, _, value = item.partition("=")
+        ctx.set_option(name.strip(), int(value))
     comm = None
     if distributed:
         holder = [native.comm_unique_id() if rank == 0 else None]

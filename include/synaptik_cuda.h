@@ -74,7 +74,10 @@ SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_release(void *context);
  * only.  "gemm_slices": 1 (default) = a two-SM product without epilogue work (a weight gradient) may
  * split its contraction into up to four slices when that shortens the last wave of the persistent
  * grid; the slices' partial products are added in ascending order by a second kernel; 0 = never.
- * Unknown names return INVALID_ARGUMENT. */
+ * "gemm_dynamic": 1 (default) = executables created afterwards let the two-SM kernel's block pairs take
+ * their tiles one by one from a counter, so a pair whose SMs were held by another kernel (an
+ * all-reduce on the communication stream) just takes fewer tiles; 0 = fixed round-robin assignment.
+ * The result does not depend on the assignment.  Unknown names return INVALID_ARGUMENT. */
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_set_option(void *context, const char *name, int64_t value);
 /* Blocks until all work issued on the context has finished. */
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_synchronize(void *context);

@@ -260,6 +260,7 @@ struct SliceParams {                         // two-SM kernel: split of the cont
     int slices, kb_per_slice;
     float *ws; int64_t ld;                   // workspace [slices][m][ld] of the slices' partial products
     int group_n;                             // tile columns per group (see tile_origin)
+    int *unit_counter;                       // dynamic assignment: the next unit number, zero before the launch
 };
 
 // Tile order of the two-SM kernel.  The 74 pairs work on 74 consecutive tiles at a time.  In plain
@@ -731,7 +732,7 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
 }
 
-template <int BN, bool SLICED>
+template <int BN, bool SLICED, bool DYNAMIC>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1) gemm_tf32x3_pair_kernel(
         const __grid_constant__ CUtensorMap map_p_hi, const __grid_constant__ CUtensorMap map_p_lo,
         const __grid_constant__ CUtensorMap map_q_hi, const __grid_constant__ CUtensorMap map_q_lo, TcParams prm, SliceParams slc) {
@@ -741,8 +742,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1)
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S * Cfg::kStageBytes);
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * S + 4);
+    // bars[0..S) full, [S..2S) empty, [2S..2S+2) accumulator full, [2S+2..2S+4) accumulator empty,
+    // [2S+4..2S+4+R) unit published, [2S+4+R..2S+4+2R) unit slot free (used in the even block)
+    constexpr int R = 4;                    // depth of the ring of published unit numbers
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * S + 4 + 2 * R);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    volatile int *sched_unit = reinterpret_cast<volatile int *>(tmem_slot + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();
@@ -751,10 +756,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1)
     auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
     auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * S + a); };
     auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * S + 2 + a); };
+    auto sched_full_bar = [&](int r) { return bar_base + 8u * (2 * S + 4 + r); };
+    auto sched_empty_bar = [&](int r) { return bar_base + 8u * (2 * S + 4 + R + r); };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int a = 0; a < 2; a++) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), 512); }
+        // a published unit is consumed by the issuer, the partner's producer and one lane of each of
+        // the 16 epilogue warps of the pair
+        for (int r = 0; r < R; r++) { mbar_init(sched_full_bar(r), 1); mbar_init(sched_empty_bar(r), 18); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -779,13 +789,42 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1)
     const uint32_t smem_base = smem_u32(smem);
     const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
 
+    // Dynamic unit assignment (DYNAMIC): the even block's producer thread takes the next unit number from
+    // a counter in global memory and publishes it to both blocks through a ring of R slots; every other
+    // role reads the ring in the same order.  A pair that starts late, because another kernel (an
+    // all-reduce) held its SMs, then simply takes fewer units, where a fixed assignment would make the
+    // whole product wait for it.  -1 ends the sequence; a wait that gives up also returns -1.
+    auto sched_publish = [&](int seq) -> int {          // even block, producer thread only
+        const int r = seq % R;
+        if (!mbar_wait_cluster(sched_empty_bar(r), (((uint32_t)seq / R) & 1u) ^ 1u, abort_flag)) return -1;
+        int u = atomicAdd(slc.unit_counter, 1);
+        if (u >= total_units) u = -1;
+        sched_unit[r] = u;
+        asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(map_to_rank(smem_u32((const void *)(sched_unit + r)), 1)), "r"(u) : "memory");
+        mbar_arrive_cluster(map_to_rank(sched_full_bar(r), 0));
+        mbar_arrive_cluster(map_to_rank(sched_full_bar(r), 1));
+        return u;
+    };
+    auto sched_take = [&](int seq, bool arrive) -> int { // every other role; `arrive` from one lane per warp
+        const int r = seq % R;
+        if (!mbar_wait_cluster(sched_full_bar(r), ((uint32_t)seq / R) & 1u, abort_flag)) return -1;
+        const int u = sched_unit[r];
+        if (arrive) mbar_arrive_cluster(map_to_rank(sched_empty_bar(r), 0));
+        return u;
+    };
+
     if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     if (warp == 0) {
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
-            for (int unit = pair; unit < total_units && ok; unit += pairs) {
+            int seq = 0;
+            int unit = !DYNAMIC ? pair : (rank == 0 ? sched_publish(seq) : sched_take(seq, true));
+            for (; unit >= 0 && unit < total_units && ok; ) {
+                // the next unit number is requested before this unit's loads, so the counter's latency hides
+                int next = unit + pairs;
+                if (DYNAMIC && rank == 0) next = sched_publish(++seq);
                 const int tile = SLICED ? unit % total_tiles : unit, slice = SLICED ? unit / total_tiles : 0;
                 int mi, ni;
                 tile_origin(tile, prm.tiles_m, prm.tiles_n, slc.group_n, mi, ni);
@@ -804,6 +843,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1)
                     load_operand_pair(sa + 2 * Cfg::kABytes + Cfg::kBBytes, &map_q_lo, leader_full, kb, n0, prm.q_mn);
                     if (++stage == S) { stage = 0; phase ^= 1u; }
                 }
+                if (DYNAMIC && rank != 0) next = sched_take(++seq, true);
+                unit = next;
             }
         }
     } else if (warp == 1 && rank == 0) {
@@ -813,7 +854,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1)
             int stage = 0; uint32_t phase = 0;
             uint32_t partial = 0;
             bool ok = true;
-            for (int unit = pair; unit < total_units && ok; unit += pairs) {
+            int seq = 0;
+            for (int unit = DYNAMIC ? sched_take(seq, true) : pair; unit >= 0 && unit < total_units && ok;
+                 unit = DYNAMIC ? sched_take(++seq, true) : unit + pairs) {
                 const int kb_first = SLICED ? (unit / total_tiles) * kb_per_slice : 0;
                 const int kb_last = (SLICED && kb_first + kb_per_slice < kb_count) ? kb_first + kb_per_slice : kb_count;
                 for (int kb0 = kb_first; kb0 < kb_last && ok; kb0 += CHUNK_KB, partial++) {
@@ -854,7 +897,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1)
         bool ok = true;
         const bool vec_ok = (prm.ldd & 3) == 0 && ((uintptr_t)prm.d & 15) == 0
                             && (!prm.second || ((uintptr_t)prm.second & 15) == 0) && (!prm.gate || ((uintptr_t)prm.gate & 15) == 0);
-        for (int unit = pair; unit < total_units && ok; unit += pairs) {
+        int seq = 0;
+        // lane 0 alone reads the ring (it frees the slot at once, so no other lane may look at it)
+        auto warp_take = [&](int sequence) -> int {
+            int u = 0;
+            if (lane == 0) u = sched_take(sequence, true);
+            return __shfl_sync(0xffffffffu, u, 0);
+        };
+        for (int unit = DYNAMIC ? warp_take(seq) : pair; unit >= 0 && unit < total_units && ok;
+             unit = DYNAMIC ? warp_take(++seq) : unit + pairs) {
             const int tile = SLICED ? unit % total_tiles : unit, slice = SLICED ? unit / total_tiles : 0;
             int mi, ni;
             tile_origin(tile, prm.tiles_m, prm.tiles_n, slc.group_n, mi, ni);
@@ -1146,7 +1197,8 @@ static cudaError_t launch_tc(cudaStream_t s, const TensorCoreGemm *g, const TcPa
                 kernel<<<g->grid, PROMOTED_THREADS, Pair::kSmemBytes, s>>>(g->p_hi, g->p_lo, g->q_hi, g->q_lo, prm, slc);
                 return cudaSuccess;
             };
-            e = g->slices > 1 ? launch_pair(gemm_tf32x3_pair_kernel<BN, true>) : launch_pair(gemm_tf32x3_pair_kernel<BN, false>);
+            if (slc.unit_counter) e = g->slices > 1 ? launch_pair(gemm_tf32x3_pair_kernel<BN, true, true>) : launch_pair(gemm_tf32x3_pair_kernel<BN, false, true>);
+            else e = g->slices > 1 ? launch_pair(gemm_tf32x3_pair_kernel<BN, true, false>) : launch_pair(gemm_tf32x3_pair_kernel<BN, false, false>);
             if (e != cudaSuccess) return e;
         } else return cudaErrorInvalidValue;
     } else if (g->promote) {
@@ -1166,11 +1218,12 @@ static cudaError_t launch_tc(cudaStream_t s, const TensorCoreGemm *g, const TcPa
 }
 
 cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, int64_t ldd, const GemmEpilogue &ep, float *workspace,
-                           int *error_word) {
+                           int *unit_counter, int *error_word) {
     TcParams prm;
     SliceParams slc;
     slc.slices = g->slices; slc.kb_per_slice = g->kb_per_slice; slc.ws = workspace; slc.ld = g->slice_ld;
     slc.group_n = g->group_n;
+    slc.unit_counter = g->pair ? unit_counter : nullptr;
     if (g->slices > 1 && (!workspace || ep.bias || ep.gate || ep.second || ep.relu || ep.plane_hi)) return cudaErrorInvalidValue;
     prm.nhi = ep.plane_hi; prm.nlo = ep.plane_lo; prm.nld = ep.plane_ld;
     prm.p_mn = g->p_mn; prm.q_mn = g->q_mn;
