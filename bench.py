@@ -107,8 +107,9 @@ class ClockSampler:
                 "samples": len(clocks), "reasons": sorted(reasons)}
 
 
-def cpu_baseline(threads: int, rows: int, steps: int = 1):
-    """Times the reference-shaped CPU training step on `rows` samples of the same workload."""
+def cpu_baseline(threads: int, rows: int, steps: int = 1, warmup: int = 0):
+    """Times the reference-shaped CPU training step on `rows` samples of the same workload: `warmup`
+    untimed steps, then the median of `steps` timed ones."""
     from oracle import oracle
     blas = oracle.baseline_bind_openblas()
     rng = np.random.default_rng(7)
@@ -119,11 +120,12 @@ def cpu_baseline(threads: int, rows: int, steps: int = 1):
     m2 = [np.zeros(a.size, dtype=np.float32) for pair in zip(weights, biases) for a in pair]
     x, labels = synthetic_batch(0, rows)
     seconds = []
-    for step in range(steps):
+    for step in range(warmup + steps):
         s, _, _ = oracle.baseline_mlp_step(DIMS, x, labels, weights, biases, m1, m2, train=True, count_total=GLOBAL_BATCH,
                                            adam_step=step + 1, threads=threads, **{"lr": ADAM["lr"], "beta1": ADAM["beta1"],
                                                                                     "beta2": ADAM["beta2"], "eps": ADAM["eps"]})
-        seconds.append(s)
+        if step >= warmup:
+            seconds.append(s)
     return rows / float(np.median(seconds)), blas, float(np.median(seconds))
 
 
@@ -133,8 +135,7 @@ def run_reference(args):
         return 0
     threads = os.cpu_count() or 1
     rows = 2048
-    total = args.steps + args.warmup
-    value, blas, seconds = cpu_baseline(threads, rows, steps=max(total, 1))
+    value, blas, seconds = cpu_baseline(threads, rows, steps=max(args.steps, 1), warmup=args.warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": seconds * 1e3 * GLOBAL_BATCH / rows, "higher_is_better": True, "scaling": "strong",
@@ -142,7 +143,7 @@ def run_reference(args):
         "config": {"workload": "mlp_784_4096x3_10_softmax_ce_adam_train", "global_batch": GLOBAL_BATCH,
                    "note": "reference-shaped CPU step (OpenBLAS sgemm as the reference calls it + scalar loops) on a row sample; ms_per_step scaled to the global batch"},
         "cpu_baseline": {"value": value, "unit": "samples/s", "cores": threads, "kind": "port",
-                         "sample": f"{rows} of {GLOBAL_BATCH} rows per step, median of {max(total, 1)} steps, BLAS: {os.path.basename(blas)}"},
+                         "sample": f"{rows} of {GLOBAL_BATCH} rows per step, median of {max(args.steps, 1)} timed steps after {args.warmup} warm-up, BLAS: {os.path.basename(blas)}"},
         "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
