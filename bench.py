@@ -317,9 +317,9 @@ def run_cuda(args):
         }
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            value, blas, seconds = cpu_baseline(threads, 1024, steps=2)
+            value, blas, seconds = cpu_baseline(threads, 4096, steps=3, warmup=1)     # about 10 s of CPU work
             line["cpu_baseline"] = {"value": value, "unit": "samples/s", "cores": threads, "kind": "port",
-                                    "sample": f"1024 of {GLOBAL_BATCH} rows, 2 steps, median {seconds:.2f} s/step, BLAS: {os.path.basename(blas)}"}
+                                    "sample": f"4096 of {GLOBAL_BATCH} rows per step, median of 3 timed steps after 1 warm-up, {seconds:.2f} s/step, BLAS: {os.path.basename(blas)}"}
         print(json.dumps(line))
     model.close()
     if comm is not None:
