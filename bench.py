@@ -336,6 +336,9 @@ def run_kernel_case(args):
     from synaptik_b200 import native, program
     from synaptik_b200.program import F32, I32, GraphBuilder
     ctx = native.Context(0)
+    for item in filter(None, os.environ.get("SYNAPTIK_BENCH_OPTIONS", "").split(",")):      # experiment hook, as in run_cuda
+        name, _, value = item.partition("=")
+        ctx.set_option(name.strip(), int(value))
     rng = np.random.default_rng(3)
     g = GraphBuilder()
     peak_data, peak_kind = peaks()

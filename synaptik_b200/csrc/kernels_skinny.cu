@@ -127,34 +127,50 @@ __global__ void __launch_bounds__(256) narrow_inner_kernel(int64_t m, int64_t n,
 }
 
 // ---- narrow weight gradient: D[i, j] = sum_r S[r, i] * T[r, j], i over a wide axis, j < N ----------
-// Phase 1: a warp owns 128 consecutive i and one slice of the long axis r, keeps N float4 sums in
-// registers and streams its rows of S once.  Phase 2 adds the slices in a fixed order.
+// Phase 1: a block owns one slice of the long axis r and eight strips of 128 consecutive i (one per
+// warp).  The slice's rows of T (N floats each) are staged in shared memory 128 rows at a time, so the
+// inner loop issues one 16-byte load of S per row and reads T as shared-memory broadcasts; each warp
+// keeps N float4 sums in registers and streams its rows of S once.  Phase 2 adds the slices in a
+// fixed order.
+constexpr int kReduceChunk = 128;
 template <int N>
 __global__ void __launch_bounds__(256) narrow_reduce_partial_kernel(int64_t wide, int64_t depth, const float *__restrict__ s, int64_t lds,
-        const float *__restrict__ t, int64_t ldt, float *partial, int strips, int64_t rows_per, int64_t slices) {
-    const int lane = threadIdx.x & 31;
-    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int strip = (int)(warp % strips);
-    const int64_t slice = warp / strips;
+        const float *__restrict__ t, int64_t ldt, float *partial, int strip_groups, int64_t rows_per, int64_t slices) {
+    __shared__ float tchunk[kReduceChunk][N];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int64_t slice = blockIdx.x / strip_groups;
+    const int strip = (int)(blockIdx.x % strip_groups) * 8 + w;
     const int64_t col = (int64_t)strip * 128 + lane * 4;
     const int64_t r0 = slice * rows_per, r1 = r0 + rows_per < depth ? r0 + rows_per : depth;
-    if (col >= wide || slice >= slices) return;          // a slice without rows still writes its zeros
+    const bool live = col < wide;                        // a slice without rows still writes its zeros
     float4 acc[N];
 #pragma unroll
     for (int j = 0; j < N; j++) acc[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int64_t c0 = r0; c0 < r1; c0 += kReduceChunk) {
+        const int rows_here = (int)(r1 - c0 < kReduceChunk ? r1 - c0 : kReduceChunk);
+        __syncthreads();                                 // the previous chunk has been consumed
+        for (int e = threadIdx.x; e < rows_here * N; e += blockDim.x) {
+            const int rr = e / N, j = e - rr * N;
+            tchunk[rr][j] = __ldg(t + (c0 + rr) * ldt + j);
+        }
+        __syncthreads();
+        if (live) {
 #pragma unroll 4
-    for (int64_t r = r0; r < r1; r++) {
-        const float4 sv = *reinterpret_cast<const float4 *>(s + r * lds + col);
-        const float *trow = t + r * ldt;
+            for (int rr = 0; rr < rows_here; rr++) {
+                const float4 sv = *reinterpret_cast<const float4 *>(s + (c0 + rr) * lds + col);
 #pragma unroll
-        for (int j = 0; j < N; j++) {
-            const float tv = __ldg(trow + j);
-            acc[j].x = fmaf(sv.x, tv, acc[j].x); acc[j].y = fmaf(sv.y, tv, acc[j].y);
-            acc[j].z = fmaf(sv.z, tv, acc[j].z); acc[j].w = fmaf(sv.w, tv, acc[j].w);
+                for (int j = 0; j < N; j++) {
+                    const float tv = tchunk[rr][j];
+                    acc[j].x = fmaf(sv.x, tv, acc[j].x); acc[j].y = fmaf(sv.y, tv, acc[j].y);
+                    acc[j].z = fmaf(sv.z, tv, acc[j].z); acc[j].w = fmaf(sv.w, tv, acc[j].w);
+                }
+            }
         }
     }
+    if (live) {
 #pragma unroll
-    for (int j = 0; j < N; j++) *reinterpret_cast<float4 *>(partial + (slice * N + j) * wide + col) = acc[j];
+        for (int j = 0; j < N; j++) *reinterpret_cast<float4 *>(partial + (slice * N + j) * wide + col) = acc[j];
+    }
 }
 
 __global__ void narrow_reduce_final_kernel(int64_t wide, int n, int64_t slices, const float *__restrict__ partial,
@@ -196,8 +212,8 @@ template <int K> struct LaunchInner {
 };
 template <int N> struct LaunchReduce {
     static void run(cudaStream_t s, int blocks, int64_t wide, int64_t depth, const float *src, int64_t lds, const float *t, int64_t ldt,
-                    float *partial, int strips, int64_t rows_per, int64_t slices) {
-        narrow_reduce_partial_kernel<N><<<blocks, 256, 0, s>>>(wide, depth, src, lds, t, ldt, partial, strips, rows_per, slices);
+                    float *partial, int strip_groups, int64_t rows_per, int64_t slices) {
+        narrow_reduce_partial_kernel<N><<<blocks, 256, 0, s>>>(wide, depth, src, lds, t, ldt, partial, strip_groups, rows_per, slices);
     }
 };
 
@@ -254,10 +270,11 @@ cudaError_t gemm_narrow_reduce(cudaStream_t s, int64_t wide, int64_t n, int64_t 
                                const float *t, int64_t ldt, float *partial, float *out, int64_t stride_wide, int64_t stride_narrow) {
     if (!narrow_reduce_supported(wide, n, depth, lds) || !aligned16(src) || !aligned16(partial)) return cudaErrorInvalidValue;
     int strips = (int)((wide + 127) / 128);
+    int strip_groups = (strips + 7) / 8;
     int64_t slices = narrow_reduce_slices(wide, depth);
     int64_t rows_per = (depth + slices - 1) / slices;
-    int blocks = (int)((slices * strips + 7) / 8);
-    dispatch_extent<LaunchReduce>((int)n, s, blocks, wide, depth, src, lds, t, ldt, partial, strips, rows_per, slices);
+    int blocks = (int)(slices * strip_groups);
+    dispatch_extent<LaunchReduce>((int)n, s, blocks, wide, depth, src, lds, t, ldt, partial, strip_groups, rows_per, slices);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     int64_t total = wide * n;

@@ -106,6 +106,24 @@ def test_tensor_core_operand_layouts_are_exact_on_small_integers(ctx, ta, tb):
         assert np.array_equal(c, (la.astype(np.int64) @ lb.astype(np.int64)).astype(np.float32))
 
 
+@pytest.mark.parametrize("option", ["gemm_dynamic", "gemm_pair", "gemm_promote", "gemm_slices"])
+def test_every_kernel_variant_is_exact_on_small_integers(ctx, option):
+    # the non-default kernels (fixed tile assignment, one-SM tiles, one accumulator over the whole
+    # contraction, unsliced contraction) stay selectable through context options: each must still give
+    # the exact integer product, on tiles with ragged edges and on a transposed (MN-major) operand
+    ctx.set_option(option, 0)
+    try:
+        for m, k, n, ta in [(520, 300, 392, False), (512, 4200, 384, True)]:
+            rng = np.random.default_rng(m + n)
+            a = rng.integers(-3, 4, (k, m) if ta else (m, k)).astype(np.float32)
+            b = rng.integers(-3, 4, (k, n)).astype(np.float32)
+            (c,) = run_image(ctx, matmul_graph(m, k, n, ta, False), [a, b], engine=2)
+            la = a.T if ta else a
+            assert np.array_equal(c, (la.astype(np.int64) @ b.astype(np.int64)).astype(np.float32)), (option, m)
+    finally:
+        ctx.set_option(option, 1)
+
+
 def test_sliced_contraction_matches_unsliced(ctx):
     # an epilogue-free two-SM product with a long contraction is split into slices that a second kernel
     # adds in order: exact on small integers, and within one rounding per slice of the unsliced result
