@@ -102,14 +102,28 @@ def sigmoid(x) -> np.ndarray:
     return y
 
 
-def activation_backward(kind: str, output, upstream) -> np.ndarray:
+def silu(x) -> np.ndarray:
+    x = _f32(x)
+    y = np.empty_like(x)
+    lib().syn_oracle_activation_f32(2, ctypes.c_int64(x.size), _p(x), _p(y))
+    return y
+
+
+def activation_backward(kind: str, output, upstream, pre_activation=None) -> np.ndarray:
     """The reference's gradient node lists, one binary32 rounding per node
-    (ElementwiseGradientRules.java:205-206,210): relu where(y > 0, g, 0); tanh g * (1 - y * y);
-    sigmoid (g * y) * (1 - y)."""
+    (ElementwiseGradientRules.java:205-206,210,290-301): relu where(y > 0, g, 0); tanh g * (1 - y * y);
+    sigmoid (g * y) * (1 - y); silu where(isInf(x), where(x > 0, g, 0), (g * s) * (1 + x * (1 - s)))
+    with s = sigmoid(x) of the pre-activation x."""
     y, g = _f32(output), _f32(upstream)
     if kind == "relu":
         return relu_backward(y, g)
     one = np.float32(1.0)
+    if kind == "silu":
+        x = _f32(pre_activation)
+        s = sigmoid(x)
+        with np.errstate(invalid="ignore", over="ignore"):
+            regular = ((g * s).astype(np.float32) * (one + (x * (one - s).astype(np.float32)).astype(np.float32)).astype(np.float32)).astype(np.float32)
+        return np.where(np.isinf(x), np.where(x > 0, g, np.float32(0.0)), regular).astype(np.float32)
     if kind == "tanh":
         return (g * (one - (y * y).astype(np.float32)).astype(np.float32)).astype(np.float32)
     return ((g * y).astype(np.float32) * (one - y).astype(np.float32)).astype(np.float32)
@@ -244,15 +258,18 @@ def adam(parameter, gradient, first, second, step, lr=1e-3, beta1=0.9, beta2=0.9
 # --------------------------------------------------------------------------------------------
 # Composite: the training graph the backend is handed (forward, loss, backward), op by op.
 # --------------------------------------------------------------------------------------------
-def mlp_forward(x, weights, biases, activation: str = "relu"):
-    """Returns the list of post-activation values [a1..aL] (aL = logits, no activation)."""
+def mlp_forward(x, weights, biases, activation: str = "relu", pre_activations=None):
+    """Returns the list of post-activation values [a1..aL] (aL = logits, no activation); appends the
+    pre-activations z1..zL to ``pre_activations`` when a list is given."""
     acts = []
     a = _f32(x)
     for index, (w, b) in enumerate(zip(weights, biases)):
         hidden_layer = index + 1 < len(weights)
         z, a = linear(a, w, b, relu_flag=hidden_layer and activation == "relu")
         if hidden_layer and activation != "relu":
-            a = tanh(z) if activation == "tanh" else sigmoid(z)
+            a = {"tanh": tanh, "sigmoid": sigmoid, "silu": silu}[activation](z)
+        if pre_activations is not None:
+            pre_activations.append(z)
         acts.append(a)
     return acts
 
@@ -269,7 +286,8 @@ def mlp_gradients(x, labels_or_target, weights, biases, loss: str = "ce", count:
     branch on another implementation).
     """
     x = _f32(x)
-    acts = mlp_forward(x, weights, biases, activation)
+    zs = []
+    acts = mlp_forward(x, weights, biases, activation, zs)
     if hidden is not None:
         acts = [_f32(h) for h in hidden] + [linear(_f32(hidden[-1]), weights[-1], biases[-1], relu_flag=False)[1]]
     logits = acts[-1]
@@ -288,7 +306,7 @@ def mlp_gradients(x, labels_or_target, weights, biases, loss: str = "ce", count:
         if index > 0:
             da = matmul(dz, _f32(weights[index]))
             # z > 0 <=> relu(z) > 0 for every binary32 value, so the stored activation serves
-            dz = activation_backward(activation, a_prev, da)
+            dz = activation_backward(activation, a_prev, da, zs[index - 1])
     return value, grads, logits
 
 

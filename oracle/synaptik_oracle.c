@@ -480,15 +480,23 @@ SYN_EXPORT int syn_oracle_accumulate_f32(int64_t count, float *accumulated, cons
 /* :1729-1742): the value widened to double, StrictMath.tanh, or the two-branch sigmoid of        */
 /* CpuScalarEmitter.java:429-439 (1 / (1 + exp(-x)) for x >= 0, exp(x) / (1 + exp(x)) below and   */
 /* for NaN), then one narrowing to float.  glibc stands in for fdlibm as for exp and log.         */
-/* op: 0 = tanh, 1 = sigmoid.                                                                    */
+/* SILU (CpuScalarReferenceKernel.java:1236-1241): -inf gives -0; x / (1 + exp(-x)) for x >= 0,    */
+/* x * exp(x) / (1 + exp(x)) below and for NaN.                                                  */
+/* op: 0 = tanh, 1 = sigmoid, 2 = silu.                                                          */
 /* ------------------------------------------------------------------------------------------ */
 SYN_EXPORT void syn_oracle_activation_f32(int op, int64_t count, const float *x, float *y) {
     for (int64_t i = 0; i < count; i++) {
         double v = (double)x[i];
         double r;
         if (op == 0) r = tanh(v);
-        else if (v < 0.0 || v != v) { double e = exp(v); r = e / (1.0 + e); }
-        else r = 1.0 / (1.0 + exp(-v));
+        else if (op == 1) {
+            if (v >= 0.0) r = 1.0 / (1.0 + exp(-v));
+            else { double e = exp(v); r = e / (1.0 + e); }
+        } else {
+            if (v == -INFINITY) r = -0.0;
+            else if (v >= 0.0) r = v / (1.0 + exp(-v));
+            else { double e = exp(v); r = v * e / (1.0 + e); }
+        }
         y[i] = (float)r;
     }
 }

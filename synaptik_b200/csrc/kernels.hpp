@@ -20,7 +20,7 @@ struct Index4 {                 // right-aligned rank-4 iteration space with per
 // ---- generic node-by-node kernels (one binary32 rounding per operation) -----------------------
 cudaError_t binary(cudaStream_t s, Op op, const float *a, const float *b, void *out, const Index4 &ix, int64_t total);
 cudaError_t scalar_op(cudaStream_t s, Op op, DType dtype, const void *a, void *out, uint64_t scalar_bits, int64_t total);
-cudaError_t unary(cudaStream_t s, Op op, const float *a, float *out, int64_t total);
+cudaError_t unary(cudaStream_t s, Op op, const float *a, void *out, int64_t total);      // IS_INF writes BOOL bytes
 cudaError_t where(cudaStream_t s, const uint8_t *cond, const float *a, const float *b, float *out, const Index4 &ix, int64_t total);
 cudaError_t one_hot(cudaStream_t s, DType index_type, const void *indices, uint8_t *out, int64_t count, int64_t depth);
 cudaError_t copy_strided(cudaStream_t s, int element_bytes, const void *src, void *dst, const Index4 &ix, int64_t total);

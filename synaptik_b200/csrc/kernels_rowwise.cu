@@ -6,6 +6,7 @@
 #include "split.cuh"
 
 #include <cfloat>
+#include <math_constants.h>
 #include <cmath>
 #include <mutex>
 
@@ -160,13 +161,26 @@ __device__ __forceinline__ float sigmoid_value(float x) {
     return (float)(1.0 / (1.0 + exp(-v)));
 }
 
-__global__ void unary_kernel(int op, const float *__restrict__ a, float *out, int64_t total) {
+// SILU, CpuScalarReferenceKernel.java:1236-1241: -inf gives -0; x / (1 + exp(-x)) for x >= 0,
+// x * exp(x) / (1 + exp(x)) below (and for NaN), in binary64, one narrowing.
+__device__ __forceinline__ float silu_value(float x) {
+    const double v = (double)x;
+    if (v == -CUDART_INF) return -0.0f;
+    if (v >= 0.0) return (float)(v / (1.0 + exp(-v)));
+    const double e = exp(v);
+    return (float)(v * e / (1.0 + e));
+}
+
+__global__ void unary_kernel(int op, const float *__restrict__ a, void *out_raw, int64_t total) {
+    float *out = static_cast<float *>(out_raw);
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         float x = a[i];
         switch ((Op)op) {
             case Op::RELU: out[i] = relu_value(x); break;
             case Op::TANH: out[i] = tanh_value(x); break;
             case Op::SIGMOID: out[i] = sigmoid_value(x); break;
+            case Op::SILU: out[i] = silu_value(x); break;
+            case Op::IS_INF: static_cast<uint8_t *>(out_raw)[i] = (__float_as_uint(x) & 0x7fffffffu) == 0x7f800000u; break;
             default: out[i] = exp_accurate(x); break;
         }
     }
@@ -766,7 +780,7 @@ cudaError_t scalar_op(cudaStream_t s, Op op, DType dtype, const void *a, void *o
     return cudaGetLastError();
 }
 
-cudaError_t unary(cudaStream_t s, Op op, const float *a, float *out, int64_t total) {
+cudaError_t unary(cudaStream_t s, Op op, const float *a, void *out, int64_t total) {
     if (total == 0) return cudaSuccess;
     unary_kernel<<<grid_for(total, kThreads), kThreads, 0, s>>>((int)op, a, out, total);
     return cudaGetLastError();

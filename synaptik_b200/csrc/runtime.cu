@@ -476,7 +476,7 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                 const void *src = ptr(st.a);
                 if (!a.dense()) return UNSUPPORTED_SHAPE;
                 if (st.kind == StepKind::SCALAR) LAUNCH(kern::scalar_op(s, st.op, a.dtype, src, ptr(st.out), st.scalar_bits, total));
-                else LAUNCH(kern::unary(s, st.op, (const float *)src, (float *)ptr(st.out), total));
+                else LAUNCH(kern::unary(s, st.op, (const float *)src, ptr(st.out), total));
                 break;
             }
             case StepKind::ONE_HOT:

@@ -24,7 +24,7 @@ OPS = {
     "PERMUTE": 1, "MATMUL": 2, "ADD": 3, "SUB": 4, "MUL": 5, "DIV": 6, "SCALAR_MUL": 7, "SCALAR_MIN": 8,
     "SCALAR_MAX": 9, "RELU": 10, "EXP": 11, "GT": 12, "WHERE": 13, "EXPAND": 14, "EXPAND_DIMS": 15,
     "CONTIGUOUS": 16, "ONE_HOT": 17, "MAX": 18, "SUM": 19, "SUM_TO_SHAPE": 20, "SOFTMAX": 21,
-    "INDEX_CROSS_ENTROPY": 22, "MEAN_SQUARED_ERROR": 23, "ARG_MAX": 24, "TANH": 25, "SIGMOID": 26,
+    "INDEX_CROSS_ENTROPY": 22, "MEAN_SQUARED_ERROR": 23, "ARG_MAX": 24, "TANH": 25, "SIGMOID": 26, "SILU": 27, "IS_INF": 28,
 }
 ROLE_INTERMEDIATE, ROLE_FEED, ROLE_CONSTANT = 0, 1, 2
 MASK64 = (1 << 64) - 1
@@ -135,9 +135,11 @@ class GraphBuilder:
     def exp(self, x): return self._node("EXP", [x], F32, x.shape)
     def tanh(self, x): return self._node("TANH", [x], F32, x.shape)
     def sigmoid(self, x): return self._node("SIGMOID", [x], F32, x.shape)
+    def silu(self, x): return self._node("SILU", [x], F32, x.shape)
+    def is_inf(self, x): return self._node("IS_INF", [x], BOOL, x.shape)
 
     def activation(self, kind: str, x: Value) -> Value:
-        return {"relu": self.relu, "tanh": self.tanh, "sigmoid": self.sigmoid}[kind](x)
+        return {"relu": self.relu, "tanh": self.tanh, "sigmoid": self.sigmoid, "silu": self.silu}[kind](x)
 
     def where(self, condition: Value, a: Value, b: Value) -> Value:
         return self._node("WHERE", [condition, a, b], F32, _broadcast(_broadcast(condition.shape, a.shape), b.shape))
@@ -217,9 +219,20 @@ class GraphBuilder:
         one = self.expand(self.constant(F32, 1.0), output.shape)
         return self.mul(self.mul(upstream, output), self.sub(one, output))
 
+    def silu_backward(self, x: Value, upstream: Value) -> Value:
+        """where(isInf(x), where(x > 0, g, 0), (g * s) * (1 + x * (1 - s))) with s = SIGMOID(x)
+        (ElementwiseGradientRules.java:290-301)."""
+        one = self.expand(self.constant(F32, 1.0), x.shape)
+        zero = self.expand(self.constant(F32, 0.0), x.shape)
+        s = self.sigmoid(x)
+        regular = self.mul(self.mul(upstream, s), self.add(one, self.mul(x, self.sub(one, s))))
+        return self.where(self.is_inf(x), self.where(self.gt(x, zero), upstream, zero), regular)
+
     def activation_backward(self, kind: str, pre_activation: Value, output: Value, upstream: Value) -> Value:
         if kind == "relu":
             return self.relu_backward(pre_activation, upstream)
+        if kind == "silu":
+            return self.silu_backward(pre_activation, upstream)
         return self.tanh_backward(output, upstream) if kind == "tanh" else self.sigmoid_backward(output, upstream)
 
     def _loss_scale(self, seed: Value, rows: int) -> Value:

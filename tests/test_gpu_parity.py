@@ -384,7 +384,7 @@ def test_prefetch_overlaps_and_stays_ordered(ctx):
         b.close()
 
 
-@pytest.mark.parametrize("kind", ["tanh", "sigmoid"])
+@pytest.mark.parametrize("kind", ["tanh", "sigmoid", "silu"])
 def test_tanh_and_sigmoid_nodes(ctx, oracle, kind):
     # binary64 function and one narrowing on both sides: identical except on the rare rounding tie
     # where the two binary64 libraries differ in the last place (stated bound: 1 ulp)
@@ -413,6 +413,25 @@ def test_tanh_and_sigmoid_backward_chains_round_per_node(ctx, oracle, kind):
     g.publish(g.tanh_backward(yv, uv) if kind == "tanh" else g.sigmoid_backward(yv, uv))
     (got,) = run_image(ctx, g, [y, up])
     assert np.array_equal(got, oracle.activation_backward(kind, y, up))
+
+
+def test_silu_backward_chain_and_is_inf(ctx, oracle):
+    # where(isInf(x), where(x > 0, g, 0), (g * s) * (1 + x * (1 - s))), s = SIGMOID(x): every node rounds
+    # once; the device's sigmoid may differ from the checker's by 1 ulp on rare ties, so the chain is
+    # compared at 4 ulp of the result plus the infinities exactly
+    rng = np.random.default_rng(6)
+    x = np.concatenate([rng.standard_normal(6000) * 3, [np.inf, -np.inf, 0.0, -0.0, 50.0, -50.0]]).astype(np.float32).reshape(-1, 6)
+    up = rng.standard_normal(x.shape).astype(np.float32)
+    g = GraphBuilder()
+    xv, uv = g.feed(F32, x.shape), g.feed(F32, x.shape)
+    g.publish(g.silu_backward(xv, uv))
+    g.publish(g.is_inf(xv))
+    got, inf_mask = run_image(ctx, g, [x, up])
+    assert np.array_equal(inf_mask.astype(bool), np.isinf(x))
+    want = oracle.activation_backward("silu", None, up, x)
+    assert np.array_equal(got[np.isinf(x)], want[np.isinf(x)])
+    finite = np.isfinite(x)
+    assert ulp_distance(got[finite], want[finite]).max() <= 4
 
 
 # ---- buffers and error statuses -----------------------------------------------------------------

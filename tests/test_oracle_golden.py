@@ -243,3 +243,14 @@ def test_tanh_and_sigmoid_special_values(oracle):
     assert s[6] == np.float32(np.exp(-20.0) / (1.0 + np.exp(-20.0))) and s[7] == 0.0       # underflows past the subnormals
     y = oracle.tanh(np.array([0.5], np.float32))
     assert oracle.activation_backward("tanh", y, np.array([2.0], np.float32))[0] == np.float32(2.0) * (np.float32(1.0) - y[0] * y[0])
+
+
+def test_silu_special_values(oracle):
+    # CpuScalarReferenceKernel.silu (:1236-1241): -inf gives -0, +inf stays +inf, NaN stays NaN, x = 0 gives 0
+    x = np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 1.0], np.float32)
+    y = oracle.silu(x)
+    assert y[0] == 0.0 and y[1] == 0.0 and np.signbit(y[1]) and y[2] == np.inf
+    assert y[3] == 0.0 and np.signbit(y[3]) and np.isnan(y[4])
+    assert y[5] == np.float32(1.0 / (1.0 + np.exp(-1.0)))
+    g = oracle.activation_backward("silu", None, np.array([3.0, 3.0], np.float32), np.array([np.inf, -np.inf], np.float32))
+    assert g[0] == 3.0 and g[1] == 0.0
