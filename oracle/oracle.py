@@ -109,6 +109,17 @@ def silu(x) -> np.ndarray:
     return y
 
 
+def gelu_tanh(x) -> np.ndarray:
+    x = _f32(x)
+    y = np.empty_like(x)
+    lib().syn_oracle_activation_f32(3, ctypes.c_int64(x.size), _p(x), _p(y))
+    return y
+
+
+def _coefficient(bits: int) -> np.float32:
+    return np.array([bits], dtype=np.uint32).view(np.float32)[0]
+
+
 def activation_backward(kind: str, output, upstream, pre_activation=None) -> np.ndarray:
     """The reference's gradient node lists, one binary32 rounding per node
     (ElementwiseGradientRules.java:205-206,210,290-301): relu where(y > 0, g, 0); tanh g * (1 - y * y);
@@ -118,6 +129,18 @@ def activation_backward(kind: str, output, upstream, pre_activation=None) -> np.
     if kind == "relu":
         return relu_backward(y, g)
     one = np.float32(1.0)
+    if kind == "gelu_tanh":
+        # ElementwiseGradientRules.geluTanhApproximation (:280-288), FLOAT32 coefficients (:370-378)
+        x = _f32(pre_activation)
+        half, s2pi = _coefficient(0x3F000000), _coefficient(0x3F4C422A)
+        cubic, cubic_d = _coefficient(0x3D372713), _coefficient(0x3E095D4F)
+        with np.errstate(invalid="ignore", over="ignore"):
+            squared = x * x
+            u = (x + (squared * x) * cubic) * s2pi
+            t = tanh(u)
+            u_prime = (one + squared * cubic_d) * s2pi
+            regular = g * ((one + t) * half + ((x * (one - t * t)) * u_prime) * half)
+        return np.where(np.isinf(x), np.where(x > 0, g, np.float32(0.0)), regular).astype(np.float32)
     if kind == "silu":
         x = _f32(pre_activation)
         s = sigmoid(x)
@@ -267,7 +290,7 @@ def mlp_forward(x, weights, biases, activation: str = "relu", pre_activations=No
         hidden_layer = index + 1 < len(weights)
         z, a = linear(a, w, b, relu_flag=hidden_layer and activation == "relu")
         if hidden_layer and activation != "relu":
-            a = {"tanh": tanh, "sigmoid": sigmoid, "silu": silu}[activation](z)
+            a = {"tanh": tanh, "sigmoid": sigmoid, "silu": silu, "gelu_tanh": gelu_tanh}[activation](z)
         if pre_activations is not None:
             pre_activations.append(z)
         acts.append(a)

@@ -482,7 +482,8 @@ SYN_EXPORT int syn_oracle_accumulate_f32(int64_t count, float *accumulated, cons
 /* for NaN), then one narrowing to float.  glibc stands in for fdlibm as for exp and log.         */
 /* SILU (CpuScalarReferenceKernel.java:1236-1241): -inf gives -0; x / (1 + exp(-x)) for x >= 0,    */
 /* x * exp(x) / (1 + exp(x)) below and for NaN.                                                  */
-/* op: 0 = tanh, 1 = sigmoid, 2 = silu.                                                          */
+/* Tanh GELU (:1224-1229): -inf gives -0; 0.5 x (1 + tanh(sqrt(2 / pi) (x + 0.044715 x^3))).      */
+/* op: 0 = tanh, 1 = sigmoid, 2 = silu, 3 = tanh-approximated GELU.                              */
 /* ------------------------------------------------------------------------------------------ */
 SYN_EXPORT void syn_oracle_activation_f32(int op, int64_t count, const float *x, float *y) {
     for (int64_t i = 0; i < count; i++) {
@@ -492,10 +493,13 @@ SYN_EXPORT void syn_oracle_activation_f32(int op, int64_t count, const float *x,
         else if (op == 1) {
             if (v >= 0.0) r = 1.0 / (1.0 + exp(-v));
             else { double e = exp(v); r = e / (1.0 + e); }
-        } else {
+        } else if (op == 2) {
             if (v == -INFINITY) r = -0.0;
             else if (v >= 0.0) r = v / (1.0 + exp(-v));
             else { double e = exp(v); r = v * e / (1.0 + e); }
+        } else {
+            if (v == -INFINITY) r = -0.0;
+            else { double cube = v * v * v; r = 0.5 * v * (1.0 + tanh(sqrt(2.0 / 3.14159265358979323846) * (v + 0.044715 * cube))); }
         }
         y[i] = (float)r;
     }

@@ -171,6 +171,15 @@ __device__ __forceinline__ float silu_value(float x) {
     return (float)(v * e / (1.0 + e));
 }
 
+// Tanh-approximated GELU, CpuScalarReferenceKernel.java:1224-1229: -inf gives -0; otherwise
+// 0.5 * x * (1 + tanh(sqrt(2 / pi) * (x + 0.044715 * x^3))) in binary64, one narrowing.
+__device__ __forceinline__ float gelu_tanh_value(float x) {
+    const double v = (double)x;
+    if (v == -CUDART_INF) return -0.0f;
+    const double cube = v * v * v;
+    return (float)(0.5 * v * (1.0 + tanh(sqrt(2.0 / 3.14159265358979323846) * (v + 0.044715 * cube))));
+}
+
 __global__ void unary_kernel(int op, const float *__restrict__ a, void *out_raw, int64_t total) {
     float *out = static_cast<float *>(out_raw);
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -180,6 +189,7 @@ __global__ void unary_kernel(int op, const float *__restrict__ a, void *out_raw,
             case Op::TANH: out[i] = tanh_value(x); break;
             case Op::SIGMOID: out[i] = sigmoid_value(x); break;
             case Op::SILU: out[i] = silu_value(x); break;
+            case Op::GELU_TANH: out[i] = gelu_tanh_value(x); break;
             case Op::IS_INF: static_cast<uint8_t *>(out_raw)[i] = (__float_as_uint(x) & 0x7fffffffu) == 0x7f800000u; break;
             default: out[i] = exp_accurate(x); break;
         }

@@ -19,7 +19,7 @@ const char *op_name(Op op) {
         case Op::INDEX_CROSS_ENTROPY: return "INDEX_CATEGORICAL_CROSS_ENTROPY_WITH_LOGITS";
         case Op::MEAN_SQUARED_ERROR: return "MEAN_SQUARED_ERROR"; case Op::ARG_MAX: return "ARG_MAX";
         case Op::TANH: return "TANH"; case Op::SIGMOID: return "SIGMOID"; case Op::SILU: return "SILU";
-        case Op::IS_INF: return "IS_INF";
+        case Op::IS_INF: return "IS_INF"; case Op::GELU_TANH: return "GELU_TANH_APPROXIMATION";
     }
     return "?";
 }
@@ -121,7 +121,7 @@ Status check_node(const Program &g, int index, std::string &message) {
             if (in(0).dtype != DType::F32) FAIL(UNSUPPORTED_OPERATION, name << ": only FLOAT32");
             if (out(0).dtype != DType::BOOL || in(0).shape != out(0).shape) FAIL(GRAPH_COMPILATION_FAILED, name << ": result");
             return OK;
-        case Op::RELU: case Op::EXP: case Op::TANH: case Op::SIGMOID: case Op::SILU:
+        case Op::RELU: case Op::EXP: case Op::TANH: case Op::SIGMOID: case Op::SILU: case Op::GELU_TANH:
             if (!need(1, 1)) FAIL(GRAPH_COMPILATION_FAILED, name << ": arity");
             if (in(0).dtype != DType::F32 || out(0).dtype != DType::F32) FAIL(UNSUPPORTED_OPERATION, name << ": only FLOAT32");
             if (in(0).shape != out(0).shape) FAIL(GRAPH_COMPILATION_FAILED, name << ": shape");

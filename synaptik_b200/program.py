@@ -24,7 +24,7 @@ OPS = {
     "PERMUTE": 1, "MATMUL": 2, "ADD": 3, "SUB": 4, "MUL": 5, "DIV": 6, "SCALAR_MUL": 7, "SCALAR_MIN": 8,
     "SCALAR_MAX": 9, "RELU": 10, "EXP": 11, "GT": 12, "WHERE": 13, "EXPAND": 14, "EXPAND_DIMS": 15,
     "CONTIGUOUS": 16, "ONE_HOT": 17, "MAX": 18, "SUM": 19, "SUM_TO_SHAPE": 20, "SOFTMAX": 21,
-    "INDEX_CROSS_ENTROPY": 22, "MEAN_SQUARED_ERROR": 23, "ARG_MAX": 24, "TANH": 25, "SIGMOID": 26, "SILU": 27, "IS_INF": 28,
+    "INDEX_CROSS_ENTROPY": 22, "MEAN_SQUARED_ERROR": 23, "ARG_MAX": 24, "TANH": 25, "SIGMOID": 26, "SILU": 27, "IS_INF": 28, "GELU_TANH": 29,
 }
 ROLE_INTERMEDIATE, ROLE_FEED, ROLE_CONSTANT = 0, 1, 2
 MASK64 = (1 << 64) - 1
@@ -137,9 +137,11 @@ class GraphBuilder:
     def sigmoid(self, x): return self._node("SIGMOID", [x], F32, x.shape)
     def silu(self, x): return self._node("SILU", [x], F32, x.shape)
     def is_inf(self, x): return self._node("IS_INF", [x], BOOL, x.shape)
+    def gelu_tanh(self, x): return self._node("GELU_TANH", [x], F32, x.shape)
 
     def activation(self, kind: str, x: Value) -> Value:
-        return {"relu": self.relu, "tanh": self.tanh, "sigmoid": self.sigmoid, "silu": self.silu}[kind](x)
+        return {"relu": self.relu, "tanh": self.tanh, "sigmoid": self.sigmoid, "silu": self.silu,
+                "gelu_tanh": self.gelu_tanh}[kind](x)
 
     def where(self, condition: Value, a: Value, b: Value) -> Value:
         return self._node("WHERE", [condition, a, b], F32, _broadcast(_broadcast(condition.shape, a.shape), b.shape))
@@ -228,7 +230,28 @@ class GraphBuilder:
         regular = self.mul(self.mul(upstream, s), self.add(one, self.mul(x, self.sub(one, s))))
         return self.where(self.is_inf(x), self.where(self.gt(x, zero), upstream, zero), regular)
 
+    # FLOAT32 coefficients of the gradient rules (ElementwiseGradientRules.java:370-378, float32Bits column)
+    _HALF, _SQRT_2_OVER_PI = 0x3F000000, 0x3F4C422A
+    _GELU_CUBIC, _GELU_CUBIC_DERIVATIVE = 0x3D372713, 0x3E095D4F
+
+    def gelu_tanh_backward(self, x: Value, upstream: Value) -> Value:
+        """The node list of ElementwiseGradientRules.geluTanhApproximation (:280-288): SCALAR_MUL by the
+        FLOAT32 coefficients, TANH, and the infinity selection shared with SiLU."""
+        f = lambda bits: struct.unpack("<f", struct.pack("<I", bits))[0]
+        one = self.expand(self.constant(F32, 1.0), x.shape)
+        zero = self.expand(self.constant(F32, 0.0), x.shape)
+        squared = self.mul(x, x)
+        u = self.scalar_mul(self.add(x, self.scalar_mul(self.mul(squared, x), f(self._GELU_CUBIC))), f(self._SQRT_2_OVER_PI))
+        t = self.tanh(u)
+        u_prime = self.scalar_mul(self.add(one, self.scalar_mul(squared, f(self._GELU_CUBIC_DERIVATIVE))), f(self._SQRT_2_OVER_PI))
+        left = self.scalar_mul(self.add(one, t), f(self._HALF))
+        right = self.scalar_mul(self.mul(self.mul(x, self.sub(one, self.mul(t, t))), u_prime), f(self._HALF))
+        regular = self.mul(upstream, self.add(left, right))
+        return self.where(self.is_inf(x), self.where(self.gt(x, zero), upstream, zero), regular)
+
     def activation_backward(self, kind: str, pre_activation: Value, output: Value, upstream: Value) -> Value:
+        if kind == "gelu_tanh":
+            return self.gelu_tanh_backward(pre_activation, upstream)
         if kind == "relu":
             return self.relu_backward(pre_activation, upstream)
         if kind == "silu":

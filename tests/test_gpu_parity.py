@@ -384,7 +384,7 @@ def test_prefetch_overlaps_and_stays_ordered(ctx):
         b.close()
 
 
-@pytest.mark.parametrize("kind", ["tanh", "sigmoid", "silu"])
+@pytest.mark.parametrize("kind", ["tanh", "sigmoid", "silu", "gelu_tanh"])
 def test_tanh_and_sigmoid_nodes(ctx, oracle, kind):
     # binary64 function and one narrowing on both sides: identical except on the rare rounding tie
     # where the two binary64 libraries differ in the last place (stated bound: 1 ulp)
@@ -415,23 +415,27 @@ def test_tanh_and_sigmoid_backward_chains_round_per_node(ctx, oracle, kind):
     assert np.array_equal(got, oracle.activation_backward(kind, y, up))
 
 
-def test_silu_backward_chain_and_is_inf(ctx, oracle):
-    # where(isInf(x), where(x > 0, g, 0), (g * s) * (1 + x * (1 - s))), s = SIGMOID(x): every node rounds
-    # once; the device's sigmoid may differ from the checker's by 1 ulp on rare ties, so the chain is
-    # compared at 4 ulp of the result plus the infinities exactly
+@pytest.mark.parametrize("kind", ["silu", "gelu_tanh"])
+def test_silu_and_gelu_backward_chains_and_is_inf(ctx, oracle, kind):
+    # silu: where(isInf(x), where(x > 0, g, 0), (g * s) * (1 + x * (1 - s))), s = SIGMOID(x); the tanh GELU
+    # rule is the longer list of ElementwiseGradientRules.java:280-288.  Every node rounds once; the
+    # device's sigmoid / tanh may differ from the checker's by 1 ulp on rare ties, so the chains are
+    # compared at a few ulp of the result (plus a rounding of the upstream gradient where 1 - t * t
+    # cancels) and exactly at the infinities
     rng = np.random.default_rng(6)
     x = np.concatenate([rng.standard_normal(6000) * 3, [np.inf, -np.inf, 0.0, -0.0, 50.0, -50.0]]).astype(np.float32).reshape(-1, 6)
     up = rng.standard_normal(x.shape).astype(np.float32)
     g = GraphBuilder()
     xv, uv = g.feed(F32, x.shape), g.feed(F32, x.shape)
-    g.publish(g.silu_backward(xv, uv))
+    g.publish(g.silu_backward(xv, uv) if kind == "silu" else g.gelu_tanh_backward(xv, uv))
     g.publish(g.is_inf(xv))
     got, inf_mask = run_image(ctx, g, [x, up])
     assert np.array_equal(inf_mask.astype(bool), np.isinf(x))
-    want = oracle.activation_backward("silu", None, up, x)
+    want = oracle.activation_backward(kind, None, up, x)
     assert np.array_equal(got[np.isinf(x)], want[np.isinf(x)])
     finite = np.isfinite(x)
-    assert ulp_distance(got[finite], want[finite]).max() <= 4
+    tol = 4 * np.spacing(np.abs(want[finite])) + np.float32(2.0 ** -22) * np.abs(up[finite])
+    assert np.all(np.abs(got[finite] - want[finite]) <= tol)
 
 
 # ---- buffers and error statuses -----------------------------------------------------------------

@@ -254,3 +254,18 @@ def test_silu_special_values(oracle):
     assert y[5] == np.float32(1.0 / (1.0 + np.exp(-1.0)))
     g = oracle.activation_backward("silu", None, np.array([3.0, 3.0], np.float32), np.array([np.inf, -np.inf], np.float32))
     assert g[0] == 3.0 and g[1] == 0.0
+
+
+def test_gelu_tanh_special_values_and_coefficients(oracle):
+    # CpuScalarReferenceKernel.geluTanhApproximation (:1224-1229): -inf gives -0, +inf stays +inf, 0 gives 0;
+    # the gradient rule's FLOAT32 coefficients are the bit patterns of ElementwiseGradientRules.java:370-378
+    x = np.array([0.0, np.inf, -np.inf, np.nan, 1.0], np.float32)
+    y = oracle.gelu_tanh(x)
+    assert y[0] == 0.0 and y[1] == np.inf and y[2] == 0.0 and np.signbit(y[2]) and np.isnan(y[3])
+    want = 0.5 * (1.0 + np.tanh(np.sqrt(2.0 / np.pi) * (1.0 + 0.044715)))
+    assert y[4] == np.float32(want)
+    assert oracle._coefficient(0x3F000000) == np.float32(0.5) and oracle._coefficient(0x3D372713) == np.float32(0.044715)
+    assert oracle._coefficient(0x3F4C422A) == np.float32(np.sqrt(2.0 / np.pi))
+    assert oracle._coefficient(0x3E095D4F) == np.float32(3 * 0.044715)
+    g = oracle.activation_backward("gelu_tanh", None, np.array([3.0, 3.0, 2.0], np.float32), np.array([np.inf, -np.inf, 0.0], np.float32))
+    assert g[0] == 3.0 and g[1] == 0.0 and g[2] == 1.0            # d/dx at 0 is 1/2, times g = 2
