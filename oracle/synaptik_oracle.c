@@ -476,6 +476,8 @@ SYN_EXPORT int syn_oracle_accumulate_f32(int64_t count, float *accumulated, cons
 }
 
 /* ------------------------------------------------------------------------------------------ */
+/* Parity unpinned: the reference's tests hold no FLOAT32 known answers for the four functions    */
+/* below; they are pinned by their special values and by this restatement of the definition only. */
 /* TANH and SIGMOID on FLOAT32 (modules/backend/cpu/.../reference/CpuScalarReferenceKernel.java   */
 /* :1729-1742): the value widened to double, StrictMath.tanh, or the two-branch sigmoid of        */
 /* CpuScalarEmitter.java:429-439 (1 / (1 + exp(-x)) for x >= 0, exp(x) / (1 + exp(x)) below and   */
