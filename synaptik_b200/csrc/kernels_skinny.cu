@@ -68,64 +68,60 @@ __global__ void __launch_bounds__(512, 1) narrow_out_kernel(int64_t m, int k, co
 }
 
 // ---- narrow contraction: C[m, n] = A[m, K] . B[K, n], optionally gated (ReLU backward) -----------
-// A block owns eight strips of 128 consecutive result columns (one per warp) and walks the rows in
-// chunks of 32 that it stages from A into shared memory once for all eight warps; a warp keeps its
-// K x 4 slice of B in registers and, four rows at a time (loads first), reads the gate, forms the
-// products and stores.  Every cell is the reference's ascending-k chain of separately rounded multiply
-// and add, so the result is bit-identical to the exact kernel.
-constexpr int kInnerChunk = 32;
+// A warp owns 128 consecutive result columns and keeps its K x 4 slice of B in registers; it then
+// streams rows: K broadcast loads of A, one gate load and one store per row.  Every cell is the
+// reference's ascending-k chain of separately rounded multiply and add, so the result is
+// bit-identical to the exact kernel.
 template <int K>
 __global__ void __launch_bounds__(256) narrow_inner_kernel(int64_t m, int64_t n, const float *__restrict__ a, int64_t lda,
-        const float *__restrict__ b, int64_t ldb, const float *__restrict__ gate, float *c, int64_t ldc, int strip_groups, int64_t row_blocks) {
-    __shared__ float arows[kInnerChunk][K];
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    const int strip = (int)(blockIdx.x % strip_groups) * 8 + w;
-    const int64_t row_block = blockIdx.x / strip_groups;
+        const float *__restrict__ b, int64_t ldb, const float *__restrict__ gate, float *c, int64_t ldc, int strips) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int strip = (int)(warp % strips);
+    const int64_t first = warp / strips, step = warps / strips;
+    if (first >= step) return;                         // warps beyond a whole number of strip groups idle
     const int64_t col = (int64_t)strip * 128 + lane * 4;
-    const bool live = col < n;
-    float4 wv[K];
+    if (col >= n) return;
+    float4 w[K];
 #pragma unroll
-    for (int p = 0; p < K; p++) wv[p] = live ? *reinterpret_cast<const float4 *>(b + p * ldb + col) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    for (int64_t r0 = row_block * kInnerChunk; r0 < m; r0 += row_blocks * kInnerChunk) {
-        const int rows_here = (int)(m - r0 < kInnerChunk ? m - r0 : kInnerChunk);
-        __syncthreads();                                 // the previous chunk has been consumed
-        for (int e = threadIdx.x; e < rows_here * K; e += blockDim.x) {
-            const int rr = e / K, p = e - rr * K;
-            arows[rr][p] = __ldg(a + (r0 + rr) * lda + p);
+    for (int p = 0; p < K; p++) w[p] = *reinterpret_cast<const float4 *>(b + p * ldb + col);
+    // Four rows per trip, all their loads issued before the arithmetic: with one row in flight per
+    // warp the kernel waited on memory latency (measured 2.2 TB/s of result + gate traffic).
+    constexpr int ROWS = 4;
+    for (int64_t r = first; r < m; r += step * ROWS) {
+        float sv[ROWS][K];
+        float4 g[ROWS];
+#pragma unroll
+        for (int q = 0; q < ROWS; q++) {
+            const int64_t rr = r + q * step;
+            const bool live = rr < m;
+#pragma unroll
+            for (int p = 0; p < K; p++) sv[q][p] = live ? __ldg(a + rr * lda + p) : 0.0f;
+            g[q] = (gate && live) ? *reinterpret_cast<const float4 *>(gate + rr * n + col) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
         }
-        __syncthreads();
-        if (!live) continue;
-        constexpr int ROWS = 4;
-        for (int rr0 = 0; rr0 < rows_here; rr0 += ROWS) {
-            float4 g[ROWS];
 #pragma unroll
-            for (int q = 0; q < ROWS; q++)
-                g[q] = (gate && rr0 + q < rows_here) ? *reinterpret_cast<const float4 *>(gate + (r0 + rr0 + q) * n + col)
-                                                     : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+        for (int q = 0; q < ROWS; q++) {
+            const int64_t rr = r + q * step;
+            if (rr >= m) break;
+            float4 acc;
+            if (K == 1) {
+                acc = make_float4(__fmul_rn(sv[q][0], w[0].x), __fmul_rn(sv[q][0], w[0].y), __fmul_rn(sv[q][0], w[0].z), __fmul_rn(sv[q][0], w[0].w));
+            } else {
+                acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
-            for (int q = 0; q < ROWS; q++) {
-                if (rr0 + q >= rows_here) break;
-                float4 acc;
-                if (K == 1) {
-                    const float sc = arows[rr0 + q][0];
-                    acc = make_float4(__fmul_rn(sc, wv[0].x), __fmul_rn(sc, wv[0].y), __fmul_rn(sc, wv[0].z), __fmul_rn(sc, wv[0].w));
-                } else {
-                    acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-#pragma unroll
-                    for (int p = 0; p < K; p++) {
-                        const float sc = arows[rr0 + q][p];
-                        acc.x = __fadd_rn(acc.x, __fmul_rn(sc, wv[p].x));
-                        acc.y = __fadd_rn(acc.y, __fmul_rn(sc, wv[p].y));
-                        acc.z = __fadd_rn(acc.z, __fmul_rn(sc, wv[p].z));
-                        acc.w = __fadd_rn(acc.w, __fmul_rn(sc, wv[p].w));
-                    }
+                for (int p = 0; p < K; p++) {
+                    const float sc = sv[q][p];
+                    acc.x = __fadd_rn(acc.x, __fmul_rn(sc, w[p].x));
+                    acc.y = __fadd_rn(acc.y, __fmul_rn(sc, w[p].y));
+                    acc.z = __fadd_rn(acc.z, __fmul_rn(sc, w[p].z));
+                    acc.w = __fadd_rn(acc.w, __fmul_rn(sc, w[p].w));
                 }
-                if (gate) {
-                    acc.x = g[q].x > 0.0f ? acc.x : 0.0f; acc.y = g[q].y > 0.0f ? acc.y : 0.0f;
-                    acc.z = g[q].z > 0.0f ? acc.z : 0.0f; acc.w = g[q].w > 0.0f ? acc.w : 0.0f;
-                }
-                *reinterpret_cast<float4 *>(c + (r0 + rr0 + q) * ldc + col) = acc;
             }
+            if (gate) {
+                acc.x = g[q].x > 0.0f ? acc.x : 0.0f; acc.y = g[q].y > 0.0f ? acc.y : 0.0f;
+                acc.z = g[q].z > 0.0f ? acc.z : 0.0f; acc.w = g[q].w > 0.0f ? acc.w : 0.0f;
+            }
+            *reinterpret_cast<float4 *>(c + rr * ldc + col) = acc;
         }
     }
 }
@@ -210,8 +206,8 @@ template <int N> struct LaunchOut {
 };
 template <int K> struct LaunchInner {
     static void run(cudaStream_t s, int blocks, int64_t m, int64_t n, const float *a, int64_t lda, const float *b, int64_t ldb,
-                    const float *gate, float *c, int64_t ldc, int strip_groups, int64_t row_blocks) {
-        narrow_inner_kernel<K><<<blocks, 256, 0, s>>>(m, n, a, lda, b, ldb, gate, c, ldc, strip_groups, row_blocks);
+                    const float *gate, float *c, int64_t ldc, int strips) {
+        narrow_inner_kernel<K><<<blocks, 256, 0, s>>>(m, n, a, lda, b, ldb, gate, c, ldc, strips);
     }
 };
 template <int N> struct LaunchReduce {
@@ -247,13 +243,12 @@ cudaError_t gemm_narrow_inner(cudaStream_t s, int64_t m, int64_t n, int64_t k, c
                               const float *b, int64_t ldb, const float *gate, float *c, int64_t ldc) {
     if (!narrow_inner_supported(m, n, k, ldb, ldc) || !aligned16(b) || !aligned16(c) || (gate && !aligned16(gate))) return cudaErrorInvalidValue;
     int strips = (int)((n + 127) / 128);
-    int strip_groups = (strips + 7) / 8;
-    int64_t row_blocks = (kNarrowWarps / 8) / strip_groups;
-    int64_t most = (m + kInnerChunk - 1) / kInnerChunk;
-    if (row_blocks > most) row_blocks = most;
-    if (row_blocks < 1) row_blocks = 1;
-    int blocks = (int)(row_blocks * strip_groups);
-    dispatch_extent<LaunchInner>((int)k, s, blocks, m, n, a, lda, b, ldb, gate, c, ldc, strip_groups, row_blocks);
+    int64_t groups = kNarrowWarps / strips;
+    if (groups < 1) groups = 1;
+    if (groups > m) groups = m;
+    int64_t warps = groups * strips;
+    int blocks = (int)((warps + 7) / 8);
+    dispatch_extent<LaunchInner>((int)k, s, blocks, m, n, a, lda, b, ldb, gate, c, ldc, strips);
     return cudaGetLastError();
 }
 
