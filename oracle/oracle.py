@@ -109,6 +109,23 @@ def silu(x) -> np.ndarray:
     return y
 
 
+def clamp(x, lo: float, hi: float) -> np.ndarray:
+    x = _f32(x)
+    y = np.empty_like(x)
+    lib().syn_oracle_clamp_f32(ctypes.c_int64(x.size), _p(x), ctypes.c_float(lo), ctypes.c_float(hi), _p(y))
+    return y
+
+
+def clamp_backward(x, upstream, lo: float, hi: float) -> np.ndarray:
+    """ElementwiseGradientRules.clamp (:263-270): lowered = max(x, lo); upper = where(lowered < hi, g,
+    where(lowered == hi, g * 0.5, 0)); where(x > lo, upper, where(x == lo, upper * 0.5, 0))."""
+    x, g = _f32(x), _f32(upstream)
+    lo32, hi32, half, zero = np.float32(lo), np.float32(hi), np.float32(0.5), np.float32(0.0)
+    lowered = clamp(x, lo, np.inf)
+    upper = np.where(lowered < hi32, g, np.where(lowered == hi32, g * half, zero)).astype(np.float32)
+    return np.where(x > lo32, upper, np.where(x == lo32, upper * half, zero)).astype(np.float32)
+
+
 def gelu_tanh(x) -> np.ndarray:
     x = _f32(x)
     y = np.empty_like(x)

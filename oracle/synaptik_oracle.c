@@ -476,6 +476,26 @@ SYN_EXPORT int syn_oracle_accumulate_f32(int64_t count, float *accumulated, cons
 }
 
 /* ------------------------------------------------------------------------------------------ */
+/* CLAMP (modules/model/.../tensor/Tensor.java:2318-2345): MIN(MAX(x, lo), hi) in that order with  */
+/* Math.max / Math.min semantics: NaN propagates, -0 is below +0.                                */
+/* ------------------------------------------------------------------------------------------ */
+static float java_max_f(float a, float b) {
+    if (a != a) return a;
+    if (b != b) return b;
+    if (a == 0.0f && b == 0.0f) return signbit(a) ? b : a;
+    return a > b ? a : b;
+}
+static float java_min_f(float a, float b) {
+    if (a != a) return a;
+    if (b != b) return b;
+    if (a == 0.0f && b == 0.0f) return signbit(a) ? a : b;
+    return a < b ? a : b;
+}
+SYN_EXPORT void syn_oracle_clamp_f32(int64_t count, const float *x, float lo, float hi, float *y) {
+    for (int64_t i = 0; i < count; i++) y[i] = java_min_f(java_max_f(x[i], lo), hi);
+}
+
+/* ------------------------------------------------------------------------------------------ */
 /* Parity unpinned: the reference's tests hold no FLOAT32 known answers for the four functions    */
 /* below; they are pinned by their special values and by this restatement of the definition only. */
 /* TANH and SIGMOID on FLOAT32 (modules/backend/cpu/.../reference/CpuScalarReferenceKernel.java   */

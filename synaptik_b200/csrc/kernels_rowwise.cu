@@ -86,6 +86,13 @@ __device__ __forceinline__ float java_max(float a, float b) {   // Math.max: NaN
     return a > b ? a : b;
 }
 
+__device__ __forceinline__ float java_min(float a, float b) {   // Math.min: NaN wins, -0 below +0
+    if (a != a) return a;
+    if (b != b) return b;
+    if (a == 0.0f && b == 0.0f) return (__float_as_uint(a) >> 31) ? a : b;
+    return a < b ? a : b;
+}
+
 __device__ __forceinline__ double warp_sum(double v) {
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
@@ -118,6 +125,8 @@ __global__ void binary_kernel(int op, const float *__restrict__ a, const float *
             case Op::SUB: ((float *)out)[i] = __fsub_rn(x, y); break;
             case Op::MUL: ((float *)out)[i] = __fmul_rn(x, y); break;
             case Op::DIV: ((float *)out)[i] = __fdiv_rn(x, y); break;
+            case Op::LT: ((uint8_t *)out)[i] = x < y ? 1 : 0; break;
+            case Op::EQ: ((uint8_t *)out)[i] = x == y ? 1 : 0; break;
             default: ((uint8_t *)out)[i] = x > y ? 1 : 0; break;          // GT
         }
     }
@@ -144,7 +153,7 @@ __global__ void scalar_f32_kernel(int op, const float *__restrict__ a, float *ou
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         float x = a[i];
         if ((Op)op == Op::SCALAR_MUL) out[i] = __fmul_rn(x, scalar);
-        else if ((Op)op == Op::SCALAR_MIN) out[i] = (x != x || scalar != scalar) ? (x != x ? x : scalar) : (x < scalar ? x : scalar);
+        else if ((Op)op == Op::SCALAR_MIN) out[i] = java_min(x, scalar);
         else out[i] = java_max(x, scalar);
     }
 }

@@ -502,7 +502,7 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
                 break;
             }
             case Op::MATMUL: message = "internal: MATMUL not grouped"; return INTERNAL_ERROR;
-            case Op::ADD: case Op::SUB: case Op::MUL: case Op::DIV: case Op::GT:
+            case Op::ADD: case Op::SUB: case Op::MUL: case Op::DIV: case Op::GT: case Op::LT: case Op::EQ:
                 assign_output(out0);
                 st.kind = StepKind::BINARY; st.a = n.inputs[0]; st.b = n.inputs[1]; st.out = out0;
                 finish_step(st);
@@ -512,6 +512,17 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
                 st.kind = StepKind::SCALAR; st.a = in0; st.out = out0; st.scalar_bits = n.attrs[0];
                 finish_step(st);
                 break;
+            case Op::CLAMP: {
+                // MIN(MAX(input, minValue), maxValue), exactly in that order (Tensor.java:2318-2345):
+                // the lower bound into the result, then the upper bound in place
+                assign_output(out0);
+                Step lower = st;
+                lower.kind = StepKind::SCALAR; lower.op = Op::SCALAR_MAX; lower.a = in0; lower.out = out0; lower.scalar_bits = n.attrs[0];
+                finish_step(lower);
+                st.kind = StepKind::SCALAR; st.op = Op::SCALAR_MIN; st.a = out0; st.out = out0; st.scalar_bits = n.attrs[1];
+                finish_step(st);
+                break;
+            }
             case Op::RELU: case Op::EXP: case Op::TANH: case Op::SIGMOID: case Op::SILU: case Op::IS_INF: case Op::GELU_TANH:
                 assign_output(out0);
                 st.kind = StepKind::UNARY; st.a = in0; st.out = out0;

@@ -20,6 +20,7 @@ const char *op_name(Op op) {
         case Op::MEAN_SQUARED_ERROR: return "MEAN_SQUARED_ERROR"; case Op::ARG_MAX: return "ARG_MAX";
         case Op::TANH: return "TANH"; case Op::SIGMOID: return "SIGMOID"; case Op::SILU: return "SILU";
         case Op::IS_INF: return "IS_INF"; case Op::GELU_TANH: return "GELU_TANH_APPROXIMATION";
+        case Op::CLAMP: return "CLAMP"; case Op::LT: return "LT"; case Op::EQ: return "EQ";
     }
     return "?";
 }
@@ -104,10 +105,10 @@ Status check_node(const Program &g, int index, std::string &message) {
                 FAIL(GRAPH_COMPILATION_FAILED, name << ": shape");
             if (in(0).shape[1] < 1) FAIL(UNSUPPORTED_SHAPE, name << ": empty contraction");
             return OK;
-        case Op::ADD: case Op::SUB: case Op::MUL: case Op::DIV: case Op::GT:
+        case Op::ADD: case Op::SUB: case Op::MUL: case Op::DIV: case Op::GT: case Op::LT: case Op::EQ:
             if (!need(2, 1)) FAIL(GRAPH_COMPILATION_FAILED, name << ": arity");
             if (in(0).dtype != DType::F32 || in(1).dtype != DType::F32) FAIL(UNSUPPORTED_OPERATION, name << ": only FLOAT32 operands");
-            if (out(0).dtype != (n.op == Op::GT ? DType::BOOL : DType::F32)) FAIL(GRAPH_COMPILATION_FAILED, name << ": result dtype");
+            if (out(0).dtype != ((n.op == Op::GT || n.op == Op::LT || n.op == Op::EQ) ? DType::BOOL : DType::F32)) FAIL(GRAPH_COMPILATION_FAILED, name << ": result dtype");
             if (!broadcastable(in(0).shape, in(1).shape, shape) || shape != out(0).shape) FAIL(GRAPH_COMPILATION_FAILED, name << ": broadcast shape");
             if (shape.size() > 4) FAIL(UNSUPPORTED_SHAPE, name << ": rank above 4");
             return OK;
@@ -115,6 +116,11 @@ Status check_node(const Program &g, int index, std::string &message) {
             if (!need(1, 1) || n.attrs.size() != 1) FAIL(GRAPH_COMPILATION_FAILED, name << ": arity");
             if (in(0).dtype != out(0).dtype || in(0).shape != out(0).shape) FAIL(GRAPH_COMPILATION_FAILED, name << ": shape or dtype");
             if (in(0).dtype == DType::BOOL || (n.op == Op::SCALAR_MUL && in(0).dtype != DType::F32)) FAIL(UNSUPPORTED_OPERATION, name << ": dtype");
+            return OK;
+        case Op::CLAMP:
+            if (!need(1, 1) || n.attrs.size() != 2) FAIL(GRAPH_COMPILATION_FAILED, name << ": arity");
+            if (in(0).dtype != DType::F32 || out(0).dtype != DType::F32) FAIL(UNSUPPORTED_OPERATION, name << ": only FLOAT32");
+            if (in(0).shape != out(0).shape) FAIL(GRAPH_COMPILATION_FAILED, name << ": shape");
             return OK;
         case Op::IS_INF:
             if (!need(1, 1)) FAIL(GRAPH_COMPILATION_FAILED, name << ": arity");

@@ -24,10 +24,15 @@ OPS = {
     "PERMUTE": 1, "MATMUL": 2, "ADD": 3, "SUB": 4, "MUL": 5, "DIV": 6, "SCALAR_MUL": 7, "SCALAR_MIN": 8,
     "SCALAR_MAX": 9, "RELU": 10, "EXP": 11, "GT": 12, "WHERE": 13, "EXPAND": 14, "EXPAND_DIMS": 15,
     "CONTIGUOUS": 16, "ONE_HOT": 17, "MAX": 18, "SUM": 19, "SUM_TO_SHAPE": 20, "SOFTMAX": 21,
-    "INDEX_CROSS_ENTROPY": 22, "MEAN_SQUARED_ERROR": 23, "ARG_MAX": 24, "TANH": 25, "SIGMOID": 26, "SILU": 27, "IS_INF": 28, "GELU_TANH": 29,
+    "INDEX_CROSS_ENTROPY": 22, "MEAN_SQUARED_ERROR": 23, "ARG_MAX": 24, "TANH": 25, "SIGMOID": 26, "SILU": 27, "IS_INF": 28, "GELU_TANH": 29, "CLAMP": 30, "LT": 31, "EQ": 32,
 }
 ROLE_INTERMEDIATE, ROLE_FEED, ROLE_CONSTANT = 0, 1, 2
 MASK64 = (1 << 64) - 1
+
+
+def _f32_round(x: float) -> float:
+    """The binary32 value nearest to x, as a Python float."""
+    return struct.unpack("<f", struct.pack("<f", float(x)))[0]
 
 
 def _f64_bits(x: float) -> int:
@@ -116,13 +121,29 @@ class GraphBuilder:
         return self._node("MATMUL", [a, b], F32, (a.shape[0], b.shape[1]))
 
     def _binary(self, op: str, a: Value, b: Value) -> Value:
-        return self._node(op, [a, b], BOOL if op == "GT" else F32, _broadcast(a.shape, b.shape))
+        return self._node(op, [a, b], BOOL if op in ("GT", "LT", "EQ") else F32, _broadcast(a.shape, b.shape))
 
     def add(self, a, b): return self._binary("ADD", a, b)
     def sub(self, a, b): return self._binary("SUB", a, b)
     def mul(self, a, b): return self._binary("MUL", a, b)
     def div(self, a, b): return self._binary("DIV", a, b)
     def gt(self, a, b): return self._binary("GT", a, b)
+    def lt(self, a, b): return self._binary("LT", a, b)
+    def eq(self, a, b): return self._binary("EQ", a, b)
+
+    def clamp(self, x: Value, min_value: float, max_value: float) -> Value:
+        """CLAMP: MIN(MAX(x, min), max) with FLOAT32 bounds (Tensor.java:2318-2345)."""
+        return self._node("CLAMP", [x], F32, x.shape, [_f64_bits(_f32_round(min_value)), _f64_bits(_f32_round(max_value))])
+
+    def clamp_backward(self, x: Value, upstream: Value, min_value: float, max_value: float) -> Value:
+        """The node list of ElementwiseGradientRules.clamp (:263-270): the gradient passes inside the
+        range, half of it at a bound, none outside."""
+        zero = self.expand(self.constant(F32, 0.0), x.shape)
+        lo = self.expand(self.constant(F32, _f32_round(min_value)), x.shape)
+        hi = self.expand(self.constant(F32, _f32_round(max_value)), x.shape)
+        lowered = self.scalar_max(x, _f32_round(min_value))
+        upper = self.where(self.lt(lowered, hi), upstream, self.where(self.eq(lowered, hi), self.scalar_mul(upstream, 0.5), zero))
+        return self.where(self.gt(x, lo), upper, self.where(self.eq(x, lo), self.scalar_mul(upper, 0.5), zero))
 
     def _scalar(self, op: str, x: Value, scalar) -> Value:
         bits = _f64_bits(scalar) if x.dtype == F32 else int(scalar)

@@ -438,6 +438,30 @@ def test_silu_and_gelu_backward_chains_and_is_inf(ctx, oracle, kind):
     assert np.all(np.abs(got[finite] - want[finite]) <= tol)
 
 
+def test_clamp_and_its_gradient_chain_are_bit_exact(ctx, oracle):
+    # CLAMP = MIN(MAX(x, lo), hi) with Math.max / Math.min semantics (NaN propagates, -0 below +0), and
+    # the gradient node list of ElementwiseGradientRules.clamp: inside the range the gradient passes, at
+    # a bound half of it, outside nothing.  Only comparisons, selections and one exact halving: bit for bit.
+    rng = np.random.default_rng(9)
+    x = np.concatenate([rng.standard_normal(4000) * 2, [-1.0, 1.5, 0.0, -0.0, np.nan, np.inf, -np.inf, -1.0000001, 1.4999999]]).astype(np.float32)
+    up = rng.standard_normal(x.shape).astype(np.float32)
+    g = GraphBuilder()
+    xv, uv = g.feed(F32, x.shape), g.feed(F32, x.shape)
+    g.publish(g.clamp(xv, -1.0, 1.5))
+    g.publish(g.clamp_backward(xv, uv, -1.0, 1.5))
+    g.publish(g.clamp(xv, -0.0, 0.0))
+    got, grad, zeros = run_image(ctx, g, [x, up])
+    want = oracle.clamp(x, -1.0, 1.5)
+    assert np.array_equal(got.view(np.uint32)[~np.isnan(want)], want.view(np.uint32)[~np.isnan(want)]) and np.array_equal(np.isnan(got), np.isnan(want))
+    want_grad = oracle.clamp_backward(x, up, -1.0, 1.5)
+    assert np.array_equal(grad, want_grad)
+    assert grad[x == np.float32(-1.0)][0] == up[x == np.float32(-1.0)][0] * np.float32(0.5)
+    # bounds [-0, +0]: negative inputs and -0 keep -0, positive inputs and +0 give +0 (Tensor.java:2328-2329)
+    finite = ~np.isnan(x)
+    assert np.array_equal(np.signbit(zeros[finite]), np.signbit(x[finite]))
+    assert not zeros[finite].any()
+
+
 # ---- buffers and error statuses -----------------------------------------------------------------
 def test_buffers_canonical_bytes_and_errors(ctx):
     values = np.array([1.0, -2.5, 3.25e-3, 7e8], dtype=np.float32)

@@ -269,3 +269,16 @@ def test_gelu_tanh_special_values_and_coefficients(oracle):
     assert oracle._coefficient(0x3E095D4F) == np.float32(3 * 0.044715)
     g = oracle.activation_backward("gelu_tanh", None, np.array([3.0, 3.0, 2.0], np.float32), np.array([np.inf, -np.inf, 0.0], np.float32))
     assert g[0] == 3.0 and g[1] == 0.0 and g[2] == 1.0            # d/dx at 0 is 1/2, times g = 2
+
+
+def test_clamp_signed_zero_and_nan_rules(oracle):
+    # documented on Tensor.clamp (Tensor.java:2325-2331): NaN input gives NaN; bounds [-0, +0] keep -0 for
+    # negative inputs and -0, +0 for positive inputs and +0; bounds [+0, -0] give -0 for every non-NaN input
+    x = np.array([-3.0, -0.0, 0.0, 2.0, np.nan], np.float32)
+    a = oracle.clamp(x, -0.0, 0.0)
+    assert list(np.signbit(a[:4])) == [True, True, False, False] and not a[:4].any() and np.isnan(a[4])
+    b = oracle.clamp(x, 0.0, -0.0)
+    assert all(np.signbit(b[:4])) and not b[:4].any() and np.isnan(b[4])
+    assert list(oracle.clamp(np.array([-5.0, 0.25, 9.0], np.float32), -1.0, 1.5)) == [-1.0, 0.25, 1.5]
+    g = oracle.clamp_backward(np.array([-2.0, -1.0, 0.0, 1.5, 2.0], np.float32), np.full(5, 4.0, np.float32), -1.0, 1.5)
+    assert list(g) == [0.0, 2.0, 4.0, 2.0, 0.0]
