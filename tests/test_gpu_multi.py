@@ -78,9 +78,9 @@ def test_ranks_match_one_rank_after_every_step(tmp_path):
         info = json.load(open(out + f".w{world}.json"))
         assert info["replicas_identical"], world
         # Adam turns gradient rounding differences near zero into fractions of lr: bound the drift per
-        # entry by 2 * lr * (steps so far) and on average by 1 % of lr per step (the trajectories of two
+        # entry by 2 * lr * (steps so far) and on average by 2 % of lr per step (the trajectories of two
         # summation orders drift apart slowly; measured on 4 ranks: 5e-5 after 17 steps), after every step
         for step in range(one.shape[0]):
             drift = np.abs(one[step] - many[step])
-            assert drift.max() <= 2e-3 * (step + 1) and drift.mean() <= 1e-5 * (step + 1), (world, step, drift.max(), drift.mean())
+            assert drift.max() <= 2e-3 * (step + 1) and drift.mean() <= 2e-5 * (step + 1), (world, step, drift.max(), drift.mean())
         assert np.allclose(info1["losses"], info["losses"], rtol=2e-4), world
