@@ -222,7 +222,7 @@ def run_cuda(args):
             exe.enqueue([xb, tb, seed] + model.param_buffers, outputs)
             optimizer.step_enqueue(grads)
             loss.download_async(loss_host.pointer, 4)
-            exe.finish(); optimizer.finish()    # the caller reads the objective (and any error) every step
+            optimizer.finish()                  # one wait per step: the objective and the context's error word (run and update)
 
     def reduce_max(value: float) -> float:
         if not distributed:
