@@ -239,6 +239,16 @@ def mse(prediction, target) -> np.float32:
     return np.float32(lib().syn_oracle_mse_f32(ctypes.c_int64(p.size), _p(p), _p(t)))
 
 
+def squared_error(prediction, target, reduction: str = "none"):
+    """MEAN_SQUARED_ERROR with reduction NONE (per element) or SUM (CpuLossReferenceKernel.java:67-87)."""
+    p, t = _f32(prediction), _f32(target)
+    if reduction == "sum":
+        lib().syn_oracle_squared_error_sum_f32.restype = ctypes.c_float
+        return np.float32(lib().syn_oracle_squared_error_sum_f32(ctypes.c_int64(p.size), _p(p.ravel()), _p(t.ravel())))
+    d = (p - t).astype(np.float32)
+    return (d * d).astype(np.float32)
+
+
 def mse_backward(prediction, target, seed: float = 1.0, count: int = 0) -> np.ndarray:
     p, t = _f32(prediction), _f32(target)
     out = np.empty_like(p)

@@ -309,6 +309,16 @@ SYN_EXPORT float syn_oracle_mse_f32(int64_t count, const float *prediction, cons
     return exact_count_quotient(sum, count);
 }
 
+/* The SUM reduction of the same kernel (CpuLossReferenceKernel.java:81-86): no quotient. */
+SYN_EXPORT float syn_oracle_squared_error_sum_f32(int64_t count, const float *prediction, const float *target) {
+    float sum = 0.0f;
+    for (int64_t i = 0; i < count; i++) {
+        float difference = prediction[i] - target[i];
+        sum += difference * difference;
+    }
+    return sum;
+}
+
 /* MSE backward chain, LossGradientRules.java:77-101,254-267:
  * d = ((p - t) * 2) * (expand(seed) / count). */
 SYN_EXPORT void syn_oracle_mse_backward_f32(int64_t count, const float *prediction,

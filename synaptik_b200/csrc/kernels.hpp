@@ -28,7 +28,9 @@ cudaError_t row_reduce(cudaStream_t s, Op op, const float *x, float *out, int64_
 cudaError_t full_sum(cudaStream_t s, const float *x, const Index4 &ix, int64_t total, float *out);
 cudaError_t argmax_rows(cudaStream_t s, const float *x, int64_t *out, int64_t rows, int64_t cols);
 cudaError_t softmax_rows(cudaStream_t s, const float *x, float *out, int64_t rows, int64_t cols);
-cudaError_t mse_mean(cudaStream_t s, const float *p, const float *t, int64_t count, float *out);
+// Squared error (CpuLossReferenceKernel.java:67-87): reduction 0 = per-element (p - t)^2 into out[count],
+// 1 = mean, 2 = sum into out[0]; up to 65536 elements the sum is the reference's sequential binary32 one.
+cudaError_t mse(cudaStream_t s, int reduction, const float *p, const float *t, int64_t count, float *out);
 
 // ---- fused memory-bound kernels ----------------------------------------------------------------
 // out = gate > 0 ? upstream : 0   (WHERE(GT(z,0), g, 0), ElementwiseGradientRules.java:210)

@@ -395,7 +395,14 @@ __global__ void softmax_kernel(const float *__restrict__ x, float *out, int64_t 
 // MEAN_SQUARED_ERROR, CpuLossReferenceKernel.java:67-87: ascending binary32 accumulation of the
 // squared differences, then the exact quotient by the count rounded once (:221-225).  Small
 // inputs are accumulated by one thread in the reference's order; large ones by a binary64 tree.
-__global__ void mse_kernel(const float *__restrict__ p, const float *__restrict__ t, int64_t count, float *out) {
+__global__ void squared_error_kernel(const float *__restrict__ p, const float *__restrict__ t, int64_t count, float *out) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x) {
+        const float d = __fsub_rn(p[i], t[i]);
+        out[i] = __fmul_rn(d, d);
+    }
+}
+
+__global__ void mse_kernel(const float *__restrict__ p, const float *__restrict__ t, int64_t count, float *out, int mean) {
     __shared__ double partial[32];
     float total;
     if (count <= 65536) {
@@ -417,6 +424,7 @@ __global__ void mse_kernel(const float *__restrict__ p, const float *__restrict_
     }
     // binary64 holds the quotient of a 24-bit numerator by a count below 2^28 to well under half a
     // binary32 ulp of any non-tie, so the second rounding cannot move the result
+    if (!mean) { out[0] = total; return; }
     out[0] = (total == 0.0f || !isfinite(total)) ? total / (float)count : (float)((double)total / (double)count);
 }
 
@@ -852,8 +860,13 @@ cudaError_t softmax_rows(cudaStream_t s, const float *x, float *out, int64_t row
     return cudaGetLastError();
 }
 
-cudaError_t mse_mean(cudaStream_t s, const float *p, const float *t, int64_t count, float *out) {
-    mse_kernel<<<1, 1024, 0, s>>>(p, t, count, out);
+cudaError_t mse(cudaStream_t s, int reduction, const float *p, const float *t, int64_t count, float *out) {
+    if (reduction == 0) {
+        if (count == 0) return cudaSuccess;
+        squared_error_kernel<<<grid_for(count, kThreads), kThreads, 0, s>>>(p, t, count, out);
+    } else {
+        mse_kernel<<<1, 1024, 0, s>>>(p, t, count, out, reduction == 1);
+    }
     return cudaGetLastError();
 }
 

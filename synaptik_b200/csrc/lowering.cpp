@@ -570,6 +570,7 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
                 if (dense_input(n.inputs[0]) < 0 || dense_input(n.inputs[1]) < 0) return UNSUPPORTED_SHAPE;
                 assign_output(out0);
                 st.kind = StepKind::MSE; st.a = n.inputs[0]; st.b = n.inputs[1]; st.out = out0; st.m = g.values[n.inputs[0]].elements();
+                st.scalar_bits = n.attrs[0];            // reduction: 0 NONE, 1 MEAN, 2 SUM
                 finish_step(st);
                 break;
             case Op::ARG_MAX:

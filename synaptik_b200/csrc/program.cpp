@@ -205,8 +205,10 @@ Status check_node(const Program &g, int index, std::string &message) {
         case Op::MEAN_SQUARED_ERROR:
             if (!need(2, 1) || n.attrs.size() < 1) FAIL(GRAPH_COMPILATION_FAILED, name << ": arity");
             if (in(0).dtype != DType::F32 || in(1).dtype != DType::F32 || out(0).dtype != DType::F32) FAIL(UNSUPPORTED_OPERATION, name << ": only FLOAT32");
-            if (in(0).shape != in(1).shape || out(0).elements() != 1) FAIL(GRAPH_COMPILATION_FAILED, name << ": shape");
-            if (n.attrs[0] != 1) FAIL(UNSUPPORTED_OPERATION, name << ": only MEAN reduction");
+            // reduction: 0 NONE (per-element result), 1 MEAN, 2 SUM
+            if (n.attrs[0] > 2) FAIL(UNSUPPORTED_OPERATION, name << ": unknown reduction");
+            if (in(0).shape != in(1).shape) FAIL(GRAPH_COMPILATION_FAILED, name << ": shape");
+            if (n.attrs[0] == 0 ? out(0).shape != in(0).shape : out(0).elements() != 1) FAIL(GRAPH_COMPILATION_FAILED, name << ": result shape");
             return OK;
         case Op::ARG_MAX: {
             if (!need(1, 1) || n.attrs.size() != 2) FAIL(GRAPH_COMPILATION_FAILED, name << ": arity");

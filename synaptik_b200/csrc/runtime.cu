@@ -524,7 +524,7 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                 if (st.out >= 0) x->launches++;
                 break;
             case StepKind::MSE:
-                LAUNCH(kern::mse_mean(s, (const float *)ptr(st.a), (const float *)ptr(st.b), st.m, (float *)ptr(st.out)));
+                LAUNCH(kern::mse(s, (int)st.scalar_bits, (const float *)ptr(st.a), (const float *)ptr(st.b), st.m, (float *)ptr(st.out)));
                 break;
             case StepKind::ARG_MAX:
                 LAUNCH(kern::argmax_rows(s, (const float *)ptr(st.a), (int64_t *)ptr(st.out), st.m, st.n));

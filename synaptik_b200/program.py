@@ -199,8 +199,11 @@ class GraphBuilder:
         """INDEX_CATEGORICAL_CROSS_ENTROPY_WITH_LOGITS, class axis 1, MEAN, no ignore index."""
         return self._node("INDEX_CROSS_ENTROPY", [logits, labels], F32, (), [1, 1, 0, 0])
 
-    def mean_squared_error(self, prediction: Value, target: Value) -> Value:
-        return self._node("MEAN_SQUARED_ERROR", [prediction, target], F32, (), [1])
+    MSE_REDUCTIONS = {"none": 0, "mean": 1, "sum": 2}
+
+    def mean_squared_error(self, prediction: Value, target: Value, reduction: str = "mean") -> Value:
+        shape = prediction.shape if reduction == "none" else ()
+        return self._node("MEAN_SQUARED_ERROR", [prediction, target], F32, shape, [self.MSE_REDUCTIONS[reduction]])
 
     def arg_max(self, x: Value, axis: int = 1, keep_dimensions: bool = False) -> Value:
         shape = list(x.shape)
@@ -295,14 +298,17 @@ class GraphBuilder:
         scale = self.expand_dims(self._loss_scale(seed, rows), 1)
         return self.mul(self.sub(p, hot), scale)
 
-    def mean_squared_error_backward(self, prediction: Value, target: Value, seed: Value) -> Value:
-        flat = prediction.elements
+    def mean_squared_error_backward(self, prediction: Value, target: Value, seed: Value, reduction: str = "mean") -> Value:
+        """((p - t) * 2) * restore(gradient) (LossGradientRules.java:77-101): MEAN restores the output
+        cotangent as expand(seed) / count, SUM as expand(seed), NONE takes it element by element."""
         doubled = self.scalar_mul(self.sub(prediction, target), 2.0)
-        ones = self.contiguous(self.expand(self.constant(F32, 1.0), prediction.shape))
-        count = self.sum_all(ones)
-        scale = self.div(self.expand(seed, prediction.shape), count)
-        del flat
-        return self.mul(doubled, scale)
+        if reduction == "none":
+            return self.mul(doubled, seed)
+        restored = self.expand(seed, prediction.shape)
+        if reduction == "mean":
+            ones = self.contiguous(self.expand(self.constant(F32, 1.0), prediction.shape))
+            restored = self.div(restored, self.sum_all(ones))
+        return self.mul(doubled, restored)
 
     # ---- serialisation --------------------------------------------------------------------
     def build(self) -> bytes:

@@ -345,6 +345,27 @@ def test_mse_matches_the_checker(ctx, oracle):
     assert np.array_equal(grad, oracle.mse_backward(p, t))
 
 
+def test_mse_sum_and_none_reductions(ctx, oracle):
+    # the other two reductions of the same reference kernel (CpuLossReferenceKernel.java:67-87) and the
+    # cotangents the gradient rule restores for them (LossGradientRules.java:77-101): bit for bit
+    rng = np.random.default_rng(16)
+    p = rng.standard_normal((96, 7)).astype(np.float32)
+    t = rng.standard_normal((96, 7)).astype(np.float32)
+    up = rng.standard_normal((96, 7)).astype(np.float32)
+    g = GraphBuilder()
+    pv, tv, sv, uv = g.feed(F32, p.shape), g.feed(F32, p.shape), g.feed(F32, ()), g.feed(F32, p.shape)
+    g.publish(g.mean_squared_error(pv, tv, "sum"))
+    g.publish(g.mean_squared_error(pv, tv, "none"))
+    g.publish(g.mean_squared_error_backward(pv, tv, sv, "sum"))
+    g.publish(g.mean_squared_error_backward(pv, tv, uv, "none"))
+    total, each, d_sum, d_none = run_image(ctx, g, [p, t, np.float32(0.75), up])
+    assert np.float32(total) == oracle.squared_error(p, t, "sum")
+    assert np.array_equal(each, oracle.squared_error(p, t, "none"))
+    doubled = ((p - t).astype(np.float32) * np.float32(2.0)).astype(np.float32)
+    assert np.array_equal(d_sum, (doubled * np.float32(0.75)).astype(np.float32))
+    assert np.array_equal(d_none, (doubled * up).astype(np.float32))
+
+
 def test_prefetch_overlaps_and_stays_ordered(ctx):
     # double-buffered feeding: while run i is enqueued, the operands of run i + 1 are copied on the
     # copy stream into the other buffer; a prefetch into a buffer waits for the run that still reads it,

@@ -282,3 +282,13 @@ def test_clamp_signed_zero_and_nan_rules(oracle):
     assert list(oracle.clamp(np.array([-5.0, 0.25, 9.0], np.float32), -1.0, 1.5)) == [-1.0, 0.25, 1.5]
     g = oracle.clamp_backward(np.array([-2.0, -1.0, 0.0, 1.5, 2.0], np.float32), np.full(5, 4.0, np.float32), -1.0, 1.5)
     assert list(g) == [0.0, 2.0, 4.0, 2.0, 0.0]
+
+
+def test_squared_error_reductions(oracle):
+    # CpuLossReferenceKernel.meanSquaredError (:67-87): NONE keeps (p - t)^2 per element, SUM adds them in
+    # increasing order in binary32, MEAN divides that sum by the count exactly
+    p = np.array([1.0, 2.0, 4.0, 1.0], np.float32)
+    t = np.array([0.0, 0.0, 1.0, 1.0 + 2.0 ** -12], np.float32)
+    assert list(oracle.squared_error(p, t, "none")) == [1.0, 4.0, 9.0, 2.0 ** -24]
+    assert oracle.squared_error(p, t, "sum") == np.float32(14.0)            # 14 + 2^-24 rounds back to 14
+    assert oracle.mse(p, t) == np.float32(3.5)
