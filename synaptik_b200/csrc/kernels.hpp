@@ -53,9 +53,11 @@ cudaError_t colsum_static(cudaStream_t s, int device, const float *g, int64_t ro
 // Index cross entropy with logits: per-row loss into row_loss (rows floats of scratch), optional
 // gradient (softmax - onehot) * (seed / rows), optional row arg-max, then the mean of row_loss
 // into loss_out (optional).  Labels outside [0, cols) set ERR_LABEL_RANGE in *error_word.
+// sum_only: loss_out receives the sum of the row losses instead of their mean (reduction SUM); for
+// reduction NONE the caller passes its result as row_loss and no loss_out.
 cudaError_t cross_entropy(cudaStream_t s, const float *logits, DType label_type, const void *labels,
                           const float *seed, int64_t rows, int64_t cols, float *row_loss, float *loss_out,
-                          float *grad_out, int64_t *argmax_out, int *error_word);
+                          float *grad_out, int64_t *argmax_out, int *error_word, int sum_only = 0);
 
 // ---- optimizers -----------------------------------------------------------------------------
 // acc: pending gradient sum of the tensor (TrainingParameter.java:373-390), used per `gradient_mode`:

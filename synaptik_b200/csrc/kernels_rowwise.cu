@@ -661,7 +661,7 @@ __global__ void ce_rows_generic_kernel(const float *__restrict__ logits, const v
 
 // Mean of the per-row losses: the reference adds them in ascending binary32 order and divides by
 // the count; one block adds them in binary64 in a fixed order and rounds once.
-__global__ void mean_kernel(const float *__restrict__ values, int64_t count, float *out) {
+__global__ void mean_kernel(const float *__restrict__ values, int64_t count, float *out, int divide) {
     __shared__ double partial[32];
     double acc = 0.0;
     for (int64_t i = threadIdx.x; i < count; i += blockDim.x) acc += (double)values[i];
@@ -671,7 +671,7 @@ __global__ void mean_kernel(const float *__restrict__ values, int64_t count, flo
     if (threadIdx.x < 32) {
         double v = threadIdx.x < (blockDim.x >> 5) ? partial[threadIdx.x] : 0.0;
         v = warp_sum(v);
-        if (threadIdx.x == 0) out[0] = __fdiv_rn((float)v, (float)count);
+        if (threadIdx.x == 0) out[0] = divide ? __fdiv_rn((float)v, (float)count) : (float)v;
     }
 }
 
@@ -932,7 +932,8 @@ cudaError_t colsum_static(cudaStream_t s, int device, const float *g, int64_t ro
 }
 
 cudaError_t cross_entropy(cudaStream_t s, const float *logits, DType label_type, const void *labels, const float *seed,
-                          int64_t rows, int64_t cols, float *row_loss, float *loss_out, float *grad_out, int64_t *argmax_out, int *error_word) {
+                          int64_t rows, int64_t cols, float *row_loss, float *loss_out, float *grad_out, int64_t *argmax_out, int *error_word,
+                          int sum_only) {
     if (rows == 0 || cols == 0) return cudaErrorInvalidValue;
     int grid = grid_for(rows, kThreads / 32);
     bool vec = (cols & 3) == 0 && cols >= 128 && cols <= 1024 && (((uintptr_t)logits | (uintptr_t)grad_out) & 15) == 0;
@@ -953,7 +954,7 @@ cudaError_t cross_entropy(cudaStream_t s, const float *logits, DType label_type,
 #undef SYN_CE_ARGS
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess || !loss_out) return e;
-    mean_kernel<<<1, 1024, 0, s>>>(row_loss, rows, loss_out);
+    mean_kernel<<<1, 1024, 0, s>>>(row_loss, rows, loss_out, !sum_only);
     return cudaGetLastError();
 }
 

@@ -106,6 +106,7 @@ struct LinearGroup {          // MATMUL [-> ADD bias] [-> RELU] [-> gate by WHER
 
 struct CrossEntropyGroup {
     int logits = -1, labels = -1, seed = -1, loss = -1, grad = -1, argmax = -1;
+    int reduction = 1;                      // of the forward loss node: 0 NONE, 1 MEAN, 2 SUM
     std::set<int> nodes;
     int emit_at = -1;
 };
@@ -329,6 +330,7 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
         for (auto &ce : ces) if (ce.loss < 0 && ce.logits == n.inputs[0] && ce.labels == n.inputs[1]) { host = &ce; break; }
         if (!host) { ces.emplace_back(); host = &ces.back(); host->logits = n.inputs[0]; host->labels = n.inputs[1]; }
         host->loss = n.outputs[0];
+        host->reduction = (int)n.attrs[1];
         host->nodes.insert(i);
         covered[i] = 1;
     }
@@ -354,6 +356,7 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
         st.kind = StepKind::CROSS_ENTROPY;
         st.a = ce.logits; st.b = ce.labels; st.c = ce.seed; st.out = ce.loss; st.out2 = ce.grad; st.out3 = ce.argmax;
         st.m = g.values[ce.logits].shape[0]; st.n = g.values[ce.logits].shape[1];
+        st.scalar_bits = (uint64_t)ce.reduction;
         st.nodes.assign(ce.nodes.begin(), ce.nodes.end());
         emit_at[first].push_back(st);
     }

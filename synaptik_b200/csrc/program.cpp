@@ -199,8 +199,10 @@ Status check_node(const Program &g, int index, std::string &message) {
                 FAIL(UNSUPPORTED_OPERATION, name << ": needs FLOAT32 logits and INT32/INT64 targets");
             if (in(0).shape.size() != 2 || in(1).shape.size() != 1 || in(1).shape[0] != in(0).shape[0] || (int64_t)n.attrs[0] != 1)
                 FAIL(UNSUPPORTED_SHAPE, name << ": only [rows, classes] logits with class axis 1");
-            if (n.attrs[1] != 1 || n.attr_i(2) != 0) FAIL(UNSUPPORTED_OPERATION, name << ": only MEAN reduction without ignore index");
-            if (out(0).elements() != 1) FAIL(GRAPH_COMPILATION_FAILED, name << ": shape");
+            // attributes: class axis, reduction (0 NONE = one loss per row, 1 MEAN, 2 SUM), has-ignore-index, ignore index
+            if (n.attrs[1] > 2 || n.attr_i(2) != 0) FAIL(UNSUPPORTED_OPERATION, name << ": no ignore index");
+            if (n.attrs[1] == 0 ? (out(0).shape.size() != 1 || out(0).shape[0] != in(0).shape[0]) : out(0).elements() != 1)
+                FAIL(GRAPH_COMPILATION_FAILED, name << ": shape");
             return OK;
         case Op::MEAN_SQUARED_ERROR:
             if (!need(2, 1) || n.attrs.size() < 1) FAIL(GRAPH_COMPILATION_FAILED, name << ": arity");

@@ -518,11 +518,16 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
             case StepKind::SOFTMAX:
                 LAUNCH(kern::softmax_rows(s, (const float *)ptr(st.a), (float *)ptr(st.out), st.m, st.n));
                 break;
-            case StepKind::CROSS_ENTROPY:
+            case StepKind::CROSS_ENTROPY: {
+                // reduction of the forward loss node: NONE publishes the row losses themselves
+                const int reduction = (int)st.scalar_bits;
+                const bool per_row = reduction == 0 && st.out >= 0;
                 LAUNCH(kern::cross_entropy(s, (const float *)ptr(st.a), plan.views[st.b].dtype, ptr(st.b), (const float *)ptr(st.c), st.m, st.n,
-                                           se.row_loss, (float *)ptr(st.out), (float *)ptr(st.out2), (int64_t *)ptr(st.out3), ctx->error_dev));
-                if (st.out >= 0) x->launches++;
+                                           per_row ? (float *)ptr(st.out) : se.row_loss, per_row ? nullptr : (float *)ptr(st.out),
+                                           (float *)ptr(st.out2), (int64_t *)ptr(st.out3), ctx->error_dev, reduction == 2));
+                if (st.out >= 0 && !per_row) x->launches++;
                 break;
+            }
             case StepKind::MSE:
                 LAUNCH(kern::mse(s, (int)st.scalar_bits, (const float *)ptr(st.a), (const float *)ptr(st.b), st.m, (float *)ptr(st.out)));
                 break;

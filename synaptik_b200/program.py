@@ -195,9 +195,11 @@ class GraphBuilder:
     def sum_to_shape(self, x, shape): return self._node("SUM_TO_SHAPE", [x], F32, shape)
     def softmax(self, x, axis=-1): return self._node("SOFTMAX", [x], F32, x.shape, [axis % len(x.shape)])
 
-    def index_cross_entropy(self, logits: Value, labels: Value) -> Value:
-        """INDEX_CATEGORICAL_CROSS_ENTROPY_WITH_LOGITS, class axis 1, MEAN, no ignore index."""
-        return self._node("INDEX_CROSS_ENTROPY", [logits, labels], F32, (), [1, 1, 0, 0])
+    def index_cross_entropy(self, logits: Value, labels: Value, reduction: str = "mean") -> Value:
+        """INDEX_CATEGORICAL_CROSS_ENTROPY_WITH_LOGITS, class axis 1, no ignore index; reduction "mean",
+        "sum" or "none" (one loss per row)."""
+        shape = (logits.shape[0],) if reduction == "none" else ()
+        return self._node("INDEX_CROSS_ENTROPY", [logits, labels], F32, shape, [1, self.MSE_REDUCTIONS[reduction], 0, 0])
 
     MSE_REDUCTIONS = {"none": 0, "mean": 1, "sum": 2}
 

@@ -252,6 +252,30 @@ def test_cross_entropy_forward_backward(ctx, oracle, rows, classes, label_dtype)
     assert np.array_equal(mx_out[:, 0], logits.max(1))
 
 
+@pytest.mark.parametrize("rows,classes", [(300, 1000), (1024, 10)])
+def test_cross_entropy_sum_and_none_reductions(ctx, oracle, rows, classes):
+    # the same row kernel publishes the row losses themselves (NONE) or their sum (SUM,
+    # CpuLossReferenceKernel.java:196-219); the reference adds the rows in binary32 order, the device in
+    # binary64 rounded once
+    rng = np.random.default_rng(rows)
+    logits = (rng.standard_normal((rows, classes)) * 2).astype(np.float32)
+    labels = rng.integers(0, classes, rows).astype(np.int32)
+    g = GraphBuilder()
+    lv, tv = g.feed(F32, (rows, classes)), g.feed(I32, (rows,))
+    g.publish(g.index_cross_entropy(lv, tv, "none"))
+    g.publish(g.index_cross_entropy(lv, tv, "sum"))
+    g.publish(g.index_cross_entropy(lv, tv, "mean"))
+    each, total, mean = run_image(ctx, g, [logits, labels])
+    per_row, ref_mean = oracle.index_cross_entropy(logits, labels)
+    lse_scale = np.abs(per_row) + np.abs(logits[np.arange(rows), labels])        # |m + log s| is below this sum
+    assert np.all(np.abs(each - per_row) <= 4 * np.spacing(lse_scale.astype(np.float32)))
+    sequential = np.float32(0.0)
+    for value in per_row:
+        sequential = np.float32(sequential + value)
+    assert abs(float(total) - float(sequential)) <= 1e-6 * abs(float(sequential))
+    assert abs(float(mean) - float(ref_mean)) <= 1e-6 * abs(float(ref_mean))
+
+
 def test_cross_entropy_rejects_out_of_range_labels(ctx):
     g = GraphBuilder()
     lv, tv = g.feed(F32, (8, 5)), g.feed(I32, (8,))
