@@ -208,6 +208,27 @@ def softmax(x) -> np.ndarray:
     return out
 
 
+def log_softmax(x) -> np.ndarray:
+    x = _f32(x)
+    rows, classes = x.shape
+    out = np.empty_like(x)
+    lib().syn_oracle_log_softmax_f32(ctypes.c_int64(rows), ctypes.c_int64(classes), _p(x), _p(out))
+    return out
+
+
+def softmax_backward(output, upstream, log_kind: bool = False) -> np.ndarray:
+    """Gradient node list of SOFTMAX / LOG_SOFTMAX (ReductionGradientRules.java:84-90), one binary32
+    rounding per node, the row SUM exactly rounded (CpuExactSumEmitter.java:14-21)."""
+    y, g = _f32(output), _f32(upstream)
+    if log_kind:
+        total = np.array([[exact_sum(row)] for row in g], dtype=np.float32)
+        e = np.exp(y.astype(np.float64)).astype(np.float32)
+        return (g - (e * total).astype(np.float32)).astype(np.float32)
+    gy = (g * y).astype(np.float32)
+    total = np.array([[exact_sum(row)] for row in gy], dtype=np.float32)
+    return (y * (g - total).astype(np.float32)).astype(np.float32)
+
+
 def index_cross_entropy(logits, labels):
     """Returns (per_row, mean).  Raises ValueError for an out-of-range label."""
     logits = _f32(logits)
@@ -232,6 +253,94 @@ def index_cross_entropy_backward(logits, labels, seed: float = 1.0, count: int =
                                            _p(logits), _p(labels, _i64p), ctypes.c_float(seed),
                                            ctypes.c_int64(count), _p(out))
     return out
+
+
+_REDUCTIONS = {"none": 0, "mean": 1, "sum": 2}
+
+
+def index_cross_entropy_ignore(logits, labels, ignore_index: int, reduction: str = "mean"):
+    """Returns (per_row, reduced) under an ignore index; `reduced` is the mean over the rows that are
+    not ignored, or the sum.  Raises ValueError for a label out of bounds that is not ignored."""
+    logits = _f32(logits)
+    labels = np.ascontiguousarray(labels, dtype=np.int64)
+    rows, classes = logits.shape
+    per_row = np.empty(rows, dtype=np.float32)
+    reduced = ctypes.c_float(0.0)
+    status = lib().syn_oracle_index_ce_ignore_f32(ctypes.c_int64(rows), ctypes.c_int64(classes), _p(logits), _p(labels, _i64p),
+                                                  ctypes.c_int64(ignore_index), ctypes.c_int(_REDUCTIONS[reduction]),
+                                                  _p(per_row), ctypes.byref(reduced))
+    if status:
+        raise ValueError("index target out of bounds")
+    return per_row, np.float32(reduced.value)
+
+
+def dense_cross_entropy(logits, target, reduction: str = "mean"):
+    """Returns (per_row, reduced) of the dense-target categorical cross entropy with logits."""
+    logits, target = _f32(logits), _f32(target)
+    rows, classes = logits.shape
+    per_row = np.empty(rows, dtype=np.float32)
+    reduced = ctypes.c_float(0.0)
+    lib().syn_oracle_dense_ce_f32(ctypes.c_int64(rows), ctypes.c_int64(classes), _p(logits), _p(target),
+                                  ctypes.c_int(_REDUCTIONS[reduction]), _p(per_row), ctypes.byref(reduced))
+    return per_row, np.float32(reduced.value)
+
+
+def _row_sums(x) -> np.ndarray:
+    """Aggregate SUM over axis 1, kept: exactly rounded (CpuExactSumEmitter.java:14-21)."""
+    return np.array([[exact_sum(row)] for row in _f32(x)], dtype=np.float32)
+
+
+def _categorical_probabilities(logits) -> np.ndarray:
+    """exp(x - MAX) / SUM(exp(x - MAX)), one binary32 rounding per node (LossGradientRules.java:239-243);
+    finite logits only (the aggregate MAX is Math.max)."""
+    x = _f32(logits)
+    shifted = (x - x.max(axis=1, keepdims=True)).astype(np.float32)
+    e = np.exp(shifted.astype(np.float64)).astype(np.float32)
+    return (e / _row_sums(e)).astype(np.float32)
+
+
+def _restored(seed, rows: int, reduction: str, count=None) -> np.ndarray:
+    """The output cotangent on the sample domain, shape [rows, 1] (LossGradientRules.restore)."""
+    if reduction == "none":
+        return _f32(seed).reshape(rows, 1)
+    scale = np.full((rows, 1), np.float32(seed), dtype=np.float32)
+    if reduction == "mean":
+        scale = (scale / np.float32(rows if count is None else count)).astype(np.float32)
+    return scale
+
+
+def index_cross_entropy_ignore_backward(logits, labels, ignore_index: int, seed=1.0, reduction: str = "mean") -> np.ndarray:
+    """The node list of LossGradientRules.indexCategorical (:172-228) with an ignore index, node by
+    node in binary32; finite logits only."""
+    logits = _f32(logits)
+    labels = np.ascontiguousarray(labels, dtype=np.int64)
+    rows, classes = logits.shape
+    ignored = (labels == ignore_index).reshape(rows, 1)
+    active = np.float32(exact_sum(np.where(ignored, 0.0, 1.0).astype(np.float32)))
+    scale = _restored(seed, rows, "none" if reduction == "none" else "sum")
+    if reduction == "mean":
+        scale = (scale / active).astype(np.float32)
+    scale = np.where(ignored, np.float32(0.0), scale).astype(np.float32)
+    safe_logits = np.where(ignored, np.float32(0.0), logits).astype(np.float32)
+    hot = np.zeros_like(logits)
+    hot[np.arange(rows), np.clip(labels, 0, classes - 1)] = 1.0
+    raw = ((_categorical_probabilities(safe_logits) - hot).astype(np.float32) * scale).astype(np.float32)
+    return np.where(ignored, np.float32(0.0), raw).astype(np.float32)
+
+
+def dense_cross_entropy_backward(logits, target, seed=1.0, reduction: str = "mean") -> np.ndarray:
+    """The logits cotangent of LossGradientRules.denseCategorical (:114-145), node by node in binary32;
+    finite logits only."""
+    logits, target = _f32(logits), _f32(target)
+    rows, _ = logits.shape
+    restored = _restored(seed, rows, reduction)
+    membership = _row_sums(np.where(target == 0.0, 0.0, 1.0).astype(np.float32))
+    empty = membership == 0.0
+    p = _categorical_probabilities(np.where(empty, np.float32(0.0), logits).astype(np.float32))
+    mass = _row_sums(target)
+    scale = np.where(empty, np.float32(0.0), restored).astype(np.float32)
+    raw = (((p * mass).astype(np.float32) - target).astype(np.float32) * scale).astype(np.float32)
+    return np.where(empty, np.float32(0.0), raw).astype(np.float32)
 
 
 def mse(prediction, target) -> np.float32:

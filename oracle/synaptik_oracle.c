@@ -184,7 +184,7 @@ SYN_EXPORT void syn_oracle_colsum_exact_f32(int64_t m, int64_t n, const float *g
 }
 
 /* ------------------------------------------------------------------------------------------ */
-/* SOFTMAX: CpuSoftmaxReferenceKernel.java:104-146 (evaluateFloat, SoftmaxKind.SOFTMAX).        */
+/* SOFTMAX and LOG_SOFTMAX: CpuSoftmaxReferenceKernel.java:104-146 (evaluateFloat).             */
 /* ------------------------------------------------------------------------------------------ */
 static inline float java_max_f32(float a, float b) {   /* Math.max: NaN wins, +0 > -0 */
     if (a != a) return a;
@@ -193,7 +193,9 @@ static inline float java_max_f32(float a, float b) {   /* Math.max: NaN wins, +0
     return a > b ? a : b;
 }
 
-SYN_EXPORT void syn_oracle_softmax_f32(int64_t rows, int64_t classes, const float *x, float *out) {
+/* log_kind 0: SOFTMAX, exp(x - max) / sum.  log_kind 1: LOG_SOFTMAX, (x - max) - (float)log(sum),
+ * -inf beside a +inf (:114-123), never the logarithm of the rounded softmax. */
+static void softmax_rows_f32(int log_kind, int64_t rows, int64_t classes, const float *x, float *out) {
     for (int64_t r = 0; r < rows; r++) {
         const float *v = x + r * classes; float *o = out + r * classes;
         float maximum = -INFINITY; int unshifted = 0;
@@ -202,7 +204,7 @@ SYN_EXPORT void syn_oracle_softmax_f32(int64_t rows, int64_t classes, const floa
             unshifted |= v[c] == -INFINITY;
         }
         if (maximum == INFINITY) {
-            for (int64_t c = 0; c < classes; c++) o[c] = v[c] == INFINITY ? NAN : 0.0f;
+            for (int64_t c = 0; c < classes; c++) o[c] = v[c] == INFINITY ? NAN : log_kind ? -INFINITY : 0.0f;
             continue;
         }
         if (unshifted && !(maximum != maximum)) maximum = 0.0f;
@@ -217,11 +219,20 @@ SYN_EXPORT void syn_oracle_softmax_f32(int64_t rows, int64_t classes, const floa
                 sum = temporary;
             }
         }
+        float logarithm = log_kind ? (float)log((double)sum) : 0.0f;
         for (int64_t c = 0; c < classes; c++) {
             float shifted = v[c] - maximum;
-            o[c] = (float)exp((double)shifted) / sum;
+            o[c] = log_kind ? shifted - logarithm : (float)exp((double)shifted) / sum;
         }
     }
+}
+
+SYN_EXPORT void syn_oracle_softmax_f32(int64_t rows, int64_t classes, const float *x, float *out) {
+    softmax_rows_f32(0, rows, classes, x, out);
+}
+
+SYN_EXPORT void syn_oracle_log_softmax_f32(int64_t rows, int64_t classes, const float *x, float *out) {
+    softmax_rows_f32(1, rows, classes, x, out);
 }
 
 /* ------------------------------------------------------------------------------------------ */
@@ -254,6 +265,47 @@ SYN_EXPORT int syn_oracle_index_ce_f32(int64_t rows, int64_t classes, const floa
     }
     if (mean_out) *mean_out = sum / (float)rows;
     return 0;
+}
+
+/* The same with an ignore index (CpuLossReferenceKernel.java:196-218,261-265): a row whose label
+ * equals `ignore` is tested before the bounds and before its logits are read; NONE gives it 0,
+ * SUM and MEAN skip it, and MEAN divides by the number of rows that are left (0 / 0 = NaN when none
+ * is).  reduction: 0 NONE (per_row only), 1 MEAN, 2 SUM.  Returns 1 for a label out of bounds. */
+SYN_EXPORT int syn_oracle_index_ce_ignore_f32(int64_t rows, int64_t classes, const float *logits,
+        const int64_t *labels, int64_t ignore, int reduction, float *per_row, float *reduced_out) {
+    for (int64_t r = 0; r < rows; r++) if (labels[r] != ignore && (labels[r] < 0 || labels[r] >= classes)) return 1;
+    float sum = 0.0f;
+    int64_t count = 0;
+    for (int64_t r = 0; r < rows; r++) {
+        const float *v = logits + r * classes;
+        if (labels[r] == ignore) { if (per_row) per_row[r] = 0.0f; continue; }
+        float loss = log_sum_exp_f32(v, classes) - v[labels[r]];
+        if (per_row) per_row[r] = loss;
+        sum += loss;
+        count++;
+    }
+    if (reduced_out) *reduced_out = reduction == 1 ? sum / (float)count : sum;
+    return 0;
+}
+
+/* Dense-target categorical cross entropy with logits, forward (CpuLossReferenceKernel.java:129-143,
+ * denseSlice :251-259): per row lse = logSumExp, loss = ascending binary32 sum over the classes with a
+ * non-zero weight of weight * (lse - logit); MEAN = sum / samples in binary32. */
+SYN_EXPORT void syn_oracle_dense_ce_f32(int64_t rows, int64_t classes, const float *logits,
+        const float *target, int reduction, float *per_row, float *reduced_out) {
+    float sum = 0.0f;
+    for (int64_t r = 0; r < rows; r++) {
+        const float *v = logits + r * classes, *w = target + r * classes;
+        float lse = log_sum_exp_f32(v, classes);
+        float loss = 0.0f;
+        for (int64_t c = 0; c < classes; c++) {
+            float weight = w[c];
+            if (weight != 0.0f) { float term = weight * (lse - v[c]); loss += term; }
+        }
+        if (per_row) per_row[r] = loss;
+        sum += loss;
+    }
+    if (reduced_out) *reduced_out = reduction == 1 ? sum / (float)rows : sum;
 }
 
 /* ------------------------------------------------------------------------------------------ */

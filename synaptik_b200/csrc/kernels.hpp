@@ -19,6 +19,8 @@ struct Index4 {                 // right-aligned rank-4 iteration space with per
 
 // ---- generic node-by-node kernels (one binary32 rounding per operation) -----------------------
 cudaError_t binary(cudaStream_t s, Op op, const float *a, const float *b, void *out, const Index4 &ix, int64_t total);
+// SUB (wrapping) and EQ on INT32 / INT64 operands
+cudaError_t binary_int(cudaStream_t s, Op op, DType dtype, const void *a, const void *b, void *out, const Index4 &ix, int64_t total);
 cudaError_t scalar_op(cudaStream_t s, Op op, DType dtype, const void *a, void *out, uint64_t scalar_bits, int64_t total);
 cudaError_t unary(cudaStream_t s, Op op, const float *a, void *out, int64_t total);      // IS_INF writes BOOL bytes
 cudaError_t where(cudaStream_t s, const uint8_t *cond, const float *a, const float *b, float *out, const Index4 &ix, int64_t total);
@@ -27,7 +29,7 @@ cudaError_t copy_strided(cudaStream_t s, int element_bytes, const void *src, voi
 cudaError_t row_reduce(cudaStream_t s, Op op, const float *x, float *out, int64_t rows, int64_t cols);
 cudaError_t full_sum(cudaStream_t s, const float *x, const Index4 &ix, int64_t total, float *out);
 cudaError_t argmax_rows(cudaStream_t s, const float *x, int64_t *out, int64_t rows, int64_t cols);
-cudaError_t softmax_rows(cudaStream_t s, const float *x, float *out, int64_t rows, int64_t cols);
+cudaError_t softmax_rows(cudaStream_t s, const float *x, float *out, int64_t rows, int64_t cols, bool log_kind);
 // Squared error (CpuLossReferenceKernel.java:67-87): reduction 0 = per-element (p - t)^2 into out[count],
 // 1 = mean, 2 = sum into out[0]; up to 65536 elements the sum is the reference's sequential binary32 one.
 cudaError_t mse(cudaStream_t s, int reduction, const float *p, const float *t, int64_t count, float *out);
@@ -57,7 +59,16 @@ cudaError_t colsum_static(cudaStream_t s, int device, const float *g, int64_t ro
 // reduction NONE the caller passes its result as row_loss and no loss_out.
 cudaError_t cross_entropy(cudaStream_t s, const float *logits, DType label_type, const void *labels,
                           const float *seed, int64_t rows, int64_t cols, float *row_loss, float *loss_out,
-                          float *grad_out, int64_t *argmax_out, int *error_word, int sum_only = 0);
+                          float *grad_out, int64_t *argmax_out, int *error_word, int sum_only = 0,
+                          int has_ignore = 0, int64_t ignore = 0);
+// has_ignore: rows whose label equals `ignore` give zero loss and zero gradient, are exempt from the
+// label range check and are left out of the MEAN's count (CpuLossReferenceKernel.java:196-218).
+
+// Dense-target categorical cross entropy with logits, forward (CpuLossReferenceKernel.java:129-143):
+// row_loss[r] = sum over classes with a non-zero weight of weight * (logsumexp(row) - logit); loss_out
+// (when given) their mean, or their sum with sum_only.
+cudaError_t dense_cross_entropy(cudaStream_t s, const float *logits, const float *target, int64_t rows, int64_t cols,
+                                float *row_loss, float *loss_out, int sum_only);
 
 // ---- optimizers -----------------------------------------------------------------------------
 // acc: pending gradient sum of the tensor (TrainingParameter.java:373-390), used per `gradient_mode`:

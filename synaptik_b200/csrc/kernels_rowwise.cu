@@ -115,6 +115,10 @@ __device__ __forceinline__ void unravel(int64_t i, const Index4 &ix, int64_t &oa
     oc = i0 * ix.sc[0] + i1 * ix.sc[1] + i2 * ix.sc[2] + i3 * ix.sc[3];
 }
 
+template <typename T> struct UnsignedOf;
+template <> struct UnsignedOf<int32_t> { typedef uint32_t type; };
+template <> struct UnsignedOf<int64_t> { typedef uint64_t type; };
+
 __global__ void binary_kernel(int op, const float *__restrict__ a, const float *__restrict__ b, void *out, Index4 ix, int64_t total) {
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         int64_t oa, ob, oc;
@@ -132,6 +136,20 @@ __global__ void binary_kernel(int op, const float *__restrict__ a, const float *
     }
 }
 
+// Integer operands: SUB wraps like Java's int / long arithmetic, EQ compares exactly.  The index
+// cross-entropy gradient rule tests labels against the ignore index with these
+// (LossGradientRules.java:203-207).
+template <typename T>
+__global__ void binary_int_kernel(int op, const T *__restrict__ a, const T *__restrict__ b, void *out, Index4 ix, int64_t total) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t oa, ob, oc;
+        unravel(i, ix, oa, ob, oc);
+        T x = a[oa], y = b[ob];
+        if ((Op)op == Op::SUB) ((T *)out)[i] = (T)((typename UnsignedOf<T>::type)x - (typename UnsignedOf<T>::type)y);
+        else ((uint8_t *)out)[i] = x == y ? 1 : 0;
+    }
+}
+
 __global__ void where_kernel(const uint8_t *__restrict__ cond, const float *__restrict__ a, const float *__restrict__ b,
                              float *out, Index4 ix, int64_t total) {
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -146,6 +164,7 @@ __global__ void scalar_kernel(int op, const T *__restrict__ a, T *out, T scalar,
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         T x = a[i];
         if ((Op)op == Op::SCALAR_MIN) out[i] = x < scalar ? x : scalar;
+        else if ((Op)op == Op::SCALAR_SUB) out[i] = (T)((typename UnsignedOf<T>::type)x - (typename UnsignedOf<T>::type)scalar);   // wraps like Java
         else out[i] = x > scalar ? x : scalar;
     }
 }
@@ -153,6 +172,7 @@ __global__ void scalar_f32_kernel(int op, const float *__restrict__ a, float *ou
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         float x = a[i];
         if ((Op)op == Op::SCALAR_MUL) out[i] = __fmul_rn(x, scalar);
+        else if ((Op)op == Op::SCALAR_SUB) out[i] = __fsub_rn(x, scalar);
         else if ((Op)op == Op::SCALAR_MIN) out[i] = java_min(x, scalar);
         else out[i] = java_max(x, scalar);
     }
@@ -365,10 +385,13 @@ __global__ void __launch_bounds__(kThreads) argmax_kernel(const float *__restric
     }
 }
 
-// SOFTMAX rows, CpuSoftmaxReferenceKernel.java:104-146: Math.max maximum; any +inf -> NaN at the
-// infinities and 0 elsewhere; any -inf (without NaN) -> unshifted exponentials; otherwise
-// exp(x - max) / sum.  The reference's Kahan-compensated binary32 sum is replaced by a binary64
-// sum rounded once (both lie within an ulp of the exact sum).
+// SOFTMAX / LOG_SOFTMAX rows, CpuSoftmaxReferenceKernel.java:104-146: Math.max maximum; any +inf ->
+// NaN at the infinities and 0 (LOG_SOFTMAX: -inf) elsewhere; any -inf (without NaN) -> unshifted
+// exponentials; otherwise exp(x - max) / sum, or (x - max) - (float)log(sum) for LOG_SOFTMAX (the
+// logarithm of the sum, never of the rounded quotient, so a far-away column keeps its finite
+// distance).  The reference's Kahan-compensated binary32 sum is replaced by a binary64 sum
+// rounded once (both lie within an ulp of the exact sum).
+template <bool LOG>
 __global__ void softmax_kernel(const float *__restrict__ x, float *out, int64_t rows, int64_t cols) {
     int lane = threadIdx.x & 31;
     int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
@@ -381,14 +404,20 @@ __global__ void softmax_kernel(const float *__restrict__ x, float *out, int64_t 
         maximum = warp_max_java(maximum);
         has_ninf = __any_sync(0xffffffffu, has_ninf);
         if (maximum == __int_as_float(0x7f800000)) {
-            for (int64_t c = lane; c < cols; c += 32) o[c] = row[c] == maximum ? __int_as_float(0x7fc00000) : 0.0f;
+            const float rest = LOG ? __int_as_float(0xff800000) : 0.0f;
+            for (int64_t c = lane; c < cols; c += 32) o[c] = row[c] == maximum ? __int_as_float(0x7fc00000) : rest;
             continue;
         }
         if (has_ninf && !(maximum != maximum)) maximum = 0.0f;
         double acc = 0.0;
         for (int64_t c = lane; c < cols; c += 32) acc += (double)exp_accurate(__fsub_rn(row[c], maximum));
         float sum = (float)warp_sum(acc);
-        for (int64_t c = lane; c < cols; c += 32) o[c] = __fdiv_rn(exp_accurate(__fsub_rn(row[c], maximum)), sum);
+        if (LOG) {
+            const float logarithm = (float)log((double)sum);
+            for (int64_t c = lane; c < cols; c += 32) o[c] = __fsub_rn(__fsub_rn(row[c], maximum), logarithm);
+        } else {
+            for (int64_t c = lane; c < cols; c += 32) o[c] = __fdiv_rn(exp_accurate(__fsub_rn(row[c], maximum)), sum);
+        }
     }
 }
 
@@ -560,7 +589,8 @@ __device__ __noinline__ void ce_row_careful(const float *__restrict__ row, int64
 
 template <int CHUNKS, typename L, bool GRAD, bool ARGMAX>
 __global__ void __launch_bounds__(kThreads, CHUNKS >= 8 ? 3 : 4) ce_rows_vec_kernel(const float *__restrict__ logits, const void *__restrict__ labels,
-        const float *__restrict__ seed, int64_t rows, int cols, float *row_loss, float *grad, int64_t *argmax_out, int *error_word) {
+        const float *__restrict__ seed, int64_t rows, int cols, float *row_loss, float *grad, int64_t *argmax_out, int *error_word,
+        int has_ignore, long long ignore) {
     int lane = threadIdx.x & 31;
     int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     const int vec_cols = cols >> 2;
@@ -572,6 +602,14 @@ __global__ void __launch_bounds__(kThreads, CHUNKS >= 8 ? 3 : 4) ce_rows_vec_ker
 #pragma unroll
         for (int j = 0; j < CHUNKS; j++) v[j] = lane + 32 * j < vec_cols ? row[lane + 32 * j] : make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
         int64_t label = load_label<L>(labels, r);
+        if (has_ignore && label == ignore) {
+            // the ignore index is tested before the bounds and before the logits are read
+            // (CpuLossReferenceKernel.java:261-265): zero loss, zero gradient
+            if (lane == 0 && row_loss) row_loss[r] = 0.0f;
+            if (GRAD) for (int c = lane; c < cols; c += 32) grad[r * cols + c] = 0.0f;
+            if (ARGMAX) ce_row_careful(row_s, cols, 0, 0.0f, nullptr, nullptr, argmax_out + r, lane);
+            continue;
+        }
         if ((label < 0 || label >= cols) && lane == 0) atomicOr(error_word, ERR_LABEL_RANGE);
         const int safe = (int)(label < 0 ? 0 : (label >= cols ? cols - 1 : label));
         // maximum (fmaxf skips NaN like the reference's plain '>' scan) and a probe that turns NaN
@@ -646,12 +684,19 @@ __global__ void __launch_bounds__(kThreads, CHUNKS >= 8 ? 3 : 4) ce_rows_vec_ker
 // 10-class head) and rows that are not 16-byte aligned.
 template <typename L>
 __global__ void ce_rows_generic_kernel(const float *__restrict__ logits, const void *__restrict__ labels, const float *__restrict__ seed,
-        int64_t rows, int64_t cols, float *row_loss, float *grad, int64_t *argmax_out, int *error_word) {
+        int64_t rows, int64_t cols, float *row_loss, float *grad, int64_t *argmax_out, int *error_word,
+        int has_ignore, long long ignore) {
     int lane = threadIdx.x & 31;
     int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     float scale = grad ? __fdiv_rn(seed ? seed[0] : 1.0f, (float)rows) : 0.0f;
     for (int64_t r = warp; r < rows; r += warps) {
         int64_t label = load_label<L>(labels, r);
+        if (has_ignore && label == ignore) {
+            if (lane == 0 && row_loss) row_loss[r] = 0.0f;
+            if (grad) for (int64_t c = lane; c < cols; c += 32) grad[r * cols + c] = 0.0f;
+            if (argmax_out) ce_row_careful(logits + r * cols, cols, 0, 0.0f, nullptr, nullptr, argmax_out + r, lane);
+            continue;
+        }
         if ((label < 0 || label >= cols) && lane == 0) atomicOr(error_word, ERR_LABEL_RANGE);
         int64_t safe = label < 0 ? 0 : (label >= cols ? cols - 1 : label);
         ce_row_careful(logits + r * cols, cols, safe, scale, row_loss ? row_loss + r : nullptr, grad ? grad + r * cols : nullptr,
@@ -672,6 +717,61 @@ __global__ void mean_kernel(const float *__restrict__ values, int64_t count, flo
         double v = threadIdx.x < (blockDim.x >> 5) ? partial[threadIdx.x] : 0.0;
         v = warp_sum(v);
         if (threadIdx.x == 0) out[0] = divide ? __fdiv_rn((float)v, (float)count) : (float)v;
+    }
+}
+
+// Reduction of the row losses under an ignore index (CpuLossReferenceKernel.java:208-218): ignored
+// rows add nothing and are not counted; MEAN divides by the number of rows that are left (0 / 0 is
+// NaN when every row is ignored, as there).
+template <typename L>
+__global__ void mean_active_kernel(const float *__restrict__ values, const void *__restrict__ labels, long long ignore, int64_t count,
+                                   float *out, int divide) {
+    __shared__ double partial[32];
+    __shared__ long long active_partial[32];
+    double acc = 0.0;
+    long long active = 0;
+    for (int64_t i = threadIdx.x; i < count; i += blockDim.x)
+        if (load_label<L>(labels, i) != ignore) { acc += (double)values[i]; active++; }
+    acc = warp_sum(acc);
+    for (int o = 16; o > 0; o >>= 1) active += __shfl_xor_sync(0xffffffffu, active, o);
+    if ((threadIdx.x & 31) == 0) { partial[threadIdx.x >> 5] = acc; active_partial[threadIdx.x >> 5] = active; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        double v = threadIdx.x < (blockDim.x >> 5) ? partial[threadIdx.x] : 0.0;
+        long long n = threadIdx.x < (blockDim.x >> 5) ? active_partial[threadIdx.x] : 0;
+        v = warp_sum(v);
+        for (int o = 16; o > 0; o >>= 1) n += __shfl_xor_sync(0xffffffffu, n, o);
+        if (threadIdx.x == 0) out[0] = divide ? __fdiv_rn((float)v, (float)n) : (float)v;
+    }
+}
+
+// ---- dense-target categorical cross entropy with logits, forward --------------------------------
+// Per row (CpuLossReferenceKernel.java:129-143,251-259,276-288): lse = m + (float)log(sum exp(x - m))
+// with the plain '>' maximum, then the sum over the classes whose target weight is not zero of
+// weight * (lse - x), each term rounded to binary32.  The reference adds the exponentials and the
+// terms in ascending binary32 order; here lanes add in binary64 and round once, which lies inside
+// the reference's own rounding error of those sums.  One warp per row, the row read twice (the
+// second pass hits L1 / L2).
+__global__ void dense_ce_rows_kernel(const float *__restrict__ logits, const float *__restrict__ target, int64_t rows, int64_t cols,
+                                     float *row_loss) {
+    int lane = threadIdx.x & 31;
+    int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t r = warp; r < rows; r += warps) {
+        const float *row = logits + r * cols, *weight = target + r * cols;
+        float mplain = __int_as_float(0xff800000);
+        for (int64_t c = lane; c < cols; c += 32) { float x = row[c]; mplain = x > mplain ? x : mplain; }
+        mplain = warp_max_plain(mplain);
+        double acc = 0.0;
+        for (int64_t c = lane; c < cols; c += 32) acc += (double)exp_accurate(__fsub_rn(row[c], mplain));
+        const float sum = (float)warp_sum(acc);
+        const float lse = __fadd_rn(mplain, (float)log((double)sum));
+        double loss = 0.0;
+        for (int64_t c = lane; c < cols; c += 32) {
+            const float w = weight[c];
+            if (w != 0.0f) loss += (double)__fmul_rn(w, __fsub_rn(lse, row[c]));
+        }
+        loss = warp_sum(loss);
+        if (lane == 0) row_loss[r] = (float)loss;
     }
 }
 
@@ -787,6 +887,15 @@ cudaError_t binary(cudaStream_t s, Op op, const float *a, const float *b, void *
     return cudaGetLastError();
 }
 
+cudaError_t binary_int(cudaStream_t s, Op op, DType dtype, const void *a, const void *b, void *out, const Index4 &ix, int64_t total) {
+    if (total == 0) return cudaSuccess;
+    if (op != Op::SUB && op != Op::EQ) return cudaErrorInvalidValue;
+    if (dtype == DType::I32) binary_int_kernel<int32_t><<<grid_for(total, kThreads), kThreads, 0, s>>>((int)op, (const int32_t *)a, (const int32_t *)b, out, ix, total);
+    else if (dtype == DType::I64) binary_int_kernel<int64_t><<<grid_for(total, kThreads), kThreads, 0, s>>>((int)op, (const int64_t *)a, (const int64_t *)b, out, ix, total);
+    else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
 cudaError_t where(cudaStream_t s, const uint8_t *cond, const float *a, const float *b, float *out, const Index4 &ix, int64_t total) {
     if (total == 0) return cudaSuccess;
     where_kernel<<<grid_for(total, kThreads), kThreads, 0, s>>>(cond, a, b, out, ix, total);
@@ -854,9 +963,10 @@ cudaError_t argmax_rows(cudaStream_t s, const float *x, int64_t *out, int64_t ro
     return cudaGetLastError();
 }
 
-cudaError_t softmax_rows(cudaStream_t s, const float *x, float *out, int64_t rows, int64_t cols) {
+cudaError_t softmax_rows(cudaStream_t s, const float *x, float *out, int64_t rows, int64_t cols, bool log_kind) {
     if (rows == 0) return cudaSuccess;
-    softmax_kernel<<<grid_for(rows, kThreads / 32), kThreads, 0, s>>>(x, out, rows, cols);
+    if (log_kind) softmax_kernel<true><<<grid_for(rows, kThreads / 32), kThreads, 0, s>>>(x, out, rows, cols);
+    else softmax_kernel<false><<<grid_for(rows, kThreads / 32), kThreads, 0, s>>>(x, out, rows, cols);
     return cudaGetLastError();
 }
 
@@ -933,12 +1043,12 @@ cudaError_t colsum_static(cudaStream_t s, int device, const float *g, int64_t ro
 
 cudaError_t cross_entropy(cudaStream_t s, const float *logits, DType label_type, const void *labels, const float *seed,
                           int64_t rows, int64_t cols, float *row_loss, float *loss_out, float *grad_out, int64_t *argmax_out, int *error_word,
-                          int sum_only) {
+                          int sum_only, int has_ignore, int64_t ignore) {
     if (rows == 0 || cols == 0) return cudaErrorInvalidValue;
     int grid = grid_for(rows, kThreads / 32);
     bool vec = (cols & 3) == 0 && cols >= 128 && cols <= 1024 && (((uintptr_t)logits | (uintptr_t)grad_out) & 15) == 0;
     bool i32 = label_type == DType::I32;
-#define SYN_CE_ARGS <<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, (int)cols, row_loss, grad_out, argmax_out, error_word)
+#define SYN_CE_ARGS <<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, (int)cols, row_loss, grad_out, argmax_out, error_word, has_ignore, (long long)ignore)
 #define SYN_CE_VEC2(C, L) do { if (grad_out && argmax_out) ce_rows_vec_kernel<C, L, true, true> SYN_CE_ARGS; \
                                else if (grad_out) ce_rows_vec_kernel<C, L, true, false> SYN_CE_ARGS; \
                                else if (argmax_out) ce_rows_vec_kernel<C, L, false, true> SYN_CE_ARGS; \
@@ -947,11 +1057,23 @@ cudaError_t cross_entropy(cudaStream_t s, const float *logits, DType label_type,
     if (vec) {
         int chunks = (int)((cols / 4 + 31) / 32);
         if (chunks <= 1) SYN_CE_VEC(1); else if (chunks <= 2) SYN_CE_VEC(2); else if (chunks <= 4) SYN_CE_VEC(4); else SYN_CE_VEC(8);
-    } else if (i32) ce_rows_generic_kernel<int32_t><<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, cols, row_loss, grad_out, argmax_out, error_word);
-    else ce_rows_generic_kernel<int64_t><<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, cols, row_loss, grad_out, argmax_out, error_word);
+    } else if (i32) ce_rows_generic_kernel<int32_t><<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, cols, row_loss, grad_out, argmax_out, error_word, has_ignore, (long long)ignore);
+    else ce_rows_generic_kernel<int64_t><<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, cols, row_loss, grad_out, argmax_out, error_word, has_ignore, (long long)ignore);
 #undef SYN_CE_VEC
 #undef SYN_CE_VEC2
 #undef SYN_CE_ARGS
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess || !loss_out) return e;
+    if (!has_ignore) mean_kernel<<<1, 1024, 0, s>>>(row_loss, rows, loss_out, !sum_only);
+    else if (i32) mean_active_kernel<int32_t><<<1, 1024, 0, s>>>(row_loss, labels, (long long)ignore, rows, loss_out, !sum_only);
+    else mean_active_kernel<int64_t><<<1, 1024, 0, s>>>(row_loss, labels, (long long)ignore, rows, loss_out, !sum_only);
+    return cudaGetLastError();
+}
+
+cudaError_t dense_cross_entropy(cudaStream_t s, const float *logits, const float *target, int64_t rows, int64_t cols,
+                                float *row_loss, float *loss_out, int sum_only) {
+    if (rows == 0 || cols == 0) return cudaErrorInvalidValue;
+    dense_ce_rows_kernel<<<grid_for(rows, kThreads / 32), kThreads, 0, s>>>(logits, target, rows, cols, row_loss);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess || !loss_out) return e;
     mean_kernel<<<1, 1024, 0, s>>>(row_loss, rows, loss_out, !sum_only);

@@ -42,7 +42,7 @@ const char *step_name(StepKind k) {
         case StepKind::GEMM: return "gemm"; case StepKind::BINARY: return "binary"; case StepKind::SCALAR: return "scalar";
         case StepKind::UNARY: return "unary"; case StepKind::WHERE: return "where"; case StepKind::ONE_HOT: return "one_hot";
         case StepKind::COPY: return "copy"; case StepKind::ROW_REDUCE: return "row_reduce"; case StepKind::FULL_SUM: return "full_sum";
-        case StepKind::COLSUM: return "colsum"; case StepKind::SOFTMAX: return "softmax"; case StepKind::CROSS_ENTROPY: return "cross_entropy";
+        case StepKind::COLSUM: return "colsum"; case StepKind::SOFTMAX: return "softmax"; case StepKind::CROSS_ENTROPY: return "cross_entropy"; case StepKind::DENSE_CROSS_ENTROPY: return "dense_cross_entropy";
         case StepKind::MSE: return "mse"; case StepKind::ARG_MAX: return "arg_max"; case StepKind::RELU_BACKWARD: return "relu_backward";
     }
     return "?";
@@ -107,6 +107,8 @@ struct LinearGroup {          // MATMUL [-> ADD bias] [-> RELU] [-> gate by WHER
 struct CrossEntropyGroup {
     int logits = -1, labels = -1, seed = -1, loss = -1, grad = -1, argmax = -1;
     int reduction = 1;                      // of the forward loss node: 0 NONE, 1 MEAN, 2 SUM
+    bool has_ignore = false;                // of the forward loss node
+    int64_t ignore = 0;
     std::set<int> nodes;
     int emit_at = -1;
 };
@@ -327,10 +329,13 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
         const Node &n = g.nodes[i];
         if (n.op != Op::INDEX_CROSS_ENTROPY || covered[i]) continue;
         CrossEntropyGroup *host = nullptr;
-        for (auto &ce : ces) if (ce.loss < 0 && ce.logits == n.inputs[0] && ce.labels == n.inputs[1]) { host = &ce; break; }
+        // the fused gradient is the chain without an ignore index; a loss node that has one runs alone
+        if (n.attr_i(2) == 0)
+            for (auto &ce : ces) if (ce.loss < 0 && ce.logits == n.inputs[0] && ce.labels == n.inputs[1]) { host = &ce; break; }
         if (!host) { ces.emplace_back(); host = &ces.back(); host->logits = n.inputs[0]; host->labels = n.inputs[1]; }
         host->loss = n.outputs[0];
         host->reduction = (int)n.attrs[1];
+        host->has_ignore = n.attr_i(2) != 0; host->ignore = n.attr_i(3);
         host->nodes.insert(i);
         covered[i] = 1;
     }
@@ -357,6 +362,7 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
         st.a = ce.logits; st.b = ce.labels; st.c = ce.seed; st.out = ce.loss; st.out2 = ce.grad; st.out3 = ce.argmax;
         st.m = g.values[ce.logits].shape[0]; st.n = g.values[ce.logits].shape[1];
         st.scalar_bits = (uint64_t)ce.reduction;
+        st.has_ignore = ce.has_ignore; st.ignore = ce.ignore;
         st.nodes.assign(ce.nodes.begin(), ce.nodes.end());
         emit_at[first].push_back(st);
     }
@@ -510,7 +516,7 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
                 st.kind = StepKind::BINARY; st.a = n.inputs[0]; st.b = n.inputs[1]; st.out = out0;
                 finish_step(st);
                 break;
-            case Op::SCALAR_MUL: case Op::SCALAR_MIN: case Op::SCALAR_MAX:
+            case Op::SCALAR_MUL: case Op::SCALAR_MIN: case Op::SCALAR_MAX: case Op::SCALAR_SUB:
                 assign_output(out0);
                 st.kind = StepKind::SCALAR; st.a = in0; st.out = out0; st.scalar_bits = n.attrs[0];
                 finish_step(st);
@@ -566,9 +572,18 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
                 assign_output(out0);
                 st.kind = StepKind::SOFTMAX; st.a = in0; st.out = out0;
                 st.n = g.values[in0].shape.back(); st.m = g.values[in0].elements() / std::max<int64_t>(st.n, 1);
+                st.scalar_bits = n.attr_i(1);           // kind: 0 SOFTMAX, 1 LOG_SOFTMAX
                 finish_step(st);
                 break;
             case Op::INDEX_CROSS_ENTROPY: message = "internal: loss not grouped"; return INTERNAL_ERROR;
+            case Op::DENSE_CROSS_ENTROPY:
+                if (dense_input(n.inputs[0]) < 0 || dense_input(n.inputs[1]) < 0) return UNSUPPORTED_SHAPE;
+                assign_output(out0);
+                st.kind = StepKind::DENSE_CROSS_ENTROPY; st.a = n.inputs[0]; st.b = n.inputs[1]; st.out = out0;
+                st.m = g.values[n.inputs[0]].shape[0]; st.n = g.values[n.inputs[0]].shape[1];
+                st.scalar_bits = n.attrs[1];            // reduction: 0 NONE, 1 MEAN, 2 SUM
+                finish_step(st);
+                break;
             case Op::MEAN_SQUARED_ERROR:
                 if (dense_input(n.inputs[0]) < 0 || dense_input(n.inputs[1]) < 0) return UNSUPPORTED_SHAPE;
                 assign_output(out0);

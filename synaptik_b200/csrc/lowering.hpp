@@ -39,7 +39,7 @@ struct View {
 
 enum class StepKind : int {
     GEMM, BINARY, SCALAR, UNARY, WHERE, ONE_HOT, COPY, ROW_REDUCE, FULL_SUM, COLSUM, SOFTMAX,
-    CROSS_ENTROPY, MSE, ARG_MAX, RELU_BACKWARD
+    CROSS_ENTROPY, MSE, ARG_MAX, RELU_BACKWARD, DENSE_CROSS_ENTROPY
 };
 const char *step_name(StepKind k);
 
@@ -54,7 +54,9 @@ struct Step {
     int bias = -1, mask = -1;       // GEMM epilogue operands
     bool relu = false;
     int64_t m = 0, n = 0, k = 0;    // GEMM extents, or rows / cols of row kernels
-    uint64_t scalar_bits = 0;       // SCALAR operand, ONE_HOT depth
+    uint64_t scalar_bits = 0;       // SCALAR operand, ONE_HOT depth, loss reduction
+    bool has_ignore = false;        // CROSS_ENTROPY: rows labelled `ignore` are skipped
+    int64_t ignore = 0;
     GemmEngine engine = GemmEngine::EXACT_SIMT;
     int publication_ready = -1;     // >= 0: this step completes that publication (for comm overlap)
     std::vector<int> ready_publications;

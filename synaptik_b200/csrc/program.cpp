@@ -21,6 +21,8 @@ const char *op_name(Op op) {
         case Op::TANH: return "TANH"; case Op::SIGMOID: return "SIGMOID"; case Op::SILU: return "SILU";
         case Op::IS_INF: return "IS_INF"; case Op::GELU_TANH: return "GELU_TANH_APPROXIMATION";
         case Op::CLAMP: return "CLAMP"; case Op::LT: return "LT"; case Op::EQ: return "EQ";
+        case Op::SCALAR_SUB: return "SCALAR_SUB";
+        case Op::DENSE_CROSS_ENTROPY: return "DENSE_CATEGORICAL_CROSS_ENTROPY_WITH_LOGITS";
     }
     return "?";
 }
@@ -107,12 +109,15 @@ Status check_node(const Program &g, int index, std::string &message) {
             return OK;
         case Op::ADD: case Op::SUB: case Op::MUL: case Op::DIV: case Op::GT: case Op::LT: case Op::EQ:
             if (!need(2, 1)) FAIL(GRAPH_COMPILATION_FAILED, name << ": arity");
-            if (in(0).dtype != DType::F32 || in(1).dtype != DType::F32) FAIL(UNSUPPORTED_OPERATION, name << ": only FLOAT32 operands");
-            if (out(0).dtype != ((n.op == Op::GT || n.op == Op::LT || n.op == Op::EQ) ? DType::BOOL : DType::F32)) FAIL(GRAPH_COMPILATION_FAILED, name << ": result dtype");
+            if (in(0).dtype != in(1).dtype) FAIL(GRAPH_COMPILATION_FAILED, name << ": operand dtypes differ");
+            // integer operands (labels against an ignore index) only for SUB and EQ
+            if (in(0).dtype != DType::F32 && !((in(0).dtype == DType::I32 || in(0).dtype == DType::I64) && (n.op == Op::SUB || n.op == Op::EQ)))
+                FAIL(UNSUPPORTED_OPERATION, name << ": only FLOAT32 operands (SUB and EQ also INT32 / INT64)");
+            if (out(0).dtype != ((n.op == Op::GT || n.op == Op::LT || n.op == Op::EQ) ? DType::BOOL : in(0).dtype)) FAIL(GRAPH_COMPILATION_FAILED, name << ": result dtype");
             if (!broadcastable(in(0).shape, in(1).shape, shape) || shape != out(0).shape) FAIL(GRAPH_COMPILATION_FAILED, name << ": broadcast shape");
             if (shape.size() > 4) FAIL(UNSUPPORTED_SHAPE, name << ": rank above 4");
             return OK;
-        case Op::SCALAR_MUL: case Op::SCALAR_MIN: case Op::SCALAR_MAX:
+        case Op::SCALAR_MUL: case Op::SCALAR_MIN: case Op::SCALAR_MAX: case Op::SCALAR_SUB:
             if (!need(1, 1) || n.attrs.size() != 1) FAIL(GRAPH_COMPILATION_FAILED, name << ": arity");
             if (in(0).dtype != out(0).dtype || in(0).shape != out(0).shape) FAIL(GRAPH_COMPILATION_FAILED, name << ": shape or dtype");
             if (in(0).dtype == DType::BOOL || (n.op == Op::SCALAR_MUL && in(0).dtype != DType::F32)) FAIL(UNSUPPORTED_OPERATION, name << ": dtype");
@@ -188,7 +193,9 @@ Status check_node(const Program &g, int index, std::string &message) {
                 FAIL(UNSUPPORTED_SHAPE, name << ": only [M,N] -> [N] (row-broadcast bias)");
             return OK;
         case Op::SOFTMAX:
-            if (!need(1, 1) || n.attrs.size() != 1) FAIL(GRAPH_COMPILATION_FAILED, name << ": arity");
+            // attributes: axis, then optionally the kind of the family (0 SOFTMAX, 1 LOG_SOFTMAX)
+            if (!need(1, 1) || n.attrs.size() < 1 || n.attrs.size() > 2) FAIL(GRAPH_COMPILATION_FAILED, name << ": arity");
+            if (n.attr_i(1) != 0 && n.attr_i(1) != 1) FAIL(UNSUPPORTED_OPERATION, name << ": unknown kind");
             if (in(0).dtype != DType::F32 || out(0).dtype != DType::F32) FAIL(UNSUPPORTED_OPERATION, name << ": only FLOAT32");
             if (in(0).shape != out(0).shape || in(0).shape.empty()) FAIL(GRAPH_COMPILATION_FAILED, name << ": shape");
             if ((int64_t)n.attrs[0] != (int64_t)in(0).shape.size() - 1) FAIL(UNSUPPORTED_SHAPE, name << ": only the last axis");
@@ -200,7 +207,18 @@ Status check_node(const Program &g, int index, std::string &message) {
             if (in(0).shape.size() != 2 || in(1).shape.size() != 1 || in(1).shape[0] != in(0).shape[0] || (int64_t)n.attrs[0] != 1)
                 FAIL(UNSUPPORTED_SHAPE, name << ": only [rows, classes] logits with class axis 1");
             // attributes: class axis, reduction (0 NONE = one loss per row, 1 MEAN, 2 SUM), has-ignore-index, ignore index
-            if (n.attrs[1] > 2 || n.attr_i(2) != 0) FAIL(UNSUPPORTED_OPERATION, name << ": no ignore index");
+            if (n.attrs[1] > 2 || n.attr_i(2) < 0 || n.attr_i(2) > 1) FAIL(UNSUPPORTED_OPERATION, name << ": unknown reduction or ignore flag");
+            if (n.attrs[1] == 0 ? (out(0).shape.size() != 1 || out(0).shape[0] != in(0).shape[0]) : out(0).elements() != 1)
+                FAIL(GRAPH_COMPILATION_FAILED, name << ": shape");
+            return OK;
+        case Op::DENSE_CROSS_ENTROPY:
+            // attributes: class axis, reduction (0 NONE = one loss per row, 1 MEAN, 2 SUM)
+            if (!need(2, 1) || n.attrs.size() < 2) FAIL(GRAPH_COMPILATION_FAILED, name << ": arity");
+            if (in(0).dtype != DType::F32 || in(1).dtype != DType::F32 || out(0).dtype != DType::F32) FAIL(UNSUPPORTED_OPERATION, name << ": only FLOAT32");
+            if (in(0).shape.size() != 2 || in(1).shape != in(0).shape || (int64_t)n.attrs[0] != 1)
+                FAIL(UNSUPPORTED_SHAPE, name << ": only [rows, classes] logits and targets with class axis 1");
+            if (in(0).shape[0] < 1 || in(0).shape[1] < 1) FAIL(UNSUPPORTED_SHAPE, name << ": empty extent");
+            if (n.attrs[1] > 2) FAIL(UNSUPPORTED_OPERATION, name << ": unknown reduction");
             if (n.attrs[1] == 0 ? (out(0).shape.size() != 1 || out(0).shape[0] != in(0).shape[0]) : out(0).elements() != 1)
                 FAIL(GRAPH_COMPILATION_FAILED, name << ": shape");
             return OK;

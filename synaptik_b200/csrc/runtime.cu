@@ -316,7 +316,7 @@ int32_t prepare_executable(Executable *x) {
         } else if (st.kind == StepKind::COLSUM) {
             void *p; if (!alloc((uint64_t)kern::colsum_partial_count(st.m, st.n) * 8, &p)) return ALLOCATION_FAILED;
             se.colsum_partials = (double *)p;
-        } else if (st.kind == StepKind::CROSS_ENTROPY) {
+        } else if (st.kind == StepKind::CROSS_ENTROPY || st.kind == StepKind::DENSE_CROSS_ENTROPY) {
             void *p; if (!alloc((uint64_t)st.m * 4, &p)) return ALLOCATION_FAILED;
             se.row_loss = (float *)p;
         }
@@ -460,7 +460,8 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                 const View &a = plan.views[st.a], &b = plan.views[st.b], &o = plan.views[st.out];
                 kern::Index4 ix = index4(o.shape, &a.strides, &b.strides, nullptr, &a.shape, &b.shape, nullptr);
                 int64_t total = 1; for (auto d : o.shape) total *= d;
-                LAUNCH(kern::binary(s, st.op, (const float *)ptr(st.a), (const float *)ptr(st.b), ptr(st.out), ix, total));
+                if (a.dtype == DType::F32) LAUNCH(kern::binary(s, st.op, (const float *)ptr(st.a), (const float *)ptr(st.b), ptr(st.out), ix, total));
+                else LAUNCH(kern::binary_int(s, st.op, a.dtype, ptr(st.a), ptr(st.b), ptr(st.out), ix, total));
                 break;
             }
             case StepKind::WHERE: {
@@ -516,7 +517,7 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                 break;
             }
             case StepKind::SOFTMAX:
-                LAUNCH(kern::softmax_rows(s, (const float *)ptr(st.a), (float *)ptr(st.out), st.m, st.n));
+                LAUNCH(kern::softmax_rows(s, (const float *)ptr(st.a), (float *)ptr(st.out), st.m, st.n, st.scalar_bits == 1));
                 break;
             case StepKind::CROSS_ENTROPY: {
                 // reduction of the forward loss node: NONE publishes the row losses themselves
@@ -524,8 +525,17 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                 const bool per_row = reduction == 0 && st.out >= 0;
                 LAUNCH(kern::cross_entropy(s, (const float *)ptr(st.a), plan.views[st.b].dtype, ptr(st.b), (const float *)ptr(st.c), st.m, st.n,
                                            per_row ? (float *)ptr(st.out) : se.row_loss, per_row ? nullptr : (float *)ptr(st.out),
-                                           (float *)ptr(st.out2), (int64_t *)ptr(st.out3), ctx->error_dev, reduction == 2));
+                                           (float *)ptr(st.out2), (int64_t *)ptr(st.out3), ctx->error_dev, reduction == 2,
+                                           st.has_ignore ? 1 : 0, st.ignore));
                 if (st.out >= 0 && !per_row) x->launches++;
+                break;
+            }
+            case StepKind::DENSE_CROSS_ENTROPY: {
+                const int reduction = (int)st.scalar_bits;
+                const bool per_row = reduction == 0;
+                LAUNCH(kern::dense_cross_entropy(s, (const float *)ptr(st.a), (const float *)ptr(st.b), st.m, st.n,
+                                                 per_row ? (float *)ptr(st.out) : se.row_loss, per_row ? nullptr : (float *)ptr(st.out), reduction == 2));
+                if (!per_row) x->launches++;
                 break;
             }
             case StepKind::MSE:

@@ -25,6 +25,7 @@ OPS = {
     "SCALAR_MAX": 9, "RELU": 10, "EXP": 11, "GT": 12, "WHERE": 13, "EXPAND": 14, "EXPAND_DIMS": 15,
     "CONTIGUOUS": 16, "ONE_HOT": 17, "MAX": 18, "SUM": 19, "SUM_TO_SHAPE": 20, "SOFTMAX": 21,
     "INDEX_CROSS_ENTROPY": 22, "MEAN_SQUARED_ERROR": 23, "ARG_MAX": 24, "TANH": 25, "SIGMOID": 26, "SILU": 27, "IS_INF": 28, "GELU_TANH": 29, "CLAMP": 30, "LT": 31, "EQ": 32,
+    "SCALAR_SUB": 33, "DENSE_CROSS_ENTROPY": 34,
 }
 ROLE_INTERMEDIATE, ROLE_FEED, ROLE_CONSTANT = 0, 1, 2
 MASK64 = (1 << 64) - 1
@@ -121,7 +122,7 @@ class GraphBuilder:
         return self._node("MATMUL", [a, b], F32, (a.shape[0], b.shape[1]))
 
     def _binary(self, op: str, a: Value, b: Value) -> Value:
-        return self._node(op, [a, b], BOOL if op in ("GT", "LT", "EQ") else F32, _broadcast(a.shape, b.shape))
+        return self._node(op, [a, b], BOOL if op in ("GT", "LT", "EQ") else a.dtype, _broadcast(a.shape, b.shape))
 
     def add(self, a, b): return self._binary("ADD", a, b)
     def sub(self, a, b): return self._binary("SUB", a, b)
@@ -152,6 +153,7 @@ class GraphBuilder:
     def scalar_mul(self, x, s): return self._scalar("SCALAR_MUL", x, s)
     def scalar_min(self, x, s): return self._scalar("SCALAR_MIN", x, s)
     def scalar_max(self, x, s): return self._scalar("SCALAR_MAX", x, s)
+    def scalar_sub(self, x, s): return self._scalar("SCALAR_SUB", x, s)
     def relu(self, x): return self._node("RELU", [x], F32, x.shape)
     def exp(self, x): return self._node("EXP", [x], F32, x.shape)
     def tanh(self, x): return self._node("TANH", [x], F32, x.shape)
@@ -195,11 +197,31 @@ class GraphBuilder:
     def sum_to_shape(self, x, shape): return self._node("SUM_TO_SHAPE", [x], F32, shape)
     def softmax(self, x, axis=-1): return self._node("SOFTMAX", [x], F32, x.shape, [axis % len(x.shape)])
 
-    def index_cross_entropy(self, logits: Value, labels: Value, reduction: str = "mean") -> Value:
-        """INDEX_CATEGORICAL_CROSS_ENTROPY_WITH_LOGITS, class axis 1, no ignore index; reduction "mean",
-        "sum" or "none" (one loss per row)."""
+    def log_softmax(self, x, axis=-1):
+        """Tensor.logSoftmax (Tensor.java:4669): the SOFTMAX node with kind LOG_SOFTMAX."""
+        return self._node("SOFTMAX", [x], F32, x.shape, [axis % len(x.shape), 1])
+
+    def softmax_backward(self, output: Value, upstream: Value, axis: int = -1) -> Value:
+        """y * (g - sum(g * y, axis, keep)) (ReductionGradientRules.java:84-90)."""
+        return self.mul(output, self.sub(upstream, self.sum(self.mul(upstream, output), axis, True)))
+
+    def log_softmax_backward(self, output: Value, upstream: Value, axis: int = -1) -> Value:
+        """g - exp(y) * sum(g, axis, keep) (ReductionGradientRules.java:84-90)."""
+        return self.sub(upstream, self.mul(self.exp(output), self.sum(upstream, axis, True)))
+
+    def index_cross_entropy(self, logits: Value, labels: Value, reduction: str = "mean", ignore_index=None) -> Value:
+        """INDEX_CATEGORICAL_CROSS_ENTROPY_WITH_LOGITS, class axis 1; reduction "mean", "sum" or "none"
+        (one loss per row); rows labelled `ignore_index` contribute nothing and MEAN does not count them
+        (TensorLossExpressions.java:301-403)."""
         shape = (logits.shape[0],) if reduction == "none" else ()
-        return self._node("INDEX_CROSS_ENTROPY", [logits, labels], F32, shape, [1, self.MSE_REDUCTIONS[reduction], 0, 0])
+        attrs = [1, self.MSE_REDUCTIONS[reduction], 0 if ignore_index is None else 1, 0 if ignore_index is None else int(ignore_index)]
+        return self._node("INDEX_CROSS_ENTROPY", [logits, labels], F32, shape, attrs)
+
+    def dense_cross_entropy(self, logits: Value, target: Value, reduction: str = "mean") -> Value:
+        """DENSE_CATEGORICAL_CROSS_ENTROPY_WITH_LOGITS with FLOAT32 target weights, class axis 1
+        (TensorLossExpressions.java:204-221)."""
+        shape = (logits.shape[0],) if reduction == "none" else ()
+        return self._node("DENSE_CROSS_ENTROPY", [logits, target], F32, shape, [1, self.MSE_REDUCTIONS[reduction]])
 
     MSE_REDUCTIONS = {"none": 0, "mean": 1, "sum": 2}
 
@@ -289,16 +311,58 @@ class GraphBuilder:
         count = self.sum_all(ones)
         return self.div(self.expand(seed, (rows,)), count)
 
-    def index_cross_entropy_backward(self, logits: Value, labels: Value, seed: Value) -> Value:
+    def _zeros(self, shape): return self.expand(self.constant(F32, 0.0), shape)
+    def _ones(self, shape): return self.expand(self.constant(F32, 1.0), shape)
+
+    def _restore(self, gradient: Value, rows: int, reduction: str) -> Value:
+        """LossGradientRules.restore (:239-252): the reduced cotangent back on the sample domain."""
+        if reduction == "none":
+            return gradient
+        return self._loss_scale(gradient, rows) if reduction == "mean" else self.expand(gradient, (rows,))
+
+    def _categorical_probabilities(self, logits: Value) -> Value:
+        """exp(x - MAX) / SUM(exp(x - MAX)) with aggregate MAX and SUM (LossGradientRules.java:239-243)."""
+        e = self.exp(self.sub(logits, self.max(logits, 1, True)))
+        return self.div(e, self.sum(e, 1, True))
+
+    def index_cross_entropy_backward(self, logits: Value, labels: Value, seed: Value, reduction: str = "mean",
+                                     ignore_index=None) -> Value:
+        """The node list of LossGradientRules.indexCategorical (:172-228).  `seed` is the output
+        cotangent: a scalar for "mean" / "sum", one value per row for "none"."""
         rows, classes = logits.shape
-        mx = self.max(logits, 1, True)
-        e = self.exp(self.sub(logits, mx))
-        p = self.div(e, self.sum(e, 1, True))
+        if ignore_index is None:
+            p = self._categorical_probabilities(logits)
         safe = self.scalar_min(self.scalar_max(labels, 0), classes - 1)
-        hot = self.where(self.one_hot(safe, classes), self.expand(self.constant(F32, 1.0), logits.shape),
-                         self.expand(self.constant(F32, 0.0), logits.shape))
-        scale = self.expand_dims(self._loss_scale(seed, rows), 1)
-        return self.mul(self.sub(p, hot), scale)
+        hot = self.where(self.one_hot(safe, classes), self._ones(logits.shape), self._zeros(logits.shape))
+        if ignore_index is None:
+            scale = self.expand_dims(self._restore(seed, rows, reduction), 1)
+            return self.mul(self.sub(p, hot), scale)
+        delta = self.scalar_sub(labels, ignore_index)
+        ignored = self.eq(delta, self.sub(delta, delta))
+        active = self.where(ignored, self._zeros((rows,)), self._ones((rows,)))
+        scale = seed if tuple(seed.shape) == (rows,) else self.expand(seed, (rows,))
+        if reduction == "mean":
+            scale = self.div(scale, self.sum_all(active))
+        scale = self.expand_dims(scale, 1)
+        ignored_row = self.expand_dims(ignored, 1)
+        safe_logits = self.where(ignored_row, self._zeros(logits.shape), logits)
+        scale = self.where(ignored_row, self._zeros(scale.shape), scale)
+        raw = self.mul(self.sub(self._categorical_probabilities(safe_logits), hot), scale)
+        return self.where(ignored_row, self._zeros(logits.shape), raw)
+
+    def dense_cross_entropy_backward(self, logits: Value, target: Value, seed: Value, reduction: str = "mean") -> Value:
+        """The logits cotangent of LossGradientRules.denseCategorical (:114-145): (p * mass - target) *
+        restored, with rows whose targets are all zero taken out."""
+        rows, _ = logits.shape
+        restored = self.expand_dims(self._restore(seed, rows, reduction), 1)
+        zero_target = self.eq(target, self._zeros(target.shape))
+        membership = self.sum(self.where(zero_target, self._zeros(target.shape), self._ones(target.shape)), 1, True)
+        empty_row = self.eq(membership, self._zeros(membership.shape))
+        probabilities = self._categorical_probabilities(self.where(empty_row, self._zeros(logits.shape), logits))
+        mass = self.sum(target, 1, True)
+        safe_scale = self.where(empty_row, self._zeros(restored.shape), restored)
+        raw = self.mul(self.sub(self.mul(probabilities, mass), target), safe_scale)
+        return self.where(empty_row, self._zeros(raw.shape), raw)
 
     def mean_squared_error_backward(self, prediction: Value, target: Value, seed: Value, reduction: str = "mean") -> Value:
         """((p - t) * 2) * restore(gradient) (LossGradientRules.java:77-101): MEAN restores the output

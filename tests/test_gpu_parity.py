@@ -225,6 +225,54 @@ def test_softmax_known_answers_and_special_rows(ctx, oracle):
     assert ulp_distance(p, oracle.softmax(big)).max() <= 4
 
 
+def test_log_softmax_known_answers_and_special_rows(ctx, oracle):
+    # the reference's known answers (CpuSoftmaxGeneratedKernelTest.java:196-236,
+    # MetalNormalizationLossNativeTest.java:294-304) beside rows with infinities and NaN
+    rows = np.array([[0, -1000, -1000, -1000], [0, 0, -np.inf, -np.inf], [-3.4028235e38, 3.4028235e38, 0, 1],
+                     [1000, 1001, -1000, 0], [np.inf, 1, np.inf, 2], [np.nan, 1, 2, 3], [-np.inf, 1000, 0, 0]], dtype=np.float32)
+    g = GraphBuilder()
+    x = g.feed(F32, rows.shape)
+    g.publish(g.log_softmax(x, 1))
+    (y,) = run_image(ctx, g, [rows])
+    expect = oracle.log_softmax(rows)
+    assert np.array_equal(np.isnan(y), np.isnan(expect))
+    inf = np.isinf(expect)
+    assert np.array_equal(y[inf], expect[inf])
+    assert y[0, 0] == 0.0 and not np.signbit(y[0, 0]) and y[0, 1] == -1000.0 and y[2, 0] == -np.inf
+    # stated tolerance: 4 units in the last place of max(1, |result|) (the row sum is rounded once
+    # from binary64 here and Kahan-compensated in binary32 there)
+    finite = np.isfinite(expect)
+    with np.errstate(over="ignore"):        # the unit in the last place above FLT_MAX
+        assert np.all(np.abs(y[finite] - expect[finite]) <= 4 * np.spacing(np.maximum(1, np.abs(expect[finite])).astype(np.float32)))
+    rng = np.random.default_rng(2)
+    big = (rng.standard_normal((257, 1000)) * 2).astype(np.float32)
+    g = GraphBuilder()
+    x = g.feed(F32, big.shape)
+    g.publish(g.log_softmax(x, 1))
+    (y,) = run_image(ctx, g, [big])
+    expect = oracle.log_softmax(big)
+    assert np.all(np.abs(y - expect) <= 4 * np.spacing(np.maximum(1, np.abs(expect)).astype(np.float32)))
+
+
+@pytest.mark.parametrize("log_kind", [False, True])
+def test_softmax_gradient_node_lists(ctx, oracle, log_kind):
+    # ReductionGradientRules.java:84-90, executed node by node on the stored forward result
+    rng = np.random.default_rng(3 + log_kind)
+    logits = (rng.standard_normal((129, 333)) * 2).astype(np.float32)
+    upstream = rng.standard_normal(logits.shape).astype(np.float32)
+    g = GraphBuilder()
+    x, up = g.feed(F32, logits.shape), g.feed(F32, logits.shape)
+    y = g.log_softmax(x, 1) if log_kind else g.softmax(x, 1)
+    g.publish(y)
+    g.publish(g.log_softmax_backward(y, up, 1) if log_kind else g.softmax_backward(y, up, 1))
+    out, grad = run_image(ctx, g, [logits, upstream])
+    # the chain is checked on the device's own forward result, so only the chain's roundings count
+    expect = oracle.softmax_backward(out, upstream, log_kind)
+    # stated tolerance: 4 units in the last place of the larger of the result and the subtracted term's bound
+    bound = np.abs(upstream).sum(axis=1).max() * np.exp(out) if log_kind else np.abs(upstream).max() * np.abs(out)
+    assert np.all(np.abs(grad - expect) <= 4 * np.spacing(np.maximum(np.abs(expect), bound).astype(np.float32)))
+
+
 @pytest.mark.parametrize("rows,classes,label_dtype", [(513, 1000, I32), (4096, 10, I32), (300, 1000, I64), (64, 37, I64), (128, 512, I32)])
 def test_cross_entropy_forward_backward(ctx, oracle, rows, classes, label_dtype):
     rng = np.random.default_rng(rows + classes)
@@ -274,6 +322,105 @@ def test_cross_entropy_sum_and_none_reductions(ctx, oracle, rows, classes):
         sequential = np.float32(sequential + value)
     assert abs(float(total) - float(sequential)) <= 1e-6 * abs(float(sequential))
     assert abs(float(mean) - float(ref_mean)) <= 1e-6 * abs(float(ref_mean))
+
+
+@pytest.mark.parametrize("rows,classes,label_dtype,ignore", [(300, 1000, I32, -100), (1024, 10, I64, 3), (65, 37, I32, -100)])
+def test_cross_entropy_ignore_index_forward_and_gradient(ctx, oracle, rows, classes, label_dtype, ignore):
+    # rows labelled with the ignore index give no loss and no gradient and are left out of the mean's
+    # count (CpuLossReferenceKernel.java:196-218; gradient node list LossGradientRules.java:172-228,
+    # executed node by node with integer SUB / EQ on the labels)
+    rng = np.random.default_rng(rows + classes)
+    logits = (rng.standard_normal((rows, classes)) * 2).astype(np.float32)
+    labels = rng.integers(0, classes, rows)
+    labels[rng.random(rows) < 0.3] = ignore
+    labels[0], labels[1] = ignore, (ignore + 1) % classes
+    for reduction in ("mean", "sum", "none"):
+        g = GraphBuilder()
+        lv, tv = g.feed(F32, (rows, classes)), g.feed(label_dtype, (rows,))
+        sv = g.feed(F32, (rows,) if reduction == "none" else ())
+        g.publish(g.index_cross_entropy(lv, tv, reduction, ignore_index=ignore))
+        g.publish(g.index_cross_entropy_backward(lv, tv, sv, reduction, ignore_index=ignore))
+        seed = rng.standard_normal(rows).astype(np.float32) if reduction == "none" else np.float32(1.0)
+        loss, grad = run_image(ctx, g, [logits, labels, seed])
+        per_row, reduced = oracle.index_cross_entropy_ignore(logits, labels, ignore, reduction)
+        if reduction == "none":
+            active = labels != ignore
+            assert np.all(loss[~active] == 0.0) and not np.any(np.signbit(loss[~active]))
+            scale = np.abs(per_row) + np.abs(logits[np.arange(rows), np.clip(labels, 0, classes - 1)])
+            assert np.all(np.abs(loss - per_row)[active] <= 4 * np.spacing(scale.astype(np.float32))[active])
+        else:
+            assert abs(float(loss) - float(reduced)) <= 4e-6 * abs(float(reduced))
+        expect = oracle.index_cross_entropy_ignore_backward(logits, labels, ignore, seed, reduction)
+        scale = np.abs(seed).max() if reduction == "none" else 1.0
+        tol = 4 * np.spacing(np.abs(expect)) + np.float32(2.0 ** -24) * scale / (rows if reduction == "mean" else 1)
+        assert np.all(np.abs(grad - expect) <= tol)
+        assert np.all(grad[labels == ignore] == 0.0)
+
+
+def test_cross_entropy_ignore_index_edge_cases(ctx, oracle):
+    # the ignore index is tested before the bounds: an ignored label far outside [0, classes) is fine,
+    # another one out of bounds still fails; all rows ignored: MEAN is 0 / 0 = NaN, SUM is 0
+    logits = np.zeros((4, 2), dtype=np.float32)
+    for reduction, labels, expect in (("mean", [1, -100, 0, -100], np.float32(np.log(2.0))), ("sum", [-100] * 4, np.float32(0.0)),
+                                      ("mean", [-100] * 4, np.float32(np.nan))):
+        g = GraphBuilder()
+        lv, tv = g.feed(F32, (4, 2)), g.feed(I64, (4,))
+        g.publish(g.index_cross_entropy(lv, tv, reduction, ignore_index=-100))
+        (loss,) = run_image(ctx, g, [logits, np.array(labels)])
+        assert np.array_equal(np.float32(loss), expect, equal_nan=True)
+        assert np.array_equal(oracle.index_cross_entropy_ignore(logits, labels, -100, reduction)[1], expect, equal_nan=True)
+    g = GraphBuilder()
+    lv, tv = g.feed(F32, (4, 2)), g.feed(I64, (4,))
+    g.publish(g.index_cross_entropy(lv, tv, "mean", ignore_index=-100))
+    with pytest.raises(native.NativeFailure) as failure:
+        run_image(ctx, g, [logits, np.array([0, -100, 2, 1])])
+    assert failure.value.status == 5
+
+
+@pytest.mark.parametrize("rows,classes", [(300, 1000), (1024, 10), (65, 37)])
+def test_dense_cross_entropy_forward_and_gradient(ctx, oracle, rows, classes):
+    # dense target weights (CpuLossReferenceKernel.java:129-143); gradient node list
+    # LossGradientRules.java:114-145 executed node by node; one row has only zero targets
+    rng = np.random.default_rng(rows * classes)
+    logits = (rng.standard_normal((rows, classes)) * 2).astype(np.float32)
+    target = rng.random((rows, classes)).astype(np.float32)
+    target[rng.random((rows, classes)) < 0.5] = 0.0
+    target /= np.maximum(target.sum(axis=1, keepdims=True), 1e-6)
+    target[3] = 0.0
+    for reduction in ("mean", "sum", "none"):
+        g = GraphBuilder()
+        lv, tv = g.feed(F32, (rows, classes)), g.feed(F32, (rows, classes))
+        sv = g.feed(F32, (rows,) if reduction == "none" else ())
+        g.publish(g.dense_cross_entropy(lv, tv, reduction))
+        g.publish(g.dense_cross_entropy_backward(lv, tv, sv, reduction))
+        seed = rng.standard_normal(rows).astype(np.float32) if reduction == "none" else np.float32(1.0)
+        loss, grad = run_image(ctx, g, [logits, target, seed])
+        per_row, reduced = oracle.dense_cross_entropy(logits, target, reduction)
+        if reduction == "none":
+            # stated tolerance: 4 units in the last place of sum |weight * (lse - x)| (the reference adds
+            # the terms in binary32 order, the device in binary64 rounded once), plus the lse's own 4
+            lse = np.log(np.exp(logits.astype(np.float64)).sum(axis=1, keepdims=True))
+            bound = (np.abs(target * (lse - logits)).sum(axis=1) * (1 + classes * 2.0 ** -24)).astype(np.float32)
+            extra = (np.abs(target).sum(axis=1) * np.spacing(np.abs(lse[:, 0]).astype(np.float32)) * 4).astype(np.float32)
+            assert np.all(np.abs(loss - per_row) <= classes * np.spacing(bound) / 2 + extra)
+            assert loss[3] == 0.0
+        else:
+            # the reference adds the rows in binary32 order (error up to rows * 2^-24 relative), the device in binary64
+            assert abs(float(loss) - float(reduced)) <= 4e-6 * abs(float(reduced))
+        expect = oracle.dense_cross_entropy_backward(logits, target, seed, reduction)
+        scale = np.abs(seed).max() if reduction == "none" else 1.0
+        tol = 4 * np.spacing(np.abs(expect)) + np.float32(2.0 ** -23) * scale / (rows if reduction == "mean" else 1)
+        assert np.all(np.abs(grad - expect) <= tol)
+        assert np.all(grad[3] == 0.0)
+
+
+def test_dense_cross_entropy_known_answer(ctx, oracle):
+    # MetalNormalizationLossNativeTest.java:59-68: logits (0, 0), target (2, 0), MEAN -> 2 ln 2
+    g = GraphBuilder()
+    lv, tv = g.feed(F32, (1, 2)), g.feed(F32, (1, 2))
+    g.publish(g.dense_cross_entropy(lv, tv, "mean"))
+    (loss,) = run_image(ctx, g, [np.zeros((1, 2), dtype=np.float32), np.array([[2, 0]], dtype=np.float32)])
+    assert np.float32(loss) == np.float32(2.0) * np.float32(np.log(2.0))
 
 
 def test_cross_entropy_rejects_out_of_range_labels(ctx):

@@ -58,6 +58,42 @@ def test_softmax_known_answers(oracle):
     assert math.isnan(p[0]) and p[1] == 0.0 and math.isnan(p[2])
 
 
+def test_log_softmax_known_answers(oracle):
+    for key in ("log_softmax_0_m1000", "log_softmax_extreme", "log_softmax_0_0", "log_softmax_inf_1"):
+        g = GOLDEN[key]
+        y, expect = oracle.log_softmax(_vals(g["x"])[None, :])[0], _vals(g["y"])
+        assert np.array_equal(y, expect, equal_nan=True), key
+    assert not np.signbit(oracle.log_softmax(_vals([0, -1000])[None, :])[0, 0])
+    g = GOLDEN["log_softmax_columns"]
+    for x, y in zip(g["x"], g["y"]):
+        assert np.allclose(oracle.log_softmax(_vals(x)[None, :])[0], _vals(y), atol=g["tol"], rtol=0)
+
+
+def test_categorical_loss_known_answers(oracle):
+    g = GOLDEN["dense_ce_0_0"]
+    per_row, mean = oracle.dense_cross_entropy(np.array(g["logits"], dtype=np.float32), np.array(g["target"], dtype=np.float32), "mean")
+    assert mean == np.float32(2.0) * np.float32(g["loss"] / 2) and per_row[0] == mean
+    g = GOLDEN["index_ce_0_0"]
+    assert oracle.index_cross_entropy(np.array(g["logits"], dtype=np.float32), g["labels"])[1] == np.float32(g["loss"])
+    # an ignore index: the ignored row is skipped before its bounds are looked at and is not counted
+    logits = np.zeros((3, 2), dtype=np.float32)
+    per_row, mean = oracle.index_cross_entropy_ignore(logits, [1, 7, 0], 7, "mean")
+    assert np.array_equal(per_row, np.array([g["loss"], 0.0, g["loss"]], dtype=np.float32)) and mean == np.float32(g["loss"])
+    assert oracle.index_cross_entropy_ignore(logits, [1, 7, 0], 7, "sum")[1] == np.float32(2.0) * np.float32(g["loss"])
+    assert np.isnan(oracle.index_cross_entropy_ignore(logits, [7, 7, 7], 7, "mean")[1])
+    # without rows to ignore the two forward checkers agree, and so do the two gradient checkers
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((33, 17)).astype(np.float32)
+    labels = rng.integers(0, 17, 33)
+    assert np.array_equal(oracle.index_cross_entropy_ignore(x, labels, -1, "mean")[0], oracle.index_cross_entropy(x, labels)[0])
+    assert np.array_equal(oracle.index_cross_entropy_ignore_backward(x, labels, -1), oracle.index_cross_entropy_backward(x, labels))
+    # a one-hot dense target is the index loss, row by row
+    hot = np.zeros_like(x)
+    hot[np.arange(33), labels] = 1.0
+    assert np.array_equal(oracle.dense_cross_entropy(x, hot, "none")[0], oracle.index_cross_entropy(x, labels)[0])
+    assert np.array_equal(oracle.dense_cross_entropy_backward(x, hot), oracle.index_cross_entropy_backward(x, labels))
+
+
 def test_relu_special_values(oracle):
     y = oracle.relu(_vals([-1.0, -0.0, 0.0, 2.5, "-inf", "inf", "nan"]))
     assert list(y[:6]) == [0.0, 0.0, 0.0, 2.5, 0.0, float("inf")] and math.isnan(y[6])
