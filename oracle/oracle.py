@@ -133,6 +133,20 @@ def gelu_tanh(x) -> np.ndarray:
     return y
 
 
+def gelu(x) -> np.ndarray:
+    x = _f32(x)
+    y = np.empty_like(x)
+    lib().syn_oracle_activation_f32(4, ctypes.c_int64(x.size), _p(x), _p(y))
+    return y
+
+
+def erf(x) -> np.ndarray:
+    x = _f32(x)
+    y = np.empty_like(x)
+    lib().syn_oracle_activation_f32(5, ctypes.c_int64(x.size), _p(x), _p(y))
+    return y
+
+
 def _coefficient(bits: int) -> np.float32:
     return np.array([bits], dtype=np.uint32).view(np.float32)[0]
 
@@ -157,6 +171,16 @@ def activation_backward(kind: str, output, upstream, pre_activation=None) -> np.
             t = tanh(u)
             u_prime = (one + squared * cubic_d) * s2pi
             regular = g * ((one + t) * half + ((x * (one - t * t)) * u_prime) * half)
+        return np.where(np.isinf(x), np.where(x > 0, g, np.float32(0.0)), regular).astype(np.float32)
+    if kind == "gelu":
+        # ElementwiseGradientRules.gelu (:272-278), FLOAT32 coefficients (:370-378)
+        x = _f32(pre_activation)
+        half, neg_half = _coefficient(0x3F000000), _coefficient(0xBF000000)
+        inv_sqrt2, inv_sqrt_2pi = _coefficient(0x3F3504F3), _coefficient(0x3ECC422A)
+        with np.errstate(invalid="ignore", over="ignore"):
+            cdf = (one + erf(x * inv_sqrt2)) * half
+            e = np.exp(((x * x) * neg_half).astype(np.float64)).astype(np.float32)
+            regular = g * (cdf + (x * e) * inv_sqrt_2pi)
         return np.where(np.isinf(x), np.where(x > 0, g, np.float32(0.0)), regular).astype(np.float32)
     if kind == "silu":
         x = _f32(pre_activation)
@@ -426,7 +450,7 @@ def mlp_forward(x, weights, biases, activation: str = "relu", pre_activations=No
         hidden_layer = index + 1 < len(weights)
         z, a = linear(a, w, b, relu_flag=hidden_layer and activation == "relu")
         if hidden_layer and activation != "relu":
-            a = {"tanh": tanh, "sigmoid": sigmoid, "silu": silu, "gelu_tanh": gelu_tanh}[activation](z)
+            a = {"tanh": tanh, "sigmoid": sigmoid, "silu": silu, "gelu_tanh": gelu_tanh, "gelu": gelu}[activation](z)
         if pre_activations is not None:
             pre_activations.append(z)
         acts.append(a)

@@ -567,7 +567,11 @@ SYN_EXPORT void syn_oracle_clamp_f32(int64_t count, const float *x, float lo, fl
 /* SILU (CpuScalarReferenceKernel.java:1236-1241): -inf gives -0; x / (1 + exp(-x)) for x >= 0,    */
 /* x * exp(x) / (1 + exp(x)) below and for NaN.                                                  */
 /* Tanh GELU (:1224-1229): -inf gives -0; 0.5 x (1 + tanh(sqrt(2 / pi) (x + 0.044715 x^3))).      */
-/* op: 0 = tanh, 1 = sigmoid, 2 = silu, 3 = tanh-approximated GELU.                              */
+/* Exact GELU (CpuScalarEmitter.java:441-452): -inf gives -0; 0.5 x (1 + erf(x / sqrt 2)); ERF     */
+/* (:353-366): erf of the widened value.  The reference's erf is a rational approximation accurate  */
+/* to binary64 rounding (CpuScalarReferenceKernel.java:1254-1268: signed zero unchanged, +-1 from     */
+/* |x| = 6 on, which is also what erf rounds to in binary64); the C library's erf stands in for it.  */
+/* op: 0 = tanh, 1 = sigmoid, 2 = silu, 3 = tanh-approximated GELU, 4 = exact GELU, 5 = erf.        */
 /* ------------------------------------------------------------------------------------------ */
 SYN_EXPORT void syn_oracle_activation_f32(int op, int64_t count, const float *x, float *y) {
     for (int64_t i = 0; i < count; i++) {
@@ -581,6 +585,11 @@ SYN_EXPORT void syn_oracle_activation_f32(int op, int64_t count, const float *x,
             if (v == -INFINITY) r = -0.0;
             else if (v >= 0.0) r = v / (1.0 + exp(-v));
             else { double e = exp(v); r = v * e / (1.0 + e); }
+        } else if (op == 4) {
+            if (v == -INFINITY) r = -0.0;
+            else r = 0.5 * v * (1.0 + erf(v / sqrt(2.0)));
+        } else if (op == 5) {
+            r = erf(v);
         } else {
             if (v == -INFINITY) r = -0.0;
             else { double cube = v * v * v; r = 0.5 * v * (1.0 + tanh(sqrt(2.0 / 3.14159265358979323846) * (v + 0.044715 * cube))); }

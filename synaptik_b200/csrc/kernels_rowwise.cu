@@ -209,6 +209,17 @@ __device__ __forceinline__ float gelu_tanh_value(float x) {
     return (float)(0.5 * v * (1.0 + tanh(sqrt(2.0 / 3.14159265358979323846) * (v + 0.044715 * cube))));
 }
 
+// ERF and the exact GELU on FLOAT32 (CpuScalarEmitter.java:353-366,441-452): the value widened to
+// binary64, erf (the reference's rational approximation is accurate to binary64 rounding, returns
+// the signed zero unchanged and +-1 from |x| = 6 on, as the library function rounds to), for GELU
+// 0.5 * x * (1 + erf(x / sqrt(2))) with -inf giving -0, then one narrowing.
+__device__ __forceinline__ float erf_value(float x) { return (float)erf((double)x); }
+__device__ __forceinline__ float gelu_value(float x) {
+    const double v = (double)x;
+    if (v == -CUDART_INF) return -0.0f;
+    return (float)(0.5 * v * (1.0 + erf(v / sqrt(2.0))));
+}
+
 __global__ void unary_kernel(int op, const float *__restrict__ a, void *out_raw, int64_t total) {
     float *out = static_cast<float *>(out_raw);
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -219,6 +230,8 @@ __global__ void unary_kernel(int op, const float *__restrict__ a, void *out_raw,
             case Op::SIGMOID: out[i] = sigmoid_value(x); break;
             case Op::SILU: out[i] = silu_value(x); break;
             case Op::GELU_TANH: out[i] = gelu_tanh_value(x); break;
+            case Op::GELU: out[i] = gelu_value(x); break;
+            case Op::ERF: out[i] = erf_value(x); break;
             case Op::IS_INF: static_cast<uint8_t *>(out_raw)[i] = (__float_as_uint(x) & 0x7fffffffu) == 0x7f800000u; break;
             default: out[i] = exp_accurate(x); break;
         }
@@ -709,7 +722,23 @@ __global__ void ce_rows_generic_kernel(const float *__restrict__ logits, const v
 __global__ void mean_kernel(const float *__restrict__ values, int64_t count, float *out, int divide) {
     __shared__ double partial[32];
     double acc = 0.0;
-    for (int64_t i = threadIdx.x; i < count; i += blockDim.x) acc += (double)values[i];
+    if ((count & 3) == 0 && ((uintptr_t)values & 15) == 0) {
+        // 16-byte loads, four of them in flight per thread: one block reading scalars one by one is
+        // bound by load latency (12 us for 65536 row losses)
+        const float4 *v4 = reinterpret_cast<const float4 *>(values);
+        const int64_t n4 = count >> 2;
+        int64_t i = threadIdx.x;
+        for (; i + 3 * (int64_t)blockDim.x < n4; i += 4 * (int64_t)blockDim.x) {
+            float4 q[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) q[u] = v4[i + u * (int64_t)blockDim.x];
+#pragma unroll
+            for (int u = 0; u < 4; u++) acc += ((double)q[u].x + (double)q[u].y) + ((double)q[u].z + (double)q[u].w);
+        }
+        for (; i < n4; i += blockDim.x) { float4 q = v4[i]; acc += ((double)q.x + (double)q.y) + ((double)q.z + (double)q.w); }
+    } else {
+        for (int64_t i = threadIdx.x; i < count; i += blockDim.x) acc += (double)values[i];
+    }
     acc = warp_sum(acc);
     if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = acc;
     __syncthreads();

@@ -7,7 +7,7 @@
 //                  when both are stored
 //   BINARY         a, b -> out (op = ADD/SUB/MUL/DIV/GT), right-aligned broadcasting by strides
 //   SCALAR         a -> out (op = SCALAR_MUL/MIN/MAX, scalar_bits)
-//   UNARY          a -> out (op = RELU/EXP/TANH/SIGMOID/SILU/GELU_TANH, or IS_INF with a BOOL result)
+//   UNARY          a -> out (op = RELU/EXP/TANH/SIGMOID/SILU/GELU_TANH/GELU/ERF, or IS_INF with a BOOL result)
 //   WHERE          a = condition, b, c -> out
 //   ONE_HOT        a -> out (scalar_bits = depth)
 //   COPY           a (any view) -> out (dense)
@@ -533,6 +533,7 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
                 break;
             }
             case Op::RELU: case Op::EXP: case Op::TANH: case Op::SIGMOID: case Op::SILU: case Op::IS_INF: case Op::GELU_TANH:
+            case Op::GELU: case Op::ERF:
                 assign_output(out0);
                 st.kind = StepKind::UNARY; st.a = in0; st.out = out0;
                 finish_step(st);

@@ -21,7 +21,7 @@ const char *op_name(Op op) {
         case Op::TANH: return "TANH"; case Op::SIGMOID: return "SIGMOID"; case Op::SILU: return "SILU";
         case Op::IS_INF: return "IS_INF"; case Op::GELU_TANH: return "GELU_TANH_APPROXIMATION";
         case Op::CLAMP: return "CLAMP"; case Op::LT: return "LT"; case Op::EQ: return "EQ";
-        case Op::SCALAR_SUB: return "SCALAR_SUB";
+        case Op::SCALAR_SUB: return "SCALAR_SUB"; case Op::GELU: return "GELU"; case Op::ERF: return "ERF";
         case Op::DENSE_CROSS_ENTROPY: return "DENSE_CATEGORICAL_CROSS_ENTROPY_WITH_LOGITS";
     }
     return "?";
@@ -132,7 +132,7 @@ Status check_node(const Program &g, int index, std::string &message) {
             if (in(0).dtype != DType::F32) FAIL(UNSUPPORTED_OPERATION, name << ": only FLOAT32");
             if (out(0).dtype != DType::BOOL || in(0).shape != out(0).shape) FAIL(GRAPH_COMPILATION_FAILED, name << ": result");
             return OK;
-        case Op::RELU: case Op::EXP: case Op::TANH: case Op::SIGMOID: case Op::SILU: case Op::GELU_TANH:
+        case Op::RELU: case Op::EXP: case Op::TANH: case Op::SIGMOID: case Op::SILU: case Op::GELU_TANH: case Op::GELU: case Op::ERF:
             if (!need(1, 1)) FAIL(GRAPH_COMPILATION_FAILED, name << ": arity");
             if (in(0).dtype != DType::F32 || out(0).dtype != DType::F32) FAIL(UNSUPPORTED_OPERATION, name << ": only FLOAT32");
             if (in(0).shape != out(0).shape) FAIL(GRAPH_COMPILATION_FAILED, name << ": shape");

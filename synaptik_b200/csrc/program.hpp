@@ -51,7 +51,7 @@ enum class Op : uint32_t {
     SCALAR_MAX = 9, RELU = 10, EXP = 11, GT = 12, WHERE = 13, EXPAND = 14, EXPAND_DIMS = 15,
     CONTIGUOUS = 16, ONE_HOT = 17, MAX = 18, SUM = 19, SUM_TO_SHAPE = 20, SOFTMAX = 21,
     INDEX_CROSS_ENTROPY = 22, MEAN_SQUARED_ERROR = 23, ARG_MAX = 24, TANH = 25, SIGMOID = 26, SILU = 27, IS_INF = 28, GELU_TANH = 29, CLAMP = 30, LT = 31, EQ = 32,
-    SCALAR_SUB = 33, DENSE_CROSS_ENTROPY = 34
+    SCALAR_SUB = 33, DENSE_CROSS_ENTROPY = 34, GELU = 35, ERF = 36
 };
 const char *op_name(Op op);
 

@@ -67,8 +67,8 @@ class Model:
 
     def __init__(self, dims: Sequence[int], context: native.Context | None = None, seed: int = 0,
                  comm: native.Comm | None = None, world_size: int = 1, bias: bool = True, activation: str = "relu"):
-        if activation not in ("relu", "tanh", "sigmoid", "silu", "gelu_tanh"):
-            raise ValueError("activation must be 'relu', 'tanh', 'sigmoid', 'silu' or 'gelu_tanh'")
+        if activation not in ("relu", "tanh", "sigmoid", "silu", "gelu_tanh", "gelu"):
+            raise ValueError("activation must be 'relu', 'tanh', 'sigmoid', 'silu', 'gelu_tanh' or 'gelu'")
         self.dims = list(dims)
         self.bias = bias
         self.activation = activation

@@ -25,7 +25,7 @@ OPS = {
     "SCALAR_MAX": 9, "RELU": 10, "EXP": 11, "GT": 12, "WHERE": 13, "EXPAND": 14, "EXPAND_DIMS": 15,
     "CONTIGUOUS": 16, "ONE_HOT": 17, "MAX": 18, "SUM": 19, "SUM_TO_SHAPE": 20, "SOFTMAX": 21,
     "INDEX_CROSS_ENTROPY": 22, "MEAN_SQUARED_ERROR": 23, "ARG_MAX": 24, "TANH": 25, "SIGMOID": 26, "SILU": 27, "IS_INF": 28, "GELU_TANH": 29, "CLAMP": 30, "LT": 31, "EQ": 32,
-    "SCALAR_SUB": 33, "DENSE_CROSS_ENTROPY": 34,
+    "SCALAR_SUB": 33, "DENSE_CROSS_ENTROPY": 34, "GELU": 35, "ERF": 36,
 }
 ROLE_INTERMEDIATE, ROLE_FEED, ROLE_CONSTANT = 0, 1, 2
 MASK64 = (1 << 64) - 1
@@ -161,10 +161,12 @@ class GraphBuilder:
     def silu(self, x): return self._node("SILU", [x], F32, x.shape)
     def is_inf(self, x): return self._node("IS_INF", [x], BOOL, x.shape)
     def gelu_tanh(self, x): return self._node("GELU_TANH", [x], F32, x.shape)
+    def gelu(self, x): return self._node("GELU", [x], F32, x.shape)
+    def erf(self, x): return self._node("ERF", [x], F32, x.shape)
 
     def activation(self, kind: str, x: Value) -> Value:
         return {"relu": self.relu, "tanh": self.tanh, "sigmoid": self.sigmoid, "silu": self.silu,
-                "gelu_tanh": self.gelu_tanh}[kind](x)
+                "gelu_tanh": self.gelu_tanh, "gelu": self.gelu}[kind](x)
 
     def where(self, condition: Value, a: Value, b: Value) -> Value:
         return self._node("WHERE", [condition, a, b], F32, _broadcast(_broadcast(condition.shape, a.shape), b.shape))
@@ -279,6 +281,7 @@ class GraphBuilder:
         return self.where(self.is_inf(x), self.where(self.gt(x, zero), upstream, zero), regular)
 
     # FLOAT32 coefficients of the gradient rules (ElementwiseGradientRules.java:370-378, float32Bits column)
+    _NEGATIVE_HALF, _INV_SQRT_2, _INV_SQRT_2_PI = 0xBF000000, 0x3F3504F3, 0x3ECC422A
     _HALF, _SQRT_2_OVER_PI = 0x3F000000, 0x3F4C422A
     _GELU_CUBIC, _GELU_CUBIC_DERIVATIVE = 0x3D372713, 0x3E095D4F
 
@@ -297,7 +300,21 @@ class GraphBuilder:
         regular = self.mul(upstream, self.add(left, right))
         return self.where(self.is_inf(x), self.where(self.gt(x, zero), upstream, zero), regular)
 
+    def gelu_backward(self, x: Value, upstream: Value) -> Value:
+        """The node list of ElementwiseGradientRules.gelu (:272-278): g * (Phi(x) + x * phi(x)) with
+        Phi = (1 + ERF(x / sqrt 2)) / 2 and phi = exp(-x^2 / 2) / sqrt(2 pi), every coefficient a
+        SCALAR_MUL by its FLOAT32 bit pattern, and the infinity selection shared with SiLU."""
+        f = lambda bits: struct.unpack("<f", struct.pack("<I", bits))[0]
+        one = self.expand(self.constant(F32, 1.0), x.shape)
+        zero = self.expand(self.constant(F32, 0.0), x.shape)
+        cdf = self.scalar_mul(self.add(one, self.erf(self.scalar_mul(x, f(self._INV_SQRT_2)))), f(self._HALF))
+        pdf_term = self.scalar_mul(self.mul(x, self.exp(self.scalar_mul(self.mul(x, x), f(self._NEGATIVE_HALF)))), f(self._INV_SQRT_2_PI))
+        regular = self.mul(upstream, self.add(cdf, pdf_term))
+        return self.where(self.is_inf(x), self.where(self.gt(x, zero), upstream, zero), regular)
+
     def activation_backward(self, kind: str, pre_activation: Value, output: Value, upstream: Value) -> Value:
+        if kind == "gelu":
+            return self.gelu_backward(pre_activation, upstream)
         if kind == "gelu_tanh":
             return self.gelu_tanh_backward(pre_activation, upstream)
         if kind == "relu":

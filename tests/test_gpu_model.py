@@ -206,7 +206,7 @@ def test_training_state_snapshot_restores_a_run_exactly(ctx):
     a.close(); b.close()
 
 
-@pytest.mark.parametrize("activation", ["tanh", "sigmoid", "silu", "gelu_tanh"])
+@pytest.mark.parametrize("activation", ["tanh", "sigmoid", "silu", "gelu_tanh", "gelu"])
 def test_tanh_and_sigmoid_networks_match_the_checker(ctx, oracle, activation):
     # ModelBuilder.linear().tanh() / .sigmoid() stacks: forward, gradients and three Adam steps on the
     # exact GEMM engine; the activations differ from the checker by at most 1 ulp on rare ties, so the

@@ -307,6 +307,26 @@ def test_gelu_tanh_special_values_and_coefficients(oracle):
     assert g[0] == 3.0 and g[1] == 0.0 and g[2] == 1.0            # d/dx at 0 is 1/2, times g = 2
 
 
+def test_erf_and_exact_gelu_special_values(oracle):
+    g = GOLDEN["erf_special_values"]
+    y, want = oracle.erf(_vals(g["x"])), _vals(g["y"])
+    assert np.isnan(y[0]) and y[1] == 1.0 and y[2] == -1.0 and y[3] == 0.0 and np.signbit(y[3])
+    assert abs(float(y[4]) - float(want[4])) <= g["tol"]
+    # the reference returns +-1 from |x| = 6 on (CpuScalarReferenceKernel.java:1258); so does erf in binary64
+    assert np.array_equal(oracle.erf(_vals([6.0, -6.0, 7.5])), _vals([1.0, -1.0, 1.0]))
+    # exact GELU (CpuScalarEmitter.java:441-452): -inf gives -0, +inf stays +inf, signed zeros kept
+    x = np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 1.0], np.float32)
+    y = oracle.gelu(x)
+    assert y[0] == 0.0 and not np.signbit(y[0]) and y[1] == 0.0 and np.signbit(y[1])
+    assert y[2] == np.inf and y[3] == 0.0 and np.signbit(y[3]) and np.isnan(y[4])
+    assert y[5] == np.float32(0.5 * (1.0 + math.erf(1.0 / math.sqrt(2.0))))
+    # gradient rule coefficients (ElementwiseGradientRules.java:370-378) and its infinity selection
+    assert oracle._coefficient(0x3F3504F3) == np.float32(1.0 / math.sqrt(2.0))
+    assert oracle._coefficient(0x3ECC422A) == np.float32(1.0 / math.sqrt(2.0 * math.pi)) and oracle._coefficient(0xBF000000) == -0.5
+    grad = oracle.activation_backward("gelu", None, np.array([3.0, 3.0, 2.0], np.float32), np.array([np.inf, -np.inf, 0.0], np.float32))
+    assert grad[0] == 3.0 and grad[1] == 0.0 and grad[2] == 1.0            # d/dx at 0 is 1/2, times g = 2
+
+
 def test_clamp_signed_zero_and_nan_rules(oracle):
     # documented on Tensor.clamp (Tensor.java:2325-2331): NaN input gives NaN; bounds [-0, +0] keep -0 for
     # negative inputs and -0, +0 for positive inputs and +0; bounds [+0, -0] give -0 for every non-NaN input
