@@ -222,6 +222,7 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
     for (int i = 0; i < node_count; i++) {
         const Node &mm = g.nodes[i];
         if (mm.op != Op::MATMUL) continue;
+        if (g.values[mm.inputs[0]].shape.size() != 2 || g.values[mm.inputs[1]].shape.size() != 2) continue;   // batched: lowered per slice below
         LinearGroup lg;
         lg.matmul = i;
         lg.emit_at = i;
@@ -440,11 +441,10 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
         return -1;
     };
 
-    for (int i = 0; i < node_count; i++) {
-        auto pending = emit_at.find(i);
-        if (pending != emit_at.end()) for (Step st : pending->second) {
-            for (int v : {st.out, st.out2, st.out3}) if (v >= 0) assign_output(v);
-            if (st.kind == StepKind::GEMM) {
+    // engine and operand checks of one GEMM step whose views are assigned
+    auto prepare_gemm = [&](Step &st) -> Status {
+        {
+            {
                 const View &c = plan.views[st.out];
                 bool transposed = c.strides.size() == 2 && c.strides[0] == 1 && c.shape[0] != 1 && c.strides[1] != 1;
                 if (transposed && (st.bias >= 0 || st.mask >= 0 || st.relu)) { message = "transposed GEMM result with an epilogue"; return UNSUPPORTED_SHAPE; }
@@ -468,6 +468,18 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
                 }
                 if (st.bias >= 0 && !plan.views[st.bias].dense()) { message = "strided bias"; return UNSUPPORTED_SHAPE; }
                 if (st.mask >= 0 && !plan.views[st.mask].dense()) { message = "strided gate"; return UNSUPPORTED_SHAPE; }
+            }
+        }
+        return OK;
+    };
+
+    for (int i = 0; i < node_count; i++) {
+        auto pending = emit_at.find(i);
+        if (pending != emit_at.end()) for (Step st : pending->second) {
+            for (int v : {st.out, st.out2, st.out3}) if (v >= 0) assign_output(v);
+            if (st.kind == StepKind::GEMM) {
+                Status gs = prepare_gemm(st);
+                if (gs != OK) return gs;
             } else if (st.kind == StepKind::CROSS_ENTROPY) {
                 if (dense_input(st.a) < 0 || dense_input(st.b) < 0) return UNSUPPORTED_SHAPE;
             } else if (st.kind == StepKind::RELU_BACKWARD) {
@@ -510,7 +522,68 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
                 finish_step(st);
                 break;
             }
-            case Op::MATMUL: message = "internal: MATMUL not grouped"; return INTERNAL_ERROR;
+            case Op::MATMUL: {
+                // Operands with leading batch dimensions (Tensor.java:1075-1096).  A left operand whose
+                // batch and row dimensions collapse into one row dimension over a right operand shared by
+                // the whole batch (Linear applied to [batch, time, features]) is one product; anything
+                // else is one product per batch slice, each over views of the operands.
+                assign_output(out0);
+                const View va = plan.views[n.inputs[0]], vb = plan.views[n.inputs[1]], vo = plan.views[out0];
+                const size_t r = vo.shape.size(), nb = r - 2;
+                auto aligned_batch_strides = [&](const View &v) {     // stride per result batch dimension, 0 where broadcast
+                    std::vector<int64_t> s(nb, 0);
+                    const size_t own = v.shape.size() - 2;
+                    for (size_t d = 0; d < own; d++) s[nb - own + d] = v.shape[d] == 1 ? 0 : v.strides[d];
+                    return s;
+                };
+                const std::vector<int64_t> sa = aligned_batch_strides(va), sb = aligned_batch_strides(vb), so = aligned_batch_strides(vo);
+                const int64_t M = vo.shape[r - 2], N = vo.shape[r - 1], K = va.shape.back();
+                int64_t batches = 1;
+                for (size_t d = 0; d < nb; d++) batches *= vo.shape[d];
+                auto rows_collapse = [&](const View &v, const std::vector<int64_t> &bs) {   // [batch.., M, X] reads as [batches * M, X]
+                    int64_t expect = v.strides[v.shape.size() - 2] * M;
+                    for (size_t d = nb; d-- > 0;) { if (vo.shape[d] != 1 && bs[d] != expect) return false; expect *= vo.shape[d]; }
+                    return true;
+                };
+                bool shared_right = true;
+                for (size_t d = 0; d < nb; d++) shared_right &= sb[d] == 0 || vo.shape[d] == 1;
+                auto slice = [&](const View &v, int64_t offset, int64_t rows) {
+                    View w;
+                    w.slot = v.slot; w.index = v.index; w.dtype = v.dtype; w.offset = v.offset + offset;
+                    w.shape = {rows, v.shape.back()};
+                    w.strides = {v.strides[v.shape.size() - 2], v.strides.back()};
+                    plan.views.push_back(w);
+                    return (int)plan.views.size() - 1;
+                };
+                auto emit = [&](int64_t oa, int64_t ob, int64_t oo, int64_t rows) -> Status {
+                    Step gs = st;
+                    gs.kind = StepKind::GEMM;
+                    gs.a = slice(va, oa, rows); gs.b = slice(vb, ob, K); gs.out = slice(vo, oo, rows);
+                    gs.m = rows; gs.n = N; gs.k = K;
+                    gs.engine = choose_engine(gs.m, gs.n, gs.k);
+                    Status status = prepare_gemm(gs);
+                    if (status != OK) return status;
+                    plan.steps.push_back(gs);
+                    return OK;
+                };
+                if (shared_right && rows_collapse(va, sa) && rows_collapse(vo, so)) {
+                    Status status = emit(0, 0, 0, batches * M);
+                    if (status != OK) return status;
+                } else {
+                    if (batches > 4096) { message = "more than 4096 batch slices"; return UNSUPPORTED_SHAPE; }
+                    std::vector<int64_t> index(nb, 0);
+                    for (int64_t bi = 0; bi < batches; bi++) {
+                        int64_t oa = 0, ob = 0, oo = 0;
+                        for (size_t d = 0; d < nb; d++) { oa += index[d] * sa[d]; ob += index[d] * sb[d]; oo += index[d] * so[d]; }
+                        Status status = emit(oa, ob, oo, M);
+                        if (status != OK) return status;
+                        for (size_t d = nb; d-- > 0;) { if (++index[d] < vo.shape[d]) break; index[d] = 0; }
+                    }
+                }
+                // the last slice completes the result
+                if (vo.slot == SlotKind::PUBLICATION) { plan.steps.back().ready_publications.push_back(vo.index); published_done[vo.index] = 1; }
+                break;
+            }
             case Op::ADD: case Op::SUB: case Op::MUL: case Op::DIV: case Op::GT: case Op::LT: case Op::EQ:
                 assign_output(out0);
                 st.kind = StepKind::BINARY; st.a = n.inputs[0]; st.b = n.inputs[1]; st.out = out0;
@@ -565,7 +638,8 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
             case Op::SUM_TO_SHAPE:
                 if (dense_input(in0) < 0) return UNSUPPORTED_SHAPE;
                 assign_output(out0);
-                st.kind = StepKind::COLSUM; st.a = in0; st.out = out0; st.m = g.values[in0].shape[0]; st.n = g.values[in0].shape[1];
+                st.kind = StepKind::COLSUM; st.a = in0; st.out = out0;
+                st.n = ov.elements(); st.m = g.values[in0].elements() / std::max<int64_t>(st.n, 1);     // leading dimensions are summed
                 finish_step(st);
                 break;
             case Op::SOFTMAX:

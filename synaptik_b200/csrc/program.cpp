@@ -1,6 +1,7 @@
 // Decoder and validator of the "SCU1" program image (layout in program.hpp).
 #include "program.hpp"
 
+#include <algorithm>
 #include <cstring>
 #include <sstream>
 
@@ -101,11 +102,20 @@ Status check_node(const Program &g, int index, std::string &message) {
             if (!need(2, 1)) FAIL(GRAPH_COMPILATION_FAILED, name << ": arity");
             if (in(0).dtype != DType::F32 || in(1).dtype != DType::F32 || out(0).dtype != DType::F32)
                 FAIL(UNSUPPORTED_OPERATION, name << ": only FLOAT32 operands");
-            if (in(0).shape.size() != 2 || in(1).shape.size() != 2 || out(0).shape.size() != 2)
-                FAIL(UNSUPPORTED_SHAPE, name << ": only rank-2 operands");
-            if (in(0).shape[1] != in(1).shape[0] || out(0).shape[0] != in(0).shape[0] || out(0).shape[1] != in(1).shape[1])
-                FAIL(GRAPH_COMPILATION_FAILED, name << ": shape");
-            if (in(0).shape[1] < 1) FAIL(UNSUPPORTED_SHAPE, name << ": empty contraction");
+            if (in(0).shape.size() == 2 && in(1).shape.size() == 2) {
+                if (out(0).shape.size() != 2 || in(0).shape[1] != in(1).shape[0] || out(0).shape[0] != in(0).shape[0] || out(0).shape[1] != in(1).shape[1])
+                    FAIL(GRAPH_COMPILATION_FAILED, name << ": shape");
+            } else {
+                // leading batch dimensions broadcast right-aligned (Tensor.java:1075-1096)
+                const size_t ra = in(0).shape.size(), rb = in(1).shape.size();
+                if (ra < 2 || rb < 2 || ra > 4 || rb > 4) FAIL(UNSUPPORTED_SHAPE, name << ": operand rank outside 2..4");
+                std::vector<int64_t> batch_a(in(0).shape.begin(), in(0).shape.end() - 2), batch_b(in(1).shape.begin(), in(1).shape.end() - 2);
+                if (!broadcastable(batch_a, batch_b, shape)) FAIL(GRAPH_COMPILATION_FAILED, name << ": batch dimensions do not broadcast");
+                shape.push_back(in(0).shape[ra - 2]); shape.push_back(in(1).shape[rb - 1]);
+                if (in(0).shape[ra - 1] != in(1).shape[rb - 2] || shape != out(0).shape) FAIL(GRAPH_COMPILATION_FAILED, name << ": shape");
+            }
+            if (in(0).shape.back() < 1) FAIL(UNSUPPORTED_SHAPE, name << ": empty contraction");
+            if (out(0).elements() < 1) FAIL(UNSUPPORTED_SHAPE, name << ": empty result");
             return OK;
         case Op::ADD: case Op::SUB: case Op::MUL: case Op::DIV: case Op::GT: case Op::LT: case Op::EQ:
             if (!need(2, 1)) FAIL(GRAPH_COMPILATION_FAILED, name << ": arity");
@@ -189,8 +199,16 @@ Status check_node(const Program &g, int index, std::string &message) {
         case Op::SUM_TO_SHAPE:
             if (!need(1, 1)) FAIL(GRAPH_COMPILATION_FAILED, name << ": arity");
             if (in(0).dtype != DType::F32 || out(0).dtype != DType::F32) FAIL(UNSUPPORTED_OPERATION, name << ": only FLOAT32");
-            if (in(0).shape.size() != 2 || out(0).elements() != in(0).shape[1] || out(0).shape.empty() || out(0).shape.back() != in(0).shape[1])
-                FAIL(UNSUPPORTED_SHAPE, name << ": only [M,N] -> [N] (row-broadcast bias)");
+            // the broadcast-reversing reduction over leading dimensions: the result's dimensions are the
+            // input's trailing ones (leading result dimensions of 1 allowed), e.g. [M,N] -> [N] for a
+            // row-broadcast bias, [B,T,N] -> [N], [B,K,N] -> [K,N]
+            {
+                std::vector<int64_t> target = out(0).shape;
+                while (target.size() > 1 && target.front() == 1) target.erase(target.begin());
+                const std::vector<int64_t> &src = in(0).shape;
+                if (target.empty() || target.size() >= src.size() || !std::equal(target.begin(), target.end(), src.end() - (long)target.size()))
+                    FAIL(UNSUPPORTED_SHAPE, name << ": only sums over leading dimensions");
+            }
             return OK;
         case Op::SOFTMAX:
             // attributes: axis, then optionally the kind of the family (0 SOFTMAX, 1 LOG_SOFTMAX)

@@ -117,9 +117,30 @@ class GraphBuilder:
         return self._node("PERMUTE", [x], x.dtype, [x.shape[p] for p in permutation], permutation)
 
     def matmul(self, a: Value, b: Value) -> Value:
-        if a.shape[1] != b.shape[0]:
+        """MATMUL over the last two dimensions; leading batch dimensions broadcast right-aligned
+        (Tensor.java:1075-1096)."""
+        if len(a.shape) < 2 or len(b.shape) < 2 or a.shape[-1] != b.shape[-2]:
             raise ValueError("MATMUL contraction extents differ")
-        return self._node("MATMUL", [a, b], F32, (a.shape[0], b.shape[1]))
+        batch = _broadcast(tuple(a.shape[:-2]), tuple(b.shape[:-2]))
+        return self._node("MATMUL", [a, b], F32, tuple(batch) + (a.shape[-2], b.shape[-1]))
+
+    def swap_last_two(self, x: Value) -> Value:
+        """PERMUTE exchanging the final two axes (LinearAlgebraGradientRules.swapLastTwo)."""
+        axes = list(range(len(x.shape)))
+        axes[-2], axes[-1] = axes[-1], axes[-2]
+        return self.permute(x, axes)
+
+    def matmul_backward(self, a: Value, b: Value, upstream: Value):
+        """MATMUL gradient rule for operands of rank two and above (LinearAlgebraGradientRules.java:97-104,
+        normalize :121-131): g x swapLastTwo(b) and swapLastTwo(a) x g, each summed back over the batch
+        dimensions its operand was broadcast along.  Returns (da, db)."""
+        da = self.matmul(upstream, self.swap_last_two(b))
+        db = self.matmul(self.swap_last_two(a), upstream)
+        if tuple(da.shape) != tuple(a.shape):
+            da = self.sum_to_shape(da, a.shape)
+        if tuple(db.shape) != tuple(b.shape):
+            db = self.sum_to_shape(db, b.shape)
+        return da, db
 
     def _binary(self, op: str, a: Value, b: Value) -> Value:
         return self._node(op, [a, b], BOOL if op in ("GT", "LT", "EQ") else a.dtype, _broadcast(a.shape, b.shape))

@@ -102,11 +102,21 @@ def test_malformed_images_are_rejected(lib):
     a = b.feed(program.I32, (4, 4)); c = b.feed(program.I32, (4, 4))
     b.publish(b._node("MATMUL", [a, c], program.F32, (4, 4)))
     assert status_of(b.build()) == 13
-    # rank-3 MATMUL is outside capability
+    # MATMUL operands above rank 4 are outside capability; batch dimensions that do not broadcast are malformed
     b = program.GraphBuilder()
-    a = b.feed(program.F32, (2, 4, 4)); c = b.feed(program.F32, (2, 4, 4))
-    b.publish(b._node("MATMUL", [a, c], program.F32, (2, 4, 4)))
+    a = b.feed(program.F32, (2, 2, 2, 4, 4)); c = b.feed(program.F32, (4, 4))
+    b.publish(b._node("MATMUL", [a, c], program.F32, (2, 2, 2, 4, 4)))
     assert status_of(b.build()) == 8
+    b = program.GraphBuilder()
+    a = b.feed(program.F32, (2, 4, 4)); c = b.feed(program.F32, (3, 4, 4))
+    b.publish(b._node("MATMUL", [a, c], program.F32, (2, 4, 4)))
+    assert status_of(b.build()) == 9
+    # a batched product lowers to one launch per slice, a collapsible one to a single launch
+    b = program.GraphBuilder()
+    a = b.feed(program.F32, (2, 4, 4)); c = b.feed(program.F32, (2, 4, 4)); w = b.feed(program.F32, (4, 4))
+    b.publish(b.matmul(a, c)); b.publish(b.matmul(a, w))
+    plan = native.describe(b.build())
+    assert plan.count("gemm") == 3 and "m=8 n=4 k=4" in plan
     # use before definition
     b = program.GraphBuilder()
     a = b.feed(program.F32, (4,))

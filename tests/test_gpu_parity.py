@@ -203,6 +203,80 @@ def test_tensor_core_special_values(ctx):
     assert np.allclose(c[9], 3.4e38 + 31, rtol=1e-6) and np.all(c[0] == 32) and np.all(np.isfinite(c[9]))
 
 
+# ---- MATMUL operands with batch dimensions ---------------------------------------------------------
+def test_linear_over_batch_and_time_with_its_gradients(ctx, oracle):
+    # Linear applied to [batch, time, features] (Tensor.java:1075-1096): the left operand's leading
+    # dimensions collapse into rows over the shared weight; the weight gradient is one product per batch
+    # slice summed back over the batch (LinearAlgebraGradientRules.java:97-131).  Exact engine: every
+    # product cell is the reference's ascending-k chain, bit for bit; the batch and bias sums are
+    # binary64 sums rounded once against the reference's exactly rounded sums (1 ulp on rare ties)
+    batch, time, k, n = 4, 6, 32, 16
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((batch, time, k)).astype(np.float32)
+    w = rng.standard_normal((n, k)).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    up = rng.standard_normal((batch, time, n)).astype(np.float32)
+    g = GraphBuilder()
+    xv, wv, bv, uv = g.feed(F32, x.shape), g.feed(F32, w.shape), g.feed(F32, bias.shape), g.feed(F32, up.shape)
+    wt = g.permute(wv, (1, 0))
+    g.publish(g.add(g.matmul(xv, wt), bv))
+    dx, dwt = g.matmul_backward(xv, wt, uv)
+    g.publish(dx)
+    g.publish(g.permute(dwt, (1, 0)))
+    g.publish(g.sum_to_shape(uv, (n,)))
+    z, dxo, dwo, dbo = run_image(ctx, g, [x, w, bias, up], engine=1)
+    want_z = (oracle.matmul(x.reshape(-1, k), w.T) + bias).astype(np.float32).reshape(batch, time, n)
+    assert np.array_equal(z, want_z)
+    assert np.array_equal(dxo, oracle.matmul(up.reshape(-1, n), w).reshape(x.shape))
+    slices = np.stack([oracle.matmul(np.ascontiguousarray(x[b].T), up[b]) for b in range(batch)])
+    want_dw = oracle.colsum_exact(slices.reshape(batch, -1)).reshape(k, n).T
+    assert ulp_distance(dwo, want_dw).max() <= 1 and (dwo == want_dw).mean() > 0.99
+    want_db = oracle.colsum_exact(up.reshape(-1, n))
+    assert ulp_distance(dbo, want_db).max() <= 1
+
+
+def test_batched_matmul_slices_and_broadcast_batches(ctx, oracle):
+    # both operands with batch dimensions, and batch dimensions that broadcast ([2,1,..] x [3,..] -> [2,3,..]):
+    # one product per slice over views of the operands, exact engine, bit for bit
+    rng = np.random.default_rng(12)
+    a = rng.standard_normal((3, 5, 7)).astype(np.float32)
+    b = rng.standard_normal((3, 7, 9)).astype(np.float32)
+    a2 = rng.standard_normal((2, 1, 5, 7)).astype(np.float32)
+    g = GraphBuilder()
+    av, bv, a2v = g.feed(F32, a.shape), g.feed(F32, b.shape), g.feed(F32, a2.shape)
+    g.publish(g.matmul(av, bv))
+    g.publish(g.matmul(a2v, bv))
+    g.publish(g.matmul(av, g.swap_last_two(g.matmul(g.swap_last_two(av), av))))       # [3,5,7] x ([3,7,7])^T, a strided right operand
+    c, c2, c3 = run_image(ctx, g, [a, b, a2], engine=1)
+    assert np.array_equal(c, np.stack([oracle.matmul(a[i], b[i]) for i in range(3)]))
+    assert np.array_equal(c2, np.stack([np.stack([oracle.matmul(a2[i, 0], b[j]) for j in range(3)]) for i in range(2)]))
+    gram = [oracle.matmul(np.ascontiguousarray(a[i].T), a[i]) for i in range(3)]
+    assert np.array_equal(c3, np.stack([oracle.matmul(a[i], np.ascontiguousarray(gram[i].T)) for i in range(3)]))
+
+
+def test_batched_matmul_on_tensor_cores(ctx):
+    # the same lowering on the tcgen05 path: a collapsed [4, 256, 512] x [512, 256] product and a
+    # per-slice [2, 256, 384] x [2, 384, 256] product, within the stated tensor-core bound
+    rng = np.random.default_rng(13)
+    x = rng.standard_normal((4, 256, 512)).astype(np.float32)
+    w = rng.standard_normal((512, 256)).astype(np.float32)
+    p = rng.standard_normal((2, 256, 384)).astype(np.float32)
+    q = rng.standard_normal((2, 384, 256)).astype(np.float32)
+    g = GraphBuilder()
+    xv, wv, pv, qv = g.feed(F32, x.shape), g.feed(F32, w.shape), g.feed(F32, p.shape), g.feed(F32, q.shape)
+    g.publish(g.matmul(xv, wv))
+    g.publish(g.matmul(pv, qv))
+    image_plan = native.describe(g.build())
+    c, d = run_image(ctx, g, [x, w, p, q], engine=2)
+    x64, w64 = x.reshape(-1, 512).astype(np.float64), w.astype(np.float64)
+    ref = x64 @ w64
+    assert np.all(np.abs(c.reshape(-1, 256) - ref) <= tc_bound(x64, w64, ref))
+    for i in range(2):
+        p64, q64 = p[i].astype(np.float64), q[i].astype(np.float64)
+        assert np.all(np.abs(d[i] - p64 @ q64) <= tc_bound(p64, q64, p64 @ q64))
+    assert image_plan.count("gemm") == 3 and "m=1024 n=256 k=512" in image_plan
+
+
 # ---- row kernels --------------------------------------------------------------------------------
 def test_softmax_known_answers_and_special_rows(ctx, oracle):
     rows = np.array([[1, 2, 3, 0], [1000, 1000, -np.inf, -np.inf], [-np.inf, 1000, 0, 0], [0, -1000, -1000, -1000],
