@@ -75,8 +75,9 @@ __device__ __forceinline__ float exp_shifted(float x) {
     q = fmaf(q, r, 1.6666667163e-1f);
     q = fmaf(q, r, 0.5f);
     float res = __fadd_rn(fmaf(__fmul_rn(r, r), q, r), 1.0f);
-    int biased = __float_as_int(t) - (0x4b400000 - 127);        // n + 127 >= 1, n read from the low bits of t
-    return __fmul_rn(res, __int_as_float(biased << 23));
+    // scaling by 2^n in the exponent field: the low bits of t hold n (the magic constant's own bits
+    // shift out), and res * 2^n stays normal because the clamp keeps n >= -126 with res >= 1 there
+    return __int_as_float(__float_as_int(res) + (__float_as_int(t) << 23));
 }
 
 __device__ __forceinline__ float java_max(float a, float b) {   // Math.max: NaN wins, +0 above -0
@@ -628,9 +629,11 @@ __global__ void __launch_bounds__(kThreads, CHUNKS >= 8 ? 3 : 4) ce_rows_vec_ker
         // maximum (fmaxf skips NaN like the reference's plain '>' scan) and a probe that turns NaN
         // for any NaN or infinity in the row: x * 0 accumulates on the FMA pipe
         float mplain = __int_as_float(0xff800000), probe = 0.0f;
+        float m4[CHUNKS];                   // maximum of each 16-byte group, kept for the arg-max search
 #pragma unroll
         for (int j = 0; j < CHUNKS; j++) {
-            mplain = fmaxf(fmaxf(mplain, fmaxf(v[j].x, v[j].y)), fmaxf(v[j].z, v[j].w));
+            m4[j] = fmaxf(fmaxf(v[j].x, v[j].y), fmaxf(v[j].z, v[j].w));
+            mplain = fmaxf(mplain, m4[j]);
             probe = fmaf(v[j].x, 0.0f, probe); probe = fmaf(v[j].y, 0.0f, probe);
             probe = fmaf(v[j].z, 0.0f, probe); probe = fmaf(v[j].w, 0.0f, probe);
         }
@@ -642,14 +645,18 @@ __global__ void __launch_bounds__(kThreads, CHUNKS >= 8 ? 3 : 4) ce_rows_vec_ker
             continue;
         }
         if (ARGMAX) {       // finite row, non-zero maximum: the first column equal to it
+            // only a group whose own maximum is the row maximum can hold it: one compare per group,
+            // the four per-element compares only inside such a group
             uint32_t first = 0xffffffffu;
 #pragma unroll
             for (int j = CHUNKS - 1; j >= 0; j--) {
-                const uint32_t c4 = (uint32_t)(lane + 32 * j) * 4;
-                first = v[j].w == mplain ? c4 + 3 : first;
-                first = v[j].z == mplain ? c4 + 2 : first;
-                first = v[j].y == mplain ? c4 + 1 : first;
-                first = v[j].x == mplain ? c4 : first;
+                if (m4[j] == mplain) {
+                    const uint32_t c4 = (uint32_t)(lane + 32 * j) * 4;
+                    first = v[j].w == mplain ? c4 + 3 : first;
+                    first = v[j].z == mplain ? c4 + 2 : first;
+                    first = v[j].y == mplain ? c4 + 1 : first;
+                    first = v[j].x == mplain ? c4 : first;
+                }
             }
             first = warp_umin(first);
             if (lane == 0) argmax_out[r] = (int64_t)first;
