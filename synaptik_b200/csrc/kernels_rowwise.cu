@@ -615,6 +615,10 @@ __global__ void __launch_bounds__(kThreads, CHUNKS >= 8 ? 3 : 4) ce_rows_vec_ker
         float4 v[CHUNKS];
 #pragma unroll
         for (int j = 0; j < CHUNKS; j++) v[j] = lane + 32 * j < vec_cols ? row[lane + 32 * j] : make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+        // the row this warp takes next, asked into L2 now (one 128-byte line per lane): its loads then
+        // wait for L2 instead of HBM, which is what the six warps per scheduler could not hide
+        if (r + warps < rows && lane * 32 < cols)
+            asm volatile("prefetch.global.L2 [%0];" :: "l"(row_s + warps * cols + lane * 32));
         int64_t label = load_label<L>(labels, r);
         if (has_ignore && label == ignore) {
             // the ignore index is tested before the bounds and before the logits are read
