@@ -222,12 +222,25 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
     for (int i = 0; i < node_count; i++) {
         const Node &mm = g.nodes[i];
         if (mm.op != Op::MATMUL) continue;
-        if (g.values[mm.inputs[0]].shape.size() != 2 || g.values[mm.inputs[1]].shape.size() != 2) continue;   // batched: lowered per slice below
+        // A left operand with batch dimensions joins a group when it is stored dense (a dense feed or a
+        // value some kernel materialises), so that [batch.., rows, k] reads as [batch * rows, k] over the
+        // shared rank-2 right operand: Linear on [batch, time, features] keeps its fused epilogue.  Other
+        // batched products are lowered per slice further down.
+        if (g.values[mm.inputs[1]].shape.size() != 2) continue;
+        if (g.values[mm.inputs[0]].shape.size() != 2) {
+            const Value &left = g.values[mm.inputs[0]];
+            bool stored_dense = left.role == Role::FEED ? left.is_dense() : false;
+            if (left.role == Role::INTERMEDIATE && left.producer >= 0) {
+                Op producer = g.nodes[left.producer].op;
+                stored_dense = producer != Op::PERMUTE && producer != Op::EXPAND && producer != Op::EXPAND_DIMS && producer != Op::CONTIGUOUS;
+            }
+            if (!stored_dense) continue;
+        }
         LinearGroup lg;
         lg.matmul = i;
         lg.emit_at = i;
         int z = mm.outputs[0];
-        int64_t n = g.values[z].shape[1];
+        int64_t n = g.values[z].shape.back();
         if (g.values[z].publication < 0 && g.values[z].consumers.size() == 1) {
             int c = g.values[z].consumers[0];
             const Node &add = g.nodes[c];
@@ -272,6 +285,47 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
         linear.push_back(lg);
     }
 
+    // ---- weight gradient of a Linear over batch dimensions -------------------------------------
+    // SUM_TO_SHAPE(MATMUL(swapLastTwo(X), G), [k, n]) with X [batch.., rows, k] and G [batch.., rows, n]
+    // both stored dense is one product X^T G contracted over batch * rows.  The per-slice products and
+    // their sum over the batch are an unobservable single-use intermediate, so only the order of the
+    // additions changes; taken where the joined product runs on the tensor cores (the exact engine keeps
+    // the reference's per-slice chains).
+    auto stored_dense = [&](int v) {
+        const Value &val = g.values[v];
+        if (val.role == Role::FEED) return val.is_dense();
+        if (val.role != Role::INTERMEDIATE || val.producer < 0) return false;
+        Op producer = g.nodes[val.producer].op;
+        return producer != Op::PERMUTE && producer != Op::EXPAND && producer != Op::EXPAND_DIMS && producer != Op::CONTIGUOUS;
+    };
+    for (int i = 0; i < node_count; i++) {
+        const Node &sum = g.nodes[i];
+        if (sum.op != Op::SUM_TO_SHAPE || covered[i]) continue;
+        const Node *mm = mt.producer(sum.inputs[0], Op::MATMUL);
+        if (!mm || !mt.only_consumer(sum.inputs[0], i)) continue;
+        const Node *swap = mt.producer(mm->inputs[0], Op::PERMUTE);
+        if (!swap) continue;
+        const int x = swap->inputs[0], up = mm->inputs[1];
+        const std::vector<int64_t> &xs = g.values[x].shape, &us = g.values[up].shape;
+        const size_t r = xs.size();
+        if (r < 3 || us.size() != r || !stored_dense(x) || !stored_dense(up)) continue;
+        bool last_two = true;
+        for (size_t d = 0; d < r; d++) last_two &= swap->attr_i(d) == (int64_t)(d == r - 2 ? r - 1 : d == r - 1 ? r - 2 : d);
+        if (!last_two || !std::equal(xs.begin(), xs.end() - 1, us.begin())) continue;
+        if (g.values[sum.outputs[0]].elements() != xs.back() * us.back()) continue;      // all batch dimensions are summed
+        const int64_t contraction = g.values[x].elements() / xs.back();
+        if (choose_engine(xs.back(), us.back(), contraction) != GemmEngine::TENSOR_CORE) continue;
+        Step st;
+        st.kind = StepKind::GEMM; st.batch_contraction = true;
+        st.a = x; st.b = up; st.out = sum.outputs[0];
+        st.m = xs.back(); st.n = us.back(); st.k = contraction;
+        st.engine = GemmEngine::TENSOR_CORE;
+        st.nodes = {mt.producer_index(sum.inputs[0]), i};
+        covered[i] = 1; covered[mt.producer_index(sum.inputs[0])] = 1;
+        if (mt.only_consumer(mm->inputs[0], mt.producer_index(sum.inputs[0]))) { covered[mt.producer_index(mm->inputs[0])] = 1; st.nodes.push_back(mt.producer_index(mm->inputs[0])); }
+        emit_at[i].push_back(st);
+    }
+
     // ---- ReLU backward: WHERE(GT(z, 0), g, 0) ----------------------------------------------
     std::vector<Step> relu_backward_steps;
     for (int i = 0; i < node_count; i++) {
@@ -306,7 +360,7 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
         Step st;
         st.kind = StepKind::GEMM;
         st.a = mm.inputs[0]; st.b = mm.inputs[1];
-        st.m = g.values[st.a].shape[0]; st.k = g.values[st.a].shape[1]; st.n = g.values[st.b].shape[1];
+        st.k = g.values[st.a].shape.back(); st.m = g.values[st.a].elements() / st.k; st.n = g.values[st.b].shape[1];
         st.bias = lg.bias; st.mask = lg.mask; st.relu = lg.relu >= 0;
         st.out = lg.out; st.out2 = lg.out2;
         st.engine = choose_engine(st.m, st.n, st.k);
@@ -478,6 +532,33 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
         if (pending != emit_at.end()) for (Step st : pending->second) {
             for (int v : {st.out, st.out2, st.out3}) if (v >= 0) assign_output(v);
             if (st.kind == StepKind::GEMM) {
+                if (st.batch_contraction) {
+                    // X^T G over batch * rows: X read as [k, batch * rows] (contraction along its rows), G
+                    // as [batch * rows, n], the result as [k, n]
+                    for (int *v : {&st.a, &st.b, &st.out}) {
+                        View w = plan.views[*v];
+                        if (!w.dense()) { message = "batch contraction over a strided tensor"; return UNSUPPORTED_SHAPE; }
+                        const int64_t cols = v == &st.out ? st.n : w.shape.back();
+                        int64_t count = 1; for (auto d : w.shape) count *= d;
+                        if (v == &st.a) { w.shape = {cols, count / cols}; w.strides = {1, cols}; }
+                        else { w.shape = {count / cols, cols}; w.strides = {cols, 1}; }
+                        plan.views.push_back(w);
+                        *v = (int)plan.views.size() - 1;
+                    }
+                } else if (plan.views[st.a].shape.size() > 2) {
+                    // grouped product over a left operand with batch dimensions: every tensor of the step
+                    // is dense, so each reads as a matrix of batch * rows rows
+                    for (int *v : {&st.a, &st.out, &st.out2, &st.mask}) {
+                        if (*v < 0) continue;
+                        View w = plan.views[*v];
+                        if (!w.dense()) { message = "batched product over a strided tensor inside a fused group"; return UNSUPPORTED_SHAPE; }
+                        const int64_t cols = w.shape.back();
+                        int64_t count = 1; for (auto d : w.shape) count *= d;
+                        w.shape = {count / cols, cols}; w.strides = {cols, 1};
+                        plan.views.push_back(w);
+                        *v = (int)plan.views.size() - 1;
+                    }
+                }
                 Status gs = prepare_gemm(st);
                 if (gs != OK) return gs;
             } else if (st.kind == StepKind::CROSS_ENTROPY) {

@@ -55,6 +55,7 @@ struct Step {
     bool relu = false;
     int64_t m = 0, n = 0, k = 0;    // GEMM extents, or rows / cols of row kernels
     uint64_t scalar_bits = 0;       // SCALAR operand, ONE_HOT depth, loss reduction
+    bool batch_contraction = false; // GEMM: a and b are dense [batch.., rows, x] tensors contracted over batch * rows
     bool has_ignore = false;        // CROSS_ENTROPY: rows labelled `ignore` are skipped
     int64_t ignore = 0;
     GemmEngine engine = GemmEngine::EXACT_SIMT;

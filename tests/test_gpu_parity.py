@@ -235,6 +235,47 @@ def test_linear_over_batch_and_time_with_its_gradients(ctx, oracle):
     assert ulp_distance(dbo, want_db).max() <= 1
 
 
+def test_two_linear_layers_over_batch_and_time_keep_their_fused_epilogues(ctx, oracle):
+    # Linear -> ReLU -> Linear on [batch, time, features] with the whole backward pass: the products over
+    # the dense rank-3 activations stay in their fused groups (bias + ReLU epilogue, ReLU gate on dX),
+    # reading every tensor as [batch * time, features]; exact engine, so forward and dX are bit for bit
+    # the flat two-dimensional network; the weight gradients are per-slice products summed over the batch
+    batch, time, dims = 4, 6, [32, 16, 8]
+    rng = np.random.default_rng(14)
+    x = rng.standard_normal((batch, time, dims[0])).astype(np.float32)
+    w1 = rng.standard_normal((dims[1], dims[0])).astype(np.float32) * 0.3
+    b1 = rng.standard_normal(dims[1]).astype(np.float32) * 0.1
+    w2 = rng.standard_normal((dims[2], dims[1])).astype(np.float32) * 0.3
+    b2 = rng.standard_normal(dims[2]).astype(np.float32) * 0.1
+    up = rng.standard_normal((batch, time, dims[2])).astype(np.float32)
+    g = GraphBuilder()
+    xv, w1v, b1v, w2v, b2v, uv = (g.feed(F32, a.shape) for a in (x, w1, b1, w2, b2, up))
+    wt1, z1 = g.linear(xv, w1v, b1v)
+    a1 = g.relu(z1)
+    wt2, z2 = g.linear(a1, w2v, b2v)
+    g.publish(z2)
+    da1, dwt2 = g.matmul_backward(a1, wt2, uv)
+    dz1 = g.relu_backward(z1, da1)
+    dx, dwt1 = g.matmul_backward(xv, wt1, dz1)
+    for v in (dx, g.permute(dwt1, (1, 0)), g.permute(dwt2, (1, 0)), g.sum_to_shape(dz1, (dims[1],))):
+        g.publish(v)
+    plan = native.describe(g.build())
+    assert "bias relu nodes=[MATMUL,ADD,RELU]" in plan and "relu_gate" in plan
+    out, dxo, dw1o, dw2o, db1o = run_image(ctx, g, [x, w1, b1, w2, b2, up], engine=1)
+    flat = x.reshape(-1, dims[0])
+    zf1, af1 = oracle.linear(flat, w1, b1, True)
+    zf2, _ = oracle.linear(af1, w2, b2, False)
+    assert np.array_equal(out.reshape(-1, dims[2]), zf2)
+    dzf1 = oracle.relu_backward(zf1, oracle.matmul(up.reshape(-1, dims[2]), w2))
+    assert np.array_equal(dxo.reshape(-1, dims[0]), oracle.matmul(dzf1, w1))
+    dz3, a3 = dzf1.reshape(batch, time, -1), af1.reshape(batch, time, -1)
+    want1 = oracle.colsum_exact(np.stack([oracle.matmul(np.ascontiguousarray(x[b].T), dz3[b]) for b in range(batch)]).reshape(batch, -1))
+    want2 = oracle.colsum_exact(np.stack([oracle.matmul(np.ascontiguousarray(a3[b].T), up[b]) for b in range(batch)]).reshape(batch, -1))
+    assert ulp_distance(dw1o, want1.reshape(dims[0], dims[1]).T).max() <= 1
+    assert ulp_distance(dw2o, want2.reshape(dims[1], dims[2]).T).max() <= 1
+    assert ulp_distance(db1o, oracle.colsum_exact(dzf1)).max() <= 1
+
+
 def test_batched_matmul_slices_and_broadcast_batches(ctx, oracle):
     # both operands with batch dimensions, and batch dimensions that broadcast ([2,1,..] x [3,..] -> [2,3,..]):
     # one product per slice over views of the operands, exact engine, bit for bit
@@ -266,15 +307,23 @@ def test_batched_matmul_on_tensor_cores(ctx):
     xv, wv, pv, qv = g.feed(F32, x.shape), g.feed(F32, w.shape), g.feed(F32, p.shape), g.feed(F32, q.shape)
     g.publish(g.matmul(xv, wv))
     g.publish(g.matmul(pv, qv))
+    # the weight gradient of the first product for an upstream gradient `pv`-shaped like its result:
+    # per-slice products summed over the batch, joined into one contraction over batch * rows
+    up = rng.standard_normal((4, 256, 256)).astype(np.float32)
+    uv = g.feed(F32, up.shape)
+    g.publish(g.sum_to_shape(g.matmul(g.swap_last_two(xv), uv), (512, 256)))
     image_plan = native.describe(g.build())
-    c, d = run_image(ctx, g, [x, w, p, q], engine=2)
+    c, d, dw = run_image(ctx, g, [x, w, p, q, up], engine=2)
+    xt64, up64 = x.reshape(-1, 512).astype(np.float64).T, up.reshape(-1, 256).astype(np.float64)
+    assert np.all(np.abs(dw - xt64 @ up64) <= tc_bound(xt64, up64, xt64 @ up64))
+    assert "m=512 n=256 k=1024" in image_plan and "SUM_TO_SHAPE" in image_plan.split("m=512 n=256 k=1024")[1].split("\n")[0]
     x64, w64 = x.reshape(-1, 512).astype(np.float64), w.astype(np.float64)
     ref = x64 @ w64
     assert np.all(np.abs(c.reshape(-1, 256) - ref) <= tc_bound(x64, w64, ref))
     for i in range(2):
         p64, q64 = p[i].astype(np.float64), q[i].astype(np.float64)
         assert np.all(np.abs(d[i] - p64 @ q64) <= tc_bound(p64, q64, p64 @ q64))
-    assert image_plan.count("gemm") == 3 and "m=1024 n=256 k=512" in image_plan
+    assert image_plan.count("gemm") == 4 and "m=1024 n=256 k=512" in image_plan
 
 
 # ---- row kernels --------------------------------------------------------------------------------
