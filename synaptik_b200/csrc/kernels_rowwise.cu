@@ -405,32 +405,108 @@ __global__ void __launch_bounds__(kThreads) argmax_kernel(const float *__restric
 // logarithm of the sum, never of the rounded quotient, so a far-away column keeps its finite
 // distance).  The reference's Kahan-compensated binary32 sum is replaced by a binary64 sum
 // rounded once (both lie within an ulp of the exact sum).
+// One row, any values and any width (three passes over the row in memory).
+template <bool LOG>
+__device__ __forceinline__ void softmax_row_careful(const float *__restrict__ row, float *o, int64_t cols, int lane) {
+    float maximum = __int_as_float(0xff800000);
+    int has_ninf = 0;
+    for (int64_t c = lane; c < cols; c += 32) { float v = row[c]; maximum = java_max(maximum, v); has_ninf |= v == __int_as_float(0xff800000); }
+    maximum = warp_max_java(maximum);
+    has_ninf = __any_sync(0xffffffffu, has_ninf);
+    if (maximum == __int_as_float(0x7f800000)) {
+        const float rest = LOG ? __int_as_float(0xff800000) : 0.0f;
+        for (int64_t c = lane; c < cols; c += 32) o[c] = row[c] == maximum ? __int_as_float(0x7fc00000) : rest;
+        return;
+    }
+    const bool unshifted = has_ninf && !(maximum != maximum);
+    float sum;
+    if (unshifted) {
+        // a row with -inf is not shifted and the reference adds its exponentials in plain ascending
+        // binary32 order, without compensation (CpuSoftmaxReferenceKernel.java:124-131): one lane follows
+        // that order, since the rounding error of such a sum is part of the reference's result
+        maximum = 0.0f;
+        float s = 0.0f;
+        if (lane == 0) for (int64_t c = 0; c < cols; c++) s = __fadd_rn(s, exp_accurate(__fsub_rn(row[c], maximum)));
+        sum = __shfl_sync(0xffffffffu, s, 0);
+    } else {
+        double acc = 0.0;
+        for (int64_t c = lane; c < cols; c += 32) acc += (double)exp_accurate(__fsub_rn(row[c], maximum));
+        sum = (float)warp_sum(acc);
+    }
+    if (LOG) {
+        const float logarithm = (float)log((double)sum);
+        for (int64_t c = lane; c < cols; c += 32) o[c] = __fsub_rn(__fsub_rn(row[c], maximum), logarithm);
+    } else {
+        for (int64_t c = lane; c < cols; c += 32) o[c] = __fdiv_rn(exp_accurate(__fsub_rn(row[c], maximum)), sum);
+    }
+}
+
 template <bool LOG>
 __global__ void softmax_kernel(const float *__restrict__ x, float *out, int64_t rows, int64_t cols) {
     int lane = threadIdx.x & 31;
     int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t r = warp; r < rows; r += warps) softmax_row_careful<LOG>(x + r * cols, out + r * cols, cols, lane);
+}
+
+// Rows of at most 1024 columns, 16-byte aligned: the row is read once into registers (one warp per
+// row, CHUNKS 16-byte groups per lane), finite rows take the exponential once per element
+// (exp_shifted, within 1.03 ulp), the row sum in binary64, and the quotient as one reciprocal per row
+// plus a remainder-corrected product per element; rows with an infinity or NaN go to the careful
+// routine with the reference's branches.  The next row of the warp is asked into L2 meanwhile.
+template <int CHUNKS, bool LOG>
+__global__ void __launch_bounds__(kThreads, CHUNKS >= 8 ? 3 : 4) softmax_rows_vec_kernel(const float *__restrict__ x, float *out, int64_t rows, int cols) {
+    int lane = threadIdx.x & 31;
+    int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int vec_cols = cols >> 2;
     for (int64_t r = warp; r < rows; r += warps) {
-        const float *row = x + r * cols;
-        float *o = out + r * cols;
-        float maximum = __int_as_float(0xff800000);
-        int has_ninf = 0;
-        for (int64_t c = lane; c < cols; c += 32) { float v = row[c]; maximum = java_max(maximum, v); has_ninf |= v == __int_as_float(0xff800000); }
-        maximum = warp_max_java(maximum);
-        has_ninf = __any_sync(0xffffffffu, has_ninf);
-        if (maximum == __int_as_float(0x7f800000)) {
-            const float rest = LOG ? __int_as_float(0xff800000) : 0.0f;
-            for (int64_t c = lane; c < cols; c += 32) o[c] = row[c] == maximum ? __int_as_float(0x7fc00000) : rest;
+        const float *row_s = x + r * cols;
+        const float4 *row = reinterpret_cast<const float4 *>(row_s);
+        float4 v[CHUNKS];
+#pragma unroll
+        for (int j = 0; j < CHUNKS; j++) v[j] = lane + 32 * j < vec_cols ? row[lane + 32 * j] : make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+        if (r + warps < rows && lane * 32 < cols)
+            asm volatile("prefetch.global.L2 [%0];" :: "l"(row_s + warps * cols + lane * 32));
+        float maximum = __int_as_float(0xff800000), probe = 0.0f;
+#pragma unroll
+        for (int j = 0; j < CHUNKS; j++) {
+            maximum = fmaxf(fmaxf(maximum, fmaxf(v[j].x, v[j].y)), fmaxf(v[j].z, v[j].w));
+            probe = fmaf(v[j].x, 0.0f, probe); probe = fmaf(v[j].y, 0.0f, probe);
+            probe = fmaf(v[j].z, 0.0f, probe); probe = fmaf(v[j].w, 0.0f, probe);
+        }
+        maximum = warp_max_plain(maximum);
+        // rare: an infinity or NaN in the row, or a zero maximum whose sign reaches a LOG_SOFTMAX result
+        if (__any_sync(0xffffffffu, probe != probe) || (LOG && maximum == 0.0f)) {
+            softmax_row_careful<LOG>(row_s, out + r * cols, cols, lane);
             continue;
         }
-        if (has_ninf && !(maximum != maximum)) maximum = 0.0f;
         double acc = 0.0;
-        for (int64_t c = lane; c < cols; c += 32) acc += (double)exp_accurate(__fsub_rn(row[c], maximum));
-        float sum = (float)warp_sum(acc);
+#pragma unroll
+        for (int j = 0; j < CHUNKS; j++) {
+            const float s0 = __fsub_rn(v[j].x, maximum), s1 = __fsub_rn(v[j].y, maximum), s2 = __fsub_rn(v[j].z, maximum), s3 = __fsub_rn(v[j].w, maximum);
+            const float e0 = exp_shifted(s0), e1 = exp_shifted(s1), e2 = exp_shifted(s2), e3 = exp_shifted(s3);
+            if (lane + 32 * j < vec_cols) acc += (double)__fadd_rn(__fadd_rn(e0, e1), __fadd_rn(e2, e3));
+            v[j] = LOG ? make_float4(s0, s1, s2, s3) : make_float4(e0, e1, e2, e3);
+        }
+        const float sum = (float)warp_sum(acc);            // finite, at least 1: the maximum contributes exp(0)
+        float4 *o = reinterpret_cast<float4 *>(out + r * cols);
         if (LOG) {
             const float logarithm = (float)log((double)sum);
-            for (int64_t c = lane; c < cols; c += 32) o[c] = __fsub_rn(__fsub_rn(row[c], maximum), logarithm);
+#pragma unroll
+            for (int j = 0; j < CHUNKS; j++)
+                if (lane + 32 * j < vec_cols)
+                    o[lane + 32 * j] = make_float4(__fsub_rn(v[j].x, logarithm), __fsub_rn(v[j].y, logarithm), __fsub_rn(v[j].z, logarithm), __fsub_rn(v[j].w, logarithm));
         } else {
-            for (int64_t c = lane; c < cols; c += 32) o[c] = __fdiv_rn(exp_accurate(__fsub_rn(row[c], maximum)), sum);
+            const float rcp = __frcp_rn(sum);
+#pragma unroll
+            for (int j = 0; j < CHUNKS; j++) {
+                float e[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    float p = __fmul_rn(e[q], rcp);
+                    e[q] = fmaf(fmaf(-p, sum, e[q]), rcp, p);
+                }
+                if (lane + 32 * j < vec_cols) o[lane + 32 * j] = make_float4(e[0], e[1], e[2], e[3]);
+            }
         }
     }
 }
@@ -1005,8 +1081,16 @@ cudaError_t argmax_rows(cudaStream_t s, const float *x, int64_t *out, int64_t ro
 
 cudaError_t softmax_rows(cudaStream_t s, const float *x, float *out, int64_t rows, int64_t cols, bool log_kind) {
     if (rows == 0) return cudaSuccess;
-    if (log_kind) softmax_kernel<true><<<grid_for(rows, kThreads / 32), kThreads, 0, s>>>(x, out, rows, cols);
-    else softmax_kernel<false><<<grid_for(rows, kThreads / 32), kThreads, 0, s>>>(x, out, rows, cols);
+    const int grid = grid_for(rows, kThreads / 32);
+    const bool vec = (cols & 3) == 0 && cols >= 128 && cols <= 1024 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0;
+#define SYN_SOFTMAX_VEC(C) do { if (log_kind) softmax_rows_vec_kernel<C, true><<<grid, kThreads, 0, s>>>(x, out, rows, (int)cols); \
+                                else softmax_rows_vec_kernel<C, false><<<grid, kThreads, 0, s>>>(x, out, rows, (int)cols); } while (0)
+    if (vec) {
+        const int chunks = (int)((cols / 4 + 31) / 32);
+        if (chunks <= 1) SYN_SOFTMAX_VEC(1); else if (chunks <= 2) SYN_SOFTMAX_VEC(2); else if (chunks <= 4) SYN_SOFTMAX_VEC(4); else SYN_SOFTMAX_VEC(8);
+    } else if (log_kind) softmax_kernel<true><<<grid, kThreads, 0, s>>>(x, out, rows, cols);
+    else softmax_kernel<false><<<grid, kThreads, 0, s>>>(x, out, rows, cols);
+#undef SYN_SOFTMAX_VEC
     return cudaGetLastError();
 }
 

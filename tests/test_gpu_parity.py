@@ -378,6 +378,41 @@ def test_log_softmax_known_answers_and_special_rows(ctx, oracle):
 
 
 @pytest.mark.parametrize("log_kind", [False, True])
+@pytest.mark.parametrize("cols", [128, 256, 500, 1000, 1024])
+def test_softmax_wide_rows_with_special_values(ctx, oracle, log_kind, cols):
+    # rows wide enough for the register-cached kernel (every group count), with rows that hold +inf,
+    # -inf, NaN, a zero maximum with both signed zeros, and a far-away column
+    rng = np.random.default_rng(cols + log_kind)
+    x = (rng.standard_normal((40, cols)) * 3).astype(np.float32)
+    x[1, 5] = np.inf
+    x[2, 7] = -np.inf
+    x[3, 9] = np.nan
+    x[4, 3], x[4, 100] = np.inf, np.inf
+    x[5, :] = -1000.0; x[5, 11], x[5, 12] = 0.0, -0.0
+    x[6, :] = -np.abs(x[6, :]) - 1.0; x[6, 20] = -0.0
+    x[7, 64] = 90.0
+    x[8, 3], x[8, 4] = -np.inf, np.nan
+    g = GraphBuilder()
+    v = g.feed(F32, x.shape)
+    g.publish(g.log_softmax(v, 1) if log_kind else g.softmax(v, 1))
+    (y,) = run_image(ctx, g, [x])
+    expect = oracle.log_softmax(x) if log_kind else oracle.softmax(x)
+    assert np.array_equal(np.isnan(y), np.isnan(expect))
+    inf = np.isinf(expect)
+    assert np.array_equal(y[inf], expect[inf])
+    finite = np.isfinite(expect)
+    if log_kind:
+        assert np.all(np.abs(y[finite] - expect[finite]) <= 4 * np.spacing(np.maximum(1, np.abs(expect[finite])).astype(np.float32)))
+        zero = finite & (expect == 0)
+        assert np.array_equal(np.signbit(y[zero]), np.signbit(expect[zero]))
+    else:
+        # 4 ulp; where the reference's quotient is subnormal or zero the device's clamped exponential
+        # leaves at most 1.2e-38 absolute
+        bad = finite & ~((ulp_distance(y, expect) <= 4) | (np.abs(y - expect) <= 1.2e-38))
+        assert not bad.any(), [(int(r), int(c), float(x[r, c]), float(y[r, c]), float(expect[r, c])) for r, c in np.argwhere(bad)[:6]]
+
+
+@pytest.mark.parametrize("log_kind", [False, True])
 def test_softmax_gradient_node_lists(ctx, oracle, log_kind):
     # ReductionGradientRules.java:84-90, executed node by node on the stored forward result
     rng = np.random.default_rng(3 + log_kind)
