@@ -358,6 +358,14 @@ def run_kernel_case(args):
         work = (2.0 if args.forward_only else 6.0) * m * k * n
         unit, denom, bound_kind = "TFLOP/s", peak_data["bf16_tflops"] / 6.0, "tensor"
         name = f"dense_layer_{'fwd' if args.forward_only else 'fwd_bwd'}_m{m}_k{k}_n{n}"
+    elif args.case == "argmax":
+        rows, classes = args.m, args.n
+        logits = g.feed(F32, (rows, classes))
+        g.publish(g.arg_max(logits, 1))
+        feeds = [(rng.standard_normal((rows, classes)) * 2).astype(np.float32)]
+        work = 4.0 * rows * classes + 8.0 * rows                 # read the logits, write one INT64 index per row
+        unit, denom, bound_kind = "GB/s", peak_data["hbm_gbs"], "hbm"
+        name = f"argmax_rows{rows}_classes{classes}"
     elif args.case in ("softmax", "log_softmax"):
         rows, classes = args.m, args.n
         logits = g.feed(F32, (rows, classes))
@@ -422,7 +430,8 @@ def run_kernel_case(args):
                 kernel_ms += t
     else:
         # the whole step is this one launch: its average duration is the timed region over the launches
-        kernel, kernel_work, kernel_ms = ("ce_rows_vec_kernel" if args.case == "ce" else "softmax_rows_vec_kernel"), work, ms / args.steps
+        kernel = {"ce": "ce_rows_vec_kernel", "argmax": "argmax_vec_kernel"}.get(args.case, "softmax_rows_vec_kernel")
+        kernel_work, kernel_ms = work, ms / args.steps
     achieved = kernel_work / (kernel_ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9) if kernel_ms > 0 else 0.0
     line = {"metric": f"{args.case}_{unit}", "value": rate, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 1),
             "ms_per_step": ms / args.steps, "median_ms_per_step": median_ms,
@@ -441,7 +450,7 @@ def run_kernel_case(args):
 
 def main():
     parser = argparse.ArgumentParser()
-    parser.add_argument("--case", default="train", choices=["train", "gemm", "ce", "softmax", "log_softmax"])
+    parser.add_argument("--case", default="train", choices=["train", "gemm", "ce", "softmax", "log_softmax", "argmax"])
     parser.add_argument("--m", type=int, default=16384)
     parser.add_argument("--k", type=int, default=4096)
     parser.add_argument("--n", type=int, default=4096)

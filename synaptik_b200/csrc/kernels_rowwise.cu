@@ -321,32 +321,30 @@ __device__ __forceinline__ uint32_t warp_umin(uint32_t v) {
 // it.  Rows with a NaN or a zero maximum take the total-order key so that NaN wins and -0 < +0.
 template <int CHUNKS>
 __device__ __forceinline__ int64_t warp_row_argmax(const float4 (&v)[CHUNKS], int vec_cols, int lane) {
-    float m = __int_as_float(0xff800000);
-    uint32_t magnitude = 0;
+    // groups past the row's end hold -FLT_MAX (the caller pads): they never win and never flag
+    float m = __int_as_float(0xff800000), probe = 0.0f;
+    float m4[CHUNKS];                       // maximum of each 16-byte group
 #pragma unroll
     for (int j = 0; j < CHUNKS; j++) {
-        if (lane + 32 * j < vec_cols) {
-            const float e[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
-#pragma unroll
-            for (int q = 0; q < 4; q++) {
-                m = fmaxf(m, e[q]);
-                uint32_t a = __float_as_uint(e[q]) & 0x7fffffffu;
-                magnitude = a > magnitude ? a : magnitude;
-            }
-        }
+        m4[j] = fmaxf(fmaxf(v[j].x, v[j].y), fmaxf(v[j].z, v[j].w));
+        m = fmaxf(m, m4[j]);
+        // x * 0 accumulates on the FMA pipe and turns NaN for any NaN or infinity in the row
+        probe = fmaf(v[j].x, 0.0f, probe); probe = fmaf(v[j].y, 0.0f, probe);
+        probe = fmaf(v[j].z, 0.0f, probe); probe = fmaf(v[j].w, 0.0f, probe);
     }
     m = warp_max_plain(m);
-    magnitude = warp_umax(magnitude);
-    if (magnitude <= 0x7f800000u && m != 0.0f) {
+    if (!__any_sync(0xffffffffu, probe != probe) && m != 0.0f) {
+        // finite row, non-zero maximum: the first column equal to it; only a group whose own maximum
+        // is the row maximum is looked into
         uint32_t first = 0xffffffffu;
 #pragma unroll
         for (int j = CHUNKS - 1; j >= 0; j--) {
-            const int c = lane + 32 * j;
-            if (c < vec_cols) {
-                if (v[j].w == m) first = (uint32_t)(c * 4 + 3);
-                if (v[j].z == m) first = (uint32_t)(c * 4 + 2);
-                if (v[j].y == m) first = (uint32_t)(c * 4 + 1);
-                if (v[j].x == m) first = (uint32_t)(c * 4);
+            if (m4[j] == m) {
+                const uint32_t c4 = (uint32_t)(lane + 32 * j) * 4;
+                first = v[j].w == m ? c4 + 3 : first;
+                first = v[j].z == m ? c4 + 2 : first;
+                first = v[j].y == m ? c4 + 1 : first;
+                first = v[j].x == m ? c4 : first;
             }
         }
         return (int64_t)warp_umin(first);
@@ -377,7 +375,10 @@ __global__ void __launch_bounds__(kThreads) argmax_vec_kernel(const float *__res
         const float4 *row = reinterpret_cast<const float4 *>(x + r * cols);
         float4 v[CHUNKS];
 #pragma unroll
-        for (int j = 0; j < CHUNKS; j++) if (lane + 32 * j < vec_cols) v[j] = row[lane + 32 * j];
+        for (int j = 0; j < CHUNKS; j++) v[j] = lane + 32 * j < vec_cols ? row[lane + 32 * j] : make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+        // the row this warp takes next, asked into L2 meanwhile (one 128-byte line per lane)
+        if (r + warps < rows && lane * 32 < cols)
+            asm volatile("prefetch.global.L2 [%0];" :: "l"(x + (r + warps) * cols + lane * 32));
         int64_t best = warp_row_argmax<CHUNKS>(v, vec_cols, lane);
         if (lane == 0) out[r] = best;
     }
