@@ -307,10 +307,6 @@ __device__ __forceinline__ unsigned long long warp_best(unsigned long long v) {
     return v;
 }
 
-__device__ __forceinline__ uint32_t warp_umax(uint32_t v) {
-    for (int o = 16; o > 0; o >>= 1) { uint32_t u = __shfl_xor_sync(0xffffffffu, v, o); v = u > v ? u : v; }
-    return v;
-}
 __device__ __forceinline__ uint32_t warp_umin(uint32_t v) {
     for (int o = 16; o > 0; o >>= 1) { uint32_t u = __shfl_xor_sync(0xffffffffu, v, o); v = u < v ? u : v; }
     return v;

@@ -48,7 +48,6 @@ namespace {
 
 struct Reader {
     const uint8_t *p; uint32_t size;
-    bool in(uint64_t off, uint64_t len) const { return off <= size && len <= size - off; }
     uint32_t u32(uint64_t off) const { uint32_t v; std::memcpy(&v, p + off, 4); return v; }
     uint64_t u64(uint64_t off) const { uint64_t v; std::memcpy(&v, p + off, 8); return v; }
 };

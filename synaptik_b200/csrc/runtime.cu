@@ -964,7 +964,7 @@ int32_t synaptik_cuda_optimizer_create(void *context, int32_t kind, const double
         if (b->ctx != ctx || b->bytes < element_counts[i] * 4) { status = INCOMPATIBLE_RESOURCE; break; }
         o->params.push_back(b); o->counts.push_back(element_counts[i]);
         float *m = nullptr, *v = nullptr;
-        uint64_t bytes = element_counts[i] * 4 ? element_counts[i] * 4 : 4;
+        uint64_t bytes = element_counts[i] ? element_counts[i] * 4 : 4;
         if (need_m && (cudaMalloc(&m, bytes) != cudaSuccess || cudaMemsetAsync(m, 0, bytes, ctx->stream) != cudaSuccess)) status = ALLOCATION_FAILED;
         if (status == OK && need_v && (cudaMalloc(&v, bytes) != cudaSuccess || cudaMemsetAsync(v, 0, bytes, ctx->stream) != cudaSuccess)) status = ALLOCATION_FAILED;
         o->m.push_back(m); o->v.push_back(v);
@@ -1003,7 +1003,7 @@ static int32_t optimizer_enqueue(void *optimizer, int32_t mode, int32_t gradient
         // pending sums start at zero (TrainingParameter.java:103-109)
         for (size_t i = 0; i < o->params.size(); i++) {
             void *p = nullptr;
-            uint64_t bytes = o->counts[i] * 4 ? o->counts[i] * 4 : 4;
+            uint64_t bytes = o->counts[i] ? o->counts[i] * 4 : 4;
             if (cudaMalloc(&p, bytes) != cudaSuccess) { cudaGetLastError(); for (float *q : o->acc) cudaFree(q); o->acc.clear(); return ALLOCATION_FAILED; }
             cudaMemsetAsync(p, 0, bytes, o->ctx->stream);
             o->acc.push_back((float *)p);
@@ -1125,7 +1125,7 @@ static int32_t optimizer_state(void *optimizer, int32_t index, int32_t slot, voi
         }
         for (size_t i = 0; i < o->params.size(); i++) {
             void *p = nullptr;
-            uint64_t size = o->counts[i] * 4 ? o->counts[i] * 4 : 4;
+            uint64_t size = o->counts[i] ? o->counts[i] * 4 : 4;
             if (cudaMalloc(&p, size) != cudaSuccess) { cudaGetLastError(); for (float *q : o->acc) cudaFree(q); o->acc.clear(); return ALLOCATION_FAILED; }
             cudaMemsetAsync(p, 0, size, o->ctx->stream);
             o->acc.push_back((float *)p);
