@@ -358,6 +358,15 @@ def run_kernel_case(args):
         work = (2.0 if args.forward_only else 6.0) * m * k * n
         unit, denom, bound_kind = "TFLOP/s", peak_data["bf16_tflops"] / 6.0, "tensor"
         name = f"dense_layer_{'fwd' if args.forward_only else 'fwd_bwd'}_m{m}_k{k}_n{n}"
+    elif args.case == "dense_ce":
+        rows, classes = args.m, args.n
+        logits, target = g.feed(F32, (rows, classes)), g.feed(F32, (rows, classes))
+        g.publish(g.dense_cross_entropy(logits, target, "mean"))
+        weights = rng.random((rows, classes)).astype(np.float32)
+        feeds = [(rng.standard_normal((rows, classes)) * 2).astype(np.float32), weights / weights.sum(axis=1, keepdims=True)]
+        work = 8.0 * rows * classes + 4.0 * rows + 4.0           # read logits and target weights, row losses, the mean
+        unit, denom, bound_kind = "GB/s", peak_data["hbm_gbs"], "hbm"
+        name = f"dense_cross_entropy_rows{rows}_classes{classes}"
     elif args.case == "argmax":
         rows, classes = args.m, args.n
         logits = g.feed(F32, (rows, classes))
@@ -430,7 +439,7 @@ def run_kernel_case(args):
                 kernel_ms += t
     else:
         # the whole step is this one launch: its average duration is the timed region over the launches
-        kernel = {"ce": "ce_rows_vec_kernel", "argmax": "argmax_vec_kernel"}.get(args.case, "softmax_rows_vec_kernel")
+        kernel = {"ce": "ce_rows_vec_kernel", "argmax": "argmax_vec_kernel", "dense_ce": "dense_ce_rows_vec_kernel"}.get(args.case, "softmax_rows_vec_kernel")
         kernel_work, kernel_ms = work, ms / args.steps
     achieved = kernel_work / (kernel_ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9) if kernel_ms > 0 else 0.0
     line = {"metric": f"{args.case}_{unit}", "value": rate, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 1),
@@ -450,7 +459,7 @@ def run_kernel_case(args):
 
 def main():
     parser = argparse.ArgumentParser()
-    parser.add_argument("--case", default="train", choices=["train", "gemm", "ce", "softmax", "log_softmax", "argmax"])
+    parser.add_argument("--case", default="train", choices=["train", "gemm", "ce", "softmax", "log_softmax", "argmax", "dense_ce"])
     parser.add_argument("--m", type=int, default=16384)
     parser.add_argument("--k", type=int, default=4096)
     parser.add_argument("--n", type=int, default=4096)

@@ -572,6 +572,31 @@ def test_dense_cross_entropy_forward_and_gradient(ctx, oracle, rows, classes):
         assert np.all(grad[3] == 0.0)
 
 
+@pytest.mark.parametrize("cols", [128, 500, 1024])
+def test_dense_cross_entropy_wide_rows_with_special_logits(ctx, oracle, cols):
+    # rows wide enough for the register-cached kernel; rows whose logits hold +inf, -inf or NaN take the
+    # careful routine and must propagate exactly as the reference's loops do (a -inf logit under a zero
+    # weight is skipped, under a non-zero weight it gives +inf)
+    rng = np.random.default_rng(cols)
+    logits = (rng.standard_normal((24, cols)) * 2).astype(np.float32)
+    target = rng.random((24, cols)).astype(np.float32)
+    target[rng.random((24, cols)) < 0.5] = 0.0
+    logits[1, 5] = np.inf
+    logits[2, 7] = -np.inf; target[2, 7] = 0.0
+    logits[3, 9] = -np.inf; target[3, 9] = 0.25
+    logits[4, 11] = np.nan
+    g = GraphBuilder()
+    lv, tv = g.feed(F32, logits.shape), g.feed(F32, target.shape)
+    g.publish(g.dense_cross_entropy(lv, tv, "none"))
+    (loss,) = run_image(ctx, g, [logits, target])
+    with np.errstate(invalid="ignore", over="ignore"):
+        per_row, _ = oracle.dense_cross_entropy(logits, target, "none")
+    assert np.array_equal(np.isnan(loss), np.isnan(per_row)) and np.isnan(per_row[1]) and np.isnan(per_row[4])
+    assert loss[3] == np.inf and per_row[3] == np.inf and np.isfinite(loss[2])
+    finite = np.isfinite(per_row)
+    assert np.all(np.abs(loss[finite] - per_row[finite]) <= 2e-6 * np.abs(per_row[finite]))
+
+
 def test_dense_cross_entropy_known_answer(ctx, oracle):
     # MetalNormalizationLossNativeTest.java:59-68: logits (0, 0), target (2, 0), MEAN -> 2 ln 2
     g = GraphBuilder()
