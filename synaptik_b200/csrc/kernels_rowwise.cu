@@ -677,12 +677,14 @@ __device__ __noinline__ void ce_row_careful(const float *__restrict__ row, int64
 template <int CHUNKS, typename L, bool GRAD, bool ARGMAX>
 __global__ void __launch_bounds__(kThreads, CHUNKS >= 8 ? 3 : 4) ce_rows_vec_kernel(const float *__restrict__ logits, const void *__restrict__ labels,
         const float *__restrict__ seed, int64_t rows, int cols, float *row_loss, float *grad, int64_t *argmax_out, int *error_word,
-        int has_ignore, long long ignore) {
+        int has_ignore, long long ignore, int scale_mode) {
     int lane = threadIdx.x & 31;
     int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     const int vec_cols = cols >> 2;
-    const float scale = GRAD ? __fdiv_rn(seed ? seed[0] : 1.0f, (float)rows) : 0.0f;
+    // the cotangent each row's (p - onehot) is multiplied by: seed / rows (MEAN), seed (SUM), seed[r] (NONE)
+    const float uniform_scale = !GRAD ? 0.0f : scale_mode == 0 ? __fdiv_rn(seed ? seed[0] : 1.0f, (float)rows) : (seed ? seed[0] : 1.0f);
     for (int64_t r = warp; r < rows; r += warps) {
+        const float scale = (GRAD && scale_mode == 2) ? seed[r] : uniform_scale;
         const float *row_s = logits + r * cols;
         const float4 *row = reinterpret_cast<const float4 *>(row_s);
         float4 v[CHUNKS];
@@ -782,11 +784,12 @@ __global__ void __launch_bounds__(kThreads, CHUNKS >= 8 ? 3 : 4) ce_rows_vec_ker
 template <typename L>
 __global__ void ce_rows_generic_kernel(const float *__restrict__ logits, const void *__restrict__ labels, const float *__restrict__ seed,
         int64_t rows, int64_t cols, float *row_loss, float *grad, int64_t *argmax_out, int *error_word,
-        int has_ignore, long long ignore) {
+        int has_ignore, long long ignore, int scale_mode) {
     int lane = threadIdx.x & 31;
     int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-    float scale = grad ? __fdiv_rn(seed ? seed[0] : 1.0f, (float)rows) : 0.0f;
+    const float uniform_scale = !grad ? 0.0f : scale_mode == 0 ? __fdiv_rn(seed ? seed[0] : 1.0f, (float)rows) : (seed ? seed[0] : 1.0f);
     for (int64_t r = warp; r < rows; r += warps) {
+        const float scale = (grad && scale_mode == 2) ? seed[r] : uniform_scale;
         int64_t label = load_label<L>(labels, r);
         if (has_ignore && label == ignore) {
             if (lane == 0 && row_loss) row_loss[r] = 0.0f;
@@ -1234,12 +1237,13 @@ cudaError_t colsum_static(cudaStream_t s, int device, const float *g, int64_t ro
 
 cudaError_t cross_entropy(cudaStream_t s, const float *logits, DType label_type, const void *labels, const float *seed,
                           int64_t rows, int64_t cols, float *row_loss, float *loss_out, float *grad_out, int64_t *argmax_out, int *error_word,
-                          int sum_only, int has_ignore, int64_t ignore) {
+                          int sum_only, int has_ignore, int64_t ignore, int scale_mode) {
     if (rows == 0 || cols == 0) return cudaErrorInvalidValue;
+    if (scale_mode < 0 || scale_mode > 2 || (scale_mode == 2 && grad_out && !seed)) return cudaErrorInvalidValue;
     int grid = grid_for(rows, kThreads / 32);
     bool vec = (cols & 3) == 0 && cols >= 128 && cols <= 1024 && (((uintptr_t)logits | (uintptr_t)grad_out) & 15) == 0;
     bool i32 = label_type == DType::I32;
-#define SYN_CE_ARGS <<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, (int)cols, row_loss, grad_out, argmax_out, error_word, has_ignore, (long long)ignore)
+#define SYN_CE_ARGS <<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, (int)cols, row_loss, grad_out, argmax_out, error_word, has_ignore, (long long)ignore, scale_mode)
 #define SYN_CE_VEC2(C, L) do { if (grad_out && argmax_out) ce_rows_vec_kernel<C, L, true, true> SYN_CE_ARGS; \
                                else if (grad_out) ce_rows_vec_kernel<C, L, true, false> SYN_CE_ARGS; \
                                else if (argmax_out) ce_rows_vec_kernel<C, L, false, true> SYN_CE_ARGS; \
@@ -1248,8 +1252,8 @@ cudaError_t cross_entropy(cudaStream_t s, const float *logits, DType label_type,
     if (vec) {
         int chunks = (int)((cols / 4 + 31) / 32);
         if (chunks <= 1) SYN_CE_VEC(1); else if (chunks <= 2) SYN_CE_VEC(2); else if (chunks <= 4) SYN_CE_VEC(4); else SYN_CE_VEC(8);
-    } else if (i32) ce_rows_generic_kernel<int32_t><<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, cols, row_loss, grad_out, argmax_out, error_word, has_ignore, (long long)ignore);
-    else ce_rows_generic_kernel<int64_t><<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, cols, row_loss, grad_out, argmax_out, error_word, has_ignore, (long long)ignore);
+    } else if (i32) ce_rows_generic_kernel<int32_t><<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, cols, row_loss, grad_out, argmax_out, error_word, has_ignore, (long long)ignore, scale_mode);
+    else ce_rows_generic_kernel<int64_t><<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, cols, row_loss, grad_out, argmax_out, error_word, has_ignore, (long long)ignore, scale_mode);
 #undef SYN_CE_VEC
 #undef SYN_CE_VEC2
 #undef SYN_CE_ARGS

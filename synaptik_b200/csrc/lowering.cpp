@@ -109,6 +109,7 @@ struct CrossEntropyGroup {
     int reduction = 1;                      // of the forward loss node: 0 NONE, 1 MEAN, 2 SUM
     bool has_ignore = false;                // of the forward loss node
     int64_t ignore = 0;
+    int scale_mode = 0;                     // of the gradient chain: 0 seed / rows, 1 seed, 2 seed[row]
     std::set<int> nodes;
     int emit_at = -1;
 };
@@ -157,24 +158,39 @@ bool match_ce_backward(Matcher &mt, int mul_index, CrossEntropyGroup &ce) {
             labels = smax->inputs[0];
         }
         if (g.values[labels].shape.size() != 1 || g.values[labels].shape[0] != rows) continue;
-        // rhs: [EXPAND] <- EXPAND_DIMS(axis 1) <- DIV(EXPAND(seed), count)
+        // rhs: [EXPAND] <- EXPAND_DIMS(axis 1) <- the restored cotangent (LossGradientRules.restore):
+        // DIV(EXPAND(seed), count) for MEAN, EXPAND(seed) for SUM, the [rows] cotangent itself for NONE
         int scale = rhs;
         if (const Node *ex = mt.producer(scale, Op::EXPAND)) { nodes.insert(mt.producer_index(scale)); scale = ex->inputs[0]; }
         const Node *ed = mt.producer(scale, Op::EXPAND_DIMS);
         if (!ed || ed->attr_i(0) != 1) continue;
         nodes.insert(mt.producer_index(scale));
         scale = ed->inputs[0];
-        const Node *sdiv = mt.producer(scale, Op::DIV);
-        if (!sdiv) continue;
-        nodes.insert(mt.producer_index(scale));
-        int seed = sdiv->inputs[0], count = sdiv->inputs[1];
-        if (const Node *ex = mt.producer(seed, Op::EXPAND)) { nodes.insert(mt.producer_index(seed)); seed = ex->inputs[0]; }
-        if (g.values[seed].elements() != 1 || g.values[seed].dtype != DType::F32) continue;
-        // count is either already folded to the splat constant `rows` or SUM over ones
-        if (!mt.is_splat(count, (double)rows)) {
-            const Node *csum = mt.producer(count, Op::SUM);
-            if (!csum || csum->attr_i(0) != -1 || !mt.is_splat(csum->inputs[0], 1.0) || g.values[csum->inputs[0]].elements() != rows) continue;
-            nodes.insert(mt.producer_index(count));
+        int seed = -1, scale_mode = 0;
+        if (const Node *sdiv = mt.producer(scale, Op::DIV)) {
+            nodes.insert(mt.producer_index(scale));
+            seed = sdiv->inputs[0];
+            const int count = sdiv->inputs[1];
+            if (const Node *ex = mt.producer(seed, Op::EXPAND)) { nodes.insert(mt.producer_index(seed)); seed = ex->inputs[0]; }
+            if (g.values[seed].elements() != 1 || g.values[seed].dtype != DType::F32) continue;
+            // count is either already folded to the splat constant `rows` or SUM over ones
+            if (!mt.is_splat(count, (double)rows)) {
+                const Node *csum = mt.producer(count, Op::SUM);
+                if (!csum || csum->attr_i(0) != -1 || !mt.is_splat(csum->inputs[0], 1.0) || g.values[csum->inputs[0]].elements() != rows) continue;
+                nodes.insert(mt.producer_index(count));
+            }
+        } else if (const Node *ex = mt.producer(scale, Op::EXPAND)) {
+            if (g.values[ex->inputs[0]].elements() != 1 || g.values[ex->inputs[0]].dtype != DType::F32 || mt.splat_source(scale) >= 0) continue;
+            nodes.insert(mt.producer_index(scale));
+            seed = ex->inputs[0];
+            scale_mode = 1;
+        } else {
+            const Value &sv = g.values[scale];
+            if (sv.dtype != DType::F32 || sv.shape.size() != 1 || sv.shape[0] != rows || sv.role == Role::CONSTANT) continue;
+            if (sv.role == Role::FEED ? !sv.is_dense() : (sv.producer < 0 || g.nodes[sv.producer].op == Op::PERMUTE || g.nodes[sv.producer].op == Op::EXPAND
+                                                          || g.nodes[sv.producer].op == Op::EXPAND_DIMS)) continue;
+            seed = scale;
+            scale_mode = 2;
         }
         // every value produced inside the chain (other than the gradient) must stay inside it;
         // view-only nodes over constants cost nothing and may be shared, so they are not claimed
@@ -195,7 +211,7 @@ bool match_ce_backward(Matcher &mt, int mul_index, CrossEntropyGroup &ce) {
             }
         }
         if (!closed) continue;
-        ce.logits = logits; ce.labels = labels; ce.seed = seed; ce.grad = mul.outputs[0];
+        ce.logits = logits; ce.labels = labels; ce.seed = seed; ce.grad = mul.outputs[0]; ce.scale_mode = scale_mode;
         ce.nodes = claimed;
         return true;
     }
@@ -417,7 +433,7 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
         st.a = ce.logits; st.b = ce.labels; st.c = ce.seed; st.out = ce.loss; st.out2 = ce.grad; st.out3 = ce.argmax;
         st.m = g.values[ce.logits].shape[0]; st.n = g.values[ce.logits].shape[1];
         st.scalar_bits = (uint64_t)ce.reduction;
-        st.has_ignore = ce.has_ignore; st.ignore = ce.ignore;
+        st.has_ignore = ce.has_ignore; st.ignore = ce.ignore; st.scale_mode = ce.scale_mode;
         st.nodes.assign(ce.nodes.begin(), ce.nodes.end());
         emit_at[first].push_back(st);
     }

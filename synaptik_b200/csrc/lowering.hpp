@@ -56,6 +56,7 @@ struct Step {
     int64_t m = 0, n = 0, k = 0;    // GEMM extents, or rows / cols of row kernels
     uint64_t scalar_bits = 0;       // SCALAR operand, ONE_HOT depth, loss reduction
     bool batch_contraction = false; // GEMM: a and b are dense [batch.., rows, x] tensors contracted over batch * rows
+    int scale_mode = 0;             // CROSS_ENTROPY gradient: 0 seed / rows (MEAN), 1 seed (SUM), 2 seed[row] (NONE)
     bool has_ignore = false;        // CROSS_ENTROPY: rows labelled `ignore` are skipped
     int64_t ignore = 0;
     GemmEngine engine = GemmEngine::EXACT_SIMT;

@@ -526,7 +526,7 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                 LAUNCH(kern::cross_entropy(s, (const float *)ptr(st.a), plan.views[st.b].dtype, ptr(st.b), (const float *)ptr(st.c), st.m, st.n,
                                            per_row ? (float *)ptr(st.out) : se.row_loss, per_row ? nullptr : (float *)ptr(st.out),
                                            (float *)ptr(st.out2), (int64_t *)ptr(st.out3), ctx->error_dev, reduction == 2,
-                                           st.has_ignore ? 1 : 0, st.ignore));
+                                           st.has_ignore ? 1 : 0, st.ignore, st.scale_mode));
                 if (st.out >= 0 && !per_row) x->launches++;
                 break;
             }

@@ -606,6 +606,35 @@ def test_dense_cross_entropy_known_answer(ctx, oracle):
     assert np.float32(loss) == np.float32(2.0) * np.float32(np.log(2.0))
 
 
+@pytest.mark.parametrize("rows,classes", [(300, 1000), (1024, 10)])
+def test_cross_entropy_sum_and_none_gradients_are_fused(ctx, oracle, rows, classes):
+    # the gradient chain with the cotangent restored for SUM (expand(seed)) and for NONE (one value per
+    # row) is recognised like the MEAN form and runs in the same row kernel (LossGradientRules.java:239-252)
+    rng = np.random.default_rng(rows + 1)
+    logits = (rng.standard_normal((rows, classes)) * 2).astype(np.float32)
+    labels = rng.integers(0, classes, rows).astype(np.int32)
+    for reduction in ("sum", "none"):
+        g = GraphBuilder()
+        lv, tv = g.feed(F32, (rows, classes)), g.feed(I32, (rows,))
+        sv = g.feed(F32, (rows,) if reduction == "none" else ())
+        g.publish(g.index_cross_entropy(lv, tv, reduction))
+        g.publish(g.index_cross_entropy_backward(lv, tv, sv, reduction))
+        plan = native.describe(g.build()).strip().split("\n")
+        assert len(plan) == 1 and plan[0].startswith("cross_entropy") and "gradient" in plan[0]
+        seed = rng.standard_normal(rows).astype(np.float32) if reduction == "none" else np.float32(0.75)
+        loss, grad = run_image(ctx, g, [logits, labels, seed])
+        if reduction == "sum":
+            expect = oracle.index_cross_entropy_backward(logits, labels, float(seed), count=1)
+        else:
+            expect = oracle.index_cross_entropy_ignore_backward(logits, labels, -1, seed, "none")
+        scale = np.abs(seed).max()
+        assert np.all(np.abs(grad - expect) <= 4 * np.spacing(np.abs(expect)) + np.float32(2.0 ** -24) * scale)
+        per_row, _ = oracle.index_cross_entropy(logits, labels)
+        if reduction == "none":
+            lse_scale = np.abs(per_row) + np.abs(logits[np.arange(rows), labels])
+            assert np.all(np.abs(loss - per_row) <= 4 * np.spacing(lse_scale.astype(np.float32)))
+
+
 def test_cross_entropy_rejects_out_of_range_labels(ctx):
     g = GraphBuilder()
     lv, tv = g.feed(F32, (8, 5)), g.feed(I32, (8,))
