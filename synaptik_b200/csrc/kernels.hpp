@@ -32,7 +32,10 @@ cudaError_t argmax_rows(cudaStream_t s, const float *x, int64_t *out, int64_t ro
 cudaError_t softmax_rows(cudaStream_t s, const float *x, float *out, int64_t rows, int64_t cols, bool log_kind);
 // Squared error (CpuLossReferenceKernel.java:67-87): reduction 0 = per-element (p - t)^2 into out[count],
 // 1 = mean, 2 = sum into out[0]; up to 65536 elements the sum is the reference's sequential binary32 one.
-cudaError_t mse(cudaStream_t s, int reduction, const float *p, const float *t, int64_t count, float *out);
+// partials: mse_partial_count(count) doubles of scratch (0 for small inputs, which one thread adds in the
+// reference's own order); without it large inputs are reduced by a single block.
+int64_t mse_partial_count(int64_t count);
+cudaError_t mse(cudaStream_t s, int reduction, const float *p, const float *t, int64_t count, float *out, double *partials = nullptr);
 
 // ---- fused memory-bound kernels ----------------------------------------------------------------
 // out = gate > 0 ? upstream : 0   (WHERE(GT(z,0), g, 0), ElementwiseGradientRules.java:210)

@@ -544,6 +544,53 @@ __global__ void mse_kernel(const float *__restrict__ p, const float *__restrict_
     out[0] = (total == 0.0f || !isfinite(total)) ? total / (float)count : (float)((double)total / (double)count);
 }
 
+// Large inputs, two phases: every block adds its share of the squared differences in binary64 (grid-
+// strided, so the order is fixed by the launch shape) and writes one partial; one block then adds the
+// partials in order, rounds once and forms the quotient as above.  One block over 65 M elements took
+// milliseconds; this form streams at HBM speed.
+constexpr int kMsePartialThreads = 256;
+__global__ void __launch_bounds__(kMsePartialThreads) mse_partial_kernel(const float *__restrict__ p, const float *__restrict__ t, int64_t count, double *partials) {
+    __shared__ double partial[kMsePartialThreads / 32];
+    const int64_t tid = blockIdx.x * (int64_t)blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
+    double acc = 0.0;
+    if ((((uintptr_t)p | (uintptr_t)t) & 15) == 0) {
+        const float4 *p4 = reinterpret_cast<const float4 *>(p), *t4 = reinterpret_cast<const float4 *>(t);
+        const int64_t n4 = count >> 2;
+        for (int64_t i = tid; i < n4; i += stride) {
+            const float4 a = p4[i], b = t4[i];
+            const float d0 = __fsub_rn(a.x, b.x), d1 = __fsub_rn(a.y, b.y), d2 = __fsub_rn(a.z, b.z), d3 = __fsub_rn(a.w, b.w);
+            acc += ((double)__fmul_rn(d0, d0) + (double)__fmul_rn(d1, d1)) + ((double)__fmul_rn(d2, d2) + (double)__fmul_rn(d3, d3));
+        }
+        for (int64_t i = (n4 << 2) + tid; i < count; i += stride) { const float d = __fsub_rn(p[i], t[i]); acc += (double)__fmul_rn(d, d); }
+    } else {
+        for (int64_t i = tid; i < count; i += stride) { const float d = __fsub_rn(p[i], t[i]); acc += (double)__fmul_rn(d, d); }
+    }
+    acc = warp_sum(acc);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double v = 0.0;
+        for (int i = 0; i < kMsePartialThreads / 32; i++) v += partial[i];
+        partials[blockIdx.x] = v;
+    }
+}
+
+__global__ void mse_final_kernel(const double *__restrict__ partials, int blocks, int64_t count, float *out, int mean) {
+    __shared__ double partial[32];
+    double acc = 0.0;
+    for (int i = threadIdx.x; i < blocks; i += blockDim.x) acc += partials[i];
+    acc = warp_sum(acc);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x >= 32) return;
+    double v = threadIdx.x < (blockDim.x >> 5) ? partial[threadIdx.x] : 0.0;
+    v = warp_sum(v);
+    if (threadIdx.x != 0) return;
+    const float total = (float)v;
+    if (!mean) { out[0] = total; return; }
+    out[0] = (total == 0.0f || !isfinite(total)) ? total / (float)count : (float)((double)total / (double)count);
+}
+
 __global__ void relu_backward_kernel(const float4 *__restrict__ gate, const float4 *__restrict__ up, float4 *out, int64_t vec_count,
                                      const float *gate_s, const float *up_s, float *out_s, int64_t total) {
     int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
@@ -1164,10 +1211,22 @@ cudaError_t softmax_rows(cudaStream_t s, const float *x, float *out, int64_t row
     return cudaGetLastError();
 }
 
-cudaError_t mse(cudaStream_t s, int reduction, const float *p, const float *t, int64_t count, float *out) {
+int64_t mse_partial_count(int64_t count) {
+    if (count <= 65536) return 0;                          // small inputs keep the reference's own order in one thread
+    const int64_t want = (count + 4 * kMsePartialThreads * 4 - 1) / (4 * kMsePartialThreads * 4);    // at least four 16-byte groups per thread
+    return want < 148 * 8 ? want : 148 * 8;
+}
+
+cudaError_t mse(cudaStream_t s, int reduction, const float *p, const float *t, int64_t count, float *out, double *partials) {
     if (reduction == 0) {
         if (count == 0) return cudaSuccess;
         squared_error_kernel<<<grid_for(count, kThreads), kThreads, 0, s>>>(p, t, count, out);
+    } else if (partials && mse_partial_count(count) > 0) {
+        const int blocks = (int)mse_partial_count(count);
+        mse_partial_kernel<<<blocks, kMsePartialThreads, 0, s>>>(p, t, count, partials);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        mse_final_kernel<<<1, 1024, 0, s>>>(partials, blocks, count, out, reduction == 1);
     } else {
         mse_kernel<<<1, 1024, 0, s>>>(p, t, count, out, reduction == 1);
     }

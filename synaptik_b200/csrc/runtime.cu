@@ -316,6 +316,9 @@ int32_t prepare_executable(Executable *x) {
         } else if (st.kind == StepKind::COLSUM) {
             void *p; if (!alloc((uint64_t)kern::colsum_partial_count(st.m, st.n) * 8, &p)) return ALLOCATION_FAILED;
             se.colsum_partials = (double *)p;
+        } else if (st.kind == StepKind::MSE && st.scalar_bits != 0 && kern::mse_partial_count(st.m) > 0) {
+            void *p; if (!alloc((uint64_t)kern::mse_partial_count(st.m) * 8, &p)) return ALLOCATION_FAILED;
+            se.colsum_partials = (double *)p;       // the same kind of scratch: binary64 partial sums
         } else if (st.kind == StepKind::CROSS_ENTROPY || st.kind == StepKind::DENSE_CROSS_ENTROPY) {
             void *p; if (!alloc((uint64_t)st.m * 4, &p)) return ALLOCATION_FAILED;
             se.row_loss = (float *)p;
@@ -539,7 +542,8 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                 break;
             }
             case StepKind::MSE:
-                LAUNCH(kern::mse(s, (int)st.scalar_bits, (const float *)ptr(st.a), (const float *)ptr(st.b), st.m, (float *)ptr(st.out)));
+                LAUNCH(kern::mse(s, (int)st.scalar_bits, (const float *)ptr(st.a), (const float *)ptr(st.b), st.m, (float *)ptr(st.out), se.colsum_partials));
+                if (se.colsum_partials && st.scalar_bits != 0) x->launches++;
                 break;
             case StepKind::ARG_MAX:
                 LAUNCH(kern::argmax_rows(s, (const float *)ptr(st.a), (int64_t *)ptr(st.out), st.m, st.n));

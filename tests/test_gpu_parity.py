@@ -728,6 +728,27 @@ def test_mse_matches_the_checker(ctx, oracle):
     assert np.array_equal(grad, oracle.mse_backward(p, t))
 
 
+@pytest.mark.parametrize("shape", [(2048, 1000), (70001,), (300, 999)])
+def test_mse_large_inputs_two_phase_reduction(ctx, oracle, shape):
+    # above 65536 elements the squared differences are added in binary64 by many blocks and rounded once,
+    # where the reference adds them in ascending binary32 order: the device result lies within a rounding
+    # of the exact sum, the reference within its own sequential-sum error (count * 2^-25 relative at worst)
+    rng = np.random.default_rng(len(shape) + shape[0])
+    p = rng.standard_normal(shape).astype(np.float32)
+    t = rng.standard_normal(shape).astype(np.float32)
+    g = GraphBuilder()
+    pv, tv = g.feed(F32, p.shape), g.feed(F32, p.shape)
+    g.publish(g.mean_squared_error(pv, tv, "mean"))
+    g.publish(g.mean_squared_error(pv, tv, "sum"))
+    mean, total = run_image(ctx, g, [p, t])
+    d = (p - t).astype(np.float32)
+    exact = (d.astype(np.float64) ** 2).astype(np.float32).astype(np.float64).sum()      # each square rounded to binary32 first
+    assert abs(float(total) - exact) <= 2.0 ** -23 * exact
+    assert abs(float(mean) - exact / p.size) <= 2.0 ** -22 * exact / p.size
+    assert abs(float(total) - float(oracle.squared_error(p, t, "sum"))) <= p.size * 2.0 ** -25 * exact
+    assert abs(float(mean) - float(oracle.mse(p, t))) <= p.size * 2.0 ** -25 * exact / p.size
+
+
 def test_mse_sum_and_none_reductions(ctx, oracle):
     # the other two reductions of the same reference kernel (CpuLossReferenceKernel.java:67-87) and the
     # cotangents the gradient rule restores for them (LossGradientRules.java:77-101): bit for bit
