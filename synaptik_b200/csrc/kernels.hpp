@@ -63,7 +63,9 @@ cudaError_t colsum_static(cudaStream_t s, int device, const float *g, int64_t ro
 cudaError_t cross_entropy(cudaStream_t s, const float *logits, DType label_type, const void *labels,
                           const float *seed, int64_t rows, int64_t cols, float *row_loss, float *loss_out,
                           float *grad_out, int64_t *argmax_out, int *error_word, int sum_only = 0,
-                          int has_ignore = 0, int64_t ignore = 0, int scale_mode = 0);
+                          int has_ignore = 0, int64_t ignore = 0, int scale_mode = 0, float *active_scratch = nullptr);
+// active_scratch: one float of device scratch, needed when a gradient with scale_mode 0 is asked for under
+// an ignore index (it receives the number of rows that are not ignored, the MEAN rule's divisor).
 // scale_mode: what each row of (softmax - onehot) is multiplied by: 0 seed / rows (the MEAN rule), 1 seed
 // (SUM), 2 seed[row] (NONE: the cotangent comes one value per row).
 // has_ignore: rows whose label equals `ignore` give zero loss and zero gradient, are exempt from the

@@ -724,12 +724,13 @@ __device__ __noinline__ void ce_row_careful(const float *__restrict__ row, int64
 template <int CHUNKS, typename L, bool GRAD, bool ARGMAX>
 __global__ void __launch_bounds__(kThreads, CHUNKS >= 8 ? 3 : 4) ce_rows_vec_kernel(const float *__restrict__ logits, const void *__restrict__ labels,
         const float *__restrict__ seed, int64_t rows, int cols, float *row_loss, float *grad, int64_t *argmax_out, int *error_word,
-        int has_ignore, long long ignore, int scale_mode) {
+        int has_ignore, long long ignore, int scale_mode, const float *__restrict__ divisor) {
     int lane = threadIdx.x & 31;
     int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     const int vec_cols = cols >> 2;
-    // the cotangent each row's (p - onehot) is multiplied by: seed / rows (MEAN), seed (SUM), seed[r] (NONE)
-    const float uniform_scale = !GRAD ? 0.0f : scale_mode == 0 ? __fdiv_rn(seed ? seed[0] : 1.0f, (float)rows) : (seed ? seed[0] : 1.0f);
+    // the cotangent each row's (p - onehot) is multiplied by: seed / rows (MEAN; under an ignore index
+    // seed / rows that are left, counted into `divisor`), seed (SUM), seed[r] (NONE)
+    const float uniform_scale = !GRAD ? 0.0f : scale_mode == 0 ? __fdiv_rn(seed ? seed[0] : 1.0f, divisor ? divisor[0] : (float)rows) : (seed ? seed[0] : 1.0f);
     for (int64_t r = warp; r < rows; r += warps) {
         const float scale = (GRAD && scale_mode == 2) ? seed[r] : uniform_scale;
         const float *row_s = logits + r * cols;
@@ -831,10 +832,10 @@ __global__ void __launch_bounds__(kThreads, CHUNKS >= 8 ? 3 : 4) ce_rows_vec_ker
 template <typename L>
 __global__ void ce_rows_generic_kernel(const float *__restrict__ logits, const void *__restrict__ labels, const float *__restrict__ seed,
         int64_t rows, int64_t cols, float *row_loss, float *grad, int64_t *argmax_out, int *error_word,
-        int has_ignore, long long ignore, int scale_mode) {
+        int has_ignore, long long ignore, int scale_mode, const float *__restrict__ divisor) {
     int lane = threadIdx.x & 31;
     int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-    const float uniform_scale = !grad ? 0.0f : scale_mode == 0 ? __fdiv_rn(seed ? seed[0] : 1.0f, (float)rows) : (seed ? seed[0] : 1.0f);
+    const float uniform_scale = !grad ? 0.0f : scale_mode == 0 ? __fdiv_rn(seed ? seed[0] : 1.0f, divisor ? divisor[0] : (float)rows) : (seed ? seed[0] : 1.0f);
     for (int64_t r = warp; r < rows; r += warps) {
         const float scale = (grad && scale_mode == 2) ? seed[r] : uniform_scale;
         int64_t label = load_label<L>(labels, r);
@@ -886,6 +887,23 @@ __global__ void mean_kernel(const float *__restrict__ values, int64_t count, flo
 // Reduction of the row losses under an ignore index (CpuLossReferenceKernel.java:208-218): ignored
 // rows add nothing and are not counted; MEAN divides by the number of rows that are left (0 / 0 is
 // NaN when every row is ignored, as there).
+// Number of rows whose label is not the ignore index, as the binary32 value the rule's exactly
+// rounded SUM over its zeros and ones gives.
+template <typename L>
+__global__ void count_active_kernel(const void *__restrict__ labels, long long ignore, int64_t count, float *out) {
+    __shared__ long long partial[32];
+    long long active = 0;
+    for (int64_t i = threadIdx.x; i < count; i += blockDim.x) active += load_label<L>(labels, i) != ignore;
+    for (int o = 16; o > 0; o >>= 1) active += __shfl_xor_sync(0xffffffffu, active, o);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = active;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        long long n = threadIdx.x < (blockDim.x >> 5) ? partial[threadIdx.x] : 0;
+        for (int o = 16; o > 0; o >>= 1) n += __shfl_xor_sync(0xffffffffu, n, o);
+        if (threadIdx.x == 0) out[0] = (float)n;
+    }
+}
+
 template <typename L>
 __global__ void mean_active_kernel(const float *__restrict__ values, const void *__restrict__ labels, long long ignore, int64_t count,
                                    float *out, int divide) {
@@ -1296,13 +1314,23 @@ cudaError_t colsum_static(cudaStream_t s, int device, const float *g, int64_t ro
 
 cudaError_t cross_entropy(cudaStream_t s, const float *logits, DType label_type, const void *labels, const float *seed,
                           int64_t rows, int64_t cols, float *row_loss, float *loss_out, float *grad_out, int64_t *argmax_out, int *error_word,
-                          int sum_only, int has_ignore, int64_t ignore, int scale_mode) {
+                          int sum_only, int has_ignore, int64_t ignore, int scale_mode, float *active_scratch) {
     if (rows == 0 || cols == 0) return cudaErrorInvalidValue;
     if (scale_mode < 0 || scale_mode > 2 || (scale_mode == 2 && grad_out && !seed)) return cudaErrorInvalidValue;
+    // the MEAN gradient under an ignore index divides by the rows that are left: counted first
+    const float *divisor = nullptr;
+    if (has_ignore && grad_out && scale_mode == 0) {
+        if (!active_scratch) return cudaErrorInvalidValue;
+        if (label_type == DType::I32) count_active_kernel<int32_t><<<1, 1024, 0, s>>>(labels, (long long)ignore, rows, active_scratch);
+        else count_active_kernel<int64_t><<<1, 1024, 0, s>>>(labels, (long long)ignore, rows, active_scratch);
+        cudaError_t ce = cudaGetLastError();
+        if (ce != cudaSuccess) return ce;
+        divisor = active_scratch;
+    }
     int grid = grid_for(rows, kThreads / 32);
     bool vec = (cols & 3) == 0 && cols >= 128 && cols <= 1024 && (((uintptr_t)logits | (uintptr_t)grad_out) & 15) == 0;
     bool i32 = label_type == DType::I32;
-#define SYN_CE_ARGS <<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, (int)cols, row_loss, grad_out, argmax_out, error_word, has_ignore, (long long)ignore, scale_mode)
+#define SYN_CE_ARGS <<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, (int)cols, row_loss, grad_out, argmax_out, error_word, has_ignore, (long long)ignore, scale_mode, divisor)
 #define SYN_CE_VEC2(C, L) do { if (grad_out && argmax_out) ce_rows_vec_kernel<C, L, true, true> SYN_CE_ARGS; \
                                else if (grad_out) ce_rows_vec_kernel<C, L, true, false> SYN_CE_ARGS; \
                                else if (argmax_out) ce_rows_vec_kernel<C, L, false, true> SYN_CE_ARGS; \
@@ -1311,8 +1339,8 @@ cudaError_t cross_entropy(cudaStream_t s, const float *logits, DType label_type,
     if (vec) {
         int chunks = (int)((cols / 4 + 31) / 32);
         if (chunks <= 1) SYN_CE_VEC(1); else if (chunks <= 2) SYN_CE_VEC(2); else if (chunks <= 4) SYN_CE_VEC(4); else SYN_CE_VEC(8);
-    } else if (i32) ce_rows_generic_kernel<int32_t><<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, cols, row_loss, grad_out, argmax_out, error_word, has_ignore, (long long)ignore, scale_mode);
-    else ce_rows_generic_kernel<int64_t><<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, cols, row_loss, grad_out, argmax_out, error_word, has_ignore, (long long)ignore, scale_mode);
+    } else if (i32) ce_rows_generic_kernel<int32_t><<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, cols, row_loss, grad_out, argmax_out, error_word, has_ignore, (long long)ignore, scale_mode, divisor);
+    else ce_rows_generic_kernel<int64_t><<<grid, kThreads, 0, s>>>(logits, labels, seed, rows, cols, row_loss, grad_out, argmax_out, error_word, has_ignore, (long long)ignore, scale_mode, divisor);
 #undef SYN_CE_VEC
 #undef SYN_CE_VEC2
 #undef SYN_CE_ARGS

@@ -110,6 +110,7 @@ struct CrossEntropyGroup {
     bool has_ignore = false;                // of the forward loss node
     int64_t ignore = 0;
     int scale_mode = 0;                     // of the gradient chain: 0 seed / rows, 1 seed, 2 seed[row]
+    bool chain_ignore = false;              // the gradient chain is the ignore-index form (rows left = rows not ignored)
     std::set<int> nodes;
     int emit_at = -1;
 };
@@ -212,6 +213,120 @@ bool match_ce_backward(Matcher &mt, int mul_index, CrossEntropyGroup &ce) {
         }
         if (!closed) continue;
         ce.logits = logits; ce.labels = labels; ce.seed = seed; ce.grad = mul.outputs[0]; ce.scale_mode = scale_mode;
+        ce.nodes = claimed;
+        return true;
+    }
+    return false;
+}
+
+// The same gradient under an ignore index (LossGradientRules.java:203-226): rows whose label equals the
+// ignore value are taken out three times over (their logits replaced by zeros, their scale by zero, their
+// result by zero), and the MEAN form divides the cotangent by the number of rows that are left.
+//   WHERE(ignoredRow, 0, MUL(SUB(p(WHERE(ignoredRow, 0, logits)), hot), WHERE(ignoredRow, 0, EXPAND_DIMS(scale))))
+//   ignoredRow = EXPAND_DIMS(ignored), ignored = EQ(delta, SUB(delta, delta)), delta = SCALAR_SUB(labels, ignore)
+//   scale = DIV(expand(seed), SUM(WHERE(ignored, 0, 1))) | expand(seed) | the [rows] cotangent
+bool match_ce_ignore_backward(Matcher &mt, int where_index, CrossEntropyGroup &ce) {
+    Program &g = mt.g;
+    const Node &fin = g.nodes[where_index];
+    if (fin.op != Op::WHERE || !mt.is_splat(fin.inputs[1], 0.0)) return false;
+    const int ignored_row = fin.inputs[0];
+    const Node *ird = mt.producer(ignored_row, Op::EXPAND_DIMS);
+    if (!ird || ird->attr_i(0) != 1) return false;
+    const int ignored = ird->inputs[0];
+    const Node *eq = mt.producer(ignored, Op::EQ);
+    if (!eq) return false;
+    const int delta = eq->inputs[0];
+    const Node *zero = mt.producer(eq->inputs[1], Op::SUB);
+    const Node *ssub = mt.producer(delta, Op::SCALAR_SUB);
+    if (!zero || zero->inputs[0] != delta || zero->inputs[1] != delta || !ssub) return false;
+    const int labels = ssub->inputs[0];
+    if (g.values[labels].dtype != DType::I32 && g.values[labels].dtype != DType::I64) return false;
+    const Node *mul = mt.producer(fin.inputs[2], Op::MUL);
+    if (!mul) return false;
+    for (int order = 0; order < 2; order++) {
+        const int lhs = mul->inputs[order], rhs = mul->inputs[1 - order];
+        const Node *sub = mt.producer(lhs, Op::SUB);
+        if (!sub) continue;
+        const int p = sub->inputs[0], hot = sub->inputs[1];
+        const Node *div = mt.producer(p, Op::DIV);
+        if (!div) continue;
+        const int e = div->inputs[0], s = div->inputs[1];
+        const Node *expn = mt.producer(e, Op::EXP);
+        const Node *sumn = mt.producer(s, Op::SUM);
+        if (!expn || !sumn || sumn->inputs[0] != e || sumn->attr_i(0) != 1 || !sumn->attr_i(1)) continue;
+        const Node *shift = mt.producer(expn->inputs[0], Op::SUB);
+        if (!shift) continue;
+        const int safe_logits = shift->inputs[0], mx = shift->inputs[1];
+        const Node *maxn = mt.producer(mx, Op::MAX);
+        if (!maxn || maxn->inputs[0] != safe_logits || maxn->attr_i(0) != 1 || !maxn->attr_i(1)) continue;
+        const Node *wl = mt.producer(safe_logits, Op::WHERE);
+        if (!wl || wl->inputs[0] != ignored_row || !mt.is_splat(wl->inputs[1], 0.0)) continue;
+        const int logits = wl->inputs[2];
+        if (g.values[logits].shape.size() != 2 || g.values[logits].dtype != DType::F32) continue;
+        const int64_t rows = g.values[logits].shape[0], classes = g.values[logits].shape[1];
+        if (g.values[labels].shape.size() != 1 || g.values[labels].shape[0] != rows) continue;
+        const Node *where_hot = mt.producer(hot, Op::WHERE);
+        if (!where_hot || !mt.is_splat(where_hot->inputs[1], 1.0) || !mt.is_splat(where_hot->inputs[2], 0.0)) continue;
+        const Node *onehot = mt.producer(where_hot->inputs[0], Op::ONE_HOT);
+        if (!onehot || onehot->attr_i(0) != classes) continue;
+        const Node *smin = mt.producer(onehot->inputs[0], Op::SCALAR_MIN);
+        const Node *smax = smin ? mt.producer(smin->inputs[0], Op::SCALAR_MAX) : nullptr;
+        if (!smin || !smax || smin->attr_i(0) != classes - 1 || smax->attr_i(0) != 0 || smax->inputs[0] != labels) continue;
+        const Node *ws = mt.producer(rhs, Op::WHERE);
+        if (!ws || ws->inputs[0] != ignored_row || !mt.is_splat(ws->inputs[1], 0.0)) continue;
+        const int scale1 = ws->inputs[2];
+        const Node *ed = mt.producer(scale1, Op::EXPAND_DIMS);
+        if (!ed || ed->attr_i(0) != 1) continue;
+        const int scale0 = ed->inputs[0];
+        std::set<int> nodes = {where_index, mt.producer_index(fin.inputs[2]), mt.producer_index(lhs), mt.producer_index(p), mt.producer_index(e),
+                               mt.producer_index(s), mt.producer_index(expn->inputs[0]), mt.producer_index(mx), mt.producer_index(safe_logits),
+                               mt.producer_index(hot), mt.producer_index(where_hot->inputs[0]), mt.producer_index(onehot->inputs[0]),
+                               mt.producer_index(smin->inputs[0]), mt.producer_index(rhs), mt.producer_index(scale1),
+                               mt.producer_index(ignored_row), mt.producer_index(ignored), mt.producer_index(eq->inputs[1]), mt.producer_index(delta)};
+        int seed = -1, scale_mode = 0;
+        if (const Node *sdiv = mt.producer(scale0, Op::DIV)) {
+            nodes.insert(mt.producer_index(scale0));
+            seed = sdiv->inputs[0];
+            if (const Node *ex = mt.producer(seed, Op::EXPAND)) { nodes.insert(mt.producer_index(seed)); seed = ex->inputs[0]; }
+            if (g.values[seed].elements() != 1 || g.values[seed].dtype != DType::F32) continue;
+            const Node *csum = mt.producer(sdiv->inputs[1], Op::SUM);
+            if (!csum || csum->attr_i(0) != -1) continue;
+            const Node *wa = mt.producer(csum->inputs[0], Op::WHERE);
+            if (!wa || wa->inputs[0] != ignored || !mt.is_splat(wa->inputs[1], 0.0) || !mt.is_splat(wa->inputs[2], 1.0)) continue;
+            nodes.insert(mt.producer_index(sdiv->inputs[1]));
+            nodes.insert(mt.producer_index(csum->inputs[0]));
+            scale_mode = 0;                 // seed / rows that are left
+        } else if (const Node *ex = mt.producer(scale0, Op::EXPAND)) {
+            if (g.values[ex->inputs[0]].elements() != 1 || g.values[ex->inputs[0]].dtype != DType::F32 || mt.splat_source(scale0) >= 0) continue;
+            nodes.insert(mt.producer_index(scale0));
+            seed = ex->inputs[0];
+            scale_mode = 1;
+        } else {
+            const Value &sv = g.values[scale0];
+            if (sv.dtype != DType::F32 || sv.shape.size() != 1 || sv.shape[0] != rows || sv.role == Role::CONSTANT) continue;
+            if (sv.role == Role::FEED ? !sv.is_dense() : (sv.producer < 0 || g.nodes[sv.producer].op == Op::PERMUTE || g.nodes[sv.producer].op == Op::EXPAND
+                                                          || g.nodes[sv.producer].op == Op::EXPAND_DIMS)) continue;
+            seed = scale0;
+            scale_mode = 2;
+        }
+        bool closed = true;
+        std::set<int> claimed;
+        for (int n : nodes) {
+            const Node &node = g.nodes[n];
+            bool view_of_constant = (node.op == Op::EXPAND || node.op == Op::EXPAND_DIMS || node.op == Op::CONTIGUOUS)
+                                    && mt.splat_source(node.outputs[0]) >= 0;
+            if (!view_of_constant) claimed.insert(n);
+        }
+        for (int n : claimed) {
+            if (n == where_index) continue;
+            for (int v : g.nodes[n].outputs) {
+                if (g.values[v].publication >= 0) closed = false;
+                for (int c : g.values[v].consumers) if (!nodes.count(c)) closed = false;
+            }
+        }
+        if (!closed) continue;
+        ce.logits = logits; ce.labels = labels; ce.seed = seed; ce.grad = fin.outputs[0]; ce.scale_mode = scale_mode;
+        ce.chain_ignore = true; ce.ignore = ssub->attr_i(0);
         ce.nodes = claimed;
         return true;
     }
@@ -397,12 +512,23 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
         for (int n : ce.nodes) covered[n] = 1;
     }
     for (int i = 0; i < node_count; i++) {
+        if (covered[i] || g.nodes[i].op != Op::WHERE) continue;
+        CrossEntropyGroup ce;
+        if (!match_ce_ignore_backward(mt, i, ce)) continue;
+        bool clash = false;
+        for (int n : ce.nodes) clash |= covered[n] != 0;
+        if (clash) continue;
+        ce.has_ignore = true;
+        ces.push_back(ce);
+        for (int n : ce.nodes) covered[n] = 1;
+    }
+    for (int i = 0; i < node_count; i++) {
         const Node &n = g.nodes[i];
         if (n.op != Op::INDEX_CROSS_ENTROPY || covered[i]) continue;
         CrossEntropyGroup *host = nullptr;
-        // the fused gradient is the chain without an ignore index; a loss node that has one runs alone
-        if (n.attr_i(2) == 0)
-            for (auto &ce : ces) if (ce.loss < 0 && ce.logits == n.inputs[0] && ce.labels == n.inputs[1]) { host = &ce; break; }
+        // a loss node joins the gradient chain over the same logits and labels with the same ignore index (or none)
+        for (auto &ce : ces) if (ce.loss < 0 && ce.logits == n.inputs[0] && ce.labels == n.inputs[1]
+                                 && ce.chain_ignore == (n.attr_i(2) != 0) && (!ce.chain_ignore || ce.ignore == n.attr_i(3))) { host = &ce; break; }
         if (!host) { ces.emplace_back(); host = &ces.back(); host->logits = n.inputs[0]; host->labels = n.inputs[1]; }
         host->loss = n.outputs[0];
         host->reduction = (int)n.attrs[1];

@@ -320,7 +320,7 @@ int32_t prepare_executable(Executable *x) {
             void *p; if (!alloc((uint64_t)kern::mse_partial_count(st.m) * 8, &p)) return ALLOCATION_FAILED;
             se.colsum_partials = (double *)p;       // the same kind of scratch: binary64 partial sums
         } else if (st.kind == StepKind::CROSS_ENTROPY || st.kind == StepKind::DENSE_CROSS_ENTROPY) {
-            void *p; if (!alloc((uint64_t)st.m * 4, &p)) return ALLOCATION_FAILED;
+            void *p; if (!alloc((uint64_t)(st.m + 4) * 4, &p)) return ALLOCATION_FAILED;     // row losses, then one cell for the count of rows left
             se.row_loss = (float *)p;
         }
     }
@@ -529,7 +529,8 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                 LAUNCH(kern::cross_entropy(s, (const float *)ptr(st.a), plan.views[st.b].dtype, ptr(st.b), (const float *)ptr(st.c), st.m, st.n,
                                            per_row ? (float *)ptr(st.out) : se.row_loss, per_row ? nullptr : (float *)ptr(st.out),
                                            (float *)ptr(st.out2), (int64_t *)ptr(st.out3), ctx->error_dev, reduction == 2,
-                                           st.has_ignore ? 1 : 0, st.ignore, st.scale_mode));
+                                           st.has_ignore ? 1 : 0, st.ignore, st.scale_mode, se.row_loss + st.m));
+                if (st.has_ignore && st.out2 >= 0 && st.scale_mode == 0) x->launches++;
                 if (st.out >= 0 && !per_row) x->launches++;
                 break;
             }

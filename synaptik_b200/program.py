@@ -377,9 +377,9 @@ class GraphBuilder:
             return self.mul(self.sub(p, hot), scale)
         delta = self.scalar_sub(labels, ignore_index)
         ignored = self.eq(delta, self.sub(delta, delta))
-        active = self.where(ignored, self._zeros((rows,)), self._ones((rows,)))
         scale = seed if tuple(seed.shape) == (rows,) else self.expand(seed, (rows,))
-        if reduction == "mean":
+        if reduction == "mean":     # the rule builds `active` always; unused, the compiler's dead-code pass drops it
+            active = self.where(ignored, self._zeros((rows,)), self._ones((rows,)))
             scale = self.div(scale, self.sum_all(active))
         scale = self.expand_dims(scale, 1)
         ignored_row = self.expand_dims(ignored, 1)

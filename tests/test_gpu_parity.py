@@ -498,8 +498,21 @@ def test_cross_entropy_ignore_index_forward_and_gradient(ctx, oracle, rows, clas
         sv = g.feed(F32, (rows,) if reduction == "none" else ())
         g.publish(g.index_cross_entropy(lv, tv, reduction, ignore_index=ignore))
         g.publish(g.index_cross_entropy_backward(lv, tv, sv, reduction, ignore_index=ignore))
+        plan = native.describe(g.build()).strip().split("\n")
+        assert len(plan) == 1 and plan[0].startswith("cross_entropy") and "gradient" in plan[0]      # the chain is fused
         seed = rng.standard_normal(rows).astype(np.float32) if reduction == "none" else np.float32(1.0)
         loss, grad = run_image(ctx, g, [logits, labels, seed])
+        # the same chain node by node (integer SCALAR_SUB / SUB / EQ on the labels): publishing the row
+        # mask keeps it from being fused
+        g2 = GraphBuilder()
+        lv2, tv2 = g2.feed(F32, (rows, classes)), g2.feed(label_dtype, (rows,))
+        sv2 = g2.feed(F32, (rows,) if reduction == "none" else ())
+        g2.publish(g2.index_cross_entropy_backward(lv2, tv2, sv2, reduction, ignore_index=ignore))
+        mask_node = next(n for n in g2.nodes if n.op == program.OPS["EQ"] and tuple(g2.values[n.outputs[0]].shape) == (rows,))
+        g2.publish(g2.values[mask_node.outputs[0]])
+        assert len(native.describe(g2.build()).strip().split("\n")) > 10
+        grad2, mask = run_image(ctx, g2, [logits, labels, seed])
+        assert np.array_equal(mask.astype(bool), labels == ignore)
         per_row, reduced = oracle.index_cross_entropy_ignore(logits, labels, ignore, reduction)
         if reduction == "none":
             active = labels != ignore
@@ -511,8 +524,9 @@ def test_cross_entropy_ignore_index_forward_and_gradient(ctx, oracle, rows, clas
         expect = oracle.index_cross_entropy_ignore_backward(logits, labels, ignore, seed, reduction)
         scale = np.abs(seed).max() if reduction == "none" else 1.0
         tol = 4 * np.spacing(np.abs(expect)) + np.float32(2.0 ** -24) * scale / (rows if reduction == "mean" else 1)
-        assert np.all(np.abs(grad - expect) <= tol)
-        assert np.all(grad[labels == ignore] == 0.0)
+        assert np.all(np.abs(grad - expect) <= tol) and np.all(np.abs(grad2 - expect) <= tol)
+        assert np.all(grad[labels == ignore] == 0.0) and np.all(grad2[labels == ignore] == 0.0)
+        assert not np.any(np.signbit(grad[labels == ignore]))
 
 
 def test_cross_entropy_ignore_index_edge_cases(ctx, oracle):
