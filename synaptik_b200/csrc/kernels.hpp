@@ -76,6 +76,10 @@ cudaError_t cross_entropy(cudaStream_t s, const float *logits, DType label_type,
 // (when given) their mean, or their sum with sum_only.
 cudaError_t dense_cross_entropy(cudaStream_t s, const float *logits, const float *target, int64_t rows, int64_t cols,
                                 float *row_loss, float *loss_out, int sum_only);
+// Its gradient with respect to the logits (LossGradientRules.java:131-145): (softmax * mass - target) *
+// scale per row, zeros for a row without target mass; scale_mode as for cross_entropy.
+cudaError_t dense_cross_entropy_backward(cudaStream_t s, const float *logits, const float *target, const float *seed, int64_t rows, int64_t cols,
+                                         float *grad, int scale_mode);
 
 // ---- optimizers -----------------------------------------------------------------------------
 // acc: pending gradient sum of the tensor (TrainingParameter.java:373-390), used per `gradient_mode`:

@@ -1026,6 +1026,116 @@ __global__ void __launch_bounds__(kThreads, CHUNKS >= 8 ? 2 : 4) dense_ce_rows_v
     }
 }
 
+// ---- dense-target categorical cross entropy, gradient with respect to the logits -----------------
+// The node list of LossGradientRules.denseCategorical (:131-145) in one pass per row:
+// (p * mass - target) * scale with p = exp(x - MAX) / SUM(exp(x - MAX)) (aggregate MAX by Math.max, so a
+// NaN logit poisons its row), mass = SUM(target) exactly rounded, every product and difference a
+// separate binary32 rounding; a row whose targets are all zero gives zeros.  scale as in the index form:
+// seed / rows, seed, or seed[row].
+__device__ __forceinline__ void dense_ce_grad_row_careful(const float *__restrict__ row, const float *__restrict__ weight, int64_t cols,
+                                                          float scale, float *grad_row, int lane) {
+    double mass_acc = 0.0;
+    int any = 0;
+    float mjava = __int_as_float(0xff800000);
+    for (int64_t c = lane; c < cols; c += 32) {
+        const float w = weight[c];
+        mass_acc += (double)w; any |= w != 0.0f;             // NaN != 0: a NaN weight counts as a member
+        mjava = java_max(mjava, row[c]);
+    }
+    any = __any_sync(0xffffffffu, any);
+    if (!any) { for (int64_t c = lane; c < cols; c += 32) grad_row[c] = 0.0f; return; }
+    const float mass = (float)warp_sum(mass_acc);
+    mjava = warp_max_java(mjava);
+    double acc = 0.0;
+    for (int64_t c = lane; c < cols; c += 32) acc += (double)exp_accurate(__fsub_rn(row[c], mjava));
+    const float sum = (float)warp_sum(acc);
+    for (int64_t c = lane; c < cols; c += 32) {
+        const float p = __fdiv_rn(exp_accurate(__fsub_rn(row[c], mjava)), sum);
+        grad_row[c] = __fmul_rn(__fsub_rn(__fmul_rn(p, mass), weight[c]), scale);
+    }
+}
+
+__global__ void dense_ce_grad_rows_kernel(const float *__restrict__ logits, const float *__restrict__ target, const float *__restrict__ seed,
+                                          int64_t rows, int64_t cols, float *grad, int scale_mode) {
+    int lane = threadIdx.x & 31;
+    int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const float uniform_scale = scale_mode == 0 ? __fdiv_rn(seed ? seed[0] : 1.0f, (float)rows) : (seed ? seed[0] : 1.0f);
+    for (int64_t r = warp; r < rows; r += warps)
+        dense_ce_grad_row_careful(logits + r * cols, target + r * cols, cols, scale_mode == 2 ? seed[r] : uniform_scale, grad + r * cols, lane);
+}
+
+// Rows of 128 to 1024 columns, 16-byte aligned: logits and weights are read once into registers (asked
+// for together), finite rows take one exponential per element and the quotient as a reciprocal per row
+// with a remainder-corrected product per element.
+template <int CHUNKS>
+__global__ void __launch_bounds__(kThreads, CHUNKS >= 8 ? 2 : 4) dense_ce_grad_rows_vec_kernel(const float *__restrict__ logits,
+        const float *__restrict__ target, const float *__restrict__ seed, int64_t rows, int cols, float *grad, int scale_mode) {
+    int lane = threadIdx.x & 31;
+    int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int vec_cols = cols >> 2;
+    const float uniform_scale = scale_mode == 0 ? __fdiv_rn(seed ? seed[0] : 1.0f, (float)rows) : (seed ? seed[0] : 1.0f);
+    for (int64_t r = warp; r < rows; r += warps) {
+        const float scale = scale_mode == 2 ? seed[r] : uniform_scale;
+        const float *row_s = logits + r * cols;
+        const float4 *row = reinterpret_cast<const float4 *>(row_s);
+        const float4 *weight = reinterpret_cast<const float4 *>(target + r * cols);
+        float4 v[CHUNKS], wv[CHUNKS];
+#pragma unroll
+        for (int j = 0; j < CHUNKS; j++) v[j] = lane + 32 * j < vec_cols ? row[lane + 32 * j] : make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+#pragma unroll
+        for (int j = 0; j < CHUNKS; j++) wv[j] = lane + 32 * j < vec_cols ? weight[lane + 32 * j] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (r + warps < rows && lane * 32 < cols) {
+            asm volatile("prefetch.global.L2 [%0];" :: "l"(row_s + warps * cols + lane * 32));
+            asm volatile("prefetch.global.L2 [%0];" :: "l"(target + (r + warps) * cols + lane * 32));
+        }
+        float maximum = __int_as_float(0xff800000), probe = 0.0f;
+        double mass_acc = 0.0;
+        int any = 0;
+#pragma unroll
+        for (int j = 0; j < CHUNKS; j++) {
+            maximum = fmaxf(fmaxf(maximum, fmaxf(v[j].x, v[j].y)), fmaxf(v[j].z, v[j].w));
+            probe = fmaf(v[j].x, 0.0f, probe); probe = fmaf(v[j].y, 0.0f, probe);
+            probe = fmaf(v[j].z, 0.0f, probe); probe = fmaf(v[j].w, 0.0f, probe);
+            mass_acc += ((double)wv[j].x + (double)wv[j].y) + ((double)wv[j].z + (double)wv[j].w);
+            any |= (wv[j].x != 0.0f) | (wv[j].y != 0.0f) | (wv[j].z != 0.0f) | (wv[j].w != 0.0f);
+        }
+        maximum = warp_max_plain(maximum);
+        if (__any_sync(0xffffffffu, probe != probe)) {      // rare: an infinity or NaN among the logits
+            dense_ce_grad_row_careful(row_s, target + r * cols, cols, scale, grad + r * cols, lane);
+            continue;
+        }
+        float4 *out = reinterpret_cast<float4 *>(grad + r * cols);
+        if (!__any_sync(0xffffffffu, any)) {                // no target mass in this row: no gradient
+#pragma unroll
+            for (int j = 0; j < CHUNKS; j++) if (lane + 32 * j < vec_cols) out[lane + 32 * j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            continue;
+        }
+        const float mass = (float)warp_sum(mass_acc);
+        double acc = 0.0;
+#pragma unroll
+        for (int j = 0; j < CHUNKS; j++) {
+            const float e0 = exp_shifted(__fsub_rn(v[j].x, maximum)), e1 = exp_shifted(__fsub_rn(v[j].y, maximum));
+            const float e2 = exp_shifted(__fsub_rn(v[j].z, maximum)), e3 = exp_shifted(__fsub_rn(v[j].w, maximum));
+            v[j] = make_float4(e0, e1, e2, e3);
+            if (lane + 32 * j < vec_cols) acc += (double)__fadd_rn(__fadd_rn(e0, e1), __fadd_rn(e2, e3));
+        }
+        const float sum = (float)warp_sum(acc);
+        const float rcp = __frcp_rn(sum);
+#pragma unroll
+        for (int j = 0; j < CHUNKS; j++) {
+            float e[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+            const float t[4] = {wv[j].x, wv[j].y, wv[j].z, wv[j].w};
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                float p = __fmul_rn(e[q], rcp);
+                p = fmaf(fmaf(-p, sum, e[q]), rcp, p);
+                e[q] = __fmul_rn(__fsub_rn(__fmul_rn(p, mass), t[q]), scale);
+            }
+            if (lane + 32 * j < vec_cols) out[lane + 32 * j] = make_float4(e[0], e[1], e[2], e[3]);
+        }
+    }
+}
+
 // ---- optimizers --------------------------------------------------------------------------------
 constexpr int kMaxSlots = 48;
 struct SlotTable { TensorSlot slot[kMaxSlots]; int64_t first_block[kMaxSlots + 1]; int count; };
@@ -1367,6 +1477,22 @@ cudaError_t dense_cross_entropy(cudaStream_t s, const float *logits, const float
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess || !loss_out) return e;
     mean_kernel<<<1, 1024, 0, s>>>(row_loss, rows, loss_out, !sum_only);
+    return cudaGetLastError();
+}
+
+cudaError_t dense_cross_entropy_backward(cudaStream_t s, const float *logits, const float *target, const float *seed, int64_t rows, int64_t cols,
+                                         float *grad, int scale_mode) {
+    if (rows == 0 || cols == 0) return cudaErrorInvalidValue;
+    if (scale_mode < 0 || scale_mode > 2 || (scale_mode == 2 && !seed)) return cudaErrorInvalidValue;
+    const int grid = grid_for(rows, kThreads / 32);
+    const bool vec = (cols & 3) == 0 && cols >= 128 && cols <= 1024 && (((uintptr_t)logits | (uintptr_t)target | (uintptr_t)grad) & 15) == 0;
+    if (vec) {
+        const int chunks = (int)((cols / 4 + 31) / 32);
+        if (chunks <= 1) dense_ce_grad_rows_vec_kernel<1><<<grid, kThreads, 0, s>>>(logits, target, seed, rows, (int)cols, grad, scale_mode);
+        else if (chunks <= 2) dense_ce_grad_rows_vec_kernel<2><<<grid, kThreads, 0, s>>>(logits, target, seed, rows, (int)cols, grad, scale_mode);
+        else if (chunks <= 4) dense_ce_grad_rows_vec_kernel<4><<<grid, kThreads, 0, s>>>(logits, target, seed, rows, (int)cols, grad, scale_mode);
+        else dense_ce_grad_rows_vec_kernel<8><<<grid, kThreads, 0, s>>>(logits, target, seed, rows, (int)cols, grad, scale_mode);
+    } else dense_ce_grad_rows_kernel<<<grid, kThreads, 0, s>>>(logits, target, seed, rows, cols, grad, scale_mode);
     return cudaGetLastError();
 }
 

@@ -42,7 +42,7 @@ const char *step_name(StepKind k) {
         case StepKind::GEMM: return "gemm"; case StepKind::BINARY: return "binary"; case StepKind::SCALAR: return "scalar";
         case StepKind::UNARY: return "unary"; case StepKind::WHERE: return "where"; case StepKind::ONE_HOT: return "one_hot";
         case StepKind::COPY: return "copy"; case StepKind::ROW_REDUCE: return "row_reduce"; case StepKind::FULL_SUM: return "full_sum";
-        case StepKind::COLSUM: return "colsum"; case StepKind::SOFTMAX: return "softmax"; case StepKind::CROSS_ENTROPY: return "cross_entropy"; case StepKind::DENSE_CROSS_ENTROPY: return "dense_cross_entropy";
+        case StepKind::COLSUM: return "colsum"; case StepKind::SOFTMAX: return "softmax"; case StepKind::CROSS_ENTROPY: return "cross_entropy"; case StepKind::DENSE_CROSS_ENTROPY: return "dense_cross_entropy"; case StepKind::DENSE_CE_BACKWARD: return "dense_cross_entropy_backward";
         case StepKind::MSE: return "mse"; case StepKind::ARG_MAX: return "arg_max"; case StepKind::RELU_BACKWARD: return "relu_backward";
     }
     return "?";
@@ -333,6 +333,112 @@ bool match_ce_ignore_backward(Matcher &mt, int where_index, CrossEntropyGroup &c
     return false;
 }
 
+// Logits cotangent of the dense-target loss (LossGradientRules.java:131-145):
+//   WHERE(emptyRow, 0, MUL(SUB(MUL(p(WHERE(emptyRow, 0, logits)), SUM(target)), target), WHERE(emptyRow, 0, restored)))
+//   emptyRow = EQ(SUM(WHERE(EQ(target, 0), 0, 1)), 0), restored = EXPAND_DIMS(the cotangent on the sample domain)
+struct DenseCrossEntropyGroup { int logits = -1, target = -1, seed = -1, grad = -1, scale_mode = 0; std::set<int> nodes; };
+
+bool match_dense_ce_backward(Matcher &mt, int where_index, DenseCrossEntropyGroup &dg) {
+    Program &g = mt.g;
+    const Node &fin = g.nodes[where_index];
+    if (fin.op != Op::WHERE || !mt.is_splat(fin.inputs[1], 0.0)) return false;
+    const int empty_row = fin.inputs[0];
+    const Node *eq_empty = mt.producer(empty_row, Op::EQ);
+    if (!eq_empty || !mt.is_splat(eq_empty->inputs[1], 0.0)) return false;
+    const int membership = eq_empty->inputs[0];
+    const Node *msum = mt.producer(membership, Op::SUM);
+    if (!msum || msum->attr_i(0) != 1 || !msum->attr_i(1)) return false;
+    const Node *member = mt.producer(msum->inputs[0], Op::WHERE);
+    if (!member || !mt.is_splat(member->inputs[1], 0.0) || !mt.is_splat(member->inputs[2], 1.0)) return false;
+    const Node *eq_zero = mt.producer(member->inputs[0], Op::EQ);
+    if (!eq_zero || !mt.is_splat(eq_zero->inputs[1], 0.0)) return false;
+    const int target = eq_zero->inputs[0];
+    const Node *mul = mt.producer(fin.inputs[2], Op::MUL);
+    if (!mul) return false;
+    for (int order = 0; order < 2; order++) {
+        const int lhs = mul->inputs[order], rhs = mul->inputs[1 - order];
+        const Node *sub = mt.producer(lhs, Op::SUB);
+        if (!sub || sub->inputs[1] != target) continue;
+        const Node *pm = mt.producer(sub->inputs[0], Op::MUL);
+        if (!pm) continue;
+        int p = -1, mass = -1;
+        for (int o = 0; o < 2 && p < 0; o++) {
+            const Node *ms = mt.producer(pm->inputs[1 - o], Op::SUM);
+            if (ms && ms->inputs[0] == target && ms->attr_i(0) == 1 && ms->attr_i(1) && mt.producer(pm->inputs[o], Op::DIV)) { p = pm->inputs[o]; mass = pm->inputs[1 - o]; }
+        }
+        if (p < 0) continue;
+        const Node *div = mt.producer(p, Op::DIV);
+        const int e = div->inputs[0], s = div->inputs[1];
+        const Node *expn = mt.producer(e, Op::EXP);
+        const Node *sumn = mt.producer(s, Op::SUM);
+        if (!expn || !sumn || sumn->inputs[0] != e || sumn->attr_i(0) != 1 || !sumn->attr_i(1)) continue;
+        const Node *shift = mt.producer(expn->inputs[0], Op::SUB);
+        if (!shift) continue;
+        const int safe_logits = shift->inputs[0], mx = shift->inputs[1];
+        const Node *maxn = mt.producer(mx, Op::MAX);
+        if (!maxn || maxn->inputs[0] != safe_logits || maxn->attr_i(0) != 1 || !maxn->attr_i(1)) continue;
+        const Node *wl = mt.producer(safe_logits, Op::WHERE);
+        if (!wl || wl->inputs[0] != empty_row || !mt.is_splat(wl->inputs[1], 0.0)) continue;
+        const int logits = wl->inputs[2];
+        if (g.values[logits].shape.size() != 2 || g.values[logits].dtype != DType::F32 || g.values[target].shape != g.values[logits].shape) continue;
+        const int64_t rows = g.values[logits].shape[0];
+        const Node *ws = mt.producer(rhs, Op::WHERE);
+        if (!ws || ws->inputs[0] != empty_row || !mt.is_splat(ws->inputs[1], 0.0)) continue;
+        const Node *ed = mt.producer(ws->inputs[2], Op::EXPAND_DIMS);
+        if (!ed || ed->attr_i(0) != 1) continue;
+        const int scale0 = ed->inputs[0];
+        std::set<int> nodes = {where_index, mt.producer_index(fin.inputs[2]), mt.producer_index(lhs), mt.producer_index(sub->inputs[0]), mt.producer_index(p),
+                               mt.producer_index(mass), mt.producer_index(e), mt.producer_index(s), mt.producer_index(expn->inputs[0]), mt.producer_index(mx),
+                               mt.producer_index(safe_logits), mt.producer_index(rhs), mt.producer_index(ws->inputs[2]), mt.producer_index(empty_row),
+                               mt.producer_index(membership), mt.producer_index(msum->inputs[0]), mt.producer_index(member->inputs[0])};
+        int seed = -1, scale_mode = 0;
+        if (const Node *sdiv = mt.producer(scale0, Op::DIV)) {
+            nodes.insert(mt.producer_index(scale0));
+            seed = sdiv->inputs[0];
+            const int count = sdiv->inputs[1];
+            if (const Node *ex = mt.producer(seed, Op::EXPAND)) { nodes.insert(mt.producer_index(seed)); seed = ex->inputs[0]; }
+            if (g.values[seed].elements() != 1 || g.values[seed].dtype != DType::F32) continue;
+            if (!mt.is_splat(count, (double)rows)) {
+                const Node *csum = mt.producer(count, Op::SUM);
+                if (!csum || csum->attr_i(0) != -1 || !mt.is_splat(csum->inputs[0], 1.0) || g.values[csum->inputs[0]].elements() != rows) continue;
+                nodes.insert(mt.producer_index(count));
+            }
+        } else if (const Node *ex = mt.producer(scale0, Op::EXPAND)) {
+            if (g.values[ex->inputs[0]].elements() != 1 || g.values[ex->inputs[0]].dtype != DType::F32 || mt.splat_source(scale0) >= 0) continue;
+            nodes.insert(mt.producer_index(scale0));
+            seed = ex->inputs[0];
+            scale_mode = 1;
+        } else {
+            const Value &sv = g.values[scale0];
+            if (sv.dtype != DType::F32 || sv.shape.size() != 1 || sv.shape[0] != rows || sv.role == Role::CONSTANT) continue;
+            if (sv.role == Role::FEED ? !sv.is_dense() : (sv.producer < 0 || g.nodes[sv.producer].op == Op::PERMUTE || g.nodes[sv.producer].op == Op::EXPAND
+                                                          || g.nodes[sv.producer].op == Op::EXPAND_DIMS)) continue;
+            seed = scale0;
+            scale_mode = 2;
+        }
+        bool closed = true;
+        std::set<int> claimed;
+        for (int n : nodes) {
+            const Node &node = g.nodes[n];
+            bool view_of_constant = (node.op == Op::EXPAND || node.op == Op::EXPAND_DIMS || node.op == Op::CONTIGUOUS)
+                                    && mt.splat_source(node.outputs[0]) >= 0;
+            if (!view_of_constant) claimed.insert(n);
+        }
+        for (int n : claimed) {
+            if (n == where_index) continue;
+            for (int v : g.nodes[n].outputs) {
+                if (g.values[v].publication >= 0) closed = false;
+                for (int c : g.values[v].consumers) if (!nodes.count(c)) closed = false;
+            }
+        }
+        if (!closed) continue;
+        dg.logits = logits; dg.target = target; dg.seed = seed; dg.grad = fin.outputs[0]; dg.scale_mode = scale_mode;
+        dg.nodes = claimed;
+        return true;
+    }
+    return false;
+}
+
 }  // namespace
 
 Status lower_program(const Program &source, const LoweringOptions &options, Plan &plan, std::string &message) {
@@ -523,6 +629,24 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
         for (int n : ce.nodes) covered[n] = 1;
     }
     for (int i = 0; i < node_count; i++) {
+        if (covered[i] || g.nodes[i].op != Op::WHERE) continue;
+        DenseCrossEntropyGroup dg;
+        if (!match_dense_ce_backward(mt, i, dg)) continue;
+        bool clash = false;
+        for (int n : dg.nodes) clash |= covered[n] != 0;
+        int first = *dg.nodes.begin();
+        auto before = [&](int v) { return g.values[v].producer < first; };
+        if (clash || !before(dg.logits) || !before(dg.target) || !before(dg.seed)) continue;
+        for (int n : dg.nodes) covered[n] = 1;
+        Step st;
+        st.kind = StepKind::DENSE_CE_BACKWARD;
+        st.a = dg.logits; st.b = dg.target; st.c = dg.seed; st.out = dg.grad;
+        st.m = g.values[dg.logits].shape[0]; st.n = g.values[dg.logits].shape[1];
+        st.scale_mode = dg.scale_mode;
+        st.nodes.assign(dg.nodes.begin(), dg.nodes.end());
+        emit_at[first].push_back(st);
+    }
+    for (int i = 0; i < node_count; i++) {
         const Node &n = g.nodes[i];
         if (n.op != Op::INDEX_CROSS_ENTROPY || covered[i]) continue;
         CrossEntropyGroup *host = nullptr;
@@ -705,6 +829,8 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
                 if (gs != OK) return gs;
             } else if (st.kind == StepKind::CROSS_ENTROPY) {
                 if (dense_input(st.a) < 0 || dense_input(st.b) < 0) return UNSUPPORTED_SHAPE;
+            } else if (st.kind == StepKind::DENSE_CE_BACKWARD) {
+                if (dense_input(st.a) < 0 || dense_input(st.b) < 0 || dense_input(st.c) < 0) return UNSUPPORTED_SHAPE;
             } else if (st.kind == StepKind::RELU_BACKWARD) {
                 if (dense_input(st.a) < 0 || dense_input(st.b) < 0) return UNSUPPORTED_SHAPE;
             }

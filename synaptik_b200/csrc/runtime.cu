@@ -542,6 +542,10 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                 if (!per_row) x->launches++;
                 break;
             }
+            case StepKind::DENSE_CE_BACKWARD:
+                LAUNCH(kern::dense_cross_entropy_backward(s, (const float *)ptr(st.a), (const float *)ptr(st.b), (const float *)ptr(st.c), st.m, st.n,
+                                                          (float *)ptr(st.out), st.scale_mode));
+                break;
             case StepKind::MSE:
                 LAUNCH(kern::mse(s, (int)st.scalar_bits, (const float *)ptr(st.a), (const float *)ptr(st.b), st.m, (float *)ptr(st.out), se.colsum_partials));
                 if (se.colsum_partials && st.scalar_bits != 0) x->launches++;

@@ -565,8 +565,20 @@ def test_dense_cross_entropy_forward_and_gradient(ctx, oracle, rows, classes):
         sv = g.feed(F32, (rows,) if reduction == "none" else ())
         g.publish(g.dense_cross_entropy(lv, tv, reduction))
         g.publish(g.dense_cross_entropy_backward(lv, tv, sv, reduction))
+        plan = native.describe(g.build()).strip().split("\n")
+        assert len(plan) == 2 and plan[1].startswith("dense_cross_entropy_backward")         # the gradient chain is fused
         seed = rng.standard_normal(rows).astype(np.float32) if reduction == "none" else np.float32(1.0)
         loss, grad = run_image(ctx, g, [logits, target, seed])
+        # the same chain node by node: publishing the empty-row mask keeps it from being fused
+        g2 = GraphBuilder()
+        lv2, tv2 = g2.feed(F32, (rows, classes)), g2.feed(F32, (rows, classes))
+        sv2 = g2.feed(F32, (rows,) if reduction == "none" else ())
+        g2.publish(g2.dense_cross_entropy_backward(lv2, tv2, sv2, reduction))
+        mask_node = next(n for n in g2.nodes if n.op == program.OPS["EQ"] and tuple(g2.values[n.outputs[0]].shape) == (rows, 1))
+        g2.publish(g2.values[mask_node.outputs[0]])
+        assert len(native.describe(g2.build()).strip().split("\n")) > 10
+        grad2, empty = run_image(ctx, g2, [logits, target, seed])
+        assert np.array_equal(empty[:, 0].astype(bool), ~(target != 0).any(axis=1))
         per_row, reduced = oracle.dense_cross_entropy(logits, target, reduction)
         if reduction == "none":
             # stated tolerance: 4 units in the last place of sum |weight * (lse - x)| (the reference adds
@@ -582,8 +594,8 @@ def test_dense_cross_entropy_forward_and_gradient(ctx, oracle, rows, classes):
         expect = oracle.dense_cross_entropy_backward(logits, target, seed, reduction)
         scale = np.abs(seed).max() if reduction == "none" else 1.0
         tol = 4 * np.spacing(np.abs(expect)) + np.float32(2.0 ** -23) * scale / (rows if reduction == "mean" else 1)
-        assert np.all(np.abs(grad - expect) <= tol)
-        assert np.all(grad[3] == 0.0)
+        assert np.all(np.abs(grad - expect) <= tol) and np.all(np.abs(grad2 - expect) <= tol)
+        assert np.all(grad[3] == 0.0) and np.all(grad2[3] == 0.0) and not np.any(np.signbit(grad[3]))
 
 
 @pytest.mark.parametrize("cols", [128, 500, 1024])
@@ -609,6 +621,24 @@ def test_dense_cross_entropy_wide_rows_with_special_logits(ctx, oracle, cols):
     assert loss[3] == np.inf and per_row[3] == np.inf and np.isfinite(loss[2])
     finite = np.isfinite(per_row)
     assert np.all(np.abs(loss[finite] - per_row[finite]) <= 2e-6 * np.abs(per_row[finite]))
+    # the fused gradient kernel against the node list executed node by node (unfused by publishing the
+    # empty-row mask): the same NaN rows, the same values elsewhere within the stated tolerance
+    target[6] = 0.0
+    grads = []
+    for unfuse in (False, True):
+        g = GraphBuilder()
+        lv, tv, sv = g.feed(F32, logits.shape), g.feed(F32, target.shape), g.feed(F32, ())
+        g.publish(g.dense_cross_entropy_backward(lv, tv, sv, "sum"))
+        if unfuse:
+            mask_node = next(n for n in g.nodes if n.op == program.OPS["EQ"] and tuple(g.values[n.outputs[0]].shape) == (24, 1))
+            g.publish(g.values[mask_node.outputs[0]])
+        assert (len(native.describe(g.build()).strip().split("\n")) == 1) == (not unfuse)
+        grads.append(run_image(ctx, g, [logits, target, np.float32(0.5)])[0])
+    fused, listed = grads
+    assert np.array_equal(np.isnan(fused), np.isnan(listed)) and np.isnan(fused[1]).all() and np.isnan(fused[4]).all()
+    assert np.all(fused[6] == 0.0) and np.all(listed[6] == 0.0)
+    ok = ~np.isnan(listed)
+    assert np.all(np.abs(fused[ok] - listed[ok]) <= 4 * np.spacing(np.abs(listed[ok])) + np.float32(2.0 ** -23) * 0.5 * np.abs(target).sum(axis=1).max())
 
 
 def test_dense_cross_entropy_known_answer(ctx, oracle):
