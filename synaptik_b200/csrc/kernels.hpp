@@ -30,6 +30,9 @@ cudaError_t row_reduce(cudaStream_t s, Op op, const float *x, float *out, int64_
 cudaError_t full_sum(cudaStream_t s, const float *x, const Index4 &ix, int64_t total, float *out);
 cudaError_t argmax_rows(cudaStream_t s, const float *x, int64_t *out, int64_t rows, int64_t cols);
 cudaError_t softmax_rows(cudaStream_t s, const float *x, float *out, int64_t rows, int64_t cols, bool log_kind);
+// The gradient node lists of both kinds in one pass per row (ReductionGradientRules.java:84-90): y the stored
+// forward result, g the upstream gradient, both dense [rows, cols].
+cudaError_t softmax_backward_rows(cudaStream_t s, const float *y, const float *g, float *out, int64_t rows, int64_t cols, bool log_kind);
 // Squared error (CpuLossReferenceKernel.java:67-87): reduction 0 = per-element (p - t)^2 into out[count],
 // 1 = mean, 2 = sum into out[0]; up to 65536 elements the sum is the reference's sequential binary32 one.
 // partials: mse_partial_count(count) doubles of scratch (0 for small inputs, which one thread adds in the

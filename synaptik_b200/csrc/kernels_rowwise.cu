@@ -508,6 +508,52 @@ __global__ void __launch_bounds__(kThreads, CHUNKS >= 8 ? 3 : 4) softmax_rows_ve
     }
 }
 
+// Gradient node lists of SOFTMAX and LOG_SOFTMAX (ReductionGradientRules.java:84-90) in one pass per row,
+// every node's rounding kept: SOFTMAX y * (g - SUM(g * y)), LOG_SOFTMAX g - exp(y) * SUM(g), the row
+// SUM exactly rounded (binary64 lanes, one rounding).  One warp per row; the second sweep over the row
+// comes from cache.
+template <bool LOG>
+__global__ void softmax_backward_rows_kernel(const float *__restrict__ y, const float *__restrict__ g, float *out, int64_t rows, int64_t cols) {
+    int lane = threadIdx.x & 31;
+    int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const bool vec = (cols & 3) == 0 && ((((uintptr_t)y | (uintptr_t)g | (uintptr_t)out) & 15) == 0);
+    for (int64_t r = warp; r < rows; r += warps) {
+        const float *yr = y + r * cols, *gr = g + r * cols;
+        float *o = out + r * cols;
+        double acc = 0.0;
+        if (vec) {
+            const float4 *y4 = reinterpret_cast<const float4 *>(yr), *g4 = reinterpret_cast<const float4 *>(gr);
+            for (int64_t c = lane; c < (cols >> 2); c += 32) {
+                const float4 b = g4[c];
+                if (LOG) acc += ((double)b.x + (double)b.y) + ((double)b.z + (double)b.w);
+                else { const float4 a = y4[c]; acc += ((double)__fmul_rn(b.x, a.x) + (double)__fmul_rn(b.y, a.y)) + ((double)__fmul_rn(b.z, a.z) + (double)__fmul_rn(b.w, a.w)); }
+            }
+        } else {
+            for (int64_t c = lane; c < cols; c += 32) acc += LOG ? (double)gr[c] : (double)__fmul_rn(gr[c], yr[c]);
+        }
+        const float total = (float)warp_sum(acc);
+        if (vec) {
+            const float4 *y4 = reinterpret_cast<const float4 *>(yr), *g4 = reinterpret_cast<const float4 *>(gr);
+            float4 *o4 = reinterpret_cast<float4 *>(o);
+            for (int64_t c = lane; c < (cols >> 2); c += 32) {
+                const float4 a = y4[c], b = g4[c];
+                float4 d;
+                if (LOG) {
+                    d.x = __fsub_rn(b.x, __fmul_rn(exp_accurate(a.x), total)); d.y = __fsub_rn(b.y, __fmul_rn(exp_accurate(a.y), total));
+                    d.z = __fsub_rn(b.z, __fmul_rn(exp_accurate(a.z), total)); d.w = __fsub_rn(b.w, __fmul_rn(exp_accurate(a.w), total));
+                } else {
+                    d.x = __fmul_rn(a.x, __fsub_rn(b.x, total)); d.y = __fmul_rn(a.y, __fsub_rn(b.y, total));
+                    d.z = __fmul_rn(a.z, __fsub_rn(b.z, total)); d.w = __fmul_rn(a.w, __fsub_rn(b.w, total));
+                }
+                o4[c] = d;
+            }
+        } else {
+            for (int64_t c = lane; c < cols; c += 32)
+                o[c] = LOG ? __fsub_rn(gr[c], __fmul_rn(exp_accurate(yr[c]), total)) : __fmul_rn(yr[c], __fsub_rn(gr[c], total));
+        }
+    }
+}
+
 // MEAN_SQUARED_ERROR, CpuLossReferenceKernel.java:67-87: ascending binary32 accumulation of the
 // squared differences, then the exact quotient by the count rounded once (:221-225).  Small
 // inputs are accumulated by one thread in the reference's order; large ones by a binary64 tree.
@@ -1343,6 +1389,14 @@ int64_t mse_partial_count(int64_t count) {
     if (count <= 65536) return 0;                          // small inputs keep the reference's own order in one thread
     const int64_t want = (count + 4 * kMsePartialThreads * 4 - 1) / (4 * kMsePartialThreads * 4);    // at least four 16-byte groups per thread
     return want < 148 * 8 ? want : 148 * 8;
+}
+
+cudaError_t softmax_backward_rows(cudaStream_t s, const float *y, const float *g, float *out, int64_t rows, int64_t cols, bool log_kind) {
+    if (rows == 0 || cols == 0) return cudaSuccess;
+    const int grid = grid_for(rows, kThreads / 32);
+    if (log_kind) softmax_backward_rows_kernel<true><<<grid, kThreads, 0, s>>>(y, g, out, rows, cols);
+    else softmax_backward_rows_kernel<false><<<grid, kThreads, 0, s>>>(y, g, out, rows, cols);
+    return cudaGetLastError();
 }
 
 cudaError_t mse(cudaStream_t s, int reduction, const float *p, const float *t, int64_t count, float *out, double *partials) {

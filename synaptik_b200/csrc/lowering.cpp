@@ -42,7 +42,7 @@ const char *step_name(StepKind k) {
         case StepKind::GEMM: return "gemm"; case StepKind::BINARY: return "binary"; case StepKind::SCALAR: return "scalar";
         case StepKind::UNARY: return "unary"; case StepKind::WHERE: return "where"; case StepKind::ONE_HOT: return "one_hot";
         case StepKind::COPY: return "copy"; case StepKind::ROW_REDUCE: return "row_reduce"; case StepKind::FULL_SUM: return "full_sum";
-        case StepKind::COLSUM: return "colsum"; case StepKind::SOFTMAX: return "softmax"; case StepKind::CROSS_ENTROPY: return "cross_entropy"; case StepKind::DENSE_CROSS_ENTROPY: return "dense_cross_entropy"; case StepKind::DENSE_CE_BACKWARD: return "dense_cross_entropy_backward";
+        case StepKind::COLSUM: return "colsum"; case StepKind::SOFTMAX: return "softmax"; case StepKind::CROSS_ENTROPY: return "cross_entropy"; case StepKind::DENSE_CROSS_ENTROPY: return "dense_cross_entropy"; case StepKind::DENSE_CE_BACKWARD: return "dense_cross_entropy_backward"; case StepKind::SOFTMAX_BACKWARD: return "softmax_backward";
         case StepKind::MSE: return "mse"; case StepKind::ARG_MAX: return "arg_max"; case StepKind::RELU_BACKWARD: return "relu_backward";
     }
     return "?";
@@ -628,6 +628,66 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
         ces.push_back(ce);
         for (int n : ce.nodes) covered[n] = 1;
     }
+    // ---- SOFTMAX / LOG_SOFTMAX gradient node lists (ReductionGradientRules.java:84-90) --------------
+    //   MUL(y, SUB(g, SUM(MUL(g, y), last axis, keep)))   and   SUB(g, MUL(EXP(y), SUM(g, last axis, keep)))
+    for (int i = 0; i < node_count; i++) {
+        if (covered[i]) continue;
+        const Node &top = g.nodes[i];
+        int y = -1, up = -1;
+        bool log_kind = false;
+        std::set<int> nodes = {i};
+        auto row_sum_of = [&](int v, int of) -> const Node * {        // SUM over the last axis, kept, of value `of`
+            const Node *sn = mt.producer(v, Op::SUM);
+            const size_t r = g.values[of].shape.size();
+            return sn && sn->inputs[0] == of && r == 2 && sn->attr_i(0) == 1 && sn->attr_i(1) ? sn : nullptr;
+        };
+        if (top.op == Op::MUL) {
+            for (int order = 0; order < 2 && y < 0; order++) {
+                const int yy = top.inputs[order];
+                const Node *sub = mt.producer(top.inputs[1 - order], Op::SUB);
+                if (!sub) continue;
+                const Node *sn = mt.producer(sub->inputs[1], Op::SUM);
+                if (!sn) continue;
+                const Node *gy = mt.producer(sn->inputs[0], Op::MUL);
+                if (!gy || !row_sum_of(sub->inputs[1], sn->inputs[0])) continue;
+                const int gg = sub->inputs[0];
+                if (!((gy->inputs[0] == gg && gy->inputs[1] == yy) || (gy->inputs[0] == yy && gy->inputs[1] == gg))) continue;
+                y = yy; up = gg;
+                nodes.insert(mt.producer_index(top.inputs[1 - order])); nodes.insert(mt.producer_index(sub->inputs[1])); nodes.insert(mt.producer_index(sn->inputs[0]));
+            }
+        } else if (top.op == Op::SUB) {
+            const Node *em = mt.producer(top.inputs[1], Op::MUL);
+            if (em) for (int order = 0; order < 2 && y < 0; order++) {
+                const Node *ex = mt.producer(em->inputs[order], Op::EXP);
+                if (!ex || !row_sum_of(em->inputs[1 - order], top.inputs[0])) continue;
+                y = ex->inputs[0]; up = top.inputs[0]; log_kind = true;
+                nodes.insert(mt.producer_index(top.inputs[1])); nodes.insert(mt.producer_index(em->inputs[order])); nodes.insert(mt.producer_index(em->inputs[1 - order]));
+            }
+        }
+        if (y < 0) continue;
+        const Value &yv = g.values[y], &uv = g.values[up];
+        if (yv.shape.size() != 2 || uv.shape != yv.shape || g.values[top.outputs[0]].shape != yv.shape || yv.dtype != DType::F32 || uv.dtype != DType::F32) continue;
+        bool ok = true;
+        for (int n : nodes) {
+            ok &= !covered[n];
+            if (n == i) continue;
+            for (int v : g.nodes[n].outputs) {
+                if (g.values[v].publication >= 0) ok = false;
+                for (int c : g.values[v].consumers) if (!nodes.count(c)) ok = false;
+            }
+        }
+        const int first = *nodes.begin();
+        if (!ok || g.values[y].producer >= first || g.values[up].producer >= first) continue;
+        for (int n : nodes) covered[n] = 1;
+        Step st;
+        st.kind = StepKind::SOFTMAX_BACKWARD;
+        st.a = y; st.b = up; st.out = top.outputs[0];
+        st.m = yv.shape[0]; st.n = yv.shape[1];
+        st.scalar_bits = log_kind ? 1 : 0;
+        st.nodes.assign(nodes.begin(), nodes.end());
+        emit_at[first].push_back(st);
+    }
+
     for (int i = 0; i < node_count; i++) {
         if (covered[i] || g.nodes[i].op != Op::WHERE) continue;
         DenseCrossEntropyGroup dg;
@@ -828,6 +888,8 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
                 Status gs = prepare_gemm(st);
                 if (gs != OK) return gs;
             } else if (st.kind == StepKind::CROSS_ENTROPY) {
+                if (dense_input(st.a) < 0 || dense_input(st.b) < 0) return UNSUPPORTED_SHAPE;
+            } else if (st.kind == StepKind::SOFTMAX_BACKWARD) {
                 if (dense_input(st.a) < 0 || dense_input(st.b) < 0) return UNSUPPORTED_SHAPE;
             } else if (st.kind == StepKind::DENSE_CE_BACKWARD) {
                 if (dense_input(st.a) < 0 || dense_input(st.b) < 0 || dense_input(st.c) < 0) return UNSUPPORTED_SHAPE;

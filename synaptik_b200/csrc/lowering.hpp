@@ -39,7 +39,7 @@ struct View {
 
 enum class StepKind : int {
     GEMM, BINARY, SCALAR, UNARY, WHERE, ONE_HOT, COPY, ROW_REDUCE, FULL_SUM, COLSUM, SOFTMAX,
-    CROSS_ENTROPY, MSE, ARG_MAX, RELU_BACKWARD, DENSE_CROSS_ENTROPY, DENSE_CE_BACKWARD
+    CROSS_ENTROPY, MSE, ARG_MAX, RELU_BACKWARD, DENSE_CROSS_ENTROPY, DENSE_CE_BACKWARD, SOFTMAX_BACKWARD
 };
 const char *step_name(StepKind k);
 

@@ -542,6 +542,9 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                 if (!per_row) x->launches++;
                 break;
             }
+            case StepKind::SOFTMAX_BACKWARD:
+                LAUNCH(kern::softmax_backward_rows(s, (const float *)ptr(st.a), (const float *)ptr(st.b), (float *)ptr(st.out), st.m, st.n, st.scalar_bits == 1));
+                break;
             case StepKind::DENSE_CE_BACKWARD:
                 LAUNCH(kern::dense_cross_entropy_backward(s, (const float *)ptr(st.a), (const float *)ptr(st.b), (const float *)ptr(st.c), st.m, st.n,
                                                           (float *)ptr(st.out), st.scale_mode));

@@ -413,16 +413,19 @@ def test_softmax_wide_rows_with_special_values(ctx, oracle, log_kind, cols):
 
 
 @pytest.mark.parametrize("log_kind", [False, True])
-def test_softmax_gradient_node_lists(ctx, oracle, log_kind):
-    # ReductionGradientRules.java:84-90, executed node by node on the stored forward result
+@pytest.mark.parametrize("shape", [(129, 333), (64, 1000)])
+def test_softmax_gradient_node_lists(ctx, oracle, log_kind, shape):
+    # ReductionGradientRules.java:84-90 on the stored forward result: the node list is matched and runs as
+    # one pass per row that keeps every node's rounding (scalar and 16-byte forms)
     rng = np.random.default_rng(3 + log_kind)
-    logits = (rng.standard_normal((129, 333)) * 2).astype(np.float32)
+    logits = (rng.standard_normal(shape) * 2).astype(np.float32)
     upstream = rng.standard_normal(logits.shape).astype(np.float32)
     g = GraphBuilder()
     x, up = g.feed(F32, logits.shape), g.feed(F32, logits.shape)
     y = g.log_softmax(x, 1) if log_kind else g.softmax(x, 1)
     g.publish(y)
     g.publish(g.log_softmax_backward(y, up, 1) if log_kind else g.softmax_backward(y, up, 1))
+    assert native.describe(g.build()).strip().split("\n")[1].startswith("softmax_backward")
     out, grad = run_image(ctx, g, [logits, upstream])
     # the chain is checked on the device's own forward result, so only the chain's roundings count
     expect = oracle.softmax_backward(out, upstream, log_kind)
