@@ -123,3 +123,76 @@ def test_malformed_images_are_rejected(lib):
     r = b.relu(a); b.publish(r)
     b.nodes[0].inputs[0] = r.index
     assert status_of(b.build()) == 9
+
+
+def _plan(builder):
+    return [line.split(" nodes=")[0] for line in native.describe(builder.build()).strip().split("\n")]
+
+
+def test_loss_gradient_node_lists_lower_to_single_row_passes(lib):
+    # the gradient rules' node lists (LossGradientRules.java:114-228, ReductionGradientRules.java:84-90) are
+    # matched structurally: index cross entropy in its three reductions, with and without an ignore index,
+    # joins its forward node in one launch; the dense-target form and both softmax kinds get one launch each
+    F32, I64 = program.F32, program.I64
+    for reduction in ("mean", "sum", "none"):
+        for ignore in (None, -100):
+            b = program.GraphBuilder()
+            x, labels = b.feed(F32, (64, 256)), b.feed(I64, (64,))
+            seed = b.feed(F32, (64,) if reduction == "none" else ())
+            b.publish(b.index_cross_entropy(x, labels, reduction, ignore_index=ignore))
+            b.publish(b.index_cross_entropy_backward(x, labels, seed, reduction, ignore_index=ignore))
+            assert _plan(b) == ["cross_entropy rows=64 classes=256 loss gradient"], (reduction, ignore)
+        b = program.GraphBuilder()
+        x, target = b.feed(F32, (64, 256)), b.feed(F32, (64, 256))
+        seed = b.feed(F32, (64,) if reduction == "none" else ())
+        b.publish(b.dense_cross_entropy(x, target, reduction))
+        b.publish(b.dense_cross_entropy_backward(x, target, seed, reduction))
+        assert _plan(b) == ["dense_cross_entropy m=64 n=256", "dense_cross_entropy_backward m=64 n=256"], reduction
+    for log_kind in (False, True):
+        b = program.GraphBuilder()
+        x, up = b.feed(F32, (64, 256)), b.feed(F32, (64, 256))
+        y = b.log_softmax(x, 1) if log_kind else b.softmax(x, 1)
+        b.publish(y)
+        b.publish(b.log_softmax_backward(y, up, 1) if log_kind else b.softmax_backward(y, up, 1))
+        assert _plan(b) == ["softmax m=64 n=256", "softmax_backward m=64 n=256"]
+    # a chain whose intermediate is observable is left as the reference's nodes
+    b = program.GraphBuilder()
+    x, up = b.feed(F32, (64, 256)), b.feed(F32, (64, 256))
+    y = b.softmax(x, 1)
+    product = b.mul(up, y)
+    b.publish(product)
+    b.publish(b.mul(y, b.sub(up, b.sum(product, 1, True))))
+    assert "softmax_backward m=64 n=256" not in _plan(b)
+    # an ignore index on the loss node alone: the forward launch only, labelled by the same kernel
+    b = program.GraphBuilder()
+    x, labels = b.feed(F32, (64, 256)), b.feed(I64, (64,))
+    b.publish(b.index_cross_entropy(x, labels, "mean", ignore_index=7))
+    assert _plan(b) == ["cross_entropy rows=64 classes=256 loss"]
+
+
+def test_linear_over_batch_dimensions_lowers_to_fused_products(lib):
+    # Linear -> ReLU -> Linear on [batch, time, features]: the forward products keep bias / ReLU epilogues,
+    # dX keeps its ReLU gate, all over batch * time rows; the weight gradients are per-slice products summed
+    # over the batch on the exact engine
+    F32 = program.F32
+    b = program.GraphBuilder()
+    x, w1, b1, w2, b2, up = (b.feed(F32, s) for s in ((4, 6, 32), (16, 32), (16,), (8, 16), (8,), (4, 6, 8)))
+    wt1, z1 = b.linear(x, w1, b1)
+    a1 = b.relu(z1)
+    wt2, z2 = b.linear(a1, w2, b2)
+    b.publish(z2)
+    da1, dwt2 = b.matmul_backward(a1, wt2, up)
+    dz1 = b.relu_backward(z1, da1)
+    dx, dwt1 = b.matmul_backward(x, wt1, dz1)
+    for v in (dx, b.permute(dwt1, (1, 0)), b.permute(dwt2, (1, 0)), b.sum_to_shape(dz1, (16,))):
+        b.publish(v)
+    plan = _plan(b)
+    assert plan[0] == "gemm engine=exact_simt m=24 n=16 k=32 bias relu" and plan[1] == "gemm engine=exact_simt m=24 n=8 k=16 bias"
+    assert "gemm engine=exact_simt m=24 n=16 k=8 relu_gate" in plan
+    assert plan.count("gemm engine=exact_simt m=16 n=8 k=6") == 4 and plan.count("gemm engine=exact_simt m=32 n=16 k=6") == 4
+    assert "colsum m=4 n=128" in plan and "colsum m=4 n=512" in plan and "colsum m=24 n=16" in plan
+    # large enough for the tensor cores, the weight gradient is one contraction over batch * time
+    b = program.GraphBuilder()
+    x, up = b.feed(F32, (4, 256, 512)), b.feed(F32, (4, 256, 256))
+    b.publish(b.sum_to_shape(b.matmul(b.swap_last_two(x), up), (512, 256)))
+    assert _plan(b) == ["gemm engine=tcgen05_3xtf32 m=512 n=256 k=1024"]
