@@ -103,11 +103,12 @@ class Model:
             buf.upload(array)
 
     # ---- inference ------------------------------------------------------------------------
-    def _inference_state(self, batch: int, arg_max: bool):
-        key = (batch, arg_max)
+    def _inference_state(self, lead, arg_max: bool):
+        key = (tuple(lead), arg_max)
         if key not in self._inference:
-            graph = program.mlp_inference_graph(self.dims, batch, arg_max, bias=self.bias, activation=self.activation)
+            graph = program.mlp_inference_graph(self.dims, tuple(lead), arg_max, bias=self.bias, activation=self.activation)
             exe = native.Executable(self.context, graph.image)
+            batch = int(np.prod(lead))
             x = self.context.buffer(batch * self.dims[0] * 4)
             out = self.context.buffer(batch * self.dims[-1] * 4)
             outs = [out] + ([self.context.buffer(batch * 8)] if arg_max else [])
@@ -115,13 +116,16 @@ class Model:
         return self._inference[key]
 
     def compute(self, x: np.ndarray, arg_max: bool = False):
-        """Model.compute: uploads ``x`` [batch, in], runs the forward graph, returns the output
-        [batch, out] (and the INT64 row arg-max when asked)."""
+        """Model.compute: uploads ``x`` [batch, in] (or [batch.., in]: every Linear applies to the last
+        dimension), runs the forward graph, returns the output [batch.., out] (and the INT64 row arg-max
+        when asked, for a [batch, in] input)."""
         x = np.ascontiguousarray(x, dtype=np.float32)
-        exe, xbuf, outs = self._inference_state(x.shape[0], arg_max)
+        if x.ndim < 2 or x.shape[-1] != self.dims[0]:
+            raise ValueError(f"input shape {x.shape} does not end in {self.dims[0]} features")
+        exe, xbuf, outs = self._inference_state(x.shape[:-1], arg_max)
         xbuf.upload(x)
         exe.run([xbuf] + self.param_buffers, outs)
-        result = outs[0].download(np.float32, (x.shape[0], self.dims[-1]))
+        result = outs[0].download(np.float32, tuple(x.shape[:-1]) + (self.dims[-1],))
         if arg_max:
             return result, outs[1].download(np.int64, (x.shape[0],))
         return result

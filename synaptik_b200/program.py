@@ -454,13 +454,19 @@ class MlpGraph:
     shapes: dict
 
 
-def mlp_inference_graph(dims: Sequence[int], batch: int, arg_max: bool = False, bias: bool = True,
+def mlp_inference_graph(dims: Sequence[int], batch, arg_max: bool = False, bias: bool = True,
                         activation: str = "relu") -> MlpGraph:
     """Model.compute of a Linear/activation stack (ModelBuilder.linear().relu() / .tanh() / .sigmoid()):
-    feeds x then (w, b) per layer; publishes the last layer's output (and its row arg-max when asked)."""
+    feeds x then (w, b) per layer; publishes the last layer's output (and its row arg-max when asked).
+    `batch` is the row count, or the tuple of leading dimensions of an input [batch.., features]
+    (Linear applies to the last dimension, Tensor.java:1270-1365)."""
     g = GraphBuilder()
-    x = g.feed(F32, (batch, dims[0]))
-    names, shapes = ["x"], {"x": (batch, dims[0])}
+    lead = tuple(batch) if isinstance(batch, (tuple, list)) else (int(batch),)
+    if arg_max and len(lead) != 1:
+        raise ValueError("row arg-max needs a [batch, features] input")
+    batch = lead[0]
+    x = g.feed(F32, lead + (dims[0],))
+    names, shapes = ["x"], {"x": lead + (dims[0],)}
     a = x
     params = []
     for l in range(len(dims) - 1):

@@ -179,6 +179,27 @@ def test_inference_with_arg_max(ctx, oracle):
     model.close()
 
 
+def test_compute_over_batch_and_time_equals_the_flat_network(ctx, oracle):
+    # Model.compute on [batch, time, features]: every Linear applies to the last dimension and keeps its
+    # fused epilogue over batch * time rows, so the result is bit for bit the flat network's (and the checker's)
+    model = nn.Model([48, 96, 64, 10], ctx, seed=4)
+    rng = np.random.default_rng(4)
+    params = model.parameters()
+    for i in range(1, len(params), 2):
+        params[i] = rng.uniform(-0.1, 0.1, params[i].shape).astype(np.float32)
+    model.load_parameters(params)
+    x = rng.standard_normal((4, 6, 48)).astype(np.float32)
+    out = model.compute(x)
+    flat = model.compute(x.reshape(24, 48))
+    assert out.shape == (4, 6, 10) and np.array_equal(out.reshape(24, 10).view(np.uint32), flat.view(np.uint32))
+    assert np.array_equal(flat.view(np.uint32), oracle.mlp_forward(x.reshape(24, 48), params[0::2], params[1::2])[-1].view(np.uint32))
+    with pytest.raises(ValueError):
+        model.compute(x, arg_max=True)
+    with pytest.raises(ValueError):
+        model.compute(x[..., :40])
+    model.close()
+
+
 def test_training_state_snapshot_restores_a_run_exactly(ctx):
     # TrainingSession.state() / restore: a model restored from a snapshot taken mid-accumulation continues
     # bit for bit like the one it was taken from
