@@ -95,6 +95,63 @@ struct Matcher {
         const Value &val = g.values[v];
         return val.publication < 0 && val.consumers.size() == 1 && val.consumers[0] == node;
     }
+    // The output cotangent restored on the sample domain (LossGradientRules.restore, :239-252), as the loss
+    // gradient chains hold it under their EXPAND_DIMS: DIV(EXPAND(seed), divisor) for MEAN (scale_mode 0;
+    // `divisor_ok` checks the divisor and claims its nodes), EXPAND(seed) for SUM (1), or the [rows]
+    // cotangent itself for NONE (2).  Claims the nodes it walks through; false when no form fits.
+    template <typename DivisorOk>
+    bool restored_cotangent(int scale, int64_t rows, std::set<int> &nodes, int &seed, int &scale_mode, DivisorOk divisor_ok) const {
+        if (const Node *sdiv = producer(scale, Op::DIV)) {
+            nodes.insert(producer_index(scale));
+            seed = sdiv->inputs[0];
+            if (const Node *ex = producer(seed, Op::EXPAND)) { nodes.insert(producer_index(seed)); seed = ex->inputs[0]; }
+            if (g.values[seed].elements() != 1 || g.values[seed].dtype != DType::F32) return false;
+            scale_mode = 0;
+            return divisor_ok(sdiv->inputs[1]);
+        }
+        if (const Node *ex = producer(scale, Op::EXPAND)) {
+            if (g.values[ex->inputs[0]].elements() != 1 || g.values[ex->inputs[0]].dtype != DType::F32 || splat_source(scale) >= 0) return false;
+            nodes.insert(producer_index(scale));
+            seed = ex->inputs[0];
+            scale_mode = 1;
+            return true;
+        }
+        const Value &sv = g.values[scale];
+        if (sv.dtype != DType::F32 || sv.shape.size() != 1 || sv.shape[0] != rows || sv.role == Role::CONSTANT) return false;
+        if (sv.role == Role::FEED ? !sv.is_dense() : (sv.producer < 0 || g.nodes[sv.producer].op == Op::PERMUTE || g.nodes[sv.producer].op == Op::EXPAND
+                                                      || g.nodes[sv.producer].op == Op::EXPAND_DIMS)) return false;
+        seed = scale;
+        scale_mode = 2;
+        return true;
+    }
+    // The divisor of the plain MEAN form: the splat constant `rows`, or SUM over `rows` ones.
+    bool row_count(int count, int64_t rows, std::set<int> &nodes) const {
+        if (is_splat(count, (double)rows)) return true;
+        const Node *csum = producer(count, Op::SUM);
+        if (!csum || csum->attr_i(0) != -1 || !is_splat(csum->inputs[0], 1.0) || g.values[csum->inputs[0]].elements() != rows) return false;
+        nodes.insert(producer_index(count));
+        return true;
+    }
+    // Every value produced inside a matched chain (other than by `final_node`) must stay inside it.  View-only
+    // nodes over constants cost nothing and may be shared, so they are not claimed.  Returns the claimed
+    // nodes in `claimed` and whether the chain is closed.
+    bool claim_closed_chain(const std::set<int> &nodes, int final_node, std::set<int> &claimed) const {
+        claimed.clear();
+        for (int n : nodes) {
+            const Node &node = g.nodes[n];
+            const bool view_of_constant = (node.op == Op::EXPAND || node.op == Op::EXPAND_DIMS || node.op == Op::CONTIGUOUS)
+                                          && splat_source(node.outputs[0]) >= 0;
+            if (!view_of_constant) claimed.insert(n);
+        }
+        for (int n : claimed) {
+            if (n == final_node) continue;
+            for (int v : g.nodes[n].outputs) {
+                if (g.values[v].publication >= 0) return false;
+                for (int c : g.values[v].consumers) if (!nodes.count(c)) return false;
+            }
+        }
+        return true;
+    }
 };
 
 struct LinearGroup {          // MATMUL [-> ADD bias] [-> RELU] [-> gate by WHERE(GT(.,0),.,0)]
@@ -168,50 +225,9 @@ bool match_ce_backward(Matcher &mt, int mul_index, CrossEntropyGroup &ce) {
         nodes.insert(mt.producer_index(scale));
         scale = ed->inputs[0];
         int seed = -1, scale_mode = 0;
-        if (const Node *sdiv = mt.producer(scale, Op::DIV)) {
-            nodes.insert(mt.producer_index(scale));
-            seed = sdiv->inputs[0];
-            const int count = sdiv->inputs[1];
-            if (const Node *ex = mt.producer(seed, Op::EXPAND)) { nodes.insert(mt.producer_index(seed)); seed = ex->inputs[0]; }
-            if (g.values[seed].elements() != 1 || g.values[seed].dtype != DType::F32) continue;
-            // count is either already folded to the splat constant `rows` or SUM over ones
-            if (!mt.is_splat(count, (double)rows)) {
-                const Node *csum = mt.producer(count, Op::SUM);
-                if (!csum || csum->attr_i(0) != -1 || !mt.is_splat(csum->inputs[0], 1.0) || g.values[csum->inputs[0]].elements() != rows) continue;
-                nodes.insert(mt.producer_index(count));
-            }
-        } else if (const Node *ex = mt.producer(scale, Op::EXPAND)) {
-            if (g.values[ex->inputs[0]].elements() != 1 || g.values[ex->inputs[0]].dtype != DType::F32 || mt.splat_source(scale) >= 0) continue;
-            nodes.insert(mt.producer_index(scale));
-            seed = ex->inputs[0];
-            scale_mode = 1;
-        } else {
-            const Value &sv = g.values[scale];
-            if (sv.dtype != DType::F32 || sv.shape.size() != 1 || sv.shape[0] != rows || sv.role == Role::CONSTANT) continue;
-            if (sv.role == Role::FEED ? !sv.is_dense() : (sv.producer < 0 || g.nodes[sv.producer].op == Op::PERMUTE || g.nodes[sv.producer].op == Op::EXPAND
-                                                          || g.nodes[sv.producer].op == Op::EXPAND_DIMS)) continue;
-            seed = scale;
-            scale_mode = 2;
-        }
-        // every value produced inside the chain (other than the gradient) must stay inside it;
-        // view-only nodes over constants cost nothing and may be shared, so they are not claimed
-        bool closed = true;
+        if (!mt.restored_cotangent(scale, rows, nodes, seed, scale_mode, [&](int count) { return mt.row_count(count, rows, nodes); })) continue;
         std::set<int> claimed;
-        for (int n : nodes) {
-            const Node &node = g.nodes[n];
-            bool view_of_constant = (node.op == Op::EXPAND || node.op == Op::EXPAND_DIMS || node.op == Op::CONTIGUOUS)
-                                    && mt.splat_source(node.outputs[0]) >= 0;
-            if (view_of_constant) continue;
-            claimed.insert(n);
-        }
-        for (int n : claimed) {
-            if (n == mul_index) continue;
-            for (int v : g.nodes[n].outputs) {
-                if (g.values[v].publication >= 0) closed = false;
-                for (int c : g.values[v].consumers) if (!nodes.count(c)) closed = false;
-            }
-        }
-        if (!closed) continue;
+        if (!mt.claim_closed_chain(nodes, mul_index, claimed)) continue;
         ce.logits = logits; ce.labels = labels; ce.seed = seed; ce.grad = mul.outputs[0]; ce.scale_mode = scale_mode;
         ce.nodes = claimed;
         return true;
@@ -284,47 +300,18 @@ bool match_ce_ignore_backward(Matcher &mt, int where_index, CrossEntropyGroup &c
                                mt.producer_index(smin->inputs[0]), mt.producer_index(rhs), mt.producer_index(scale1),
                                mt.producer_index(ignored_row), mt.producer_index(ignored), mt.producer_index(eq->inputs[1]), mt.producer_index(delta)};
         int seed = -1, scale_mode = 0;
-        if (const Node *sdiv = mt.producer(scale0, Op::DIV)) {
-            nodes.insert(mt.producer_index(scale0));
-            seed = sdiv->inputs[0];
-            if (const Node *ex = mt.producer(seed, Op::EXPAND)) { nodes.insert(mt.producer_index(seed)); seed = ex->inputs[0]; }
-            if (g.values[seed].elements() != 1 || g.values[seed].dtype != DType::F32) continue;
-            const Node *csum = mt.producer(sdiv->inputs[1], Op::SUM);
-            if (!csum || csum->attr_i(0) != -1) continue;
+        auto rows_left = [&](int count) {       // SUM over WHERE(ignored, 0, 1): the rows that are not ignored
+            const Node *csum = mt.producer(count, Op::SUM);
+            if (!csum || csum->attr_i(0) != -1) return false;
             const Node *wa = mt.producer(csum->inputs[0], Op::WHERE);
-            if (!wa || wa->inputs[0] != ignored || !mt.is_splat(wa->inputs[1], 0.0) || !mt.is_splat(wa->inputs[2], 1.0)) continue;
-            nodes.insert(mt.producer_index(sdiv->inputs[1]));
+            if (!wa || wa->inputs[0] != ignored || !mt.is_splat(wa->inputs[1], 0.0) || !mt.is_splat(wa->inputs[2], 1.0)) return false;
+            nodes.insert(mt.producer_index(count));
             nodes.insert(mt.producer_index(csum->inputs[0]));
-            scale_mode = 0;                 // seed / rows that are left
-        } else if (const Node *ex = mt.producer(scale0, Op::EXPAND)) {
-            if (g.values[ex->inputs[0]].elements() != 1 || g.values[ex->inputs[0]].dtype != DType::F32 || mt.splat_source(scale0) >= 0) continue;
-            nodes.insert(mt.producer_index(scale0));
-            seed = ex->inputs[0];
-            scale_mode = 1;
-        } else {
-            const Value &sv = g.values[scale0];
-            if (sv.dtype != DType::F32 || sv.shape.size() != 1 || sv.shape[0] != rows || sv.role == Role::CONSTANT) continue;
-            if (sv.role == Role::FEED ? !sv.is_dense() : (sv.producer < 0 || g.nodes[sv.producer].op == Op::PERMUTE || g.nodes[sv.producer].op == Op::EXPAND
-                                                          || g.nodes[sv.producer].op == Op::EXPAND_DIMS)) continue;
-            seed = scale0;
-            scale_mode = 2;
-        }
-        bool closed = true;
+            return true;
+        };
+        if (!mt.restored_cotangent(scale0, rows, nodes, seed, scale_mode, rows_left)) continue;
         std::set<int> claimed;
-        for (int n : nodes) {
-            const Node &node = g.nodes[n];
-            bool view_of_constant = (node.op == Op::EXPAND || node.op == Op::EXPAND_DIMS || node.op == Op::CONTIGUOUS)
-                                    && mt.splat_source(node.outputs[0]) >= 0;
-            if (!view_of_constant) claimed.insert(n);
-        }
-        for (int n : claimed) {
-            if (n == where_index) continue;
-            for (int v : g.nodes[n].outputs) {
-                if (g.values[v].publication >= 0) closed = false;
-                for (int c : g.values[v].consumers) if (!nodes.count(c)) closed = false;
-            }
-        }
-        if (!closed) continue;
+        if (!mt.claim_closed_chain(nodes, where_index, claimed)) continue;
         ce.logits = logits; ce.labels = labels; ce.seed = seed; ce.grad = fin.outputs[0]; ce.scale_mode = scale_mode;
         ce.chain_ignore = true; ce.ignore = ssub->attr_i(0);
         ce.nodes = claimed;
@@ -392,46 +379,9 @@ bool match_dense_ce_backward(Matcher &mt, int where_index, DenseCrossEntropyGrou
                                mt.producer_index(safe_logits), mt.producer_index(rhs), mt.producer_index(ws->inputs[2]), mt.producer_index(empty_row),
                                mt.producer_index(membership), mt.producer_index(msum->inputs[0]), mt.producer_index(member->inputs[0])};
         int seed = -1, scale_mode = 0;
-        if (const Node *sdiv = mt.producer(scale0, Op::DIV)) {
-            nodes.insert(mt.producer_index(scale0));
-            seed = sdiv->inputs[0];
-            const int count = sdiv->inputs[1];
-            if (const Node *ex = mt.producer(seed, Op::EXPAND)) { nodes.insert(mt.producer_index(seed)); seed = ex->inputs[0]; }
-            if (g.values[seed].elements() != 1 || g.values[seed].dtype != DType::F32) continue;
-            if (!mt.is_splat(count, (double)rows)) {
-                const Node *csum = mt.producer(count, Op::SUM);
-                if (!csum || csum->attr_i(0) != -1 || !mt.is_splat(csum->inputs[0], 1.0) || g.values[csum->inputs[0]].elements() != rows) continue;
-                nodes.insert(mt.producer_index(count));
-            }
-        } else if (const Node *ex = mt.producer(scale0, Op::EXPAND)) {
-            if (g.values[ex->inputs[0]].elements() != 1 || g.values[ex->inputs[0]].dtype != DType::F32 || mt.splat_source(scale0) >= 0) continue;
-            nodes.insert(mt.producer_index(scale0));
-            seed = ex->inputs[0];
-            scale_mode = 1;
-        } else {
-            const Value &sv = g.values[scale0];
-            if (sv.dtype != DType::F32 || sv.shape.size() != 1 || sv.shape[0] != rows || sv.role == Role::CONSTANT) continue;
-            if (sv.role == Role::FEED ? !sv.is_dense() : (sv.producer < 0 || g.nodes[sv.producer].op == Op::PERMUTE || g.nodes[sv.producer].op == Op::EXPAND
-                                                          || g.nodes[sv.producer].op == Op::EXPAND_DIMS)) continue;
-            seed = scale0;
-            scale_mode = 2;
-        }
-        bool closed = true;
+        if (!mt.restored_cotangent(scale0, rows, nodes, seed, scale_mode, [&](int count) { return mt.row_count(count, rows, nodes); })) continue;
         std::set<int> claimed;
-        for (int n : nodes) {
-            const Node &node = g.nodes[n];
-            bool view_of_constant = (node.op == Op::EXPAND || node.op == Op::EXPAND_DIMS || node.op == Op::CONTIGUOUS)
-                                    && mt.splat_source(node.outputs[0]) >= 0;
-            if (!view_of_constant) claimed.insert(n);
-        }
-        for (int n : claimed) {
-            if (n == where_index) continue;
-            for (int v : g.nodes[n].outputs) {
-                if (g.values[v].publication >= 0) closed = false;
-                for (int c : g.values[v].consumers) if (!nodes.count(c)) closed = false;
-            }
-        }
-        if (!closed) continue;
+        if (!mt.claim_closed_chain(nodes, where_index, claimed)) continue;
         dg.logits = logits; dg.target = target; dg.seed = seed; dg.grad = fin.outputs[0]; dg.scale_mode = scale_mode;
         dg.nodes = claimed;
         return true;

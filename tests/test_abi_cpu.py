@@ -163,6 +163,18 @@ def test_loss_gradient_node_lists_lower_to_single_row_passes(lib):
     b.publish(product)
     b.publish(b.mul(y, b.sub(up, b.sum(product, 1, True))))
     assert "softmax_backward m=64 n=256" not in _plan(b)
+    # so is a loss gradient chain whose row mask is published: it runs as the reference's nodes
+    for dense in (False, True):
+        b = program.GraphBuilder()
+        x = b.feed(F32, (64, 256))
+        second = b.feed(F32, (64, 256)) if dense else b.feed(I64, (64,))
+        seed = b.feed(F32, ())
+        b.publish(b.dense_cross_entropy_backward(x, second, seed, "mean") if dense else b.index_cross_entropy_backward(x, second, seed, "mean", ignore_index=3))
+        mask_shape = (64, 1) if dense else (64,)
+        mask = next(n for n in b.nodes if n.op == program.OPS["EQ"] and tuple(b.values[n.outputs[0]].shape) == mask_shape)
+        b.publish(b.values[mask.outputs[0]])
+        plan = _plan(b)
+        assert len(plan) > 10 and not any(line.startswith(("cross_entropy", "dense_cross_entropy")) for line in plan)
     # an ignore index on the loss node alone: the forward launch only, labelled by the same kernel
     b = program.GraphBuilder()
     x, labels = b.feed(F32, (64, 256)), b.feed(I64, (64,))
