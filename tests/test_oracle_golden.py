@@ -94,6 +94,61 @@ def test_categorical_loss_known_answers(oracle):
     assert np.array_equal(oracle.dense_cross_entropy_backward(x, hot), oracle.index_cross_entropy_backward(x, labels))
 
 
+def test_loss_gradient_chains_are_the_derivatives_of_their_losses(oracle):
+    # the reference's tests hold no FLOAT32 known answers for these gradient node lists, so the restatements
+    # are checked against central differences of the binary64 loss they differentiate
+    rng = np.random.default_rng(21)
+    x = rng.standard_normal((6, 9)).astype(np.float32)
+    labels = np.array([3, -100, 0, 8, -100, 5])
+    target = rng.random((6, 9)).astype(np.float32)
+    target[rng.random((6, 9)) < 0.4] = 0.0
+    target[2] = 0.0
+
+    def lse(z):
+        m = z.max(axis=1, keepdims=True)
+        return (m + np.log(np.exp(z - m).sum(axis=1, keepdims=True)))[:, 0]
+
+    def index_loss(z, reduction):
+        active = labels != -100
+        rows = lse(z)[active] - z[active, labels[active]]
+        return rows.mean() if reduction == "mean" else rows.sum()
+
+    def dense_loss(z, reduction):
+        rows = (target.astype(np.float64) * (lse(z)[:, None] - z)).sum(axis=1)
+        return rows.mean() if reduction == "mean" else rows.sum()
+
+    def central(loss, reduction):
+        z = x.astype(np.float64)
+        grad = np.zeros_like(z)
+        for i in range(z.shape[0]):
+            for j in range(z.shape[1]):
+                hi, lo = z.copy(), z.copy()
+                hi[i, j] += 1e-5
+                lo[i, j] -= 1e-5
+                grad[i, j] = (loss(hi, reduction) - loss(lo, reduction)) / 2e-5
+        return grad
+
+    for reduction in ("mean", "sum"):
+        got = oracle.index_cross_entropy_ignore_backward(x, labels, -100, 1.0, reduction)
+        assert np.abs(got - central(index_loss, reduction)).max() <= 1e-5
+        got = oracle.dense_cross_entropy_backward(x, target, 1.0, reduction)
+        assert np.abs(got - central(dense_loss, reduction)).max() <= 1e-5
+    # per-row cotangents (reduction NONE): each row's derivative scaled by its own cotangent
+    seed = rng.standard_normal(6).astype(np.float32)
+    got = oracle.index_cross_entropy_ignore_backward(x, labels, -100, seed, "none")
+    assert np.abs(got - central(index_loss, "sum") * seed[:, None]).max() <= 1e-5
+    got = oracle.dense_cross_entropy_backward(x, target, seed, "none")
+    assert np.abs(got - central(dense_loss, "sum") * seed[:, None]).max() <= 1e-5
+    # softmax and log-softmax: y and the upstream gradient give the vector-Jacobian product
+    up = rng.standard_normal(x.shape).astype(np.float32)
+    z = x.astype(np.float64)
+    p = np.exp(z - lse(z)[:, None])
+    want = p * (up - (up * p).sum(axis=1, keepdims=True))
+    assert np.abs(oracle.softmax_backward(oracle.softmax(x), up, False) - want).max() <= 1e-6
+    want = up - p * up.sum(axis=1, keepdims=True)
+    assert np.abs(oracle.softmax_backward(oracle.log_softmax(x), up, True) - want).max() <= 2e-6
+
+
 def test_relu_special_values(oracle):
     y = oracle.relu(_vals([-1.0, -0.0, 0.0, 2.5, "-inf", "inf", "nan"]))
     assert list(y[:6]) == [0.0, 0.0, 0.0, 2.5, 0.0, float("inf")] and math.isnan(y[6])
