@@ -149,6 +149,26 @@ def test_loss_gradient_chains_are_the_derivatives_of_their_losses(oracle):
     assert np.abs(oracle.softmax_backward(oracle.log_softmax(x), up, True) - want).max() <= 2e-6
 
 
+def test_activation_gradient_chains_are_the_derivatives_of_their_activations(oracle):
+    # the five activation gradient rules against central differences of the binary64 functions
+    x = np.linspace(-4.0, 4.0, 33).astype(np.float32)
+    up = np.full_like(x, 1.5)
+    z = x.astype(np.float64)
+    erf = np.vectorize(math.erf)
+    functions = {
+        "tanh": np.tanh,
+        "sigmoid": lambda v: 1.0 / (1.0 + np.exp(-v)),
+        "silu": lambda v: v / (1.0 + np.exp(-v)),
+        "gelu": lambda v: 0.5 * v * (1.0 + erf(v / math.sqrt(2.0))),
+        "gelu_tanh": lambda v: 0.5 * v * (1.0 + np.tanh(math.sqrt(2.0 / math.pi) * (v + 0.044715 * v ** 3))),
+    }
+    for kind, f in functions.items():
+        want = 1.5 * (f(z + 1e-6) - f(z - 1e-6)) / 2e-6
+        y = getattr(oracle, kind)(x)
+        got = oracle.activation_backward(kind, y, up, x)
+        assert np.abs(got - want).max() <= 2e-6, kind
+
+
 def test_relu_special_values(oracle):
     y = oracle.relu(_vals([-1.0, -0.0, 0.0, 2.5, "-inf", "inf", "nan"]))
     assert list(y[:6]) == [0.0, 0.0, 0.0, 2.5, 0.0, float("inf")] and math.isnan(y[6])
