@@ -11,8 +11,12 @@
  *
  * Pinning: the Java reference cannot be built or executed in an image without a JDK, so this
  * restatement is pinned against the reference's own known-answer tests (see tests/golden/):
- * integer MATMUL results, softmax documented values, the scalar SGD training trace, the Adam
- * multiply-before-divide overflow case and the double-precision Adam oracle of its unit test.
+ * integer MATMUL results, softmax and log-softmax documented values, the dense-target and index
+ * cross-entropy answers of the Metal native test, erf special values, the scalar SGD training trace,
+ * the Adam multiply-before-divide overflow case and the double-precision Adam oracle of its unit
+ * test.  Parity unpinned (no FLOAT32 known answers in the reference's tests; pinned by special
+ * values, by the definition restated here, and for gradient rules by central differences): TANH,
+ * SIGMOID, SILU, tanh GELU, rows under an ignore index, the gradient node lists of the loss forms.
  * For arbitrary real-valued GEMM operands the reference's OpenBLAS route is itself unpinned
  * (any OpenBLAS version), so parity there is a stated tolerance, not bit equality.
  */
