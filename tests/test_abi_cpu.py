@@ -208,3 +208,57 @@ def test_linear_over_batch_dimensions_lowers_to_fused_products(lib):
     x, up = b.feed(F32, (4, 256, 512)), b.feed(F32, (4, 256, 256))
     b.publish(b.sum_to_shape(b.matmul(b.swap_last_two(x), up), (512, 256)))
     assert _plan(b) == ["gemm engine=tcgen05_3xtf32 m=512 n=256 k=1024"]
+
+
+def test_new_operations_are_validated(lib):
+    F32, I32, I64, BOOL = program.F32, program.I32, program.I64, program.BOOL
+
+    def status_of(builder):
+        data = builder.build()
+        required = ctypes.c_uint64()
+        return lib.synaptik_cuda_program_describe(bytes(data), ctypes.c_uint32(len(data)), None, ctypes.c_uint64(0), ctypes.byref(required))
+
+    # SOFTMAX: kinds 0 and 1 only, last axis only
+    b = program.GraphBuilder(); x = b.feed(F32, (4, 8))
+    b.publish(b._node("SOFTMAX", [x], F32, (4, 8), [1, 2]))
+    assert status_of(b) == 13
+    b = program.GraphBuilder(); x = b.feed(F32, (4, 8))
+    b.publish(b._node("SOFTMAX", [x], F32, (4, 8), [0, 1]))
+    assert status_of(b) == 8
+    b = program.GraphBuilder(); x = b.feed(F32, (4, 8))
+    b.publish(b.log_softmax(x, 1))
+    assert status_of(b) == 1                                    # valid: size probe
+    # dense-target cross entropy: the target has the logits' shape and FLOAT32 weights
+    b = program.GraphBuilder(); x = b.feed(F32, (4, 8)); t = b.feed(F32, (4, 7))
+    b.publish(b._node("DENSE_CROSS_ENTROPY", [x, t], F32, (), [1, 1]))
+    assert status_of(b) == 8
+    b = program.GraphBuilder(); x = b.feed(F32, (4, 8)); t = b.feed(I32, (4, 8))
+    b.publish(b._node("DENSE_CROSS_ENTROPY", [x, t], F32, (), [1, 1]))
+    assert status_of(b) == 13
+    b = program.GraphBuilder(); x = b.feed(F32, (4, 8)); t = b.feed(F32, (4, 8))
+    b.publish(b._node("DENSE_CROSS_ENTROPY", [x, t], F32, (4,), [1, 1]))       # MEAN publishes one value
+    assert status_of(b) == 9
+    # index cross entropy: the ignore flag is 0 or 1
+    b = program.GraphBuilder(); x = b.feed(F32, (4, 8)); t = b.feed(I64, (4,))
+    b.publish(b._node("INDEX_CROSS_ENTROPY", [x, t], F32, (), [1, 1, 2, 0]))
+    assert status_of(b) == 13
+    # integer operands only for SUB and EQ, and both of one type; SCALAR_SUB not on BOOL
+    b = program.GraphBuilder(); p = b.feed(I32, (4,)); q = b.feed(I32, (4,))
+    b.publish(b._node("ADD", [p, q], I32, (4,)))
+    assert status_of(b) == 13
+    b = program.GraphBuilder(); p = b.feed(I32, (4,)); q = b.feed(I64, (4,))
+    b.publish(b._node("EQ", [p, q], BOOL, (4,)))
+    assert status_of(b) == 9
+    b = program.GraphBuilder(); p = b.feed(I64, (4,)); q = b.feed(I64, (4,))
+    b.publish(b.eq(b.sub(p, q), b.scalar_sub(p, 3)))
+    assert status_of(b) == 1
+    b = program.GraphBuilder(); p = b.feed(BOOL, (4,))
+    b.publish(b._node("SCALAR_SUB", [p], BOOL, (4,), [1]))
+    assert status_of(b) == 13
+    # SUM_TO_SHAPE sums leading dimensions only
+    b = program.GraphBuilder(); x = b.feed(F32, (2, 3, 4))
+    b.publish(b._node("SUM_TO_SHAPE", [x], F32, (3, 1)))
+    assert status_of(b) == 8
+    b = program.GraphBuilder(); x = b.feed(F32, (2, 3, 4))
+    b.publish(b.sum_to_shape(x, (3, 4)))
+    assert status_of(b) == 1
