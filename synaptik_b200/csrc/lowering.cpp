@@ -398,6 +398,20 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
     std::vector<int> covered(node_count, 0);
     std::map<int, std::vector<Step>> emit_at;
 
+    // Nodes nothing observes (no output is published or read by a node that is itself observed) are
+    // never launched: marked covered before any pattern looks at them.  The reference's compiler removes
+    // such nodes itself; a hand-written image may still hold them.
+    {
+        std::vector<char> observed(node_count, 0);
+        for (int i = node_count - 1; i >= 0; i--) {
+            for (int v : g.nodes[i].outputs) {
+                if (g.values[v].publication >= 0) observed[i] = 1;
+                for (int c : g.values[v].consumers) if (observed[c]) observed[i] = 1;
+            }
+            if (!observed[i]) covered[i] = 1;
+        }
+    }
+
     auto choose_engine = [&](int64_t m, int64_t n, int64_t k) {
         bool tc = options.gemm_engine == 1 ? false : options.gemm_engine == 2 ? tensor_core_eligible(m, n, k) : tensor_core_preferred(m, n, k);
         return tc ? GemmEngine::TENSOR_CORE : GemmEngine::EXACT_SIMT;
@@ -408,7 +422,7 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
     std::map<int, int> group_of_matmul_output;      // result value -> group index
     for (int i = 0; i < node_count; i++) {
         const Node &mm = g.nodes[i];
-        if (mm.op != Op::MATMUL) continue;
+        if (mm.op != Op::MATMUL || covered[i]) continue;
         // A left operand with batch dimensions joins a group when it is stored dense (a dense feed or a
         // value some kernel materialises), so that [batch.., rows, k] reads as [batch * rows, k] over the
         // shared rank-2 right operand: Linear on [batch, time, features] keeps its fused epilogue.  Other
@@ -517,7 +531,7 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
     std::vector<Step> relu_backward_steps;
     for (int i = 0; i < node_count; i++) {
         const Node &w = g.nodes[i];
-        if (w.op != Op::WHERE || !mt.is_splat(w.inputs[2], 0.0)) continue;
+        if (w.op != Op::WHERE || covered[i] || !mt.is_splat(w.inputs[2], 0.0)) continue;
         const Node *gt = mt.producer(w.inputs[0], Op::GT);
         if (!gt || !mt.is_splat(gt->inputs[1], 0.0)) continue;
         int gate = gt->inputs[0], upstream = w.inputs[1], result = w.outputs[0];

@@ -262,3 +262,16 @@ def test_new_operations_are_validated(lib):
     b = program.GraphBuilder(); x = b.feed(F32, (2, 3, 4))
     b.publish(b.sum_to_shape(x, (3, 4)))
     assert status_of(b) == 1
+
+
+def test_unobserved_nodes_are_not_launched(lib):
+    # the reference's compiler removes nodes nothing observes before a backend sees the graph; an image
+    # that still holds some (here an unused dX product and an unused elementwise chain) does not launch them
+    F32 = program.F32
+    b = program.GraphBuilder()
+    x, w, up = b.feed(F32, (64, 32)), b.feed(F32, (16, 32)), b.feed(F32, (64, 16))
+    wt = b.permute(w, (1, 0))
+    _, dwt = b.matmul_backward(x, wt, up)
+    b.publish(b.permute(dwt, (1, 0)))
+    b.relu(b.add(x, x))
+    assert _plan(b) == ["gemm engine=exact_simt m=32 n=16 k=64 transposed_result"]
