@@ -77,7 +77,11 @@ SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_release(void *context);
  * "gemm_dynamic": 1 (default) = executables created afterwards let the two-SM kernel's block pairs take
  * their tiles one by one from a counter, so a pair whose SMs were held by another kernel (an
  * all-reduce on the communication stream) just takes fewer tiles; 0 = fixed round-robin assignment.
- * The result does not depend on the assignment.  Unknown names return INVALID_ARGUMENT. */
+ * The result does not depend on the assignment.  "fused_planes": 2 = write operand planes from the
+ * producing GEMM's epilogue even while "gemm_promote" is 1.  "comm_timeout_ms" (default 30000): how
+ * long the host waits, in any call that returns results, for work that has a collective in front of it
+ * before it gives up, aborts the communicator and returns COMM_FAILED.  Unknown names return
+ * INVALID_ARGUMENT. */
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_set_option(void *context, const char *name, int64_t value);
 /* Blocks until all work issued on the context has finished. */
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_synchronize(void *context);
@@ -86,6 +90,13 @@ SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_synchronize(void *context);
  * time between the two in milliseconds. */
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_timer_start(void *context);
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_timer_stop(void *context, double *out_milliseconds);
+/* Self-test of the bounded device-side waits (no counterpart in the reference).  Every wait inside the
+ * tensor-core GEMM kernels gives up after two seconds instead of spinning forever; the kernel then
+ * leaves in an orderly way and the run returns TIMEOUT.  This call launches one 32-thread block that
+ * runs the same wait routine on a barrier which nothing ever signals, with a limit of
+ * `limit_microseconds` (1 .. 2000000), and reports the outcome like a run would: it returns
+ * SYNAPTIK_CUDA_STATUS_TIMEOUT, never OK, and the context is as usable afterwards as before. */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_wait_probe(void *context, uint64_t limit_microseconds);
 
 /* ---- buffers: replace synaptik_metal_buffer_create / _release / _upload / _download ----------
  * Device-resident linear memory.  upload/download move raw little-endian element bytes and
@@ -169,9 +180,22 @@ SYNAPTIK_CUDA_API int32_t synaptik_cuda_executable_launch_count(void *executable
  *   kind 0 = SGD   : hyper = {learning_rate, momentum, dampening, weight_decay, nesterov(0/1)}
  *   kind 1 = Adam  : hyper = {learning_rate, beta1, beta2, epsilon, weight_decay}
  *   kind 2 = AdamW : same five values, decoupled decay
- * step applies one update with gradients[i] matching parameters[i] element for element and
- * returns EXECUTION_FAILED when any intermediate was non-finite (the reference refuses such a
- * step; here the failing step's writes are not rolled back). */
+ * step applies one update with gradients[i] matching parameters[i] element for element.
+ *
+ * A step is a transaction, like the reference's stage / validate / commit
+ * (modules/training/.../TrainingSession.java:1151-1171, TrainingParameter.java:391-409).  When any
+ * intermediate of the update is non-finite the step returns EXECUTION_FAILED, and when the run whose
+ * gradients it consumes had already failed on the device (a label outside [0, classes): status 5; a
+ * bounded wait that expired: 14; a collective that was given up: 15) it returns that status; in both
+ * cases parameters, moments, the pending gradient sum, the step count and the count of accumulated
+ * runs are bit for bit what they were before the call.  The update kernels write candidates into a
+ * second set of arrays and the handle exchanges the two sets, so creating an optimizer allocates one
+ * more array per parameter and per moment, and the device address of a parameter buffer
+ * (synaptik_cuda_buffer_device_pointer) changes with every step; bytes of a parameter buffer past
+ * element_counts[i] elements are not carried from step to step.  With the *_enqueue forms the verdict
+ * arrives with the next *_finish of the context (optimizer or executable): a failure voids the failed
+ * step and every step enqueued after it, and synaptik_cuda_optimizer_steps counts enqueued steps
+ * until then. */
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_create(void *context, int32_t kind, const double *hyper, int32_t hyper_count,
                                        int32_t parameter_count, void *const *parameters,
                                        const uint64_t *element_counts, void **out_optimizer);
@@ -185,7 +209,7 @@ SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_finish(void *optimizer);
  * pending sum.  ACCUMULATE (1): pending = pending + gradient (one binary32 addition per element,
  * TrainingParameter.java:373-390); parameters, moments and the step count do not change.
  * ACCUMULATE_AND_STEP (2): update from pending + gradient, then clear the pending sum.  A non-finite
- * sum reports status 11 like any other non-finite intermediate.  zero_grad clears the pending sum
+ * sum reports status 11 like any other non-finite intermediate and leaves the pending sum as it was.  zero_grad clears the pending sum
  * (TrainingSession.zeroGrad, :640-652); accumulated_runs counts the runs in it. */
 enum { SYNAPTIK_CUDA_GRADIENT_RESET_AND_STEP = 0, SYNAPTIK_CUDA_GRADIENT_ACCUMULATE = 1, SYNAPTIK_CUDA_GRADIENT_ACCUMULATE_AND_STEP = 2 };
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_run(void *optimizer, int32_t gradient_mode, int32_t gradient_count, void *const *gradients);
@@ -213,7 +237,14 @@ SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_set_progress(void *optimizer, 
  * synaptik_cuda_comm_unique_id on rank 0 and distributed by the caller.  An executable with an
  * attached communicator sum-allreduces the listed publications (gradients) on the context's
  * communication stream as soon as each is final, overlapping the rest of the backward pass, and
- * run/finish return after the reductions. */
+ * run/finish return after the reductions.  attach_comm refuses (INCOMPATIBLE_RESOURCE) a publication
+ * that a later step of the same executable still reads.  The host never waits for a collective without
+ * a limit: finish, run and comm_allreduce_sum_f32 poll NCCL's asynchronous error state and, after the
+ * context option "comm_timeout_ms", mark the steps in flight as failed, abort the communicator and
+ * return COMM_FAILED; the communicator is unusable from then on (every call on it returns
+ * COMM_FAILED), the context and its buffers are not.  The environment variable
+ * SYNAPTIK_NCCL_LIBRARY names the NCCL library file to bind; when it is set and the file does not
+ * load, the communicator calls return COMM_FAILED (no other copy is looked for). */
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_comm_unique_id(uint8_t *out_id128);
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_comm_create(void *context, int32_t world_size, int32_t rank, const uint8_t *unique_id128,
                                   void **out_comm);

@@ -10,7 +10,8 @@ namespace syn {
 namespace kern {
 
 // Bits of the device-side error word (one per context, checked after each run).
-enum : int { ERR_LABEL_RANGE = 1, ERR_NON_FINITE = 2, ERR_WAIT_TIMEOUT = 4 };
+// ERR_COMM is written by the host, when it gives up on a collective, so that kernels queued behind it see a failure.
+enum : int { ERR_LABEL_RANGE = 1, ERR_NON_FINITE = 2, ERR_WAIT_TIMEOUT = 4, ERR_COMM = 8 };
 
 struct Index4 {                 // right-aligned rank-4 iteration space with per-operand element strides
     int64_t shape[4];
@@ -85,15 +86,32 @@ cudaError_t dense_cross_entropy_backward(cudaStream_t s, const float *logits, co
                                          float *grad, int scale_mode);
 
 // ---- optimizers -----------------------------------------------------------------------------
+// A step is a transaction, like the reference's stage / validate / commit (TrainingSession.java:1151-1171,
+// TrainingParameter.java:391-409): the kernels read the current parameter, moments and pending sum and
+// write CANDIDATES into a second set of arrays (p_out, m_out, v_out); nothing the step reads is
+// overwritten.  The host makes the candidate set current by exchanging pointers and exchanges them back
+// when the step turns out to have failed.  Every optimizer kernel first looks at the context's error
+// word: when an earlier launch has already reported a failure (a label outside its range, a bounded wait
+// that ran out, a non-finite intermediate of an earlier step) it writes nothing at all.  A kernel that
+// skips or fails records its sequence number in *failed_sequence (atomic minimum), so the host knows the
+// first step that did not take place.
 // acc: pending gradient sum of the tensor (TrainingParameter.java:373-390), used per `gradient_mode`:
-// 0 the step uses g (and clears acc when clear_acc is set), 2 the step uses acc + g and clears acc.
-struct TensorSlot { float *p; const float *g; float *m; float *v; int64_t count; float *acc; };
-struct SgdArgs { float lr, momentum, dampening, weight_decay; int nesterov, first_step, has_buffer, zero_buffer; int gradient_mode, clear_acc; };
-struct AdamArgs { float lr, b1, b2, eps, decay, correction1, correction2, decay_factor; int decoupled; int gradient_mode, clear_acc; };
+// 0 the step uses g, 2 the step uses acc + g.  The step kernels never write acc; clear_pending zeroes it
+// afterwards, and only when the error word is still clear.
+struct TensorSlot { const float *p; const float *g; const float *m; const float *v; int64_t count; float *acc; float *p_out, *m_out, *v_out; };
+struct SgdArgs { float lr, momentum, dampening, weight_decay; int nesterov, first_step, has_buffer, zero_buffer; int gradient_mode; int sequence; int *failed_sequence; };
+struct AdamArgs { float lr, b1, b2, eps, decay, correction1, correction2, decay_factor; int decoupled; int gradient_mode; int sequence; int *failed_sequence; };
 cudaError_t sgd_step(cudaStream_t s, const TensorSlot *slots, int slot_count, const SgdArgs &args, int *error_word);
 cudaError_t adam_step(cudaStream_t s, const TensorSlot *slots, int slot_count, const AdamArgs &args, int *error_word);
-// acc = acc + g for every tensor (GradientMode.ACCUMULATE), one launch; a non-finite sum sets ERR_NON_FINITE.
-cudaError_t accumulate_gradients(cudaStream_t s, const TensorSlot *slots, int slot_count, int *error_word);
+// acc = 0 for every tensor unless the error word is set (one launch, after the step kernel).
+cudaError_t clear_pending(cudaStream_t s, const TensorSlot *slots, int slot_count, int *error_word);
+// acc = acc + g for every tensor (GradientMode.ACCUMULATE) in two launches: the first only looks for a
+// non-finite sum (ERR_NON_FINITE, *failed_sequence), the second adds unless the error word is set.
+cudaError_t accumulate_gradients(cudaStream_t s, const TensorSlot *slots, int slot_count, int sequence, int *failed_sequence, int *error_word);
+// One block whose only work is a bounded wait on a barrier that nothing signals: the wait gives up after
+// limit_ns and the kernel sets ERR_WAIT_TIMEOUT and returns normally.  It runs the same wait routine as
+// the tensor-core GEMMs, whose limit is fixed at two seconds.
+cudaError_t wait_probe(cudaStream_t s, uint64_t limit_ns, int *error_word);
 
 // ---- GEMM -------------------------------------------------------------------------------------
 struct GemmEpilogue {

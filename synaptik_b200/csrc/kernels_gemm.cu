@@ -153,17 +153,38 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return done != 0;
 }
 // Bounded wait: returns false (after raising the block's abort flag) when the phase has not
-// completed within WAIT_LIMIT_NS or another role has already given up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+// completed within limit_ns or another role has already given up.
+__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, volatile int *abort_flag, uint64_t limit_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t start = global_timer();
     for (uint32_t spin = 0;; spin++) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((spin & 63u) == 63u) {
             if (*abort_flag) return false;
-            if (global_timer() - start > WAIT_LIMIT_NS) { *abort_flag = 1; return false; }
+            if (global_timer() - start > limit_ns) { *abort_flag = 1; return false; }
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    return mbar_wait_limited(bar, parity, abort_flag, WAIT_LIMIT_NS);
+}
+
+// The give-up path of the wait above, run on purpose: one warp waits for a phase of a barrier that
+// nothing ever completes, the wait expires after limit_ns, and the kernel reports it the way the GEMM
+// kernels do (abort flag -> ERR_WAIT_TIMEOUT in the context's error word) and returns normally.
+__global__ void __launch_bounds__(32) wait_probe_kernel(uint64_t limit_ns, int *error_word) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    bool ok = true;
+    if (threadIdx.x == 0) ok = mbar_wait_limited(smem_u32(&bar), 0u, &abort_flag, limit_ns);
+    __syncwarp();
+    if (threadIdx.x == 0 && (!ok || abort_flag)) atomicOr(error_word, ERR_WAIT_TIMEOUT);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
@@ -1045,6 +1066,12 @@ cudaError_t gemm_exact(cudaStream_t s, int64_t m, int64_t n, int64_t k, const fl
     dim3 grid((unsigned)((n + XT - 1) / XT), (unsigned)((m + XT - 1) / XT));
     if (grid.y > 65535) return cudaErrorInvalidValue;
     gemm_exact_kernel<<<grid, 256, 0, s>>>(m, n, k, a, a_ms, a_ks, b, b_ks, b_ns, c, c_ms, c_ns, ep);
+    return cudaGetLastError();
+}
+
+cudaError_t wait_probe(cudaStream_t s, uint64_t limit_ns, int *error_word) {
+    // never longer than the GEMM kernels' own limit
+    wait_probe_kernel<<<1, 32, 0, s>>>(limit_ns < WAIT_LIMIT_NS ? limit_ns : WAIT_LIMIT_NS, error_word);
     return cudaGetLastError();
 }
 

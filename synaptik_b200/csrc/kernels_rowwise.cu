@@ -1183,14 +1183,24 @@ __global__ void __launch_bounds__(kThreads, CHUNKS >= 8 ? 2 : 4) dense_ce_grad_r
 }
 
 // ---- optimizers --------------------------------------------------------------------------------
-constexpr int kMaxSlots = 48;
+constexpr int kMaxSlots = 40;       // the table travels as a kernel argument: 40 slots keep it under 4 KB
 struct SlotTable { TensorSlot slot[kMaxSlots]; int64_t first_block[kMaxSlots + 1]; int count; };
 constexpr int kOptElemsPerBlock = kThreads * 8;
 
 __device__ __forceinline__ bool finite(float x) { return (__float_as_uint(x) & 0x7f800000u) != 0x7f800000u; }
 
-// SGD, TrainingParameter.java:622-672: every product and sum is a separate binary32 rounding.
+// True when an earlier launch on this context has already reported a failure: the step this kernel
+// belongs to must then leave no trace.  The first thread records the step as not taken.
+__device__ __forceinline__ bool step_is_void(const int *error_word, int sequence, int *failed_sequence) {
+    if (*reinterpret_cast<const volatile int *>(error_word) == 0) return false;
+    if (blockIdx.x == 0 && threadIdx.x == 0) atomicMin(failed_sequence, sequence);
+    return true;
+}
+
+// SGD, TrainingParameter.java:622-672: every product and sum is a separate binary32 rounding.  Reads
+// p, m, acc, g; writes the candidates p_out, m_out.
 __global__ void __launch_bounds__(kThreads) sgd_kernel(SlotTable table, SgdArgs a, int *error_word) {
+    if (step_is_void(error_word, a.sequence, a.failed_sequence)) return;
     int t = 0;
     while (t + 1 < table.count && (int64_t)blockIdx.x >= table.first_block[t + 1]) t++;
     const TensorSlot s = table.slot[t];
@@ -1199,8 +1209,7 @@ __global__ void __launch_bounds__(kThreads) sgd_kernel(SlotTable table, SgdArgs 
     for (int64_t i = base + threadIdx.x; i < base + kOptElemsPerBlock && i < s.count; i += kThreads) {
         float p = s.p[i];
         float g = s.g[i];
-        if (a.gradient_mode == 2) { g = __fadd_rn(s.acc[i], g); bad |= !finite(g); s.acc[i] = 0.0f; }
-        else if (a.clear_acc) s.acc[i] = 0.0f;
+        if (a.gradient_mode == 2) { g = __fadd_rn(s.acc[i], g); bad |= !finite(g); }
         float decay_term = __fmul_rn(a.weight_decay, p);
         float adjusted = __fadd_rn(g, decay_term);
         float update = adjusted;
@@ -1208,21 +1217,23 @@ __global__ void __launch_bounds__(kThreads) sgd_kernel(SlotTable table, SgdArgs 
             float buf;
             if (a.first_step) buf = adjusted;
             else buf = __fadd_rn(__fmul_rn(a.momentum, s.m[i]), __fmul_rn(__fsub_rn(1.0f, a.dampening), adjusted));
-            s.m[i] = buf;
+            s.m_out[i] = buf;
             update = a.nesterov ? __fadd_rn(adjusted, __fmul_rn(a.momentum, buf)) : buf;
             bad |= !finite(buf);
-        } else if (a.zero_buffer) s.m[i] = 0.0f;
+        } else if (a.zero_buffer) s.m_out[i] = 0.0f;
         float scaled = __fmul_rn(a.lr, update);
         float candidate = __fsub_rn(p, scaled);
         bad |= !finite(p) || !finite(decay_term) || !finite(adjusted) || !finite(update) || !finite(scaled) || !finite(candidate);
-        s.p[i] = candidate;
+        s.p_out[i] = candidate;
     }
-    if (bad) atomicOr(error_word, ERR_NON_FINITE);
+    if (bad) { atomicOr(error_word, ERR_NON_FINITE); atomicMin(a.failed_sequence, a.sequence); }
 }
 
 // Adam / AdamW, TrainingParameter.java:433-525: m = b1*m + (1-b1)*g; v = b2*v + (1-b2)*(g*g);
-// update = (lr * (m / c1)) / (sqrt(v / c2) + eps), the product formed before the division.
+// update = (lr * (m / c1)) / (sqrt(v / c2) + eps), the product formed before the division.  Reads
+// p, m, v, acc, g; writes the candidates p_out, m_out, v_out (28 bytes per parameter either way).
 __global__ void __launch_bounds__(kThreads) adam_kernel(SlotTable table, AdamArgs a, int *error_word) {
+    if (step_is_void(error_word, a.sequence, a.failed_sequence)) return;
     int t = 0;
     while (t + 1 < table.count && (int64_t)blockIdx.x >= table.first_block[t + 1]) t++;
     const TensorSlot s = table.slot[t];
@@ -1231,8 +1242,7 @@ __global__ void __launch_bounds__(kThreads) adam_kernel(SlotTable table, AdamArg
     bool bad = false;
     for (int64_t i = base + threadIdx.x; i < base + kOptElemsPerBlock && i < s.count; i += kThreads) {
         float p = s.p[i], g = s.g[i], basev;
-        if (a.gradient_mode == 2) { g = __fadd_rn(s.acc[i], g); bad |= !finite(g); s.acc[i] = 0.0f; }
-        else if (a.clear_acc) s.acc[i] = 0.0f;
+        if (a.gradient_mode == 2) { g = __fadd_rn(s.acc[i], g); bad |= !finite(g); }
         if (a.decoupled) basev = __fmul_rn(p, a.decay_factor);
         else { g = __fadd_rn(g, __fmul_rn(a.decay, p)); basev = p; }
         float m = __fadd_rn(__fmul_rn(a.b1, s.m[i]), __fmul_rn(one_minus_b1, g));
@@ -1245,14 +1255,29 @@ __global__ void __launch_bounds__(kThreads) adam_kernel(SlotTable table, AdamArg
         float candidate = __fsub_rn(basev, update);
         bad |= !finite(p) || !finite(g) || !finite(m) || !finite(sq) || !finite(v) || !finite(mh) || !finite(vh)
                || !finite(den) || !(den > 0.0f) || !finite(num) || !finite(update) || !finite(candidate);
-        s.p[i] = candidate; s.m[i] = m; s.v[i] = v;
+        s.p_out[i] = candidate; s.m_out[i] = m; s.v_out[i] = v;
     }
-    if (bad) atomicOr(error_word, ERR_NON_FINITE);
+    if (bad) { atomicOr(error_word, ERR_NON_FINITE); atomicMin(a.failed_sequence, a.sequence); }
 }
 
-// GradientMode.ACCUMULATE (TrainingParameter.java:373-390): the pending sum takes one binary32 addition per run.
+// Zeroes the pending sums once the step that consumed (or dropped) them has gone through.
 struct NoArgs {};
-__global__ void __launch_bounds__(kThreads) accumulate_kernel(SlotTable table, NoArgs, int *error_word) {
+__global__ void __launch_bounds__(kThreads) clear_pending_kernel(SlotTable table, NoArgs, int *error_word) {
+    if (*reinterpret_cast<const volatile int *>(error_word) != 0) return;
+    int t = 0;
+    while (t + 1 < table.count && (int64_t)blockIdx.x >= table.first_block[t + 1]) t++;
+    const TensorSlot s = table.slot[t];
+    int64_t base = ((int64_t)blockIdx.x - table.first_block[t]) * kOptElemsPerBlock;
+    for (int64_t i = base + threadIdx.x; i < base + kOptElemsPerBlock && i < s.count; i += kThreads) s.acc[i] = 0.0f;
+}
+
+// GradientMode.ACCUMULATE (TrainingParameter.java:373-390): the pending sum takes one binary32 addition
+// per run.  COMMIT false: only looks for a non-finite sum; COMMIT true: adds, unless anything has failed.
+struct AccumulateArgs { int sequence; int *failed_sequence; };
+template <bool COMMIT>
+__global__ void __launch_bounds__(kThreads) accumulate_kernel(SlotTable table, AccumulateArgs a, int *error_word) {
+    if (COMMIT) { if (*reinterpret_cast<const volatile int *>(error_word) != 0) return; }
+    else if (step_is_void(error_word, a.sequence, a.failed_sequence)) return;
     int t = 0;
     while (t + 1 < table.count && (int64_t)blockIdx.x >= table.first_block[t + 1]) t++;
     const TensorSlot s = table.slot[t];
@@ -1260,10 +1285,9 @@ __global__ void __launch_bounds__(kThreads) accumulate_kernel(SlotTable table, N
     bool bad = false;
     for (int64_t i = base + threadIdx.x; i < base + kOptElemsPerBlock && i < s.count; i += kThreads) {
         float sum = __fadd_rn(s.acc[i], s.g[i]);
-        bad |= !finite(sum);
-        s.acc[i] = sum;
+        if (COMMIT) s.acc[i] = sum; else bad |= !finite(sum);
     }
-    if (bad) atomicOr(error_word, ERR_NON_FINITE);
+    if (bad) { atomicOr(error_word, ERR_NON_FINITE); atomicMin(a.failed_sequence, a.sequence); }
 }
 
 template <typename K, typename A>
@@ -1556,8 +1580,14 @@ cudaError_t sgd_step(cudaStream_t s, const TensorSlot *slots, int slot_count, co
 cudaError_t adam_step(cudaStream_t s, const TensorSlot *slots, int slot_count, const AdamArgs &args, int *error_word) {
     return launch_slots(s, adam_kernel, slots, slot_count, args, error_word);
 }
-cudaError_t accumulate_gradients(cudaStream_t s, const TensorSlot *slots, int slot_count, int *error_word) {
-    return launch_slots(s, accumulate_kernel, slots, slot_count, NoArgs{}, error_word);
+cudaError_t clear_pending(cudaStream_t s, const TensorSlot *slots, int slot_count, int *error_word) {
+    return launch_slots(s, clear_pending_kernel, slots, slot_count, NoArgs{}, error_word);
+}
+cudaError_t accumulate_gradients(cudaStream_t s, const TensorSlot *slots, int slot_count, int sequence, int *failed_sequence, int *error_word) {
+    AccumulateArgs args{sequence, failed_sequence};
+    cudaError_t e = launch_slots(s, accumulate_kernel<false>, slots, slot_count, args, error_word);
+    if (e != cudaSuccess) return e;
+    return launch_slots(s, accumulate_kernel<true>, slots, slot_count, args, error_word);
 }
 
 }  // namespace kern

@@ -4,9 +4,12 @@
 // does the same, modules/backend/metal/macos-arm64/README.md "Status values": 10).
 #include <cuda_runtime.h>
 #include <dlfcn.h>
+#include <time.h>
 
 #include <algorithm>
 #include <array>
+#include <chrono>
+#include <climits>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -27,6 +30,9 @@ namespace {
 enum : uint32_t { TAG_CONTEXT = 0x58544353u, TAG_BUFFER = 0x46554253u, TAG_EXECUTABLE = 0x45584553u,
                   TAG_OPTIMIZER = 0x54504f53u, TAG_COMM = 0x4d4f4353u };
 
+struct Optimizer;
+struct Comm;
+
 struct Context {
     uint32_t tag = TAG_CONTEXT;
     int device = 0;
@@ -42,6 +48,10 @@ struct Context {
     int gemm_dynamic = 1;                   // two-SM products take their tiles from a counter instead of a fixed assignment
     int gemm_slices = 1;                    // split long contractions of epilogue-free GEMMs when that shortens the last wave
     cudaEvent_t timer_start = nullptr, timer_stop = nullptr;
+    cudaEvent_t drained = nullptr;          // recorded behind the error-word copy of a drain; polled when a communicator exists
+    int64_t comm_timeout_ms = 30000;        // host-side deadline of every wait that has a collective in front of it
+    std::vector<Optimizer *> optimizers;    // a failed drain rolls their unfinished steps back
+    std::vector<Comm *> comms;
     std::mutex mutex;
 };
 
@@ -65,6 +75,8 @@ struct NcclApi {
     int (*AllReduce)(const void *, void *, size_t, int, int, void *, cudaStream_t) = nullptr;
     int (*GroupStart)() = nullptr;
     int (*GroupEnd)() = nullptr;
+    int (*CommGetAsyncError)(void *, int *) = nullptr;      // optional: polled while the host waits
+    int (*CommAbort)(void *) = nullptr;                     // optional: ends a collective that will never finish
     bool ok = false;
 };
 
@@ -72,11 +84,17 @@ NcclApi &nccl() {
     static NcclApi api;
     static std::once_flag once;
     std::call_once(once, [] {
-        void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD | RTLD_GLOBAL);   // the copy the process already uses, if any
+        // An explicit path decides alone (a file that does not load leaves the communicator unavailable,
+        // it is not replaced by another copy); otherwise the copy the process already uses, then the
+        // loader's own search.
         const char *env = getenv("SYNAPTIK_NCCL_LIBRARY");
-        if (!h && env && env[0]) h = dlopen(env, RTLD_NOW | RTLD_GLOBAL);
-        if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
-        if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        void *h = nullptr;
+        if (env && env[0]) h = dlopen(env, RTLD_NOW | RTLD_GLOBAL);
+        else {
+            h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD | RTLD_GLOBAL);
+            if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+            if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        }
         if (!h) return;
         api.GetUniqueId = (decltype(api.GetUniqueId))dlsym(h, "ncclGetUniqueId");
         api.CommInitRank = (decltype(api.CommInitRank))dlsym(h, "ncclCommInitRank");
@@ -84,6 +102,8 @@ NcclApi &nccl() {
         api.AllReduce = (decltype(api.AllReduce))dlsym(h, "ncclAllReduce");
         api.GroupStart = (decltype(api.GroupStart))dlsym(h, "ncclGroupStart");
         api.GroupEnd = (decltype(api.GroupEnd))dlsym(h, "ncclGroupEnd");
+        api.CommGetAsyncError = (decltype(api.CommGetAsyncError))dlsym(h, "ncclCommGetAsyncError");
+        api.CommAbort = (decltype(api.CommAbort))dlsym(h, "ncclCommAbort");
         api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllReduce && api.GroupStart && api.GroupEnd;
     });
     return api;
@@ -94,6 +114,7 @@ struct Comm {
     Context *ctx = nullptr;
     void *comm = nullptr;
     int world = 1, rank = 0;
+    bool dead = false;                      // aborted after a deadline or an asynchronous error: every later use fails
 };
 
 struct Planes { float *hi = nullptr, *lo = nullptr; int64_t rows = 0, kp = 0, pitch = 0; int last_run = -1; };
@@ -154,11 +175,21 @@ struct Optimizer {
     std::vector<Buffer *> params;
     std::vector<uint64_t> counts;
     std::vector<float *> m, v;
+    // A step writes candidates into the second set and the host then exchanges the sets (for the
+    // parameters: the device pointers of the caller's buffer handles); a failed step is undone by
+    // exchanging them back, so what the step read is what is current again.
+    std::vector<float *> p_alt, m_alt, v_alt;
     std::vector<float *> acc;               // pending gradient sums, allocated on the first accumulating run
     uint64_t steps = 0;
     uint64_t accumulated_runs = 0;          // runs in the pending sum (TrainingSession.java:593-594)
     bool acc_dirty = false;                 // the pending sums may be non-zero
     bool pending = false;
+    // Runs enqueued since the last drain of the context's error word, oldest first, each with the host
+    // counters as they were before it.  The kernels of run i carry sequence number i; the device keeps
+    // the smallest sequence number that skipped or failed in *failed_dev.
+    struct Entry { bool stepped; uint64_t steps, accumulated_runs; bool acc_dirty; };
+    std::vector<Entry> journal;
+    int *failed_dev = nullptr;
 };
 
 template <typename T> T *as(void *h, uint32_t tag) {
@@ -175,19 +206,103 @@ int32_t cuda_status(cudaError_t e, int32_t fallback) {
 }
 
 int32_t error_word_status(int word) {
+    if (word & kern::ERR_COMM) return COMM_FAILED;
     if (word & kern::ERR_WAIT_TIMEOUT) return TIMEOUT;
     if (word & kern::ERR_LABEL_RANGE) return RANGE_OUT_OF_BOUNDS;
     if (word & kern::ERR_NON_FINITE) return EXECUTION_FAILED;
     return OK;
 }
 
-// Reads and clears the device error word; the stream is synchronised on return.
+constexpr int kNoFailedSequence = 0x7f7f7f7f;       // what cudaMemset(.., 0x7f, 4) leaves: larger than any sequence number
+
+// Makes the candidate set of an optimizer current, or the previous set current again (the exchange is
+// its own inverse).  The parameter pointers live in the caller's buffer handles.
+void exchange_sets(Optimizer *o) {
+    for (size_t i = 0; i < o->params.size(); i++) {
+        void *current = o->params[i]->ptr;
+        o->params[i]->ptr = o->p_alt[i];
+        o->p_alt[i] = (float *)current;
+        if (o->m[i]) std::swap(o->m[i], o->m_alt[i]);
+        if (o->v[i]) std::swap(o->v[i], o->v_alt[i]);
+    }
+}
+
+// After a drain (the compute stream is idle).  A clean drain makes every enqueued step final.  A failed
+// one undoes, per optimizer, every run from the first that skipped or failed: those kernels wrote
+// candidates at most, so putting the pointers and the host counters back restores parameters, moments,
+// pending sums and step count to the bits they had before that run.
+void settle_optimizers(Context *ctx, bool failed) {
+    for (Optimizer *o : ctx->optimizers) {
+        if (o->journal.empty()) continue;
+        if (failed) {
+            int first = kNoFailedSequence;
+            if (cudaMemcpy(&first, o->failed_dev, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); first = 0; }
+            cudaMemset(o->failed_dev, 0x7f, sizeof(int));
+            if (first >= 0 && first < (int)o->journal.size()) {
+                int undone = 0;
+                for (size_t i = (size_t)first; i < o->journal.size(); i++) undone += o->journal[i].stepped ? 1 : 0;
+                if (undone & 1) exchange_sets(o);
+                const Optimizer::Entry &before = o->journal[first];
+                o->steps = before.steps; o->accumulated_runs = before.accumulated_runs; o->acc_dirty = before.acc_dirty;
+            }
+        }
+        o->journal.clear();
+    }
+}
+
+// Waits for `event` (recorded on the compute stream) while a communicator exists: the host polls
+// instead of blocking, looks at NCCL's asynchronous error state and gives up after the context's
+// comm_timeout_ms.  Giving up marks the context's error word (so that optimizer steps queued behind the
+// collective become void), aborts the communicators, which ends their kernels, and then lets the
+// streams run dry.  Returns OK or COMM_FAILED with the streams idle either way.
+int32_t wait_with_deadline(Context *ctx, cudaEvent_t event) {
+    const auto start = std::chrono::steady_clock::now();
+    bool failed = false;
+    for (uint64_t spin = 0;; spin++) {
+        cudaError_t q = cudaEventQuery(event);
+        if (q == cudaSuccess) return OK;
+        if (q != cudaErrorNotReady) { cudaGetLastError(); return EXECUTION_FAILED; }
+        if ((spin & 127u) != 127u) continue;
+        for (Comm *c : ctx->comms) {
+            int async = 0;
+            if (c->dead) failed = true;
+            else if (nccl().CommGetAsyncError && nccl().CommGetAsyncError(c->comm, &async) == 0 && async != 0 && async != 7 /*ncclInProgress*/) failed = true;
+        }
+        const auto waited = std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - start).count();
+        if (waited > ctx->comm_timeout_ms * 1000) failed = true;
+        if (failed) break;
+        if (waited > 5000) {            // a long wait: stop spinning at full speed
+            struct timespec nap = {0, 50000};
+            nanosleep(&nap, nullptr);
+        }
+    }
+    int word = kern::ERR_COMM;
+    if (cudaMemcpyAsync(ctx->error_dev, &word, sizeof(int), cudaMemcpyHostToDevice, ctx->copy_stream) == cudaSuccess) cudaStreamSynchronize(ctx->copy_stream);
+    for (Comm *c : ctx->comms) {
+        if (!c->dead && nccl().CommAbort) { nccl().CommAbort(c->comm); c->comm = nullptr; }
+        c->dead = true;
+    }
+    cudaStreamSynchronize(ctx->comm_stream);
+    cudaStreamSynchronize(ctx->stream);
+    cudaGetLastError();
+    return COMM_FAILED;
+}
+
+// Reads and clears the device error word; the stream is synchronised on return.  A failure undoes the
+// optimizer steps that did not take place (settle_optimizers).
 int32_t drain_errors(Context *ctx) {
     cudaError_t e = cudaMemcpyAsync(ctx->error_host, ctx->error_dev, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream);
     if (e == cudaSuccess) e = cudaMemsetAsync(ctx->error_dev, 0, sizeof(int), ctx->stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
-    if (e != cudaSuccess) { cudaGetLastError(); return EXECUTION_FAILED; }
-    return error_word_status(*ctx->error_host);
+    int32_t status = OK;
+    if (e == cudaSuccess && !ctx->comms.empty()) {
+        if (!ctx->drained) e = cudaEventCreateWithFlags(&ctx->drained, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventRecord(ctx->drained, ctx->stream);
+        if (e == cudaSuccess) status = wait_with_deadline(ctx, ctx->drained);
+    } else if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) { cudaGetLastError(); status = EXECUTION_FAILED; }
+    if (status == OK) status = error_word_status(*ctx->error_host);
+    settle_optimizers(ctx, status != OK);
+    return status;
 }
 
 struct DeviceGuard {
@@ -339,7 +454,12 @@ int32_t prepare_executable(Executable *x) {
         StepExec &se = x->exec[i];
         // worth it only when the producer's main loop is long enough to hide the extra stores behind
         // the next tile (measured: a K = 784 producer doubles in time, K = 4096 producers gain)
-        if (st.kind != StepKind::GEMM || st.engine != GemmEngine::TENSOR_CORE || se.swapped || !ctx->fused_planes || ctx->gemm_promote || st.k < 2048) continue;
+        // (with FP32 promotion the epilogue warps also add the partial sums, and the extra stores bought
+        // nothing: fused_planes = 2 asks for them all the same.)  A product whose contraction is split into
+        // slices has no epilogue of its own: its planes are written by the ordinary split pass.
+        if (st.kind != StepKind::GEMM || st.engine != GemmEngine::TENSOR_CORE || se.swapped || !ctx->fused_planes || st.k < 2048) continue;
+        if (ctx->gemm_promote && ctx->fused_planes < 2) continue;
+        if (kern::tc_gemm_launches(se.tc) > 1) continue;
         const View &u = plan.views[st.out2 >= 0 ? st.out2 : st.out];
         if (u.shape.size() != 2 || !u.dense()) continue;
         auto normal = x->plane_index.find(plane_key(u, 0));
@@ -575,7 +695,7 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
             cudaStreamWaitEvent(ctx->comm_stream, ev, 0);
             Buffer *buf = bind.publications[j];
             uint64_t count = x->publication_bytes[j] / 4;
-            if (nccl().AllReduce(buf->ptr, buf->ptr, count, /*ncclFloat32*/ 7, /*ncclSum*/ 0, x->comm->comm, ctx->comm_stream) != 0) return COMM_FAILED;
+            if (x->comm->dead || nccl().AllReduce(buf->ptr, buf->ptr, count, /*ncclFloat32*/ 7, /*ncclSum*/ 0, x->comm->comm, ctx->comm_stream) != 0) return COMM_FAILED;
         }
     }
     if (x->comm && ready_cursor > 0) {
@@ -676,6 +796,7 @@ int32_t synaptik_cuda_context_release(void *context) {
     cudaFreeHost(ctx->error_host);
     if (ctx->timer_start) cudaEventDestroy(ctx->timer_start);
     if (ctx->timer_stop) cudaEventDestroy(ctx->timer_stop);
+    if (ctx->drained) cudaEventDestroy(ctx->drained);
     ctx->tag = 0;
     delete ctx;
     return OK;
@@ -689,7 +810,8 @@ int32_t synaptik_cuda_context_set_option(void *context, const char *name, int64_
     if (!strcmp(name, "gemm_slices")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->gemm_slices = (int)value; return OK; }
     if (!strcmp(name, "gemm_pair")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->gemm_pair = (int)value; return OK; }
     if (!strcmp(name, "gemm_promote")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->gemm_promote = (int)value; return OK; }
-    if (!strcmp(name, "fused_planes")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->fused_planes = (int)value; return OK; }
+    if (!strcmp(name, "fused_planes")) { if (value < 0 || value > 2) return INVALID_ARGUMENT; ctx->fused_planes = (int)value; return OK; }
+    if (!strcmp(name, "comm_timeout_ms")) { if (value < 1 || value > 3600000) return INVALID_ARGUMENT; ctx->comm_timeout_ms = value; return OK; }
     if (!strcmp(name, "time_steps")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->time_steps = (int)value; return OK; }
     return INVALID_ARGUMENT;
 }
@@ -758,12 +880,15 @@ static int32_t transfer(void *buffer, uint64_t offset, void *host, uint64_t byte
     if (!b || (!host && bytes)) return INVALID_ARGUMENT;
     if (offset > b->bytes || bytes > b->bytes - offset) return RANGE_OUT_OF_BOUNDS;
     if (!bytes) return OK;
+    std::lock_guard<std::mutex> lock(b->ctx->mutex);
     DeviceGuard guard(b->ctx->device);
     uint8_t *dev = (uint8_t *)b->ptr + offset;
     if (b->fill_pending) { cudaStreamWaitEvent(b->ctx->stream, b->filled, 0); b->fill_pending = false; }
     cudaError_t e = upload ? cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, b->ctx->stream)
                            : cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, b->ctx->stream);
     if (e == cudaSuccess && !async) e = cudaStreamSynchronize(b->ctx->stream);
+    // a later prefetch into this buffer has to wait for a copy that is still in flight
+    if (e == cudaSuccess && async && b->released) { cudaEventRecord(b->released, b->ctx->stream); b->release_recorded = true; }
     if (e != cudaSuccess) { cudaGetLastError(); return COPY_FAILED; }
     return OK;
 }
@@ -791,9 +916,12 @@ int32_t synaptik_cuda_buffer_prefetch(void *buffer, uint64_t offset, const void 
     DeviceGuard guard(ctx->device);
     if (!b->filled && (cudaEventCreateWithFlags(&b->filled, cudaEventDisableTiming) != cudaSuccess
                        || cudaEventCreateWithFlags(&b->released, cudaEventDisableTiming) != cudaSuccess)) { cudaGetLastError(); return INTERNAL_ERROR; }
-    // the copy may not overtake the runs already enqueued that read or write this buffer
+    // The copy may not overtake the runs and copies already enqueued that read or write this buffer.
+    // Runs record `released` only for buffers that have these events, so the first prefetch into a
+    // buffer records it here, behind everything the compute stream holds so far.
     cudaError_t e = cudaSuccess;
-    if (b->release_recorded) e = cudaStreamWaitEvent(ctx->copy_stream, b->released, 0);
+    if (!b->release_recorded) { e = cudaEventRecord(b->released, ctx->stream); b->release_recorded = true; }
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->copy_stream, b->released, 0);
     if (e == cudaSuccess) e = cudaMemcpyAsync((uint8_t *)b->ptr + offset, source, bytes, cudaMemcpyHostToDevice, ctx->copy_stream);
     if (e == cudaSuccess) e = cudaEventRecord(b->filled, ctx->copy_stream);
     if (e != cudaSuccess) { cudaGetLastError(); return COPY_FAILED; }
@@ -970,25 +1098,35 @@ int32_t synaptik_cuda_optimizer_create(void *context, int32_t kind, const double
     DeviceGuard guard(ctx->device);
     bool need_m = kind != 0 || hyper[1] != 0.0, need_v = kind != 0;
     int32_t status = OK;
+    std::lock_guard<std::mutex> lock(ctx->mutex);
+    auto zeroed = [&](uint64_t bytes, float **out) {
+        if (cudaMalloc(out, bytes) != cudaSuccess || cudaMemsetAsync(*out, 0, bytes, ctx->stream) != cudaSuccess) status = ALLOCATION_FAILED;
+    };
     for (int i = 0; i < parameter_count && status == OK; i++) {
         Buffer *b = as<Buffer>(parameters[i], TAG_BUFFER);
         if (!b) { status = INVALID_ARGUMENT; break; }
         if (b->ctx != ctx || b->bytes < element_counts[i] * 4) { status = INCOMPATIBLE_RESOURCE; break; }
         o->params.push_back(b); o->counts.push_back(element_counts[i]);
-        float *m = nullptr, *v = nullptr;
+        float *m = nullptr, *v = nullptr, *p2 = nullptr, *m2 = nullptr, *v2 = nullptr;
         uint64_t bytes = element_counts[i] ? element_counts[i] * 4 : 4;
-        if (need_m && (cudaMalloc(&m, bytes) != cudaSuccess || cudaMemsetAsync(m, 0, bytes, ctx->stream) != cudaSuccess)) status = ALLOCATION_FAILED;
-        if (status == OK && need_v && (cudaMalloc(&v, bytes) != cudaSuccess || cudaMemsetAsync(v, 0, bytes, ctx->stream) != cudaSuccess)) status = ALLOCATION_FAILED;
-        o->m.push_back(m); o->v.push_back(v);
+        if (need_m) { zeroed(bytes, &m); if (status == OK) zeroed(bytes, &m2); }
+        if (status == OK && need_v) { zeroed(bytes, &v); if (status == OK) zeroed(bytes, &v2); }
+        // the second parameter array has the buffer's full size and starts as a copy of it, so whatever the
+        // buffer holds past the parameter's elements is in both
+        if (status == OK && (cudaMalloc(&p2, b->bytes ? b->bytes : 4) != cudaSuccess
+                             || (b->bytes && cudaMemcpyAsync(p2, b->ptr, b->bytes, cudaMemcpyDeviceToDevice, ctx->stream) != cudaSuccess))) status = ALLOCATION_FAILED;
+        o->m.push_back(m); o->v.push_back(v); o->p_alt.push_back(p2); o->m_alt.push_back(m2); o->v_alt.push_back(v2);
     }
+    if (status == OK && (cudaMalloc(&o->failed_dev, sizeof(int)) != cudaSuccess || cudaMemsetAsync(o->failed_dev, 0x7f, sizeof(int), ctx->stream) != cudaSuccess)) status = ALLOCATION_FAILED;
     if (status == OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) status = EXECUTION_FAILED;
     if (status != OK) {
         cudaGetLastError();
-        for (float *p : o->m) cudaFree(p);
-        for (float *p : o->v) cudaFree(p);
+        for (auto *set : {&o->m, &o->v, &o->p_alt, &o->m_alt, &o->v_alt}) for (float *q : *set) cudaFree(q);
+        cudaFree(o->failed_dev);
         delete o;
         return status;
     }
+    ctx->optimizers.push_back(o);
     *out_optimizer = o;
     return OK;
 }
@@ -996,11 +1134,15 @@ int32_t synaptik_cuda_optimizer_create(void *context, int32_t kind, const double
 int32_t synaptik_cuda_optimizer_release(void *optimizer) {
     Optimizer *o = as<Optimizer>(optimizer, TAG_OPTIMIZER);
     if (!o) return INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(o->ctx->mutex);
     DeviceGuard guard(o->ctx->device);
-    cudaStreamSynchronize(o->ctx->stream);
-    for (float *p : o->m) cudaFree(p);
-    for (float *p : o->v) cudaFree(p);
-    for (float *p : o->acc) cudaFree(p);
+    // steps still in flight are settled first, so the parameter buffers are left holding a committed state
+    if (!o->journal.empty()) drain_errors(o->ctx);
+    else cudaStreamSynchronize(o->ctx->stream);
+    auto &list = o->ctx->optimizers;
+    list.erase(std::remove(list.begin(), list.end(), o), list.end());
+    for (auto *set : {&o->m, &o->v, &o->p_alt, &o->m_alt, &o->v_alt, &o->acc}) for (float *q : *set) cudaFree(q);
+    cudaFree(o->failed_dev);
     o->tag = 0;
     delete o;
     return OK;
@@ -1021,19 +1163,26 @@ static int32_t optimizer_enqueue(void *optimizer, int32_t mode, int32_t gradient
             o->acc.push_back((float *)p);
         }
     }
+    if (o->journal.size() >= 65536) {        // a caller that never finishes: settle what is in flight
+        int32_t settled = drain_errors(o->ctx);
+        if (settled != OK) return settled;
+    }
     std::vector<kern::TensorSlot> slots(o->params.size());
     for (size_t i = 0; i < slots.size(); i++) {
         Buffer *g = as<Buffer>(gradients[i], TAG_BUFFER);
         if (!g) return INVALID_ARGUMENT;
         if (g->ctx != o->ctx || g->bytes < o->counts[i] * 4 || g == o->params[i]) return INCOMPATIBLE_RESOURCE;
-        slots[i] = {(float *)o->params[i]->ptr, (const float *)g->ptr, o->m[i], o->v[i], (int64_t)o->counts[i],
-                    o->acc.empty() ? nullptr : o->acc[i]};
+        slots[i] = {(const float *)o->params[i]->ptr, (const float *)g->ptr, o->m[i], o->v[i], (int64_t)o->counts[i],
+                    o->acc.empty() ? nullptr : o->acc[i], o->p_alt[i], o->m_alt[i], o->v_alt[i]};
     }
     cudaError_t e;
-    const int clear_acc = mode == 0 && o->acc_dirty;       // RESET_AND_STEP drops an earlier pending sum
+    cudaStream_t stream = o->ctx->stream;
+    const int sequence = (int)o->journal.size();
+    const Optimizer::Entry before{mode != 1, o->steps, o->accumulated_runs, o->acc_dirty};
     if (mode == 1) {
-        e = kern::accumulate_gradients(o->ctx->stream, slots.data(), (int)slots.size(), o->ctx->error_dev);
+        e = kern::accumulate_gradients(stream, slots.data(), (int)slots.size(), sequence, o->failed_dev, o->ctx->error_dev);
         if (e != cudaSuccess) { cudaGetLastError(); return EXECUTION_FAILED; }
+        o->journal.push_back(before);
         o->accumulated_runs++;
         o->acc_dirty = true;
         o->pending = true;
@@ -1044,8 +1193,8 @@ static int32_t optimizer_enqueue(void *optimizer, int32_t mode, int32_t gradient
         a.lr = (float)o->hyper[0]; a.momentum = (float)o->hyper[1]; a.dampening = (float)o->hyper[2]; a.weight_decay = (float)o->hyper[3];
         a.nesterov = o->hyper[4] != 0.0; a.first_step = o->steps == 0; a.has_buffer = o->hyper[1] != 0.0;
         a.zero_buffer = o->hyper[1] != 0.0 && a.momentum == 0.0f;
-        a.gradient_mode = mode; a.clear_acc = clear_acc;
-        e = kern::sgd_step(o->ctx->stream, slots.data(), (int)slots.size(), a, o->ctx->error_dev);
+        a.gradient_mode = mode; a.sequence = sequence; a.failed_sequence = o->failed_dev;
+        e = kern::sgd_step(stream, slots.data(), (int)slots.size(), a, o->ctx->error_dev);
     } else {
         // coefficients narrowed to binary32 first (AdaptiveCoefficients.java:33-58); corrections
         // 1f - (float)Math.pow(beta, step) evaluated in binary64 on the narrowed beta
@@ -1058,10 +1207,17 @@ static int32_t optimizer_enqueue(void *optimizer, int32_t mode, int32_t gradient
         a.decoupled = o->kind == 2;
         a.decay_factor = 1.0f;
         if (a.decoupled) { float scale = a.lr * a.decay; a.decay_factor = 1.0f - scale; }
-        a.gradient_mode = mode; a.clear_acc = clear_acc;
-        e = kern::adam_step(o->ctx->stream, slots.data(), (int)slots.size(), a, o->ctx->error_dev);
+        a.gradient_mode = mode; a.sequence = sequence; a.failed_sequence = o->failed_dev;
+        e = kern::adam_step(stream, slots.data(), (int)slots.size(), a, o->ctx->error_dev);
     }
+    // the pending sum is consumed (ACCUMULATE_AND_STEP) or dropped (RESET_AND_STEP after accumulating
+    // runs) only once the step has gone through: a second launch, which the error word turns into a no-op
+    if (e == cudaSuccess && o->acc_dirty && !o->acc.empty()) e = kern::clear_pending(stream, slots.data(), (int)slots.size(), o->ctx->error_dev);
     if (e != cudaSuccess) { cudaGetLastError(); return EXECUTION_FAILED; }
+    // The candidates become current at once, so that runs enqueued behind this step read them; the
+    // exchange and the counters are taken back by the next drain if the step did not take place.
+    o->journal.push_back(before);
+    exchange_sets(o);
     o->steps++;
     o->accumulated_runs = 0;
     o->acc_dirty = false;
@@ -1205,6 +1361,10 @@ int32_t synaptik_cuda_comm_create(void *context, int32_t world_size, int32_t ran
     if (nccl().CommInitRank(&comm, world_size, id, rank) != 0 || !comm) return COMM_FAILED;
     Comm *c = new Comm();
     c->ctx = ctx; c->comm = comm; c->world = world_size; c->rank = rank;
+    {
+        std::lock_guard<std::mutex> lock(ctx->mutex);
+        ctx->comms.push_back(c);
+    }
     *out_comm = c;
     return OK;
 }
@@ -1212,9 +1372,12 @@ int32_t synaptik_cuda_comm_create(void *context, int32_t world_size, int32_t ran
 int32_t synaptik_cuda_comm_release(void *comm) {
     Comm *c = as<Comm>(comm, TAG_COMM);
     if (!c) return INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(c->ctx->mutex);
     DeviceGuard guard(c->ctx->device);
     cudaStreamSynchronize(c->ctx->comm_stream);
-    nccl().CommDestroy(c->comm);
+    if (c->comm) nccl().CommDestroy(c->comm);       // an aborted communicator is already gone
+    auto &list = c->ctx->comms;
+    list.erase(std::remove(list.begin(), list.end(), c), list.end());
     c->tag = 0;
     delete c;
     return OK;
@@ -1228,7 +1391,9 @@ int32_t synaptik_cuda_comm_allreduce_sum_f32(void *comm, void *buffer, uint64_t 
     if (offset % 4 || offset > b->bytes || element_count * 4 > b->bytes - offset) return RANGE_OUT_OF_BOUNDS;
     std::lock_guard<std::mutex> lock(c->ctx->mutex);
     DeviceGuard guard(c->ctx->device);
-    // ordered after the compute stream's earlier work, executed on the communication stream
+    if (c->dead) return COMM_FAILED;
+    // ordered after the compute stream's earlier work, executed on the communication stream, and the
+    // compute stream continues behind it
     cudaEvent_t ev;
     if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return INTERNAL_ERROR;
     cudaEventRecord(ev, c->ctx->stream);
@@ -1237,10 +1402,11 @@ int32_t synaptik_cuda_comm_allreduce_sum_f32(void *comm, void *buffer, uint64_t 
     int rc = nccl().AllReduce(p, p, element_count, 7, 0, c->comm, c->ctx->comm_stream);
     cudaEventRecord(ev, c->ctx->comm_stream);
     cudaStreamWaitEvent(c->ctx->stream, ev, 0);
-    cudaError_t e = cudaStreamSynchronize(c->ctx->comm_stream);
+    // the host waits with the context's deadline; whatever else was in flight on the context is settled too
+    int32_t status = drain_errors(c->ctx);
     cudaEventDestroy(ev);
-    if (rc != 0 || e != cudaSuccess) { cudaGetLastError(); return COMM_FAILED; }
-    return OK;
+    if (rc != 0) return COMM_FAILED;
+    return status;
 }
 
 int32_t synaptik_cuda_executable_attach_comm(void *executable, void *comm, int32_t output_count, const int32_t *output_indices) {
@@ -1257,9 +1423,35 @@ int32_t synaptik_cuda_executable_attach_comm(void *executable, void *comm, int32
         if (x->program.values[x->program.publications[j]].dtype != DType::F32) return INCOMPATIBLE_RESOURCE;
         flags[j] = 1;
     }
+    // The reduction runs in place on the communication stream as soon as the publication is final, while
+    // the compute stream goes on: a publication that a later step of the plan still reads would be read
+    // half reduced.
+    for (size_t ready = 0; ready < x->plan.steps.size(); ready++)
+        for (int j : x->plan.steps[ready].ready_publications) {
+            if (!flags[j]) continue;
+            for (size_t later = ready + 1; later < x->plan.steps.size(); later++) {
+                const Step &st = x->plan.steps[later];
+                for (int value : {st.a, st.b, st.c, st.bias, st.mask}) {
+                    if (value < 0) continue;
+                    const View &v = x->plan.views[value];
+                    if (v.slot == SlotKind::PUBLICATION && v.index == j) return INCOMPATIBLE_RESOURCE;
+                }
+            }
+        }
     x->comm = c;
     x->sync_publication = flags;
     return OK;
+}
+
+// Runs the give-up path of the device-side waits on purpose (see kern::wait_probe): the status is TIMEOUT
+// and the context stays usable.
+int32_t synaptik_cuda_context_wait_probe(void *context, uint64_t limit_microseconds) {
+    Context *ctx = as<Context>(context, TAG_CONTEXT);
+    if (!ctx || limit_microseconds < 1 || limit_microseconds > 2000000) return INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(ctx->mutex);
+    DeviceGuard guard(ctx->device);
+    if (kern::wait_probe(ctx->stream, limit_microseconds * 1000ull, ctx->error_dev) != cudaSuccess) { cudaGetLastError(); return EXECUTION_FAILED; }
+    return drain_errors(ctx);
 }
 
 // Column sums whose scratch lives in a static device array: no allocation of any kind on this path

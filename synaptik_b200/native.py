@@ -28,7 +28,7 @@ STATUS_NAMES = {
 SYMBOLS = [
     "synaptik_cuda_abi_version", "synaptik_cuda_context_create", "synaptik_cuda_context_release",
     "synaptik_cuda_context_set_option", "synaptik_cuda_context_synchronize",
-    "synaptik_cuda_context_timer_start", "synaptik_cuda_context_timer_stop",
+    "synaptik_cuda_context_timer_start", "synaptik_cuda_context_timer_stop", "synaptik_cuda_context_wait_probe",
     "synaptik_cuda_executable_describe", "synaptik_cuda_executable_step_timings",
     "synaptik_cuda_buffer_create", "synaptik_cuda_buffer_release", "synaptik_cuda_buffer_upload",
     "synaptik_cuda_buffer_download", "synaptik_cuda_buffer_upload_canonical",
@@ -107,6 +107,10 @@ class Context:
         ms = ctypes.c_double()
         _check("context_timer_stop", library().synaptik_cuda_context_timer_stop(self._h, ctypes.byref(ms)))
         return float(ms.value)
+
+    def wait_probe(self, limit_microseconds: int) -> None:
+        """Runs the give-up path of the device-side bounded waits; always raises NativeFailure(14)."""
+        _check("context_wait_probe", library().synaptik_cuda_context_wait_probe(self._h, ctypes.c_uint64(limit_microseconds)))
 
     def buffer(self, nbytes: int) -> "Buffer":
         return Buffer(self, nbytes)
