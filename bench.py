@@ -1,22 +1,29 @@
-"""Benchmark of the data-parallel MLP training step (BASELINE.json configs[4]).
+"""Benchmark of the data-parallel MLP training step and of the kernels under it.
 
     python bench.py --gpus N --steps K --warmup W            # the CUDA backend, one rank per GPU
     python bench.py --impl reference --gpus N --steps K ...  # the reference-shaped CPU path
+    python bench.py --case gemm --m 65536 --k 4096 --n 4096  # one kernel case alone (also the ncu workloads)
 
-Workload: 784 -> 4096 -> 4096 -> 4096 -> 10 Linear/ReLU classifier, softmax cross-entropy, Adam
-(1e-3, 0.9, 0.999, 1e-8), global batch 65536 split evenly over the ranks, gradients sum-allreduced
-with NCCL over NVLink overlapped with the backward pass, FP32 (GEMMs in 3xTF32 on tcgen05).
-Synthetic seeded data: x ~ U(0,1), labels ~ U{0..9}, Glorot-uniform weights, zero biases.
+Workload of the headline line: 784 -> 4096 -> 4096 -> 4096 -> 10 Linear/ReLU classifier, softmax
+cross-entropy, Adam (1e-3, 0.9, 0.999, 1e-8), global batch 65536 split evenly over the ranks,
+gradients sum-allreduced with NCCL over NVLink overlapped with the backward pass, FP32 (GEMMs in 3xTF32
+on tcgen05).  Synthetic seeded data: x ~ U(0,1), labels ~ U{0..9}, Glorot-uniform weights, zero biases.
+The batch is a function of the global row index alone, so every number of ranks trains on the same
+65536 rows; `config.final_loss` and `config.parameter_checksums` are therefore comparable across N.
 
 One JSON line is printed by rank 0.  `value` times K steps with the batch already resident in HBM;
 `e2e` times K steps through the same C-ABI calls with the batch uploaded from pinned host memory
-and the loss read back every step.
+and the loss read back every step.  Further records on the same line: `inference` (the same network,
+forward and row arg-max, 8192 rows per GPU, weights replicated, no collective), `kernels` (the
+standalone dense layer and classifier-head cases, one GPU only), `tf32_peak` (a cuBLAS TF32 GEMM timed
+in this run, the direct denominator of the 3xTF32 roofline), `cpu_baseline`.
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
+import re
 import subprocess
 import sys
 import threading
@@ -30,9 +37,17 @@ if ROOT not in sys.path:
 
 DIMS = [784, 4096, 4096, 4096, 10]
 GLOBAL_BATCH = 65536
+INFERENCE_ROWS_PER_GPU = 8192
 ADAM = dict(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8)
 METRIC = "mlp_train_samples_per_s"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+DATA_BLOCK = 1024       # rows per independently seeded block of the synthetic batch
+
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch of the two-SM 3xTF32 kernel, from
+# an ncu capture of the forward product [8192 x 4096] . [4096 x 4096]^T of this build (`--case gemm
+# --m 8192 --forward-only`).  A 65536-row launch re-reads the weight planes once per group of row bands
+# from L2, so its traffic is the activation-plane and result terms times eight plus the weight term once.
+NCU_TRAFFIC_8192 = {"total": 1.43e9, "weight_term": 2 * 2 * 4096 * 4128 * 4.0, "algorithmic": 4.0 * (8192 * 4096 + 4096 * 4096 + 4096 + 8192 * 4096)}
 
 
 def step_flops(batch: int) -> float:
@@ -41,28 +56,40 @@ def step_flops(batch: int) -> float:
     return 6.0 * batch * weights - 2.0 * batch * DIMS[0] * DIMS[1]
 
 
+def forward_flops(batch: int) -> float:
+    return 2.0 * batch * sum(DIMS[i] * DIMS[i + 1] for i in range(len(DIMS) - 1))
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
-        data = json.load(open(path))
-        return data, "measured"
+        return json.load(open(path)), "measured"
     return dict(FALLBACK_PEAKS), "fallback"
 
 
-def synthetic_batch(rank: int, rows: int):
-    rng = np.random.default_rng(1234 + rank)
-    x = rng.random((rows, DIMS[0]), dtype=np.float32)
-    labels = rng.integers(0, DIMS[-1], rows).astype(np.int32)
+def synthetic_rows(first_row: int, rows: int, seed: int = 1234):
+    """Rows [first_row, first_row + rows) of the synthetic batch.  Each block of DATA_BLOCK rows has its
+    own generator keyed by (seed, block index), so a row's values depend on its global index only and
+    not on how the batch is cut into ranks."""
+    if first_row % DATA_BLOCK or rows % DATA_BLOCK:
+        raise ValueError(f"rank slices must be multiples of {DATA_BLOCK} rows")
+    x = np.empty((rows, DIMS[0]), dtype=np.float32)
+    labels = np.empty(rows, dtype=np.int32)
+    for i in range(rows // DATA_BLOCK):
+        rng = np.random.default_rng([seed, first_row // DATA_BLOCK + i])
+        x[i * DATA_BLOCK:(i + 1) * DATA_BLOCK] = rng.random((DATA_BLOCK, DIMS[0]), dtype=np.float32)
+        labels[i * DATA_BLOCK:(i + 1) * DATA_BLOCK] = rng.integers(0, DIMS[-1], DATA_BLOCK)
     return x, labels
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, device_index: int):
+    def __init__(self, device_index: int, period_ms: int = 200):
         self.device_index = device_index
+        self.period_ms = period_ms
         self.proc = None
         self.lines = []
         self.thread = None
@@ -70,15 +97,16 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.device_index}", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE, text=True)
+                                          "--format=csv,noheader,nounits", "-lms", str(self.period_ms)], stdout=subprocess.PIPE, text=True)
         except OSError:
             self.proc = None
-            return
+            return self
         def pump():
             for line in self.proc.stdout:
                 self.lines.append(line.strip())
         self.thread = threading.Thread(target=pump, daemon=True)
         self.thread.start()
+        return self
 
     def stop(self):
         if self.proc is None:
@@ -107,6 +135,14 @@ class ClockSampler:
                 "samples": len(clocks), "reasons": sorted(reasons)}
 
 
+def at_equal_clock(ms: float, clocks) -> float | None:
+    """Duration x median SM MHz: a clock-independent figure (kilo-cycles) for comparing runs whose boxes
+    settled at different clocks."""
+    if not clocks or not clocks.get("sm_mhz"):
+        return None
+    return ms * clocks["sm_mhz"]
+
+
 def cpu_baseline(threads: int, rows: int, steps: int = 1, warmup: int = 0):
     """Times the reference-shaped CPU training step on `rows` samples of the same workload: `warmup`
     untimed steps, then the median of `steps` timed ones."""
@@ -118,7 +154,7 @@ def cpu_baseline(threads: int, rows: int, steps: int = 1, warmup: int = 0):
     biases = [np.zeros(DIMS[i + 1], dtype=np.float32) for i in range(len(DIMS) - 1)]
     m1 = [np.zeros(a.size, dtype=np.float32) for pair in zip(weights, biases) for a in pair]
     m2 = [np.zeros(a.size, dtype=np.float32) for pair in zip(weights, biases) for a in pair]
-    x, labels = synthetic_batch(0, rows)
+    x, labels = synthetic_rows(0, rows)
     seconds = []
     for step in range(warmup + steps):
         s, _, _ = oracle.baseline_mlp_step(DIMS, x, labels, weights, biases, m1, m2, train=True, count_total=GLOBAL_BATCH,
@@ -151,11 +187,55 @@ def run_reference(args):
     return 0
 
 
+def measure_tf32_peak(device_index: int):
+    """A cuBLAS TF32 GEMM (torch.matmul on FP32 operands with TF32 allowed, 8192^3) timed here: best of
+    ten single launches (burst) and back to back for about four seconds (sustained, under the power cap),
+    with the clocks seen during the sustained run.  A library GEMM as the yardstick of the tensor-core
+    roofline; nothing in the product path calls it."""
+    import torch
+    n = 8192
+    before = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        a = torch.randn(n, n, device="cuda", dtype=torch.float32)
+        b = torch.randn(n, n, device="cuda", dtype=torch.float32)
+        c = torch.empty(n, n, device="cuda", dtype=torch.float32)
+        for _ in range(3):
+            torch.matmul(a, b, out=c)
+        torch.cuda.synchronize()
+        flops = 2.0 * n ** 3
+        best = float("inf")
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); torch.matmul(a, b, out=c); e1.record(); torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        sampler = ClockSampler(device_index).start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches = 0
+        wall = time.perf_counter()
+        e0.record()
+        while time.perf_counter() - wall < 4.0:
+            for _ in range(50):
+                torch.matmul(a, b, out=c)
+            launches += 50
+            torch.cuda.synchronize()
+        e1.record(); torch.cuda.synchronize()
+        sustained_ms = e0.elapsed_time(e1) / launches
+        clocks = sampler.stop()
+        del a, b, c
+        torch.cuda.empty_cache()
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = before
+    return {"burst_tflops": flops / (best * 1e-3) / 1e12, "sustained_tflops": flops / (sustained_ms * 1e-3) / 1e12,
+            "how": "torch.matmul FP32 operands, TF32 allowed, 8192^3: best of 10 (burst), back to back for 4 s (sustained)", "clocks": clocks}
+
+
 def run_cuda(args):
     import torch
     import torch.distributed as dist
     from synaptik_b200 import native, nn
 
+    global_batch = args.global_batch
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -178,7 +258,7 @@ def run_cuda(args):
         holder = [native.comm_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(holder, src=0)
         comm = native.Comm(ctx, world, rank, holder[0])
-    rows = GLOBAL_BATCH // world
+    rows = global_batch // world
     model = nn.Model(DIMS, ctx, seed=42, comm=comm, world_size=world)       # same seed: replicas start identical
     model.configure_training("ce", nn.Adam(ADAM["lr"], ADAM["beta1"], ADAM["beta2"], ADAM["eps"]))
     exe, xbuf, tbuf, seed, loss, grads = model.training_state(rows)
@@ -186,7 +266,7 @@ def run_cuda(args):
     x_host = native.PinnedArray((rows, DIMS[0]), np.float32)
     t_host = native.PinnedArray((rows,), np.int32)
     loss_host = native.PinnedArray((1,), np.float32)
-    x, labels = synthetic_batch(rank, rows)
+    x, labels = synthetic_rows(rank * rows, rows)           # this rank's slice of the one global batch
     x_host.array[...] = x
     t_host.array[...] = labels
     xbuf.upload(x)
@@ -231,6 +311,13 @@ def run_cuda(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def reduce_mean(value: float) -> float:
+        if not distributed:
+            return value
+        t = torch.tensor([value], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item()) / world
+
     for _ in range(max(args.warmup, 3)):
         resident_step()
     exe.finish(); optimizer.finish()
@@ -270,189 +357,377 @@ def run_cuda(args):
     exe.finish(); optimizer.finish()
     clocks = sampler.stop() if rank == 0 else None
     e2e_ms = reduce_max(max(e2e_ms, wall))
-    final_loss = float(loss_host.array[0])
+    total_steps = max(args.warmup, 3) + 2 * args.steps + 4
+    # the objective of the last step over the WHOLE batch (mean of the ranks' equal-sized means), and a
+    # checksum of every parameter tensor after the last step: the same for every N up to the rounding of
+    # the gradient sums
+    final_loss = reduce_mean(float(loss_host.array[0]))
+    parameters = model.parameters()
+    checksums = [[float(np.sum(p, dtype=np.float64)), float(np.sum(np.square(p, dtype=np.float64)))] for p in parameters]
+    replicas_identical = True
+    if distributed:
+        mine = torch.tensor(checksums, dtype=torch.float64, device="cuda")
+        everyone = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(everyone, mine)
+        replicas_identical = all(bool(torch.equal(everyone[0], other)) for other in everyone)
+    del parameters
+
+    # ---- inference: the same network, forward + row arg-max, 8192 rows per GPU, no collective --------
+    inference = None
+    if not args.no_inference:
+        inference = measure_inference(ctx, model, rank, world, local_rank, max(200, 20 * args.steps), barrier, reduce_max)
+
+    tf32 = None
+    if rank == 0 and not args.no_peak:
+        tf32 = measure_tf32_peak(local_rank)
+    barrier()
 
     if rank == 0:
         peak_data, peak_kind = peaks()
         # dominant kernel: the tcgen05 3xTF32 GEMM; algorithmic FLOPs 2*m*n*k per launch
-        import re
         flops, ms = 0.0, 0.0
         gemm_launches = 0
         shares = {}
-        for line, t in zip(plan, step_ms):
-            kind = line.split()[0] + (":" + re.search(r"engine=(\w+)", line).group(1) if line.startswith("gemm") else "")
+        for text, t in zip(plan, step_ms):
+            kind = text.split()[0] + (":" + re.search(r"engine=(\w+)", text).group(1) if text.startswith("gemm") else "")
             shares[kind] = shares.get(kind, 0.0) + t
-            if "engine=tcgen05_3xtf32" in line:
-                m, n, k = (int(re.search(rf" {d}=(\d+)", line).group(1)) for d in "mnk")
+            if "engine=tcgen05_3xtf32" in text:
+                m, n, k = (int(re.search(rf" {d}=(\d+)", text).group(1)) for d in "mnk")
                 flops += 2.0 * m * n * k
                 ms += t
                 gemm_launches += 1
-        tf32_peak = peak_data["bf16_tflops_sustained"] / 2.0          # TF32 dense = BF16 / 2 on B200
-        emulated_peak = tf32_peak / 3.0                                 # three MMAs per FP32 product
+        emulated_peak = peak_data["bf16_tflops_sustained"] / 2.0 / 3.0       # TF32 dense = BF16 / 2; three MMAs per FP32 product
         achieved = flops / (ms * 1e-3) / 1e12 if ms > 0 else 0.0
         total_step = sum(step_ms) or 1.0
+        # DRAM traffic of one launch from the 8192-row capture: terms that grow with the rows scaled by rows / 8192
+        scale = rows / 8192.0
+        traffic = (NCU_TRAFFIC_8192["total"] - NCU_TRAFFIC_8192["weight_term"]) * scale + NCU_TRAFFIC_8192["weight_term"]
+        roofline = {"bound": "tensor", "kernel": "gemm_tf32x3_pair_kernel", "achieved": achieved, "peak": emulated_peak, "unit": "TFLOP/s",
+                    "frac": achieved / emulated_peak if emulated_peak else None,
+                    "peak_source": f"{peak_kind} cuBLAS BF16 sustained / 2 (TF32) / 3 (three MMAs per FP32 product)",
+                    "traffic": traffic,
+                    "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one 8192 x 4096 x 4096 launch of this kernel; "
+                                      "the operand-plane and result terms scaled to this run's rows, the weight-plane term counted once",
+                    "algorithmic_bytes_per_launch": 4.0 * (2 * rows * 4096 + 4096 * 4096 + 4096),
+                    "launches_per_step": gemm_launches, "ms_per_step_in_kernel": ms,
+                    "kilocycles_in_kernel": at_equal_clock(ms, clocks),
+                    "step_time_shares": {k: v / total_step for k, v in sorted(shares.items())},
+                    "steps_ms": [[text.split(" nodes=")[0], round(t, 4)] for text, t in zip(plan, step_ms)]}
+        if clocks and clocks.get("sm_mhz"):
+            # the tensor pipe's own ceiling at the clock this run held: NVIDIA's dense TF32 figure (1125 TFLOP/s at
+            # the 1965 MHz boost clock) scaled to the sampled clock, three MMAs per FP32 product
+            nominal = 1125.0 * clocks["sm_mhz"] / 1965.0 / 3.0
+            roofline["peak_nominal_at_sampled_clock"] = nominal
+            roofline["frac_of_nominal_at_sampled_clock"] = achieved / nominal
+        if tf32:
+            direct = tf32["sustained_tflops"] / 3.0
+            roofline["peak_tf32_measured"] = direct
+            roofline["frac_of_tf32_measured"] = achieved / direct
+            roofline["frac_of_tf32_burst"] = achieved / (tf32["burst_tflops"] / 3.0)
+            roofline["peak_tf32_source"] = "cuBLAS TF32 GEMM timed in this run (tf32_peak.sustained_tflops) / 3"
         line = {
-            "metric": METRIC, "value": GLOBAL_BATCH * args.steps / (resident_ms * 1e-3), "unit": "samples/s",
+            "metric": METRIC, "value": global_batch * args.steps / (resident_ms * 1e-3), "unit": "samples/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": resident_ms / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "mlp_784_4096x3_10_softmax_ce_adam_train", "global_batch": GLOBAL_BATCH, "rows_per_gpu": rows,
+            "config": {"workload": "mlp_784_4096x3_10_softmax_ce_adam_train", "global_batch": global_batch, "rows_per_gpu": rows,
                        "parallelism": f"dp{world}", "gemm": "3xTF32 on tcgen05", "l2": "inputs_exceed_l2 (per-step working set > 1 GB)",
-                       "final_loss": final_loss},
-            "e2e": {"value": GLOBAL_BATCH * args.steps / (e2e_ms * 1e-3), "unit": "samples/s",
+                       "data_seed": "one global batch, row blocks seeded by global index: identical rows for every number of ranks",
+                       "optimizer_steps_taken": total_steps, "final_loss": final_loss,
+                       "parameter_checksums": checksums, "replicas_identical": replicas_identical},
+            "e2e": {"value": global_batch * args.steps / (e2e_ms * 1e-3), "unit": "samples/s",
                     "h2d_bytes_per_step": x_host.nbytes + t_host.nbytes, "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
-            "roofline": {"bound": "tensor", "kernel": "gemm_tf32x3_pair_kernel", "achieved": achieved, "peak": emulated_peak, "unit": "TFLOP/s",
-                         "frac": achieved / emulated_peak if emulated_peak else None,
-                         # DRAM bytes per launch (read + written, mean over the step's 8 GEMM launches) from the
-                         # committed ncu capture of exactly these launches; other shapes were not captured
-                         "traffic": 8.67e9 if rows == GLOBAL_BATCH else None,
-                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, profiles/train_step_launch_list.md" if rows == GLOBAL_BATCH else None,
-                         "algorithmic_bytes_per_launch": 28.7e9 / 8 if rows == GLOBAL_BATCH else None,
-                         "peak_source": f"{peak_kind} bf16_tflops_sustained / 2 (TF32) / 3 (3xTF32)",
-                         "launches_per_step": gemm_launches, "ms_per_step_in_kernel": ms,
-                         "step_time_shares": {k: v / total_step for k, v in sorted(shares.items())},
-                         "steps_ms": [[line.split(" nodes=")[0], round(t, 4)] for line, t in zip(plan, step_ms)]},
-            "model_tflops": step_flops(GLOBAL_BATCH) * args.steps / (resident_ms * 1e-3) / 1e12,
+            "roofline": roofline,
+            "model_tflops": step_flops(global_batch) * args.steps / (resident_ms * 1e-3) / 1e12,
+            "inference": inference,
         }
-        if world == 1 and not args.no_cpu_baseline:
+        if tf32:
+            line["tf32_peak"] = tf32
+    model.close()
+    for xb, tb in input_sets[1:]:
+        xb.close(); tb.close()
+    if rank == 0:
+        if world == 1 and not args.no_kernels and global_batch == GLOBAL_BATCH:
+            line["kernels"] = kernel_cases(ctx, local_rank)
+        if world == 1 and not args.no_cpu_baseline and global_batch == GLOBAL_BATCH:
             threads = os.cpu_count() or 1
             value, blas, seconds = cpu_baseline(threads, 4096, steps=3, warmup=1)     # about 10 s of CPU work
             line["cpu_baseline"] = {"value": value, "unit": "samples/s", "cores": threads, "kind": "port",
                                     "sample": f"4096 of {GLOBAL_BATCH} rows per step, median of 3 timed steps after 1 warm-up, {seconds:.2f} s/step, BLAS: {os.path.basename(blas)}"}
         print(json.dumps(line))
-    model.close()
     if comm is not None:
         comm.close()
     if distributed:
+        dist.barrier()
         dist.destroy_process_group()
     return 0
 
 
-def run_kernel_case(args):
-    """Single-GPU kernel cases behind the same C ABI: BASELINE.json configs[1] (fused dense layer,
-    forward and backward) and configs[2] (classifier head).  Used for the roofline lines and as the
-    small workloads of the ncu captures."""
-    from synaptik_b200 import native, program
+def measure_inference(ctx, model, rank, world, local_rank, steps, barrier, reduce_max):
+    """Model.compute with the row arg-max at INFERENCE_ROWS_PER_GPU rows per GPU: every rank holds the
+    weights and runs its own rows, nothing is exchanged (weak scaling).  Resident: the batch already in
+    HBM.  End to end: per batch the input is copied from pinned host memory (on the copy stream, under
+    the previous batch) and logits and arg-max are copied back, all inside the timed region."""
+    from synaptik_b200 import native
+    rows = INFERENCE_ROWS_PER_GPU
+    exe, xbuf, outs = model._inference_state((rows,), True)
+    x, _ = synthetic_rows(rank * rows, rows, seed=4321)
+    x_host = native.PinnedArray((rows, DIMS[0]), np.float32)
+    x_host.array[...] = x
+    logits_host = native.PinnedArray((rows, DIMS[-1]), np.float32)
+    index_host = native.PinnedArray((rows,), np.int64)
+    xbuf.upload(x)
+    feeds = [xbuf] + model.param_buffers
+    for _ in range(5):
+        exe.enqueue(feeds, outs)
+    exe.finish()
+    sampler = ClockSampler(local_rank, 100)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    ctx.timer_start()
+    for _ in range(steps):
+        exe.enqueue(feeds, outs)
+    resident_ms = reduce_max(ctx.timer_stop())
+    exe.finish()
+    ctx.set_option("time_steps", 1)
+    exe.run(feeds, outs)
+    ctx.set_option("time_steps", 0)
+    plan, step_ms = exe.describe().strip().split("\n"), exe.step_timings_ms()
+    launches = exe.launch_count()
+    second = ctx.buffer(x_host.nbytes)
+    sets = [xbuf, second]
+
+    def batches(count):
+        sets[0].prefetch(x_host.pointer, x_host.nbytes)
+        for i in range(count):
+            if i + 1 < count:
+                sets[(i + 1) & 1].prefetch(x_host.pointer, x_host.nbytes)
+            exe.enqueue([sets[i & 1]] + model.param_buffers, outs)
+            outs[0].download_async(logits_host.pointer, logits_host.nbytes)
+            outs[1].download_async(index_host.pointer, index_host.nbytes)
+            exe.finish()
+
+    batches(2)
+    barrier()
+    ctx.timer_start()
+    wall = time.perf_counter()
+    batches(steps)
+    e2e_ms = ctx.timer_stop()
+    wall = (time.perf_counter() - wall) * 1e3
+    e2e_ms = reduce_max(max(e2e_ms, wall))
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    checksum = int(np.sum(index_host.array))
+    second.close(); x_host.close(); logits_host.close(); index_host.close()
+    if rank != 0:
+        return None
+    peak_data, peak_kind = peaks()
+    flops = gemm_ms = 0.0
+    for text, t in zip(plan, step_ms):
+        if "engine=tcgen05_3xtf32" in text:
+            m, n, k = (int(re.search(rf" {d}=(\d+)", text).group(1)) for d in "mnk")
+            flops += 2.0 * m * n * k
+            gemm_ms += t
+    achieved = flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms else 0.0
+    peak = peak_data["bf16_tflops_sustained"] / 6.0
+    return {"metric": "mlp_inference_samples_per_s", "value": world * rows * steps / (resident_ms * 1e-3), "unit": "samples/s",
+            "scaling": "weak", "n_gpus": world, "rows_per_gpu": rows, "steps": steps, "ms_per_batch": resident_ms / steps,
+            "workload": "mlp_784_4096x3_10_forward_argmax", "collective": "none (weights replicated, rows split)",
+            "e2e": {"value": world * rows * steps / (e2e_ms * 1e-3), "unit": "samples/s", "ms_per_batch": e2e_ms / steps,
+                    "h2d_bytes_per_step": rows * DIMS[0] * 4, "d2h_bytes_per_step": rows * DIMS[-1] * 4 + rows * 8},
+            "model_tflops_per_gpu": forward_flops(rows) * steps / (resident_ms * 1e-3) / 1e12,
+            "gpu_launches": launches * steps,
+            "roofline": {"bound": "tensor", "kernel": "gemm_tf32x3_pair_kernel", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak if peak else None, "peak_source": f"{peak_kind} cuBLAS BF16 sustained / 2 / 3",
+                         "ms_per_batch_in_kernel": gemm_ms,
+                         "steps_ms": [[text.split(" nodes=")[0], round(t, 4)] for text, t in zip(plan, step_ms)]},
+            "arg_max_checksum": checksum, "clocks": clocks, "kilocycles_per_batch": at_equal_clock(resident_ms / steps, clocks)}
+
+
+def measure_kernel_case(ctx, device_index, case, m, k, n, forward_only=False, steps=10, warmup=3, blocks=31, warm_seconds=1.0):
+    """One kernel case through the C ABI on context `ctx`: the standalone fused dense layer (forward and
+    backward) or a piece of the classifier head.  Times `steps` back-to-back launches between two CUDA
+    events on the context's stream, then follows the reference's own protocol (warm-up of at least
+    `warm_seconds`, then `blocks` timed blocks of at least 30 ms, median reported), samples the clocks
+    during all of it, and brackets every plan step with events once for the per-kernel times."""
+    from synaptik_b200 import native
     from synaptik_b200.program import F32, I32, GraphBuilder
-    ctx = native.Context(0)
-    for item in filter(None, os.environ.get("SYNAPTIK_BENCH_OPTIONS", "").split(",")):      # experiment hook, as in run_cuda
-        name, _, value = item.partition("=")
-        ctx.set_option(name.strip(), int(value))
     rng = np.random.default_rng(3)
     g = GraphBuilder()
     peak_data, peak_kind = peaks()
-    if args.case == "gemm":
-        m, k, n = args.m, args.k, args.n
+    if case == "gemm":
         x, w, b, dy = g.feed(F32, (m, k)), g.feed(F32, (n, k)), g.feed(F32, (n,)), g.feed(F32, (m, n))
         wt, z = g.linear(x, w, b)
         g.publish(g.relu(z))
-        if not args.forward_only:
+        if not forward_only:
             dz = g.relu_backward(z, dy)
             dx, dw, db = g.linear_backward(x, wt, dz, need_dx=True)
             for v in (dx, dw, db):
                 g.publish(v)
         bound = np.sqrt(6.0 / (k + n))
-        feeds = [rng.uniform(-1, 1, (m, k)).astype(np.float32), rng.uniform(-bound, bound, (n, k)).astype(np.float32),
-                 rng.uniform(-0.1, 0.1, n).astype(np.float32), rng.standard_normal((m, n)).astype(np.float32)]
-        work = (2.0 if args.forward_only else 6.0) * m * k * n
+        feeds = [rng.random((m, k), dtype=np.float32) * 2 - 1, (rng.random((n, k), dtype=np.float32) * 2 - 1) * np.float32(bound),
+                 (rng.random(n, dtype=np.float32) * 2 - 1) * np.float32(0.1), rng.standard_normal((m, n), dtype=np.float32)]
+        work = (2.0 if forward_only else 6.0) * m * k * n
         unit, denom, bound_kind = "TFLOP/s", peak_data["bf16_tflops"] / 6.0, "tensor"
-        name = f"dense_layer_{'fwd' if args.forward_only else 'fwd_bwd'}_m{m}_k{k}_n{n}"
-    elif args.case == "dense_ce":
-        rows, classes = args.m, args.n
+        name = f"dense_layer_{'fwd' if forward_only else 'fwd_bwd'}_m{m}_k{k}_n{n}"
+    elif case == "dense_ce":
+        rows, classes = m, n
         logits, target = g.feed(F32, (rows, classes)), g.feed(F32, (rows, classes))
         g.publish(g.dense_cross_entropy(logits, target, "mean"))
-        weights = rng.random((rows, classes)).astype(np.float32)
-        feeds = [(rng.standard_normal((rows, classes)) * 2).astype(np.float32), weights / weights.sum(axis=1, keepdims=True)]
+        weights = rng.random((rows, classes), dtype=np.float32)
+        feeds = [rng.standard_normal((rows, classes), dtype=np.float32) * 2, weights / weights.sum(axis=1, keepdims=True)]
         work = 8.0 * rows * classes + 4.0 * rows + 4.0           # read logits and target weights, row losses, the mean
         unit, denom, bound_kind = "GB/s", peak_data["hbm_gbs"], "hbm"
         name = f"dense_cross_entropy_rows{rows}_classes{classes}"
-    elif args.case == "argmax":
-        rows, classes = args.m, args.n
+    elif case == "argmax":
+        rows, classes = m, n
         logits = g.feed(F32, (rows, classes))
         g.publish(g.arg_max(logits, 1))
-        feeds = [(rng.standard_normal((rows, classes)) * 2).astype(np.float32)]
+        feeds = [rng.standard_normal((rows, classes), dtype=np.float32) * 2]
         work = 4.0 * rows * classes + 8.0 * rows                 # read the logits, write one INT64 index per row
         unit, denom, bound_kind = "GB/s", peak_data["hbm_gbs"], "hbm"
         name = f"argmax_rows{rows}_classes{classes}"
-    elif args.case in ("softmax", "log_softmax"):
-        rows, classes = args.m, args.n
+    elif case in ("softmax", "log_softmax"):
+        rows, classes = m, n
         logits = g.feed(F32, (rows, classes))
-        g.publish(g.softmax(logits, 1) if args.case == "softmax" else g.log_softmax(logits, 1))
-        feeds = [(rng.standard_normal((rows, classes)) * 2).astype(np.float32)]
+        g.publish(g.softmax(logits, 1) if case == "softmax" else g.log_softmax(logits, 1))
+        feeds = [rng.standard_normal((rows, classes), dtype=np.float32) * 2]
         work = 8.0 * rows * classes                              # one pass: read the logits, write the result
         unit, denom, bound_kind = "GB/s", peak_data["hbm_gbs"], "hbm"
-        name = f"{args.case}_rows{rows}_classes{classes}"
+        name = f"{case}_rows{rows}_classes{classes}"
     else:
-        rows, classes = args.m, args.n
+        rows, classes = m, n
         logits, labels, seed = g.feed(F32, (rows, classes)), g.feed(I32, (rows,)), g.feed(F32, ())
         g.publish(g.index_cross_entropy(logits, labels))
         g.publish(g.index_cross_entropy_backward(logits, labels, seed))
         g.publish(g.arg_max(logits, 1))
-        feeds = [(rng.standard_normal((rows, classes)) * 2).astype(np.float32), rng.integers(0, classes, rows).astype(np.int32),
+        feeds = [rng.standard_normal((rows, classes), dtype=np.float32) * 2, rng.integers(0, classes, rows).astype(np.int32),
                  np.array(1.0, dtype=np.float32)]
         work = 8.0 * rows * classes + 12.0 * rows + 4.0          # one pass: read logits, write gradient, labels, arg-max, loss
         unit, denom, bound_kind = "GB/s", peak_data["hbm_gbs"], "hbm"
         name = f"classifier_head_rows{rows}_classes{classes}"
     exe = native.Executable(ctx, g.build())
     inputs = [ctx.upload(a) for a in feeds]
+    del feeds
     outputs = [ctx.buffer(max(g.values[i].nbytes, 4)) for i in g.publications]
-    for _ in range(max(args.warmup, 1)):
+    resident_bytes = sum(b.nbytes for b in inputs + outputs)
+    # Inputs and results smaller than twice the 126 MB L2 would be timed warm: such a case is timed one run
+    # at a time (the run's own start / stop events), with a 524 MB streaming pass in front of every timed run.
+    flush = None
+    if resident_bytes < 2 * 126e6:
+        fg = GraphBuilder()
+        fg.publish(fg.softmax(fg.feed(F32, (65536, 1000)), 1))
+        flush = (native.Executable(ctx, fg.build()), [ctx.buffer(65536 * 1000 * 4)], [ctx.buffer(65536 * 1000 * 4)])
+    for _ in range(max(warmup, 3)):
         exe.run(inputs, outputs)
-    # timed region: the launches back to back between two CUDA events on the context's stream
-    ctx.timer_start()
-    for _ in range(args.steps):
-        exe.enqueue(inputs, outputs)
-    ms = ctx.timer_stop()
-    exe.finish()
-    # the reference's own timing protocol (warm-up of at least 20 calls and 1 s, then 31 timed blocks of
-    # at least 30 ms each, median reported): blocks of back-to-back launches between two CUDA events
-    per_step = max(ms / args.steps, 1e-3)
-    block_steps = max(1, int(np.ceil(30.0 / per_step)))
-    for _ in range(max(20, int(np.ceil(1000.0 / per_step)))):
-        exe.enqueue(inputs, outputs)
-    exe.finish()
-    blocks = []
-    for _ in range(31):
+    sampler = ClockSampler(device_index, 100).start()
+    if flush is None:
+        # timed region: the launches back to back between two CUDA events on the context's stream
         ctx.timer_start()
-        for _ in range(block_steps):
+        for _ in range(steps):
             exe.enqueue(inputs, outputs)
-        blocks.append(ctx.timer_stop() / block_steps)
-    exe.finish()
-    median_ms = float(np.median(blocks))
+        ms = ctx.timer_stop()
+        exe.finish()
+        per_step = max(ms / steps, 1e-3)
+        block_steps = max(1, int(np.ceil(30.0 / per_step)))
+        for _ in range(max(20, int(np.ceil(1000.0 * warm_seconds / per_step))) if warm_seconds > 0 else 0):
+            exe.enqueue(inputs, outputs)
+        exe.finish()
+        timed = []
+        for _ in range(blocks):
+            ctx.timer_start()
+            for _ in range(block_steps):
+                exe.enqueue(inputs, outputs)
+            timed.append(ctx.timer_stop() / block_steps)
+        exe.finish()
+        protocol = f"median of {blocks} blocks of {block_steps} back-to-back launches after a warm-up of at least {warm_seconds} s"
+        l2 = "inputs_exceed_l2"
+    else:
+        timed = []
+        for _ in range(max(steps, 40 * blocks)):
+            flush[0].enqueue(flush[1], flush[2])
+            exe.enqueue(inputs, outputs)
+            exe.finish()
+            timed.append(exe.last_timing_ms())
+        ms = float(np.sum(timed[:steps]))
+        protocol = f"median of {len(timed)} single runs, each behind a streaming pass over 524 MB"
+        l2 = f"flushed before every timed run (inputs and results are {resident_bytes / 1e6:.0f} MB)"
+    clocks = sampler.stop()
+    median_ms = float(np.median(timed))
     # one more run with an event pair around every plan step, for the per-kernel times
     ctx.set_option("time_steps", 1)
+    if flush is not None:
+        flush[0].enqueue(flush[1], flush[2])
     exe.run(inputs, outputs)
     ctx.set_option("time_steps", 0)
     plan = exe.describe().strip().split("\n")
-    steps = exe.step_timings_ms()
-    rate = work * args.steps / (ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9)
+    step_times = exe.step_timings_ms()
+    per_unit = 1e12 if unit == "TFLOP/s" else 1e9
     # roofline of the dominant kernel: its algorithmic work over its own event-bracketed time (the
-    # per-step CUDA events of the last timed run), not over the whole run with its other launches
-    import re
-    if args.case == "gemm":
+    # per-step CUDA events of the last run) for the dense layer, whose step has other launches too; for
+    # the one-launch cases the median block time over the launches
+    if case == "gemm":
         kernel, kernel_work, kernel_ms = "gemm_tf32x3_pair_kernel", 0.0, 0.0
-        for text, t in zip(plan, steps):
+        for text, t in zip(plan, step_times):
             if "engine=tcgen05_3xtf32" in text:
-                mm, nn, kk = (int(re.search(rf" {d}=(\d+)", text).group(1)) for d in "mnk")
-                kernel_work += 2.0 * mm * nn * kk
+                mm, nn_, kk = (int(re.search(rf" {d}=(\d+)", text).group(1)) for d in "mnk")
+                kernel_work += 2.0 * mm * nn_ * kk
                 kernel_ms += t
     else:
-        # the whole step is this one launch: its average duration is the timed region over the launches
-        kernel = {"ce": "ce_rows_vec_kernel", "argmax": "argmax_vec_kernel", "dense_ce": "dense_ce_rows_vec_kernel"}.get(args.case, "softmax_rows_vec_kernel")
-        kernel_work, kernel_ms = work, ms / args.steps
-    achieved = kernel_work / (kernel_ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9) if kernel_ms > 0 else 0.0
-    line = {"metric": f"{args.case}_{unit}", "value": rate, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 1),
-            "ms_per_step": ms / args.steps, "median_ms_per_step": median_ms,
-            "protocol": f"median of 31 blocks of {block_steps} launches after a warm-up of at least 1 s",
-            "higher_is_better": True, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": name}, "gpu_launches": exe.launch_count() * args.steps,
-            "roofline": {"bound": bound_kind, "kernel": kernel, "achieved": achieved, "peak": denom, "unit": unit, "frac": achieved / denom,
-                         "ms_in_kernel": kernel_ms,
-                         "peak_source": peak_kind + (" bf16_tflops / 2 / 3" if unit == "TFLOP/s" else " hbm_gbs"), "traffic": None},
-            "steps_ms": {line.split(" nodes=")[0]: t for line, t in zip(plan, steps)}}
-    print(json.dumps(line))
+        kernel = {"ce": "ce_rows_vec_kernel", "argmax": "argmax_vec_kernel", "dense_ce": "dense_ce_rows_vec_kernel"}.get(case, "softmax_rows_vec_kernel")
+        kernel_work, kernel_ms = work, median_ms
+    achieved = kernel_work / (kernel_ms * 1e-3) / per_unit if kernel_ms > 0 else 0.0
+    record = {"metric": f"{case}_{unit}", "value": work / (median_ms * 1e-3) / per_unit, "unit": unit, "n_gpus": 1, "steps": steps,
+              "warmup": max(warmup, 3), "ms_per_step": ms / steps, "median_ms_per_step": median_ms,
+              "protocol": protocol,
+              "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+              "config": {"workload": name, "l2": l2},
+              "gpu_launches": exe.launch_count() * steps, "clocks": clocks, "kilocycles_per_step": at_equal_clock(median_ms, clocks),
+              "roofline": {"bound": bound_kind, "kernel": kernel, "achieved": achieved, "peak": denom, "unit": unit, "frac": achieved / denom,
+                           "ms_in_kernel": kernel_ms,
+                           "peak_source": peak_kind + (" cuBLAS BF16 burst / 2 / 3" if unit == "TFLOP/s" else " copy bandwidth"), "traffic": None},
+              "steps_ms": {text.split(" nodes=")[0]: t for text, t in zip(plan, step_times)}}
     exe.close()
+    if flush is not None:
+        flush[0].close()
+        inputs = inputs + flush[1] + flush[2]
+    for b in inputs + outputs:
+        b.close()
+    return record
+
+
+def kernel_cases(ctx, device_index):
+    """The standalone cases the headline names beside the training step, each for a second or so: the six
+    fused dense layer shapes (forward + dX + dW + db) and the 1000-class classifier head."""
+    records = []
+    for m in (4096, 16384, 65536):
+        for kn in (1024, 4096):
+            r = measure_kernel_case(ctx, device_index, "gemm", m, kn, kn, steps=5, blocks=9, warm_seconds=0.3)
+            records.append({"workload": r["config"]["workload"], "unit": r["unit"], "whole_layer": r["value"], "median_ms": r["median_ms_per_step"],
+                            "kernel": r["roofline"]["kernel"], "in_kernel": r["roofline"]["achieved"], "ms_in_kernel": r["roofline"]["ms_in_kernel"],
+                            "peak": r["roofline"]["peak"], "frac": r["roofline"]["frac"], "algorithmic_flop": 6.0 * m * kn * kn,
+                            "clocks": r["clocks"], "kilocycles": r["kilocycles_per_step"]})
+    for case in ("ce", "softmax", "argmax"):
+        r = measure_kernel_case(ctx, device_index, case, 65536, 0, 1000, steps=20, blocks=9, warm_seconds=0.3)
+        records.append({"workload": r["config"]["workload"], "unit": r["unit"], "value": r["value"], "median_ms": r["median_ms_per_step"],
+                        "kernel": r["roofline"]["kernel"], "peak": r["roofline"]["peak"], "frac": r["roofline"]["frac"],
+                        "clocks": r["clocks"], "kilocycles": r["kilocycles_per_step"]})
+    return records
+
+
+def run_kernel_case(args):
+    from synaptik_b200 import native
+    ctx = native.Context(0)
+    for item in filter(None, os.environ.get("SYNAPTIK_BENCH_OPTIONS", "").split(",")):      # experiment hook, as in run_cuda
+        name, _, value = item.partition("=")
+        ctx.set_option(name.strip(), int(value))
+    if args.quick:
+        record = measure_kernel_case(ctx, 0, args.case, args.m, args.k, args.n, args.forward_only, args.steps, args.warmup, blocks=1, warm_seconds=0.0)
+    else:
+        record = measure_kernel_case(ctx, 0, args.case, args.m, args.k, args.n, args.forward_only, args.steps, args.warmup)
+    print(json.dumps(record))
     ctx.close()
     return 0
 
@@ -464,11 +739,17 @@ def main():
     parser.add_argument("--k", type=int, default=4096)
     parser.add_argument("--n", type=int, default=4096)
     parser.add_argument("--forward-only", action="store_true")
+    parser.add_argument("--quick", action="store_true", help="kernel cases: only the plain timed region (few launches: the workload of a profiler capture)")
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=10)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-kernels", action="store_true")
+    parser.add_argument("--no-peak", action="store_true")
+    parser.add_argument("--no-inference", action="store_true")
+    parser.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,
+                        help="rows of the training batch; anything but the default is a reduced workload for profiler captures, not a benchmark")
     args = parser.parse_args()
     if args.impl == "reference":
         return run_reference(args)

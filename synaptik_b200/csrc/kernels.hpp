@@ -116,11 +116,12 @@ cudaError_t wait_probe(cudaStream_t s, uint64_t limit_ns, int *error_word);
 // ---- GEMM -------------------------------------------------------------------------------------
 struct GemmEpilogue {
     const float *bias = nullptr;        // [n], added to every row
-    int relu = 0;                       // out = max(z, +0)
+    int act = 0;                        // activation applied to z: 0 none, else the wire code of RELU, TANH, SIGMOID,
+                                        // SILU, GELU_TANH or GELU (the CPU backend's epilogue vocabulary, CpuMatmulIr.java:96-101)
     const float *gate = nullptr;        // dense [m,n]: out = gate > 0 ? z : 0
-    float *second = nullptr;            // dense [m,n]: when set, `out` receives z and `second` relu(z)
+    float *second = nullptr;            // dense [m,n]: when set, `out` receives z and `second` act(z)
     // tensor-core kernel only: also write the hi/lo operand planes of the result (the activation when
-    // relu / second is set) for later GEMMs, [m, plane_ld]
+    // act is set) for later GEMMs, [m, plane_ld]
     float *plane_hi = nullptr, *plane_lo = nullptr; int64_t plane_ld = 0;
 };
 // Exact CUDA-core product: every output cell is the reference's ascending-k chain of separately

@@ -10,6 +10,7 @@
 //    that issues lo*hi, hi*lo and hi*hi into one accumulator (3xTF32).  The dropped lo*lo term is
 //    below 2^-22 of each product.
 #include "kernels.hpp"
+#include "activation.cuh"
 #include "split.cuh"
 
 #include <cuda.h>
@@ -21,8 +22,6 @@ namespace syn {
 namespace kern {
 
 namespace {
-
-__device__ __forceinline__ float relu_value(float x) { return x != x ? x : (x > 0.0f ? x : 0.0f); }
 
 // ------------------------------------------------------------------------------------------------
 // Exact CUDA-core GEMM: 64x64 result tile, 16-deep k slices, 256 threads, 4x4 cells per thread.
@@ -86,8 +85,8 @@ __global__ void __launch_bounds__(256) gemm_exact_kernel(int64_t m, int64_t n, i
             float z = acc[i][j];
             if (ep.bias) z = __fadd_rn(z, ep.bias[gn]);
             if (ep.gate) z = ep.gate[gm * n + gn] > 0.0f ? z : 0.0f;
-            if (ep.second) { c[gm * c_ms + gn * c_ns] = z; ep.second[gm * n + gn] = relu_value(z); }
-            else c[gm * c_ms + gn * c_ns] = ep.relu ? relu_value(z) : z;
+            if (ep.second) { c[gm * c_ms + gn * c_ns] = z; ep.second[gm * n + gn] = activation_value(ep.act, z); }
+            else c[gm * c_ms + gn * c_ns] = activation_value(ep.act, z);
         }
     }
 }
@@ -267,7 +266,7 @@ struct TcParams {
     float *d; int64_t ldd;
     int m, n, k_blocks;
     int tiles_m, tiles_n;
-    const float *bias; const float *gate; float *second; int relu;
+    const float *bias; const float *gate; float *second; int act;    // act: 0 none, else the activation's wire code
     float *nhi, *nlo; int64_t nld;          // optional [m, nld] hi/lo planes of the result
     int p_mn, q_mn;                          // operand planes are MN-major ([k, rows]) instead of K-major ([rows, k])
     int chunk_kb;                            // promoted kernel: k-blocks per tensor-memory partial sum
@@ -300,9 +299,17 @@ __device__ __forceinline__ void tile_origin(int tile, int tiles_m, int tiles_n, 
 }
 
 
+// The activations other than ReLU evaluate an elementary function in binary64 (activation.cuh).  Kept out
+// of line and out of the kernels that never need them: inlined into the 32 call sites of an epilogue
+// thread that holds 128 register sums they would take the registers the sums live in.
+__device__ __noinline__ float4 activate4(int act, float4 z) {
+    return make_float4(activation_value(act, z.x), activation_value(act, z.y), activation_value(act, z.z), activation_value(act, z.w));
+}
+
 // Finishes four adjacent result cells of one row: bias, ReLU-backward gate, activation, the stores
 // of the result (and of the second output), and the hi/lo operand planes when later GEMMs read this
-// result.
+// result.  GENERAL: the activation may be any of the epilogue vocabulary; otherwise it is ReLU or none.
+template <bool GENERAL>
 __device__ __forceinline__ void epilogue_emit4(const TcParams &prm, int row, int col,
                                                float z0, float z1, float z2, float z3, bool vec_ok) {
     float *drow = prm.d + (int64_t)row * prm.ldd;
@@ -314,8 +321,13 @@ __device__ __forceinline__ void epilogue_emit4(const TcParams &prm, int row, int
             z[0] = __fadd_rn(z[0], bv.x); z[1] = __fadd_rn(z[1], bv.y); z[2] = __fadd_rn(z[2], bv.z); z[3] = __fadd_rn(z[3], bv.w); }
         if (prm.gate) { float4 gv = *reinterpret_cast<const float4 *>(prm.gate + dense + col);
             z[0] = gv.x > 0.0f ? z[0] : 0.0f; z[1] = gv.y > 0.0f ? z[1] : 0.0f; z[2] = gv.z > 0.0f ? z[2] : 0.0f; z[3] = gv.w > 0.0f ? z[3] : 0.0f; }
+        if (GENERAL) {
+            const float4 a = activate4(prm.act, make_float4(z[0], z[1], z[2], z[3]));
+            y[0] = a.x; y[1] = a.y; y[2] = a.z; y[3] = a.w;
+        } else {
 #pragma unroll
-        for (int e = 0; e < 4; e++) y[e] = (prm.second || prm.relu) ? relu_value(z[e]) : z[e];
+            for (int e = 0; e < 4; e++) y[e] = prm.act ? relu_value(z[e]) : z[e];
+        }
         if (prm.second) {
             *reinterpret_cast<float4 *>(drow + col) = make_float4(z[0], z[1], z[2], z[3]);
             *reinterpret_cast<float4 *>(prm.second + dense + col) = make_float4(y[0], y[1], y[2], y[3]);
@@ -323,18 +335,28 @@ __device__ __forceinline__ void epilogue_emit4(const TcParams &prm, int row, int
             *reinterpret_cast<float4 *>(drow + col) = make_float4(y[0], y[1], y[2], y[3]);
         }
     } else {
+        if (prm.bias) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) if (col + e < prm.n) z[e] = __fadd_rn(z[e], prm.bias[col + e]);
+        }
+        if (prm.gate) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) if (col + e < prm.n) z[e] = prm.gate[dense + col + e] > 0.0f ? z[e] : 0.0f;
+        }
+        if (GENERAL) {
+            const float4 a = activate4(prm.act, make_float4(z[0], z[1], z[2], z[3]));
+            y[0] = a.x; y[1] = a.y; y[2] = a.z; y[3] = a.w;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; e++) y[e] = prm.act ? relu_value(z[e]) : z[e];
+        }
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             const int cc = col + e;
-            y[e] = 0.0f;
             if (cc < prm.n) {
-                float zz = z[e];
-                if (prm.bias) zz = __fadd_rn(zz, prm.bias[cc]);
-                if (prm.gate) zz = prm.gate[dense + cc] > 0.0f ? zz : 0.0f;
-                y[e] = (prm.second || prm.relu) ? relu_value(zz) : zz;
-                if (prm.second) { drow[cc] = zz; prm.second[dense + cc] = y[e]; }
+                if (prm.second) { drow[cc] = z[e]; prm.second[dense + cc] = y[e]; }
                 else drow[cc] = y[e];
-            }
+            } else y[e] = 0.0f;
         }
     }
     if (prm.nhi) {
@@ -348,7 +370,7 @@ __device__ __forceinline__ void epilogue_emit4(const TcParams &prm, int row, int
     }
 }
 
-template <int BN>
+template <int BN, bool GENERAL>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tf32x3_kernel(
         const __grid_constant__ CUtensorMap map_p_hi, const __grid_constant__ CUtensorMap map_p_lo,
         const __grid_constant__ CUtensorMap map_q_hi, const __grid_constant__ CUtensorMap map_q_lo, TcParams prm) {
@@ -472,7 +494,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tf32x3_kernel(
                 if (row_ok && col0 < prm.n) {
 #pragma unroll
                     for (int q = 0; q < 8; q++)
-                        epilogue_emit4(prm, row, col0 + q * 4, v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3], vec_ok);
+                        epilogue_emit4<GENERAL>(prm, row, col0 + q * 4, v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3], vec_ok);
                 }
             }
             tc_fence_before();
@@ -516,7 +538,7 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, float (&v)[16]) {
 }
 
 
-template <int BN>
+template <int BN, bool GENERAL>
 __global__ void __launch_bounds__(PROMOTED_THREADS, 1) gemm_tf32x3_promoted_kernel(
         const __grid_constant__ CUtensorMap map_p_hi, const __grid_constant__ CUtensorMap map_p_lo,
         const __grid_constant__ CUtensorMap map_q_hi, const __grid_constant__ CUtensorMap map_q_lo, TcParams prm) {
@@ -665,7 +687,7 @@ __global__ void __launch_bounds__(PROMOTED_THREADS, 1) gemm_tf32x3_promoted_kern
                 for (int g = 0; g < CPT / 4; g++) {
                     const int col = n0 + half * CPT + g * 4;
                     if ((col & ~31) < prm.n)
-                        epilogue_emit4(prm, row, col, sum[g * 4], sum[g * 4 + 1], sum[g * 4 + 2], sum[g * 4 + 3], vec_ok);
+                        epilogue_emit4<GENERAL>(prm, row, col, sum[g * 4], sum[g * 4 + 1], sum[g * 4 + 2], sum[g * 4 + 3], vec_ok);
                 }
             }
         }
@@ -753,7 +775,7 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
 }
 
-template <int BN, bool SLICED, bool DYNAMIC>
+template <int BN, bool SLICED, bool DYNAMIC, bool GENERAL>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1) gemm_tf32x3_pair_kernel(
         const __grid_constant__ CUtensorMap map_p_hi, const __grid_constant__ CUtensorMap map_p_lo,
         const __grid_constant__ CUtensorMap map_q_hi, const __grid_constant__ CUtensorMap map_q_lo, TcParams prm, SliceParams slc) {
@@ -982,7 +1004,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1)
                 for (int g = 0; g < CPT / 4; g++) {
                     const int col = n0 + half * CPT + g * 4;
                     if ((col & ~31) < prm.n)
-                        epilogue_emit4(prm, row, col, sum[g * 4], sum[g * 4 + 1], sum[g * 4 + 2], sum[g * 4 + 3], vec_ok);
+                        epilogue_emit4<GENERAL>(prm, row, col, sum[g * 4], sum[g * 4 + 1], sum[g * 4 + 2], sum[g * 4 + 3], vec_ok);
                 }
             }
         }
@@ -1209,16 +1231,15 @@ TensorCoreGemm *tc_gemm_prepare(const TcOperand &p, const TcOperand &q, int64_t 
 void tc_gemm_release(TensorCoreGemm *g) { delete g; }
 int64_t tc_gemm_workspace_floats(const TensorCoreGemm *g) { return g->slices > 1 ? (int64_t)g->slices * g->m * g->slice_ld : 0; }
 
-template <int BN>
+template <int BN, bool GENERAL>
 static cudaError_t launch_tc(cudaStream_t s, const TensorCoreGemm *g, const TcParams &prm, const SliceParams &slc) {
     using Cfg = TileConfig<BN>;
-    // a per-device attribute: set on every launch so each GPU of the process has it
-    cudaError_t e = cudaFuncSetAttribute(gemm_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-    if (e != cudaSuccess) return e;
+    cudaError_t e = cudaSuccess;
     if (g->pair) {
         if constexpr (BN >= 128) {
             using Pair = PairConfig<BN>;
             auto launch_pair = [&](auto kernel) -> cudaError_t {
+                // per-device attributes: set on every launch so each GPU of the process has them
                 cudaFuncAttributes attr;
                 cudaError_t pe = cudaFuncGetAttributes(&attr, kernel);
                 if (pe != cudaSuccess) return pe;
@@ -1228,22 +1249,25 @@ static cudaError_t launch_tc(cudaStream_t s, const TensorCoreGemm *g, const TcPa
                 kernel<<<g->grid, PROMOTED_THREADS, Pair::kSmemBytes, s>>>(g->p_hi, g->p_lo, g->q_hi, g->q_lo, prm, slc);
                 return cudaSuccess;
             };
-            if (slc.unit_counter) e = g->slices > 1 ? launch_pair(gemm_tf32x3_pair_kernel<BN, true, true>) : launch_pair(gemm_tf32x3_pair_kernel<BN, false, true>);
-            else e = g->slices > 1 ? launch_pair(gemm_tf32x3_pair_kernel<BN, true, false>) : launch_pair(gemm_tf32x3_pair_kernel<BN, false, false>);
+            // a sliced product has no epilogue work, so no activation either
+            if (g->slices > 1) e = slc.unit_counter ? launch_pair(gemm_tf32x3_pair_kernel<BN, true, true, false>) : launch_pair(gemm_tf32x3_pair_kernel<BN, true, false, false>);
+            else e = slc.unit_counter ? launch_pair(gemm_tf32x3_pair_kernel<BN, false, true, GENERAL>) : launch_pair(gemm_tf32x3_pair_kernel<BN, false, false, GENERAL>);
             if (e != cudaSuccess) return e;
         } else return cudaErrorInvalidValue;
     } else if (g->promote) {
         // the kernel redistributes registers between its warpgroups (72 and 216 per thread); that only
         // terminates when the launch allocation covers the sum, so check it instead of trusting it
         cudaFuncAttributes attr;
-        e = cudaFuncGetAttributes(&attr, gemm_tf32x3_promoted_kernel<BN>);
+        e = cudaFuncGetAttributes(&attr, gemm_tf32x3_promoted_kernel<BN, GENERAL>);
         if (e != cudaSuccess) return e;
         if (attr.numRegs * PROMOTED_THREADS < 128 * 72 + 256 * 216) return cudaErrorLaunchOutOfResources;
-        e = cudaFuncSetAttribute(gemm_tf32x3_promoted_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        e = cudaFuncSetAttribute(gemm_tf32x3_promoted_kernel<BN, GENERAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
         if (e != cudaSuccess) return e;
-        gemm_tf32x3_promoted_kernel<BN><<<g->grid, PROMOTED_THREADS, Cfg::kSmemBytes, s>>>(g->p_hi, g->p_lo, g->q_hi, g->q_lo, prm);
+        gemm_tf32x3_promoted_kernel<BN, GENERAL><<<g->grid, PROMOTED_THREADS, Cfg::kSmemBytes, s>>>(g->p_hi, g->p_lo, g->q_hi, g->q_lo, prm);
     } else {
-        gemm_tf32x3_kernel<BN><<<g->grid, GEMM_THREADS, Cfg::kSmemBytes, s>>>(g->p_hi, g->p_lo, g->q_hi, g->q_lo, prm);
+        e = cudaFuncSetAttribute(gemm_tf32x3_kernel<BN, GENERAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        if (e != cudaSuccess) return e;
+        gemm_tf32x3_kernel<BN, GENERAL><<<g->grid, GEMM_THREADS, Cfg::kSmemBytes, s>>>(g->p_hi, g->p_lo, g->q_hi, g->q_lo, prm);
     }
     return cudaGetLastError();
 }
@@ -1255,15 +1279,18 @@ cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, in
     slc.slices = g->slices; slc.kb_per_slice = g->kb_per_slice; slc.ws = workspace; slc.ld = g->slice_ld;
     slc.group_n = g->group_n;
     slc.unit_counter = g->pair ? unit_counter : nullptr;
-    if (g->slices > 1 && (!workspace || ep.bias || ep.gate || ep.second || ep.relu || ep.plane_hi)) return cudaErrorInvalidValue;
+    if (g->slices > 1 && (!workspace || ep.bias || ep.gate || ep.second || ep.act || ep.plane_hi)) return cudaErrorInvalidValue;
     prm.nhi = ep.plane_hi; prm.nlo = ep.plane_lo; prm.nld = ep.plane_ld;
     prm.p_mn = g->p_mn; prm.q_mn = g->q_mn;
     prm.d = d; prm.ldd = ldd; prm.m = g->m; prm.n = g->n; prm.k_blocks = g->k_blocks;
     const int tile_m = g->pair ? 2 * BM : BM;
     prm.tiles_m = (g->m + tile_m - 1) / tile_m; prm.tiles_n = (g->n + g->bn - 1) / g->bn;
     prm.chunk_kb = g->chunk_kb;
-    prm.bias = ep.bias; prm.gate = ep.gate; prm.second = ep.second; prm.relu = ep.relu; prm.error_word = error_word;
-    cudaError_t e = g->bn == 256 ? launch_tc<256>(s, g, prm, slc) : g->bn == 128 ? launch_tc<128>(s, g, prm, slc) : launch_tc<64>(s, g, prm, slc);
+    prm.bias = ep.bias; prm.gate = ep.gate; prm.second = ep.second; prm.act = ep.act; prm.error_word = error_word;
+    const bool general = ep.act != 0 && ep.act != (int)Op::RELU;
+    cudaError_t e;
+    if (general) e = g->bn == 256 ? launch_tc<256, true>(s, g, prm, slc) : g->bn == 128 ? launch_tc<128, true>(s, g, prm, slc) : launch_tc<64, true>(s, g, prm, slc);
+    else e = g->bn == 256 ? launch_tc<256, false>(s, g, prm, slc) : g->bn == 128 ? launch_tc<128, false>(s, g, prm, slc) : launch_tc<64, false>(s, g, prm, slc);
     if (e != cudaSuccess || g->slices <= 1) return e;
     const int64_t total = (int64_t)g->m * (g->slice_ld >> 2);
     const int64_t blocks = (total + 255) / 256;

@@ -3,6 +3,7 @@
 // passes.  All use coalesced (128-bit where alignment allows) accesses and warp-shuffle
 // reductions; none uses tensor cores on purpose -- they are bounded by HBM bandwidth.
 #include "kernels.hpp"
+#include "activation.cuh"
 #include "split.cuh"
 
 #include <cfloat>
@@ -21,10 +22,6 @@ inline int grid_for(int64_t total, int per_block, int cap = 148 * 16) {
     int64_t blocks = (total + per_block - 1) / per_block;
     if (blocks < 1) blocks = 1;
     return (int)(blocks > cap ? cap : blocks);
-}
-
-__device__ __forceinline__ float relu_value(float x) {      // Math.max(x, +0.0f): NaN stays NaN, -0 -> +0
-    return x != x ? x : (x > 0.0f ? x : 0.0f);
 }
 
 // exp(x) in binary32, within 0.78 ulp of the exact value (measured on the host over a uniform
@@ -177,48 +174,6 @@ __global__ void scalar_f32_kernel(int op, const float *__restrict__ a, float *ou
         else if ((Op)op == Op::SCALAR_MIN) out[i] = java_min(x, scalar);
         else out[i] = java_max(x, scalar);
     }
-}
-
-// TANH and SIGMOID follow the reference's FLOAT32 path: the elementary function in binary64, one
-// narrowing to binary32 (CpuScalarReferenceKernel.java:1729-1742; sigmoid as 1 / (1 + exp(-x)) for
-// x >= 0 and exp(x) / (1 + exp(x)) below, CpuScalarEmitter.java:429-439).  The device's binary64 tanh
-// and exp are within 1-2 ulp of binary64, so the narrowed result differs from (float)StrictMath only on
-// rounding ties of probability ~2^-28.
-__device__ __forceinline__ float tanh_value(float x) { return (float)tanh((double)x); }
-__device__ __forceinline__ float sigmoid_value(float x) {
-    const double v = (double)x;
-    if (v < 0.0 || v != v) { const double e = exp(v); return (float)(e / (1.0 + e)); }
-    return (float)(1.0 / (1.0 + exp(-v)));
-}
-
-// SILU, CpuScalarReferenceKernel.java:1236-1241: -inf gives -0; x / (1 + exp(-x)) for x >= 0,
-// x * exp(x) / (1 + exp(x)) below (and for NaN), in binary64, one narrowing.
-__device__ __forceinline__ float silu_value(float x) {
-    const double v = (double)x;
-    if (v == -CUDART_INF) return -0.0f;
-    if (v >= 0.0) return (float)(v / (1.0 + exp(-v)));
-    const double e = exp(v);
-    return (float)(v * e / (1.0 + e));
-}
-
-// Tanh-approximated GELU, CpuScalarReferenceKernel.java:1224-1229: -inf gives -0; otherwise
-// 0.5 * x * (1 + tanh(sqrt(2 / pi) * (x + 0.044715 * x^3))) in binary64, one narrowing.
-__device__ __forceinline__ float gelu_tanh_value(float x) {
-    const double v = (double)x;
-    if (v == -CUDART_INF) return -0.0f;
-    const double cube = v * v * v;
-    return (float)(0.5 * v * (1.0 + tanh(sqrt(2.0 / 3.14159265358979323846) * (v + 0.044715 * cube))));
-}
-
-// ERF and the exact GELU on FLOAT32 (CpuScalarEmitter.java:353-366,441-452): the value widened to
-// binary64, erf (the reference's rational approximation is accurate to binary64 rounding, returns
-// the signed zero unchanged and +-1 from |x| = 6 on, as the library function rounds to), for GELU
-// 0.5 * x * (1 + erf(x / sqrt(2))) with -inf giving -0, then one narrowing.
-__device__ __forceinline__ float erf_value(float x) { return (float)erf((double)x); }
-__device__ __forceinline__ float gelu_value(float x) {
-    const double v = (double)x;
-    if (v == -CUDART_INF) return -0.0f;
-    return (float)(0.5 * v * (1.0 + erf(v / sqrt(2.0))));
 }
 
 __global__ void unary_kernel(int op, const float *__restrict__ a, void *out_raw, int64_t total) {
@@ -1232,30 +1187,66 @@ __global__ void __launch_bounds__(kThreads) sgd_kernel(SlotTable table, SgdArgs 
 // Adam / AdamW, TrainingParameter.java:433-525: m = b1*m + (1-b1)*g; v = b2*v + (1-b2)*(g*g);
 // update = (lr * (m / c1)) / (sqrt(v / c2) + eps), the product formed before the division.  Reads
 // p, m, v, acc, g; writes the candidates p_out, m_out, v_out (28 bytes per parameter either way).
+// One element; returns true when any intermediate is non-finite.
+__device__ __forceinline__ bool adam_element(const AdamArgs &a, float one_minus_b1, float one_minus_b2, float p, float g, float pending,
+                                             float m0, float v0, float &p_new, float &m_new, float &v_new) {
+    bool bad = false;
+    float basev;
+    if (a.gradient_mode == 2) { g = __fadd_rn(pending, g); bad |= !finite(g); }
+    if (a.decoupled) basev = __fmul_rn(p, a.decay_factor);
+    else { g = __fadd_rn(g, __fmul_rn(a.decay, p)); basev = p; }
+    const float m = __fadd_rn(__fmul_rn(a.b1, m0), __fmul_rn(one_minus_b1, g));
+    const float sq = __fmul_rn(g, g);
+    const float v = __fadd_rn(__fmul_rn(a.b2, v0), __fmul_rn(one_minus_b2, sq));
+    const float mh = __fdiv_rn(m, a.correction1), vh = __fdiv_rn(v, a.correction2);
+    const float den = __fadd_rn(__fsqrt_rn(vh), a.eps);
+    const float num = __fmul_rn(a.lr, mh);
+    const float update = __fdiv_rn(num, den);
+    const float candidate = __fsub_rn(basev, update);
+    bad |= !finite(p) || !finite(g) || !finite(m) || !finite(sq) || !finite(v) || !finite(mh) || !finite(vh)
+           || !finite(den) || !(den > 0.0f) || !finite(num) || !finite(update) || !finite(candidate);
+    p_new = candidate; m_new = m; v_new = v;
+    return bad;
+}
+
 __global__ void __launch_bounds__(kThreads) adam_kernel(SlotTable table, AdamArgs a, int *error_word) {
     if (step_is_void(error_word, a.sequence, a.failed_sequence)) return;
     int t = 0;
     while (t + 1 < table.count && (int64_t)blockIdx.x >= table.first_block[t + 1]) t++;
     const TensorSlot s = table.slot[t];
-    int64_t base = ((int64_t)blockIdx.x - table.first_block[t]) * kOptElemsPerBlock;
+    const int64_t base = ((int64_t)blockIdx.x - table.first_block[t]) * kOptElemsPerBlock;
+    const int64_t end = base + kOptElemsPerBlock < s.count ? base + kOptElemsPerBlock : s.count;
     const float one_minus_b1 = __fsub_rn(1.0f, a.b1), one_minus_b2 = __fsub_rn(1.0f, a.b2);
+    const bool with_pending = a.gradient_mode == 2;
     bool bad = false;
-    for (int64_t i = base + threadIdx.x; i < base + kOptElemsPerBlock && i < s.count; i += kThreads) {
-        float p = s.p[i], g = s.g[i], basev;
-        if (a.gradient_mode == 2) { g = __fadd_rn(s.acc[i], g); bad |= !finite(g); }
-        if (a.decoupled) basev = __fmul_rn(p, a.decay_factor);
-        else { g = __fadd_rn(g, __fmul_rn(a.decay, p)); basev = p; }
-        float m = __fadd_rn(__fmul_rn(a.b1, s.m[i]), __fmul_rn(one_minus_b1, g));
-        float sq = __fmul_rn(g, g);
-        float v = __fadd_rn(__fmul_rn(a.b2, s.v[i]), __fmul_rn(one_minus_b2, sq));
-        float mh = __fdiv_rn(m, a.correction1), vh = __fdiv_rn(v, a.correction2);
-        float den = __fadd_rn(__fsqrt_rn(vh), a.eps);
-        float num = __fmul_rn(a.lr, mh);
-        float update = __fdiv_rn(num, den);
-        float candidate = __fsub_rn(basev, update);
-        bad |= !finite(p) || !finite(g) || !finite(m) || !finite(sq) || !finite(v) || !finite(mh) || !finite(vh)
-               || !finite(den) || !(den > 0.0f) || !finite(num) || !finite(update) || !finite(candidate);
-        s.p_out[i] = candidate; s.m_out[i] = m; s.v_out[i] = v;
+    // 16-byte loads and stores (the block's first element is a multiple of 2048, so alignment is that of
+    // the arrays themselves); whatever is left at the end of the tensor goes element by element
+    const bool vec = ((((uintptr_t)s.p | (uintptr_t)s.g | (uintptr_t)s.m | (uintptr_t)s.v | (uintptr_t)s.p_out | (uintptr_t)s.m_out
+                        | (uintptr_t)s.v_out | (with_pending ? (uintptr_t)s.acc : 0)) & 15) == 0);
+    int64_t scalar_from = base;
+    if (vec) {
+        const int64_t quads = (end - base) >> 2;
+        for (int64_t q = threadIdx.x; q < quads; q += kThreads) {
+            const int64_t i = base + (q << 2);
+            const float4 p = *reinterpret_cast<const float4 *>(s.p + i), g = *reinterpret_cast<const float4 *>(s.g + i);
+            const float4 m = *reinterpret_cast<const float4 *>(s.m + i), v = *reinterpret_cast<const float4 *>(s.v + i);
+            float4 pending = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (with_pending) pending = *reinterpret_cast<const float4 *>(s.acc + i);
+            float4 pn, mn, vn;
+            bad |= adam_element(a, one_minus_b1, one_minus_b2, p.x, g.x, pending.x, m.x, v.x, pn.x, mn.x, vn.x);
+            bad |= adam_element(a, one_minus_b1, one_minus_b2, p.y, g.y, pending.y, m.y, v.y, pn.y, mn.y, vn.y);
+            bad |= adam_element(a, one_minus_b1, one_minus_b2, p.z, g.z, pending.z, m.z, v.z, pn.z, mn.z, vn.z);
+            bad |= adam_element(a, one_minus_b1, one_minus_b2, p.w, g.w, pending.w, m.w, v.w, pn.w, mn.w, vn.w);
+            *reinterpret_cast<float4 *>(s.p_out + i) = pn;
+            *reinterpret_cast<float4 *>(s.m_out + i) = mn;
+            *reinterpret_cast<float4 *>(s.v_out + i) = vn;
+        }
+        scalar_from = base + (quads << 2);
+    }
+    for (int64_t i = scalar_from + threadIdx.x; i < end; i += kThreads) {
+        float pn, mn, vn;
+        bad |= adam_element(a, one_minus_b1, one_minus_b2, s.p[i], s.g[i], with_pending ? s.acc[i] : 0.0f, s.m[i], s.v[i], pn, mn, vn);
+        s.p_out[i] = pn; s.m_out[i] = mn; s.v_out[i] = vn;
     }
     if (bad) { atomicOr(error_word, ERR_NON_FINITE); atomicMin(a.failed_sequence, a.sequence); }
 }

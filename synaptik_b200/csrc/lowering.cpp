@@ -156,6 +156,7 @@ struct Matcher {
 
 struct LinearGroup {          // MATMUL [-> ADD bias] [-> RELU] [-> gate by WHERE(GT(.,0),.,0)]
     int matmul = -1, add = -1, relu = -1, where = -1, gt = -1;
+    int act = 0;                  // wire code of a fused activation other than ReLU (its node is `relu`)
     int bias = -1, mask = -1;
     int out = -1, out2 = -1;
     int emit_at = -1;
@@ -481,6 +482,19 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
             } else {
                 lg.out2 = y;
             }
+        } else {
+            // the other activations of the CPU backend's epilogue vocabulary (CpuMatmulIr.java:96-101): the
+            // first such reader of z joins the product; z itself is stored as well when anything else reads
+            // it (the SILU / GELU gradient rules do) or it is published
+            for (int c : g.values[z].consumers) {
+                const Op op = g.nodes[c].op;
+                if (covered[c] || (op != Op::TANH && op != Op::SIGMOID && op != Op::SILU && op != Op::GELU_TANH && op != Op::GELU)) continue;
+                lg.relu = c; lg.act = (int)op;
+                const int y = g.nodes[c].outputs[0];
+                if (g.values[z].publication < 0 && g.values[z].consumers.size() == 1) lg.out = y;
+                else lg.out2 = y;
+                break;
+            }
         }
         if (lg.add < 0 && lg.relu < 0) group_of_matmul_output[mm.outputs[0]] = (int)linear.size();
         linear.push_back(lg);
@@ -562,7 +576,7 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
         st.kind = StepKind::GEMM;
         st.a = mm.inputs[0]; st.b = mm.inputs[1];
         st.k = g.values[st.a].shape.back(); st.m = g.values[st.a].elements() / st.k; st.n = g.values[st.b].shape[1];
-        st.bias = lg.bias; st.mask = lg.mask; st.relu = lg.relu >= 0;
+        st.bias = lg.bias; st.mask = lg.mask; st.relu = lg.relu >= 0 && lg.act == 0; st.act = lg.act;
         st.out = lg.out; st.out2 = lg.out2;
         st.engine = choose_engine(st.m, st.n, st.k);
         for (int n : {lg.matmul, lg.add, lg.relu, lg.where, lg.gt}) if (n >= 0) { covered[n] = 1; st.nodes.push_back(n); }
@@ -791,7 +805,7 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
             {
                 const View &c = plan.views[st.out];
                 bool transposed = c.strides.size() == 2 && c.strides[0] == 1 && c.shape[0] != 1 && c.strides[1] != 1;
-                if (transposed && (st.bias >= 0 || st.mask >= 0 || st.relu)) { message = "transposed GEMM result with an epilogue"; return UNSUPPORTED_SHAPE; }
+                if (transposed && (st.bias >= 0 || st.mask >= 0 || st.relu || st.act)) { message = "transposed GEMM result with an epilogue"; return UNSUPPORTED_SHAPE; }
                 const View &a = plan.views[st.a], &b = plan.views[st.b];
                 bool a_ok = a.strides[0] == 1 || a.strides[1] == 1 || a.shape[0] == 1 || a.shape[1] == 1;
                 bool b_ok = b.strides[0] == 1 || b.strides[1] == 1 || b.shape[0] == 1 || b.shape[1] == 1;
@@ -800,13 +814,13 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
                 if (options.gemm_engine != 1 && st.engine == GemmEngine::EXACT_SIMT && st.out2 < 0
                     && (double)st.m * (double)st.n * (double)st.k >= 16.0 * 1024 * 1024) {
                     const bool c_rows = c.strides[1] == 1 || c.shape[1] == 1;
-                    if (st.n <= 16 && st.mask < 0 && a.strides[1] == 1 && b.strides[0] == 1
+                    if (st.n <= 16 && st.mask < 0 && !st.act && a.strides[1] == 1 && b.strides[0] == 1
                         && kern::narrow_out_supported(st.m, st.n, st.k, a.strides[0], b.strides[1]))
                         st.engine = GemmEngine::NARROW_OUT;
-                    else if (st.k <= 16 && st.bias < 0 && !st.relu && a.strides[1] == 1 && b.strides[1] == 1 && c_rows && !transposed
+                    else if (st.k <= 16 && st.bias < 0 && !st.relu && !st.act && a.strides[1] == 1 && b.strides[1] == 1 && c_rows && !transposed
                              && kern::narrow_inner_supported(st.m, st.n, st.k, b.strides[0], c.strides[0]))
                         st.engine = GemmEngine::NARROW_INNER;
-                    else if (st.n <= 16 && st.bias < 0 && !st.relu && st.mask < 0 && a.strides[0] == 1 && b.strides[1] == 1
+                    else if (st.n <= 16 && st.bias < 0 && !st.relu && !st.act && st.mask < 0 && a.strides[0] == 1 && b.strides[1] == 1
                              && kern::narrow_reduce_supported(st.m, st.n, st.k, a.strides[1]))
                         st.engine = GemmEngine::NARROW_REDUCE;
                 }
@@ -1076,6 +1090,7 @@ std::string describe_plan(const Program &g, const Plan &plan) {
                << " m=" << st.m << " n=" << st.n << " k=" << st.k;
             if (st.bias >= 0) os << " bias";
             if (st.relu) os << " relu";
+            if (st.act) os << " act=" << op_name((Op)st.act);
             if (st.out2 >= 0) os << " keep_preactivation";
             if (st.mask >= 0) os << " relu_gate";
             const View &c = plan.views[st.out];

@@ -3,7 +3,8 @@
 // The partition is pattern-matched structurally (never by node position, because the reference's
 // exact graph optimisations may fold constants or merge duplicates,
 // docs/explanation/packages/execution.md:398-406):
-//   * MATMUL -> ADD(row-broadcast bias) -> RELU            one GEMM with a bias/activation epilogue
+//   * MATMUL -> ADD(row-broadcast bias) -> RELU | TANH | SIGMOID | SILU | GELU_TANH | GELU
+//                                                         one GEMM with a bias/activation epilogue
 //     (the anchor-epilogue fusion the Metal backend recognises,
 //     modules/backend/metal/.../MetalAnchorEpilogueRecognizer.java:70-147); the pre-activation is
 //     not stored when its only other readers are GT(z, 0) predicates, which then read the stored
@@ -53,6 +54,7 @@ struct Step {
     int out = -1, out2 = -1, out3 = -1;   // output value ids
     int bias = -1, mask = -1;       // GEMM epilogue operands
     bool relu = false;
+    int act = 0;                    // GEMM epilogue activation other than ReLU: the wire code of TANH, SIGMOID, SILU, GELU_TANH or GELU
     int64_t m = 0, n = 0, k = 0;    // GEMM extents, or rows / cols of row kernels
     uint64_t scalar_bits = 0;       // SCALAR operand, ONE_HOT depth, loss reduction
     bool batch_contraction = false; // GEMM: a and b are dense [batch.., rows, x] tensors contracted over batch * rows

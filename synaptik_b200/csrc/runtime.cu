@@ -265,8 +265,8 @@ int32_t wait_with_deadline(Context *ctx, cudaEvent_t event) {
         if ((spin & 127u) != 127u) continue;
         for (Comm *c : ctx->comms) {
             int async = 0;
-            if (c->dead) failed = true;
-            else if (nccl().CommGetAsyncError && nccl().CommGetAsyncError(c->comm, &async) == 0 && async != 0 && async != 7 /*ncclInProgress*/) failed = true;
+            if (c->dead) continue;          // already given up on: nothing of it is in flight
+            if (nccl().CommGetAsyncError && nccl().CommGetAsyncError(c->comm, &async) == 0 && async != 0 && async != 7 /*ncclInProgress*/) failed = true;
         }
         const auto waited = std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - start).count();
         if (waited > ctx->comm_timeout_ms * 1000) failed = true;
@@ -419,7 +419,7 @@ int32_t prepare_executable(Executable *x) {
             oa.hi = A.hi; oa.lo = A.lo; oa.pitch = A.pitch; oa.mn_major = se.orient_a == 1;
             ob.hi = B.hi; ob.lo = B.lo; ob.pitch = B.pitch; ob.mn_major = se.orient_b == 0;
             int status = OK;
-            const bool plain = st.bias < 0 && st.mask < 0 && !st.relu && st.out2 < 0;
+            const bool plain = st.bias < 0 && st.mask < 0 && !st.relu && !st.act && st.out2 < 0;
             const int mode = ctx->gemm_promote | (ctx->gemm_pair << 1) | ((plain && ctx->gemm_slices) ? 4 : 0);
             se.tc = se.swapped ? kern::tc_gemm_prepare(ob, oa, st.n, st.m, st.k, ctx->sm_count, mode, &status)
                                : kern::tc_gemm_prepare(oa, ob, st.m, st.n, st.k, ctx->sm_count, mode, &status);
@@ -534,12 +534,12 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                 kern::GemmEpilogue ep;
                 ep.bias = (const float *)ptr(st.bias);
                 ep.gate = (const float *)ptr(st.mask);
-                ep.relu = st.relu && st.out2 < 0;
+                ep.act = st.relu ? (int)Op::RELU : st.act;        // with a second output: out = z, second = act(z)
                 ep.second = (float *)ptr(st.out2);
                 cudaError_t narrow = cudaErrorInvalidValue;
                 if (st.engine == GemmEngine::NARROW_OUT)
                     narrow = kern::gemm_narrow_out(s, ctx->sm_count, st.m, st.n, st.k, (const float *)ptr(st.a), a.strides[0], (const float *)ptr(st.b),
-                                                   b.strides[1], ep.bias, ep.relu, (float *)ptr(st.out), c.strides[0], c.strides[1]);
+                                                   b.strides[1], ep.bias, st.relu ? 1 : 0, (float *)ptr(st.out), c.strides[0], c.strides[1]);
                 else if (st.engine == GemmEngine::NARROW_INNER)
                     narrow = kern::gemm_narrow_inner(s, st.m, st.n, st.k, (const float *)ptr(st.a), a.strides[0], (const float *)ptr(st.b),
                                                      b.strides[0], ep.gate, (float *)ptr(st.out), c.strides[0]);

@@ -24,14 +24,16 @@ typedef int (*launch_host_fn)(void *stream, void (*fn)(void *), void *user);
 static volatile int g_aborted = 0;
 
 /* Sleeps for the given time in slices of 5 ms and returns early once a communicator has been aborted
- * after the stall began (the real library ends its kernels on abort). */
+ * after the all-reduce was CALLED (the real library ends its kernels on abort; the count is taken at the
+ * call, not when the stream gets round to running this function, which may be after the abort). */
+typedef struct { long ms; int aborted_at_call; } stall_request;
 static void stall(void *user) {
-    long ms = (long)(intptr_t)user;
-    const int aborted_before = g_aborted;
-    for (long waited = 0; waited < ms && g_aborted == aborted_before; waited += 5) {
+    stall_request *request = (stall_request *)user;
+    for (long waited = 0; waited < request->ms && g_aborted == request->aborted_at_call; waited += 5) {
         struct timespec nap = {0, 5 * 1000000L};
         nanosleep(&nap, NULL);
     }
+    free(request);
 }
 
 FAKE_EXPORT int ncclGetUniqueId(fake_unique_id *id) {
@@ -61,6 +63,9 @@ FAKE_EXPORT int ncclAllReduce(const void *send, void *recv, size_t count, int dt
     void *cuda = dlopen("libcuda.so.1", RTLD_NOW | RTLD_NOLOAD);
     launch_host_fn launch = cuda ? (launch_host_fn)dlsym(cuda, "cuLaunchHostFunc") : NULL;
     if (!launch) return 0;
-    return launch(stream, stall, (void *)(intptr_t)ms) == 0 ? 0 : 1;
+    stall_request *request = (stall_request *)malloc(sizeof *request);
+    if (!request) return 2;
+    request->ms = ms; request->aborted_at_call = g_aborted;
+    return launch(stream, stall, request) == 0 ? 0 : 1;
 }
 FAKE_EXPORT int fake_nccl_abort_count(void) { return g_aborted; }

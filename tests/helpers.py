@@ -1,4 +1,7 @@
 """Shared helpers of the GPU parity tests: run a program image through the C ABI."""
+import json
+import os
+
 import numpy as np
 
 from synaptik_b200 import native, program
@@ -43,3 +46,26 @@ def ulp_distance(a: np.ndarray, b: np.ndarray) -> np.ndarray:
     ia = np.where(ia < 0, -(ia & 0x7FFFFFFF), ia)
     ib = np.where(ib < 0, -(ib & 0x7FFFFFFF), ib)
     return np.abs(ia - ib)
+
+
+def report(name: str, table) -> None:
+    """Writes a test's measured figures as JSON into the folder SYNAPTIK_TEST_REPORT_DIR names (when it
+    is set), so that stated tolerances can be compared with what a run actually measured."""
+    folder = os.environ.get("SYNAPTIK_TEST_REPORT_DIR")
+    if not folder:
+        return
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, f"parity_{name}.json"), "w") as out:
+        json.dump(table, out, indent=1)
+
+
+def trajectory_distance(got, want, start, lr: float, step: int) -> dict:
+    """How far two optimizer trajectories are apart after `step` steps: the relative L2 distance of the
+    cumulative updates (p - p0), the share of entries further apart than a tenth of lr * step (the
+    furthest Adam can have moved them is about lr * step), mean and maximum absolute difference."""
+    got, want, start = (np.asarray(a, dtype=np.float32).ravel() for a in (got, want, start))
+    drift = np.abs(got - want)
+    moved = float(np.linalg.norm((want - start).astype(np.float64)))
+    apart = float(np.linalg.norm((got - want).astype(np.float64)))
+    return {"relative_l2": apart / moved if moved > 0 else (0.0 if apart == 0 else float("inf")),
+            "share_apart": float(np.mean(drift > 0.1 * lr * step)), "mean": float(drift.mean()), "max": float(drift.max())}

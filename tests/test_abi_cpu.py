@@ -275,3 +275,20 @@ def test_unobserved_nodes_are_not_launched(lib):
     b.publish(b.permute(dwt, (1, 0)))
     b.relu(b.add(x, x))
     assert _plan(b) == ["gemm engine=exact_simt m=32 n=16 k=64 transposed_result"]
+
+
+@pytest.mark.parametrize("activation,name", [("tanh", "TANH"), ("sigmoid", "SIGMOID"), ("silu", "SILU"), ("gelu_tanh", "GELU_TANH_APPROXIMATION"), ("gelu", "GELU")])
+def test_the_other_activations_ride_in_the_gemm_epilogue_too(lib, activation, name):
+    # the CPU backend's epilogue vocabulary (CpuMatmulIr.java:96-101): bias, then one terminal activation
+    g = program.mlp_inference_graph([784, 4096, 4096, 10], 8192, activation=activation)
+    plan = native.describe(g.image).strip().split("\n")
+    assert not any(p.startswith("unary") for p in plan), plan
+    assert sum(f"bias act={name}" in p and "tcgen05_3xtf32" in p for p in plan) == 2
+    # training: TANH / SIGMOID differentiate through the stored activation, SILU / GELU through the stored
+    # pre-activation, which the product then writes beside the activation
+    g = program.mlp_training_graph([784, 4096, 4096, 10], 8192, "ce", activation=activation)
+    plan = native.describe(g.image).strip().split("\n")
+    fused = [p for p in plan if f"act={name}" in p]
+    assert len(fused) == 2 and not any(p.startswith("unary") and f"op={name}" in p for p in plan), plan
+    keeps = sum("keep_preactivation" in p for p in fused)
+    assert keeps == (0 if activation in ("tanh", "sigmoid") else 2), plan

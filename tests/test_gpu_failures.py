@@ -231,6 +231,7 @@ try:
 except native.NativeFailure as failure:
     status = failure.status
 waited = time.perf_counter() - start
+print("first all-reduce: status", status, "after", round(waited, 4), "s", flush=True)
 assert status == 15, status
 limit = float(os.environ["SYN_EXPECT_WITHIN"])
 assert waited < limit, waited

@@ -4,7 +4,7 @@ import pytest
 
 from synaptik_b200 import native, nn
 
-from helpers import ulp_distance
+from helpers import report, trajectory_distance, ulp_distance
 
 pytestmark = pytest.mark.gpu
 
@@ -119,6 +119,8 @@ def test_classifier_training_tracks_the_checker_for_20_steps(ctx, oracle, engine
         x = rng.uniform(0, 1, (batch, dims[0])).astype(np.float32)
         labels = rng.integers(0, 10, batch)
         ref = [p.copy() for p in model.parameters()]
+        initial = [p.copy() for p in ref]
+        table = []
         m = [np.zeros(p.size, dtype=np.float32) for p in ref]
         v = [np.zeros(p.size, dtype=np.float32) for p in ref]
         grad_tol = 1e-4 if engine == 2 else 2e-6
@@ -143,19 +145,23 @@ def test_classifier_training_tracks_the_checker_for_20_steps(ctx, oracle, engine
                 for i, g in enumerate(ref_grads):
                     flat = ref[i].reshape(-1)
                     assert oracle.adam(flat, g.reshape(-1), m[i], v[i], step)
-                # post-step parameters: Adam's update is lr * mhat / (sqrt(vhat) + eps) ~ lr in size, so
-                # a relative gradient error e moves a parameter by about lr * e
-                # Adam divides by sqrt(vhat) + eps, so a gradient entry near zero turns an absolute
-                # gradient error of 1e-8 into a visible fraction of lr: no entry can move further
-                # than 2 * lr per step, and the mean drift stays at rounding level (on the tensor-core
-                # engine a hidden unit gated the other way than in the checker moves its own bias and
-                # weights visibly, so only the looser mean holds there; the tight checks of that engine
-                # are the backward-on-own-gates test above and the bit-exact optimizer tests)
-                for got, want in zip(model.parameters(), ref):
-                    drift = np.abs(got - want)
+                # post-step parameters.  Adam's update is lr * mhat / (sqrt(vhat) + eps): about lr whatever the
+                # gradient's size, so a gradient entry at rounding level (or a hidden unit gated the other way
+                # than in the checker, on the tensor-core engine) can move its parameter by a visible fraction
+                # of lr while every kernel is right.  A bound of 2 * lr * step per entry would hold for ANY two
+                # trajectories; what binds is (a) the cumulative update as a whole: relative L2 distance of
+                # (p - p0) between device and checker, (b) the share of entries further apart than a tenth of
+                # the distance the optimizer can have moved them, and (c) the mean drift.
+                distances = [trajectory_distance(got, want, start, 1e-3, step) for got, want, start in zip(model.parameters(), ref, initial)]
+                table.append({"step": step, "tensors": distances})
+                report(f"classifier_training_engine{engine}", table)
+                for d in distances:
                     if engine == 1:
-                        assert drift.max() <= 1e-3 * 2e-2, (step, drift.max())
-                    assert drift.max() <= 2e-3 * step and drift.mean() <= (2e-6 if engine == 1 else 1e-4) * step, (step, drift.max(), drift.mean())
+                        assert d["max"] <= 2e-5 and d["mean"] <= 2e-6 * step, (step, d)
+                        assert d["relative_l2"] <= 2e-3 and d["share_apart"] == 0.0, (step, d)
+                    else:
+                        # measured: relative L2 up to 0.056, share apart up to 0.008 (unrelated trajectories: 1.4 and > 0.5)
+                        assert d["relative_l2"] <= 0.15 and d["share_apart"] <= 0.02 and d["mean"] <= 2e-5 * step, (step, d)
                 assert abs(device_loss - float(ref_loss)) <= (1e-4 if engine == 1 else 1e-3) * abs(float(ref_loss))
         assert model.optimizer_steps() == 20
         model.close()
@@ -263,7 +269,7 @@ def test_tanh_and_sigmoid_networks_match_the_checker(ctx, oracle, activation):
                 assert oracle.adam(ref[i], g.reshape(-1), m[i], v[i], step)
             for got, want in zip(model.parameters(), ref):
                 drift = np.abs(got.reshape(-1) - want)
-                assert drift.max() <= 2e-3 * step and drift.mean() <= 2e-6 * step, (step, drift.max(), drift.mean())
+                assert drift.max() <= 5e-5 and drift.mean() <= 2e-6 * step, (step, drift.max(), drift.mean())
         model.close()
     finally:
         ctx.set_option("gemm_engine", 0)

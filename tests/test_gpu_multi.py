@@ -33,6 +33,11 @@ rng = np.random.default_rng(5)
 x = rng.uniform(0, 1, (batch, dims[0])).astype(np.float32)
 labels = rng.integers(0, 10, batch)
 rows = batch // world
+# before any step: the all-reduced gradients of the ranks' slices are the gradient of the whole batch
+_, first_gradients = model.gradients(x[rank * rows:(rank + 1) * rows], labels[rank * rows:(rank + 1) * rows])
+if rank == 0:
+    np.save(os.environ["SYN_OUT"] + f".w{world}.start.npy", np.concatenate([p.reshape(-1) for p in model.parameters()]))
+    np.save(os.environ["SYN_OUT"] + f".w{world}.grads.npy", np.concatenate([g.reshape(-1) for g in first_gradients]))
 losses, history, same = [], [], True
 for step in range(20):
     losses.append(model.train(x[rank * rows:(rank + 1) * rows], labels[rank * rows:(rank + 1) * rows]))
@@ -70,17 +75,26 @@ def test_ranks_match_one_rank_after_every_step(tmp_path):
         pytest.skip("needs two GPUs")
     out = str(tmp_path / "dp")
     _run(1, out, 29731)
+    from helpers import report, trajectory_distance
     one = np.load(out + ".w1.npy")                      # [steps, parameters]
+    start = np.load(out + ".w1.start.npy")
     info1 = json.load(open(out + ".w1.json"))
     for world in [w for w in (2, 4, 8) if w <= available]:
         _run(world, out, 29731 + 2 * world)
         many = np.load(out + f".w{world}.npy")
         info = json.load(open(out + f".w{world}.json"))
         assert info["replicas_identical"], world
-        # Adam turns gradient rounding differences near zero into fractions of lr: bound the drift per
-        # entry by 2 * lr * (steps so far) and on average by 2 % of lr per step (the trajectories of two
-        # summation orders drift apart slowly; measured on 4 ranks: 5e-5 after 17 steps), after every step
+        # step 0: a wrong reduction (scale, a missing bucket, a stale buffer) shows at once in the gradients,
+        # which must agree with the single-rank gradient of the whole batch to GEMM rounding
+        g1, gn = np.load(out + ".w1.grads.npy").astype(np.float64), np.load(out + f".w{world}.grads.npy").astype(np.float64)
+        assert np.linalg.norm(g1 - gn) <= 2e-5 * np.linalg.norm(g1), (world, np.linalg.norm(g1 - gn) / np.linalg.norm(g1))
+        # then every step: two summation orders drift apart slowly (Adam turns gradient rounding near zero
+        # into fractions of lr); bounded as whole trajectories, since 2 * lr * step per entry would hold
+        # for any two runs
+        table = []
         for step in range(one.shape[0]):
-            drift = np.abs(one[step] - many[step])
-            assert drift.max() <= 2e-3 * (step + 1) and drift.mean() <= 2e-5 * (step + 1), (world, step, drift.max(), drift.mean())
+            d = trajectory_distance(many[step], one[step], start, 1e-3, step + 1)
+            table.append(d)
+            assert d["relative_l2"] <= 0.02 and d["share_apart"] <= 2e-3 and d["mean"] <= 2e-5 * (step + 1) and d["max"] <= 1.5e-3, (world, step, d)
+        report(f"data_parallel_world{world}", table)
         assert np.allclose(info1["losses"], info["losses"], rtol=2e-4), world

@@ -19,6 +19,7 @@ import pytest
 from synaptik_b200 import native, program
 from synaptik_b200.program import BOOL, F32, I32, I64, GraphBuilder
 
+import golden_cases
 from helpers import run_image, ulp_distance
 
 pytestmark = pytest.mark.gpu
@@ -1169,3 +1170,139 @@ def test_narrow_head_kernels(ctx, oracle):
     assert np.array_equal(out, (acti.astype(np.int64) @ wi.T.astype(np.int64)).astype(np.float32))
     assert np.array_equal(dxg, (dzi.astype(np.int64) @ wi.astype(np.int64)).astype(np.float32) * (gate > 0))
     assert np.array_equal(dwg, (dzi.T.astype(np.int64) @ acti.astype(np.int64)).astype(np.float32))
+
+
+# ---- the reference-held vectors of the gradient rules, on the device ------------------------------
+class DeviceBackend:
+    """The device behind the interface of golden_cases: every call is one program through the C ABI."""
+
+    def __init__(self, ctx):
+        self.ctx = ctx
+
+    def softmax(self, x, log):
+        g = GraphBuilder()
+        v = g.feed(F32, x.shape)
+        g.publish(g.log_softmax(v, 1) if log else g.softmax(v, 1))
+        return run_image(self.ctx, g, [x])[0]
+
+    def softmax_backward(self, y, upstream, log):
+        g = GraphBuilder()
+        yv, gv = g.feed(F32, y.shape), g.feed(F32, y.shape)
+        g.publish(g.log_softmax_backward(yv, gv, 1) if log else g.softmax_backward(yv, gv, 1))
+        return run_image(self.ctx, g, [y, upstream])[0]
+
+    def softmax_with_backward(self, x, upstream, log):
+        g = GraphBuilder()
+        xv, gv = g.feed(F32, x.shape), g.feed(F32, x.shape)
+        y = g.log_softmax(xv, 1) if log else g.softmax(xv, 1)
+        g.publish(y)
+        g.publish(g.log_softmax_backward(y, gv, 1) if log else g.softmax_backward(y, gv, 1))
+        saved, dx = run_image(self.ctx, g, [x, upstream])
+        return saved, dx
+
+    @staticmethod
+    def _label_type(dtype):
+        return I32 if np.dtype(dtype) == np.int32 else I64
+
+    def index_ce(self, logits, labels, reduction, ignore, label_dtype):
+        g = GraphBuilder()
+        lv, tv = g.feed(F32, logits.shape), g.feed(self._label_type(label_dtype), (logits.shape[0],))
+        g.publish(g.index_cross_entropy(lv, tv, reduction, ignore))
+        return run_image(self.ctx, g, [logits, np.asarray(labels, dtype=label_dtype)])[0]
+
+    def index_ce_backward(self, logits, labels, seed, reduction, ignore, label_dtype):
+        g = GraphBuilder()
+        rows = logits.shape[0]
+        lv, tv = g.feed(F32, logits.shape), g.feed(self._label_type(label_dtype), (rows,))
+        sv = g.feed(F32, (rows,) if reduction == "none" else ())
+        g.publish(g.index_cross_entropy_backward(lv, tv, sv, reduction, ignore))
+        return run_image(self.ctx, g, [logits, np.asarray(labels, dtype=label_dtype), np.asarray(seed, dtype=np.float32)])[0]
+
+    def dense_ce(self, logits, target, reduction):
+        g = GraphBuilder()
+        lv, tv = g.feed(F32, logits.shape), g.feed(F32, logits.shape)
+        g.publish(g.dense_cross_entropy(lv, tv, reduction))
+        return run_image(self.ctx, g, [logits, target])[0]
+
+    def dense_ce_backward(self, logits, target, seed, reduction):
+        g = GraphBuilder()
+        rows = logits.shape[0]
+        lv, tv = g.feed(F32, logits.shape), g.feed(F32, logits.shape)
+        sv = g.feed(F32, (rows,) if reduction == "none" else ())
+        g.publish(g.dense_cross_entropy_backward(lv, tv, sv, reduction))
+        return run_image(self.ctx, g, [logits, target, np.asarray(seed, dtype=np.float32)])[0]
+
+    def unary(self, name, x):
+        g = GraphBuilder()
+        v = g.feed(F32, x.shape)
+        g.publish(g.erf(v) if name == "erf" else g.gelu(v))
+        return run_image(self.ctx, g, [x])[0]
+
+
+@pytest.mark.parametrize("check", golden_cases.ALL_CHECKS, ids=lambda f: f.__name__)
+def test_reference_held_gradient_rule_vectors_on_the_device(ctx, check):
+    # the same expectations the CPU checker is held to (tests/golden_cases.py): raw-bit equality wherever
+    # the reference's own tests ask for it
+    check(DeviceBackend(ctx))
+
+
+# ---- activations other than ReLU in the GEMM epilogue ---------------------------------------------
+@pytest.mark.parametrize("engine,m,k,n", [(2, 512, 256, 384), (2, 128, 96, 64), (2, 100, 70, 130), (1, 70, 33, 45)])
+@pytest.mark.parametrize("activation", ["tanh", "sigmoid", "silu", "gelu_tanh", "gelu"])
+def test_activation_epilogues_give_the_bits_of_the_separate_pass(ctx, oracle, activation, engine, m, k, n):
+    # Y = act(X W^T + b) with the activation fused into the product (two-SM, one-SM and exact kernels):
+    # (a) with the pre-activation published beside it, the activation is bit for bit what the element-wise
+    # kernel makes of that pre-activation, and within the activation's own bound of the checker's value;
+    # (b) without the pre-activation the product writes the same activation.
+    rng = np.random.default_rng(m + k)
+    x = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    w = rng.uniform(-0.3, 0.3, (n, k)).astype(np.float32)
+    b = rng.uniform(-0.5, 0.5, n).astype(np.float32)
+    x[0, :4] = [np.inf, 1.0, 1.0, 1.0]                         # a row of non-finite pre-activations on the exact engine
+    both = GraphBuilder()
+    xv, wv, bv = both.feed(F32, (m, k)), both.feed(F32, (n, k)), both.feed(F32, (n,))
+    _, z = both.linear(xv, wv, bv)
+    both.publish(z)
+    both.publish(both.activation(activation, z))
+    assert f"act={ {'tanh': 'TANH', 'sigmoid': 'SIGMOID', 'silu': 'SILU', 'gelu_tanh': 'GELU_TANH_APPROXIMATION', 'gelu': 'GELU'}[activation]}" in native.describe(both.build())
+    z_dev, y_dev = run_image(ctx, both, [x, w, b], engine=engine)
+    alone = GraphBuilder()
+    zv = alone.feed(F32, (m, n))
+    alone.publish(alone.activation(activation, zv))
+    (y_pass,) = run_image(ctx, alone, [z_dev])
+    assert np.array_equal(y_dev.view(np.uint32), y_pass.view(np.uint32))
+    want = {"tanh": oracle.tanh, "sigmoid": oracle.sigmoid, "silu": oracle.silu, "gelu_tanh": oracle.gelu_tanh, "gelu": oracle.gelu}[activation](z_dev)
+    finite = np.isfinite(want)
+    assert np.array_equal(np.isnan(y_dev), np.isnan(want))
+    assert ulp_distance(y_dev[finite], want[finite]).max() <= 1 or np.abs(y_dev[finite] - want[finite]).max() <= 2 ** -52 * np.abs(z_dev[finite]).max() + 1e-45
+    only = GraphBuilder()
+    xv, wv, bv = only.feed(F32, (m, k)), only.feed(F32, (n, k)), only.feed(F32, (n,))
+    _, z = only.linear(xv, wv, bv)
+    only.publish(only.activation(activation, z))
+    (y_only,) = run_image(ctx, only, [x, w, b], engine=engine)
+    assert np.array_equal(y_only.view(np.uint32), y_dev.view(np.uint32))
+
+
+@pytest.mark.parametrize("activation", ["tanh", "gelu"])
+def test_tanh_and_gelu_networks_on_the_tensor_cores_follow_the_checker(ctx, oracle, activation):
+    from synaptik_b200 import nn
+    dims, batch = [256, 512, 384, 10], 512
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((batch, dims[0])).astype(np.float32)
+    labels = rng.integers(0, 10, batch)
+    ctx.set_option("gemm_engine", 2)
+    try:
+        model = nn.Model(dims, ctx, seed=21, activation=activation)
+        model.configure_training("ce", nn.Adam(1e-3))
+        params = model.parameters()
+        logits = model.compute(x)
+        want = oracle.mlp_forward(x, params[0::2], params[1::2], activation)[-1]
+        assert np.abs(logits - want).max() <= 2e-5 * np.abs(want).max()
+        loss, grads = model.gradients(x, labels)
+        ref_loss, ref_grads, _ = oracle.mlp_gradients(x, labels, params[0::2], params[1::2], "ce", activation=activation)
+        assert abs(loss - float(ref_loss)) <= 1e-5 * abs(float(ref_loss))
+        for got, ref in zip(grads, ref_grads):          # smooth activations: no gates to flip, so element-wise
+            assert np.abs(got - ref).max() <= 5e-5 * np.abs(ref).max() + 1e-12
+        model.close()
+    finally:
+        ctx.set_option("gemm_engine", 0)

@@ -4,6 +4,9 @@ import math
 import os
 
 import numpy as np
+import pytest
+
+import golden_cases
 
 GOLDEN = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_known_answers.json")))
 
@@ -423,3 +426,47 @@ def test_squared_error_reductions(oracle):
     assert list(oracle.squared_error(p, t, "none")) == [1.0, 4.0, 9.0, 2.0 ** -24]
     assert oracle.squared_error(p, t, "sum") == np.float32(14.0)            # 14 + 2^-24 rounds back to 14
     assert oracle.mse(p, t) == np.float32(3.5)
+
+
+class CheckerBackend:
+    """The CPU checker behind the interface of golden_cases."""
+
+    def __init__(self, oracle):
+        self.o = oracle
+
+    def softmax(self, x, log):
+        return self.o.log_softmax(x) if log else self.o.softmax(x)
+
+    def softmax_backward(self, y, g, log):
+        with np.errstate(all="ignore"):
+            return self.o.softmax_backward(y, g, log)
+
+    def softmax_with_backward(self, x, g, log):
+        y = self.softmax(x, log)
+        return y, self.softmax_backward(y, g, log)
+
+    def index_ce(self, logits, labels, reduction, ignore, label_dtype):
+        ignore = -(2 ** 40) if ignore is None else ignore           # a value no label takes
+        per_row, reduced = self.o.index_cross_entropy_ignore(logits, labels, ignore, reduction)
+        return per_row if reduction == "none" else reduced
+
+    def index_ce_backward(self, logits, labels, seed, reduction, ignore, label_dtype):
+        ignore = -(2 ** 40) if ignore is None else ignore
+        with np.errstate(all="ignore"):
+            return self.o.index_cross_entropy_ignore_backward(logits, labels, ignore, seed, reduction)
+
+    def dense_ce(self, logits, target, reduction):
+        per_row, reduced = self.o.dense_cross_entropy(logits, target, reduction)
+        return per_row if reduction == "none" else reduced
+
+    def dense_ce_backward(self, logits, target, seed, reduction):
+        with np.errstate(all="ignore"):
+            return self.o.dense_cross_entropy_backward(logits, target, seed, reduction)
+
+    def unary(self, name, x):
+        return {"erf": self.o.erf, "gelu": self.o.gelu}[name](x)
+
+
+@pytest.mark.parametrize("check", golden_cases.ALL_CHECKS, ids=lambda f: f.__name__)
+def test_reference_held_gradient_rule_vectors(oracle, check):
+    check(CheckerBackend(oracle))
