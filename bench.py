@@ -43,11 +43,21 @@ METRIC = "mlp_train_samples_per_s"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 DATA_BLOCK = 1024       # rows per independently seeded block of the synthetic batch
 
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch of the two-SM 3xTF32 kernel, from
-# an ncu capture of the forward product [8192 x 4096] . [4096 x 4096]^T of this build (`--case gemm
-# --m 8192 --forward-only`).  A 65536-row launch re-reads the weight planes once per group of row bands
-# from L2, so its traffic is the activation-plane and result terms times eight plus the weight term once.
-NCU_TRAFFIC_8192 = {"total": 1.43e9, "weight_term": 2 * 2 * 4096 * 4128 * 4.0, "algorithmic": 4.0 * (8192 * 4096 + 4096 * 4096 + 4096 + 8192 * 4096)}
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch of the two-SM 3xTF32 kernel, mean over
+# the eight launches of one training step, from two ncu captures of exactly these launches: at 8192 rows per
+# GPU (this build) and at 65536 rows (the same main loop and tile order).  The weight planes are read once per
+# group of row bands whatever the batch, so traffic does not grow in proportion to the rows; other row counts
+# are interpolated between the two captures.
+NCU_GEMM_TRAFFIC = {8192: 8.955e9 / 8, 65536: (62.5e9 + 6.9e9) / 8}
+# FP32 operands read once and results written once, per launch (mean over the same eight launches)
+ALGORITHMIC_GEMM_BYTES = {8192: 2.628e9 / 8, 65536: 28.7e9 / 8}
+TENSOR_FLOP_PER_CLOCK_PER_SM = 4096.0       # dense TF32 multiply-add throughput of one SM's tensor pipe (2048 FMA per clock)
+SM_COUNT = 148
+
+
+def interpolate_rows(table, rows):
+    (r0, v0), (r1, v1) = sorted(table.items())
+    return v0 + (rows - r0) * (v1 - v0) / (r1 - r0)
 
 
 def step_flops(batch: int) -> float:
@@ -399,26 +409,24 @@ def run_cuda(args):
         emulated_peak = peak_data["bf16_tflops_sustained"] / 2.0 / 3.0       # TF32 dense = BF16 / 2; three MMAs per FP32 product
         achieved = flops / (ms * 1e-3) / 1e12 if ms > 0 else 0.0
         total_step = sum(step_ms) or 1.0
-        # DRAM traffic of one launch from the 8192-row capture: terms that grow with the rows scaled by rows / 8192
-        scale = rows / 8192.0
-        traffic = (NCU_TRAFFIC_8192["total"] - NCU_TRAFFIC_8192["weight_term"]) * scale + NCU_TRAFFIC_8192["weight_term"]
+        traffic = interpolate_rows(NCU_GEMM_TRAFFIC, rows)
         roofline = {"bound": "tensor", "kernel": "gemm_tf32x3_pair_kernel", "achieved": achieved, "peak": emulated_peak, "unit": "TFLOP/s",
                     "frac": achieved / emulated_peak if emulated_peak else None,
                     "peak_source": f"{peak_kind} cuBLAS BF16 sustained / 2 (TF32) / 3 (three MMAs per FP32 product)",
                     "traffic": traffic,
-                    "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one 8192 x 4096 x 4096 launch of this kernel; "
-                                      "the operand-plane and result terms scaled to this run's rows, the weight-plane term counted once",
-                    "algorithmic_bytes_per_launch": 4.0 * (2 * rows * 4096 + 4096 * 4096 + 4096),
+                    "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, mean over the step's eight launches of this kernel, "
+                                      "captured at 8192 and at 65536 rows per GPU and interpolated to this run's rows",
+                    "algorithmic_bytes_per_launch": interpolate_rows(ALGORITHMIC_GEMM_BYTES, rows),
                     "launches_per_step": gemm_launches, "ms_per_step_in_kernel": ms,
                     "kilocycles_in_kernel": at_equal_clock(ms, clocks),
                     "step_time_shares": {k: v / total_step for k, v in sorted(shares.items())},
                     "steps_ms": [[text.split(" nodes=")[0], round(t, 4)] for text, t in zip(plan, step_ms)]}
         if clocks and clocks.get("sm_mhz"):
-            # the tensor pipe's own ceiling at the clock this run held: NVIDIA's dense TF32 figure (1125 TFLOP/s at
-            # the 1965 MHz boost clock) scaled to the sampled clock, three MMAs per FP32 product
-            nominal = 1125.0 * clocks["sm_mhz"] / 1965.0 / 3.0
-            roofline["peak_nominal_at_sampled_clock"] = nominal
-            roofline["frac_of_nominal_at_sampled_clock"] = achieved / nominal
+            # the tensor pipe's own ceiling at the clock this run held: 148 SMs x 4096 dense TF32 FLOP per clock,
+            # three MMAs per FP32 product (ncu: the pipe is active 96 % of the cycles of a 4096-deep product)
+            ceiling = SM_COUNT * TENSOR_FLOP_PER_CLOCK_PER_SM * clocks["sm_mhz"] * 1e6 / 3.0 / 1e12
+            roofline["peak_tensor_pipe_at_sampled_clock"] = ceiling
+            roofline["frac_of_tensor_pipe_at_sampled_clock"] = achieved / ceiling
         if tf32:
             direct = tf32["sustained_tflops"] / 3.0
             roofline["peak_tf32_measured"] = direct

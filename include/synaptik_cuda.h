@@ -69,7 +69,10 @@ SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_release(void *context);
  * epilogue (default 1; only used while "gemm_promote" is 0).  "gemm_promote": 1 (default) = the
  * tensor-core GEMM keeps only short partial sums (256 or 512 contraction steps) in tensor memory and
  * adds them into round-to-nearest FP32 register sums; 0 = one tensor-memory accumulator over the
- * whole contraction (faster epilogue, error grows with K).  "gemm_pair": 1 (default) = products with
+ * whole contraction (faster epilogue, error grows with K).  "gemm_chunk": contraction steps per
+ * tensor-memory partial sum of executables created afterwards, a multiple of 32, 0 (default) = 512 (256
+ * from K = 8192 on); shorter partial sums are more exact and slower (128: a quarter of the error, about
+ * 10 % more time on the 4096-wide layers).  "gemm_pair": 1 (default) = products with
  * at least 256 rows use two-SM tiles (clusters of two blocks, tcgen05 cta_group::2); 0 = one-SM tiles
  * only.  "gemm_slices": 1 (default) = a two-SM product without epilogue work (a weight gradient) may
  * split its contraction into up to four slices when that shortens the last wave of the persistent

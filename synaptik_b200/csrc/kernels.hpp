@@ -163,7 +163,8 @@ struct TensorCoreGemm;       // opaque: tensor maps and launch geometry prepared
 // mode: bit 0 = FP32 promotion of partial sums, bit 1 = two-SM tiles where the shape fills them,
 // bit 2 = the launch will have no epilogue work (bias, gate, activation, second output, planes), so the
 // contraction may be split into slices whose partial products are added by a second kernel; such a
-// GEMM needs tc_gemm_workspace_floats(g) floats of scratch at launch.
+// GEMM needs tc_gemm_workspace_floats(g) floats of scratch at launch.  Bits 8-15: k-blocks (of 32 contraction
+// steps) per tensor-memory partial sum of the promoted kernels, 0 = the default (16, or 8 from K = 8192 on).
 TensorCoreGemm *tc_gemm_prepare(const TcOperand &p, const TcOperand &q, int64_t m, int64_t n, int64_t k,
                                 int sm_count, int mode, int *status);
 void tc_gemm_release(TensorCoreGemm *g);

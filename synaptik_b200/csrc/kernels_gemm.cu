@@ -1143,6 +1143,7 @@ TensorCoreGemm *tc_gemm_prepare(const TcOperand &p, const TcOperand &q, int64_t 
                                 int sm_count, int promote, int *status) {
     const int pair_requested = (promote >> 1) & 1;      // bit 1 of the mode: two-SM tiles
     const int may_slice = (promote >> 2) & 1;           // bit 2: the result has no epilogue, the contraction may be split
+    const int chunk_requested = (promote >> 8) & 0xff;  // bits 8-15: k-blocks per tensor-memory partial sum, 0 = default
     promote &= 1;
     *status = OK;
     if (m < 1 || n < 1 || k < 1 || m > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30)) { *status = UNSUPPORTED_SHAPE; return nullptr; }
@@ -1157,6 +1158,7 @@ TensorCoreGemm *tc_gemm_prepare(const TcOperand &p, const TcOperand &q, int64_t 
     // tile end unless the tile's main loop is very long (the weight gradients, K = batch).  Measured on
     // the 65536 x 4096 x 4096 layers: partials of 128 contraction steps cost 17 % of the step, 512 nothing.
     g->chunk_kb = (g->k_blocks * BK >= 8192 ? 256 : 512) / BK;
+    if (chunk_requested > 0) g->chunk_kb = chunk_requested;
     if (forced_chunk_kb() > 0) g->chunk_kb = forced_chunk_kb();
     // tile width: the widest tile has the best operand reuse, but a persistent grid pays for the last
     // partial wave; take the width with the least (waves x width), narrower tiles handicapped a little

@@ -675,6 +675,20 @@ __global__ void colsum_final_kernel(const double *__restrict__ partials, int64_t
     out[col] = (float)s;
 }
 
+// Phase 2 for narrow matrices (few columns, many row splits): one warp per column, lanes stride over the
+// splits and a fixed shuffle tree joins them, instead of one thread walking all the splits of a column
+// (1024 sequential additions for the 10-wide head at batch 65536: 0.11 ms for 80 KB of partials).
+__global__ void __launch_bounds__(256) colsum_final_narrow_kernel(const double *__restrict__ partials, int64_t splits, int64_t cols, float *out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t col = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (col >= cols) return;
+    double s = 0;
+    for (int64_t i = lane; i < splits; i += 32) s += partials[i * cols + col];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) out[col] = (float)s;
+}
+
 inline int64_t colsum_splits(int64_t rows, int64_t cols) {
     int64_t strips = (cols + 127) / 128;
     int64_t want = (148 * 8 + strips - 1) / strips;            // about eight blocks per SM in total
@@ -1459,7 +1473,8 @@ cudaError_t colsum(cudaStream_t s, const float *g, int64_t rows, int64_t cols, d
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    colsum_final_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, s>>>(partials, splits, cols, out);
+    if (cols < 128 && splits >= 64) colsum_final_narrow_kernel<<<(unsigned)((cols + 7) / 8), 256, 0, s>>>(partials, splits, cols, out);
+    else colsum_final_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, s>>>(partials, splits, cols, out);
     return cudaGetLastError();
 }
 

@@ -35,14 +35,6 @@ __global__ void __launch_bounds__(512, 1) narrow_out_kernel(int64_t m, int k, co
         const float *rows[4];
 #pragma unroll
         for (int r = 0; r < 4; r++) rows[r] = a + (r0 + r < m ? r0 + r : m - 1) * lda;
-        // the four rows this warp takes next, asked into L2 now (one 128-byte line per lane and step), so
-        // that their loads wait for L2 instead of HBM
-        if (r0 + warps * 4 + 3 < m) {
-#pragma unroll
-            for (int r = 0; r < 4; r++)
-                for (int kk = lane * 32; kk < k; kk += 32 * 32)
-                    asm volatile("prefetch.global.L2 [%0];" :: "l"(a + (r0 + warps * 4 + r) * lda + kk));
-        }
 #pragma unroll 2
         for (int kk = lane * 4; kk < k; kk += 128) {
             float4 x[4];
@@ -99,14 +91,6 @@ __global__ void __launch_bounds__(256) narrow_inner_kernel(int64_t m, int64_t n,
     for (int64_t r = first; r < m; r += step * ROWS) {
         float sv[ROWS][K];
         float4 g[ROWS];
-        // the gate lines of the next trip, asked into L2 now (one lane per 128-byte line)
-        if (gate && (lane & 7) == 0) {
-#pragma unroll
-            for (int q = 0; q < ROWS; q++) {
-                const int64_t rr = r + (ROWS + q) * step;
-                if (rr < m) asm volatile("prefetch.global.L2 [%0];" :: "l"(gate + rr * n + col));
-            }
-        }
 #pragma unroll
         for (int q = 0; q < ROWS; q++) {
             const int64_t rr = r + q * step;
@@ -171,16 +155,7 @@ __global__ void __launch_bounds__(256) narrow_reduce_partial_kernel(int64_t wide
         }
         __syncthreads();
         if (live) {
-            // this warp's strip of the next chunk, asked into L2 now: lane l takes rows l, l + 32, ... and
-            // the four 128-byte lines of each
-            if (c0 + kReduceChunk < r1) {
-                for (int rr = lane; rr < kReduceChunk && c0 + kReduceChunk + rr < r1; rr += 32) {
-                    const float *line = s + (c0 + kReduceChunk + rr) * lds + (int64_t)strip * 128;
-#pragma unroll
-                    for (int q = 0; q < 4; q++) asm volatile("prefetch.global.L2 [%0];" :: "l"(line + q * 32));
-                }
-            }
-#pragma unroll 8
+#pragma unroll 4
             for (int rr = 0; rr < rows_here; rr++) {
                 const float4 sv = *reinterpret_cast<const float4 *>(s + (c0 + rr) * lds + col);
 #pragma unroll
@@ -283,7 +258,7 @@ bool narrow_reduce_supported(int64_t wide, int64_t n, int64_t depth, int64_t lds
 
 static int64_t narrow_reduce_slices(int64_t wide, int64_t depth) {
     int64_t strips = (wide + 127) / 128;
-    int64_t slices = 2 * kNarrowWarps / strips;        // four blocks of eight warps per SM: at two the loads in flight did not cover the HBM latency
+    int64_t slices = kNarrowWarps / strips;
     int64_t most = (depth + 63) / 64;
     if (slices > most) slices = most;
     return slices < 1 ? 1 : slices;

@@ -95,6 +95,8 @@ def test_ranks_match_one_rank_after_every_step(tmp_path):
         for step in range(one.shape[0]):
             d = trajectory_distance(many[step], one[step], start, 1e-3, step + 1)
             table.append(d)
-            assert d["relative_l2"] <= 0.02 and d["share_apart"] <= 2e-3 and d["mean"] <= 2e-5 * (step + 1) and d["max"] <= 1.5e-3, (world, step, d)
+            # measured on 2 ranks: identical to 5e-8 after 20 steps (the ranks' forward passes are the single rank's
+            # bit for bit; only the sums over the batch are split)
+            assert d["relative_l2"] <= 0.01 and d["share_apart"] <= 1e-3 and d["mean"] <= 2e-6 * (step + 1) and d["max"] <= 1e-3, (world, step, d)
         report(f"data_parallel_world{world}", table)
         assert np.allclose(info1["losses"], info["losses"], rtol=2e-4), world
