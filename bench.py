@@ -554,7 +554,7 @@ def measure_inference(ctx, model, rank, world, local_rank, steps, barrier, reduc
             "arg_max_checksum": checksum, "clocks": clocks, "kilocycles_per_batch": at_equal_clock(resident_ms / steps, clocks)}
 
 
-def measure_kernel_case(ctx, device_index, case, m, k, n, forward_only=False, steps=10, warmup=3, blocks=31, warm_seconds=1.0):
+def measure_kernel_case(ctx, device_index, case, m, k, n, forward_only=False, steps=10, warmup=3, blocks=31, warm_seconds=1.0, dtype="f32"):
     """One kernel case through the C ABI on context `ctx`: the standalone fused dense layer (forward and
     backward) or a piece of the classifier head.  Times `steps` back-to-back launches between two CUDA
     events on the context's stream, then follows the reference's own protocol (warm-up of at least
@@ -565,7 +565,23 @@ def measure_kernel_case(ctx, device_index, case, m, k, n, forward_only=False, st
     rng = np.random.default_rng(3)
     g = GraphBuilder()
     peak_data, peak_kind = peaks()
-    if case == "gemm":
+    if case == "gemm" and dtype != "f32":
+        # the dense layer on 16-bit storage (BFLOAT16 / FLOAT16 values, FLOAT32 accumulation): forward only,
+        # operands read by TMA straight from the tensors, one tcgen05 kind::f16 MMA per 16 contraction steps
+        from synaptik_b200 import program
+        storage = program.STORAGE_DTYPES[dtype]
+        x, w, b = g.feed(storage, (m, k)), g.feed(storage, (n, k)), g.feed(storage, (n,))
+        _, z = g.linear(x, w, b)
+        g.publish(g.relu(z))
+        bound = np.sqrt(6.0 / (k + n))
+        feeds = [program.to_storage(dtype, rng.random((m, k), dtype=np.float32) * 2 - 1),
+                 program.to_storage(dtype, (rng.random((n, k), dtype=np.float32) * 2 - 1) * np.float32(bound)),
+                 program.to_storage(dtype, (rng.random(n, dtype=np.float32) * 2 - 1) * np.float32(0.1))]
+        forward_only = True
+        work = 2.0 * m * k * n
+        unit, denom, bound_kind = "TFLOP/s", peak_data["bf16_tflops"], "tensor"
+        name = f"dense_layer_fwd_{dtype}_m{m}_k{k}_n{n}"
+    elif case == "gemm":
         x, w, b, dy = g.feed(F32, (m, k)), g.feed(F32, (n, k)), g.feed(F32, (n,)), g.feed(F32, (m, n))
         wt, z = g.linear(x, w, b)
         g.publish(g.relu(z))
@@ -679,10 +695,12 @@ def measure_kernel_case(ctx, device_index, case, m, k, n, forward_only=False, st
     if case == "gemm":
         kernel, kernel_work, kernel_ms = "gemm_tf32x3_pair_kernel", 0.0, 0.0
         for text, t in zip(plan, step_times):
-            if "engine=tcgen05_3xtf32" in text:
+            if "engine=tcgen05_3xtf32" in text or "engine=tcgen05_f16" in text:
                 mm, nn_, kk = (int(re.search(rf" {d}=(\d+)", text).group(1)) for d in "mnk")
                 kernel_work += 2.0 * mm * nn_ * kk
                 kernel_ms += t
+        if dtype != "f32":
+            kernel = "gemm_low_kernel"
     else:
         kernel = {"ce": "ce_rows_vec_kernel", "argmax": "argmax_vec_kernel", "dense_ce": "dense_ce_rows_vec_kernel"}.get(case, "softmax_rows_vec_kernel")
         kernel_work, kernel_ms = work, median_ms
@@ -690,12 +708,12 @@ def measure_kernel_case(ctx, device_index, case, m, k, n, forward_only=False, st
     record = {"metric": f"{case}_{unit}", "value": work / (median_ms * 1e-3) / per_unit, "unit": unit, "n_gpus": 1, "steps": steps,
               "warmup": max(warmup, 3), "ms_per_step": ms / steps, "median_ms_per_step": median_ms,
               "protocol": protocol,
-              "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+              "higher_is_better": True, "dtype": dtype, "data": "synthetic",
               "config": {"workload": name, "l2": l2},
               "gpu_launches": exe.launch_count() * steps, "clocks": clocks, "kilocycles_per_step": at_equal_clock(median_ms, clocks),
               "roofline": {"bound": bound_kind, "kernel": kernel, "achieved": achieved, "peak": denom, "unit": unit, "frac": achieved / denom,
                            "ms_in_kernel": kernel_ms,
-                           "peak_source": peak_kind + (" cuBLAS BF16 burst / 2 / 3" if unit == "TFLOP/s" else " copy bandwidth"), "traffic": None},
+                           "peak_source": peak_kind + ((" cuBLAS BF16 burst" if dtype != "f32" else " cuBLAS BF16 burst / 2 / 3") if unit == "TFLOP/s" else " copy bandwidth"), "traffic": None},
               "steps_ms": {text.split(" nodes=")[0]: t for text, t in zip(plan, step_times)}}
     exe.close()
     if flush is not None:
@@ -717,6 +735,12 @@ def kernel_cases(ctx, device_index):
                             "kernel": r["roofline"]["kernel"], "in_kernel": r["roofline"]["achieved"], "ms_in_kernel": r["roofline"]["ms_in_kernel"],
                             "peak": r["roofline"]["peak"], "frac": r["roofline"]["frac"], "algorithmic_flop": 6.0 * m * kn * kn,
                             "clocks": r["clocks"], "kilocycles": r["kilocycles_per_step"]})
+    for low in ("bf16", "f16"):
+        r = measure_kernel_case(ctx, device_index, "gemm", 65536, 4096, 4096, steps=5, blocks=9, warm_seconds=0.3, dtype=low)
+        records.append({"workload": r["config"]["workload"], "unit": r["unit"], "whole_layer": r["value"], "median_ms": r["median_ms_per_step"],
+                        "kernel": r["roofline"]["kernel"], "in_kernel": r["roofline"]["achieved"], "ms_in_kernel": r["roofline"]["ms_in_kernel"],
+                        "peak": r["roofline"]["peak"], "frac": r["roofline"]["frac"], "algorithmic_flop": 2.0 * 65536 * 4096 * 4096,
+                        "clocks": r["clocks"], "kilocycles": r["kilocycles_per_step"]})
     for case in ("ce", "softmax", "argmax"):
         r = measure_kernel_case(ctx, device_index, case, 65536, 0, 1000, steps=20, blocks=9, warm_seconds=0.3)
         records.append({"workload": r["config"]["workload"], "unit": r["unit"], "value": r["value"], "median_ms": r["median_ms_per_step"],
@@ -732,9 +756,9 @@ def run_kernel_case(args):
         name, _, value = item.partition("=")
         ctx.set_option(name.strip(), int(value))
     if args.quick:
-        record = measure_kernel_case(ctx, 0, args.case, args.m, args.k, args.n, args.forward_only, args.steps, args.warmup, blocks=1, warm_seconds=0.0)
+        record = measure_kernel_case(ctx, 0, args.case, args.m, args.k, args.n, args.forward_only, args.steps, args.warmup, blocks=1, warm_seconds=0.0, dtype=args.dtype)
     else:
-        record = measure_kernel_case(ctx, 0, args.case, args.m, args.k, args.n, args.forward_only, args.steps, args.warmup)
+        record = measure_kernel_case(ctx, 0, args.case, args.m, args.k, args.n, args.forward_only, args.steps, args.warmup, dtype=args.dtype)
     print(json.dumps(record))
     ctx.close()
     return 0
@@ -747,6 +771,7 @@ def main():
     parser.add_argument("--k", type=int, default=4096)
     parser.add_argument("--n", type=int, default=4096)
     parser.add_argument("--forward-only", action="store_true")
+    parser.add_argument("--dtype", default="f32", choices=["f32", "bf16", "f16"], help="storage type of the dense-layer case (16-bit: forward only)")
     parser.add_argument("--quick", action="store_true", help="kernel cases: only the plain timed region (few launches: the workload of a profiler capture)")
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=10)

@@ -546,3 +546,94 @@ def baseline_mlp_step(dims, x, labels, weights, biases, m1, m2, train=True, coun
         ctypes.c_double(lr), ctypes.c_double(beta1), ctypes.c_double(beta2), ctypes.c_double(eps),
         ctypes.byref(loss), _p(logits) if logits is not None else None)
     return seconds, np.float32(loss.value), logits
+
+
+# --------------------------------------------------------------------------------------------
+# 16-bit storage (BFLOAT16 / FLOAT16) with a FLOAT32 working type
+# --------------------------------------------------------------------------------------------
+# The reference keeps low-precision tensors as raw 16-bit patterns, widens every operand to FLOAT32,
+# computes in FLOAT32 and narrows each NODE's result once, round to nearest even
+# (CpuScalarReferenceKernel.java:93-115 lowFloat / lowBits, BFloat16Bits.java:17-29, Float16Bits =
+# IEEE binary16).  Storage arrays here are uint16; `kind` is "bf16" or "f16".
+def low_encode(kind: str, x) -> np.ndarray:
+    """FLOAT32 -> storage bits.  BFLOAT16: NaN becomes 0x7FC0, otherwise round half to even on the
+    discarded 16 bits (BFloat16Bits.fromFloat); FLOAT16: IEEE conversion (Float.floatToFloat16)."""
+    x = _f32(x)
+    if kind == "f16":
+        with np.errstate(over="ignore"):
+            out = x.astype(np.float16).view(np.uint16).copy()
+        out[np.isnan(x)] = 0x7E00           # Float16Bits.CANONICAL_NAN
+        return out
+    bits = x.view(np.uint32)
+    upper = (bits >> 16).astype(np.uint32)
+    discarded = bits & np.uint32(0xFFFF)
+    up = (discarded > 0x8000) | ((discarded == 0x8000) & ((upper & 1) == 1))
+    upper = upper + up.astype(np.uint32)
+    out = (upper & 0xFFFF).astype(np.uint16)
+    out[np.isnan(x)] = 0x7FC0
+    return out
+
+
+def low_decode(kind: str, bits) -> np.ndarray:
+    bits = np.ascontiguousarray(bits, dtype=np.uint16)
+    if kind == "f16":
+        return bits.view(np.float16).astype(np.float32)
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+def low_round(kind: str, x) -> np.ndarray:
+    """A FLOAT32 working value as the storage type will hold it."""
+    return low_decode(kind, low_encode(kind, x))
+
+
+def low_activation(name: str, x) -> np.ndarray:
+    """FLOAT32 working result of an activation on exactly decoded low inputs, before the one narrowing.
+    SIGMOID, SILU and both GELUs are FLOAT32 composites (CpuScalarReferenceKernel.lowActivation, :1753-1775:
+    every product, sum and quotient a binary32 rounding, the elementary function in binary64 and narrowed
+    at once; -inf gives -0 except for SIGMOID); RELU and TANH take the binary64 function of the widened
+    value and one narrowing (:1722-1742)."""
+    x = _f32(x)
+    one, half = np.float32(1.0), np.float32(0.5)
+    with np.errstate(all="ignore"):
+        if name == "relu":
+            return relu(x)
+        if name == "tanh":
+            return tanh(x)
+        if name in ("sigmoid", "silu"):
+            e = np.exp(np.where(x >= 0, -x, x).astype(np.float64)).astype(np.float32)
+            if name == "sigmoid":
+                return (np.where(x >= 0, one, e) / (one + e)).astype(np.float32)
+            y = (np.where(x >= 0, x, (x * e).astype(np.float32)) / (one + e)).astype(np.float32)
+        elif name == "gelu":
+            root = np.float32(np.sqrt(np.float64(np.float32(2.0))))
+            inner = erf((x / root).astype(np.float32))
+            y = ((half * x).astype(np.float32) * (one + inner).astype(np.float32)).astype(np.float32)
+        elif name == "gelu_tanh":
+            cube = ((x * x).astype(np.float32) * x).astype(np.float32)
+            scale = np.float32(np.sqrt(np.float64(np.float32(2.0) / np.float32(np.pi))))
+            argument = (scale * (x + (np.float32(0.044715) * cube).astype(np.float32)).astype(np.float32)).astype(np.float32)
+            inner = np.tanh(argument.astype(np.float64)).astype(np.float32)
+            y = ((half * x).astype(np.float32) * (one + inner).astype(np.float32)).astype(np.float32)
+        else:
+            raise ValueError(name)
+        return np.where(np.isneginf(x), np.float32(-0.0), y).astype(np.float32)
+
+
+def low_linear(kind: str, x_bits, w_bits, bias_bits, activation: str | None):
+    """Tensor.linear on 16-bit storage, node by node: MATMUL as the sequential FLOAT32 chain over the
+    widened operands with one narrowing of the sum (CpuMatmulReferenceKernel.java:71-93), ADD of the
+    row-broadcast bias in FLOAT32 with one narrowing, then the activation with one narrowing.
+    Returns the storage bits of (z, y)."""
+    u = low_round(kind, matmul(low_decode(kind, x_bits), low_decode(kind, w_bits).T))
+    z = low_round(kind, (u + low_decode(kind, bias_bits)[None, :]).astype(np.float32)) if bias_bits is not None else u
+    y = low_round(kind, low_activation(activation, z)) if activation else z
+    return low_encode(kind, z), low_encode(kind, y)
+
+
+def low_mlp_forward(kind: str, x_bits, weights_bits, biases_bits, activation: str = "relu"):
+    """Model.compute on 16-bit storage: the storage bits of the last layer's output."""
+    a = x_bits
+    for index, (w, b) in enumerate(zip(weights_bits, biases_bits)):
+        z, y = low_linear(kind, a, w, b, activation if index + 1 < len(weights_bits) else None)
+        a = y
+    return a

@@ -14,9 +14,12 @@
  * integer MATMUL results, softmax and log-softmax documented values, the dense-target and index
  * cross-entropy answers of the Metal native test, erf special values, the scalar SGD training trace,
  * the Adam multiply-before-divide overflow case and the double-precision Adam oracle of its unit
- * test.  Parity unpinned (no FLOAT32 known answers in the reference's tests; pinned by special
- * values, by the definition restated here, and for gradient rules by central differences): TANH,
- * SIGMOID, SILU, tanh GELU, rows under an ignore index, the gradient node lists of the loss forms.
+ * test; and, for the gradient rules, the vectors of the reference's softmax-backward conformance and
+ * integration tests (the FLOAT32 recipe with its exactly rounded row sum, non-finite rows, tied
+ * extremes, cross-entropy rows at the finite extremes, with infinities, without target mass and under
+ * an ignore index), its ERF / GELU extremes and its finite softmax cases.  Parity unpinned (no FLOAT32
+ * known answers in the reference's tests; pinned by special values and by the definition restated
+ * here): TANH, SIGMOID, SILU, tanh GELU.
  * For arbitrary real-valued GEMM operands the reference's OpenBLAS route is itself unpinned
  * (any OpenBLAS version), so parity there is a stated tolerance, not bit equality.
  */

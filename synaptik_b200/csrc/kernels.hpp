@@ -175,5 +175,25 @@ int tc_gemm_launches(const TensorCoreGemm *g);
 cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, int64_t ldd, const GemmEpilogue &ep, float *workspace,
                            int *unit_counter, int *error_word);
 
+// ---- 16-bit storage (BFLOAT16 = kind 1, FLOAT16 = kind 2), FLOAT32 working type ---------------------
+// Every node narrows its result once (round to nearest even); a fused MATMUL -> ADD(bias) -> activation
+// narrows after each of the three, as the separate nodes would.  Buffers hold raw 16-bit patterns.
+// Exact product: the reference's ascending-k FLOAT32 chain over the widened operands, any strides.
+cudaError_t gemm_exact_low(cudaStream_t s, int kind, int64_t m, int64_t n, int64_t k, const void *a, int64_t a_ms, int64_t a_ks,
+                           const void *b, int64_t b_ks, int64_t b_ns, void *c, int64_t c_ms, int64_t c_ns,
+                           const void *bias, int act, void *second);
+// Tensor-core product C[m, n] = A[m, k] . W[n, k]^T on K-major operands (rows lda / ldw elements apart,
+// multiples of 8; 16-byte aligned bases), result rows ldc apart; bias [n], activation wire code, optional
+// second output as for the FP32 epilogue.  chunk_steps: contraction steps per tensor-memory partial sum
+// (0 = default).  The tensor maps are encoded from the pointers on every launch.
+bool low_gemm_supported(int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldw, int64_t ldc);
+cudaError_t low_gemm_launch(cudaStream_t s, int kind, int sm_count, int64_t m, int64_t n, int64_t k, const void *a, int64_t lda,
+                            const void *w, int64_t ldw, void *c, int64_t ldc, const void *bias, int act, void *second,
+                            int chunk_steps, int *error_word);
+// Element-wise nodes and the row arg-max on 16-bit storage.
+cudaError_t binary_low(cudaStream_t s, int kind, Op op, const void *a, const void *b, void *out, const Index4 &ix, int64_t total);
+cudaError_t unary_low(cudaStream_t s, int kind, Op op, const void *a, void *out, int64_t total);
+cudaError_t argmax_rows_low(cudaStream_t s, int kind, const void *x, int64_t *out, int64_t rows, int64_t cols);
+
 }  // namespace kern
 }  // namespace syn

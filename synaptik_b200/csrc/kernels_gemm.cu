@@ -11,6 +11,7 @@
 //    below 2^-22 of each product.
 #include "kernels.hpp"
 #include "activation.cuh"
+#include "lowp.cuh"
 #include "split.cuh"
 
 #include <cuda.h>
@@ -1080,6 +1081,337 @@ bool make_plane_map_mn(CUtensorMap *map, const float *plane, int64_t k, int64_t 
               CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// 16-bit storage (BFLOAT16 / FLOAT16) with a FLOAT32 working type.
+//
+//  * gemm_exact_low_kernel: the exact CUDA-core product on 16-bit operands: every cell is the reference's
+//    ascending-k FLOAT32 chain over the widened operands and one narrowing of the sum
+//    (CpuMatmulReferenceKernel.java:71-93), then ADD of the bias and the activation, each narrowed once.
+//  * gemm_low_kernel: the tensor-core product.  16-bit values need no hi / lo split: TMA loads the operand
+//    tiles straight from the matrices themselves (K-major, 64 elements = one 128-byte swizzle row per
+//    k-block) and one tcgen05.mma kind::f16 per 16 contraction steps accumulates in FP32 in tensor memory.
+//    Partial sums are promoted to round-to-nearest FP32 register sums exactly as in the 3xTF32 kernels
+//    (the tensor core's own accumulation truncates).  Same warp roles and barriers as
+//    gemm_tf32x3_promoted_kernel.
+// ------------------------------------------------------------------------------------------------
+struct LowEpilogue {
+    const uint16_t *bias;       // [n] storage bits, or null
+    int act;                    // activation wire code, 0 none
+    uint16_t *second;           // dense [m,n]: when set, `out` receives z and `second` act(z)
+};
+
+template <int KIND>
+__device__ __forceinline__ void low_finish(float sum, const LowEpilogue &ep, int64_t col, float &z_out, float &y_out) {
+    float z = low_round<KIND>(sum);                                                // MATMUL's own narrowing
+    if (ep.bias) z = low_round<KIND>(__fadd_rn(z, low_decode<KIND>(ep.bias[col])));   // ADD
+    z_out = z;
+    y_out = ep.act ? low_round<KIND>(low_activation_value(ep.act, z)) : z;          // activation
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(256) gemm_exact_low_kernel(int64_t m, int64_t n, int64_t k,
+        const uint16_t *__restrict__ a, int64_t a_ms, int64_t a_ks, const uint16_t *__restrict__ b, int64_t b_ks, int64_t b_ns,
+        uint16_t *c, int64_t c_ms, int64_t c_ns, LowEpilogue ep) {
+    __shared__ float as[XK][XT + 4];
+    __shared__ float bs[XK][XT + 4];
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int64_t m0 = (int64_t)blockIdx.y * XT, n0 = (int64_t)blockIdx.x * XT;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+    const bool a_kfast = a_ks == 1, b_nfast = b_ns == 1;
+    for (int64_t k0 = 0; k0 < k; k0 += XK) {
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            int e = tid + q * 256;
+            int row = a_kfast ? e / XK : e % XT, kk = a_kfast ? e % XK : e / XT;
+            int64_t gm = m0 + row, gk = k0 + kk;
+            as[kk][row] = (gm < m && gk < k) ? low_decode<KIND>(a[gm * a_ms + gk * a_ks]) : 0.0f;
+            int col = b_nfast ? e % XT : e / XK, kb = b_nfast ? e / XT : e % XK;
+            int64_t gn = n0 + col, gkb = k0 + kb;
+            bs[kb][col] = (gn < n && gkb < k) ? low_decode<KIND>(b[gkb * b_ks + gn * b_ns]) : 0.0f;
+        }
+        __syncthreads();
+        const int depth = (int)((k - k0) < XK ? (k - k0) : XK);
+        if (k == 1) {
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = __fmul_rn(as[0][ty * 4 + i], bs[0][tx * 4 + j]);
+        } else {
+            for (int kk = 0; kk < depth; kk++) {
+                float av[4], bv[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) av[i] = as[kk][ty * 4 + i];
+#pragma unroll
+                for (int j = 0; j < 4; j++) bv[j] = bs[kk][tx * 4 + j];
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(av[i], bv[j]));
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int64_t gm = m0 + ty * 4 + i;
+        if (gm >= m) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            int64_t gn = n0 + tx * 4 + j;
+            if (gn >= n) continue;
+            float z, y;
+            low_finish<KIND>(acc[i][j], ep, gn, z, y);
+            if (ep.second) { c[gm * c_ms + gn * c_ns] = low_encode<KIND>(z); ep.second[gm * n + gn] = low_encode<KIND>(y); }
+            else c[gm * c_ms + gn * c_ns] = low_encode<KIND>(y);
+        }
+    }
+}
+
+constexpr int LOW_BK = 64;              // 16-bit elements per k-block: one 128-byte swizzle row
+constexpr int LOW_UMMA_K = 16;          // kind::f16 contracts 16 elements (32 bytes) per instruction
+
+template <int BN> struct LowConfig {
+    static constexpr int kABytes = BM * 128;                // 128 rows of one k-block
+    static constexpr int kBBytes = BN * 128;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
+
+struct LowParams {
+    uint16_t *d; int64_t ldd;
+    int m, n, k_blocks;
+    int tiles_m, tiles_n;
+    int chunk_kb;
+    LowEpilogue ep;
+    int *error_word;
+};
+
+// Instruction descriptor of kind::f16: FP32 accumulate, both operands BF16 (format 1) or F16 (format 0), K-major.
+__device__ __forceinline__ uint32_t umma_idesc_low(int rows, int bn, int kind) {
+    const uint32_t format = kind == 1 ? 1u : 0u;
+    return (1u << 4) | (format << 7) | (format << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(rows >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// The elementary functions of the activations, out of line (see activate4).
+template <int KIND>
+__device__ __noinline__ float4 low_activate4(int act, float4 z) {
+    return make_float4(low_round<KIND>(low_activation_value(act, z.x)), low_round<KIND>(low_activation_value(act, z.y)),
+                       low_round<KIND>(low_activation_value(act, z.z)), low_round<KIND>(low_activation_value(act, z.w)));
+}
+
+// Four adjacent result cells of one row: narrow the sum, add the bias and narrow, apply the activation and
+// narrow, store 8 bytes (and the pre-activation beside it when asked).
+template <int KIND>
+__device__ __forceinline__ void low_emit4(const LowParams &prm, int row, int col, float s0, float s1, float s2, float s3, bool vec_ok) {
+    float z[4] = {low_round<KIND>(s0), low_round<KIND>(s1), low_round<KIND>(s2), low_round<KIND>(s3)};
+    const bool full = col + 3 < prm.n;
+    if (prm.ep.bias) {
+        if (full && vec_ok) {
+            const uint2 raw = *reinterpret_cast<const uint2 *>(prm.ep.bias + col);
+            const uint16_t bits[4] = {(uint16_t)(raw.x & 0xffffu), (uint16_t)(raw.x >> 16), (uint16_t)(raw.y & 0xffffu), (uint16_t)(raw.y >> 16)};
+#pragma unroll
+            for (int e = 0; e < 4; e++) z[e] = low_round<KIND>(__fadd_rn(z[e], low_decode<KIND>(bits[e])));
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; e++) if (col + e < prm.n) z[e] = low_round<KIND>(__fadd_rn(z[e], low_decode<KIND>(prm.ep.bias[col + e])));
+        }
+    }
+    float y[4] = {z[0], z[1], z[2], z[3]};
+    if (prm.ep.act == (int)Op::RELU) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) y[e] = relu_value(z[e]);            // exact on a storage value: no second narrowing needed
+    } else if (prm.ep.act) {
+        const float4 a = low_activate4<KIND>(prm.ep.act, make_float4(z[0], z[1], z[2], z[3]));
+        y[0] = a.x; y[1] = a.y; y[2] = a.z; y[3] = a.w;
+    }
+    uint16_t *drow = prm.d + (int64_t)row * prm.ldd;
+    uint16_t *srow = prm.ep.second ? prm.ep.second + (int64_t)row * prm.n : nullptr;
+    auto pack = [](const float (&v)[4]) {
+        return make_uint2((uint32_t)low_encode<KIND>(v[0]) | ((uint32_t)low_encode<KIND>(v[1]) << 16),
+                          (uint32_t)low_encode<KIND>(v[2]) | ((uint32_t)low_encode<KIND>(v[3]) << 16));
+    };
+    if (full && vec_ok) {
+        if (srow) { *reinterpret_cast<uint2 *>(drow + col) = pack(z); *reinterpret_cast<uint2 *>(srow + col) = pack(y); }
+        else *reinterpret_cast<uint2 *>(drow + col) = pack(y);
+    } else {
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            if (col + e >= prm.n) continue;
+            if (srow) { drow[col + e] = low_encode<KIND>(z[e]); srow[col + e] = low_encode<KIND>(y[e]); }
+            else drow[col + e] = low_encode<KIND>(y[e]);
+        }
+    }
+}
+
+template <int BN, int KIND>
+__global__ void __launch_bounds__(PROMOTED_THREADS, 1) gemm_low_kernel(
+        const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, LowParams prm) {
+    using Cfg = LowConfig<BN>;
+    constexpr int S = Cfg::kStages;
+    constexpr int CPT = BN / 2;             // result columns per epilogue thread
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S * Cfg::kStageBytes);
+    // bars[0..S) full, [S..2S) empty, [2S..2S+2) accumulator full, [2S+2..2S+4) accumulator empty
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * S + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar_base = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
+    auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * S + a); };
+    auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * S + 2 + a); };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), 256); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)Cfg::kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int total_tiles = prm.tiles_m * prm.tiles_n;
+    const int kb_count = prm.k_blocks;
+    const int CHUNK_KB = prm.chunk_kb;
+    const uint32_t smem_base = smem_u32(smem);
+
+    if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            uint32_t armed_phase[S]; bool armed[S];
+            for (int s = 0; s < S; s++) { armed[s] = false; armed_phase[s] = 0; }
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile / prm.tiles_n) * BM, n0 = (tile % prm.tiles_n) * BN;
+                for (int kb = 0; kb < kb_count; kb++) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t sa = smem_base + stage * Cfg::kStageBytes;
+                    mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
+                    armed[stage] = true; armed_phase[stage] = phase;
+                    // element coordinate kb * 64: 128 bytes, always a multiple of 16; rows and columns past the
+                    // matrix read as zeros
+                    tma_load_2d(sa, &map_p, full_bar(stage), kb * LOW_BK, m0);
+                    tma_load_2d(sa + Cfg::kABytes, &map_q, full_bar(stage), kb * LOW_BK, n0);
+                    if (++stage == S) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok || *abort_flag) {
+                for (int s = 0; s < S; s++) if (armed[s]) mbar_wait(full_bar(s), armed_phase[s], abort_flag);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_low(BM, BN, KIND);
+            const OperandForm form = operand_form(0);       // K-major, 128-byte swizzle: 32 bytes per MMA step
+            int stage = 0; uint32_t phase = 0;
+            uint32_t partial = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                for (int kb0 = 0; kb0 < kb_count && ok; kb0 += CHUNK_KB, partial++) {
+                    const int buf = partial & 1;
+                    if (!mbar_wait(acc_empty_bar(buf), ((partial >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                    const int kb1 = kb0 + CHUNK_KB < kb_count ? kb0 + CHUNK_KB : kb_count;
+                    for (int kb = kb0; kb < kb1; kb++) {
+                        if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint32_t pa = smem_base + stage * Cfg::kStageBytes, qa = pa + Cfg::kABytes;
+#pragma unroll
+                        for (int k4 = 0; k4 < LOW_BK / LOW_UMMA_K; k4++) {
+                            const uint32_t step = k4 * form.k8_step;
+                            umma_f16(tmem_d, umma_desc(form, pa + step), umma_desc(form, qa + step), idesc, (kb != kb0 || k4 != 0) ? 1u : 0u);
+                        }
+                        umma_commit(empty_bar(stage));
+                        if (++stage == S) { stage = 0; phase ^= 1u; }
+                    }
+                    if (ok) umma_commit(acc_full_bar(buf));
+                }
+            }
+        }
+    }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+        const int quarter = warp & 3;           // tensor-memory lanes 32*quarter .. +31
+        const int half = (warp - 4) >> 2;       // which half of the tile's columns
+        uint32_t partial = 0;
+        bool ok = true;
+        const bool vec_ok = (prm.ldd & 3) == 0 && ((uintptr_t)prm.d & 7) == 0 && (prm.n & 3) == 0
+                            && (!prm.ep.second || ((uintptr_t)prm.ep.second & 7) == 0) && (!prm.ep.bias || ((uintptr_t)prm.ep.bias & 7) == 0);
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int m0 = (tile / prm.tiles_n) * BM, n0 = (tile % prm.tiles_n) * BN;
+            float sum[CPT];
+            for (int kb0 = 0; kb0 < kb_count; kb0 += CHUNK_KB, partial++) {
+                const int buf = partial & 1;
+                ok = mbar_wait(acc_full_bar(buf), (partial >> 1) & 1u, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * CPT);
+                if (kb0 == 0) {
+#pragma unroll
+                    for (int s16 = 0; s16 < CPT / 16; s16++) {
+                        float t[16];
+                        tmem_load16(taddr + (uint32_t)(s16 * 16), t);
+#pragma unroll
+                        for (int i = 0; i < 16; i++) sum[s16 * 16 + i] = t[i];
+                    }
+                } else {
+#pragma unroll
+                    for (int s16 = 0; s16 < CPT / 16; s16++) {
+                        float t[16];
+                        tmem_load16(taddr + (uint32_t)(s16 * 16), t);
+#pragma unroll
+                        for (int i = 0; i < 16; i++) sum[s16 * 16 + i] = __fadd_rn(sum[s16 * 16 + i], t[i]);
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(acc_empty_bar(buf));
+            }
+            if (!ok) break;
+            const int row = m0 + quarter * 32 + lane;
+            if (row < prm.m) {
+#pragma unroll
+                for (int g = 0; g < CPT / 4; g++) {
+                    const int col = n0 + half * CPT + g * 4;
+                    if (col < prm.n) low_emit4<KIND>(prm, row, col, sum[g * 4], sum[g * 4 + 1], sum[g * 4 + 2], sum[g * 4 + 3], vec_ok);
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicOr(prm.error_word, ERR_WAIT_TIMEOUT);
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::kTmemCols) : "memory");
+    }
+}
+
 }  // namespace
 
 cudaError_t gemm_exact(cudaStream_t s, int64_t m, int64_t n, int64_t k, const float *a, int64_t a_ms, int64_t a_ks,
@@ -1300,6 +1632,83 @@ cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, in
     return cudaGetLastError();
 }
 int tc_gemm_launches(const TensorCoreGemm *g) { return g->slices > 1 ? 2 : 1; }
+
+// ---- 16-bit storage ------------------------------------------------------------------------------
+cudaError_t gemm_exact_low(cudaStream_t s, int kind, int64_t m, int64_t n, int64_t k, const void *a, int64_t a_ms, int64_t a_ks,
+                           const void *b, int64_t b_ks, int64_t b_ns, void *c, int64_t c_ms, int64_t c_ns,
+                           const void *bias, int act, void *second) {
+    if (m == 0 || n == 0) return cudaSuccess;
+    dim3 grid((unsigned)((n + XT - 1) / XT), (unsigned)((m + XT - 1) / XT));
+    if (grid.y > 65535 || (kind != 1 && kind != 2)) return cudaErrorInvalidValue;
+    LowEpilogue ep{(const uint16_t *)bias, act, (uint16_t *)second};
+    if (kind == 1) gemm_exact_low_kernel<1><<<grid, 256, 0, s>>>(m, n, k, (const uint16_t *)a, a_ms, a_ks, (const uint16_t *)b, b_ks, b_ns, (uint16_t *)c, c_ms, c_ns, ep);
+    else gemm_exact_low_kernel<2><<<grid, 256, 0, s>>>(m, n, k, (const uint16_t *)a, a_ms, a_ks, (const uint16_t *)b, b_ks, b_ns, (uint16_t *)c, c_ms, c_ns, ep);
+    return cudaGetLastError();
+}
+
+bool low_gemm_supported(int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldw, int64_t ldc) {
+    // TMA needs 16-byte row pitches (8 elements); the kernel's tiles need nothing else (edges read as zeros)
+    return m >= 1 && n >= 1 && k >= 8 && (k & 7) == 0 && (lda & 7) == 0 && (ldw & 7) == 0 && ldc >= n
+           && m < (1ll << 30) && n < (1ll << 30) && k < (1ll << 30);
+}
+
+static bool make_low_map(CUtensorMap *map, int kind, const void *base, int64_t rows, int64_t k, int64_t pitch, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)pitch * 2};
+    cuuint32_t box[2] = {(cuuint32_t)LOW_BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int KIND>
+static cudaError_t launch_low(cudaStream_t s, int grid, const CUtensorMap &p, const CUtensorMap &q, const LowParams &prm) {
+    using Cfg = LowConfig<BN>;
+    cudaFuncAttributes attr;
+    cudaError_t e = cudaFuncGetAttributes(&attr, gemm_low_kernel<BN, KIND>);
+    if (e != cudaSuccess) return e;
+    if (attr.numRegs * PROMOTED_THREADS < 128 * 72 + 256 * 216) return cudaErrorLaunchOutOfResources;
+    e = cudaFuncSetAttribute(gemm_low_kernel<BN, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    gemm_low_kernel<BN, KIND><<<grid, PROMOTED_THREADS, Cfg::kSmemBytes, s>>>(p, q, prm);
+    return cudaGetLastError();
+}
+
+cudaError_t low_gemm_launch(cudaStream_t s, int kind, int sm_count, int64_t m, int64_t n, int64_t k, const void *a, int64_t lda,
+                            const void *w, int64_t ldw, void *c, int64_t ldc, const void *bias, int act, void *second,
+                            int chunk_steps, int *error_word) {
+    if ((kind != 1 && kind != 2) || !low_gemm_supported(m, n, k, lda, ldw, ldc)) return cudaErrorInvalidValue;
+    if (((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return cudaErrorInvalidValue;
+    // tile width as for the FP32 products: least (waves x width), narrower tiles handicapped a little
+    auto cost = [&](int bn) {
+        int64_t t = ((m + BM - 1) / BM) * ((n + bn - 1) / bn);
+        int64_t waves = (t + sm_count - 1) / sm_count;
+        return (double)waves * bn * (bn == 256 ? 1.0 : (bn == 128 ? 1.05 : 1.15));
+    };
+    int bn = 64;
+    if (n >= 96 && cost(128) <= cost(bn)) bn = 128;
+    if (n >= 192 && cost(256) <= cost(bn)) bn = 256;
+    CUtensorMap map_p, map_q;
+    if (!make_low_map(&map_p, kind, a, m, k, lda, BM) || !make_low_map(&map_q, kind, w, n, k, ldw, bn)) return cudaErrorInvalidValue;
+    LowParams prm;
+    prm.d = (uint16_t *)c; prm.ldd = ldc; prm.m = (int)m; prm.n = (int)n;
+    prm.k_blocks = (int)((k + LOW_BK - 1) / LOW_BK);
+    prm.tiles_m = (int)((m + BM - 1) / BM); prm.tiles_n = (int)((n + bn - 1) / bn);
+    // A sum kept in tensor memory drifts by about 0.2 * (steps) * 2^-24 of itself (the MMA's accumulation
+    // truncates): over 4096 steps that is 5e-5, far below the storage types' own 2^-9 / 2^-12, so a 16-bit
+    // result needs no promotion until the contraction is much longer; one partial per 4096 steps keeps the
+    // write-out of a tile entirely under the next tile's main loop.
+    if (chunk_steps <= 0) chunk_steps = 4096;
+    prm.chunk_kb = chunk_steps / LOW_BK < 1 ? 1 : chunk_steps / LOW_BK;
+    prm.ep = LowEpilogue{(const uint16_t *)bias, act, (uint16_t *)second};
+    prm.error_word = error_word;
+    const int64_t tiles = (int64_t)prm.tiles_m * prm.tiles_n;
+    const int grid = (int)(tiles < sm_count ? tiles : sm_count);
+    if (kind == 1) return bn == 256 ? launch_low<256, 1>(s, grid, map_p, map_q, prm) : bn == 128 ? launch_low<128, 1>(s, grid, map_p, map_q, prm) : launch_low<64, 1>(s, grid, map_p, map_q, prm);
+    return bn == 256 ? launch_low<256, 2>(s, grid, map_p, map_q, prm) : bn == 128 ? launch_low<128, 2>(s, grid, map_p, map_q, prm) : launch_low<64, 2>(s, grid, map_p, map_q, prm);
+}
 
 }  // namespace kern
 }  // namespace syn

@@ -4,6 +4,7 @@
 // reductions; none uses tensor cores on purpose -- they are bounded by HBM bandwidth.
 #include "kernels.hpp"
 #include "activation.cuh"
+#include "lowp.cuh"
 #include "split.cuh"
 
 #include <cfloat>
@@ -1315,6 +1316,48 @@ cudaError_t launch_slots(cudaStream_t s, K kernel, const TensorSlot *slots, int 
     return cudaSuccess;
 }
 
+// ---- 16-bit storage: element-wise nodes and the row arg-max ---------------------------------------
+// Operands widened to FLOAT32, the operation there, one narrowing (CpuScalarReferenceKernel.java:93-115,
+// arithmetic :975-985).
+template <int KIND>
+__global__ void binary_low_kernel(int op, const uint16_t *__restrict__ a, const uint16_t *__restrict__ b, uint16_t *out, Index4 ix, int64_t total) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t oa, ob, oc;
+        unravel(i, ix, oa, ob, oc);
+        const float x = low_decode<KIND>(a[oa]), y = low_decode<KIND>(b[ob]);
+        float r;
+        switch ((Op)op) {
+            case Op::ADD: r = __fadd_rn(x, y); break;
+            case Op::SUB: r = __fsub_rn(x, y); break;
+            case Op::MUL: r = __fmul_rn(x, y); break;
+            default: r = __fdiv_rn(x, y); break;
+        }
+        out[i] = low_encode<KIND>(r);
+    }
+}
+
+template <int KIND>
+__global__ void unary_low_kernel(int op, const uint16_t *__restrict__ a, uint16_t *out, int64_t total) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = low_encode<KIND>(low_activation_value(op, low_decode<KIND>(a[i])));
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(kThreads) argmax_low_kernel(const uint16_t *__restrict__ x, int64_t *out, int64_t rows, int64_t cols) {
+    int lane = threadIdx.x & 31;
+    int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t r = warp; r < rows; r += warps) {
+        const uint16_t *row = x + r * cols;
+        unsigned long long best = 0;        // larger key wins; among equal keys the smaller index (FIRST_INDEX ties)
+        for (int64_t c = lane; c < cols; c += 32) {
+            unsigned long long cand = ((unsigned long long)order_key(low_decode<KIND>(row[c])) << 32) | (0xffffffffu - (uint32_t)c);
+            best = cand > best ? cand : best;
+        }
+        best = warp_best(best);
+        if (lane == 0) out[r] = (int64_t)(0xffffffffu - (uint32_t)(best & 0xffffffffu));
+    }
+}
+
 }  // namespace
 
 cudaError_t binary(cudaStream_t s, Op op, const float *a, const float *b, void *out, const Index4 &ix, int64_t total) {
@@ -1371,7 +1414,35 @@ cudaError_t copy_strided(cudaStream_t s, int element_bytes, const void *src, voi
     int grid = grid_for(total, kThreads);
     if (element_bytes == 4) copy_kernel<uint32_t><<<grid, kThreads, 0, s>>>((const uint32_t *)src, (uint32_t *)dst, ix, total);
     else if (element_bytes == 8) copy_kernel<uint64_t><<<grid, kThreads, 0, s>>>((const uint64_t *)src, (uint64_t *)dst, ix, total);
+    else if (element_bytes == 2) copy_kernel<uint16_t><<<grid, kThreads, 0, s>>>((const uint16_t *)src, (uint16_t *)dst, ix, total);
     else copy_kernel<uint8_t><<<grid, kThreads, 0, s>>>((const uint8_t *)src, (uint8_t *)dst, ix, total);
+    return cudaGetLastError();
+}
+
+cudaError_t binary_low(cudaStream_t s, int kind, Op op, const void *a, const void *b, void *out, const Index4 &ix, int64_t total) {
+    if (total == 0) return cudaSuccess;
+    if ((kind != 1 && kind != 2) || (op != Op::ADD && op != Op::SUB && op != Op::MUL && op != Op::DIV)) return cudaErrorInvalidValue;
+    const int grid = grid_for(total, kThreads);
+    if (kind == 1) binary_low_kernel<1><<<grid, kThreads, 0, s>>>((int)op, (const uint16_t *)a, (const uint16_t *)b, (uint16_t *)out, ix, total);
+    else binary_low_kernel<2><<<grid, kThreads, 0, s>>>((int)op, (const uint16_t *)a, (const uint16_t *)b, (uint16_t *)out, ix, total);
+    return cudaGetLastError();
+}
+
+cudaError_t unary_low(cudaStream_t s, int kind, Op op, const void *a, void *out, int64_t total) {
+    if (total == 0) return cudaSuccess;
+    if (kind != 1 && kind != 2) return cudaErrorInvalidValue;
+    const int grid = grid_for(total, kThreads);
+    if (kind == 1) unary_low_kernel<1><<<grid, kThreads, 0, s>>>((int)op, (const uint16_t *)a, (uint16_t *)out, total);
+    else unary_low_kernel<2><<<grid, kThreads, 0, s>>>((int)op, (const uint16_t *)a, (uint16_t *)out, total);
+    return cudaGetLastError();
+}
+
+cudaError_t argmax_rows_low(cudaStream_t s, int kind, const void *x, int64_t *out, int64_t rows, int64_t cols) {
+    if (rows == 0) return cudaSuccess;
+    if (kind != 1 && kind != 2) return cudaErrorInvalidValue;
+    const int grid = grid_for(rows, kThreads / 32);
+    if (kind == 1) argmax_low_kernel<1><<<grid, kThreads, 0, s>>>((const uint16_t *)x, out, rows, cols);
+    else argmax_low_kernel<2><<<grid, kThreads, 0, s>>>((const uint16_t *)x, out, rows, cols);
     return cudaGetLastError();
 }
 

@@ -450,7 +450,7 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
                 int other = add.inputs[0] == z ? add.inputs[1] : add.inputs[0];
                 const Value &bv = g.values[other];
                 bool row_bias = other != z && bv.elements() == n && !bv.shape.empty() && bv.shape.back() == n
-                                && bv.dtype == DType::F32 && (bv.role != Role::INTERMEDIATE ? true : bv.producer < i);
+                                && bv.dtype == g.values[z].dtype && (bv.role != Role::INTERMEDIATE ? true : bv.producer < i);
                 if (row_bias && (add.inputs[0] == z || add.inputs[1] == z)) {
                     lg.add = c; lg.bias = other; lg.emit_at = c;
                     z = add.outputs[0];
@@ -810,6 +810,20 @@ Status lower_program(const Program &source, const LoweringOptions &options, Plan
                 bool a_ok = a.strides[0] == 1 || a.strides[1] == 1 || a.shape[0] == 1 || a.shape[1] == 1;
                 bool b_ok = b.strides[0] == 1 || b.strides[1] == 1 || b.shape[0] == 1 || b.shape[1] == 1;
                 if (!a_ok || !b_ok) st.engine = GemmEngine::EXACT_SIMT;
+                if (dtype_low(a.dtype)) {
+                    // 16-bit storage: the tensor-core kernel reads K-major operands straight from the tensors
+                    // (x [m, k] and W [n, k] as Linear stores them) and writes a row-major result; anything
+                    // else takes the exact kernel.  No narrow engines, no gate.
+                    const bool direct = a.strides[1] == 1 && b.strides[0] == 1 && (c.strides[1] == 1 || c.shape[1] == 1) && !transposed && st.mask < 0
+                                        && a.offset % 8 == 0 && b.offset % 8 == 0
+                                        && kern::low_gemm_supported(st.m, st.n, st.k, a.strides[0], b.strides[1], c.strides[0]);
+                    if (st.engine == GemmEngine::TENSOR_CORE && !direct) st.engine = GemmEngine::EXACT_SIMT;
+                    // narrow products too (the 10-class head): a 64-wide tile wastes tensor work, not time
+                    if (st.engine == GemmEngine::EXACT_SIMT && direct && options.gemm_engine != 1
+                        && (double)st.m * (double)st.n * (double)st.k >= 16.0 * 1024 * 1024) st.engine = GemmEngine::TENSOR_CORE;
+                    if (st.bias >= 0 && !plan.views[st.bias].dense()) { message = "strided bias"; return UNSUPPORTED_SHAPE; }
+                    return OK;
+                }
                 // large products with one extent of at most 16 stream through the narrow kernels
                 if (options.gemm_engine != 1 && st.engine == GemmEngine::EXACT_SIMT && st.out2 < 0
                     && (double)st.m * (double)st.n * (double)st.k >= 16.0 * 1024 * 1024) {
@@ -1086,8 +1100,11 @@ std::string describe_plan(const Program &g, const Plan &plan) {
     for (const Step &st : plan.steps) {
         os << step_name(st.kind);
         if (st.kind == StepKind::GEMM) {
-            os << " engine=" << engine_name(st.engine)
+            const DType operand_type = plan.views[st.a].dtype;
+            os << " engine=" << (dtype_low(operand_type) && st.engine == GemmEngine::TENSOR_CORE ? "tcgen05_f16" : engine_name(st.engine))
                << " m=" << st.m << " n=" << st.n << " k=" << st.k;
+            if (operand_type == DType::BF16) os << " bf16";
+            if (operand_type == DType::F16) os << " f16";
             if (st.bias >= 0) os << " bias";
             if (st.relu) os << " relu";
             if (st.act) os << " act=" << op_name((Op)st.act);

@@ -99,8 +99,10 @@ Status check_node(const Program &g, int index, std::string &message) {
         }
         case Op::MATMUL:
             if (!need(2, 1)) FAIL(GRAPH_COMPILATION_FAILED, name << ": arity");
-            if (in(0).dtype != DType::F32 || in(1).dtype != DType::F32 || out(0).dtype != DType::F32)
-                FAIL(UNSUPPORTED_OPERATION, name << ": only FLOAT32 operands");
+            if (!dtype_floating(in(0).dtype) || in(1).dtype != in(0).dtype || out(0).dtype != in(0).dtype)
+                FAIL(UNSUPPORTED_OPERATION, name << ": operands and result of one floating type (FLOAT32, BFLOAT16, FLOAT16)");
+            if (dtype_low(in(0).dtype) && (in(0).shape.size() != 2 || in(1).shape.size() != 2))
+                FAIL(UNSUPPORTED_OPERATION, name << ": 16-bit operands only of rank 2");
             if (in(0).shape.size() == 2 && in(1).shape.size() == 2) {
                 if (out(0).shape.size() != 2 || in(0).shape[1] != in(1).shape[0] || out(0).shape[0] != in(0).shape[0] || out(0).shape[1] != in(1).shape[1])
                     FAIL(GRAPH_COMPILATION_FAILED, name << ": shape");
@@ -120,8 +122,10 @@ Status check_node(const Program &g, int index, std::string &message) {
             if (!need(2, 1)) FAIL(GRAPH_COMPILATION_FAILED, name << ": arity");
             if (in(0).dtype != in(1).dtype) FAIL(GRAPH_COMPILATION_FAILED, name << ": operand dtypes differ");
             // integer operands (labels against an ignore index) only for SUB and EQ
-            if (in(0).dtype != DType::F32 && !((in(0).dtype == DType::I32 || in(0).dtype == DType::I64) && (n.op == Op::SUB || n.op == Op::EQ)))
-                FAIL(UNSUPPORTED_OPERATION, name << ": only FLOAT32 operands (SUB and EQ also INT32 / INT64)");
+            // 16-bit storage for the four arithmetic nodes (FLOAT32 working type, one narrowing)
+            if (in(0).dtype != DType::F32 && !((in(0).dtype == DType::I32 || in(0).dtype == DType::I64) && (n.op == Op::SUB || n.op == Op::EQ))
+                && !(dtype_low(in(0).dtype) && (n.op == Op::ADD || n.op == Op::SUB || n.op == Op::MUL || n.op == Op::DIV)))
+                FAIL(UNSUPPORTED_OPERATION, name << ": only FLOAT32 operands (SUB and EQ also INT32 / INT64; ADD, SUB, MUL, DIV also BFLOAT16 / FLOAT16)");
             if (out(0).dtype != ((n.op == Op::GT || n.op == Op::LT || n.op == Op::EQ) ? DType::BOOL : in(0).dtype)) FAIL(GRAPH_COMPILATION_FAILED, name << ": result dtype");
             if (!broadcastable(in(0).shape, in(1).shape, shape) || shape != out(0).shape) FAIL(GRAPH_COMPILATION_FAILED, name << ": broadcast shape");
             if (shape.size() > 4) FAIL(UNSUPPORTED_SHAPE, name << ": rank above 4");
@@ -143,7 +147,9 @@ Status check_node(const Program &g, int index, std::string &message) {
             return OK;
         case Op::RELU: case Op::EXP: case Op::TANH: case Op::SIGMOID: case Op::SILU: case Op::GELU_TANH: case Op::GELU: case Op::ERF:
             if (!need(1, 1)) FAIL(GRAPH_COMPILATION_FAILED, name << ": arity");
-            if (in(0).dtype != DType::F32 || out(0).dtype != DType::F32) FAIL(UNSUPPORTED_OPERATION, name << ": only FLOAT32");
+            if (out(0).dtype != in(0).dtype) FAIL(GRAPH_COMPILATION_FAILED, name << ": dtype");
+            if (in(0).dtype != DType::F32 && !(dtype_low(in(0).dtype) && n.op != Op::EXP && n.op != Op::ERF))
+                FAIL(UNSUPPORTED_OPERATION, name << ": only FLOAT32 (the activations also BFLOAT16 / FLOAT16)");
             if (in(0).shape != out(0).shape) FAIL(GRAPH_COMPILATION_FAILED, name << ": shape");
             return OK;
         case Op::WHERE: {
@@ -249,7 +255,7 @@ Status check_node(const Program &g, int index, std::string &message) {
             return OK;
         case Op::ARG_MAX: {
             if (!need(1, 1) || n.attrs.size() != 2) FAIL(GRAPH_COMPILATION_FAILED, name << ": arity");
-            if (in(0).dtype != DType::F32 || out(0).dtype != DType::I64) FAIL(UNSUPPORTED_OPERATION, name << ": needs FLOAT32 input and INT64 result");
+            if (!dtype_floating(in(0).dtype) || out(0).dtype != DType::I64) FAIL(UNSUPPORTED_OPERATION, name << ": needs a floating input and an INT64 result");
             int64_t axis = (int64_t)n.attrs[0];
             if (in(0).shape.size() != 2 || axis != 1) FAIL(UNSUPPORTED_SHAPE, name << ": only [rows, classes] with axis 1");
             if (in(0).shape[1] < 1) FAIL(GRAPH_COMPILATION_FAILED, name << ": empty axis");
@@ -283,7 +289,7 @@ Status parse_program(const uint8_t *bytes, uint32_t size, Program &g, std::strin
         uint64_t o = off_v + i * 40;
         Value &v = g.values[i];
         uint32_t dt = r.u32(o), rank = r.u32(o + 4), doff = r.u32(o + 8), soff = r.u32(o + 12);
-        if (dt < 1 || dt > 4) FAIL(UNSUPPORTED_OPERATION, "value " << i << ": data type code " << dt);
+        if (dt < 1 || dt > 6) FAIL(UNSUPPORTED_OPERATION, "value " << i << ": data type code " << dt);
         if (rank > 8) FAIL(UNSUPPORTED_SHAPE, "value " << i << ": rank above 8");
         if ((uint64_t)doff + rank > nd) FAIL(GRAPH_COMPILATION_FAILED, "value " << i << ": dimensions out of range");
         v.dtype = (DType)dt;
@@ -311,6 +317,7 @@ Status parse_program(const uint8_t *bytes, uint32_t size, Program &g, std::strin
         v.role = (Role)role;
         v.constant_bits = r.u64(o + 32);
         if (v.role == Role::CONSTANT && v.elements() != 1) FAIL(UNSUPPORTED_SHAPE, "value " << i << ": only splat scalar constants");
+        if (v.role == Role::CONSTANT && dtype_low(v.dtype)) FAIL(UNSUPPORTED_OPERATION, "value " << i << ": 16-bit constants");
         if (v.role != Role::FEED && (soff != 0xffffffffu && v.role == Role::CONSTANT)) FAIL(GRAPH_COMPILATION_FAILED, "value " << i << ": constant with strides");
     }
     auto ref = [&](uint64_t index) { return r.u32(off_r + index * 4); };

@@ -39,8 +39,13 @@ enum Status : int32_t {
     KERNEL_COMPILATION_FAILED = 12, UNSUPPORTED_OPERATION = 13, TIMEOUT = 14, COMM_FAILED = 15
 };
 
-enum class DType : uint32_t { F32 = 1, I32 = 2, I64 = 3, BOOL = 4 };
-inline int dtype_bytes(DType t) { return t == DType::F32 || t == DType::I32 ? 4 : t == DType::I64 ? 8 : 1; }
+// BF16 / F16 are storage types (DataType.BFLOAT16 / FLOAT16 of the reference): raw 16-bit patterns in memory,
+// a FLOAT32 working type inside every node, one narrowing (round to nearest even; BFLOAT16 NaN -> 0x7FC0,
+// BFloat16Bits.java:17-29) of each node's result (CpuScalarReferenceKernel.java:93-115).
+enum class DType : uint32_t { F32 = 1, I32 = 2, I64 = 3, BOOL = 4, BF16 = 5, F16 = 6 };
+inline int dtype_bytes(DType t) { return t == DType::F32 || t == DType::I32 ? 4 : t == DType::I64 ? 8 : (t == DType::BF16 || t == DType::F16) ? 2 : 1; }
+inline bool dtype_low(DType t) { return t == DType::BF16 || t == DType::F16; }
+inline bool dtype_floating(DType t) { return t == DType::F32 || dtype_low(t); }
 
 // Operation wire codes: one per reference operation kind on the dense-MLP path
 // (modules/model/.../tensor/Tensor.java expression builders; node lists in

@@ -401,7 +401,7 @@ int32_t prepare_executable(Executable *x) {
     for (size_t i = 0; i < plan.steps.size(); i++) {
         const Step &st = plan.steps[i];
         StepExec &se = x->exec[i];
-        if (st.kind == StepKind::GEMM && st.engine == GemmEngine::TENSOR_CORE) {
+        if (st.kind == StepKind::GEMM && st.engine == GemmEngine::TENSOR_CORE && !dtype_low(plan.views[st.a].dtype)) {
             const View &c = plan.views[st.out];
             se.swapped = c.strides[0] == 1 && c.shape[0] != 1 && c.strides[1] != 1;
             // Plane rows follow the axis of the operand view that is NOT contiguous, so every split is a
@@ -458,7 +458,7 @@ int32_t prepare_executable(Executable *x) {
         // (with FP32 promotion the epilogue warps also add the partial sums, and the extra stores bought
         // nothing: fused_planes = 2 asks for them all the same.)  A product whose contraction is split into
         // slices has no epilogue of its own: its planes are written by the ordinary split pass.
-        if (st.kind != StepKind::GEMM || st.engine != GemmEngine::TENSOR_CORE || se.swapped || !ctx->fused_planes || st.k < 2048) continue;
+        if (st.kind != StepKind::GEMM || st.engine != GemmEngine::TENSOR_CORE || !se.tc || se.swapped || !ctx->fused_planes || st.k < 2048) continue;
         if (ctx->gemm_promote && ctx->fused_planes < 2) continue;
         if (kern::tc_gemm_launches(se.tc) > 1) continue;
         const View &u = plan.views[st.out2 >= 0 ? st.out2 : st.out];
@@ -527,7 +527,7 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
     for (size_t i = 0; i < plan.steps.size(); i++) {
         const Step &st = plan.steps[i];
         StepExec &se = x->exec[i];
-        const bool tc_step = st.kind == StepKind::GEMM && st.engine == GemmEngine::TENSOR_CORE;
+        const bool tc_step = st.kind == StepKind::GEMM && st.engine == GemmEngine::TENSOR_CORE && se.tc;
         if (time_steps && !tc_step) cudaEventRecord(x->step_events[2 * i], s);
         switch (st.kind) {
             case StepKind::GEMM: {
@@ -537,6 +537,22 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                 ep.gate = (const float *)ptr(st.mask);
                 ep.act = st.relu ? (int)Op::RELU : st.act;        // with a second output: out = z, second = act(z)
                 ep.second = (float *)ptr(st.out2);
+                if (dtype_low(a.dtype)) {
+                    // 16-bit storage: tensor cores straight from the operands, or the exact chain
+                    const int kind = a.dtype == DType::BF16 ? 1 : 2;
+                    const int act = st.relu ? (int)Op::RELU : st.act;
+                    cudaError_t le = cudaErrorInvalidValue;
+                    if (st.engine == GemmEngine::TENSOR_CORE)
+                        le = kern::low_gemm_launch(s, kind, ctx->sm_count, st.m, st.n, st.k, ptr(st.a), a.strides[0], ptr(st.b), b.strides[1],
+                                                   ptr(st.out), c.strides[0], ptr(st.bias), act, ptr(st.out2), ctx->gemm_chunk, ctx->error_dev);
+                    if (le != cudaSuccess) {        // a misaligned binding: the exact kernel takes every shape and alignment
+                        cudaGetLastError();
+                        le = kern::gemm_exact_low(s, kind, st.m, st.n, st.k, ptr(st.a), a.strides[0], a.strides[1], ptr(st.b), b.strides[0], b.strides[1],
+                                                  ptr(st.out), c.strides[0], c.strides[1], ptr(st.bias), act, ptr(st.out2));
+                    }
+                    LAUNCH(le);
+                    break;
+                }
                 cudaError_t narrow = cudaErrorInvalidValue;
                 if (st.engine == GemmEngine::NARROW_OUT)
                     narrow = kern::gemm_narrow_out(s, ctx->sm_count, st.m, st.n, st.k, (const float *)ptr(st.a), a.strides[0], (const float *)ptr(st.b),
@@ -584,7 +600,8 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                 const View &a = plan.views[st.a], &b = plan.views[st.b], &o = plan.views[st.out];
                 kern::Index4 ix = index4(o.shape, &a.strides, &b.strides, nullptr, &a.shape, &b.shape, nullptr);
                 int64_t total = 1; for (auto d : o.shape) total *= d;
-                if (a.dtype == DType::F32) LAUNCH(kern::binary(s, st.op, (const float *)ptr(st.a), (const float *)ptr(st.b), ptr(st.out), ix, total));
+                if (dtype_low(a.dtype)) LAUNCH(kern::binary_low(s, a.dtype == DType::BF16 ? 1 : 2, st.op, ptr(st.a), ptr(st.b), ptr(st.out), ix, total));
+                else if (a.dtype == DType::F32) LAUNCH(kern::binary(s, st.op, (const float *)ptr(st.a), (const float *)ptr(st.b), ptr(st.out), ix, total));
                 else LAUNCH(kern::binary_int(s, st.op, a.dtype, ptr(st.a), ptr(st.b), ptr(st.out), ix, total));
                 break;
             }
@@ -601,6 +618,7 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                 const void *src = ptr(st.a);
                 if (!a.dense()) return UNSUPPORTED_SHAPE;
                 if (st.kind == StepKind::SCALAR) LAUNCH(kern::scalar_op(s, st.op, a.dtype, src, ptr(st.out), st.scalar_bits, total));
+                else if (dtype_low(a.dtype)) LAUNCH(kern::unary_low(s, a.dtype == DType::BF16 ? 1 : 2, st.op, src, ptr(st.out), total));
                 else LAUNCH(kern::unary(s, st.op, (const float *)src, ptr(st.out), total));
                 break;
             }
@@ -675,7 +693,8 @@ int32_t enqueue_executable(Executable *x, const Binding &bind) {
                 if (se.colsum_partials && st.scalar_bits != 0) x->launches++;
                 break;
             case StepKind::ARG_MAX:
-                LAUNCH(kern::argmax_rows(s, (const float *)ptr(st.a), (int64_t *)ptr(st.out), st.m, st.n));
+                if (dtype_low(plan.views[st.a].dtype)) LAUNCH(kern::argmax_rows_low(s, plan.views[st.a].dtype == DType::BF16 ? 1 : 2, ptr(st.a), (int64_t *)ptr(st.out), st.m, st.n));
+                else LAUNCH(kern::argmax_rows(s, (const float *)ptr(st.a), (int64_t *)ptr(st.out), st.m, st.n));
                 break;
             case StepKind::RELU_BACKWARD: {
                 int64_t total = 1; for (auto d : plan.views[st.out].shape) total *= d;

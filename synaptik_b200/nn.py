@@ -66,9 +66,15 @@ class Model:
     """
 
     def __init__(self, dims: Sequence[int], context: native.Context | None = None, seed: int = 0,
-                 comm: native.Comm | None = None, world_size: int = 1, bias: bool = True, activation: str = "relu"):
+                 comm: native.Comm | None = None, world_size: int = 1, bias: bool = True, activation: str = "relu",
+                 dtype: str = "f32"):
         if activation not in ("relu", "tanh", "sigmoid", "silu", "gelu_tanh", "gelu"):
             raise ValueError("activation must be 'relu', 'tanh', 'sigmoid', 'silu', 'gelu_tanh' or 'gelu'")
+        if dtype not in ("f32", "bf16", "f16"):
+            raise ValueError("dtype must be 'f32', 'bf16' or 'f16'")
+        # 16-bit storage (DataType.BFLOAT16 / FLOAT16): parameters, input and output are held as 16-bit values,
+        # every node computes in FLOAT32 and narrows once; inference only (compute)
+        self.dtype = dtype
         self.dims = list(dims)
         self.bias = bias
         self.activation = activation
@@ -83,7 +89,7 @@ class Model:
             w = glorot_uniform(rng, self.dims[l + 1], self.dims[l])
             b = np.zeros(self.dims[l + 1], dtype=np.float32)
             for array in ((w, b) if bias else (w,)):
-                self.param_buffers.append(self.context.upload(array))
+                self.param_buffers.append(self.context.upload(program.to_storage(self.dtype, array)))
                 self.param_shapes.append(array.shape)
         self._inference = {}
         self._training = {}
@@ -93,6 +99,9 @@ class Model:
 
     # ---- parameters -----------------------------------------------------------------------
     def parameters(self) -> List[np.ndarray]:
+        """The parameters as FLOAT32 arrays (exactly the stored values, also for 16-bit storage)."""
+        if self.dtype != "f32":
+            return [program.from_storage(self.dtype, b.download(np.uint16, s)) for b, s in zip(self.param_buffers, self.param_shapes)]
         return [b.download(np.float32, s) for b, s in zip(self.param_buffers, self.param_shapes)]
 
     def load_parameters(self, arrays: Sequence[np.ndarray]) -> None:
@@ -100,17 +109,19 @@ class Model:
             array = np.ascontiguousarray(array, dtype=np.float32)
             if array.shape != tuple(shape):
                 raise ValueError(f"parameter shape {array.shape} != {shape}")
-            buf.upload(array)
+            buf.upload(program.to_storage(self.dtype, array))
 
     # ---- inference ------------------------------------------------------------------------
     def _inference_state(self, lead, arg_max: bool):
         key = (tuple(lead), arg_max)
         if key not in self._inference:
-            graph = program.mlp_inference_graph(self.dims, tuple(lead), arg_max, bias=self.bias, activation=self.activation)
+            graph = program.mlp_inference_graph(self.dims, tuple(lead), arg_max, bias=self.bias, activation=self.activation,
+                                                dtype=program.STORAGE_DTYPES[self.dtype])
             exe = native.Executable(self.context, graph.image)
             batch = int(np.prod(lead))
-            x = self.context.buffer(batch * self.dims[0] * 4)
-            out = self.context.buffer(batch * self.dims[-1] * 4)
+            width = 4 if self.dtype == "f32" else 2
+            x = self.context.buffer(batch * self.dims[0] * width)
+            out = self.context.buffer(batch * self.dims[-1] * width)
             outs = [out] + ([self.context.buffer(batch * 8)] if arg_max else [])
             self._inference[key] = (exe, x, outs)
         return self._inference[key]
@@ -123,9 +134,12 @@ class Model:
         if x.ndim < 2 or x.shape[-1] != self.dims[0]:
             raise ValueError(f"input shape {x.shape} does not end in {self.dims[0]} features")
         exe, xbuf, outs = self._inference_state(x.shape[:-1], arg_max)
-        xbuf.upload(x)
+        xbuf.upload(program.to_storage(self.dtype, x))
         exe.run([xbuf] + self.param_buffers, outs)
-        result = outs[0].download(np.float32, tuple(x.shape[:-1]) + (self.dims[-1],))
+        if self.dtype != "f32":
+            result = program.from_storage(self.dtype, outs[0].download(np.uint16, tuple(x.shape[:-1]) + (self.dims[-1],)))
+        else:
+            result = outs[0].download(np.float32, tuple(x.shape[:-1]) + (self.dims[-1],))
         if arg_max:
             return result, outs[1].download(np.int64, (x.shape[0],))
         return result
@@ -136,6 +150,8 @@ class Model:
         MEAN) or "mse" (MEAN); ``optimizer`` is Sgd, Adam or AdamW."""
         if loss not in ("ce", "mse"):
             raise ValueError("loss must be 'ce' or 'mse'")
+        if self.dtype != "f32":
+            raise ValueError("training needs FLOAT32 storage")
         self._loss = loss
         self._optimizer_config = optimizer
         kind, hyper = optimizer.native_kind()

@@ -17,8 +17,47 @@ import struct
 from dataclasses import dataclass, field
 from typing import List, Sequence
 
-F32, I32, I64, BOOL = 1, 2, 3, 4
-DTYPE_BYTES = {F32: 4, I32: 4, I64: 8, BOOL: 1}
+F32, I32, I64, BOOL, BF16, F16 = 1, 2, 3, 4, 5, 6
+DTYPE_BYTES = {F32: 4, I32: 4, I64: 8, BOOL: 1, BF16: 2, F16: 2}
+# BFLOAT16 / FLOAT16 are storage types (DataType.BFLOAT16 / FLOAT16): values travel as raw 16-bit patterns,
+# every node widens its operands to FLOAT32, computes there and narrows its result once.  They are accepted
+# by the views, MATMUL, ADD / SUB / MUL / DIV, the activations, CONTIGUOUS and ARG_MAX: the inference path.
+
+STORAGE_DTYPES = {"f32": F32, "bf16": BF16, "f16": F16}
+
+
+def to_storage(kind: str, array):
+    """FLOAT32 values as the storage type holds them: the array itself for "f32", raw 16-bit patterns
+    (uint16) for "bf16" (round to nearest even, NaN -> 0x7FC0: BFloat16Bits.fromFloat) and "f16" (IEEE
+    binary16, NaN -> 0x7E00: Float16Bits.fromFloat)."""
+    import numpy as np
+    array = np.ascontiguousarray(array, dtype=np.float32)
+    if kind == "f32":
+        return array
+    if kind == "f16":
+        with np.errstate(over="ignore"):
+            bits = array.astype(np.float16).view(np.uint16).copy()
+        bits[np.isnan(array)] = 0x7E00
+        return bits
+    raw = array.view(np.uint32)
+    upper = raw >> 16
+    discarded = raw & np.uint32(0xFFFF)
+    upper = upper + ((discarded > 0x8000) | ((discarded == 0x8000) & ((upper & 1) == 1))).astype(np.uint32)
+    bits = (upper & 0xFFFF).astype(np.uint16)
+    bits[np.isnan(array)] = 0x7FC0
+    return bits
+
+
+def from_storage(kind: str, bits):
+    """The FLOAT32 values of raw storage patterns (exact)."""
+    import numpy as np
+    if kind == "f32":
+        return np.ascontiguousarray(bits, dtype=np.float32)
+    bits = np.ascontiguousarray(bits, dtype=np.uint16)
+    if kind == "f16":
+        return bits.view(np.float16).astype(np.float32)
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
 
 OPS = {
     "PERMUTE": 1, "MATMUL": 2, "ADD": 3, "SUB": 4, "MUL": 5, "DIV": 6, "SCALAR_MUL": 7, "SCALAR_MIN": 8,
@@ -122,7 +161,7 @@ class GraphBuilder:
         if len(a.shape) < 2 or len(b.shape) < 2 or a.shape[-1] != b.shape[-2]:
             raise ValueError("MATMUL contraction extents differ")
         batch = _broadcast(tuple(a.shape[:-2]), tuple(b.shape[:-2]))
-        return self._node("MATMUL", [a, b], F32, tuple(batch) + (a.shape[-2], b.shape[-1]))
+        return self._node("MATMUL", [a, b], a.dtype, tuple(batch) + (a.shape[-2], b.shape[-1]))
 
     def swap_last_two(self, x: Value) -> Value:
         """PERMUTE exchanging the final two axes (LinearAlgebraGradientRules.swapLastTwo)."""
@@ -175,15 +214,15 @@ class GraphBuilder:
     def scalar_min(self, x, s): return self._scalar("SCALAR_MIN", x, s)
     def scalar_max(self, x, s): return self._scalar("SCALAR_MAX", x, s)
     def scalar_sub(self, x, s): return self._scalar("SCALAR_SUB", x, s)
-    def relu(self, x): return self._node("RELU", [x], F32, x.shape)
-    def exp(self, x): return self._node("EXP", [x], F32, x.shape)
-    def tanh(self, x): return self._node("TANH", [x], F32, x.shape)
-    def sigmoid(self, x): return self._node("SIGMOID", [x], F32, x.shape)
-    def silu(self, x): return self._node("SILU", [x], F32, x.shape)
+    def relu(self, x): return self._node("RELU", [x], x.dtype, x.shape)
+    def exp(self, x): return self._node("EXP", [x], x.dtype, x.shape)
+    def tanh(self, x): return self._node("TANH", [x], x.dtype, x.shape)
+    def sigmoid(self, x): return self._node("SIGMOID", [x], x.dtype, x.shape)
+    def silu(self, x): return self._node("SILU", [x], x.dtype, x.shape)
     def is_inf(self, x): return self._node("IS_INF", [x], BOOL, x.shape)
-    def gelu_tanh(self, x): return self._node("GELU_TANH", [x], F32, x.shape)
-    def gelu(self, x): return self._node("GELU", [x], F32, x.shape)
-    def erf(self, x): return self._node("ERF", [x], F32, x.shape)
+    def gelu_tanh(self, x): return self._node("GELU_TANH", [x], x.dtype, x.shape)
+    def gelu(self, x): return self._node("GELU", [x], x.dtype, x.shape)
+    def erf(self, x): return self._node("ERF", [x], x.dtype, x.shape)
 
     def activation(self, kind: str, x: Value) -> Value:
         return {"relu": self.relu, "tanh": self.tanh, "sigmoid": self.sigmoid, "silu": self.silu,
@@ -455,27 +494,28 @@ class MlpGraph:
 
 
 def mlp_inference_graph(dims: Sequence[int], batch, arg_max: bool = False, bias: bool = True,
-                        activation: str = "relu") -> MlpGraph:
+                        activation: str = "relu", dtype: int = F32) -> MlpGraph:
     """Model.compute of a Linear/activation stack (ModelBuilder.linear().relu() / .tanh() / .sigmoid()):
     feeds x then (w, b) per layer; publishes the last layer's output (and its row arg-max when asked).
     `batch` is the row count, or the tuple of leading dimensions of an input [batch.., features]
-    (Linear applies to the last dimension, Tensor.java:1270-1365)."""
+    (Linear applies to the last dimension, Tensor.java:1270-1365).  `dtype` is the storage type of input,
+    parameters and output: FLOAT32, or BFLOAT16 / FLOAT16 (FLOAT32 working type, one narrowing per node)."""
     g = GraphBuilder()
     lead = tuple(batch) if isinstance(batch, (tuple, list)) else (int(batch),)
     if arg_max and len(lead) != 1:
         raise ValueError("row arg-max needs a [batch, features] input")
     batch = lead[0]
-    x = g.feed(F32, lead + (dims[0],))
+    x = g.feed(dtype, lead + (dims[0],))
     names, shapes = ["x"], {"x": lead + (dims[0],)}
     a = x
     params = []
     for l in range(len(dims) - 1):
-        w = g.feed(F32, (dims[l + 1], dims[l]))
+        w = g.feed(dtype, (dims[l + 1], dims[l]))
         names.append(f"w{l}")
         shapes[f"w{l}"] = w.shape
         b = None
         if bias:
-            b = g.feed(F32, (dims[l + 1],))
+            b = g.feed(dtype, (dims[l + 1],))
             names.append(f"b{l}")
             shapes[f"b{l}"] = b.shape
         params.append((w, b))

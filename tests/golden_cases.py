@@ -200,3 +200,86 @@ def check_softmax_finite_cases(b):
 ALL_CHECKS = [check_softmax_backward_recipe, check_softmax_backward_nonfinite, check_softmax_backward_through_forward,
               check_softmax_tied_extremes, check_ce_finite_extremes, check_ce_mixed_infinity, check_dense_ce_zero_rows,
               check_index_ce_ignored_rows, check_ce_active_poison_rows, check_erf_gelu_extremes, check_softmax_finite_cases]
+
+
+# ---- 16-bit storage -------------------------------------------------------------------------------
+# A backend additionally provides, on storage bit patterns (uint16) of kind "bf16" / "f16":
+#     low_matmul(kind, a_bits [m,k] view, b_bits [k,n] view) -> bits [m,n]   (views may be transposed arrays)
+#     low_unary(kind, name, bits) -> bits
+def _encode(kind, x):
+    """FLOAT32 -> storage bits, as BFloat16Bits.fromFloat / Float16Bits.fromFloat."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    if kind == "f16":
+        with np.errstate(over="ignore"):
+            out = x.astype(np.float16).view(np.uint16).copy()
+        out[np.isnan(x)] = 0x7E00
+        return out
+    raw = x.view(np.uint32)
+    upper = raw >> 16
+    discarded = raw & np.uint32(0xFFFF)
+    upper = upper + ((discarded > 0x8000) | ((discarded == 0x8000) & ((upper & 1) == 1))).astype(np.uint32)
+    out = (upper & 0xFFFF).astype(np.uint16)
+    out[np.isnan(x)] = 0x7FC0
+    return out
+
+
+def _decode(kind, bits):
+    bits = np.ascontiguousarray(bits, dtype=np.uint16)
+    return bits.view(np.float16).astype(np.float32) if kind == "f16" else (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+def check_matmul_mod5_low_precision(b):
+    case = GOLDEN["matmul_mod5_low_precision"]
+    m, k, n = case["m"], case["k"], case["n"]
+    for kind in ("bf16", "f16"):
+        for right_transposed in (False, True):
+            if right_transposed:        # left [m,k] row-major, right stored as [n,k]
+                left = (np.arange(m * k) % 5 - 2).astype(np.float32).reshape(m, k)
+                stored = (np.arange(n * k) % 5 - 2).astype(np.float32).reshape(n, k)
+                a_bits, b_bits = _encode(kind, left), _encode(kind, stored).T
+                want = left.astype(np.int64) @ stored.astype(np.int64).T
+            else:                       # left stored as [k,m], right [k,n] row-major
+                stored = (np.arange(k * m) % 5 - 2).astype(np.float32).reshape(k, m)
+                right = (np.arange(k * n) % 5 - 2).astype(np.float32).reshape(k, n)
+                a_bits, b_bits = _encode(kind, stored).T, _encode(kind, right)
+                want = stored.astype(np.int64).T @ right.astype(np.int64)
+            got = _decode(kind, b.low_matmul(kind, a_bits, b_bits))
+            assert np.array_equal(got, want.astype(np.float32)), (kind, right_transposed)
+
+
+def check_activation_low_extremes(b):
+    case = GOLDEN["activation_low_extremes"]
+    one, half = np.float32(1.0), np.float32(0.5)
+    for kind in ("bf16", "f16"):
+        x_bits = _encode(kind, vals(case["x"]))
+        for name in case["kinds"]:
+            want = []
+            for f in _decode(kind, x_bits):
+                f = np.float32(f)
+                with np.errstate(all="ignore"):
+                    if np.isnan(f):
+                        r = np.float32(np.nan)
+                    elif name == "gelu":
+                        r = np.float32(np.copysign(0.0, f)) if f <= 0 else f
+                    elif name == "gelu_tanh":
+                        if np.isneginf(f):
+                            r = np.float32(-0.0)
+                        else:
+                            cube = np.float32(np.float32(f * f) * f)
+                            scale = np.float32(math.sqrt(float(np.float32(np.float32(2.0) / np.float32(math.pi)))))
+                            inner = np.float32(scale * np.float32(f + np.float32(np.float32(0.044715) * cube)))
+                            r = np.float32(np.float32(half * f) * np.float32(one + np.float32(math.tanh(float(inner)))))
+                    elif name == "silu" and np.isneginf(f):
+                        r = np.float32(-0.0)
+                    else:
+                        e = np.float32(math.exp(float(-f if f >= 0 else f))) if np.isfinite(f) else np.float32(0.0)
+                        numerator = (one if f >= 0 else e) if name == "sigmoid" else (f if f >= 0 else np.float32(f * e))
+                        r = np.float32(numerator / np.float32(one + e))
+                want.append(r)
+            want_bits = _encode(kind, np.array(want, dtype=np.float32))
+            got_bits = b.low_unary(kind, name, x_bits)
+            nan = np.isnan(_decode(kind, want_bits))
+            assert np.all(np.isnan(_decode(kind, got_bits)[nan])) and np.array_equal(got_bits[~nan], want_bits[~nan]), (kind, name, got_bits, want_bits)
+
+
+LOW_CHECKS = [check_matmul_mod5_low_precision, check_activation_low_extremes]

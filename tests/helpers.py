@@ -6,7 +6,8 @@ import numpy as np
 
 from synaptik_b200 import native, program
 
-NP_DTYPES = {program.F32: np.float32, program.I32: np.int32, program.I64: np.int64, program.BOOL: np.uint8}
+NP_DTYPES = {program.F32: np.float32, program.I32: np.int32, program.I64: np.int64, program.BOOL: np.uint8,
+             program.BF16: np.uint16, program.F16: np.uint16}      # 16-bit storage travels as raw bit patterns
 
 
 def run_image(context, builder: program.GraphBuilder, feeds, engine: int | None = None):

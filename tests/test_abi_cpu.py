@@ -292,3 +292,28 @@ def test_the_other_activations_ride_in_the_gemm_epilogue_too(lib, activation, na
     assert len(fused) == 2 and not any(p.startswith("unary") and f"op={name}" in p for p in plan), plan
     keeps = sum("keep_preactivation" in p for p in fused)
     assert keeps == (0 if activation in ("tanh", "sigmoid") else 2), plan
+
+
+def test_16_bit_storage_lowers_to_the_f16_tensor_core_kernel_and_is_validated(lib):
+    # Model.compute on BFLOAT16 / FLOAT16 storage: every Linear is one product with bias and activation in
+    # its epilogue, the wide ones and the 10-class head on the tensor cores (kind::f16), no split passes
+    for dtype, tag in ((program.BF16, "bf16"), (program.F16, "f16")):
+        g = program.mlp_inference_graph([784, 4096, 4096, 10], 8192, True, dtype=dtype)
+        plan = native.describe(g.image).strip().split("\n")
+        assert [p.split(" nodes=")[0] for p in plan[:3]] == [
+            f"gemm engine=tcgen05_f16 m=8192 n=4096 k=784 {tag} bias relu", f"gemm engine=tcgen05_f16 m=8192 n=4096 k=4096 {tag} bias relu",
+            f"gemm engine=tcgen05_f16 m=8192 n=10 k=4096 {tag} bias"]
+        assert plan[3].startswith("arg_max")
+    # a contraction that is not a multiple of 8 elements has no 16-byte row pitch for TMA: the exact kernel
+    g = program.mlp_inference_graph([100, 4100, 10], 8192, dtype=program.BF16)
+    plan = native.describe(g.image).strip().split("\n")
+    assert "engine=exact_simt" in plan[0] and "engine=exact_simt" in plan[1]
+    # outside the inference path 16-bit values are refused, not silently widened
+    b = program.GraphBuilder()
+    x = b.feed(program.BF16, (4, 8))
+    b.publish(b.softmax(x, 1))
+    status = lib.synaptik_cuda_program_describe(b.build(), len(b.build()), None, 0, None)
+    assert status == 13
+    b = program.GraphBuilder()
+    b.publish(b.add(b.feed(program.BF16, (4, 8)), b.feed(program.F16, (4, 8))))
+    assert lib.synaptik_cuda_program_describe(b.build(), len(b.build()), None, 0, None) == 9

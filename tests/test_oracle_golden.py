@@ -470,3 +470,21 @@ class CheckerBackend:
 @pytest.mark.parametrize("check", golden_cases.ALL_CHECKS, ids=lambda f: f.__name__)
 def test_reference_held_gradient_rule_vectors(oracle, check):
     check(CheckerBackend(oracle))
+
+
+class LowCheckerBackend:
+    """The CPU checker's 16-bit storage functions behind the interface of golden_cases."""
+
+    def __init__(self, oracle):
+        self.o = oracle
+
+    def low_matmul(self, kind, a_bits, b_bits):
+        return self.o.low_encode(kind, self.o.matmul(self.o.low_decode(kind, np.ascontiguousarray(a_bits)), self.o.low_decode(kind, np.ascontiguousarray(b_bits))))
+
+    def low_unary(self, kind, name, bits):
+        return self.o.low_encode(kind, self.o.low_activation(name, self.o.low_decode(kind, bits)))
+
+
+@pytest.mark.parametrize("check", golden_cases.LOW_CHECKS, ids=lambda f: f.__name__)
+def test_reference_held_low_precision_vectors(oracle, check):
+    check(LowCheckerBackend(oracle))
