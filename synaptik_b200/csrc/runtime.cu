@@ -1307,6 +1307,10 @@ static int32_t optimizer_state(void *optimizer, int32_t index, int32_t slot, voi
     if (bytes != o->counts[index] * 4) return RANGE_OUT_OF_BOUNDS;
     std::lock_guard<std::mutex> lock(o->ctx->mutex);
     DeviceGuard guard(o->ctx->device);
+    if (!o->journal.empty()) {              // steps still in flight: settle them first, so the state moved is a committed one
+        int32_t settled = drain_errors(o->ctx);
+        if (settled != OK) return settled;
+    }
     if (slot == 2 && o->acc.empty()) {
         if (!upload) {                      // no run has accumulated yet: the pending sum is all zeros
             memset(host, 0, bytes);

@@ -137,7 +137,7 @@ def test_classifier_head_at_full_size(ctx):
 
 
 def test_classifier_inference_at_full_size(ctx):
-    # BASELINE inference configuration: 784-4096-4096-4096-10, batch 8192 per GPU, arg-max published
+    # the benchmark inference configuration: 784-4096-4096-4096-10, batch 8192 per GPU, arg-max published
     from synaptik_b200 import nn
     dims, batch = [784, 4096, 4096, 4096, 10], 8192
     rng = np.random.default_rng(21)
@@ -226,7 +226,7 @@ def test_full_width_classifier_training_against_the_openblas_cpu_tier_for_20_ste
         table.append({"step": step, "device_loss": device_loss, "cpu_loss": losses[0], "cpu_reordered_loss": losses[1],
                       "device_vs_cpu": device, "cpu_reordered_vs_cpu": floor})
         report("full_width_training_20_steps", table)
-    # Measured (see the design notes for the table): the reordered CPU run stays within 1e-4 (relative L2) of
+    # Measured: the reordered CPU run stays within 1e-4 (relative L2) of
     # the CPU run for the first two steps and reaches 0.10 after twenty, the device starts at 0.04 and reaches
     # 0.19.  The device's head start is the 3xTF32 product: its error (about one unit of 2^-24 sum|a b|, see
     # the GEMM bound) is some twenty times that of OpenBLAS's blocked FMA sums, so about twenty times as many

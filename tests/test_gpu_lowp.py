@@ -154,8 +154,8 @@ def test_tensor_core_product_on_16_bit_storage(ctx, oracle, kind, m, k, n):
         z_dev, y_dev = run_bits(ctx, linear_graph(kind, m, k, n, activation, keep_preactivation=True), [x, w, b], engine=2)
         z_ref, y_ref = oracle.low_linear(kind, x, w, b, activation)
         # two FLOAT32 sums that differ by e narrow to values that differ by at most e plus one unit of the storage
-        # type; e is the tensor-core bound of the FP32 products (section "Numerical contract": one accumulator over
-        # up to 4096 steps truncates by 0.2 * K units of 2^-24 of the sum of |a b|)
+        # type; e is the tensor-core bound of the FP32 products (one accumulator over up to 4096 steps truncates
+        # by 0.2 * K units of 2^-24 of the sum of |a b|)
         fx, fw = oracle.low_decode(kind, x).astype(np.float64), oracle.low_decode(kind, w).astype(np.float64)
         e = (8.0 + 0.25 * k) * 2.0 ** -24 * (np.abs(fx) @ np.abs(fw).T)
         unit = 2.0 ** (-8 if kind == "bf16" else -11)
