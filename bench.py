@@ -700,7 +700,7 @@ def measure_kernel_case(ctx, device_index, case, m, k, n, forward_only=False, st
                 kernel_work += 2.0 * mm * nn_ * kk
                 kernel_ms += t
         if dtype != "f32":
-            kernel = "gemm_low_kernel"
+            kernel = "gemm_low_pair_kernel (gemm_low_kernel where the product has few tiles)"
     else:
         kernel = {"ce": "ce_rows_vec_kernel", "argmax": "argmax_vec_kernel", "dense_ce": "dense_ce_rows_vec_kernel"}.get(case, "softmax_rows_vec_kernel")
         kernel_work, kernel_ms = work, median_ms

@@ -1179,9 +1179,10 @@ template <int BN> struct LowConfig {
     static constexpr int kABytes = BM * 128;                // 128 rows of one k-block
     static constexpr int kBBytes = BN * 128;
     static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStagingBytes = BN >= 128 ? 8 * 4096 : 0;      // one box of 32 rows x 64 columns per epilogue warp
     static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
     static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
 };
 
 struct LowParams {
@@ -1191,6 +1192,7 @@ struct LowParams {
     int chunk_kb;
     LowEpilogue ep;
     int *error_word;
+    int staged;         // results leave through shared memory and TMA stores (see low_emit_staged)
 };
 
 // Instruction descriptor of kind::f16: FP32 accumulate, both operands BF16 (format 1) or F16 (format 0), K-major.
@@ -1254,15 +1256,138 @@ __device__ __forceinline__ void low_emit4(const LowParams &prm, int row, int col
     }
 }
 
+// ---- write-out through shared memory ------------------------------------------------------------
+// An epilogue thread owns one result row (tensor-memory lane = row), so direct stores of a warp go to 32
+// different rows, 8 bytes each: measured on 8192 x 4096 x 4096 BF16 the write-out of a tile then takes
+// twice as long as the tile's MMAs (tensor pipe 53-58 % active; with the write-out switched off the same
+// launch ran 1.5x faster).  Staged form: every warp converts its 32 rows x CPT columns with packed
+// conversions into 128-byte-swizzled boxes of 32 rows x 64 columns in shared memory and one lane hands each
+// box to a TMA store, which also clips rows and columns past the matrix.  Same arithmetic, node by node, as
+// low_emit4: narrow the sum; add the bias in FLOAT32 and narrow; activation and narrow.
+template <int KIND> __device__ __forceinline__ uint32_t low_pack2(float lo, float hi) {
+    uint32_t r;
+    if constexpr (KIND == 1) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+template <int KIND> __device__ __forceinline__ void low_unpack2(uint32_t r, float &lo, float &hi) {
+    if constexpr (KIND == 1) { lo = __uint_as_float(r << 16); hi = __uint_as_float(r & 0xffff0000u); }
+    else { lo = __half2float(__ushort_as_half((uint16_t)(r & 0xffffu))); hi = __half2float(__ushort_as_half((uint16_t)(r >> 16))); }
+}
+// Math.max(x, +0) on both halves: NaN stays NaN, -0 and negatives give +0.
+template <int KIND> __device__ __forceinline__ uint32_t low_relu2(uint32_t r) {
+    uint32_t d;
+    if constexpr (KIND == 1) asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(r), "r"(0u));
+    else asm("max.NaN.f16x2 %0, %1, %2;" : "=r"(d) : "r"(r), "r"(0u));
+    return d;
+}
+// The packed instructions give every NaN as 0x7FFF; the storage types' NaN is 0x7FC0 / 0x7E00 (low_encode).
+template <int KIND> __device__ __forceinline__ uint32_t low_canonical_nan2(uint32_t r) {
+    constexpr uint32_t inf2 = KIND == 1 ? 0x7F807F80u : 0x7C007C00u, nan2 = KIND == 1 ? 0x7FC07FC0u : 0x7E007E00u;
+    const uint32_t mask = __vcmpgtu2(r & 0x7FFF7FFFu, inf2);
+    return mask ? ((r & ~mask) | (nan2 & mask)) : r;
+}
+
+// The bias of a warp's columns lives in its lanes' registers, four columns per lane (lane l: columns
+// 4 l .. 4 l + 3 of the warp's first 128), fetched before the warp waits for the accumulator: a load from
+// global memory between the stores of the write-out would cost a round trip to L2 per eight columns.
+__device__ __forceinline__ uint2 low_bias_lane(const LowParams &prm, int col) {
+    uint2 b = make_uint2(0u, 0u);
+    if (!prm.ep.bias || col >= prm.n) return b;
+    if (col + 3 < prm.n && ((uintptr_t)(prm.ep.bias + col) & 7) == 0) return *reinterpret_cast<const uint2 *>(prm.ep.bias + col);
+#pragma unroll
+    for (int e = 0; e < 4; e++)
+        if (col + e < prm.n) (e < 2 ? b.x : b.y) |= (uint32_t)prm.ep.bias[col + e] << (16 * (e & 1));
+    return b;
+}
+
+// Eight adjacent result cells of one row as four packed words; `group` is their index among the warp's
+// groups of eight columns (the bias of group g is in lanes 2 g and 2 g + 1).
+template <int KIND>
+__device__ __forceinline__ uint4 low_finish8(const LowParams &prm, int group, const float *s, uint2 bias_lane) {
+    uint32_t w[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) w[e] = low_pack2<KIND>(s[2 * e], s[2 * e + 1]);            // MATMUL's own narrowing
+    if (prm.ep.bias) {
+        uint32_t b[4];
+        b[0] = __shfl_sync(0xffffffffu, bias_lane.x, 2 * group);
+        b[1] = __shfl_sync(0xffffffffu, bias_lane.y, 2 * group);
+        b[2] = __shfl_sync(0xffffffffu, bias_lane.x, 2 * group + 1);
+        b[3] = __shfl_sync(0xffffffffu, bias_lane.y, 2 * group + 1);
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            float z0, z1, b0, b1;
+            low_unpack2<KIND>(w[e], z0, z1);
+            low_unpack2<KIND>(b[e], b0, b1);
+            w[e] = low_pack2<KIND>(__fadd_rn(z0, b0), __fadd_rn(z1, b1));                 // ADD
+        }
+    }
+    if (prm.ep.act == (int)Op::RELU) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) w[e] = low_relu2<KIND>(w[e]);
+    } else if (prm.ep.act) {
+        float z[8];
+#pragma unroll
+        for (int e = 0; e < 4; e++) low_unpack2<KIND>(w[e], z[2 * e], z[2 * e + 1]);
+        const float4 a0 = low_activate4<KIND>(prm.ep.act, make_float4(z[0], z[1], z[2], z[3]));
+        const float4 a1 = low_activate4<KIND>(prm.ep.act, make_float4(z[4], z[5], z[6], z[7]));
+        w[0] = low_pack2<KIND>(a0.x, a0.y); w[1] = low_pack2<KIND>(a0.z, a0.w);
+        w[2] = low_pack2<KIND>(a1.x, a1.y); w[3] = low_pack2<KIND>(a1.z, a1.w);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; e++) w[e] = low_canonical_nan2<KIND>(w[e]);
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+
+// One warp's 32 rows x CPT columns of a finished tile, 64 columns at a time.  `stage` is this warp's 4 KB of
+// shared memory (1024-byte aligned): one box of 32 rows x 128 bytes, 16-byte chunk j of row r at chunk
+// j ^ (r & 7) as the 128-byte swizzle of the store's tensor map expects (and conflict-free for a thread per row).
+// One box per warp rather than one per 64 columns: the shared memory saved is one more stage of operands, and
+// the main loop is bound by how many operand bytes are in flight (see LowPairConfig).
+template <int KIND, int CPT>
+__device__ __forceinline__ void low_emit_staged(const LowParams &prm, const CUtensorMap *map_d, uint32_t stage, int row0, int col0,
+                                                const float (&sum)[CPT], uint2 bias_lane, int lane) {
+    static_assert(CPT % 64 == 0 && CPT <= 128, "boxes of 64 columns; the bias registers cover 128");
+#pragma unroll
+    for (int b = 0; b < CPT / 64; b++) {
+        if (col0 + b * 64 >= prm.n) break;          // warp-uniform
+        // the previous box has been read out of shared memory
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const uint4 words = low_finish8<KIND>(prm, b * 8 + j, &sum[b * 64 + j * 8], bias_lane);
+            const uint32_t dst = stage + (uint32_t)(lane * 128 + ((j ^ (lane & 7)) << 4));
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(words.x), "r"(words.y), "r"(words.z), "r"(words.w) : "memory");
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0 && row0 < prm.m) {
+            tma_store_2d(map_d, stage, col0 + b * 64, row0);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+    }
+}
+// Before a block leaves: its stores have completed.
+__device__ __forceinline__ void low_staged_drain(int lane) {
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    __syncwarp();
+}
+
 template <int BN, int KIND>
 __global__ void __launch_bounds__(PROMOTED_THREADS, 1) gemm_low_kernel(
-        const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, LowParams prm) {
+        const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_d,
+        LowParams prm) {
     using Cfg = LowConfig<BN>;
     constexpr int S = Cfg::kStages;
     constexpr int CPT = BN / 2;             // result columns per epilogue thread
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S * Cfg::kStageBytes);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S * Cfg::kStageBytes + Cfg::kStagingBytes);
     // bars[0..S) full, [S..2S) empty, [2S..2S+2) accumulator full, [2S+2..2S+4) accumulator empty
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * S + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -1362,6 +1487,7 @@ __global__ void __launch_bounds__(PROMOTED_THREADS, 1) gemm_low_kernel(
                             && (!prm.ep.second || ((uintptr_t)prm.ep.second & 7) == 0) && (!prm.ep.bias || ((uintptr_t)prm.ep.bias & 7) == 0);
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             const int m0 = (tile / prm.tiles_n) * BM, n0 = (tile % prm.tiles_n) * BN;
+            const uint2 bias_lane = prm.staged ? low_bias_lane(prm, n0 + half * CPT + lane * 4) : make_uint2(0u, 0u);
             float sum[CPT];
             for (int kb0 = 0; kb0 < kb_count; kb0 += CHUNK_KB, partial++) {
                 const int buf = partial & 1;
@@ -1391,6 +1517,13 @@ __global__ void __launch_bounds__(PROMOTED_THREADS, 1) gemm_low_kernel(
                 mbar_arrive(acc_empty_bar(buf));
             }
             if (!ok) break;
+            if constexpr (CPT >= 64) {
+                if (prm.staged) {
+                    low_emit_staged<KIND, CPT>(prm, &map_d, smem_base + (uint32_t)(S * Cfg::kStageBytes + (warp - 4) * 4096),
+                                               m0 + quarter * 32, n0 + half * CPT, sum, bias_lane, lane);
+                    continue;
+                }
+            }
             const int row = m0 + quarter * 32 + lane;
             if (row < prm.m) {
 #pragma unroll
@@ -1400,6 +1533,7 @@ __global__ void __launch_bounds__(PROMOTED_THREADS, 1) gemm_low_kernel(
                 }
             }
         }
+        if (prm.staged) low_staged_drain(lane);
     }
 
     tc_fence_before();
@@ -1409,6 +1543,204 @@ __global__ void __launch_bounds__(PROMOTED_THREADS, 1) gemm_low_kernel(
         __syncwarp();
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::kTmemCols) : "memory");
+    }
+}
+
+
+// Two-SM form of the 16-bit product (cta_group::2, M = 256, tiles of 256 x 256).  Each block of the pair loads
+// its 128 rows of P and its 128 of the tile's 256 rows of Q, so one stage is 32 KB per block and six stages
+// fit beside the write-out boxes; the even block issues the MMAs for both.  A k-block of 64 elements is 512
+// clocks of MMA, a third of the FP32 kernel's, so the operand bytes in flight, not a bandwidth, bound the
+// main loop: with five stages ncu showed the tensor pipe active in 73 % of the cycles while L1, L2 and DRAM
+// were below half of their peaks.  Roles, barriers and tile order are those of the two-SM FP32 kernel above;
+// tiles are assigned to pairs in fixed rotation.
+struct LowPairConfig {
+    static constexpr int BN = 256;
+    static constexpr int kStages = 6;
+    static constexpr int kABytes = BM * 128;
+    static constexpr int kBBytes = (BN / 2) * 128;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStagingBytes = 8 * 4096;
+    static constexpr int kTmemCols = 2 * BN;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
+};
+
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+template <int KIND>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1) gemm_low_pair_kernel(
+        const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_d,
+        LowParams prm, int group_n) {
+    using Cfg = LowPairConfig;
+    constexpr int BN = Cfg::BN;
+    constexpr int S = Cfg::kStages;
+    constexpr int CPT = BN / 2;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S * Cfg::kStageBytes + Cfg::kStagingBytes);
+    // bars[0..S) full (even block), [S..2S) empty, [2S..2S+2) accumulator full, [2S+2..2S+4) accumulator empty (even block)
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * S + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const uint32_t bar_base = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
+    auto acc_full_bar = [&](int a) { return bar_base + 8u * (2 * S + a); };
+    auto acc_empty_bar = [&](int a) { return bar_base + 8u * (2 * S + 2 + a); };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), 512); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)Cfg::kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int total_tiles = prm.tiles_m * prm.tiles_n;      // tiles of 256 x 256
+    const int kb_count = prm.k_blocks;
+    const int CHUNK_KB = prm.chunk_kb;
+    const uint32_t smem_base = smem_u32(smem);
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+    if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
+                int mi, ni;
+                tile_origin(tile, prm.tiles_m, prm.tiles_n, group_n, mi, ni);
+                const int m0 = mi * (2 * BM) + (int)rank * BM;
+                const int n0 = ni * BN + (int)rank * (BN / 2);
+                for (int kb = 0; kb < kb_count; kb++) {
+                    if (!mbar_wait_cluster(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t sa = smem_base + stage * Cfg::kStageBytes;
+                    const uint32_t leader_full = map_to_rank(full_bar(stage), 0);
+                    if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * Cfg::kStageBytes);
+                    tma_load_2d_pair(sa, &map_p, leader_full, kb * LOW_BK, m0);
+                    tma_load_2d_pair(sa + Cfg::kABytes, &map_q, leader_full, kb * LOW_BK, n0);
+                    if (++stage == S) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1 && rank == 0) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_low(2 * BM, BN, KIND);
+            const OperandForm form = operand_form(0);
+            int stage = 0; uint32_t phase = 0;
+            uint32_t partial = 0;
+            bool ok = true;
+            for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
+                for (int kb0 = 0; kb0 < kb_count && ok; kb0 += CHUNK_KB, partial++) {
+                    const int buf = partial & 1;
+                    if (!mbar_wait_cluster(acc_empty_bar(buf), ((partial >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+                    const int kb1 = kb0 + CHUNK_KB < kb_count ? kb0 + CHUNK_KB : kb_count;
+                    for (int kb = kb0; kb < kb1; kb++) {
+                        if (!mbar_wait_cluster(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint32_t pa = smem_base + stage * Cfg::kStageBytes, qa = pa + Cfg::kABytes;
+#pragma unroll
+                        for (int k4 = 0; k4 < LOW_BK / LOW_UMMA_K; k4++) {
+                            const uint32_t step = k4 * form.k8_step;
+                            umma_f16_pair(tmem_d, umma_desc(form, pa + step), umma_desc(form, qa + step), idesc, (kb != kb0 || k4 != 0) ? 1u : 0u);
+                        }
+                        umma_commit_pair(empty_bar(stage));
+                        umma_commit_pair(map_to_rank(empty_bar(stage), 1));
+                        if (++stage == S) { stage = 0; phase ^= 1u; }
+                    }
+                    if (ok) {
+                        umma_commit_pair(acc_full_bar(buf));
+                        umma_commit_pair(map_to_rank(acc_full_bar(buf), 1));
+                    }
+                }
+            }
+        }
+    }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+        const int quarter = warp & 3;
+        const int half = (warp - 4) >> 2;
+        uint32_t partial = 0;
+        bool ok = true;
+        const bool vec_ok = (prm.ldd & 3) == 0 && ((uintptr_t)prm.d & 7) == 0 && (prm.n & 3) == 0
+                            && (!prm.ep.second || ((uintptr_t)prm.ep.second & 7) == 0) && (!prm.ep.bias || ((uintptr_t)prm.ep.bias & 7) == 0);
+        for (int tile = pair; tile < total_tiles && ok; tile += pairs) {
+            int mi, ni;
+            tile_origin(tile, prm.tiles_m, prm.tiles_n, group_n, mi, ni);
+            const int m0 = mi * (2 * BM) + (int)rank * BM, n0 = ni * BN;
+            const uint2 bias_lane = prm.staged ? low_bias_lane(prm, n0 + half * CPT + lane * 4) : make_uint2(0u, 0u);
+            float sum[CPT];
+            for (int kb0 = 0; kb0 < kb_count; kb0 += CHUNK_KB, partial++) {
+                const int buf = partial & 1;
+                ok = mbar_wait_cluster(acc_full_bar(buf), (partial >> 1) & 1u, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * CPT);
+                if (kb0 == 0) {
+#pragma unroll
+                    for (int s16 = 0; s16 < CPT / 16; s16++) {
+                        float t[16];
+                        tmem_load16(taddr + (uint32_t)(s16 * 16), t);
+#pragma unroll
+                        for (int i = 0; i < 16; i++) sum[s16 * 16 + i] = t[i];
+                    }
+                } else {
+#pragma unroll
+                    for (int s16 = 0; s16 < CPT / 16; s16++) {
+                        float t[16];
+                        tmem_load16(taddr + (uint32_t)(s16 * 16), t);
+#pragma unroll
+                        for (int i = 0; i < 16; i++) sum[s16 * 16 + i] = __fadd_rn(sum[s16 * 16 + i], t[i]);
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive_cluster(map_to_rank(acc_empty_bar(buf), 0));
+            }
+            if (!ok) break;
+            if (prm.staged) {
+                low_emit_staged<KIND, CPT>(prm, &map_d, smem_base + (uint32_t)(S * Cfg::kStageBytes + (warp - 4) * 4096),
+                                           m0 + quarter * 32, n0 + half * CPT, sum, bias_lane, lane);
+                continue;
+            }
+            const int row = m0 + quarter * 32 + lane;
+            if (row < prm.m) {
+#pragma unroll
+                for (int g = 0; g < CPT / 4; g++) {
+                    const int col = n0 + half * CPT + g * 4;
+                    if (col < prm.n) low_emit4<KIND>(prm, row, col, sum[g * 4], sum[g * 4 + 1], sum[g * 4 + 2], sum[g * 4 + 3], vec_ok);
+                }
+            }
+        }
+        if (prm.staged) low_staged_drain(lane);
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    __syncwarp();
+    cluster_sync_all();     // neither block frees tensor memory or leaves while the partner may still signal it
+    if (threadIdx.x == 0 && *abort_flag) atomicOr(prm.error_word, ERR_WAIT_TIMEOUT);
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::kTmemCols) : "memory");
     }
 }
 
@@ -1663,8 +1995,31 @@ static bool make_low_map(CUtensorMap *map, int kind, const void *base, int64_t r
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// SYNAPTIK_CUDA_LOW_STAGED=0 keeps the direct stores of the 16-bit kernels (for comparisons).
+static bool low_staged_enabled() {
+    static const bool on = [] { const char *v = getenv("SYNAPTIK_CUDA_LOW_STAGED"); return !(v && v[0] == '0'); }();
+    return on;
+}
+// SYNAPTIK_CUDA_LOW_PAIR=0 keeps 16-bit products on the one-SM kernel (for comparisons).
+static bool low_pair_enabled() {
+    static const bool on = [] { const char *v = getenv("SYNAPTIK_CUDA_LOW_PAIR"); return !(v && v[0] == '0'); }();
+    return on;
+}
+
+// Tensor map of the result for the staged write-out: boxes of 32 rows x 64 columns, 128-byte swizzle.
+static bool make_low_store_map(CUtensorMap *map, const void *base, int64_t rows, int64_t cols, int64_t pitch) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)pitch * 2};
+    cuuint32_t box[2] = {64, 32};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void *>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int BN, int KIND>
-static cudaError_t launch_low(cudaStream_t s, int grid, const CUtensorMap &p, const CUtensorMap &q, const LowParams &prm) {
+static cudaError_t launch_low(cudaStream_t s, int grid, const CUtensorMap &p, const CUtensorMap &q, const CUtensorMap &d, const LowParams &prm) {
     using Cfg = LowConfig<BN>;
     cudaFuncAttributes attr;
     cudaError_t e = cudaFuncGetAttributes(&attr, gemm_low_kernel<BN, KIND>);
@@ -1672,7 +2027,20 @@ static cudaError_t launch_low(cudaStream_t s, int grid, const CUtensorMap &p, co
     if (attr.numRegs * PROMOTED_THREADS < 128 * 72 + 256 * 216) return cudaErrorLaunchOutOfResources;
     e = cudaFuncSetAttribute(gemm_low_kernel<BN, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
-    gemm_low_kernel<BN, KIND><<<grid, PROMOTED_THREADS, Cfg::kSmemBytes, s>>>(p, q, prm);
+    gemm_low_kernel<BN, KIND><<<grid, PROMOTED_THREADS, Cfg::kSmemBytes, s>>>(p, q, d, prm);
+    return cudaGetLastError();
+}
+
+template <int KIND>
+static cudaError_t launch_low_pair(cudaStream_t s, int grid, const CUtensorMap &p, const CUtensorMap &q, const CUtensorMap &d, const LowParams &prm, int group_n) {
+    using Cfg = LowPairConfig;
+    cudaFuncAttributes attr;
+    cudaError_t e = cudaFuncGetAttributes(&attr, gemm_low_pair_kernel<KIND>);
+    if (e != cudaSuccess) return e;
+    if (attr.numRegs * PROMOTED_THREADS < 128 * 72 + 256 * 216) return cudaErrorLaunchOutOfResources;
+    e = cudaFuncSetAttribute(gemm_low_pair_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    gemm_low_pair_kernel<KIND><<<grid, PROMOTED_THREADS, Cfg::kSmemBytes, s>>>(p, q, d, prm, group_n);
     return cudaGetLastError();
 }
 
@@ -1681,17 +2049,27 @@ cudaError_t low_gemm_launch(cudaStream_t s, int kind, int sm_count, int64_t m, i
                             int chunk_steps, int *error_word) {
     if ((kind != 1 && kind != 2) || !low_gemm_supported(m, n, k, lda, ldw, ldc)) return cudaErrorInvalidValue;
     if (((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return cudaErrorInvalidValue;
-    // tile width as for the FP32 products: least (waves x width), narrower tiles handicapped a little
+    // Kernel and tile width by least (waves x width x cost per column).  A one-SM block loads and reads
+    // (128 + BN) x 128 bytes of shared memory per 2 BN clocks of MMA, which narrow tiles cannot sustain; measured
+    // clocks per tile column relative to the two-SM kernel on K = 4096 products: 1.2 (BN = 256), 1.8 (128), about
+    // 2.5 (64).
     auto cost = [&](int bn) {
         int64_t t = ((m + BM - 1) / BM) * ((n + bn - 1) / bn);
         int64_t waves = (t + sm_count - 1) / sm_count;
-        return (double)waves * bn * (bn == 256 ? 1.0 : (bn == 128 ? 1.05 : 1.15));
+        return (double)waves * bn * (bn == 256 ? 1.2 : (bn == 128 ? 1.8 : 2.5));
     };
     int bn = 64;
     if (n >= 96 && cost(128) <= cost(bn)) bn = 128;
     if (n >= 192 && cost(256) <= cost(bn)) bn = 256;
+    const int pairs = sm_count / 2;
+    const int64_t pair_tiles = ((m + 2 * BM - 1) / (2 * BM)) * ((n + 255) / 256);
+    bool pair = false;
+    if (low_pair_enabled() && pairs > 0 && m > BM && n >= 192) {
+        const double pair_cost = (double)((pair_tiles + pairs - 1) / pairs) * 256.0;
+        if (pair_cost <= cost(bn)) { pair = true; bn = 256; }
+    }
     CUtensorMap map_p, map_q;
-    if (!make_low_map(&map_p, kind, a, m, k, lda, BM) || !make_low_map(&map_q, kind, w, n, k, ldw, bn)) return cudaErrorInvalidValue;
+    if (!make_low_map(&map_p, kind, a, m, k, lda, BM) || !make_low_map(&map_q, kind, w, n, k, ldw, pair ? bn / 2 : bn)) return cudaErrorInvalidValue;
     LowParams prm;
     prm.d = (uint16_t *)c; prm.ldd = ldc; prm.m = (int)m; prm.n = (int)n;
     prm.k_blocks = (int)((k + LOW_BK - 1) / LOW_BK);
@@ -1704,10 +2082,23 @@ cudaError_t low_gemm_launch(cudaStream_t s, int kind, int sm_count, int64_t m, i
     prm.chunk_kb = chunk_steps / LOW_BK < 1 ? 1 : chunk_steps / LOW_BK;
     prm.ep = LowEpilogue{(const uint16_t *)bias, act, (uint16_t *)second};
     prm.error_word = error_word;
+    // write-out through shared memory and TMA stores when the result can be described by a tensor map
+    // (16-byte pitch and base) and only one tensor is written
+    CUtensorMap map_d;
+    prm.staged = low_staged_enabled() && bn >= 128 && !second && (ldc & 7) == 0 && ((uintptr_t)c & 15) == 0
+                 && make_low_store_map(&map_d, c, m, n, ldc);
+    if (!prm.staged) map_d = map_p;         // unused then
+    if (pair) {
+        prm.tiles_m = (int)((m + 2 * BM - 1) / (2 * BM));
+        const int groups = (prm.tiles_n + 7) / 8;
+        const int group_n = (prm.tiles_n + groups - 1) / groups;
+        const int grid = 2 * (int)(pair_tiles < pairs ? pair_tiles : pairs);
+        return kind == 1 ? launch_low_pair<1>(s, grid, map_p, map_q, map_d, prm, group_n) : launch_low_pair<2>(s, grid, map_p, map_q, map_d, prm, group_n);
+    }
     const int64_t tiles = (int64_t)prm.tiles_m * prm.tiles_n;
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
-    if (kind == 1) return bn == 256 ? launch_low<256, 1>(s, grid, map_p, map_q, prm) : bn == 128 ? launch_low<128, 1>(s, grid, map_p, map_q, prm) : launch_low<64, 1>(s, grid, map_p, map_q, prm);
-    return bn == 256 ? launch_low<256, 2>(s, grid, map_p, map_q, prm) : bn == 128 ? launch_low<128, 2>(s, grid, map_p, map_q, prm) : launch_low<64, 2>(s, grid, map_p, map_q, prm);
+    if (kind == 1) return bn == 256 ? launch_low<256, 1>(s, grid, map_p, map_q, map_d, prm) : bn == 128 ? launch_low<128, 1>(s, grid, map_p, map_q, map_d, prm) : launch_low<64, 1>(s, grid, map_p, map_q, map_d, prm);
+    return bn == 256 ? launch_low<256, 2>(s, grid, map_p, map_q, map_d, prm) : bn == 128 ? launch_low<128, 2>(s, grid, map_p, map_q, map_d, prm) : launch_low<64, 2>(s, grid, map_p, map_q, map_d, prm);
 }
 
 }  // namespace kern
