@@ -27,6 +27,9 @@ dist.broadcast_object_list(holder, src=0)
 comm = native.Comm(ctx, world, rank, holder[0]) if world > 1 else None
 dims, batch = [784, 512, 256, 10], 1024
 ctx.set_option("gemm_engine", 2)
+if os.environ.get("SYN_CHUNK"):
+    ctx.set_option("gemm_chunk", int(os.environ["SYN_CHUNK"]))
+tag = os.environ.get("SYN_TAG") or f"w{world}"
 model = nn.Model(dims, ctx, seed=9, comm=comm, world_size=world)
 model.configure_training("ce", nn.Adam(1e-3))
 rng = np.random.default_rng(5)
@@ -36,8 +39,8 @@ rows = batch // world
 # before any step: the all-reduced gradients of the ranks' slices are the gradient of the whole batch
 _, first_gradients = model.gradients(x[rank * rows:(rank + 1) * rows], labels[rank * rows:(rank + 1) * rows])
 if rank == 0:
-    np.save(os.environ["SYN_OUT"] + f".w{world}.start.npy", np.concatenate([p.reshape(-1) for p in model.parameters()]))
-    np.save(os.environ["SYN_OUT"] + f".w{world}.grads.npy", np.concatenate([g.reshape(-1) for g in first_gradients]))
+    np.save(os.environ["SYN_OUT"] + f".{tag}.start.npy", np.concatenate([p.reshape(-1) for p in model.parameters()]))
+    np.save(os.environ["SYN_OUT"] + f".{tag}.grads.npy", np.concatenate([g.reshape(-1) for g in first_gradients]))
 losses, history, same = [], [], True
 for step in range(20):
     losses.append(model.train(x[rank * rows:(rank + 1) * rows], labels[rank * rows:(rank + 1) * rows]))
@@ -50,16 +53,16 @@ for step in range(20):
 l = torch.tensor(losses, dtype=torch.float64, device="cuda")
 dist.all_reduce(l)
 if rank == 0:
-    np.save(os.environ["SYN_OUT"] + f".w{world}.npy", np.stack(history))
-    json.dump({"replicas_identical": same, "losses": (l / world).tolist()}, open(os.environ["SYN_OUT"] + f".w{world}.json", "w"))
+    np.save(os.environ["SYN_OUT"] + f".{tag}.npy", np.stack(history))
+    json.dump({"replicas_identical": same, "losses": (l / world).tolist()}, open(os.environ["SYN_OUT"] + f".{tag}.json", "w"))
 model.close()
 if comm is not None: comm.close()
 dist.destroy_process_group()
 '''
 
 
-def _run(world, out, port):
-    env = dict(os.environ, SYN_ROOT=ROOT, SYN_OUT=out, NCCL_NVLS_ENABLE="0")
+def _run(world, out, port, tag="", chunk=""):
+    env = dict(os.environ, SYN_ROOT=ROOT, SYN_OUT=out, NCCL_NVLS_ENABLE="0", SYN_TAG=tag, SYN_CHUNK=chunk)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), "-c", WORKER]
     script = out + ".worker.py"
@@ -79,6 +82,14 @@ def test_ranks_match_one_rank_after_every_step(tmp_path):
     one = np.load(out + ".w1.npy")                      # [steps, parameters]
     start = np.load(out + ".w1.start.npy")
     info1 = json.load(open(out + ".w1.json"))
+    # what a rounding-level change does to 20 Adam steps, measured rather than assumed: the same single rank with
+    # FP32 partial sums of 256 instead of 512 contraction steps (the weight gradients then are four partial sums
+    # of 256 rows, the very split four ranks make)
+    _run(1, out, 29733, tag="reordered", chunk="256")
+    reordered = np.load(out + ".reordered.npy")
+    info_reordered = json.load(open(out + ".reordered.json"))
+    floor = [trajectory_distance(reordered[step], one[step], start, 1e-3, step + 1) for step in range(one.shape[0])]
+    report("data_parallel_rounding_floor", floor)
     for world in [w for w in (2, 4, 8) if w <= available]:
         _run(world, out, 29731 + 2 * world)
         many = np.load(out + f".w{world}.npy")
@@ -95,8 +106,19 @@ def test_ranks_match_one_rank_after_every_step(tmp_path):
         for step in range(one.shape[0]):
             d = trajectory_distance(many[step], one[step], start, 1e-3, step + 1)
             table.append(d)
-            # measured on 2 ranks: identical to 5e-8 after 20 steps (the ranks' forward passes are the single rank's
-            # bit for bit; only the sums over the batch are split)
-            assert d["relative_l2"] <= 0.01 and d["share_apart"] <= 1e-3 and d["mean"] <= 2e-6 * (step + 1) and d["max"] <= 1e-3, (world, step, d)
+            # measured on 2 ranks: identical to 5e-8 after 20 steps (the forward passes are the single rank's bit for
+            # bit, and two partial sums of 512 rows are exactly the single rank's two promoted partials).  More
+            # ranks round the weight gradients differently, entries whose gradient is near zero take Adam steps of
+            # opposite sign, the ReLU gates follow, and the trajectories part as fast as the reordered single rank's
+            # does (measured on 4 ranks: relative L2 2.3e-3 at step 7, 2.4e-2 at step 14): bounded by three times that
+            f = floor[step]
+            if world == 2:
+                ok = d["relative_l2"] <= 0.01 and d["share_apart"] <= 1e-3 and d["mean"] <= 2e-6 * (step + 1) and d["max"] <= 1e-3
+            else:
+                ok = d["relative_l2"] <= 3 * f["relative_l2"] + 0.01 and d["share_apart"] <= 3 * f["share_apart"] + 1e-3 \
+                    and d["mean"] <= 3 * f["mean"] + 2e-6 * (step + 1) and d["max"] <= 3 * f["max"] + 1e-3
+            assert ok, (world, step, d, f)
         report(f"data_parallel_world{world}", table)
-        assert np.allclose(info1["losses"], info["losses"], rtol=2e-4), world
+        l1, ln = np.asarray(info1["losses"]), np.asarray(info["losses"])
+        slack = 0.0 if world == 2 else 3 * np.abs(np.asarray(info_reordered["losses"]) - l1).max()
+        assert np.all(np.abs(ln - l1) <= 2e-4 * np.abs(l1) + slack), (world, np.abs(ln - l1).max(), slack)
