@@ -64,9 +64,11 @@ SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_release(void *context);
 /* Named integer options.  "gemm_engine": 0 = automatic (tensor cores for large products, exact
  * sequential CUDA-core kernel for small ones), 1 = always the exact CUDA-core kernel,
  * 2 = tensor cores whenever the shape allows.  "time_steps": 1 = bracket every step of later runs
- * with CUDA events (see synaptik_cuda_executable_step_timings).  "fused_planes": 0 = executables
- * created afterwards split GEMM operands in separate passes instead of in the producing GEMM's
- * epilogue (default 1; only used while "gemm_promote" is 0).  "gemm_promote": 1 (default) = the
+ * with CUDA events (see synaptik_cuda_executable_step_timings).  "fused_planes": whether a GEMM whose
+ * result a later GEMM reads writes that operand's hi / lo planes from its own epilogue instead of leaving
+ * them to a separate pass; 0 = never, 1 (default) = where it pays (two-SM products, whose write-out goes
+ * through shared memory and TMA stores, and one-accumulator products with K >= 2048), 2 = every product
+ * with K >= 2048, 3 = every product.  Results do not depend on it.  "gemm_promote": 1 (default) = the
  * tensor-core GEMM keeps only short partial sums (256 or 512 contraction steps) in tensor memory and
  * adds them into round-to-nearest FP32 register sums; 0 = one tensor-memory accumulator over the
  * whole contraction (faster epilogue, error grows with K).  "gemm_chunk": contraction steps per
@@ -80,8 +82,7 @@ SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_release(void *context);
  * "gemm_dynamic": 1 (default) = executables created afterwards let the two-SM kernel's block pairs take
  * their tiles one by one from a counter, so a pair whose SMs were held by another kernel (an
  * all-reduce on the communication stream) just takes fewer tiles; 0 = fixed round-robin assignment.
- * The result does not depend on the assignment.  "fused_planes": 2 = write operand planes from the
- * producing GEMM's epilogue even while "gemm_promote" is 1.  "comm_timeout_ms" (default 30000): how
+ * The result does not depend on the assignment.  "comm_timeout_ms" (default 30000): how
  * long the host waits, in any call that returns results, for work that has a collective in front of it
  * before it gives up, aborts the communicator and returns COMM_FAILED.  Unknown names return
  * INVALID_ARGUMENT. */

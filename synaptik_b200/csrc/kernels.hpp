@@ -170,6 +170,9 @@ TensorCoreGemm *tc_gemm_prepare(const TcOperand &p, const TcOperand &q, int64_t 
 void tc_gemm_release(TensorCoreGemm *g);
 int64_t tc_gemm_workspace_floats(const TensorCoreGemm *g);
 int tc_gemm_launches(const TensorCoreGemm *g);
+// The product's write-out goes through shared memory and TMA stores (two-SM kernel, unsliced, 16-byte rows)
+// when its result arrays are 16-byte aligned: further arrays written from the epilogue are then cheap.
+bool tc_gemm_staged_shape(const TensorCoreGemm *g);
 // unit_counter (optional, two-SM products only): a device int that is zero when the kernel starts; the
 // pairs then take their tiles from it one by one instead of by a fixed assignment.
 cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, int64_t ldd, const GemmEpilogue &ep, float *workspace,

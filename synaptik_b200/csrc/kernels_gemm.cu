@@ -776,16 +776,138 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
 }
 
-template <int BN, bool SLICED, bool DYNAMIC, bool GENERAL>
+// ---- write-out of the two-SM kernel through shared memory and TMA stores ----------------------------
+// An epilogue thread owns one result row, so direct stores of a warp touch 32 rows, 16 bytes each, and every
+// further array written from the epilogue (a second result, the hi / lo operand planes of the result) costs as
+// much again; with the FP32 promotion the write-out has two partial sums' time (about 49 000 clocks at K = 4096)
+// before the tensor core waits for it.  Staged form: a warp finishes 32 columns of its 32 rows at a time in
+// registers, writes them as one 128-byte-swizzled box of 32 x 32 floats to its 4 KB of shared memory and one
+// lane hands the box to a TMA store, per array; the store also clips rows and columns past the matrix.
+struct StoreMaps { CUtensorMap d, second, hi, lo; };
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+// Before a block leaves: its stores have completed.
+__device__ __forceinline__ void staged_drain(int lane) {
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    __syncwarp();
+}
+constexpr int STAGING_BYTES = 8 * 4096;     // one box per epilogue warp
+
+// `sum` holds the warp's CPT columns of this thread's row and is finished in place, 32 columns at a time.
+// `bias_lane`: bias of columns col0 + 4 lane .. + 3 (fetched before the accumulator was waited for).
+template <int CPT, bool GENERAL>
+__device__ __forceinline__ void epilogue_emit_staged(const TcParams &prm, const StoreMaps &maps, uint32_t stage, int row0, int col0,
+                                                     float (&sum)[CPT], float4 bias_lane, int lane) {
+    const int row = row0 + lane;
+    const bool row_ok = row < prm.m;
+    const bool rows_left = row0 < prm.m;                            // warp-uniform
+    const int width = prm.nhi ? (int)prm.nld : prm.n;               // planes carry zero padding up to their pitch
+    const uint32_t mine = stage + (uint32_t)(lane * 128);
+    const uint32_t twist = (uint32_t)(lane & 7);
+    auto put4 = [&](int j, float a, float b, float c, float d) {     // 16-byte chunk j of this lane's row of the box
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(mine + ((((uint32_t)j) ^ twist) << 4)), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+    };
+    auto reclaim = [&]() {          // the previous box has been read out of shared memory
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        __syncwarp();
+    };
+    auto ship = [&](const CUtensorMap *map, int c0) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0 && rows_left) {
+            tma_store_2d(map, stage, c0, row0);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+    };
+#pragma unroll
+    for (int b = 0; b < CPT / 32; b++) {
+        const int c0 = col0 + b * 32;
+        if (c0 >= width) break;                                     // warp-uniform
+        float *v = &sum[b * 32];
+        float4 gate[8];
+        if (prm.gate) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int col = c0 + 4 * j;
+                gate[j] = (row_ok && col < prm.n) ? *reinterpret_cast<const float4 *>(prm.gate + (int64_t)row * prm.n + col) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+        }
+        reclaim();
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int col = c0 + 4 * j;
+            float z[4] = {v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]};
+            if (prm.bias) {
+                const int src = b * 8 + j;
+                z[0] = __fadd_rn(z[0], __shfl_sync(0xffffffffu, bias_lane.x, src));
+                z[1] = __fadd_rn(z[1], __shfl_sync(0xffffffffu, bias_lane.y, src));
+                z[2] = __fadd_rn(z[2], __shfl_sync(0xffffffffu, bias_lane.z, src));
+                z[3] = __fadd_rn(z[3], __shfl_sync(0xffffffffu, bias_lane.w, src));
+            }
+            if (prm.gate) {
+                z[0] = gate[j].x > 0.0f ? z[0] : 0.0f; z[1] = gate[j].y > 0.0f ? z[1] : 0.0f;
+                z[2] = gate[j].z > 0.0f ? z[2] : 0.0f; z[3] = gate[j].w > 0.0f ? z[3] : 0.0f;
+            }
+            float y[4];
+            if (GENERAL) {
+                const float4 a = activate4(prm.act, make_float4(z[0], z[1], z[2], z[3]));
+                y[0] = a.x; y[1] = a.y; y[2] = a.z; y[3] = a.w;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; e++) y[e] = prm.act ? relu_value(z[e]) : z[e];
+            }
+            if (prm.second) put4(j, z[0], z[1], z[2], z[3]);
+            else put4(j, y[0], y[1], y[2], y[3]);
+            const bool inside = col < prm.n;                        // n is a multiple of 4 here
+#pragma unroll
+            for (int e = 0; e < 4; e++) v[4 * j + e] = inside ? y[e] : 0.0f;
+        }
+        if (c0 < prm.n) {
+            ship(&maps.d, c0);
+            if (prm.second) {
+                reclaim();
+#pragma unroll
+                for (int j = 0; j < 8; j++) put4(j, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                ship(&maps.second, c0);
+            }
+        }
+        if (prm.nhi) {
+            reclaim();
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                float h[4], l[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) split_value(v[4 * j + e], h[e], l[e]);
+                put4(j, h[0], h[1], h[2], h[3]);
+            }
+            ship(&maps.hi, c0);
+            reclaim();
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                float h[4], l[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) split_value(v[4 * j + e], h[e], l[e]);
+                put4(j, l[0], l[1], l[2], l[3]);
+            }
+            ship(&maps.lo, c0);
+        }
+    }
+}
+
+template <int BN, bool SLICED, bool DYNAMIC, bool GENERAL, bool STAGED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1) gemm_tf32x3_pair_kernel(
         const __grid_constant__ CUtensorMap map_p_hi, const __grid_constant__ CUtensorMap map_p_lo,
-        const __grid_constant__ CUtensorMap map_q_hi, const __grid_constant__ CUtensorMap map_q_lo, TcParams prm, SliceParams slc) {
+        const __grid_constant__ CUtensorMap map_q_hi, const __grid_constant__ CUtensorMap map_q_lo,
+        const __grid_constant__ StoreMaps stores, TcParams prm, SliceParams slc) {
+    static_assert(!(STAGED && SLICED), "a slice writes its raw partial product directly");
     using Cfg = PairConfig<BN>;
     constexpr int S = Cfg::kStages;
     constexpr int CPT = BN / 2;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S * Cfg::kStageBytes);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S * Cfg::kStageBytes + (STAGED ? STAGING_BYTES : 0));
     // bars[0..S) full, [S..2S) empty, [2S..2S+2) accumulator full, [2S+2..2S+4) accumulator empty,
     // [2S+4..2S+4+R) unit published, [2S+4+R..2S+4+2R) unit slot free (used in the even block)
     constexpr int R = 4;                    // depth of the ring of published unit numbers
@@ -956,6 +1078,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1)
             const int m0 = mi * (2 * BM) + (int)rank * BM, n0 = ni * BN;
             const int kb_first = slice * kb_per_slice;
             const int kb_last = (SLICED && kb_first + kb_per_slice < kb_count) ? kb_first + kb_per_slice : kb_count;
+            float4 bias_lane = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if constexpr (STAGED) {
+                const int bias_col = n0 + half * CPT + lane * 4;
+                if (prm.bias && bias_col < prm.n) bias_lane = *reinterpret_cast<const float4 *>(prm.bias + bias_col);
+            }
             float sum[CPT];
             for (int kb0 = kb_first; kb0 < kb_last; kb0 += CHUNK_KB, partial++) {
                 const int buf = partial & 1;
@@ -985,6 +1112,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1)
                 mbar_arrive_cluster(map_to_rank(acc_empty_bar(buf), 0));
             }
             if (!ok) break;
+            if constexpr (STAGED) {
+                epilogue_emit_staged<CPT, GENERAL>(prm, stores, smem_base + (uint32_t)(S * Cfg::kStageBytes + (warp - 4) * 4096),
+                                                   m0 + quarter * 32, n0 + half * CPT, sum, bias_lane, lane);
+                continue;
+            }
             const int row = m0 + quarter * 32 + lane;
             const bool row_ok = row < prm.m;
             if constexpr (SLICED) {
@@ -1009,6 +1141,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1)
                 }
             }
         }
+        if constexpr (STAGED) staged_drain(lane);
     }
 
     tc_fence_before();
@@ -1339,10 +1472,6 @@ __device__ __forceinline__ uint4 low_finish8(const LowParams &prm, int group, co
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
-}
-
 // One warp's 32 rows x CPT columns of a finished tile, 64 columns at a time.  `stage` is this warp's 4 KB of
 // shared memory (1024-byte aligned): one box of 32 rows x 128 bytes, 16-byte chunk j of row r at chunk
 // j ^ (r & 7) as the 128-byte swizzle of the store's tensor map expects (and conflict-free for a thread per row).
@@ -1371,11 +1500,6 @@ __device__ __forceinline__ void low_emit_staged(const LowParams &prm, const CUte
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
     }
-}
-// Before a block leaves: its stores have completed.
-__device__ __forceinline__ void low_staged_drain(int lane) {
-    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-    __syncwarp();
 }
 
 template <int BN, int KIND>
@@ -1533,7 +1657,7 @@ __global__ void __launch_bounds__(PROMOTED_THREADS, 1) gemm_low_kernel(
                 }
             }
         }
-        if (prm.staged) low_staged_drain(lane);
+        if (prm.staged) staged_drain(lane);
     }
 
     tc_fence_before();
@@ -1729,7 +1853,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PROMOTED_THREADS, 1)
                 }
             }
         }
-        if (prm.staged) low_staged_drain(lane);
+        if (prm.staged) staged_drain(lane);
     }
 
     tc_fence_before();
@@ -1801,7 +1925,42 @@ struct TensorCoreGemm {
     int p_mn, q_mn;
     int slices, kb_per_slice; int64_t slice_ld;
     int group_n;
+    // tensor maps of the staged write-out, encoded when the result arrays change (they rarely do)
+    mutable StoreMaps stores;
+    mutable const void *stored_for[4] = {nullptr, nullptr, nullptr, nullptr};
+    mutable int64_t stored_pitch[2] = {0, 0};
 };
+
+// SYNAPTIK_CUDA_STAGED=0 keeps the direct stores of the two-SM FP32 kernel (for comparisons).
+static bool staged_enabled() {
+    static const bool on = [] { const char *v = getenv("SYNAPTIK_CUDA_STAGED"); return !(v && v[0] == '0'); }();
+    return on;
+}
+// Boxes of 32 rows x 32 floats, 128-byte swizzle, over a [rows, cols] FP32 array.
+static bool make_store_map(CUtensorMap *map, const float *base, int64_t rows, int64_t cols, int64_t pitch) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)pitch * 4};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+// Whether this launch can write out through TMA stores, and its tensor maps if so.
+static bool prepare_stores(const TensorCoreGemm *g, const TcParams &prm) {
+    if (!staged_enabled() || !g->pair || g->slices > 1 || (prm.n & 3) || (prm.ldd & 3) || ((uintptr_t)prm.d & 15)) return false;
+    if ((prm.bias && ((uintptr_t)prm.bias & 15)) || (prm.gate && ((uintptr_t)prm.gate & 15)) || (prm.second && ((uintptr_t)prm.second & 15))) return false;
+    if (prm.nhi && ((prm.nld & 3) || ((uintptr_t)prm.nhi & 15) || ((uintptr_t)prm.nlo & 15))) return false;
+    const void *now[4] = {prm.d, prm.second, prm.nhi, prm.nlo};
+    if (!memcmp(now, g->stored_for, sizeof(now)) && g->stored_pitch[0] == prm.ldd && g->stored_pitch[1] == prm.nld) return true;
+    if (!make_store_map(&g->stores.d, prm.d, prm.m, prm.n, prm.ldd)) return false;
+    if (prm.second && !make_store_map(&g->stores.second, prm.second, prm.m, prm.n, prm.n)) return false;
+    if (prm.nhi && (!make_store_map(&g->stores.hi, prm.nhi, prm.m, prm.nld, prm.nld) || !make_store_map(&g->stores.lo, prm.nlo, prm.m, prm.nld, prm.nld))) return false;
+    memcpy(g->stored_for, now, sizeof(now));
+    g->stored_pitch[0] = prm.ldd; g->stored_pitch[1] = prm.nld;
+    return true;
+}
 
 TensorCoreGemm *tc_gemm_prepare(const TcOperand &p, const TcOperand &q, int64_t m, int64_t n, int64_t k,
                                 int sm_count, int promote, int *status) {
@@ -1904,20 +2063,23 @@ static cudaError_t launch_tc(cudaStream_t s, const TensorCoreGemm *g, const TcPa
     if (g->pair) {
         if constexpr (BN >= 128) {
             using Pair = PairConfig<BN>;
+            const bool staged = prepare_stores(g, prm);
             auto launch_pair = [&](auto kernel) -> cudaError_t {
                 // per-device attributes: set on every launch so each GPU of the process has them
                 cudaFuncAttributes attr;
                 cudaError_t pe = cudaFuncGetAttributes(&attr, kernel);
                 if (pe != cudaSuccess) return pe;
                 if (attr.numRegs * PROMOTED_THREADS < 128 * 72 + 256 * 216) return cudaErrorLaunchOutOfResources;
-                pe = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Pair::kSmemBytes);
+                const int smem_bytes = Pair::kSmemBytes + (staged ? STAGING_BYTES : 0);
+                pe = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
                 if (pe != cudaSuccess) return pe;
-                kernel<<<g->grid, PROMOTED_THREADS, Pair::kSmemBytes, s>>>(g->p_hi, g->p_lo, g->q_hi, g->q_lo, prm, slc);
+                kernel<<<g->grid, PROMOTED_THREADS, smem_bytes, s>>>(g->p_hi, g->p_lo, g->q_hi, g->q_lo, g->stores, prm, slc);
                 return cudaSuccess;
             };
             // a sliced product has no epilogue work, so no activation either
-            if (g->slices > 1) e = slc.unit_counter ? launch_pair(gemm_tf32x3_pair_kernel<BN, true, true, false>) : launch_pair(gemm_tf32x3_pair_kernel<BN, true, false, false>);
-            else e = slc.unit_counter ? launch_pair(gemm_tf32x3_pair_kernel<BN, false, true, GENERAL>) : launch_pair(gemm_tf32x3_pair_kernel<BN, false, false, GENERAL>);
+            if (g->slices > 1) e = slc.unit_counter ? launch_pair(gemm_tf32x3_pair_kernel<BN, true, true, false, false>) : launch_pair(gemm_tf32x3_pair_kernel<BN, true, false, false, false>);
+            else if (staged) e = slc.unit_counter ? launch_pair(gemm_tf32x3_pair_kernel<BN, false, true, GENERAL, true>) : launch_pair(gemm_tf32x3_pair_kernel<BN, false, false, GENERAL, true>);
+            else e = slc.unit_counter ? launch_pair(gemm_tf32x3_pair_kernel<BN, false, true, GENERAL, false>) : launch_pair(gemm_tf32x3_pair_kernel<BN, false, false, GENERAL, false>);
             if (e != cudaSuccess) return e;
         } else return cudaErrorInvalidValue;
     } else if (g->promote) {
@@ -1964,6 +2126,7 @@ cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, in
     return cudaGetLastError();
 }
 int tc_gemm_launches(const TensorCoreGemm *g) { return g->slices > 1 ? 2 : 1; }
+bool tc_gemm_staged_shape(const TensorCoreGemm *g) { return staged_enabled() && g->pair && g->slices == 1 && (g->n & 3) == 0; }
 
 // ---- 16-bit storage ------------------------------------------------------------------------------
 cudaError_t gemm_exact_low(cudaStream_t s, int kind, int64_t m, int64_t n, int64_t k, const void *a, int64_t a_ms, int64_t a_ks,

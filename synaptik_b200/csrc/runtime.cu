@@ -453,13 +453,16 @@ int32_t prepare_executable(Executable *x) {
     for (size_t i = 0; i < plan.steps.size(); i++) {
         const Step &st = plan.steps[i];
         StepExec &se = x->exec[i];
-        // worth it only when the producer's main loop is long enough to hide the extra stores behind
-        // the next tile (measured: a K = 784 producer doubles in time, K = 4096 producers gain)
-        // (with FP32 promotion the epilogue warps also add the partial sums, and the extra stores bought
-        // nothing: fused_planes = 2 asks for them all the same.)  A product whose contraction is split into
-        // slices has no epilogue of its own: its planes are written by the ordinary split pass.
-        if (st.kind != StepKind::GEMM || st.engine != GemmEngine::TENSOR_CORE || !se.tc || se.swapped || !ctx->fused_planes || st.k < 2048) continue;
-        if (ctx->gemm_promote && ctx->fused_planes < 2) continue;
+        // fused_planes 1 (default): where it pays.  That is every two-SM product with the staged write-out
+        // (measured on the training step, cycle counts of all launches: 79.3 M clocks per step against 81.7 with
+        // separate split passes) and, on the other kernels, one-accumulator products with a long main loop
+        // (direct stores: a K = 784 producer doubled in time, K = 4096 producers gained; with FP32 promotion
+        // the extra direct stores bought nothing).  2: every producer with K >= 2048; 3: every producer.
+        // A product whose contraction is split into slices has no epilogue of its own: its planes are
+        // written by the ordinary split pass.
+        if (st.kind != StepKind::GEMM || st.engine != GemmEngine::TENSOR_CORE || !se.tc || se.swapped || !ctx->fused_planes) continue;
+        if (ctx->fused_planes == 1 && !kern::tc_gemm_staged_shape(se.tc) && (ctx->gemm_promote || st.k < 2048)) continue;
+        if (ctx->fused_planes == 2 && st.k < 2048) continue;
         if (kern::tc_gemm_launches(se.tc) > 1) continue;
         const View &u = plan.views[st.out2 >= 0 ? st.out2 : st.out];
         if (u.shape.size() != 2 || !u.dense()) continue;
@@ -831,7 +834,7 @@ int32_t synaptik_cuda_context_set_option(void *context, const char *name, int64_
     if (!strcmp(name, "gemm_pair")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->gemm_pair = (int)value; return OK; }
     if (!strcmp(name, "gemm_chunk")) { if (value < 0 || value > 4096 || value % 32) return INVALID_ARGUMENT; ctx->gemm_chunk = (int)value; return OK; }
     if (!strcmp(name, "gemm_promote")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->gemm_promote = (int)value; return OK; }
-    if (!strcmp(name, "fused_planes")) { if (value < 0 || value > 2) return INVALID_ARGUMENT; ctx->fused_planes = (int)value; return OK; }
+    if (!strcmp(name, "fused_planes")) { if (value < 0 || value > 3) return INVALID_ARGUMENT; ctx->fused_planes = (int)value; return OK; }
     if (!strcmp(name, "comm_timeout_ms")) { if (value < 1 || value > 3600000) return INVALID_ARGUMENT; ctx->comm_timeout_ms = value; return OK; }
     if (!strcmp(name, "time_steps")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->time_steps = (int)value; return OK; }
     return INVALID_ARGUMENT;
