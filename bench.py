@@ -48,9 +48,10 @@ DATA_BLOCK = 1024       # rows per independently seeded block of the synthetic b
 # GPU (this build) and at 65536 rows (the same main loop and tile order).  The weight planes are read once per
 # group of row bands whatever the batch, so traffic does not grow in proportion to the rows; other row counts
 # are interpolated between the two captures.
-NCU_GEMM_TRAFFIC = {8192: 8.955e9 / 8, 65536: (62.5e9 + 6.9e9) / 8}
-# FP32 operands read once and results written once, per launch (mean over the same eight launches)
-ALGORITHMIC_GEMM_BYTES = {8192: 2.628e9 / 8, 65536: 28.7e9 / 8}
+NCU_GEMM_TRAFFIC = {8192: 9.912e9 / 8, 65536: (66.31e9 + 14.58e9) / 8}
+# FP32 operands read once, results written once and the hi / lo planes that four of the launches write for the
+# products that read their results, per launch (mean over the same eight launches)
+ALGORITHMIC_GEMM_BYTES = {8192: (2.628e9 + 1.074e9) / 8, 65536: (28.7e9 + 8.59e9) / 8}
 TENSOR_FLOP_PER_CLOCK_PER_SM = 4096.0       # dense TF32 multiply-add throughput of one SM's tensor pipe (2048 FMA per clock)
 SM_COUNT = 148
 
