@@ -78,7 +78,9 @@ SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_release(void *context);
  * at least 256 rows use two-SM tiles (clusters of two blocks, tcgen05 cta_group::2); 0 = one-SM tiles
  * only.  "gemm_slices": 1 (default) = a two-SM product without epilogue work (a weight gradient) may
  * split its contraction into up to four slices when that shortens the last wave of the persistent
- * grid; the slices' partial products are added in ascending order by a second kernel; 0 = never.
+ * grid; the slices' partial products are added in ascending order by a second kernel; 0 = never;
+ * 2 = also cut a product of one wave or less into at least two slices, so that it has units to spare
+ * when another kernel (an all-reduce) holds some SMs.
  * "gemm_dynamic": 1 (default) = executables created afterwards let the two-SM kernel's block pairs take
  * their tiles one by one from a counter, so a pair whose SMs were held by another kernel (an
  * all-reduce on the communication stream) just takes fewer tiles; 0 = fixed round-robin assignment.

@@ -1966,6 +1966,7 @@ TensorCoreGemm *tc_gemm_prepare(const TcOperand &p, const TcOperand &q, int64_t 
                                 int sm_count, int promote, int *status) {
     const int pair_requested = (promote >> 1) & 1;      // bit 1 of the mode: two-SM tiles
     const int may_slice = (promote >> 2) & 1;           // bit 2: the result has no epilogue, the contraction may be split
+    const int fine_units = (promote >> 3) & 1;          // bit 3: a product of one wave or less is cut into at least two slices
     const int chunk_requested = (promote >> 8) & 0xff;  // bits 8-15: k-blocks per tensor-memory partial sum, 0 = default
     promote &= 1;
     *status = OK;
@@ -2019,9 +2020,12 @@ TensorCoreGemm *tc_gemm_prepare(const TcOperand &p, const TcOperand &q, int64_t 
         // a workspace and are added in a fixed order by a second kernel.
         if (may_slice) {
             double best = 1e30;
-            for (int sl = 1; sl <= 4; sl++) {
+            // A product of at most one wave cannot rebalance when another kernel (an all-reduce) holds some of
+            // the SMs: its tiles then take two waves.  Cut into slices it has units to spare (fine_units).
+            const int first = (fine_units && pair_tiles <= pairs && g->k_blocks >= 128) ? 2 : 1;
+            for (int sl = first; sl <= 4; sl++) {
                 const int per = (g->k_blocks + sl - 1) / sl;
-                if (sl > 1 && per < 64) break;                  // slices shorter than 2048 steps do not pay for their epilogue
+                if (sl > first && per < 64) break;              // slices shorter than 2048 steps do not pay for their epilogue
                 const int64_t units = pair_tiles * ((g->k_blocks + per - 1) / per);
                 const int64_t waves = (units + pairs - 1) / pairs;
                 const double cost = (double)waves * per * (1.0 + 0.02 * (sl - 1));

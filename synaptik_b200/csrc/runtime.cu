@@ -421,7 +421,7 @@ int32_t prepare_executable(Executable *x) {
             ob.hi = B.hi; ob.lo = B.lo; ob.pitch = B.pitch; ob.mn_major = se.orient_b == 0;
             int status = OK;
             const bool plain = st.bias < 0 && st.mask < 0 && !st.relu && !st.act && st.out2 < 0;
-            const int mode = ctx->gemm_promote | (ctx->gemm_pair << 1) | ((plain && ctx->gemm_slices) ? 4 : 0) | ((ctx->gemm_chunk / 32) << 8);
+            const int mode = ctx->gemm_promote | (ctx->gemm_pair << 1) | ((plain && ctx->gemm_slices) ? 4 : 0) | ((plain && ctx->gemm_slices == 2) ? 8 : 0) | ((ctx->gemm_chunk / 32) << 8);
             se.tc = se.swapped ? kern::tc_gemm_prepare(ob, oa, st.n, st.m, st.k, ctx->sm_count, mode, &status)
                                : kern::tc_gemm_prepare(oa, ob, st.m, st.n, st.k, ctx->sm_count, mode, &status);
             if (se.tc) workspace_floats = std::max(workspace_floats, kern::tc_gemm_workspace_floats(se.tc));
@@ -830,7 +830,7 @@ int32_t synaptik_cuda_context_set_option(void *context, const char *name, int64_
     if (!ctx || !name) return INVALID_ARGUMENT;
     if (!strcmp(name, "gemm_engine")) { if (value < 0 || value > 2) return INVALID_ARGUMENT; ctx->gemm_engine = (int)value; return OK; }
     if (!strcmp(name, "gemm_dynamic")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->gemm_dynamic = (int)value; return OK; }
-    if (!strcmp(name, "gemm_slices")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->gemm_slices = (int)value; return OK; }
+    if (!strcmp(name, "gemm_slices")) { if (value < 0 || value > 2) return INVALID_ARGUMENT; ctx->gemm_slices = (int)value; return OK; }
     if (!strcmp(name, "gemm_pair")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->gemm_pair = (int)value; return OK; }
     if (!strcmp(name, "gemm_chunk")) { if (value < 0 || value > 4096 || value % 32) return INVALID_ARGUMENT; ctx->gemm_chunk = (int)value; return OK; }
     if (!strcmp(name, "gemm_promote")) { if (value < 0 || value > 1) return INVALID_ARGUMENT; ctx->gemm_promote = (int)value; return OK; }
