@@ -290,7 +290,13 @@ def run_cuda(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # experiment hook: SYNAPTIK_BENCH_OCCUPY="blocks,microseconds" puts a co-tenant on the communication stream
+    # at the start of every resident step (blocks that each hold one SM for that long, as a collective's do)
+    cotenant = [int(v) for v in os.environ.get("SYNAPTIK_BENCH_OCCUPY", "0,0").split(",")]
+
     def resident_step():
+        if cotenant[0] > 0:
+            ctx.occupy(cotenant[0], cotenant[1])
         exe.enqueue(inputs, outputs)
         optimizer.step_enqueue(grads)
 

@@ -103,6 +103,12 @@ SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_timer_stop(void *context, double
  * `limit_microseconds` (1 .. 2000000), and reports the outcome like a run would: it returns
  * SYNAPTIK_CUDA_STATUS_TIMEOUT, never OK, and the context is as usable afterwards as before. */
 SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_wait_probe(void *context, uint64_t limit_microseconds);
+/* Measurement and test instrument (no counterpart in the reference): enqueues, on the context's
+ * communication stream, `blocks` thread blocks (0 .. the SM count) that each hold one SM for
+ * `hold_microseconds` (at most 100000) and then end by themselves, the way the blocks of an all-reduce
+ * hold SMs while the backward pass runs.  Returns at once.  With it one GPU shows how the tensor-core
+ * products give way to a co-tenant: their results must not change, only their duration. */
+SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_occupy(void *context, int32_t blocks, uint64_t hold_microseconds);
 
 /* ---- buffers: replace synaptik_metal_buffer_create / _release / _upload / _download ----------
  * Device-resident linear memory.  upload/download move raw little-endian element bytes and
@@ -244,7 +250,10 @@ SYNAPTIK_CUDA_API int32_t synaptik_cuda_optimizer_set_progress(void *optimizer, 
  * attached communicator sum-allreduces the listed publications (gradients) on the context's
  * communication stream as soon as each is final, overlapping the rest of the backward pass, and
  * run/finish return after the reductions.  attach_comm refuses (INCOMPATIBLE_RESOURCE) a publication
- * that a later step of the same executable still reads.  The host never waits for a collective without
+ * that a later step of the same executable still reads.  It waits for the executable's runs in flight and
+ * plans tensor-core products of at most one tile per SM pair again with their contraction in slices (see
+ * "gemm_slices"), because a single wave of tiles cannot give way to the collective's blocks; such a product's
+ * sums then round differently than without a communicator, within the same bound.  The host never waits for a collective without
  * a limit: finish, run and comm_allreduce_sum_f32 poll NCCL's asynchronous error state and, after the
  * context option "comm_timeout_ms", mark the steps in flight as failed, abort the communicator and
  * return COMM_FAILED; the communicator is unusable from then on (every call on it returns

@@ -112,6 +112,8 @@ cudaError_t accumulate_gradients(cudaStream_t s, const TensorSlot *slots, int sl
 // limit_ns and the kernel sets ERR_WAIT_TIMEOUT and returns normally.  It runs the same wait routine as
 // the tensor-core GEMMs, whose limit is fixed at two seconds.
 cudaError_t wait_probe(cudaStream_t s, uint64_t limit_ns, int *error_word);
+// `blocks` blocks that each hold one SM (all of its shared memory) for `hold_ns`, then end by themselves.
+cudaError_t occupy(cudaStream_t s, int blocks, uint64_t hold_ns);
 
 // ---- GEMM -------------------------------------------------------------------------------------
 struct GemmEpilogue {
@@ -173,6 +175,9 @@ int tc_gemm_launches(const TensorCoreGemm *g);
 // The product's write-out goes through shared memory and TMA stores (two-SM kernel, unsliced, 16-byte rows)
 // when its result arrays are 16-byte aligned: further arrays written from the epilogue are then cheap.
 bool tc_gemm_staged_shape(const TensorCoreGemm *g);
+// A two-SM product, not cut into slices, whose tiles are at most one per SM pair: it cannot rebalance when
+// another kernel holds some of the SMs.
+bool tc_gemm_single_wave(const TensorCoreGemm *g);
 // unit_counter (optional, two-SM products only): a device int that is zero when the kernel starts; the
 // pairs then take their tiles from it one by one instead of by a fixed assignment.
 cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, int64_t ldd, const GemmEpilogue &ep, float *workspace,

@@ -1879,6 +1879,23 @@ cudaError_t gemm_exact(cudaStream_t s, int64_t m, int64_t n, int64_t k, const fl
     return cudaGetLastError();
 }
 
+// Holds SMs the way a collective's blocks do: `blocks` blocks of 1024 threads that each take a whole SM's
+// shared memory and sleep until `hold_ns` have passed on the global timer.  No flag, no peer: it ends by itself.
+__global__ void __launch_bounds__(1024) occupy_kernel(uint64_t hold_ns) {
+    extern __shared__ uint8_t held[];
+    const uint64_t start = global_timer();
+    while (global_timer() - start < hold_ns) __nanosleep(2000);
+    if (hold_ns == ~0ull) held[threadIdx.x] = 0;        // keeps the allocation; never true
+}
+cudaError_t occupy(cudaStream_t s, int blocks, uint64_t hold_ns) {
+    if (blocks < 1) return cudaSuccess;
+    const int smem = 200 * 1024;
+    cudaError_t e = cudaFuncSetAttribute(occupy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    occupy_kernel<<<blocks, 1024, smem, s>>>(hold_ns);
+    return cudaGetLastError();
+}
+
 cudaError_t wait_probe(cudaStream_t s, uint64_t limit_ns, int *error_word) {
     // never longer than the GEMM kernels' own limit
     wait_probe_kernel<<<1, 32, 0, s>>>(limit_ns < WAIT_LIMIT_NS ? limit_ns : WAIT_LIMIT_NS, error_word);
@@ -1925,6 +1942,7 @@ struct TensorCoreGemm {
     int p_mn, q_mn;
     int slices, kb_per_slice; int64_t slice_ld;
     int group_n;
+    bool single_wave = false;               // two-SM product whose tiles are at most one per SM pair
     // tensor maps of the staged write-out, encoded when the result arrays change (they rarely do)
     mutable StoreMaps stores;
     mutable const void *stored_for[4] = {nullptr, nullptr, nullptr, nullptr};
@@ -2033,6 +2051,7 @@ TensorCoreGemm *tc_gemm_prepare(const TcOperand &p, const TcOperand &q, int64_t 
             }
         }
         const int64_t units = pair_tiles * g->slices;
+        g->single_wave = pair_tiles <= pairs;
         g->grid = (int)(2 * (units < pairs ? units : pairs));
         // tile columns per group: about eight, spread evenly, so that the 74 concurrent tiles form a
         // near-square patch (9 row bands x 8 columns) whatever the contraction length.  Measured on the
@@ -2130,6 +2149,7 @@ cudaError_t tc_gemm_launch(cudaStream_t s, const TensorCoreGemm *g, float *d, in
     return cudaGetLastError();
 }
 int tc_gemm_launches(const TensorCoreGemm *g) { return g->slices > 1 ? 2 : 1; }
+bool tc_gemm_single_wave(const TensorCoreGemm *g) { return g->pair && g->slices == 1 && g->single_wave; }
 bool tc_gemm_staged_shape(const TensorCoreGemm *g) { return staged_enabled() && g->pair && g->slices == 1 && (g->n & 3) == 0; }
 
 // ---- 16-bit storage ------------------------------------------------------------------------------

@@ -29,6 +29,7 @@ SYMBOLS = [
     "synaptik_cuda_abi_version", "synaptik_cuda_context_create", "synaptik_cuda_context_release",
     "synaptik_cuda_context_set_option", "synaptik_cuda_context_synchronize",
     "synaptik_cuda_context_timer_start", "synaptik_cuda_context_timer_stop", "synaptik_cuda_context_wait_probe",
+    "synaptik_cuda_context_occupy",
     "synaptik_cuda_executable_describe", "synaptik_cuda_executable_step_timings",
     "synaptik_cuda_buffer_create", "synaptik_cuda_buffer_release", "synaptik_cuda_buffer_upload",
     "synaptik_cuda_buffer_download", "synaptik_cuda_buffer_upload_canonical",
@@ -111,6 +112,10 @@ class Context:
     def wait_probe(self, limit_microseconds: int) -> None:
         """Runs the give-up path of the device-side bounded waits; always raises NativeFailure(14)."""
         _check("context_wait_probe", library().synaptik_cuda_context_wait_probe(self._h, ctypes.c_uint64(limit_microseconds)))
+
+    def occupy(self, blocks: int, hold_microseconds: int) -> None:
+        """Enqueues `blocks` blocks on the communication stream that each hold one SM for the given time."""
+        _check("context_occupy", library().synaptik_cuda_context_occupy(self._h, ctypes.c_int32(blocks), ctypes.c_uint64(hold_microseconds)))
 
     def buffer(self, nbytes: int) -> "Buffer":
         return Buffer(self, nbytes)

@@ -287,3 +287,68 @@ def test_a_collective_that_never_answers_ends_with_comm_failed(tmp_path, async_e
                SYN_EXPECT_WITHIN="1.4" if async_error == "0" else "0.25")
     done = subprocess.run([sys.executable, str(script)], env=env, capture_output=True, text=True, timeout=300)
     assert done.returncode == 0 and "ok" in done.stdout, done.stdout + done.stderr
+
+
+def test_products_give_way_to_a_co_tenant_without_changing_their_result(ctx):
+    """While other blocks hold a third of the SMs (as a collective's do), the two-SM kernel's pairs take fewer
+    tiles each; the product must come out bit for bit as on a free GPU."""
+    from synaptik_b200.program import GraphBuilder, F32
+    rng = np.random.default_rng(11)
+    m, k, n = 4096, 1024, 2048
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    w = rng.standard_normal((n, k)).astype(np.float32)
+    g = GraphBuilder()
+    xv, wv = g.feed(F32, (m, k)), g.feed(F32, (n, k))
+    g.publish(g.linear(xv, wv, None)[1])
+    ctx.set_option("gemm_engine", 2)
+    try:
+        exe = native.Executable(ctx, g.build())
+    finally:
+        ctx.set_option("gemm_engine", 0)
+    assert "tcgen05" in exe.describe()
+    feeds = [ctx.buffer(a.nbytes) for a in (x, w)]
+    for b, a in zip(feeds, (x, w)):
+        b.upload(a)
+    out = ctx.buffer(m * n * 4)
+    exe.run(feeds, [out])
+    free = out.download(np.float32, (m, n)).copy()
+    for blocks in (16, 48, 100):
+        ctx.occupy(blocks, 20000)                   # 20 ms: longer than the product
+        exe.run(feeds, [out])
+        assert np.array_equal(out.download(np.float32, (m, n)), free), blocks
+    ctx.synchronize()
+    exe.close()
+
+
+def test_a_single_wave_weight_gradient_is_planned_again_in_slices_under_a_communicator(ctx):
+    """A product of at most one tile per SM pair cannot give way to a collective's blocks; attaching a communicator
+    plans it again with its contraction in slices (one more launch: the kernel that adds the slices)."""
+    import torch  # noqa: F401  (brings the process's NCCL with it)
+    try:
+        comm = native.Comm(ctx, 1, 0, native.comm_unique_id())
+    except native.NativeFailure:
+        pytest.skip("no NCCL in this process")
+    rows, k, n = 4096, 784, 4096
+    rng = np.random.default_rng(12)
+    x = rng.uniform(0, 1, (rows, k)).astype(np.float32)
+    dz = rng.standard_normal((rows, n)).astype(np.float32)
+    g = GraphBuilder()
+    xv, dzv = g.feed(F32, (rows, k)), g.feed(F32, (rows, n))
+    g.publish(g.matmul(g.permute(xv, (1, 0)), dzv))                 # [k, n]: 4 x 16 tiles of 256 x 256 on 74 pairs
+    ctx.set_option("gemm_engine", 2)
+    try:
+        exe = native.Executable(ctx, g.build())
+    finally:
+        ctx.set_option("gemm_engine", 0)
+    feeds, out = [ctx.upload(x), ctx.upload(dz)], ctx.buffer(k * n * 4)
+    exe.run(feeds, [out])
+    whole, launches = out.download(np.float32, (k, n)).copy(), exe.launch_count()
+    exe.attach_comm(comm, [0])
+    exe.run(feeds, [out])
+    sliced = out.download(np.float32, (k, n))
+    assert exe.launch_count() == launches + 1
+    ref = x.astype(np.float64).T @ dz.astype(np.float64)
+    bound = (8 + 512 / 4) * 2.0 ** -24 * (np.abs(x.astype(np.float64)).T @ np.abs(dz.astype(np.float64)))
+    assert np.all(np.abs(sliced - ref) <= bound) and np.all(np.abs(whole - ref) <= bound)
+    exe.attach_comm(None)
+    exe.close(); comm.close()
