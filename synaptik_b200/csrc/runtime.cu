@@ -1484,7 +1484,7 @@ int32_t synaptik_cuda_executable_attach_comm(void *executable, void *comm, int32
         bool synced = false;
         for (size_t i = 0; i < x->exec.size(); i++) {
             StepExec &se = x->exec[i];
-            if (!se.tc || !se.tc_plain || !kern::tc_gemm_single_wave(se.tc)) continue;
+            if (!se.tc || !se.tc_plain || se.emit_planes >= 0 || !kern::tc_gemm_single_wave(se.tc)) continue;    // (a sliced product has no epilogue to write planes from)
             int status = OK;
             kern::TensorCoreGemm *again = kern::tc_gemm_prepare(se.tc_p, se.tc_q, se.tc_m, se.tc_n, x->plan.steps[i].k, x->ctx->sm_count, se.tc_mode | 4 | 8, &status);
             if (!again) continue;
