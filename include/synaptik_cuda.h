@@ -74,7 +74,7 @@ SYNAPTIK_CUDA_API int32_t synaptik_cuda_context_release(void *context);
  * whole contraction (faster epilogue, error grows with K).  "gemm_chunk": contraction steps per
  * tensor-memory partial sum of executables created afterwards, a multiple of 32, 0 (default) = 512 (256
  * from K = 8192 on); shorter partial sums are more exact and slower (128: a quarter of the error, about
- * 10 % more time on the 4096-wide layers).  "gemm_pair": 1 (default) = products with
+ * 6 % more time on the 4096-wide layers).  "gemm_pair": 1 (default) = products with
  * at least 256 rows use two-SM tiles (clusters of two blocks, tcgen05 cta_group::2); 0 = one-SM tiles
  * only.  "gemm_slices": 1 (default) = a two-SM product without epilogue work (a weight gradient) may
  * split its contraction into up to four slices when that shortens the last wave of the persistent
